@@ -1,0 +1,146 @@
+"""The batch of one step: what runs, described once on the host and copied to the
+device in a single transfer.
+
+A step is a list of entries, one per request taking part: its next tokens (a
+portion of its prompt or a single decoded token), the position of the first of
+them, which of them want logits, its block table in every cache group and its
+state slot.  ``StepContext.pack`` flattens the entries along one token axis and
+lays all integer arrays out in one pinned host buffer:
+
+  token_ids[T] positions[T] seq_of_token[T] cu_q[S+1] ctx_len[S] state_slots[S]
+  logit_rows[R] block_tables[group][S, max_pages] ...
+
+Parts read these through the context (see ``parts/base.py``).  Reference
+analogue: the per-step Python lists and ``SeqMeta(offset, q_len, ctx_len,
+block_table)`` built by the engine (servelab/engine/engine.py:176-215); the flat
+``slots`` array is replaced by a block-table lookup on the device.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+
+@dataclass
+class BatchEntry:
+    """One request's share of a step."""
+    tokens: Sequence[int]
+    start: int                                   # position of tokens[0]
+    want: Sequence[int] = ()                     # indices into ``tokens`` whose logits are wanted
+    block_tables: Sequence[Sequence[int]] = ()   # one table per cache group
+    state_slot: int = 0
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class StepContext:
+    """Device-side view of a step plus a few host-side facts about it."""
+
+    def __init__(self, device: str):
+        self.device = device
+        self.num_tokens = 0
+        self.num_seqs = 0
+        self.num_logit_rows = 0
+        self.q_lens: List[int] = []
+        self.ctx_lens: List[int] = []
+        self.decode_only = False
+        self.max_ctx_len = 0
+        self.token_ids = self.positions = self.seq_of_token = None
+        self.cu_q = self.ctx_len = self.state_slots = self.logit_rows = None
+        self.block_tables: List[torch.Tensor] = []
+        self._tiles: Dict[Tuple[int, int], Tuple[torch.Tensor, torch.Tensor, int]] = {}
+        self.scratch: Dict[str, torch.Tensor] = {}   # per-step scratch parts may share
+
+    # ------------------------------------------------------------ packing
+    @classmethod
+    def pack(cls, entries: Sequence[BatchEntry], num_groups: int, device: str,
+             min_table_width: int = 1) -> "StepContext":
+        ctx = cls(device)
+        S = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        T = sum(q_lens)
+        want_rows: List[int] = []
+        off = 0
+        for e, n in zip(entries, q_lens):
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"wanted index {w} outside the entry's {n} tokens")
+                want_rows.append(off + w)
+            off += n
+        R = len(want_rows)
+        widths = []
+        for g in range(num_groups):
+            widths.append(max([min_table_width] + [len(e.block_tables[g]) for e in entries]))
+
+        sizes = [T, T, T, S + 1, S, S, R] + [S * w for w in widths]
+        offsets, total = [], 0
+        for n in sizes:
+            offsets.append(total)
+            total += _align4(max(n, 1))
+        host = torch.empty(total, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        hv = host.numpy()
+        hv[:] = 0
+        o_tok, o_pos, o_seq, o_cu, o_ctx, o_slot, o_rows = offsets[:7]
+        t = 0
+        hv[o_cu] = 0
+        for s, (e, n) in enumerate(zip(entries, q_lens)):
+            hv[o_tok + t:o_tok + t + n] = e.tokens
+            hv[o_pos + t:o_pos + t + n] = range(e.start, e.start + n)
+            hv[o_seq + t:o_seq + t + n] = s
+            t += n
+            hv[o_cu + s + 1] = t
+            hv[o_ctx + s] = e.start + n
+            hv[o_slot + s] = e.state_slot
+        hv[o_rows:o_rows + R] = want_rows
+        for g, w in enumerate(widths):
+            base = offsets[7 + g]
+            tab = hv[base:base + S * w].reshape(S, w) if S else None
+            if tab is not None:
+                tab[:] = -1
+                for s, e in enumerate(entries):
+                    row = e.block_tables[g]
+                    tab[s, :len(row)] = row
+        dev = host.to(device, non_blocking=True)
+        ctx._host = host                              # keep the pinned buffer alive
+
+        def view(o, n):
+            return dev[o:o + n]
+        ctx.token_ids, ctx.positions, ctx.seq_of_token = view(o_tok, T), view(o_pos, T), view(o_seq, T)
+        ctx.cu_q, ctx.ctx_len = view(o_cu, S + 1), view(o_ctx, S)
+        ctx.state_slots, ctx.logit_rows = view(o_slot, S), view(o_rows, R)
+        ctx.block_tables = [dev[offsets[7 + g]:offsets[7 + g] + S * w].view(S, w)
+                            for g, w in enumerate(widths)]
+        ctx.num_tokens, ctx.num_seqs, ctx.num_logit_rows = T, S, R
+        ctx.q_lens = q_lens
+        ctx.ctx_lens = [e.start + n for e, n in zip(entries, q_lens)]
+        ctx.max_ctx_len = max(ctx.ctx_lens) if ctx.ctx_lens else 0
+        ctx.decode_only = S > 0 and all(n == 1 for n in q_lens)
+        return ctx
+
+    # ------------------------------------------------- attention work list
+    def attention_tiles(self, group_size: int, rows_per_tile: int):
+        """Tiles of ``rows_per_tile`` query rows over each request's q_len *
+        group_size flattened rows: (tile_seq, tile_row0, count) on the device."""
+        key = (group_size, rows_per_tile)
+        hit = self._tiles.get(key)
+        if hit is None:
+            seqs, row0s = [], []
+            for s, n in enumerate(self.q_lens):
+                rows = n * group_size
+                for r0 in range(0, rows, rows_per_tile):
+                    seqs.append(s)
+                    row0s.append(r0)
+            n_tiles = len(seqs)
+            host = torch.tensor(seqs + row0s, dtype=torch.int32)
+            if torch.cuda.is_available():
+                host = host.pin_memory()
+            dev = host.to(self.device, non_blocking=True)
+            hit = (dev[:n_tiles], dev[n_tiles:], n_tiles)
+            self._tiles[key] = hit
+            self.scratch[f"_tiles_host_{key}"] = host
+        return hit

@@ -1,0 +1,90 @@
+"""The step function: runs a batch of (request, its next tokens) from the cache.
+
+``ModelRunner`` owns the model, the device cache and the cache manager.  Its
+``step(entries)`` takes any mix of prompt portions and single decoded tokens, cut
+anywhere, runs exactly those tokens as one batch against what earlier steps left
+in the cache, and returns float32 logits at the wanted places.  Generation
+(``LLMEngine``), trace replay (``bin/trace_run``) and the benchmark all drive this
+one function.  Reference analogue: the packing and forward part of
+``LLMEngine.step`` (servelab/engine/engine.py:183-218).
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.storage import CacheStorage, pages_from_memory, plan_groups
+from ..config.engine import CacheConfig
+from ..config.registry import load_config
+from ..models.causal_lm import CausalLM
+from ..ops import kernels as K
+from ..parts import BuildEnv
+from ..weights.source import FolderSource, WeightSource
+from .batch import BatchEntry, StepContext
+
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class ModelRunner:
+    def __init__(self, config, weights: WeightSource, dtype: str = "bfloat16",
+                 cache_config: Optional[CacheConfig] = None, max_num_seqs: int = 64,
+                 device: str = "cuda:0"):
+        K.require_cuda()
+        if dtype not in _DTYPES:
+            raise ValueError(f"dtype must be bfloat16 or float32, got {dtype}")
+        self.config = config
+        self.device = device
+        self.dtype = _DTYPES[dtype]
+        cache_config = cache_config or CacheConfig()
+        self.page_size = cache_config.block_size
+        self.spec = config.to_model_spec()
+        torch.cuda.set_device(device)
+        env = BuildEnv(device=device, dtype=self.dtype, page_size=self.page_size)
+        self.model = CausalLM(self.spec, env)
+        with torch.no_grad():
+            self.model.load(weights)
+        requests = self.model.cache_requests()
+        groups, _ = plan_groups(requests)
+        num_pages = cache_config.num_blocks
+        if num_pages is None:
+            torch.cuda.synchronize()
+            free_bytes = torch.cuda.mem_get_info()[0]
+            num_pages = pages_from_memory(groups, self.page_size, self.dtype, free_bytes,
+                                          cache_config.gpu_memory_utilization)
+        self.num_pages = num_pages
+        self.storage = CacheStorage(requests, num_pages, self.page_size, max_num_seqs, self.dtype,
+                                    device)
+        self.cache = CacheManager(self.storage.group_windows, num_pages, self.page_size,
+                                  max_num_seqs, reserve_pages=cache_config.reserve_blocks)
+        self.num_groups = len(self.storage.groups)
+
+    @classmethod
+    def from_folder(cls, folder: str, **kw) -> "ModelRunner":
+        return cls(load_config(folder), FolderSource(folder), **kw)
+
+    # ---------------------------------------------------------------- step
+    def entry(self, request_id: str, tokens: Sequence[int], start: int,
+              want: Sequence[int] = ()) -> BatchEntry:
+        """A batch entry with the request's current block tables and state slot."""
+        return BatchEntry(tokens=tokens, start=start, want=want,
+                          block_tables=[self.cache.block_table(request_id, g)
+                                        for g in range(self.num_groups)],
+                          state_slot=self.cache.state_slot(request_id))
+
+    def check_tokens(self, tokens: Sequence[int]) -> None:
+        v = self.spec.vocab_size
+        for t in tokens:
+            if not 0 <= t < v:
+                raise ValueError(f"token id {t} outside the vocabulary [0, {v})")
+
+    @torch.no_grad()
+    def step(self, entries: List[BatchEntry]) -> torch.Tensor:
+        """Logits [wanted, vocab] float32 (on the device) of this batch."""
+        self.storage.clear_state_slots(self.cache.slots.drain_to_clear())
+        ctx = StepContext.pack(entries, self.num_groups, self.device)
+        if ctx.num_tokens == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        return self.model.forward(ctx, self.storage.layer_caches)

@@ -1,0 +1,136 @@
+"""Python entry points of the CUDA kernels (thin: pointer passing, no math).
+
+Every function launches on torch's current CUDA stream and returns without
+synchronising.  Tensors must be CUDA tensors, contiguous in their last dimension.
+The dtype of the activations selects the float32 or the bfloat16 instance.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import library as L
+
+_F32, _BF16 = torch.float32, torch.bfloat16
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _suffix(dt: torch.dtype) -> str:
+    if dt == _F32:
+        return "f32"
+    if dt == _BF16:
+        return "bf16"
+    raise L.KernelError(f"kernels take float32 or bfloat16, not {dt}")
+
+
+def require_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise L.KernelsUnavailable(
+            "servelab_b200 needs a CUDA device (sm_100a): there is no CPU path")
+    L.core()
+
+
+# ------------------------------------------------------------- elementwise
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = table[ids[t]] as float32; ids int32 [T], out float32 [T, h]."""
+    fn = getattr(L.core(), "slb_embedding_" + _suffix(table.dtype))
+    L.check(fn(ids.data_ptr(), table.data_ptr(), out.data_ptr(), ids.numel(), table.shape[1],
+               table.shape[0], _stream()), "embedding")
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                eps: float, out: torch.Tensor, row_map: Optional[torch.Tensor] = None) -> None:
+    """resid += delta (in place, float32; skipped when ``row_map`` selects rows);
+    out[r] = rmsnorm(resid[src(r)] (+ delta)) * weight."""
+    rows = out.shape[0]
+    fn = getattr(L.core(), "slb_add_rmsnorm_" + _suffix(out.dtype))
+    L.check(fn(resid.data_ptr(), _p(delta), weight.data_ptr(), out.data_ptr(), _p(row_map),
+               rows, out.shape[1], float(eps), _stream()), "add_rmsnorm")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i], I = out.shape[1]."""
+    fn = getattr(L.core(), "slb_swiglu_" + _suffix(out.dtype))
+    L.check(fn(gate_up.data_ptr(), out.data_ptr(), out.shape[0], out.shape[1],
+               gate_up.stride(0), out.stride(0), _stream()), "swiglu")
+
+
+# ----------------------------------------------------- rotary + cache write
+def qkv_rope_cache(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
+                   seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                   inv_freq: Optional[torch.Tensor], rotary_dim: int, q_out: torch.Tensor,
+                   k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                   num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+    fn = getattr(L.core(), "slb_qkv_rope_cache_" + _suffix(qkv.dtype))
+    L.check(fn(qkv.data_ptr(), qkv.stride(0), _p(bias), positions.data_ptr(),
+               seq_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size,
+               _p(inv_freq), rotary_dim, q_out.data_ptr(), q_out.stride(0), _p(k_cache),
+               _p(v_cache), qkv.shape[0], num_heads, num_kv_heads, head_dim, _stream()),
+            "qkv_rope_cache")
+
+
+# ---------------------------------------------------------------- attention
+def generic_attention_tile_rows() -> int:
+    return L.core().slb_paged_attention_generic_tile_rows()
+
+
+def paged_attention_generic(q, k_cache, v_cache, out, block_table, cu_q, ctx_len, tile_seq,
+                            tile_row0, num_tiles: int, num_heads: int, num_kv_heads: int,
+                            head_dim: int, page_size: int, scale: float, window: int) -> None:
+    fn = getattr(L.core(), "slb_paged_attention_generic_" + _suffix(q.dtype))
+    L.check(fn(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+               out.stride(0), block_table.data_ptr(), block_table.shape[1], cu_q.data_ptr(),
+               ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), num_tiles,
+               num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window),
+               _stream()), "paged_attention_generic")
+
+
+# ---------------------------------------------------------- matrix products
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+              bias: Optional[torch.Tensor] = None) -> None:
+    """out[M,N] = a[M,K] . w[N,K]^T (+ bias) on CUDA cores, float32 accumulation."""
+    M, K = a.shape
+    N = w.shape[0]
+    if a.dtype == _F32 and out.dtype == _F32:
+        fn = L.core().slb_gemm_simt_f32
+    elif a.dtype == _BF16 and out.dtype == _BF16:
+        fn = L.core().slb_gemm_simt_bf16
+    elif a.dtype == _BF16 and out.dtype == _F32:
+        fn = L.core().slb_gemm_simt_bf16_f32out
+    else:
+        raise L.KernelError(f"gemm_simt: unsupported dtypes {a.dtype} -> {out.dtype}")
+    L.check(fn(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
+               out.stride(0), _p(bias), M, N, K, _stream()), "gemm_simt")
+
+
+# ----------------------------------------------------------------- sampling
+def sample_rows(logits: torch.Tensor, out: torch.Tensor, temperature=None, top_k=None,
+                top_p=None, seed=None, stream=None, position=None) -> None:
+    """out[r] = sampled token of row r; all per-row parameter arrays live on the
+    device (float32 / int32 / int64); ``temperature=None`` means greedy rows."""
+    R, V = logits.shape
+    L.check(L.core().slb_sample_rows(
+        logits.data_ptr(), logits.stride(0), R, V, _p(temperature), _p(top_k), _p(top_p),
+        _p(seed), _p(stream), _p(position), out.data_ptr(), _stream()), "sample_rows")
+
+
+# ------------------------------------------- optional fast kernels (bfloat16)
+def has_decode_attention(head_dim: int, group: int) -> bool:
+    return False
+
+
+def has_prefill_attention(head_dim: int) -> bool:
+    return False
+
+
+def gemm_skinny(x, w, out, bias=None) -> None:
+    raise L.KernelError("gemm_skinny is not built")

@@ -1,0 +1,109 @@
+"""Loads the compiled kernel libraries and declares their C signatures.
+
+The kernels are the only implementation of their operations: there is no CPU or
+framework fallback.  If the library cannot be built or loaded, or no CUDA device
+is present, the first use raises ``KernelsUnavailable``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from typing import Dict
+
+from ..csrc import build as _build
+
+
+class KernelsUnavailable(RuntimeError):
+    pass
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+P, I, F = c_void_p, c_int, c_float
+
+_CORE_SIGNATURES = {
+    "slb_embedding_f32": [P, P, P, I, I, I, P],
+    "slb_embedding_bf16": [P, P, P, I, I, I, P],
+    "slb_add_rmsnorm_f32": [P, P, P, P, P, I, I, F, P],
+    "slb_add_rmsnorm_bf16": [P, P, P, P, P, I, I, F, P],
+    "slb_swiglu_f32": [P, P, I, I, I, I, P],
+    "slb_swiglu_bf16": [P, P, I, I, I, I, P],
+    "slb_qkv_rope_cache_f32": [P, I, P, P, P, P, I, I, P, I, P, I, P, P, I, I, I, I, P],
+    "slb_qkv_rope_cache_bf16": [P, I, P, P, P, P, I, I, P, I, P, I, P, P, I, I, I, I, P],
+    "slb_paged_attention_generic_f32": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, P],
+    "slb_paged_attention_generic_bf16": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, P],
+    "slb_paged_attention_generic_tile_rows": [],
+    "slb_gemm_simt_f32": [P, I, P, I, P, I, P, I, I, I, P],
+    "slb_gemm_simt_bf16": [P, I, P, I, P, I, P, I, I, I, P],
+    "slb_gemm_simt_bf16_f32out": [P, I, P, I, P, I, P, I, I, I, P],
+    "slb_sample_rows": [P, I, I, I, P, P, P, P, P, P, P, P],
+}
+
+# optional entry points: declared when the library exports them
+_OPTIONAL_SIGNATURES = {
+    "slb_decode_attention_bf16": [P, I, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
+    "slb_decode_attention_max_splits": [],
+    "slb_gemm_skinny_bf16": [P, I, P, I, P, I, P, P, I, I, I, I, P],
+}
+
+_libs: Dict[str, ctypes.CDLL] = {}
+
+
+def _declare(lib: ctypes.CDLL, sigs: dict, required: bool) -> None:
+    for name, args in sigs.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            if required:
+                raise KernelsUnavailable(f"kernel library lacks symbol {name}") from None
+            continue
+        fn.argtypes = args
+        fn.restype = c_int
+
+
+def core() -> ctypes.CDLL:
+    lib = _libs.get("core")
+    if lib is None:
+        try:
+            path = _build.ensure_library()
+            lib = ctypes.CDLL(path)
+        except (OSError, _build.BuildError) as e:
+            raise KernelsUnavailable(f"the servelab_b200 CUDA kernels are not available: {e}") from e
+        _declare(lib, _CORE_SIGNATURES, True)
+        _declare(lib, _OPTIONAL_SIGNATURES, False)
+        _libs["core"] = lib
+    return lib
+
+
+_ATTN_SIGNATURES = {
+    "slb_prefill_attention_bf16": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, F, I, P],
+    "slb_prefill_attention_tile_rows": [],
+    "slb_prefill_attention_head_dim": [],
+}
+
+
+def attention(head_dim: int) -> ctypes.CDLL:
+    key = f"attn{head_dim}"
+    lib = _libs.get(key)
+    if lib is None:
+        try:
+            lib = ctypes.CDLL(_build.attention_library(head_dim))
+        except (OSError, _build.BuildError) as e:
+            raise KernelsUnavailable(
+                f"the attention kernels for head size {head_dim} are not available: {e}") from e
+        _declare(lib, _ATTN_SIGNATURES, True)
+        _libs[key] = lib
+    return lib
+
+
+def check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == -1:
+        raise KernelError(f"{what}: arguments refused (a size or pointer the kernel does not take)")
+    if code == -2:
+        raise KernelError(f"{what}: a size is beyond the kernel's stated maximum")
+    raise KernelError(f"{what}: CUDA error {code} at launch")

@@ -1,0 +1,56 @@
+"""Matrix products y = x W^T (+ b) for weights stored [out, in].
+
+float32: always this package's CUDA-core kernel (true 32-bit, fixed summation
+order per output).  bfloat16: the vendor library's tensor-core GEMM through
+torch (the reference's engine also calls a library for its products,
+servelab/parallel/tp_model.py:48-53), except for shapes whose rows are not
+16-byte aligned, which go to the CUDA-core kernel, and for small token counts,
+which go to this package's weight-streaming kernel when it is present.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import kernels as K
+from . import library as L
+
+_SKINNY_MAX_M = 16
+use_skinny = True          # switch for measurements
+
+
+def _skinny_ok(x, w, M):
+    return (use_skinny and M <= _SKINNY_MAX_M and hasattr(L.core(), "slb_gemm_skinny_bf16")
+            and w.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    M, Kd = x.shape
+    N = w.shape[0]
+    out_dtype = out_dtype or x.dtype
+    if x.dtype == torch.float32:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        K.gemm_simt(x, w, out, bias)
+        return out
+    # bfloat16 activations
+    if M == 0:
+        return torch.empty((0, N), dtype=out_dtype, device=x.device)
+    if _skinny_ok(x, w, M):
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        K.gemm_skinny(x, w, out, bias)
+        return out
+    if Kd % 8 or N % 8:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        K.gemm_simt(x, w, out, bias)
+        return out
+    if out_dtype == torch.float32:
+        out = torch.mm(x, w.t(), out_dtype=torch.float32)
+        if bias is not None:
+            out += bias
+        return out
+    if bias is not None:
+        return torch.addmm(bias.to(x.dtype), x, w.t())
+    return torch.mm(x, w.t())

@@ -1,0 +1,85 @@
+"""Grouped-query softmax attention over the paged cache.
+
+Per step: one fused q|k|v product (weights concatenated at load), then one
+kernel that adds the q/k/v bias, rotates q and k by the token positions and
+writes k (rotated) and v into the request's pages, then attention of every query
+of the step over its request's cached keys (the step's own included), then the
+output projection.  Order and formulas: servelab/parallel/tp_model.py:48-53
+(projections with bias), :128-129 (rotation before the cache write), :136-157
+(scores * D^-1/2, causal mask, float32 softmax, P.V), :131 (bias-free output
+projection).  ``window`` limits the visible keys to the last w positions.
+
+Which attention kernel runs: float32 always takes the plain kernel; bfloat16
+takes the tensor-core kernels when they exist for the head size (decode kernel
+for steps of single tokens, prefill kernel otherwise) and the plain kernel else.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache.manager import PagedKVRequest
+from ..ops import attention as A
+from ..ops import kernels as K
+from ..ops.linear import linear
+from ..weights.source import BIAS, MATRIX, TensorDecl
+from .base import Mixer
+from .registry import POSITIONS, build_part, register_mixer
+
+
+@register_mixer("paged_attention")
+class PagedAttention(Mixer):
+    def __init__(self, spec, prefix, env):
+        super().__init__(spec, prefix, env)
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        self.position = build_part(POSITIONS, spec.position, prefix + ".rotary_emb", env)
+        self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(spec.head_dim)
+        self.q_size = spec.num_heads * spec.head_dim
+        self.kv_size = spec.num_kv_heads * spec.head_dim
+        A.check_supported(spec.head_dim, env.dtype)
+
+    @classmethod
+    def declare(cls, spec, prefix):
+        h, q, kv = spec.hidden_size, spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
+        out = [TensorDecl(prefix + ".q_proj.weight", (q, h), MATRIX),
+               TensorDecl(prefix + ".k_proj.weight", (kv, h), MATRIX),
+               TensorDecl(prefix + ".v_proj.weight", (kv, h), MATRIX),
+               TensorDecl(prefix + ".o_proj.weight", (h, q), MATRIX)]
+        if spec.qkv_bias:
+            out += [TensorDecl(prefix + ".q_proj.bias", (q,), BIAS),
+                    TensorDecl(prefix + ".k_proj.bias", (kv,), BIAS),
+                    TensorDecl(prefix + ".v_proj.bias", (kv,), BIAS)]
+        if spec.out_bias:
+            out.append(TensorDecl(prefix + ".o_proj.bias", (h,), BIAS))
+        return out
+
+    @classmethod
+    def cache_request(cls, spec):
+        return PagedKVRequest(spec.num_kv_heads, spec.head_dim, spec.window)
+
+    def load(self, store):
+        p = self.prefix
+        self.w_qkv = store.cat([p + ".q_proj.weight", p + ".k_proj.weight", p + ".v_proj.weight"])
+        self.b_qkv = (store.cat([p + ".q_proj.bias", p + ".k_proj.bias", p + ".v_proj.bias"])
+                      if self.spec.qkv_bias else None)
+        self.w_o = store.get(p + ".o_proj.weight")
+        self.b_o = store.get(p + ".o_proj.bias") if self.spec.out_bias else None
+
+    def forward(self, ctx, x, cache, owns_cache):
+        s = self.spec
+        T = x.shape[0]
+        qkv = linear(x, self.w_qkv)
+        q = torch.empty((T, self.q_size), dtype=x.dtype, device=x.device)
+        table = ctx.block_tables[cache.group]
+        rot = self.position.rotary_table()
+        inv_freq, rotary_dim = rot if rot is not None else (None, 0)
+        K.qkv_rope_cache(qkv, self.b_qkv, ctx.positions, ctx.seq_of_token, table, cache.page_size,
+                         inv_freq, rotary_dim, q, cache.k if owns_cache else None,
+                         cache.v if owns_cache else None, s.num_heads, s.num_kv_heads, s.head_dim)
+        out = torch.empty_like(q)
+        A.paged_attention(ctx, q, cache.k, cache.v, out, table, s.num_heads, s.num_kv_heads,
+                          s.head_dim, cache.page_size, self.scale, s.window or 0)
+        return linear(out, self.w_o, self.b_o)

@@ -1,0 +1,46 @@
+"""Arrangement of a layer's parts.
+
+``pre_norm``: x += mixer(norm1(x)); x += ff(norm2(x)) -- the order of the
+reference's layer body (servelab/parallel/tp_model.py:125-133).  The stream x is
+float32; an update that has not been added yet travels beside it so that the add
+happens inside the next norm kernel.
+"""
+
+from __future__ import annotations
+
+from .base import Block
+from .registry import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, build_part, part_class,
+                       register_block)
+
+
+@register_block("pre_norm")
+class PreNormBlock(Block):
+    def __init__(self, spec, prefix, env):
+        super().__init__(spec, prefix, env)
+        self.mixer_norm = build_part(NORMS, spec.mixer_norm, prefix + ".input_layernorm", env)
+        self.mixer = build_part(MIXERS, spec.mixer, prefix + ".self_attn", env)
+        self.ff_norm = build_part(NORMS, spec.ff_norm, prefix + ".post_attention_layernorm", env)
+        self.feed_forward = build_part(FEED_FORWARDS, spec.feed_forward, prefix + ".mlp", env)
+
+    @classmethod
+    def declare(cls, spec, prefix):
+        return (part_class(NORMS, spec.mixer_norm).declare(spec.mixer_norm, prefix + ".input_layernorm")
+                + part_class(MIXERS, spec.mixer).declare(spec.mixer, prefix + ".self_attn")
+                + part_class(NORMS, spec.ff_norm).declare(spec.ff_norm,
+                                                          prefix + ".post_attention_layernorm")
+                + part_class(FEED_FORWARDS, spec.feed_forward).declare(spec.feed_forward,
+                                                                       prefix + ".mlp"))
+
+    @classmethod
+    def cache_request(cls, spec):
+        return part_class(MIXERS, spec.mixer).cache_request(spec.mixer)
+
+    def load(self, store):
+        for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward):
+            p.load(store)
+
+    def forward(self, ctx, resid, delta, cache, owns_cache):
+        x = self.mixer_norm.forward(ctx, resid, delta)
+        a = self.mixer.forward(ctx, x, cache, owns_cache)
+        x = self.ff_norm.forward(ctx, resid, a)
+        return resid, self.feed_forward.forward(ctx, x)

@@ -1,0 +1,64 @@
+"""Device sampler: one kernel launch per step for all rows.
+
+Semantics of greedy / temperature / top-k / top-p follow the reference's
+``Sampler`` (servelab/engine/sampler.py:15-45).  Randomness differs on purpose:
+the reference consumes one host generator in batch order and re-seeds a
+per-request generator for every token (sampler.py:26-28); here each draw is a
+counter-based random number keyed by (seed, request stream, output position), so
+a request's tokens do not depend on what else is in the batch.  A request with
+``seed >= 0`` uses that seed with stream 0; others use the engine's seed and
+their own stream number.
+"""
+
+from __future__ import annotations
+
+import struct
+from typing import List, Sequence
+
+import torch
+
+from ..ops import kernels as K
+
+
+def _f2i(x: float) -> int:
+    return struct.unpack("<i", struct.pack("<f", x))[0]
+
+
+class Sampler:
+    def __init__(self, seed: int = 0, device: str = "cuda:0"):
+        self.seed = int(seed) & ((1 << 63) - 1)
+        self.device = device
+
+    def sample(self, logits: torch.Tensor, seqs: Sequence) -> List[int]:
+        """One token per row of ``logits`` [R, V]; ``seqs[r]`` supplies
+        ``sampling_params``, ``stream_id`` and ``num_output_tokens``."""
+        R = logits.shape[0]
+        if R == 0:
+            return []
+        out = torch.empty(R, dtype=torch.int32, device=self.device)
+        if all(s.sampling_params.temperature == 0.0 for s in seqs):
+            K.sample_rows(logits, out)
+            return out.tolist()
+        # [temperature | top_k | top_p | position | seed (2 words) | stream (2 words)]
+        words: List[int] = []
+        words += [_f2i(float(s.sampling_params.temperature)) for s in seqs]
+        words += [int(s.sampling_params.top_k) for s in seqs]
+        words += [_f2i(float(s.sampling_params.top_p)) for s in seqs]
+        words += [int(s.num_output_tokens) for s in seqs]
+        for s in seqs:
+            sd = s.sampling_params.seed if s.sampling_params.seed >= 0 else self.seed
+            words += [sd & 0xFFFFFFFF, (sd >> 32) & 0xFFFFFFFF]
+        for s in seqs:
+            st = 0 if s.sampling_params.seed >= 0 else int(s.stream_id)
+            words += [st & 0xFFFFFFFF, (st >> 32) & 0xFFFFFFFF]
+        host = torch.tensor([w - (1 << 32) if w >= (1 << 31) else w for w in words],
+                            dtype=torch.int32)
+        dev = host.to(self.device)
+        temp = dev[0:R].view(torch.float32)
+        top_k = dev[R:2 * R]
+        top_p = dev[2 * R:3 * R].view(torch.float32)
+        pos = dev[3 * R:4 * R]
+        seed = dev[4 * R:6 * R]
+        stream = dev[6 * R:8 * R]
+        K.sample_rows(logits, out, temp, top_k, top_p, seed, stream, pos)
+        return out.tolist()

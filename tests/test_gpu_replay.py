@@ -1,0 +1,137 @@
+"""Trace replay against the plain implementation: whole, bulk + tail, portions,
+mixed with page reuse -- in float32 and bfloat16, for three tiny configurations."""
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+# Largest absolute logit error allowed against the float32 plain implementation.
+# float32: rounding of a handful of float32 reductions.  bfloat16: inputs of
+# every matrix product and the cache are rounded to 8 bits of mantissa.
+TOL = {"float32": 1e-5, "bfloat16": 2e-2}
+LENGTHS = [70, 45, 97, 33, 58, 81]
+
+
+@pytest.fixture(scope="module", params=["A", "B", "C"])
+def model(request, tmp_path_factory):
+    cfg, seed, page = H.CONFIGS[request.param]
+    folder = str(tmp_path_factory.mktemp(f"tiny_{request.param}"))
+    H.make_model(folder, cfg, seed)
+    reqs = {f"r{i}": H.random_ids(n, cfg["vocab_size"], 100 * seed + i)
+            for i, n in enumerate(LENGTHS)}
+    ref = {rid: H.plain_logits(folder, ids) for rid, ids in reqs.items()}
+    return {"name": request.param, "cfg": cfg, "folder": folder, "page": page,
+            "requests": reqs, "ref": ref}
+
+
+def _session(model, dtype, max_tokens):
+    from servelab_b200.replay import TraceSession
+    return TraceSession(model["folder"], dtype, max_tokens, page_size=model["page"], max_live=4)
+
+
+def _check(model, dtype, steps, max_tokens=None):
+    sess = _session(model, dtype, max_tokens or H.peak_tokens(steps))
+    got = H.collect(steps, H.run_session(sess, steps), model["cfg"]["vocab_size"])
+    sess.cache.check_invariants()
+    assert not sess.held and all(p.num_free() == p.num_pages for p in sess.cache.pools)
+    worst = 0.0
+    for rid, ids in model["requests"].items():
+        if rid not in got:
+            continue
+        assert sorted(got[rid]) == list(range(len(ids))), f"{rid}: positions missing"
+        for pos in range(len(ids)):
+            err = float(np.abs(got[rid][pos] - model["ref"][rid][pos]).max())
+            assert np.isfinite(err)
+            assert err <= TOL[dtype], (f"config {model['name']} {dtype} request {rid}: first "
+                                       f"wrong position {pos} (err {err:.3e})")
+            worst = max(worst, err)
+    print(f"config {model['name']} {dtype}: worst abs logit error {worst:.3e}")
+    return got
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole(model, dtype):
+    _check(model, dtype, H.trace_whole(model["requests"]))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_bulk_then_tail(model, dtype):
+    _check(model, dtype, H.trace_bulk_tail(model["requests"]))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_portions(model, dtype):
+    _check(model, dtype, H.trace_portions(model["requests"]))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_with_page_reuse(model, dtype):
+    steps = H.trace_mixed(model["requests"], seed=11)
+    need = H.peak_tokens(steps)
+    total = sum(-(-len(v) // 64) * 64 for v in model["requests"].values())
+    assert need < total, "the pool must be too small to hold all requests at once"
+    _check(model, dtype, steps, need)
+
+
+def test_float32_cut_invariance(model):
+    """In float32 the logits of a position are bit-identical however the tokens are cut."""
+    a = _check(model, "float32", H.trace_whole(model["requests"]))
+    b = _check(model, "float32", H.trace_portions(model["requests"]))
+    c = _check(model, "float32", H.trace_mixed(model["requests"], seed=5))
+    for rid in a:
+        for pos in a[rid]:
+            assert np.array_equal(a[rid][pos], b[rid][pos]), (rid, pos)
+            assert np.array_equal(a[rid][pos], c[rid][pos]), (rid, pos)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decode_and_first_tokens(model, dtype):
+    """A 2-token prompt, then every further token decoded one by one."""
+    cfg = model["cfg"]
+    n = min(200, cfg["max_position_embeddings"] - 8)
+    ids = H.random_ids(n, cfg["vocab_size"], 999)
+    ref = H.plain_logits(model["folder"], ids)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": ids[:2], "want": [0, 1]}], "end": []}]
+    for i in range(2, n):
+        steps.append({"step": i - 1, "entries": [{"id": "x", "tokens": [ids[i]], "want": [0]}],
+                      "end": ["x"] if i == n - 1 else []})
+    sess = _session(model, dtype, H.peak_tokens(steps))
+    got = H.collect(steps, H.run_session(sess, steps), cfg["vocab_size"])["x"]
+    for pos in range(n):
+        err = float(np.abs(got[pos] - ref[pos]).max())
+        assert err <= TOL[dtype], f"first wrong position {pos} (err {err:.3e})"
+
+
+def test_trace_run_program(model, tmp_path):
+    """bin/trace_run as a program: JSON lines in, <step>.f32 files and 'done' lines out."""
+    if model["name"] != "B":
+        pytest.skip("one configuration is enough for the program itself")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    reqs = {k: model["requests"][k] for k in ("r1", "r3")}
+    steps = H.trace_mixed(reqs, seed=3, max_live=2)
+    out = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", model["folder"],
+         "--dtype", "float32", "--out", str(out), "--max-tokens", str(H.peak_tokens(steps)),
+         "--page-size", str(model["page"])],
+        input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+        timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == \
+        [f"done {s['step']}" for s in steps]
+    V = model["cfg"]["vocab_size"]
+    outputs = {s["step"]: np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, V)
+               for s in steps if any(e["want"] for e in s["entries"])}
+    got = H.collect(steps, outputs, V)
+    for rid, ids in reqs.items():
+        for pos in range(len(ids)):
+            assert np.abs(got[rid][pos] - model["ref"][rid][pos]).max() <= TOL["float32"]
