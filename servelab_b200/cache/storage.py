@@ -1,8 +1,9 @@
 """Device memory of the cache: pages per layer group, state records per layer.
 
-``plan_groups`` sorts the layers' cache requests into groups: paged requests with
-equal (kv heads, head size, window) share a group (one page pool, one block table
-per request); layers that run from another layer's cache own nothing.  Page
+``plan_groups`` sorts the cache requests of the run order's entries into groups:
+paged requests with equal (kv heads, head size, window) share a group (one page
+pool, one block table per request); runs that read an earlier run's cache own
+nothing.  "layer" below means an entry of the run order.  Page
 layout of one layer: k and v each [num_pages, kv_heads, page_size, head_dim], so
 the page_size x head_dim tile of one (page, kv head) is contiguous.  The
 reference keeps [layers, rows, kv_heads, head_dim] (servelab/kv_cache/pool.py:54-57).

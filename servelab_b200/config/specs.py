@@ -3,7 +3,7 @@
 A model is a list of *layers*, each a block that names its parts (mixer,
 feed-forward, norms) by registry kind together with their sizes and constants,
 plus a *run order*: the sequence in which layers execute, which may name a layer
-twice or let a layer read another layer's cache.  Nothing in here knows any
+twice or let a run read the cache that an earlier run filled.  Nothing in here knows any
 model family; the family's config class (for example ``Qwen2Config``) translates
 its own ``config.json`` keys into these specs.
 
@@ -96,10 +96,12 @@ class BlockSpec(PartSpec):
 class LayerRun:
     """One entry of the run order.
 
-    ``layer``      index into ``ModelSpec.layers`` (weights and parts).
-    ``cache_of``   index of the layer whose cache this run reads *instead of
-                   owning one*: such a run writes no keys or values.  None means
-                   the layer uses (and fills) its own cache.
+    ``layer``      index into ``ModelSpec.layers`` (weights and parts).  A layer may
+                   be named by several runs; they share its weights, and each run
+                   that owns a cache gets one of its own.
+    ``cache_of``   index of an EARLIER RUN whose cache this run reads instead of
+                   owning one: such a run writes no keys, values or state.  None
+                   means the run owns (and fills) its cache.
     """
     layer: int
     cache_of: Optional[int] = None

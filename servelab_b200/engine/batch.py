@@ -47,6 +47,7 @@ class StepContext:
         self.num_seqs = 0
         self.num_logit_rows = 0
         self.q_lens: List[int] = []
+        self.state_slot_ids: List[int] = []
         self.ctx_lens: List[int] = []
         self.decode_only = False
         self.max_ctx_len = 0
@@ -117,6 +118,7 @@ class StepContext:
                             for g, w in enumerate(widths)]
         ctx.num_tokens, ctx.num_seqs, ctx.num_logit_rows = T, S, R
         ctx.q_lens = q_lens
+        ctx.state_slot_ids = [e.state_slot for e in entries]
         ctx.ctx_lens = [e.start + n for e, n in zip(entries, q_lens)]
         ctx.max_ctx_len = max(ctx.ctx_lens) if ctx.ctx_lens else 0
         ctx.decode_only = S > 0 and all(n == 1 for n in q_lens)

@@ -38,11 +38,13 @@ def declare_tensors(spec: ModelSpec) -> List[TensorDecl]:
 class CausalLM:
     def __init__(self, spec: ModelSpec, env: BuildEnv):
         self.spec, self.env = spec, env
-        for run in spec.run_order:
+        for i, run in enumerate(spec.run_order):
             if not 0 <= run.layer < len(spec.layers):
                 raise ValueError(f"run order names layer {run.layer}, model has {len(spec.layers)}")
-            if run.cache_of is not None and not 0 <= run.cache_of < len(spec.layers):
-                raise ValueError(f"run order reads the cache of unknown layer {run.cache_of}")
+            if run.cache_of is not None and (
+                    not 0 <= run.cache_of < i or spec.run_order[run.cache_of].cache_of is not None):
+                raise ValueError(f"run {i} reads the cache of run {run.cache_of}, which must be "
+                                 f"an earlier run that owns a cache")
         self.blocks = [build_part(BLOCKS, b, spec.layer_prefix.format(i), env)
                        for i, b in enumerate(spec.layers)]
         self.final_norm = build_part(NORMS, spec.final_norm, spec.final_norm_prefix, env)
@@ -51,11 +53,11 @@ class CausalLM:
 
     # ------------------------------------------------------------ caches
     def cache_requests(self) -> List[Optional[object]]:
-        """Per layer, what its mixer asks of the cache; None for layers that only
-        ever run from another layer's cache."""
-        owners = {run.layer for run in self.spec.run_order if run.cache_of is None}
-        return [part_class(BLOCKS, b).cache_request(b) if i in owners else None
-                for i, b in enumerate(self.spec.layers)]
+        """Per run of the run order, what its mixer asks of the cache; None for
+        runs that read an earlier run's cache."""
+        return [part_class(BLOCKS, self.spec.layers[run.layer]).cache_request(
+                    self.spec.layers[run.layer]) if run.cache_of is None else None
+                for run in self.spec.run_order]
 
     # ----------------------------------------------------------- weights
     def load(self, source: WeightSource) -> None:
@@ -91,13 +93,14 @@ class CausalLM:
 
     # ----------------------------------------------------------- forward
     def forward(self, ctx, caches: Dict[int, LayerCache]) -> torch.Tensor:
-        """Run the step's tokens; returns logits [wanted rows, vocab] float32."""
+        """Run the step's tokens; ``caches`` maps a run's index to its cache.
+        Returns logits [wanted rows, vocab] float32."""
         T = ctx.num_tokens
         resid = torch.empty((T, self.spec.hidden_size), dtype=torch.float32, device=self.env.device)
         K.embedding(ctx.token_ids, self.embed_tokens, resid)
         delta = None
-        for run in self.spec.run_order:
-            owner = run.layer if run.cache_of is None else run.cache_of
+        for i, run in enumerate(self.spec.run_order):
+            owner = i if run.cache_of is None else run.cache_of
             resid, delta = self.blocks[run.layer].forward(ctx, resid, delta, caches[owner],
                                                           run.cache_of is None)
         if ctx.num_logit_rows == 0:

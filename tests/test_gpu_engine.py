@@ -1,0 +1,149 @@
+"""Generation through the Python entry point and the command line, compared with
+the plain implementation; the same tokens whatever the batching, the portion
+size or the number of pages (preemption); sampling is reproducible and follows
+the host mirror."""
+
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+import plain_model as P
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module", params=["A", "B", "C"])
+def model(request, tmp_path_factory):
+    cfg, seed, page = H.CONFIGS[request.param]
+    folder = str(tmp_path_factory.mktemp(f"gen_{request.param}"))
+    H.make_model(folder, cfg, seed)
+    lengths = {"A": [5, 17, 33], "B": [1, 9, 40, 70], "C": [3, 26, 48]}[request.param]
+    prompts = [H.random_ids(n, cfg["vocab_size"] - 2, seed + 1 + i) for i, n in enumerate(lengths)]
+    return {"name": request.param, "cfg": cfg, "folder": folder, "page": page, "prompts": prompts}
+
+
+def _engine(model, dtype="float32", num_blocks=256, budget=2048, max_seqs=8, **kw):
+    from servelab_b200.config import CacheConfig, SchedulerConfig
+    from servelab_b200.engine.llm_engine import LLMEngine
+    return LLMEngine(model["folder"], CacheConfig(block_size=model["page"], num_blocks=num_blocks),
+                     SchedulerConfig(max_num_seqs=max_seqs, max_num_batched_tokens=budget),
+                     dtype=dtype, **kw)
+
+
+def test_greedy_generation_equals_the_plain_implementation(model):
+    from servelab_b200.sampling import SamplingParams
+    n_new = 8 if model["name"] == "A" else 12
+    cfg, w = P.load_folder(model["folder"])
+    want = [P.generate_greedy(cfg, w, p, n_new) for p in model["prompts"]]
+    eng = _engine(model)
+    outs = eng.generate(model["prompts"], SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True))
+    assert [o.outputs[0].token_ids for o in outs] == want
+    assert all(o.finished and o.outputs[0].finish_reason == "length" for o in outs)
+    assert [o.prompt_token_ids for o in outs] == model["prompts"]
+    st = eng.stats()
+    assert st["running"] == 0 and st["waiting"] == 0 and st["pages_used"] == [0] * len(st["pages_used"])
+
+
+def test_same_tokens_alone_batched_chunked_and_with_few_pages(model):
+    from servelab_b200.sampling import SamplingParams
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    base = [o.outputs[0].token_ids for o in _engine(model).generate(model["prompts"], sp)]
+    alone = [_engine(model).generate([p], sp)[0].outputs[0].token_ids for p in model["prompts"][:2]]
+    assert alone == base[:2]
+    chunked = _engine(model, budget=24).generate(model["prompts"], sp)
+    assert [o.outputs[0].token_ids for o in chunked] == base
+    # so few pages that running requests are preempted and recomputed
+    longest = max(len(p) for p in model["prompts"]) + 10
+    few = -(-longest // model["page"]) + 2
+    eng = _engine(model, num_blocks=few, budget=24)
+    outs = eng.generate(model["prompts"], sp)
+    assert [o.outputs[0].token_ids for o in outs] == base
+    assert eng.scheduler.num_preemptions > 0, "the pool was meant to be too small"
+    eng.runner.cache.check_invariants()
+
+
+def test_bfloat16_generation_follows_float32_logits(model):
+    """bfloat16 may pick another token only where the float32 logits nearly tie."""
+    from servelab_b200.sampling import SamplingParams
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    outs = _engine(model, dtype="bfloat16").generate(model["prompts"], sp)
+    cfg, w = P.load_folder(model["folder"])
+    for prompt, o in zip(model["prompts"], outs):
+        ids = list(prompt)
+        for tok in o.outputs[0].token_ids:
+            logits = P.forward_logits(cfg, w, ids)[-1]
+            assert float(logits.max() - logits[tok]) <= 4e-2
+            ids.append(tok)
+
+
+def test_temperature_sampling_is_reproducible_and_batch_independent(model):
+    from servelab_b200.sampling import SamplingParams
+    sp = SamplingParams(temperature=0.7, max_tokens=12, ignore_eos=True)
+    a = [o.outputs[0].token_ids for o in _engine(model, seed=4).generate(model["prompts"], sp)]
+    b = [o.outputs[0].token_ids for o in _engine(model, seed=4, budget=24).generate(model["prompts"], sp)]
+    c = [o.outputs[0].token_ids for o in _engine(model, seed=5).generate(model["prompts"], sp)]
+    assert a == b and a != c
+    # the host mirror draws the same tokens from the plain implementation's logits
+    cfg, w = P.load_folder(model["folder"])
+    ids = list(model["prompts"][1])
+    mismatches = 0
+    for i, tok in enumerate(a[1]):
+        logits = P.forward_logits(cfg, w, ids)[-1]
+        want = P.sample_token(logits, 0.7, P.philox_uniform(4, 2, i))   # request 2 of the engine
+        mismatches += int(want != tok)
+        ids.append(tok)
+    assert mismatches == 0
+    # a per-request seed makes a request independent of the engine's seed and order
+    sp2 = SamplingParams(temperature=0.9, max_tokens=6, ignore_eos=True, seed=77)
+    x = _engine(model, seed=1).generate([model["prompts"][0]], sp2)[0].outputs[0].token_ids
+    y = _engine(model, seed=2).generate([model["prompts"][1], model["prompts"][0]], sp2)[1].outputs[0].token_ids
+    assert x == y
+
+
+def test_stop_conditions_abort_and_rejections(model):
+    from servelab_b200.sampling import SamplingParams
+    cfg, w = P.load_folder(model["folder"])
+    prompt = model["prompts"][1]
+    greedy = P.generate_greedy(cfg, w, prompt, 5)
+    eng = _engine(model)
+    out = eng.generate([prompt], SamplingParams(temperature=0.0, max_tokens=5,
+                                                stop_token_ids=(greedy[2],)))[0]
+    first = greedy.index(greedy[2])
+    assert out.outputs[0].token_ids == greedy[:first + 1] and out.outputs[0].finish_reason == "eos"
+    with pytest.raises(ValueError):
+        eng.add_request(prompt_token_ids=[model["cfg"]["vocab_size"]])
+    with pytest.raises(ValueError):
+        eng.add_request(prompt_token_ids=[])
+    rid = eng.add_request(prompt_token_ids=prompt, sampling_params=SamplingParams(max_tokens=50))
+    eng.step()
+    assert eng.abort_request(rid) and not eng.has_unfinished() and not eng.abort_request(rid)
+    # longer than the pool can ever hold: reported as aborted, others still run
+    small = _engine(model, num_blocks=3)
+    outs = small.generate([list(range(1, 3 * model["page"] + 2)), prompt[:4]],
+                          SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+    assert outs[0].outputs[0].finish_reason == "aborted" and outs[0].outputs[0].token_ids == []
+    assert outs[1].outputs[0].finish_reason == "length"
+
+
+def test_command_line(model, tmp_path):
+    if model["name"] != "A":
+        pytest.skip("one configuration is enough for the command line")
+    cfg, w = P.load_folder(model["folder"])
+    want = P.generate_greedy(cfg, w, [3, 1, 4, 1, 5], 6)
+    r = subprocess.run([sys.executable, "-m", "servelab_b200", "--model", model["folder"],
+                        "--prompt-ids", "3,1,4,1,5", "--max-tokens", "6", "--temperature", "0",
+                        "--dtype", "float32", "--ignore-eos", "--block-size", "16",
+                        "--num-blocks", "32"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert f"finish=length -> {want}" in r.stdout and "stats:" in r.stdout
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "run_engine.py"),
+                        "--max-tokens", "4", "--num-blocks", "16"], cwd=str(tmp_path),
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "finish=" in r.stdout, r.stderr[-2000:]

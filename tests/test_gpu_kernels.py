@@ -1,0 +1,344 @@
+"""Each CUDA kernel alone against a plain float32 torch expression of the same
+operation, at sizes other than the engine's tiny models (odd widths, head sizes in
+steps of 16, groups that are no power of two), in float32 and bfloat16.  Inputs are
+shaped so that faults show: one far key that must win the softmax, keys at page and
+window edges, shuffled page tables, equal maxima for the argmax."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+
+
+def K():
+    from servelab_b200.ops import kernels
+    return kernels
+
+
+def i32(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+# ------------------------------------------------------------------ embedding
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding(dtype):
+    table = torch.randn(301, 72, device=DEV).to(DT[dtype])
+    ids = i32([0, 300, 17, 17, 5])
+    out = torch.full((5, 72), 7.0, device=DEV)
+    K().embedding(ids, table, out)
+    assert torch.equal(out, table.float()[ids.long()])
+
+
+# ---------------------------------------------------------------------- norms
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("h", [72, 1000, 3584])
+def test_add_rmsnorm(dtype, h):
+    dt = DT[dtype]
+    resid = torch.randn(9, h, device=DEV) * 3
+    delta = (torch.randn(9, h, device=DEV)).to(dt)
+    w = 1 + 0.1 * torch.randn(h, device=DEV)
+    want_resid = resid + delta.float()
+    want = P.rms_norm(want_resid, w, 1e-5)
+    out = torch.empty(9, h, device=DEV, dtype=dt)
+    r = resid.clone()
+    K().add_rmsnorm(r, delta, w, 1e-5, out)
+    assert torch.equal(r, want_resid)                       # the stream is updated in float32
+    assert (out.float() - want).abs().max() <= TOL[dtype] * 4
+    # without delta the stream is untouched
+    r2 = resid.clone()
+    K().add_rmsnorm(r2, None, w, 1e-5, out)
+    assert torch.equal(r2, resid)
+    assert (out.float() - P.rms_norm(resid, w, 1e-5)).abs().max() <= TOL[dtype] * 4
+    # selected rows: nothing is written back
+    rows = i32([8, 0, 3])
+    r3 = resid.clone()
+    sel = torch.empty(3, h, device=DEV, dtype=dt)
+    K().add_rmsnorm(r3, delta, w, 1e-5, sel, rows)
+    assert torch.equal(r3, resid)
+    assert (sel.float() - want[rows.long()]).abs().max() <= TOL[dtype] * 4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu(dtype):
+    dt = DT[dtype]
+    gu = (torch.randn(7, 2 * 173, device=DEV) * 3).to(dt)
+    out = torch.empty(7, 173, device=DEV, dtype=dt)
+    K().swiglu(gu, out)
+    g, u = gu.float()[:, :173], gu.float()[:, 173:]
+    want = g * torch.sigmoid(g) * u
+    # results reach |30|: the bound is relative (one rounding to the output dtype)
+    rel = 2.0 ** -8 if dtype == "bfloat16" else 2.0 ** -21
+    assert bool(((out.float() - want).abs() <= want.abs() * rel + 1e-6).all())
+
+
+# ------------------------------------------------------ rotary + cache write
+def _paged(num_pages, Hkv, ps, D, dt):
+    return (torch.zeros(num_pages, Hkv, ps, D, device=DEV, dtype=dt),
+            torch.zeros(num_pages, Hkv, ps, D, device=DEV, dtype=dt))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,Hkv,D,rot", [(6, 2, 48, 48), (5, 5, 16, 8), (3, 1, 80, 0)])
+def test_qkv_rope_cache(dtype, H, Hkv, D, rot):
+    dt = DT[dtype]
+    ps, T = 4, 11
+    # two requests: 7 tokens from position 5, 4 tokens from position 0
+    positions = list(range(5, 12)) + list(range(0, 4))
+    seq = [0] * 7 + [1] * 4
+    table = i32([[9, 2, 7], [4, -1, -1]])
+    qkv = torch.randn(T, (H + 2 * Hkv) * D, device=DEV).to(dt)
+    bias = torch.randn((H + 2 * Hkv) * D, device=DEV)
+    inv = P.rope_inv_freq(rot, 10000.0).to(DEV) if rot else None
+    q_out = torch.empty(T, H * D, device=DEV, dtype=dt)
+    kc, vc = _paged(12, Hkv, ps, D, dt)
+    K().qkv_rope_cache(qkv, bias, i32(positions), i32(seq), table, ps, inv, rot, q_out, kc, vc,
+                       H, Hkv, D)
+    x = qkv.float() + bias
+    q = x[:, :H * D].view(T, H, D)
+    k = x[:, H * D:(H + Hkv) * D].view(T, Hkv, D)
+    v = x[:, (H + Hkv) * D:].view(T, Hkv, D)
+    pos_t = torch.tensor(positions)
+    if rot:
+        q = torch.cat([P.rope(q[..., :rot].cpu(), pos_t, inv.cpu()).to(DEV), q[..., rot:]], -1)
+        k = torch.cat([P.rope(k[..., :rot].cpu(), pos_t, inv.cpu()).to(DEV), k[..., rot:]], -1)
+    tol = TOL[dtype] * 8
+    assert (q_out.float().view(T, H, D) - q).abs().max() <= tol
+    tab = table.cpu()
+    for t in range(T):
+        page = int(tab[seq[t], positions[t] // ps])
+        assert (kc[page, :, positions[t] % ps].float() - k[t]).abs().max() <= tol
+        assert (vc[page, :, positions[t] % ps].float() - v[t]).abs().max() <= tol
+    written = {int(tab[seq[t], positions[t] // ps]) for t in range(T)}
+    for page in range(12):
+        if page not in written:
+            assert float(kc[page].abs().max()) == 0 and float(vc[page].abs().max()) == 0
+    # a run that reads another layer's cache writes nothing
+    kc2, vc2 = _paged(12, Hkv, ps, D, dt)
+    K().qkv_rope_cache(qkv, bias, i32(positions), i32(seq), table, ps, inv, rot, q_out, None, None,
+                       H, Hkv, D)
+    assert float(kc2.abs().max()) == 0
+
+
+# ------------------------------------------------------------------ attention
+class PagedCase:
+    """Requests with dense K/V scattered into shuffled pages."""
+
+    def __init__(self, ctx_lens, q_lens, H, Hkv, D, ps, dt, seed=0, pad_pages=3):
+        g = torch.Generator().manual_seed(seed)
+        self.H, self.Hkv, self.D, self.ps, self.dt = H, Hkv, D, ps, dt
+        self.ctx_lens, self.q_lens = ctx_lens, q_lens
+        need = [-(-c // ps) for c in ctx_lens]
+        total = sum(need) + pad_pages
+        perm = torch.randperm(total, generator=g).tolist()
+        self.tables, self.k, self.v = [], [], []
+        self.kc, self.vc = _paged(total, Hkv, ps, D, dt)
+        self.kc.normal_(generator=None)                       # stale data in unused slots
+        self.vc.normal_(generator=None)
+        for c, n in zip(ctx_lens, need):
+            pages = [perm.pop() for _ in range(n)]
+            self.tables.append(pages)
+            k = torch.randn(c, Hkv, D, generator=g).to(dt)
+            v = torch.randn(c, Hkv, D, generator=g).to(dt)
+            self.k.append(k)
+            self.v.append(v)
+        self.q = [torch.randn(n, H, D, generator=g).to(dt) for n in q_lens]
+
+    def scatter(self):
+        for pages, k, v in zip(self.tables, self.k, self.v):
+            for p in range(k.shape[0]):
+                self.kc[pages[p // self.ps], :, p % self.ps] = k[p].to(DEV)
+                self.vc[pages[p // self.ps], :, p % self.ps] = v[p].to(DEV)
+
+    def device_args(self):
+        width = max(len(t) for t in self.tables)
+        table = i32([t + [-1] * (width - len(t)) for t in self.tables])
+        cu = [0]
+        for n in self.q_lens:
+            cu.append(cu[-1] + n)
+        q = torch.cat(self.q).reshape(cu[-1], self.H * self.D).to(DEV)
+        return q, table, i32(cu), i32(self.ctx_lens)
+
+    def reference(self, window=None, scale=None):
+        outs = []
+        g = self.H // self.Hkv
+        for q, k, v, c, n in zip(self.q, self.k, self.v, self.ctx_lens, self.q_lens):
+            qf, kf, vf = q.float(), k.float().repeat_interleave(g, 1), v.float().repeat_interleave(g, 1)
+            s = torch.einsum("qhd,rhd->hqr", qf, kf) * (scale or 1 / math.sqrt(self.D))
+            a = torch.arange(c - n, c)[:, None]
+            r = torch.arange(c)[None, :]
+            mask = r > a
+            if window:
+                mask = mask | (a - r >= window)
+            s = s.masked_fill(mask[None], float("-inf"))
+            outs.append(torch.einsum("hqr,rhd->qhd", torch.softmax(s, -1), vf).reshape(n, -1))
+        return torch.cat(outs)
+
+
+def run_generic(case, window=0, scale=None):
+    from servelab_b200.engine.batch import StepContext
+    k = K()
+    case.scatter()
+    q, table, cu, ctx_len = case.device_args()
+    ctx = StepContext(DEV)
+    ctx.q_lens = case.q_lens
+    tile_seq, tile_row0, n = ctx.attention_tiles(case.H // case.Hkv, k.generic_attention_tile_rows())
+    out = torch.empty_like(q)
+    k.paged_attention_generic(q, case.kc, case.vc, out, table, cu, ctx_len, tile_seq, tile_row0, n,
+                              case.H, case.Hkv, case.D, case.ps, scale or 1 / math.sqrt(case.D),
+                              window)
+    return out.float().cpu()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,Hkv,D,ps", [(6, 2, 16, 16), (7, 1, 64, 8), (5, 5, 48, 4),
+                                        (28, 4, 128, 16), (2, 1, 256, 32), (12, 2, 80, 5)])
+def test_generic_attention_mixed_batch(dtype, H, Hkv, D, ps):
+    # a whole prompt, a portion in the middle of one, two single tokens, a 2-token portion
+    case = PagedCase([37, 150, 1, 263, 34], [37, 19, 1, 1, 2], H, Hkv, D, ps, DT[dtype], seed=D)
+    got, want = run_generic(case), case.reference()
+    assert (got - want).abs().max() <= TOL[dtype] * (5 if dtype == "float32" else 1)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [1, 7, 16, 33])
+def test_generic_attention_window_edges(dtype, window):
+    case = PagedCase([90, 41, 64], [23, 1, 64], 6, 3, 32, 8, DT[dtype], seed=window)
+    # the key just outside the window would win by far if it were visible; the key
+    # just inside must be seen
+    for q, k, c, n in zip(case.q, case.k, case.ctx_lens, case.q_lens):
+        a = c - 1                                        # last query
+        if a - window >= 0:
+            k[a - window] = (q[-1, 0::2].mean(0) * 50).to(k.dtype)
+    got, want = run_generic(case, window=window), case.reference(window=window)
+    assert (got - want).abs().max() <= TOL[dtype] * (5 if dtype == "float32" else 1)
+    full = case.reference()
+    assert (want - full).abs().max() > 1e-2              # the window does change the result
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("needle", [0, 15, 16, 511, 512, 700])
+def test_generic_attention_finds_one_far_key(dtype, needle):
+    """One key among 701 is aligned with the query and scaled so that it takes all
+    the weight: the output must be that key's value (page edges included)."""
+    H, Hkv, D, ps = 4, 2, 64, 16
+    case = PagedCase([701], [1], H, Hkv, D, ps, DT[dtype], seed=needle)
+    for kvh in range(Hkv):
+        qdir = case.q[0][0, kvh * 2].float()
+        case.k[0][needle, kvh] = (qdir * 40 / qdir.norm()).to(case.dt)
+        case.q[0][0, kvh * 2 + 1] = case.q[0][0, kvh * 2]
+    case.q[0] = (case.q[0].float() * 8).to(case.dt)
+    got = run_generic(case).view(1, H, D)
+    for h in range(H):
+        assert (got[0, h] - case.v[0][needle, h // 2].float()).abs().max() <= 2e-2
+
+
+# ------------------------------------------------------------ matrix product
+@pytest.mark.parametrize("M,N,Kd", [(1, 7, 5), (33, 172, 64), (70, 65, 173), (5, 300, 129)])
+def test_gemm_simt(M, N, Kd):
+    a = torch.randn(M, Kd, device=DEV)
+    w = torch.randn(N, Kd, device=DEV)
+    b = torch.randn(N, device=DEV)
+    out = torch.empty(M, N, device=DEV)
+    K().gemm_simt(a, w, out, b)
+    want = (a.double() @ w.double().t() + b.double()).float()
+    assert (out - want).abs().max() <= 1e-5 * math.sqrt(Kd) * 4
+    # a row does not depend on the rest of the batch (bit-exact)
+    one = torch.empty(1, N, device=DEV)
+    K().gemm_simt(a[M - 1:M].contiguous(), w, one, b)
+    assert torch.equal(one[0], out[M - 1])
+    ab, wb = a.bfloat16(), w.bfloat16()
+    o32 = torch.empty(M, N, device=DEV)
+    K().gemm_simt(ab, wb, o32, None)
+    assert (o32 - (ab.double() @ wb.double().t()).float()).abs().max() <= 1e-4 * math.sqrt(Kd)
+    ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    K().gemm_simt(ab, wb, ob, None)
+    assert torch.equal(ob, o32.bfloat16())
+
+
+def test_bf16_linear_dispatch_shapes():
+    """Aligned shapes go to the library GEMM, ragged ones to the CUDA-core kernel;
+    both agree with float64 within bfloat16 rounding."""
+    from servelab_b200.ops.linear import linear
+    for M, N, Kd in [(40, 256, 96), (40, 172, 64), (3, 64, 172), (100, 300, 80)]:
+        x = torch.randn(M, Kd, device=DEV).bfloat16()
+        w = (torch.randn(N, Kd, device=DEV) * 0.05).bfloat16()
+        want = (x.double() @ w.double().t()).float()
+        y = linear(x, w)
+        assert y.dtype == torch.bfloat16 and (y.float() - want).abs().max() <= 2e-2
+        y32 = linear(x, w, out_dtype=torch.float32)
+        assert y32.dtype == torch.float32 and (y32 - want).abs().max() <= 2e-3
+
+
+# ------------------------------------------------------------------- sampling
+def test_argmax_takes_the_first_of_equal_maxima():
+    V = 152064 + 7
+    logits = torch.randn(5, V, device=DEV)
+    logits[0, 1000] = logits[0, 77] = 50.0
+    logits[1, V - 1] = 60.0
+    logits[2, 0] = 60.0
+    logits[3, :] = 1.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    K().sample_rows(logits, out)
+    assert out.tolist()[:4] == [77, V - 1, 0, 0]
+    assert out.tolist()[4] == int(torch.argmax(logits[4]))
+
+
+def _sample(logits, temp, top_k, top_p, seed, stream, pos):
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=DEV)
+    K().sample_rows(logits, out, torch.tensor(temp, dtype=torch.float32, device=DEV), i32(top_k),
+                    torch.tensor(top_p, dtype=torch.float32, device=DEV),
+                    torch.tensor(seed, dtype=torch.int64, device=DEV),
+                    torch.tensor(stream, dtype=torch.int64, device=DEV), i32(pos))
+    return out.tolist()
+
+
+@pytest.mark.parametrize("mode", ["temperature", "top_k", "top_p"])
+def test_sampler_matches_the_host_mirror(mode):
+    V, R = 1031, 256
+    g = torch.Generator().manual_seed(3)
+    row = torch.randn(V, generator=g) * 2
+    logits = row.repeat(R, 1).to(DEV)
+    temp, top_k, top_p = 0.7, -1, 1.0
+    if mode == "top_k":
+        top_k = 5
+    if mode == "top_p":
+        top_p = 0.6
+    seed, stream = 1234 + (1 << 40), 9
+    got = _sample(logits, [temp] * R, [top_k] * R, [top_p] * R, [seed] * R, [stream] * R,
+                  list(range(R)))
+    want = [P.sample_token(row, temp, P.philox_uniform(seed, stream, i), top_k, top_p)
+            for i in range(R)]
+    same = sum(int(a == b) for a, b in zip(got, want))
+    assert same >= R - 1, f"{R - same} draws differ from the host mirror"
+    kept = (P.filtered_probs(row, temp, top_k, top_p) > 0).nonzero().flatten().tolist()
+    assert set(got) <= set(kept)
+    if mode == "top_k":
+        assert len(kept) == 5
+    # the draw depends on (seed, stream, position) only, not on the row's place in the batch
+    again = _sample(logits[:3], [temp] * 3, [top_k] * 3, [top_p] * 3, [seed] * 3, [stream] * 3,
+                    [200, 7, 31])
+    assert again == [got[200], got[7], got[31]]
+    other = _sample(logits[:64], [temp] * 64, [top_k] * 64, [top_p] * 64, [seed + 1] * 64,
+                    [stream] * 64, list(range(64)))
+    assert other != got[:64]
+
+
+def test_sampler_mixes_greedy_and_random_rows_and_follows_the_distribution():
+    V, R = 50, 4000
+    row = torch.linspace(-2, 2, V)
+    logits = row.repeat(R, 1).to(DEV)
+    temps = [0.0 if i % 2 else 1.3 for i in range(R)]
+    got = _sample(logits, temps, [-1] * R, [1.0] * R, [7] * R, [1] * R, list(range(R)))
+    assert all(got[i] == V - 1 for i in range(1, R, 2))
+    counts = np.bincount([got[i] for i in range(0, R, 2)], minlength=V) / (R / 2)
+    want = torch.softmax(row.double() / 1.3, -1).numpy()
+    assert np.abs(counts - want).max() < 0.03

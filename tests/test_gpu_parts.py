@@ -1,0 +1,296 @@
+"""Each part of a layer alone against the plain implementation's function, and
+the generality of the composition: a toy mixer with state of its own, defined
+here, is registered, built into a model, loaded and stepped (whole and cut into
+portions, with slot reuse) without any change to the framework's files; the run
+order names a layer twice and lets a run read an earlier run's cache."""
+
+from dataclasses import dataclass
+from typing import Tuple
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+import plain_model as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 1e-5, "bfloat16": 2e-2}
+
+
+def _env(dtype, page=4):
+    from servelab_b200.parts import BuildEnv
+    return BuildEnv(device=DEV, dtype=DT[dtype], page_size=page)
+
+
+def _build(table, spec, prefix, dtype, seed=0, page=4):
+    """Build one part from random tensors; returns (part, CPU float32 tensors)."""
+    from servelab_b200.parts import build_part, part_class
+    from servelab_b200.weights import RandomSource, WeightStore
+    decls = part_class(table, spec).declare(spec, prefix)
+    src = RandomSource(decls, seed, std=0.08, dtype=DT[dtype])
+    part = build_part(table, spec, prefix, _env(dtype, page))
+    part.load(WeightStore(src, decls, DT[dtype], DEV))
+    return part, {d.name: src.read(d.name).float() for d in decls}
+
+
+def _ctx(entries, groups=1):
+    from servelab_b200.engine.batch import StepContext
+    return StepContext.pack(entries, groups, DEV)
+
+
+def _entry(tokens, start, table, want=(), slot=0):
+    from servelab_b200.engine.batch import BatchEntry
+    return BatchEntry(tokens=tokens, start=start, want=want, block_tables=[table], state_slot=slot)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_part(dtype):
+    from servelab_b200.config import RMSNormSpec
+    from servelab_b200.parts import NORMS
+    part, w = _build(NORMS, RMSNormSpec(dim=88, eps=2e-5), "n", dtype)
+    resid = torch.randn(5, 88, device=DEV)
+    delta = torch.randn(5, 88, device=DEV).to(DT[dtype])
+    want = P.rms_norm((resid + delta.float()).cpu(), w["n.weight"], 2e-5)
+    got = part.forward(None, resid, delta)
+    assert got.dtype == DT[dtype] and (got.float().cpu() - want).abs().max() <= TOL[dtype] * 4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_feed_forward_part(dtype):
+    from servelab_b200.config import GatedMLPSpec
+    from servelab_b200.parts import FEED_FORWARDS
+    part, w = _build(FEED_FORWARDS, GatedMLPSpec(hidden_size=72, intermediate_size=172), "mlp", dtype)
+    x = torch.randn(9, 72, device=DEV).to(DT[dtype])
+    want = P.swiglu(x.float().cpu(), w["mlp.gate_proj.weight"], w["mlp.up_proj.weight"],
+                    w["mlp.down_proj.weight"])
+    got = part.forward(None, x)
+    assert (got.float().cpu() - want).abs().max() <= TOL[dtype]
+
+
+def _attention_reference(w, x, H_, Hkv, D, theta, window, rot=None):
+    T = x.shape[0]
+    q = P.linear(x, w["a.q_proj.weight"], w["a.q_proj.bias"]).view(T, H_, D)
+    k = P.linear(x, w["a.k_proj.weight"], w["a.k_proj.bias"]).view(T, Hkv, D)
+    v = P.linear(x, w["a.v_proj.weight"], w["a.v_proj.bias"]).view(T, Hkv, D)
+    if theta:
+        rot = rot or D
+        inv, pos = P.rope_inv_freq(rot, theta), torch.arange(T)
+        q = torch.cat([P.rope(q[..., :rot], pos, inv), q[..., rot:]], -1)
+        k = torch.cat([P.rope(k[..., :rot], pos, inv), k[..., rot:]], -1)
+    return P.linear(P.causal_attention(q, k, v, window), w["a.o_proj.weight"],
+                    w.get("a.o_proj.bias"))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("variant", ["rotary", "window", "no_position", "partial_rotary_out_bias"])
+def test_attention_mixer_alone_whole_and_in_portions(dtype, variant):
+    from servelab_b200.config import AttentionSpec, NoPositionSpec, RotarySpec
+    from servelab_b200.parts import MIXERS, LayerCache
+    H_, Hkv, D, hid, T, ps = 6, 2, 32, 40, 29, 4
+    theta, window, rot, out_bias = 10000.0, None, D, False
+    if variant == "window":
+        window = 5
+    if variant == "no_position":
+        theta = 0.0
+    if variant == "partial_rotary_out_bias":
+        rot, out_bias = 16, True
+    pos_spec = RotarySpec(head_dim=D, rotary_dim=rot, theta=theta) if theta else NoPositionSpec()
+    spec = AttentionSpec(hidden_size=hid, num_heads=H_, num_kv_heads=Hkv, head_dim=D,
+                         qkv_bias=True, out_bias=out_bias, window=window, position=pos_spec)
+    part, w = _build(MIXERS, spec, "a", dtype, page=ps)
+    x = torch.randn(T, hid).to(DT[dtype])
+    want = _attention_reference(w, x.float(), H_, Hkv, D, theta, window, rot)
+    pages = [5, 0, 7, 3, 9, 1, 8, 2]
+    for cuts in ([T], [3, 2, 11, 1, 1, 9, 2]):
+        k = torch.zeros(10, Hkv, ps, D, device=DEV, dtype=DT[dtype])
+        cache = LayerCache(group=0, k=k, v=torch.zeros_like(k), page_size=ps)
+        outs, start = [], 0
+        for n in cuts:
+            ctx = _ctx([_entry([0] * n, start, pages[:-(-(start + n) // ps)])])
+            outs.append(part.forward(ctx, x[start:start + n].to(DEV), cache, True).float().cpu())
+            start += n
+        got = torch.cat(outs)
+        assert (got - want).abs().max() <= TOL[dtype], (variant, cuts)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_block_alone(dtype):
+    from servelab_b200.config import (AttentionSpec, BlockSpec, GatedMLPSpec, RMSNormSpec,
+                                      RotarySpec)
+    from servelab_b200.parts import BLOCKS, LayerCache
+    hid, H_, Hkv, D, I, T, ps = 48, 3, 3, 16, 100, 13, 8
+    norm = RMSNormSpec(dim=hid, eps=1e-6)
+    spec = BlockSpec(
+        mixer=AttentionSpec(hidden_size=hid, num_heads=H_, num_kv_heads=Hkv, head_dim=D,
+                            qkv_bias=True, position=RotarySpec(head_dim=D, rotary_dim=D, theta=1e4)),
+        feed_forward=GatedMLPSpec(hidden_size=hid, intermediate_size=I), mixer_norm=norm, ff_norm=norm)
+    part, w = _build(BLOCKS, spec, "L", dtype, page=ps)
+    x = torch.randn(T, hid)
+    wa = {k.replace("L.self_attn", "a"): v for k, v in w.items()}
+    h1 = x + _attention_reference(wa, P.rms_norm(x, w["L.input_layernorm.weight"], 1e-6),
+                                  H_, Hkv, D, 1e4, None)
+    want = h1 + P.swiglu(P.rms_norm(h1, w["L.post_attention_layernorm.weight"], 1e-6),
+                         w["L.mlp.gate_proj.weight"], w["L.mlp.up_proj.weight"],
+                         w["L.mlp.down_proj.weight"])
+    k = torch.zeros(4, Hkv, ps, D, device=DEV, dtype=DT[dtype])
+    cache = LayerCache(group=0, k=k, v=torch.zeros_like(k), page_size=ps)
+    resid = x.to(DEV).clone()
+    ctx = _ctx([_entry([0] * T, 0, [2, 0])])
+    resid, delta = part.forward(ctx, resid, None, cache, True)
+    got = (resid + delta.float()).cpu()
+    assert (got - want).abs().max() <= TOL[dtype] * 2
+
+
+# --------------------------------------------------------------------------- #
+# a toy architecture, defined entirely in this test
+# --------------------------------------------------------------------------- #
+
+def _register_toy():
+    """Registers (once) a mixer with per-request state -- a running mean of its
+    inputs scaled by a learned vector -- and a toy architecture that uses it."""
+    from servelab_b200.cache import FixedStateRequest
+    from servelab_b200.config import (AttentionSpec, BlockSpec, GatedMLPSpec, LayerRun, ModelSpec,
+                                      PartSpec, RMSNormSpec, RotarySpec, register_architecture)
+    from servelab_b200.parts import MIXERS, Mixer, register_mixer
+    from servelab_b200.weights import NORM, TensorDecl
+
+    if "toy_running_mean" in MIXERS:
+        return
+
+    @dataclass(frozen=True)
+    class RunningMeanSpec(PartSpec):
+        kind: str = "toy_running_mean"
+        hidden_size: int = 0
+
+    @register_mixer("toy_running_mean")
+    class RunningMean(Mixer):
+        """y_t = gain * mean(x_0 .. x_t); the state slot holds [sum | count]."""
+
+        @classmethod
+        def declare(cls, spec, prefix):
+            return [TensorDecl(prefix + ".gain", (spec.hidden_size,), NORM)]
+
+        @classmethod
+        def cache_request(cls, spec):
+            return FixedStateRequest((spec.hidden_size + 1,))
+
+        def load(self, store):
+            self.gain = store.get(self.prefix + ".gain")
+
+        def forward(self, ctx, x, cache, owns_cache):
+            out = torch.empty_like(x)
+            t0 = 0
+            for n, slot in zip(ctx.q_lens, ctx.state_slot_ids):
+                st = cache.state[slot]
+                sums = st[:-1] + torch.cumsum(x[t0:t0 + n].float(), 0)
+                counts = st[-1] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+                out[t0:t0 + n] = (sums / counts[:, None] * self.gain).to(x.dtype)
+                if owns_cache:
+                    st[:-1] = sums[-1]
+                    st[-1] = counts[-1]
+                t0 += n
+            return out
+
+    class ToyConfig:
+        architecture = "ToyStateForCausalLM"
+
+        def __init__(self, d):
+            self.d = dict(d)
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+        def to_dict(self):
+            return dict(self.d, architectures=[self.architecture])
+
+        def to_model_spec(self):
+            d = self.d
+            hid, D = d["hidden_size"], d["head_dim"]
+            norm = RMSNormSpec(dim=hid, eps=d["eps"])
+            ff = GatedMLPSpec(hidden_size=hid, intermediate_size=d["intermediate_size"])
+            attn = AttentionSpec(hidden_size=hid, num_heads=d["heads"], num_kv_heads=d["kv_heads"],
+                                 head_dim=D, qkv_bias=True,
+                                 position=RotarySpec(head_dim=D, rotary_dim=D, theta=d["theta"]))
+            layers = (BlockSpec(mixer=attn, feed_forward=ff, mixer_norm=norm, ff_norm=norm),
+                      BlockSpec(mixer=RunningMeanSpec(hidden_size=hid), feed_forward=ff,
+                                mixer_norm=norm, ff_norm=norm))
+            # layer 0, the state layer, layer 0 again with a cache of its own, then layer 0
+            # reading the cache that run 0 filled
+            order = (LayerRun(0), LayerRun(1), LayerRun(0), LayerRun(0, cache_of=0))
+            return ModelSpec(architecture=self.architecture, hidden_size=hid,
+                             vocab_size=d["vocab_size"], layers=layers, run_order=order,
+                             final_norm=norm, tie_word_embeddings=True,
+                             max_position_embeddings=256)
+
+    register_architecture(ToyConfig.architecture, ToyConfig)
+
+
+TOY = {"architectures": ["ToyStateForCausalLM"], "hidden_size": 48, "head_dim": 16, "heads": 3,
+       "kv_heads": 1, "intermediate_size": 56, "vocab_size": 130, "eps": 1e-6, "theta": 10000.0}
+
+
+def _toy_plain(folder, ids):
+    cfg, w = P.load_folder(folder)
+    T, hid, D, H_, Hkv = len(ids), 48, 16, 3, 1
+    x = P.embed(torch.tensor(ids), w["model.embed_tokens.weight"])
+    inv, pos = P.rope_inv_freq(D, 10000.0), torch.arange(T)
+
+    def qkv(layer, h):
+        p = f"model.layers.{layer}.self_attn."
+        q = P.rope(P.linear(h, w[p + "q_proj.weight"], w[p + "q_proj.bias"]).view(T, H_, D), pos, inv)
+        k = P.rope(P.linear(h, w[p + "k_proj.weight"], w[p + "k_proj.bias"]).view(T, Hkv, D), pos, inv)
+        v = P.linear(h, w[p + "v_proj.weight"], w[p + "v_proj.bias"]).view(T, Hkv, D)
+        return q, k, v
+
+    def ff(layer, h):
+        p = f"model.layers.{layer}."
+        return P.swiglu(P.rms_norm(h, w[p + "post_attention_layernorm.weight"], 1e-6),
+                        w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                        w[p + "mlp.down_proj.weight"])
+
+    kv0 = None
+    for run, (layer, shared) in enumerate([(0, False), (1, False), (0, False), (0, True)]):
+        h = P.rms_norm(x, w[f"model.layers.{layer}.input_layernorm.weight"], 1e-6)
+        if layer == 1:
+            mean = torch.cumsum(h, 0) / torch.arange(1, T + 1)[:, None]
+            a = mean * w["model.layers.1.self_attn.gain"]
+        else:
+            q, k, v = qkv(0, h)
+            if run == 0:
+                kv0 = (k, v)
+            if shared:
+                k, v = kv0
+            a = P.linear(P.causal_attention(q, k, v), w["model.layers.0.self_attn.o_proj.weight"])
+        x = x + a
+        x = x + ff(layer, x)
+    return P.linear(P.rms_norm(x, w["model.norm.weight"], 1e-6),
+                    w["model.embed_tokens.weight"]).numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype, tmp_path):
+    _register_toy()
+    from servelab_b200.config import config_from_dict
+    from servelab_b200.replay import TraceSession
+    from servelab_b200.weights import write_random_model
+    folder = write_random_model(str(tmp_path / "toy"), config_from_dict(TOY), seed=5)
+    reqs = {f"t{i}": H.random_ids(n, 130, 50 + i) for i, n in enumerate([41, 60, 35, 52])}
+    ref = {rid: _toy_plain(folder, ids) for rid, ids in reqs.items()}
+    for steps in (H.trace_whole(reqs), H.trace_portions(reqs),
+                  H.trace_mixed(reqs, seed=2, max_live=2)):
+        sess = TraceSession(folder, dtype, H.peak_tokens(steps), page_size=8, max_live=2)
+        storage = sess.runner.storage
+        assert len(storage.groups) == 1 and len(storage.groups[0].layers) == 2   # runs 0 and 2
+        assert storage.state_layers == [1]
+        got = H.collect(steps, H.run_session(sess, steps), 130)
+        for rid, ids in reqs.items():
+            for pos in range(len(ids)):
+                err = float(np.abs(got[rid][pos] - ref[rid][pos]).max())
+                assert err <= TOL[dtype] * 2, (rid, pos, err)
+        sess.cache.check_invariants()
+        assert sess.cache.slots.num_free() == 2
