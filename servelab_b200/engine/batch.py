@@ -60,7 +60,10 @@ class StepContext:
     # ------------------------------------------------------------ packing
     @classmethod
     def pack(cls, entries: Sequence[BatchEntry], num_groups: int, device: str,
-             min_table_width: int = 1) -> "StepContext":
+             min_table_width: int = 1, into: Optional["StepContext"] = None) -> "StepContext":
+        """``into``: a context packed earlier for the same number of requests,
+        tokens, wanted rows and table widths; its device buffer is overwritten in
+        place (a captured CUDA graph keeps reading the same addresses)."""
         ctx = cls(device)
         S = len(entries)
         q_lens = [len(e.tokens) for e in entries]
@@ -106,8 +109,19 @@ class StepContext:
                 for s, e in enumerate(entries):
                     row = e.block_tables[g]
                     tab[s, :len(row)] = row
+        if into is not None:
+            if into._dev.numel() != total or into._layout != (T, S, R, tuple(widths)):
+                raise ValueError("batch does not have the shape of the context to overwrite")
+            into._dev.copy_(host, non_blocking=True)
+            into._host = host
+            into.q_lens, into.state_slot_ids = q_lens, [e.state_slot for e in entries]
+            into.ctx_lens = [e.start + n for e, n in zip(entries, q_lens)]
+            into.max_ctx_len = max(into.ctx_lens) if into.ctx_lens else 0
+            return into
         dev = host.to(device, non_blocking=True)
         ctx._host = host                              # keep the pinned buffer alive
+        ctx._dev = dev
+        ctx._layout = (T, S, R, tuple(widths))
 
         def view(o, n):
             return dev[o:o + n]

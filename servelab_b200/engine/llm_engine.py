@@ -38,7 +38,8 @@ class LLMEngine:
                  scheduler_config: Optional[SchedulerConfig] = None, seed: int = 1234,
                  dtype: str = "bfloat16", device: str = "cuda:0", tokenizer=None,
                  clock: Optional[Callable[[], float]] = None,
-                 weights: Optional[WeightSource] = None, cuda_graphs: bool = True):
+                 weights: Optional[WeightSource] = None, cuda_graphs: bool = True,
+                 max_model_len: Optional[int] = None):
         """``model``: a model folder (config.json + safetensors), or a typed
         architecture config together with ``weights``."""
         if isinstance(model, str):
@@ -53,12 +54,12 @@ class LLMEngine:
         self.tokenizer = tokenizer
         self.clock = clock or time.monotonic
         self.runner = ModelRunner(config, weights, dtype=dtype, cache_config=self.cache_config,
-                                  max_num_seqs=self.scheduler_config.max_num_seqs, device=device)
-        self.runner.cuda_graphs = cuda_graphs
+                                  max_num_seqs=self.scheduler_config.max_num_seqs, device=device,
+                                  cuda_graphs=cuda_graphs, max_model_len=max_model_len)
         spec = self.runner.spec
         self.scheduler = Scheduler(self.scheduler_config, self.runner.cache, self.clock,
                                    eos_token_ids=spec.eos_token_ids,
-                                   max_model_len=spec.max_position_embeddings)
+                                   max_model_len=self.runner.max_model_len)
         self.sampler = Sampler(seed, device)
         self._req_counter = 0
         self.num_steps = 0

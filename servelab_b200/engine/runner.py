@@ -31,7 +31,8 @@ _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 class ModelRunner:
     def __init__(self, config, weights: WeightSource, dtype: str = "bfloat16",
                  cache_config: Optional[CacheConfig] = None, max_num_seqs: int = 64,
-                 device: str = "cuda:0"):
+                 device: str = "cuda:0", cuda_graphs: bool = False,
+                 max_model_len: Optional[int] = None):
         K.require_cuda()
         if dtype not in _DTYPES:
             raise ValueError(f"dtype must be bfloat16 or float32, got {dtype}")
@@ -60,6 +61,18 @@ class ModelRunner:
         self.cache = CacheManager(self.storage.group_windows, num_pages, self.page_size,
                                   max_num_seqs, reserve_pages=cache_config.reserve_blocks)
         self.num_groups = len(self.storage.groups)
+        self.max_model_len = min(max_model_len or self.spec.max_position_embeddings,
+                                 self.spec.max_position_embeddings, num_pages * self.page_size)
+        # decode-only steps replay a CUDA graph per batch size (fixed addresses,
+        # block tables padded to the longest request the engine admits)
+        self.cuda_graphs = cuda_graphs
+        self.max_graph_batch = max_num_seqs
+        self._graphs = {}
+        self._graph_pool = None
+        self._graph_safe = not self.storage.state_layers and all(
+            getattr(b, "graph_safe", False) for b in self.model.blocks)
+        self.graph_replays = 0
+        self.graph_kernel_launches = {}   # batch size -> this package's kernels per replay
 
     @classmethod
     def from_folder(cls, folder: str, **kw) -> "ModelRunner":
@@ -84,7 +97,35 @@ class ModelRunner:
     def step(self, entries: List[BatchEntry]) -> torch.Tensor:
         """Logits [wanted, vocab] float32 (on the device) of this batch."""
         self.storage.clear_state_slots(self.cache.slots.drain_to_clear())
+        if (self.cuda_graphs and self._graph_safe and 0 < len(entries) <= self.max_graph_batch
+                and all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries)):
+            return self._step_graph(entries)
         ctx = StepContext.pack(entries, self.num_groups, self.device)
         if ctx.num_tokens == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         return self.model.forward(ctx, self.storage.layer_caches)
+
+    def _step_graph(self, entries: List[BatchEntry]) -> torch.Tensor:
+        """A step of single decoded tokens, all wanting logits: replay the graph
+        captured for this batch size.  The returned logits live in the graph's
+        memory and are overwritten by the next replay of the same size."""
+        B = len(entries)
+        width = -(-self.max_model_len // self.page_size)
+        hit = self._graphs.get(B)
+        if hit is None:
+            ctx = StepContext.pack(entries, self.num_groups, self.device, min_table_width=width)
+            self.model.forward(ctx, self.storage.layer_caches)      # warm-up outside capture
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            before = K.launch_count
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                logits = self.model.forward(ctx, self.storage.layer_caches)
+            self.graph_kernel_launches[B] = K.launch_count - before
+            hit = self._graphs[B] = (graph, ctx, logits)
+        graph, ctx, logits = hit
+        StepContext.pack(entries, self.num_groups, self.device, min_table_width=width, into=ctx)
+        graph.replay()
+        self.graph_replays += 1
+        return logits

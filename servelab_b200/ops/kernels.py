@@ -16,7 +16,12 @@ from . import library as L
 _F32, _BF16 = torch.float32, torch.bfloat16
 
 
+launch_count = 0       # launches of this package's kernels (library GEMMs not included)
+
+
 def _stream() -> int:
+    global launch_count
+    launch_count += 1
     return torch.cuda.current_stream().cuda_stream
 
 

@@ -31,6 +31,8 @@ from .registry import POSITIONS, build_part, register_mixer
 
 @register_mixer("paged_attention")
 class PagedAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, spec, prefix, env):
         super().__init__(spec, prefix, env)
         if spec.num_heads % spec.num_kv_heads:

@@ -62,6 +62,10 @@ class LayerCache:
 
 
 class Part:
+    # True iff forward() only launches kernels on device buffers of the step
+    # context (no host-side reads of the batch), so a step can be graph-captured
+    graph_safe = False
+
     def __init__(self, spec, prefix: str, env: BuildEnv):
         self.spec, self.prefix, self.env = spec, prefix, env
 

@@ -17,6 +17,13 @@ from .registry import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, build_part, part_cl
 class PreNormBlock(Block):
     def __init__(self, spec, prefix, env):
         super().__init__(spec, prefix, env)
+        self._build(spec, prefix, env)
+        # a step of this block may be captured in a CUDA graph iff every part only
+        # launches kernels whose arguments are device buffers of the step context
+        self.graph_safe = all(getattr(p, "graph_safe", False) for p in
+                              (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward))
+
+    def _build(self, spec, prefix, env):
         self.mixer_norm = build_part(NORMS, spec.mixer_norm, prefix + ".input_layernorm", env)
         self.mixer = build_part(MIXERS, spec.mixer, prefix + ".self_attn", env)
         self.ff_norm = build_part(NORMS, spec.ff_norm, prefix + ".post_attention_layernorm", env)

@@ -16,6 +16,8 @@ from .registry import register_feed_forward
 
 @register_feed_forward("gated_mlp")
 class GatedMLP(FeedForward):
+    graph_safe = True
+
     def __init__(self, spec, prefix, env):
         super().__init__(spec, prefix, env)
         if spec.activation != "silu":

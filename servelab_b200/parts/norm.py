@@ -17,6 +17,8 @@ from .registry import register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
+    graph_safe = True
+
     @classmethod
     def declare(cls, spec, prefix):
         return [TensorDecl(prefix + ".weight", (spec.dim,), NORM)]
