@@ -32,8 +32,8 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--compiler-options", "-fPIC",
               "-Xcudafe", "--diag_suppress=177"]
 
 CORE_SOURCES = ["elementwise.cu", "rope_cache.cu", "attention_generic.cu", "gemm_simt.cu",
-                "sampling.cu", "attention_decode.cu", "gemm_skinny.cu", "no_alloc.cu"]
-HEADERS = ["common.cuh", "attention_mma.cuh", "no_alloc.h"]
+                "sampling.cu", "gemm_skinny.cu"]
+HEADERS = ["common.cuh"]
 
 _lock = threading.Lock()
 _done: Dict[str, str] = {}

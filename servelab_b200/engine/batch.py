@@ -51,6 +51,7 @@ class StepContext:
         self.ctx_lens: List[int] = []
         self.decode_only = False
         self.max_ctx_len = 0
+        self.split_hint_len = 0       # context length the decode kernel sizes its splits for
         self.token_ids = self.positions = self.seq_of_token = None
         self.cu_q = self.ctx_len = self.state_slots = self.logit_rows = None
         self.block_tables: List[torch.Tensor] = []
@@ -135,6 +136,7 @@ class StepContext:
         ctx.state_slot_ids = [e.state_slot for e in entries]
         ctx.ctx_lens = [e.start + n for e, n in zip(entries, q_lens)]
         ctx.max_ctx_len = max(ctx.ctx_lens) if ctx.ctx_lens else 0
+        ctx.split_hint_len = ctx.max_ctx_len
         ctx.decode_only = S > 0 and all(n == 1 for n in q_lens)
         return ctx
 

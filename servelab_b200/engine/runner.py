@@ -114,6 +114,7 @@ class ModelRunner:
         hit = self._graphs.get(B)
         if hit is None:
             ctx = StepContext.pack(entries, self.num_groups, self.device, min_table_width=width)
+            ctx.split_hint_len = self.max_model_len     # launch shapes must not depend on the step
             self.model.forward(ctx, self.storage.layer_caches)      # warm-up outside capture
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()

@@ -1,9 +1,10 @@
 """Chooses and launches the attention kernel for a step.
 
   float32                      plain kernel (CUDA cores, float32 throughout)
-  bfloat16, all q_len == 1     split-KV decode kernel (tensor cores), when built
-  bfloat16, otherwise          tensor-core prefill kernel for the head size, when
-                               built; else the plain kernel
+  bfloat16, all q_len == 1     split-KV decode kernel (tensor cores)
+  bfloat16, otherwise          tensor-core prefill kernel
+  bfloat16, head size not a    plain kernel
+  multiple of 16
 
 ``force_generic`` switches every call to the plain kernel (tests and
 measurements compare the fast kernels with it).
@@ -37,12 +38,12 @@ def _generic(ctx, q, k_cache, v_cache, out, table, H, Hkv, D, page_size, scale, 
 
 def paged_attention(ctx, q, k_cache, v_cache, out, table, H, Hkv, D, page_size, scale,
                     window) -> None:
-    if q.dtype == torch.bfloat16 and not force_generic:
-        if ctx.decode_only and use_decode_kernel and K.has_decode_attention(D, H // Hkv):
+    if q.dtype == torch.bfloat16 and not force_generic and K.has_fast_attention(D):
+        if ctx.decode_only and use_decode_kernel:
             K.decode_attention(ctx, q, k_cache, v_cache, out, table, H, Hkv, D, page_size, scale,
                                window)
             return
-        if use_prefill_kernel and K.has_prefill_attention(D):
+        if use_prefill_kernel:
             K.prefill_attention(ctx, q, k_cache, v_cache, out, table, H, Hkv, D, page_size,
                                 scale, window)
             return

@@ -128,13 +128,62 @@ def sample_rows(logits: torch.Tensor, out: torch.Tensor, temperature=None, top_k
         _p(seed), _p(stream), _p(position), out.data_ptr(), _stream()), "sample_rows")
 
 
-# ------------------------------------------- optional fast kernels (bfloat16)
-def has_decode_attention(head_dim: int, group: int) -> bool:
-    return False
+# ------------------------------------- tensor-core attention (bfloat16 only)
+_sm_count = None
 
 
-def has_prefill_attention(head_dim: int) -> bool:
-    return False
+def _num_sms() -> int:
+    global _sm_count
+    if _sm_count is None:
+        _sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _sm_count
+
+
+def has_fast_attention(head_dim: int) -> bool:
+    """The tensor-core kernels exist for head sizes that are multiples of 16 up to
+    256; the library for a head size is built when it is first asked for."""
+    return head_dim % 16 == 0 and 16 <= head_dim <= 256
+
+
+def prefill_attention(ctx, q, k_cache, v_cache, out, block_table, num_heads, num_kv_heads,
+                      head_dim, page_size, scale, window) -> None:
+    lib = L.attention(head_dim)
+    tile_seq, tile_row0, n = ctx.attention_tiles(num_heads // num_kv_heads,
+                                                 lib.slb_prefill_attention_tile_rows())
+    L.check(lib.slb_prefill_attention_bf16(
+        q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+        out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.cu_q.data_ptr(),
+        ctx.ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), n, num_heads,
+        num_kv_heads, page_size, float(scale), int(window), _stream()), "prefill_attention")
+
+
+def decode_splits(num_seqs: int, num_kv_heads: int, group: int, longest_context: int,
+                  max_splits: int) -> int:
+    """How many ways the keys of each request are split: enough blocks for two per
+    SM, at most one split per 64 keys of the longest context."""
+    ctas = num_seqs * num_kv_heads * ((group + 15) // 16)
+    want = max(1, (2 * _num_sms()) // max(ctas, 1))
+    return max(1, min(want, max_splits, -(-longest_context // 64)))
+
+
+def decode_attention(ctx, q, k_cache, v_cache, out, block_table, num_heads, num_kv_heads,
+                     head_dim, page_size, scale, window) -> None:
+    """Attention for a step of single tokens (every q_len == 1)."""
+    lib = L.attention(head_dim)
+    S = ctx.num_seqs
+    splits = decode_splits(S, num_kv_heads, num_heads // num_kv_heads, ctx.split_hint_len,
+                           lib.slb_decode_attention_max_splits())
+    scratch = None
+    if splits > 1:
+        nbytes = lib.slb_decode_attention_scratch_bytes(S, num_heads, splits)
+        scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=q.device)
+    L.check(lib.slb_decode_attention_bf16(
+        q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+        out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.ctx_len.data_ptr(),
+        _p(scratch), S, num_heads, num_kv_heads, page_size, float(scale), int(window), splits,
+        _stream()), "decode_attention")
+    global launch_count
+    launch_count += 1 if splits > 1 else 0          # the combine kernel
 
 
 def gemm_skinny(x, w, out, bias=None) -> None:

@@ -44,8 +44,6 @@ _CORE_SIGNATURES = {
 
 # optional entry points: declared when the library exports them
 _OPTIONAL_SIGNATURES = {
-    "slb_decode_attention_bf16": [P, I, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
-    "slb_decode_attention_max_splits": [],
     "slb_gemm_skinny_bf16": [P, I, P, I, P, I, P, P, I, I, I, I, P],
 }
 
@@ -80,8 +78,10 @@ def core() -> ctypes.CDLL:
 
 _ATTN_SIGNATURES = {
     "slb_prefill_attention_bf16": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, F, I, P],
+    "slb_decode_attention_bf16": [P, I, P, P, P, I, P, I, P, P, I, I, I, I, F, I, I, P],
     "slb_prefill_attention_tile_rows": [],
-    "slb_prefill_attention_head_dim": [],
+    "slb_decode_attention_max_splits": [],
+    "slb_attention_head_dim": [],
 }
 
 
@@ -95,6 +95,11 @@ def attention(head_dim: int) -> ctypes.CDLL:
             raise KernelsUnavailable(
                 f"the attention kernels for head size {head_dim} are not available: {e}") from e
         _declare(lib, _ATTN_SIGNATURES, True)
+        lib.slb_decode_attention_scratch_bytes.argtypes = [I, I, I]
+        lib.slb_decode_attention_scratch_bytes.restype = ctypes.c_longlong
+        if lib.slb_attention_head_dim() != head_dim:
+            raise KernelsUnavailable(f"attention library built for head size "
+                                     f"{lib.slb_attention_head_dim()}, wanted {head_dim}")
         _libs[key] = lib
     return lib
 

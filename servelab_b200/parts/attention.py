@@ -42,6 +42,10 @@ class PagedAttention(Mixer):
         self.q_size = spec.num_heads * spec.head_dim
         self.kv_size = spec.num_kv_heads * spec.head_dim
         A.check_supported(spec.head_dim, env.dtype)
+        if env.dtype == torch.bfloat16 and K.has_fast_attention(spec.head_dim) \
+                and torch.cuda.is_available():
+            from ..ops import library
+            library.attention(spec.head_dim)      # built now, not in the middle of a step
 
     @classmethod
     def declare(cls, spec, prefix):

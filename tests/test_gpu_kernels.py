@@ -342,3 +342,79 @@ def test_sampler_mixes_greedy_and_random_rows_and_follows_the_distribution():
     counts = np.bincount([got[i] for i in range(0, R, 2)], minlength=V) / (R / 2)
     want = torch.softmax(row.double() / 1.3, -1).numpy()
     assert np.abs(counts - want).max() < 0.03
+
+
+# -------------------------------------------- tensor-core attention (bfloat16)
+def _ctx_for(case):
+    from servelab_b200.engine.batch import StepContext
+    q, table, cu, ctx_len = case.device_args()
+    ctx = StepContext(DEV)
+    ctx.q_lens, ctx.num_seqs = case.q_lens, len(case.q_lens)
+    ctx.cu_q, ctx.ctx_len = cu, ctx_len
+    ctx.max_ctx_len = ctx.split_hint_len = max(case.ctx_lens)
+    return ctx, q, table
+
+
+@pytest.mark.parametrize("H,Hkv,D,ps", [(6, 2, 16, 16), (7, 1, 64, 8), (4, 2, 48, 4),
+                                        (28, 4, 128, 16), (2, 1, 256, 32), (20, 1, 32, 16)])
+@pytest.mark.parametrize("window", [0, 40])
+def test_prefill_attention_tensor_cores(H, Hkv, D, ps, window):
+    case = PagedCase([37, 150, 1, 263, 34, 300], [37, 19, 1, 1, 2, 300], H, Hkv, D, ps,
+                     torch.bfloat16, seed=D + window)
+    case.scatter()
+    ctx, q, table = _ctx_for(case)
+    out = torch.empty_like(q)
+    K().prefill_attention(ctx, q, case.kc, case.vc, out, table, H, Hkv, D, ps, 1 / math.sqrt(D), window)
+    want = case.reference(window=window or None)
+    assert (out.float().cpu() - want).abs().max() <= TOL["bfloat16"]
+    plain = run_generic(case, window=window)
+    assert (out.float().cpu() - plain).abs().max() <= TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("H,Hkv,D,ps", [(6, 2, 16, 16), (7, 1, 64, 8), (4, 2, 48, 4),
+                                        (28, 4, 128, 16), (2, 1, 256, 32), (20, 1, 32, 16)])
+@pytest.mark.parametrize("window", [0, 70])
+@pytest.mark.parametrize("splits", [1, 3, 32])
+def test_decode_attention_tensor_cores(H, Hkv, D, ps, window, splits):
+    from servelab_b200.ops import library as L
+    ctxs = [1, 63, 64, 65, 700, 2049, 17]
+    case = PagedCase(ctxs, [1] * len(ctxs), H, Hkv, D, ps, torch.bfloat16, seed=D + splits)
+    case.scatter()
+    ctx, q, table = _ctx_for(case)
+    out = torch.full_like(q, 7.0)
+    lib = L.attention(D)
+    S = len(ctxs)
+    scratch = torch.full((max(1, lib.slb_decode_attention_scratch_bytes(S, H, splits) // 4),),
+                         float("nan"), device=DEV)
+    L.check(lib.slb_decode_attention_bf16(
+        q.data_ptr(), q.stride(0), case.kc.data_ptr(), case.vc.data_ptr(), out.data_ptr(),
+        out.stride(0), table.data_ptr(), table.shape[1], ctx.ctx_len.data_ptr(),
+        scratch.data_ptr(), S, H, Hkv, ps, 1 / math.sqrt(D), window, splits,
+        torch.cuda.current_stream().cuda_stream), "decode")
+    want = case.reference(window=window or None)
+    assert (out.float().cpu() - want).abs().max() <= TOL["bfloat16"]
+    # the dispatching wrapper (its own choice of splits) gives the same
+    out2 = torch.empty_like(q)
+    K().decode_attention(ctx, q, case.kc, case.vc, out2, table, H, Hkv, D, ps, 1 / math.sqrt(D), window)
+    assert (out2.float().cpu() - want).abs().max() <= TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("needle", [0, 63, 64, 1023, 1024, 1500])
+def test_fast_attention_finds_one_far_key(needle):
+    H, Hkv, D, ps = 14, 2, 128, 16
+    for q_len in (1, 5):
+        case = PagedCase([1501], [q_len], H, Hkv, D, ps, torch.bfloat16, seed=needle)
+        for kvh in range(Hkv):
+            qdir = case.q[0][-1, kvh * 7].float()
+            case.k[0][needle, kvh] = (qdir * 60 / qdir.norm()).to(case.dt)
+            for h in range(7):
+                case.q[0][-1, kvh * 7 + h] = case.q[0][-1, kvh * 7]
+        case.q[0] = (case.q[0].float() * 8).to(case.dt)
+        case.scatter()
+        ctx, q, table = _ctx_for(case)
+        out = torch.empty_like(q)
+        fn = K().decode_attention if q_len == 1 else K().prefill_attention
+        fn(ctx, q, case.kc, case.vc, out, table, H, Hkv, D, ps, 1 / math.sqrt(D), 0)
+        got = out.float().cpu().view(q_len, H, D)[-1]
+        for h in range(H):
+            assert (got[h] - case.v[0][needle, h // 7].float()).abs().max() <= 3e-2
