@@ -533,3 +533,72 @@ int slb_decode_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf16
 }
 
 }  // extern "C"
+
+// --------------------------------------------------------------------------
+// The same decode attention for callers that may not allocate (see no_alloc.h).
+// --------------------------------------------------------------------------
+#include "no_alloc.h"
+
+namespace {
+
+constexpr long long NOALLOC_SCRATCH_BYTES = 4ll << 20;
+constexpr int NOALLOC_MAX_DEVICES = 64;
+
+// The scratch lives in the library image.  In host code this name is only a
+// handle for the runtime, not an address a kernel could use: the device address
+// is looked up per device below.
+static __device__ __align__(256) float noalloc_scratch[NOALLOC_SCRATCH_BYTES / sizeof(float)];
+
+float* noalloc_scratch_on_device[NOALLOC_MAX_DEVICES] = {nullptr};
+
+// Device address of the scratch on the current device; looked up on first use.
+int noalloc_scratch_address(float** ptr) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return SLB_ERR_BAD_ARG;
+    if (noalloc_scratch_on_device[dev] == nullptr) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, noalloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (p == nullptr) return SLB_ERR_BAD_ARG;
+        noalloc_scratch_on_device[dev] = p;
+    }
+    *ptr = noalloc_scratch_on_device[dev];
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+long long slb_decode_attention_noalloc_capacity_bytes(void) { return NOALLOC_SCRATCH_BYTES; }
+
+const char* slb_decode_attention_noalloc_strerror(int code) {
+    switch (code) {
+        case 0: return "success";
+        case SLB_ERR_BAD_ARG: return "an argument is not taken (sizes, alignment, or device index)";
+        case SLB_ERR_TOO_LARGE:
+            return "S * H * num_splits * (head_dim + 2) * 4 bytes exceed the built-in scratch "
+                   "(slb_decode_attention_noalloc_capacity_bytes), or a launch dimension is too "
+                   "large: use fewer splits or fewer requests per call";
+        default: return "CUDA runtime error (the code is a cudaError_t)";
+    }
+}
+
+int slb_decode_attention_bf16_noalloc(const bf16* q, int ldq, const bf16* kc, const bf16* vc,
+                                      bf16* out, int ldo, const int* block_table, int max_pages,
+                                      const int* ctx_len, int S, int H, int Hkv, int ps, float scale,
+                                      int window, int num_splits, cudaStream_t st) {
+    if (S <= 0) return 0;
+    if (H <= 0 || num_splits < 1) return SLB_ERR_BAD_ARG;
+    if (slb_decode_attention_scratch_bytes(S, H, num_splits) > NOALLOC_SCRATCH_BYTES)
+        return SLB_ERR_TOO_LARGE;
+    float* scratch = nullptr;
+    const int rc = noalloc_scratch_address(&scratch);
+    if (rc != 0) return rc;
+    return slb_decode_attention_bf16(q, ldq, kc, vc, out, ldo, block_table, max_pages, ctx_len,
+                                     scratch, S, H, Hkv, ps, scale, window, num_splits, st);
+}
+
+}  // extern "C"

@@ -33,7 +33,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--compiler-options", "-fPIC",
 
 CORE_SOURCES = ["elementwise.cu", "rope_cache.cu", "attention_generic.cu", "gemm_simt.cu",
                 "sampling.cu", "gemm_skinny.cu"]
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "no_alloc.h"]
 
 _lock = threading.Lock()
 _done: Dict[str, str] = {}
