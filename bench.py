@@ -63,7 +63,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "25"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -116,6 +116,14 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (0 = all)")
     ap.add_argument("--skip-points", action="store_true", help="no batch 1/64 and no prefill")
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+                    help="profiling aid: run only the decode loop or only the prefill")
+    ap.add_argument("--no-graphs", action="store_true", help="profiling aid: launch kernels eagerly")
+    ap.add_argument("--tune", action="append", default=[], metavar="NAME=VALUE",
+                    help="measurement aid: set a dispatch tunable (skinny_max_tokens, "
+                         "decode_ctas_per_sm, pdl)")
+    ap.add_argument("--profile-region", action="store_true",
+                    help="profiling aid: cudaProfilerStart/Stop around the device-timed region")
     args = ap.parse_args(argv)
 
     if args.impl == "reference":
@@ -137,12 +145,27 @@ def main(argv=None) -> int:
     from servelab_b200.sampling import SamplingParams
     from servelab_b200.weights import RandomSource
 
+    from servelab_b200.ops import linear as linear_ops
+    for item in args.tune:
+        name, value = item.split("=")
+        if name == "skinny_max_tokens":
+            linear_ops.skinny_max_tokens = int(value)
+        elif name == "decode_ctas_per_sm":
+            K.decode_ctas_per_sm = int(value)
+        elif name == "pdl":
+            from servelab_b200.ops import library as kernel_library
+            kernel_library.set_pdl(bool(int(value)))
+        else:
+            raise SystemExit(f"unknown tunable {name}")
+
     cfg = dict(QWEN25_7B)
     full_layers = cfg["num_hidden_layers"]
     layers = args.layers or full_layers
     cfg["num_hidden_layers"] = layers
     config = config_from_dict(cfg)
     peaks = load_peaks()
+    if args.only:
+        args.skip_points = True
     max_batch = 64 if not args.skip_points else max(args.batch, 1)
     max_batch = max(max_batch, args.batch)
     pages = max_batch * (CONTEXT // PAGE) + 64
@@ -150,7 +173,8 @@ def main(argv=None) -> int:
                           dtype=torch.bfloat16)
     engine = LLMEngine(config, CacheConfig(block_size=PAGE, num_blocks=pages),
                        SchedulerConfig(max_num_seqs=max_batch, max_num_batched_tokens=PROMPT_LEN),
-                       dtype="bfloat16", weights=source, cuda_graphs=True, max_model_len=CONTEXT)
+                       dtype="bfloat16", weights=source, cuda_graphs=not args.no_graphs,
+                       max_model_len=CONTEXT)
     runner = engine.runner
     gen = torch.Generator().manual_seed(1)
     V = cfg["vocab_size"]
@@ -172,7 +196,8 @@ def main(argv=None) -> int:
         for _ in range(warmup):
             engine.step()
         torch.cuda.synchronize()
-        launches0, replays0 = K.launch_count, runner.graph_replays
+        if clocks:
+            clocks.start()
         t0 = time.perf_counter()
         for _ in range(steps):
             engine.step()
@@ -188,15 +213,17 @@ def main(argv=None) -> int:
         for _ in range(warmup):
             K.sample_rows(runner.step(entries), out_ids)
         torch.cuda.synchronize()
-        if clocks:
-            clocks.start()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         k0 = K.launch_count
+        if args.profile_region:
+            torch.cuda.profiler.start()
         start.record()
         for _ in range(steps):
             K.sample_rows(runner.step(entries), out_ids)
         stop.record()
         torch.cuda.synchronize()
+        if args.profile_region:
+            torch.cuda.profiler.stop()
         dev_ms = start.elapsed_time(stop) / steps
         clk = clocks.stop() if clocks else None
         ctx_tokens = sum(s.get_len() for s in seqs)
@@ -208,6 +235,37 @@ def main(argv=None) -> int:
         return {"dev_ms": dev_ms, "e2e_ms": e2e_s * 1000 / steps, "ctx_tokens": ctx_tokens,
                 "launches": launches, "h2d": desc_bytes, "d2h": batch * 4, "clocks": clk}
 
+    def run_prefill():
+        """One 2,048-token prompt through the step function, timed on the device
+        (median of the runs after two warm-ups)."""
+        ids = prompts(1)[0]
+        times = []
+        for i in range(5):
+            rid = f"prefill-{i}"
+            runner.cache.open(rid)
+            runner.cache.ensure(rid, PROMPT_LEN)
+            entry = runner.entry(rid, ids, 0, (PROMPT_LEN - 1,))
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            if args.profile_region and i == 4:
+                torch.cuda.profiler.start()
+            start.record()
+            runner.step([entry])
+            stop.record()
+            torch.cuda.synchronize()
+            if args.profile_region and i == 4:
+                torch.cuda.profiler.stop()
+            times.append(start.elapsed_time(stop))
+            runner.cache.release(rid)
+        ms = sorted(times[2:])[len(times[2:]) // 2]
+        flops = prefill_flops(cfg, layers, PROMPT_LEN)
+        return {"value": round(PROMPT_LEN / (ms * 1e-3), 1), "tokens": PROMPT_LEN,
+                "ms": round(ms, 3),
+                "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "layers": layers, "prefill": run_prefill()}))
+        return 0
     clocks = ClockSampler()
     main_run = run_decode(args.batch, args.steps, args.warmup, clocks)
     wbytes, _ = weight_bytes_per_step(cfg, layers)
@@ -226,7 +284,7 @@ def main(argv=None) -> int:
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": V, "page_size": PAGE,
-                   "parallelism": "single GPU", "cuda_graphs": True,
+                   "parallelism": "single GPU", "cuda_graphs": not args.no_graphs,
                    "l2": "weights (14 GB) exceed L2; no flush", "peaks": peaks["source"]},
         "e2e": {"value": round(args.batch / (main_run["e2e_ms"] * 1e-3), 1), "unit": "tok/s",
                 "ms_per_step": round(main_run["e2e_ms"], 4),
@@ -237,27 +295,7 @@ def main(argv=None) -> int:
         "clocks": main_run["clocks"],
     }
     if not args.skip_points:
-        # prefill of one 2,048-token prompt, timed on the device
-        ids = prompts(1)[0]
-        times = []
-        for i in range(5):
-            rid = f"prefill-{i}"
-            runner.cache.open(rid)
-            runner.cache.ensure(rid, PROMPT_LEN)
-            entry = runner.entry(rid, ids, 0, (PROMPT_LEN - 1,))
-            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            start.record()
-            runner.step([entry])
-            stop.record()
-            torch.cuda.synchronize()
-            times.append(start.elapsed_time(stop))
-            runner.cache.release(rid)
-        ms = sorted(times[2:])[len(times[2:]) // 2]
-        flops = prefill_flops(cfg, layers, PROMPT_LEN)
-        result["prefill"] = {"value": round(PROMPT_LEN / (ms * 1e-3), 1), "tokens": PROMPT_LEN,
-                             "ms": round(ms, 3),
-                             "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+        result["prefill"] = run_prefill()
         points = {}
         for b in (1, 64):
             r = run_decode(b, max(16, args.steps // 2), args.warmup)

@@ -36,6 +36,7 @@ __global__ void __launch_bounds__(AG_THREADS) paged_attention_generic_kernel(
     const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
     int H, int Hkv, int D, int ps, float scale, int window) {
     extern __shared__ float smem[];
+    pdl_wait();
     const int ldd = D + 1;
     float* Qs = smem;
     float* Ks = Qs + AG_BM * ldd;
@@ -180,10 +181,9 @@ static int launch_generic(const T* q, int ldq, const T* kc, const T* vc, T* out,
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    paged_attention_generic_kernel<T><<<dim3(num_tiles, Hkv), AG_THREADS, smem, st>>>(
-        q, ldq, kc, vc, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq, tile_row0, H,
-        Hkv, D, ps, scale, window);
-    return slb_launch_status();
+    return slb_launch(paged_attention_generic_kernel<T>, dim3(num_tiles, Hkv), dim3(AG_THREADS), smem,
+                      st, q, ldq, kc, vc, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq,
+                      tile_row0, H, Hkv, D, ps, scale, window);
 }
 
 extern "C" {

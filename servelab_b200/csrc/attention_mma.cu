@@ -42,6 +42,7 @@ constexpr int KSTEPS = D / 16;        // k-steps of Q.K^T
 constexpr int NT_O = D / 8;           // 8-wide column tiles of the output
 constexpr int STAGE_ELEMS = 2 * BN * LDS;                 // K tile + V tile
 constexpr int MAX_SPLITS = 32;
+constexpr int DSTAGES = 3;            // key/value tiles buffered by the decode kernel
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gptr, bool valid) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -82,14 +83,18 @@ __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __r
                                              const bf16* __restrict__ vc,
                                              const int* __restrict__ table, int k0, int kend,
                                              int kvh, int Hkv, int ps) {
+    const bool pow2 = (ps & (ps - 1)) == 0;
+    const int shift = __ffs(ps) - 1;
     for (int idx = threadIdx.x; idx < BN * CHUNKS; idx += NTHREADS) {
         const int r = idx / CHUNKS, c = idx - r * CHUNKS;
         const int kp = k0 + r;
         bool ok = kp < kend;
+        const int lp = pow2 ? kp >> shift : kp / ps;
+        const int slot = pow2 ? kp & (ps - 1) : kp - lp * ps;
         int page = -1;
-        if (ok) page = table[kp / ps];
+        if (ok) page = table[lp];
         ok = ok && page >= 0;
-        const size_t off = ok ? (((size_t)page * Hkv + kvh) * ps + kp % ps) * D + c * 8 : 0;
+        const size_t off = ok ? (((size_t)page * Hkv + kvh) * ps + slot) * D + c * 8 : 0;
         cp_async16(Ks + r * LDS + c * 8, kc + off, ok);
         cp_async16(Vs + r * LDS + c * 8, vc + off, ok);
     }
@@ -152,8 +157,10 @@ __device__ __forceinline__ void pv_tile(float (&o)[NT_O][4], const float (&p)[NT
 // Online-softmax update of one thread's two rows (lane/4 and lane/4 + 8) for a
 // score tile whose first key sits at position kpos0.  pos_lo / pos_hi are the
 // rows' query positions (-1: padding row, sees nothing).  Scores arrive raw and
-// leave as probabilities relative to the new running max.
-template <int NT>
+// leave as probabilities relative to the new running max (kept in the base-2
+// domain, i.e. already multiplied by scale*log2 e).  MASKED = false is the fast
+// path for tiles every row of the warp sees completely.
+template <int NT, bool MASKED>
 __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[NT_O][4], float (&m)[2],
                                              float (&l)[2], int kpos0, int kend, int pos_lo,
                                              int pos_hi, int window, float scale_log2) {
@@ -163,33 +170,41 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[NT_O]
     for (int j = 0; j < NT; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const int kp = kpos0 + j * 8 + tig * 2 + (e & 1);
-            const int pos = (e < 2) ? pos_lo : pos_hi;
-            const bool vis = kp < kend && kp <= pos && (window <= 0 || pos - kp < window);
-            s[j][e] = vis ? s[j][e] * scale_log2 : -INFINITY;
+            if (MASKED) {
+                const int kp = kpos0 + j * 8 + tig * 2 + (e & 1);
+                const int pos = (e < 2) ? pos_lo : pos_hi;
+                const bool vis = kp < kend && kp <= pos && (window <= 0 || pos - kp < window);
+                if (!vis) s[j][e] = -INFINITY;
+            }
             mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
         }
     }
+    float alpha[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-        const float m_new = fmaxf(m[h], mx[h]);
+        const float m_new = fmaxf(m[h], mx[h] * scale_log2);      // scale_log2 > 0
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = exp2f(m[h] - m_use);          // 0 while nothing was seen
+        alpha[h] = exp2f(m[h] - m_use);                            // 0 while nothing was seen
         m[h] = m_new;
         float sum = 0.f;
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
-            s[j][2 * h] = exp2f(s[j][2 * h] - m_use);
-            s[j][2 * h + 1] = exp2f(s[j][2 * h + 1] - m_use);
+            s[j][2 * h] = exp2f(fmaf(s[j][2 * h], scale_log2, -m_use));
+            s[j][2 * h + 1] = exp2f(fmaf(s[j][2 * h + 1], scale_log2, -m_use));
             sum += s[j][2 * h] + s[j][2 * h + 1];
         }
-        l[h] = l[h] * alpha + sum;                        // partial over this thread's columns
+        l[h] = l[h] * alpha[h] + sum;                              // partial over this thread's columns
+    }
+    // the accumulator is rescaled only when some row of the warp got a new max
+    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
         for (int n = 0; n < NT_O; ++n) {
-            o[n][2 * h] *= alpha;
-            o[n][2 * h + 1] *= alpha;
+            o[n][0] *= alpha[0];
+            o[n][1] *= alpha[0];
+            o[n][2] *= alpha[1];
+            o[n][3] *= alpha[1];
         }
     }
 }
@@ -202,13 +217,17 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
     const int* __restrict__ tile_seq, const int* __restrict__ tile_row0, int H, int Hkv, int ps,
     float scale_log2, int window) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_wait();
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [BM][LDS], later the output stage
     bf16* stage0 = Qs + BM * LDS;                          // 2 x (K tile | V tile)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = blockIdx.y;
-    const int s = tile_seq[blockIdx.x];
-    const int row0 = tile_row0[blockIdx.x];
+    // tiles are listed in position order; the last ones see the most keys, so they
+    // are started first
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int s = tile_seq[tile];
+    const int row0 = tile_row0[tile];
     const int g = H / Hkv;
     const int q0 = cu_q[s];
     const int qlen = cu_q[s + 1] - q0;
@@ -244,6 +263,8 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
     const int pos_hi = r_hi < nrows ? pos_base + (row0 + r_hi) / g : -1;
     const int wr_last = min(nrows - 1, warp * 16 + 15);
     const int warp_pos_max = warp * 16 < nrows ? pos_base + (row0 + wr_last) / g : -1;
+    const bool warp_rows_full = warp * 16 + 15 < nrows;
+    const int warp_pos_min = pos_base + (row0 + warp * 16) / g;
 
     unsigned qf[KSTEPS][4];
     float o[NT_O][4];
@@ -270,12 +291,19 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
         if (k0 <= warp_pos_max) {                          // else: every key is in this warp's future
             float sc[BN / 8][4];
             qk_tile<BN / 8>(sc, qf, Ks, 0);
-            softmax_tile<BN / 8>(sc, o, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2);
+            // all 64 keys visible to all 16 rows of the warp: no mask to evaluate
+            const bool open = warp_rows_full && k0 + BN - 1 <= warp_pos_min &&
+                              (window <= 0 || warp_pos_max - k0 < window);
+            if (open)
+                softmax_tile<BN / 8, false>(sc, o, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2);
+            else
+                softmax_tile<BN / 8, true>(sc, o, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2);
             pv_tile<BN / 8>(o, sc, Vs, 0);
         }
         __syncthreads();                                   // the stage may be refilled next round
     }
 
+    pdl_launch_dependents();
     // normalise, stage the warp's 16 rows in its own Q rows, store 16 bytes at a time
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -315,6 +343,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
     const int* __restrict__ ctx_len, float* __restrict__ part_o, float* __restrict__ part_ml,
     int H, int Hkv, int ps, float scale_log2, int window, int num_splits, int head_tiles) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_wait();
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [16][LDS]
     bf16* stage0 = Qs + 16 * LDS;
     float* red_o = reinterpret_cast<float*>(stage0);       // [4][16][D] after the key loop
@@ -346,9 +375,16 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
         cp_async16(Qs + r * LDS + c * 8,
                    q + (size_t)s * ldq + (size_t)(kvh * g + h0 + (ok ? r : 0)) * D + c * 8, ok);
     }
-    cp_async_commit();
-    if (ntiles > 0) load_kv_tile(stage0, stage0 + BN * LDS, kc, vc, table, kstart, ctx, kvh, Hkv, ps);
-    cp_async_commit();
+    // groups: {Q, tile 0}, {tile 1}, ... ; DSTAGES - 1 tiles are in flight ahead of the
+    // one being used (empty groups keep the count uniform)
+#pragma unroll
+    for (int p = 0; p < DSTAGES - 1; ++p) {
+        if (p < ntiles) {
+            bf16* Kp = stage0 + p * STAGE_ELEMS;
+            load_kv_tile(Kp, Kp + BN * LDS, kc, vc, table, kstart + p * BN, ctx, kvh, Hkv, ps);
+        }
+        cp_async_commit();
+    }
 
     const int r_lo = lane >> 2, r_hi = r_lo + 8;
     const int pos_lo = r_lo < nrows ? pos : -1;
@@ -362,32 +398,30 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
     for (int t = 0; t < ntiles; ++t) {
-        bf16* Ks = stage0 + (t & 1) * STAGE_ELEMS;
+        bf16* Ks = stage0 + (t % DSTAGES) * STAGE_ELEMS;
         bf16* Vs = Ks + BN * LDS;
-        if (t + 1 < ntiles) {
-            bf16* Kn = stage0 + ((t + 1) & 1) * STAGE_ELEMS;
-            load_kv_tile(Kn, Kn + BN * LDS, kc, vc, table, kstart + (t + 1) * BN, ctx, kvh, Hkv, ps);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
+        const int tn = t + DSTAGES - 1;                      // its stage was freed by round t - 1
+        if (tn < ntiles) {
+            bf16* Kn = stage0 + (tn % DSTAGES) * STAGE_ELEMS;
+            load_kv_tile(Kn, Kn + BN * LDS, kc, vc, table, kstart + tn * BN, ctx, kvh, Hkv, ps);
         }
+        cp_async_commit();
+        cp_async_wait<DSTAGES - 1>();
         __syncthreads();
         if (t == 0) load_q_frags(qf, Qs);
         const int k0 = kstart + t * BN + warp * 16;         // this warp's 16 keys of the tile
         if (k0 < ctx) {
             float sc[2][4];
             qk_tile<2>(sc, qf, Ks, warp * 16);
-            softmax_tile<2>(sc, o, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2);
+            softmax_tile<2, true>(sc, o, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2);
             pv_tile<2>(o, sc, Vs, warp * 16);
         }
         __syncthreads();
     }
-    if (ntiles == 0) {
-        cp_async_wait<0>();
-        __syncthreads();
-    }
+    cp_async_wait<0>();
+    __syncthreads();
 
+    pdl_launch_dependents();
     // merge the four warps (each saw a quarter of the keys)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -436,6 +470,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
 __global__ void decode_combine_kernel(const float* __restrict__ part_o,
                                       const float* __restrict__ part_ml, bf16* __restrict__ out,
                                       int ldo, int H, int num_splits) {
+    pdl_wait();
     const int head = blockIdx.x, s = blockIdx.y, d = threadIdx.x;
     if (d >= D) return;
     const size_t base = ((size_t)s * H + head) * num_splits;
@@ -455,12 +490,14 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o,
 }
 
 constexpr size_t PREFILL_SMEM = (size_t)(BM * LDS + 2 * STAGE_ELEMS) * sizeof(bf16);
-constexpr size_t DECODE_STAGE_BYTES = (size_t)2 * STAGE_ELEMS * sizeof(bf16);
+constexpr size_t DECODE_STAGE_BYTES = (size_t)DSTAGES * STAGE_ELEMS * sizeof(bf16);
 constexpr size_t DECODE_RED_BYTES = (size_t)4 * 16 * D * sizeof(float);
 constexpr size_t DECODE_SMEM = (size_t)16 * LDS * sizeof(bf16) +
                                (DECODE_STAGE_BYTES > DECODE_RED_BYTES ? DECODE_STAGE_BYTES : DECODE_RED_BYTES);
 
 }  // namespace
+
+SLB_DEFINE_PDL_SWITCH
 
 extern "C" {
 
@@ -480,7 +517,8 @@ int slb_prefill_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf1
                                int num_tiles, int H, int Hkv, int ps, float scale, int window,
                                cudaStream_t st) {
     if (num_tiles <= 0) return 0;
-    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0) return SLB_ERR_BAD_ARG;
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || !(scale > 0.f))
+        return SLB_ERR_BAD_ARG;
     if (ldq % 8 || ldo % 8 || ((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)out) % 16)
         return SLB_ERR_BAD_ARG;                            // 16-byte copies
     if (Hkv > 65535) return SLB_ERR_TOO_LARGE;
@@ -492,10 +530,9 @@ int slb_prefill_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf1
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    prefill_attention_kernel<<<dim3(num_tiles, Hkv), NTHREADS, PREFILL_SMEM, st>>>(
-        q, ldq, kc, vc, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq, tile_row0, H,
-        Hkv, ps, scale * 1.4426950408889634f, window);
-    return slb_launch_status();
+    return slb_launch(prefill_attention_kernel, dim3(num_tiles, Hkv), dim3(NTHREADS), PREFILL_SMEM, st,
+                      q, ldq, kc, vc, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq,
+                      tile_row0, H, Hkv, ps, scale * 1.4426950408889634f, window);
 }
 
 // scratch: float32 buffer of at least slb_decode_attention_scratch_bytes(...) bytes
@@ -505,7 +542,8 @@ int slb_decode_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf16
                               float* scratch, int S, int H, int Hkv, int ps, float scale,
                               int window, int num_splits, cudaStream_t st) {
     if (S <= 0) return 0;
-    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0) return SLB_ERR_BAD_ARG;
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || !(scale > 0.f))
+        return SLB_ERR_BAD_ARG;
     if (num_splits < 1 || (num_splits > 1 && scratch == nullptr)) return SLB_ERR_BAD_ARG;
     if (ldq % 8 || ((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc) % 16) return SLB_ERR_BAD_ARG;
     if (num_splits > MAX_SPLITS || S > 65535) return SLB_ERR_TOO_LARGE;
@@ -522,14 +560,13 @@ int slb_decode_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf16
     }
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)S * H * num_splits * D : nullptr;
-    decode_attention_kernel<<<dim3(num_splits, Hkv * head_tiles, S), NTHREADS, DECODE_SMEM, st>>>(
-        q, ldq, kc, vc, out, ldo, block_table, max_pages, ctx_len, part_o, part_ml, H, Hkv, ps,
-        scale * 1.4426950408889634f, window, num_splits, head_tiles);
-    int rc = slb_launch_status();
+    const int rc = slb_launch(decode_attention_kernel, dim3(num_splits, Hkv * head_tiles, S),
+                              dim3(NTHREADS), DECODE_SMEM, st, q, ldq, kc, vc, out, ldo, block_table,
+                              max_pages, ctx_len, part_o, part_ml, H, Hkv, ps,
+                              scale * 1.4426950408889634f, window, num_splits, head_tiles);
     if (rc != 0 || num_splits == 1) return rc;
-    decode_combine_kernel<<<dim3(H, S), (D + 31) / 32 * 32, 0, st>>>(part_o, part_ml, out, ldo, H,
-                                                                     num_splits);
-    return slb_launch_status();
+    return slb_launch(decode_combine_kernel, dim3(H, S), dim3((D + 31) / 32 * 32), 0, st,
+                      (const float*)part_o, (const float*)part_ml, out, ldo, H, num_splits);
 }
 
 }  // extern "C"

@@ -73,3 +73,44 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 static inline int slb_launch_status() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch ------------------------------------------
+// Every kernel of this library calls pdl_wait() before it touches activations: it
+// blocks until the preceding kernel of the stream has finished and its writes are
+// visible.  The long kernels call pdl_launch_dependents() when their main loop is
+// done, which lets the next kernel be scheduled while this one drains (an early
+// trigger was measured to hurt: blocks that wait share the SMs with blocks that
+// work).  What a kernel does before pdl_wait() may only read data that no kernel
+// of the step writes (weights).  Launches go through
+// slb_launch(), which sets the launch attribute when the switch is on; without
+// the attribute both device calls do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+extern int slb_pdl_enabled;          // defined once per shared library (SLB_DEFINE_PDL_SWITCH)
+
+template <typename... KArgs, typename... Args>
+static inline int slb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = slb_pdl_enabled ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#define SLB_DEFINE_PDL_SWITCH                                                         \
+    int slb_pdl_enabled = 0;                                                          \
+    extern "C" int slb_set_pdl(int on) {                                              \
+        const int old = slb_pdl_enabled;                                              \
+        slb_pdl_enabled = on ? 1 : 0;                                                 \
+        return old;                                                                   \
+    }

@@ -9,115 +9,201 @@
 // float32 x*rsqrt(mean(x^2)+eps)*w), silu(gate)*up (tp_model.py:67-68).
 #include "common.cuh"
 
+// Vector helpers: 4 consecutive elements as float4 (float32: one 16-byte access,
+// bfloat16: one 8-byte access).  Callers guarantee the alignment.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    const float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(hi);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<unsigned*>(&lo);
+    raw.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
 // out[t, :] = table[ids[t], :] as float32.  An id outside [0, vocab) yields a
-// row of zeros (callers validate ids on the host).
-template <typename T>
+// row of zeros (callers validate ids on the host).  VEC: h % 4 == 0.
+template <typename T, bool VEC>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int h, int vocab) {
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < vocab;
     const T* row = table + (size_t)(ok ? id : 0) * h;
     float* o = out + (size_t)t * h;
-    for (int i = threadIdx.x; i < h; i += blockDim.x) o[i] = ok ? to_float(row[i]) : 0.f;
+    if (VEC) {
+        for (int i = threadIdx.x * 4; i < h; i += blockDim.x * 4)
+            store4(o + i, ok ? load4(row + i) : make_float4(0.f, 0.f, 0.f, 0.f));
+    } else {
+        for (int i = threadIdx.x; i < h; i += blockDim.x) o[i] = ok ? to_float(row[i]) : 0.f;
+    }
 }
 
 // One block per output row r.  src = row_map ? row_map[r] : r.
 //   v = resid[src] + delta[src]        (delta may be null)
 //   if no row_map: resid[src] = v      (the stream is updated in place)
 //   out[r] = v * (1/sqrt(mean(v^2) + eps)) * weight
-template <typename TD, typename TO>
+// The sum of squares is accumulated per thread over a strided walk and then
+// reduced over the block; both depend only on h and the block size, never on the
+// batch.  VEC: h % 4 == 0 (all rows then start 16-byte aligned).
+template <typename TD, typename TO, bool VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const float* __restrict__ weight, TO* __restrict__ out,
                                    const int* __restrict__ row_map, int h, float eps) {
     __shared__ float scratch[33];
+    pdl_wait();
+
     const int r = blockIdx.x;
     const int src = row_map ? row_map[r] : r;
     float* x = resid + (size_t)src * h;
     const TD* d = delta ? delta + (size_t)src * h : nullptr;
     const bool write_back = (row_map == nullptr) && (d != nullptr);
+    TO* o = out + (size_t)r * h;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < h; i += blockDim.x) {
-        float v = x[i];
-        if (d) v += to_float(d[i]);
-        if (write_back) x[i] = v;
-        ss += v * v;
+    if (VEC) {
+        for (int i = threadIdx.x * 4; i < h; i += blockDim.x * 4) {
+            float4 v = load4(x + i);
+            if (d) {
+                const float4 dv = load4(d + i);
+                v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+            }
+            if (write_back) store4(x + i, v);
+            ss += v.x * v.x;
+            ss += v.y * v.y;
+            ss += v.z * v.z;
+            ss += v.w * v.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < h; i += blockDim.x) {
+            float v = x[i];
+            if (d) v += to_float(d[i]);
+            if (write_back) x[i] = v;
+            ss += v * v;
+        }
     }
     ss = block_sum(ss, scratch);
+    pdl_launch_dependents();
     const float rstd = 1.0f / sqrtf(ss / (float)h + eps);
-    TO* o = out + (size_t)r * h;
-    for (int i = threadIdx.x; i < h; i += blockDim.x) {
-        float v = x[i];
-        if (d && !write_back) v += to_float(d[i]);
-        o[i] = from_float<TO>(v * rstd * weight[i]);
+    if (VEC) {
+        for (int i = threadIdx.x * 4; i < h; i += blockDim.x * 4) {
+            float4 v = load4(x + i);
+            if (d && !write_back) {
+                const float4 dv = load4(d + i);
+                v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+            }
+            const float4 w = load4(weight + i);
+            store4(o + i, make_float4(v.x * rstd * w.x, v.y * rstd * w.y, v.z * rstd * w.z,
+                                      v.w * rstd * w.w));
+        }
+    } else {
+        for (int i = threadIdx.x; i < h; i += blockDim.x) {
+            float v = x[i];
+            if (d && !write_back) v += to_float(d[i]);
+            o[i] = from_float<TO>(v * rstd * weight[i]);
+        }
     }
 }
 
 // out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(z) = z / (1 + exp(-z)), in float32.
-template <typename T>
+// VEC: inter, ld_gu and ld_out are multiples of 4.
+template <typename T, bool VEC>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
                               int ld_gu, int ld_out) {
+    pdl_wait();
     const int t = blockIdx.y;
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= inter) return;
-    const float g = to_float(gu[(size_t)t * ld_gu + i]);
-    const float u = to_float(gu[(size_t)t * ld_gu + inter + i]);
-    out[(size_t)t * ld_out + i] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    const T* row = gu + (size_t)t * ld_gu;
+    T* o = out + (size_t)t * ld_out;
+    if (VEC) {
+        const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+        if (i >= inter) return;
+        const float4 g = load4(row + i), u = load4(row + inter + i);
+        store4(o + i, make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y,
+                                  g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w));
+    } else {
+        const int i = blockIdx.x * blockDim.x + threadIdx.x;
+        if (i >= inter) return;
+        const float g = to_float(row[i]);
+        const float u = to_float(row[inter + i]);
+        o[i] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    }
 }
 
 static int norm_threads(int h) {
-    int t = 32;
-    while (t < 1024 && t * 4 < h) t <<= 1;
-    return t;
+    int t = ((h + 7) / 8 + 31) / 32 * 32;          // about two vectors of 4 per thread
+    return t < 32 ? 32 : (t > 1024 ? 1024 : t);
 }
+
+template <typename T>
+static int launch_embedding(const int* ids, const T* table, float* out, int T_, int h, int vocab,
+                            cudaStream_t st) {
+    if (T_ <= 0) return 0;
+    if (h <= 0 || vocab <= 0) return SLB_ERR_BAD_ARG;
+    if (h % 4 == 0)
+        return slb_launch(embedding_kernel<T, true>, dim3(T_), dim3(256), 0, st, ids, table, out, h, vocab);
+    return slb_launch(embedding_kernel<T, false>, dim3(T_), dim3(256), 0, st, ids, table, out, h, vocab);
+}
+
+template <typename TD, typename TO>
+static int launch_add_rmsnorm(float* resid, const TD* delta, const float* weight, TO* out,
+                              const int* row_map, int rows, int h, float eps, cudaStream_t st) {
+    if (rows <= 0) return 0;
+    if (h <= 0) return SLB_ERR_BAD_ARG;
+    if (h % 4 == 0)
+        return slb_launch(add_rmsnorm_kernel<TD, TO, true>, dim3(rows), dim3(norm_threads(h)), 0, st,
+                          resid, delta, weight, out, row_map, h, eps);
+    return slb_launch(add_rmsnorm_kernel<TD, TO, false>, dim3(rows), dim3(norm_threads(h)), 0, st,
+                      resid, delta, weight, out, row_map, h, eps);
+}
+
+template <typename T>
+static int launch_swiglu(const T* gu, T* out, int T_, int inter, int ld_gu, int ld_out,
+                         cudaStream_t st) {
+    if (T_ <= 0) return 0;
+    if (inter <= 0 || T_ > 65535) return SLB_ERR_BAD_ARG;
+    if (inter % 4 == 0 && ld_gu % 4 == 0 && ld_out % 4 == 0)
+        return slb_launch(swiglu_kernel<T, true>, dim3((inter / 4 + 255) / 256, T_), dim3(256), 0, st,
+                          gu, out, inter, ld_gu, ld_out);
+    return slb_launch(swiglu_kernel<T, false>, dim3((inter + 255) / 256, T_), dim3(256), 0, st, gu,
+                      out, inter, ld_gu, ld_out);
+}
+
+SLB_DEFINE_PDL_SWITCH
 
 extern "C" {
 
 int slb_embedding_f32(const int* ids, const float* table, float* out, int T, int h, int vocab,
                       cudaStream_t st) {
-    if (T <= 0) return 0;
-    if (h <= 0 || vocab <= 0) return SLB_ERR_BAD_ARG;
-    embedding_kernel<float><<<T, 256, 0, st>>>(ids, table, out, h, vocab);
-    return slb_launch_status();
+    return launch_embedding<float>(ids, table, out, T, h, vocab, st);
 }
 int slb_embedding_bf16(const int* ids, const bf16* table, float* out, int T, int h, int vocab,
                        cudaStream_t st) {
-    if (T <= 0) return 0;
-    if (h <= 0 || vocab <= 0) return SLB_ERR_BAD_ARG;
-    embedding_kernel<bf16><<<T, 256, 0, st>>>(ids, table, out, h, vocab);
-    return slb_launch_status();
+    return launch_embedding<bf16>(ids, table, out, T, h, vocab, st);
 }
 
 int slb_add_rmsnorm_f32(float* resid, const float* delta, const float* weight, float* out,
                         const int* row_map, int rows, int h, float eps, cudaStream_t st) {
-    if (rows <= 0) return 0;
-    if (h <= 0) return SLB_ERR_BAD_ARG;
-    add_rmsnorm_kernel<float, float><<<rows, norm_threads(h), 0, st>>>(resid, delta, weight, out,
-                                                                      row_map, h, eps);
-    return slb_launch_status();
+    return launch_add_rmsnorm<float, float>(resid, delta, weight, out, row_map, rows, h, eps, st);
 }
 int slb_add_rmsnorm_bf16(float* resid, const bf16* delta, const float* weight, bf16* out,
                          const int* row_map, int rows, int h, float eps, cudaStream_t st) {
-    if (rows <= 0) return 0;
-    if (h <= 0) return SLB_ERR_BAD_ARG;
-    add_rmsnorm_kernel<bf16, bf16><<<rows, norm_threads(h), 0, st>>>(resid, delta, weight, out,
-                                                                    row_map, h, eps);
-    return slb_launch_status();
+    return launch_add_rmsnorm<bf16, bf16>(resid, delta, weight, out, row_map, rows, h, eps, st);
 }
 
 int slb_swiglu_f32(const float* gu, float* out, int T, int inter, int ld_gu, int ld_out,
                    cudaStream_t st) {
-    if (T <= 0) return 0;
-    if (inter <= 0 || T > 65535) return SLB_ERR_BAD_ARG;
-    swiglu_kernel<float><<<dim3((inter + 255) / 256, T), 256, 0, st>>>(gu, out, inter, ld_gu, ld_out);
-    return slb_launch_status();
+    return launch_swiglu<float>(gu, out, T, inter, ld_gu, ld_out, st);
 }
 int slb_swiglu_bf16(const bf16* gu, bf16* out, int T, int inter, int ld_gu, int ld_out,
                     cudaStream_t st) {
-    if (T <= 0) return 0;
-    if (inter <= 0 || T > 65535) return SLB_ERR_BAD_ARG;
-    swiglu_kernel<bf16><<<dim3((inter + 255) / 256, T), 256, 0, st>>>(gu, out, inter, ld_gu, ld_out);
-    return slb_launch_status();
+    return launch_swiglu<bf16>(gu, out, T, inter, ld_gu, ld_out, st);
 }
 
 }  // extern "C"

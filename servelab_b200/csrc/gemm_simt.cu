@@ -20,6 +20,7 @@ __global__ void __launch_bounds__(256) gemm_tn_simt_kernel(
     const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw, TC* __restrict__ C,
     int ldc, const float* __restrict__ bias, int M, int N, int K) {
     __shared__ __align__(16) float As[GS_BK][GS_BM + 4];
+    pdl_wait();
     __shared__ __align__(16) float Ws[GS_BK][GS_BN + 4];
     const int tid = threadIdx.x;
     const int ty = tid >> 4, tx = tid & 15;
@@ -73,9 +74,8 @@ static int launch_gemm(const TA* A, int lda, const TW* W, int ldw, TC* C, int ld
     if (K <= 0 || lda < K || ldw < K || ldc < N) return SLB_ERR_BAD_ARG;
     const int gy = (M + GS_BM - 1) / GS_BM;
     if (gy > 65535) return SLB_ERR_TOO_LARGE;
-    gemm_tn_simt_kernel<TA, TW, TC><<<dim3((N + GS_BN - 1) / GS_BN, gy), 256, 0, st>>>(
-        A, lda, W, ldw, C, ldc, bias, M, N, K);
-    return slb_launch_status();
+    return slb_launch(gemm_tn_simt_kernel<TA, TW, TC>, dim3((N + GS_BN - 1) / GS_BN, gy), dim3(256),
+                      0, st, A, lda, W, ldw, C, ldc, bias, M, N, K);
 }
 
 extern "C" {

@@ -13,6 +13,10 @@
 // manager.py:309-313).  Page layout here: [page][kv head][slot in page][D].
 #include "common.cuh"
 
+// One block per token.  A head is D/2 "slots" of two elements: slot i < rot/2 is the
+// rotation pair (i, i + rot/2); the slots after that are pairs of neighbouring
+// elements beyond the rotary part, which pass through.  Thread (i, lane-of-heads)
+// computes sin/cos of its slot once and walks the heads with them.
 template <typename T>
 __global__ void qkv_rope_cache_kernel(
     const T* __restrict__ qkv, int ld_qkv, const float* __restrict__ bias,
@@ -20,38 +24,53 @@ __global__ void qkv_rope_cache_kernel(
     const int* __restrict__ block_table, int max_pages, int page_size,
     const float* __restrict__ inv_freq, int rotary_dim,
     T* __restrict__ q_out, int ld_q, T* __restrict__ k_cache, T* __restrict__ v_cache,
-    int H, int Hkv, int D) {
+    int H, int Hkv, int D, int slots_per_head) {
+    pdl_wait();
     const int t = blockIdx.x;
-    const int j = blockIdx.y;                       // 0..H-1 q, H..H+Hkv-1 k, then v
+    const int i = threadIdx.x % slots_per_head;
+    const int head_lane = threadIdx.x / slots_per_head;
+    const int head_lanes = blockDim.x / slots_per_head;
+    if (i >= D / 2) return;
     const int pos = positions[t];
-    const T* x = qkv + (size_t)t * ld_qkv + (size_t)j * D;
-    const float* b = bias ? bias + (size_t)j * D : nullptr;
-    const bool is_q = j < H;
-    const bool is_v = j >= H + Hkv;
-    const bool rotate = !is_v && inv_freq != nullptr && rotary_dim > 0;
-    const int half = rotary_dim >> 1;
-
-    T* dst;
-    if (is_q) {
-        dst = q_out + (size_t)t * ld_q + (size_t)j * D;
-    } else {
-        const int kvh = is_v ? j - H - Hkv : j - H;
+    const int half = (inv_freq != nullptr) ? rotary_dim >> 1 : 0;
+    const bool rot = i < half;
+    float sn = 0.f, cs = 1.f;
+    if (rot) sincosf((float)pos * inv_freq[i], &sn, &cs);
+    // the two elements of this slot in a rotated head, and in a head that is copied
+    const int e0 = rot ? i : 2 * half + 2 * (i - half);
+    const int e1 = rot ? i + half : e0 + 1;
+    const int c0 = 2 * i, c1 = 2 * i + 1;
+    const bool write = k_cache != nullptr && v_cache != nullptr;
+    size_t kv_base = 0;
+    bool have_page = false;
+    if (write) {
         const int page = block_table[(size_t)seq_of_token[t] * max_pages + pos / page_size];
-        if (page < 0) return;                       // no page: nothing may be written
-        T* base = is_v ? v_cache : k_cache;
-        dst = base + (((size_t)page * Hkv + kvh) * page_size + pos % page_size) * D;
+        have_page = page >= 0;                         // no page: nothing may be written
+        kv_base = ((size_t)(have_page ? page : 0) * Hkv * page_size + pos % page_size) * D;
     }
-    for (int i = threadIdx.x; i < D; i += blockDim.x) {
-        float v = to_float(x[i]) + (b ? b[i] : 0.f);
-        if (rotate && i < rotary_dim) {
-            const int fi = i < half ? i : i - half;
-            const int pi = i < half ? i + half : i - half;
-            const float other = to_float(x[pi]) + (b ? b[pi] : 0.f);
-            float sn, cs;
-            sincosf((float)pos * inv_freq[fi], &sn, &cs);
-            v = i < half ? v * cs - other * sn : v * cs + other * sn;
+    const T* x = qkv + (size_t)t * ld_qkv;
+    const int heads = write ? H + 2 * Hkv : H;
+    for (int j = head_lane; j < heads; j += head_lanes) {
+        const bool is_v = j >= H + Hkv;
+        const int a = is_v ? c0 : e0, b = is_v ? c1 : e1;
+        const size_t off = (size_t)j * D;
+        float va = to_float(x[off + a]), vb = to_float(x[off + b]);
+        if (bias) { va += bias[off + a]; vb += bias[off + b]; }
+        if (rot && !is_v) {
+            const float ra = va * cs - vb * sn;
+            vb = vb * cs + va * sn;
+            va = ra;
         }
-        dst[i] = from_float<T>(v);
+        T* dst;
+        if (j < H) {
+            dst = q_out + (size_t)t * ld_q + off;
+        } else {
+            if (!have_page) continue;
+            const int kvh = is_v ? j - H - Hkv : j - H;
+            dst = (is_v ? v_cache : k_cache) + kv_base + (size_t)kvh * page_size * D;
+        }
+        dst[a] = from_float<T>(va);
+        dst[b] = from_float<T>(vb);
     }
 }
 
@@ -62,17 +81,21 @@ static int launch_qkv_rope_cache(const T* qkv, int ld_qkv, const float* bias, co
                                  int ld_q, T* k_cache, T* v_cache, int T_, int H, int Hkv, int D,
                                  cudaStream_t st) {
     if (T_ <= 0) return 0;
-    if (H <= 0 || Hkv <= 0 || D <= 0 || page_size <= 0 || max_pages <= 0) return SLB_ERR_BAD_ARG;
+    if (H <= 0 || Hkv <= 0 || D <= 0 || (D & 1) || page_size <= 0 || max_pages <= 0)
+        return SLB_ERR_BAD_ARG;
     if (rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1)) return SLB_ERR_BAD_ARG;
-    const bool write = k_cache != nullptr && v_cache != nullptr;
-    const int heads = write ? H + 2 * Hkv : H;
-    if (heads > 65535) return SLB_ERR_TOO_LARGE;
-    int threads = 32;
-    while (threads < 128 && threads < D) threads <<= 1;
-    qkv_rope_cache_kernel<T><<<dim3(T_, heads), threads, 0, st>>>(
-        qkv, ld_qkv, bias, positions, seq_of_token, block_table, max_pages, page_size, inv_freq,
-        rotary_dim, q_out, ld_q, k_cache, v_cache, H, Hkv, D);
-    return slb_launch_status();
+    if (D > 1024) return SLB_ERR_TOO_LARGE;
+    int slots = 1;
+    while (slots < D / 2) slots <<= 1;                 // power of two >= D/2, at most 512
+    const int heads = H + 2 * Hkv;
+    int lanes = 256 / slots;
+    if (lanes < 1) lanes = 1;
+    if (lanes > heads) lanes = heads;
+    int threads = slots * lanes;
+    threads = (threads + 31) / 32 * 32;
+    return slb_launch(qkv_rope_cache_kernel<T>, dim3(T_), dim3(threads), 0, st, qkv, ld_qkv, bias,
+                      positions, seq_of_token, block_table, max_pages, page_size, inv_freq,
+                      rotary_dim, q_out, ld_q, k_cache, v_cache, H, Hkv, D, slots);
 }
 
 extern "C" {

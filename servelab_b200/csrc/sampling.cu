@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(SM_THREADS) sample_rows_kernel(
     const unsigned long long* __restrict__ seed, const unsigned long long* __restrict__ stream,
     const int* __restrict__ position, int* __restrict__ out) {
     __shared__ float scratch[33];
+    pdl_wait();
     __shared__ float sv[33];
     __shared__ int si[33];
     __shared__ float warp_tot[32];
@@ -193,8 +194,7 @@ int slb_sample_rows(const float* logits, int ld, int R, int V, const float* temp
     if (R <= 0) return 0;
     if (V <= 0 || ld < V) return SLB_ERR_BAD_ARG;
     if (temperature && (!seed || !stream || !position)) return SLB_ERR_BAD_ARG;
-    sample_rows_kernel<<<R, SM_THREADS, 0, st>>>(logits, ld, V, temperature, top_k, top_p, seed,
-                                                 stream, position, out);
-    return slb_launch_status();
+    return slb_launch(sample_rows_kernel, dim3(R), dim3(SM_THREADS), 0, st, logits, ld, V,
+                      temperature, top_k, top_p, seed, stream, position, out);
 }
 }

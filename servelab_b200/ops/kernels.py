@@ -130,6 +130,7 @@ def sample_rows(logits: torch.Tensor, out: torch.Tensor, temperature=None, top_k
 
 # ------------------------------------- tensor-core attention (bfloat16 only)
 _sm_count = None
+decode_ctas_per_sm = 2      # blocks per SM the split heuristic aims for
 
 
 def _num_sms() -> int:
@@ -159,10 +160,11 @@ def prefill_attention(ctx, q, k_cache, v_cache, out, block_table, num_heads, num
 
 def decode_splits(num_seqs: int, num_kv_heads: int, group: int, longest_context: int,
                   max_splits: int) -> int:
-    """How many ways the keys of each request are split: enough blocks for two per
-    SM, at most one split per 64 keys of the longest context."""
+    """How many ways the keys of each request are split: enough blocks for
+    ``decode_ctas_per_sm`` per SM, at most one split per 64 keys of the longest
+    context."""
     ctas = num_seqs * num_kv_heads * ((group + 15) // 16)
-    want = max(1, (2 * _num_sms()) // max(ctas, 1))
+    want = max(1, (decode_ctas_per_sm * _num_sms()) // max(ctas, 1))
     return max(1, min(want, max_splits, -(-longest_context // 64)))
 
 
@@ -186,5 +188,12 @@ def decode_attention(ctx, q, k_cache, v_cache, out, block_table, num_heads, num_
     launch_count += 1 if splits > 1 else 0          # the combine kernel
 
 
-def gemm_skinny(x, w, out, bias=None) -> None:
-    raise L.KernelError("gemm_skinny is not built")
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+                bias: Optional[torch.Tensor] = None, rows_per_block_hint: int = 0) -> None:
+    """out[M,N] = x[M,K] . w[N,K]^T (+ bias) for up to 64 tokens, streaming w once;
+    bfloat16 operands, float32 or bfloat16 output."""
+    M, Kd = x.shape
+    L.check(L.core().slb_gemm_skinny_bf16(
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+        _p(bias), 1 if out.dtype == _F32 else 0, M, w.shape[0], Kd, rows_per_block_hint,
+        _stream()), "gemm_skinny")

@@ -40,14 +40,29 @@ _CORE_SIGNATURES = {
     "slb_gemm_simt_bf16": [P, I, P, I, P, I, P, I, I, I, P],
     "slb_gemm_simt_bf16_f32out": [P, I, P, I, P, I, P, I, I, I, P],
     "slb_sample_rows": [P, I, I, I, P, P, P, P, P, P, P, P],
+    "slb_gemm_skinny_bf16": [P, I, P, I, P, I, P, I, I, I, I, I, P],
 }
 
 # optional entry points: declared when the library exports them
-_OPTIONAL_SIGNATURES = {
-    "slb_gemm_skinny_bf16": [P, I, P, I, P, I, P, P, I, I, I, I, P],
-}
+_OPTIONAL_SIGNATURES = {}
 
 _libs: Dict[str, ctypes.CDLL] = {}
+_pdl = False
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch for every kernel of this package: a kernel may
+    be scheduled while its predecessor in the stream drains (each kernel waits on
+    the device for its predecessor before it touches activations).  Applies to the
+    libraries loaded so far and to those loaded later."""
+    global _pdl
+    _pdl = bool(on)
+    for lib in _libs.values():
+        lib.slb_set_pdl(1 if _pdl else 0)
+
+
+def pdl_enabled() -> bool:
+    return _pdl
 
 
 def _declare(lib: ctypes.CDLL, sigs: dict, required: bool) -> None:
@@ -72,6 +87,8 @@ def core() -> ctypes.CDLL:
             raise KernelsUnavailable(f"the servelab_b200 CUDA kernels are not available: {e}") from e
         _declare(lib, _CORE_SIGNATURES, True)
         _declare(lib, _OPTIONAL_SIGNATURES, False)
+        lib.slb_set_pdl.argtypes = [I]
+        lib.slb_set_pdl(1 if _pdl else 0)
         _libs["core"] = lib
     return lib
 
@@ -100,6 +117,8 @@ def attention(head_dim: int) -> ctypes.CDLL:
         if lib.slb_attention_head_dim() != head_dim:
             raise KernelsUnavailable(f"attention library built for head size "
                                      f"{lib.slb_attention_head_dim()}, wanted {head_dim}")
+        lib.slb_set_pdl.argtypes = [I]
+        lib.slb_set_pdl(1 if _pdl else 0)
         _libs[key] = lib
     return lib
 

@@ -4,8 +4,8 @@ float32: always this package's CUDA-core kernel (true 32-bit, fixed summation
 order per output).  bfloat16: the vendor library's tensor-core GEMM through
 torch (the reference's engine also calls a library for its products,
 servelab/parallel/tp_model.py:48-53), except for shapes whose rows are not
-16-byte aligned, which go to the CUDA-core kernel, and for small token counts,
-which go to this package's weight-streaming kernel when it is present.
+16-byte aligned, which go to the CUDA-core kernel, and for small token counts
+(decode steps), which go to this package's weight-streaming kernel.
 """
 
 from __future__ import annotations
@@ -17,13 +17,14 @@ import torch
 from . import kernels as K
 from . import library as L
 
-_SKINNY_MAX_M = 16
+skinny_max_tokens = 0      # up to this many tokens the weight-streaming kernel runs (0: the
+                           # library GEMM measured faster inside a captured step)
 use_skinny = True          # switch for measurements
 
 
 def _skinny_ok(x, w, M):
-    return (use_skinny and M <= _SKINNY_MAX_M and hasattr(L.core(), "slb_gemm_skinny_bf16")
-            and w.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
+    return (use_skinny and M <= skinny_max_tokens and w.shape[1] % 8 == 0
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,

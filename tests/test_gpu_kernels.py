@@ -418,3 +418,30 @@ def test_fast_attention_finds_one_far_key(needle):
         got = out.float().cpu().view(q_len, H, D)[-1]
         for h in range(H):
             assert (got[h] - case.v[0][needle, h // 7].float()).abs().max() <= 3e-2
+
+
+# ------------------------------------------------- weight-streaming product
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 32, 40, 64])
+@pytest.mark.parametrize("N,Kd", [(3584, 3584), (4608, 3584), (37888, 1024), (1000, 152), (24, 18944)])
+def test_gemm_skinny(M, N, Kd):
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    w = (torch.randn(N, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    b = torch.randn(N, device=DEV)
+    want = (x.double() @ w.double().t() + b.double()).float()
+    o32 = torch.full((M, N), 9.0, device=DEV)
+    K().gemm_skinny(x, w, o32, b)
+    assert (o32 - want).abs().max() <= 2e-3
+    ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    K().gemm_skinny(x, w, ob, None)
+    assert (ob.float() - (want - b)).abs().max() <= 2e-2
+    # deterministic: the same call gives the same bits
+    again = torch.empty(M, N, device=DEV)
+    K().gemm_skinny(x, w, again, b)
+    assert torch.equal(again, o32)
+    # a token's result does not depend on its neighbours in the batch
+    if M >= 2:
+        x2 = x.clone()
+        x2[0] = 0
+        other = torch.empty(M, N, device=DEV)
+        K().gemm_skinny(x2, w, other, b)
+        assert torch.equal(other[1:], o32[1:])
