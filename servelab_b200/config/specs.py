@@ -119,6 +119,10 @@ class ModelSpec:
     tie_word_embeddings: bool
     max_position_embeddings: int
     eos_token_ids: Tuple[int, ...] = ()
+    # a position encoding that acts on the embedded tokens (learned or sinusoidal
+    # absolute positions); encodings that act inside a mixer belong to its spec
+    embedding_position: PartSpec = field(default_factory=NoPositionSpec)
+    embedding_position_prefix: str = "model.embed_positions"
     # checkpoint naming: prefix of layer i is layer_prefix.format(i)
     embed_name: str = "model.embed_tokens.weight"
     lm_head_name: str = "lm_head.weight"

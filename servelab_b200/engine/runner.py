@@ -70,7 +70,8 @@ class ModelRunner:
         self._graphs = {}
         self._graph_pool = None
         self._graph_safe = not self.storage.state_layers and all(
-            getattr(b, "graph_safe", False) for b in self.model.blocks)
+            getattr(b, "graph_safe", False)
+            for b in list(self.model.blocks) + [self.model.embedding_position])
         self.graph_replays = 0
         self.graph_kernel_launches = {}   # batch size -> this package's kernels per replay
 

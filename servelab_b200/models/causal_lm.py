@@ -20,13 +20,15 @@ import torch
 from ..config.specs import ModelSpec
 from ..ops import kernels as K
 from ..ops.linear import linear
-from ..parts import BLOCKS, NORMS, BuildEnv, LayerCache, build_part, part_class
+from ..parts import BLOCKS, NORMS, POSITIONS, BuildEnv, LayerCache, build_part, part_class
 from ..weights.source import MATRIX, TensorDecl, WeightSource
 from ..weights.store import WeightStore
 
 
 def declare_tensors(spec: ModelSpec) -> List[TensorDecl]:
     out = [TensorDecl(spec.embed_name, (spec.vocab_size, spec.hidden_size), MATRIX)]
+    out += part_class(POSITIONS, spec.embedding_position).declare(spec.embedding_position,
+                                                                  spec.embedding_position_prefix)
     for i, block in enumerate(spec.layers):
         out += part_class(BLOCKS, block).declare(block, spec.layer_prefix.format(i))
     out += part_class(NORMS, spec.final_norm).declare(spec.final_norm, spec.final_norm_prefix)
@@ -48,6 +50,8 @@ class CausalLM:
         self.blocks = [build_part(BLOCKS, b, spec.layer_prefix.format(i), env)
                        for i, b in enumerate(spec.layers)]
         self.final_norm = build_part(NORMS, spec.final_norm, spec.final_norm_prefix, env)
+        self.embedding_position = build_part(POSITIONS, spec.embedding_position,
+                                             spec.embedding_position_prefix, env)
         self.embed_tokens: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
 
@@ -65,6 +69,7 @@ class CausalLM:
         store = WeightStore(source, declare_tensors(self.spec), self.env.dtype, self.env.device,
                             ignored_suffixes=self.spec.ignored_suffixes, optional=optional)
         self.embed_tokens = store.get(self.spec.embed_name)
+        self.embedding_position.load(store)
         for b in self.blocks:
             b.load(store)
         self.final_norm.load(store)
@@ -98,6 +103,7 @@ class CausalLM:
         T = ctx.num_tokens
         resid = torch.empty((T, self.spec.hidden_size), dtype=torch.float32, device=self.env.device)
         K.embedding(ctx.token_ids, self.embed_tokens, resid)
+        self.embedding_position.apply_to_embedding(ctx, resid)
         delta = None
         for i, run in enumerate(self.spec.run_order):
             owner = i if run.cache_of is None else run.cache_of

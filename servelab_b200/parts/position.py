@@ -17,6 +17,8 @@ from .registry import register_position
 
 @register_position("rotary")
 class RotaryEmbedding(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, spec, prefix, env):
         super().__init__(spec, prefix, env)
         rd = spec.rotary_dim or spec.head_dim
@@ -32,4 +34,4 @@ class RotaryEmbedding(PositionEncoding):
 
 @register_position("none")
 class NoPosition(PositionEncoding):
-    pass
+    graph_safe = True

@@ -97,7 +97,7 @@ def rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor) -> to
     x' = [x1 cos - x2 sin | x2 cos + x1 sin], angle = pos * inv_freq
     (docs/architecture.md:69, docs/knowledge_checklist.md:12; call site
     servelab/parallel/tp_model.py:128).  The angle is formed in float32."""
-    ang = positions.to(torch.float32)[:, None] * inv_freq[None, :]      # [T, D/2]
+    ang = positions.to(torch.float32)[:, None] * inv_freq.to(positions.device)[None, :]   # [T, D/2]
     cos = torch.cos(ang).to(x.dtype)[:, None, :]
     sin = torch.sin(ang).to(x.dtype)[:, None, :]
     half = x.shape[-1] // 2
@@ -120,8 +120,8 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     k = k.repeat_interleave(g, dim=1)
     v = v.repeat_interleave(g, dim=1)
     scores = torch.einsum("qhd,rhd->hqr", q, k) * (1.0 / math.sqrt(D))
-    a = torch.arange(T)[:, None]
-    r = torch.arange(T)[None, :]
+    a = torch.arange(T, device=q.device)[:, None]
+    r = torch.arange(T, device=q.device)[None, :]
     mask = r > a
     if window is not None:
         mask = mask | (a - r >= window)
@@ -163,9 +163,10 @@ def forward_logits(cfg: dict, w: Dict[str, torch.Tensor], ids: Sequence[int]) ->
     D = cfg.get("head_dim", cfg["hidden_size"] // H)
     eps = cfg["rms_norm_eps"]
     inv_freq = rope_inv_freq(D, cfg.get("rope_theta", 1000000.0))
-    ids_t = torch.tensor(list(ids), dtype=torch.long)
+    device = w["model.embed_tokens.weight"].device          # tensors may live on any device
+    ids_t = torch.tensor(list(ids), dtype=torch.long, device=device)
     T = ids_t.numel()
-    pos = torch.arange(T)
+    pos = torch.arange(T, device=device)
 
     hidden = embed(ids_t, w["model.embed_tokens.weight"])
     for i in range(cfg["num_hidden_layers"]):

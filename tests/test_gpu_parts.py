@@ -294,3 +294,100 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype, tmp_path):
                 assert err <= TOL[dtype] * 2, (rid, pos, err)
         sess.cache.check_invariants()
         assert sess.cache.slots.num_free() == 2
+
+
+# --------------------------------------------------------------------------- #
+# another position encoding, defined in this test: learned absolute positions
+# --------------------------------------------------------------------------- #
+
+def _register_learned_positions():
+    from servelab_b200.config import (AttentionSpec, BlockSpec, GatedMLPSpec, LayerRun, ModelSpec,
+                                      NoPositionSpec, PartSpec, RMSNormSpec, register_architecture)
+    from servelab_b200.parts import POSITIONS, PositionEncoding, register_position
+    from servelab_b200.weights import MATRIX, TensorDecl
+
+    if "toy_learned_absolute" in POSITIONS:
+        return
+
+    @dataclass(frozen=True)
+    class LearnedSpec(PartSpec):
+        kind: str = "toy_learned_absolute"
+        max_positions: int = 0
+        hidden_size: int = 0
+
+    @register_position("toy_learned_absolute")
+    class LearnedAbsolute(PositionEncoding):
+        """resid[t] += table[position[t]]: acts on the embedded tokens, not in the mixer."""
+
+        @classmethod
+        def declare(cls, spec, prefix):
+            return [TensorDecl(prefix + ".weight", (spec.max_positions, spec.hidden_size), MATRIX)]
+
+        def load(self, store):
+            self.table = store.get(self.prefix + ".weight")
+
+        def apply_to_embedding(self, ctx, resid):
+            resid += self.table[ctx.positions.long()].float()
+
+    class ToyAbsConfig:
+        architecture = "ToyAbsoluteForCausalLM"
+
+        def __init__(self, d):
+            self.d = dict(d)
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+        def to_dict(self):
+            return dict(self.d, architectures=[self.architecture])
+
+        def to_model_spec(self):
+            d = self.d
+            hid = d["hidden_size"]
+            norm = RMSNormSpec(dim=hid, eps=1e-5)
+            attn = AttentionSpec(hidden_size=hid, num_heads=2, num_kv_heads=2, head_dim=hid // 2,
+                                 qkv_bias=False, position=NoPositionSpec())
+            block = BlockSpec(mixer=attn, feed_forward=GatedMLPSpec(hidden_size=hid, intermediate_size=72),
+                              mixer_norm=norm, ff_norm=norm)
+            return ModelSpec(architecture=self.architecture, hidden_size=hid, vocab_size=d["vocab_size"],
+                             layers=(block, block), run_order=(LayerRun(0), LayerRun(1)),
+                             final_norm=norm, tie_word_embeddings=False, max_position_embeddings=128,
+                             embedding_position=LearnedSpec(max_positions=128, hidden_size=hid))
+
+    register_architecture(ToyAbsConfig.architecture, ToyAbsConfig)
+
+
+def _toy_abs_plain(folder, ids):
+    _, w = P.load_folder(folder)
+    T, hid = len(ids), 32
+    x = P.embed(torch.tensor(ids), w["model.embed_tokens.weight"]) + w["model.embed_positions.weight"][:T]
+    for layer in range(2):
+        p = f"model.layers.{layer}."
+        h = P.rms_norm(x, w[p + "input_layernorm.weight"], 1e-5)
+        q = P.linear(h, w[p + "self_attn.q_proj.weight"]).view(T, 2, 16)
+        k = P.linear(h, w[p + "self_attn.k_proj.weight"]).view(T, 2, 16)
+        v = P.linear(h, w[p + "self_attn.v_proj.weight"]).view(T, 2, 16)
+        x = x + P.linear(P.causal_attention(q, k, v), w[p + "self_attn.o_proj.weight"])
+        x = x + P.swiglu(P.rms_norm(x, w[p + "post_attention_layernorm.weight"], 1e-5),
+                         w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                         w[p + "mlp.down_proj.weight"])
+    return P.linear(P.rms_norm(x, w["model.norm.weight"], 1e-5), w["lm_head.weight"]).numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_another_position_encoding_defined_in_the_test(dtype, tmp_path):
+    _register_learned_positions()
+    from servelab_b200.config import config_from_dict
+    from servelab_b200.replay import TraceSession
+    from servelab_b200.weights import write_random_model
+    cfg = {"architectures": ["ToyAbsoluteForCausalLM"], "hidden_size": 32, "vocab_size": 90}
+    folder = write_random_model(str(tmp_path / "abs"), config_from_dict(cfg), seed=9)
+    reqs = {f"p{i}": H.random_ids(n, 90, 20 + i) for i, n in enumerate([37, 50])}
+    ref = {rid: _toy_abs_plain(folder, ids) for rid, ids in reqs.items()}
+    for steps in (H.trace_whole(reqs), H.trace_mixed(reqs, seed=4, max_live=2, tail=10)):
+        sess = TraceSession(folder, dtype, H.peak_tokens(steps), page_size=8, max_live=2)
+        got = H.collect(steps, H.run_session(sess, steps), 90)
+        for rid, ids in reqs.items():
+            for pos in range(len(ids)):
+                assert float(np.abs(got[rid][pos] - ref[rid][pos]).max()) <= TOL[dtype] * 2, (rid, pos)
