@@ -150,6 +150,10 @@ def main(argv=None) -> int:
         name, value = item.split("=")
         if name == "skinny_max_tokens":
             linear_ops.skinny_max_tokens = int(value)
+        elif name == "tc_max_tokens":
+            linear_ops.tc_max_tokens = int(value)
+        elif name == "tc_max_stages":
+            K.tc_max_stages = int(value)
         elif name == "decode_ctas_per_sm":
             K.decode_ctas_per_sm = int(value)
         elif name == "pdl":

@@ -470,6 +470,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
 __global__ void decode_combine_kernel(const float* __restrict__ part_o,
                                       const float* __restrict__ part_ml, bf16* __restrict__ out,
                                       int ldo, int H, int num_splits) {
+    pdl_launch_dependents();
     pdl_wait();
     const int head = blockIdx.x, s = blockIdx.y, d = threadIdx.x;
     if (d >= D) return;

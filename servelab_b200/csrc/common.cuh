@@ -77,11 +77,12 @@ static inline int slb_launch_status() { return (int)cudaGetLastError(); }
 // ---- programmatic dependent launch ------------------------------------------
 // Every kernel of this library calls pdl_wait() before it touches activations: it
 // blocks until the preceding kernel of the stream has finished and its writes are
-// visible.  The long kernels call pdl_launch_dependents() when their main loop is
-// done, which lets the next kernel be scheduled while this one drains (an early
-// trigger was measured to hurt: blocks that wait share the SMs with blocks that
-// work).  What a kernel does before pdl_wait() may only read data that no kernel
-// of the step writes (weights).  Launches go through
+// visible.  pdl_launch_dependents() lets the next kernel be scheduled: the short
+// kernels call it at their start (what follows them is a matrix product, which
+// fetches its first weight tiles while they run), the long ones when their main
+// loop is done (blocks that only wait would otherwise share the SMs with blocks
+// that work).  What a kernel does before pdl_wait() may only read data that no
+// kernel of the step writes (weights).  Launches go through
 // slb_launch(), which sets the launch attribute when the switch is on; without
 // the attribute both device calls do nothing.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

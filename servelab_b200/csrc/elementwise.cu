@@ -33,6 +33,7 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
 template <typename T, bool VEC>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int h, int vocab) {
+    pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
@@ -59,6 +60,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
                                    const float* __restrict__ weight, TO* __restrict__ out,
                                    const int* __restrict__ row_map, int h, float eps) {
     __shared__ float scratch[33];
+    pdl_launch_dependents();
     pdl_wait();
 
     const int r = blockIdx.x;
@@ -90,7 +92,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
         }
     }
     ss = block_sum(ss, scratch);
-    pdl_launch_dependents();
     const float rstd = 1.0f / sqrtf(ss / (float)h + eps);
     if (VEC) {
         for (int i = threadIdx.x * 4; i < h; i += blockDim.x * 4) {
@@ -117,6 +118,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
 template <typename T, bool VEC>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
                               int ld_gu, int ld_out) {
+    pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.y;
     const T* row = gu + (size_t)t * ld_gu;

@@ -1,0 +1,367 @@
+// Weight-streaming matrix product on the 5th-generation tensor cores (tcgen05):
+//   out[M, N] = x[M, K] . W[N, K]^T (+ bias[N]),  bfloat16 in, float32 accumulate in
+//   tensor memory, bfloat16 or float32 out,  M <= 64 tokens ("swap-AB": the 128 rows
+//   of a W tile are the M side of the MMA, the tokens are its N side).
+//
+// A decode step reads every weight once and does little arithmetic with it, so the
+// kernel is built around moving W with as few instructions as possible:
+//   * one thread issues TMA tile loads (cp.async.bulk.tensor, 128-byte swizzle) of
+//     W [128 rows x 64 k] and x [tokens x 64 k] into a ring of shared-memory stages,
+//     completion counted in bytes on an mbarrier per stage;
+//   * one thread issues tcgen05.mma (M = 128, N = tokens padded to 16, K = 16, four
+//     per stage) on shared-memory descriptors, accumulating into TMEM; a
+//     tcgen05.commit per stage hands the stage back to the loader;
+//   * four warps read the accumulator with tcgen05.ld and store it.
+// The K range is split over gridDim.y blocks so that narrow outputs still occupy
+// every SM; with more than one split the blocks write float32 partial sums and a
+// second kernel adds them in a fixed order (deterministic).
+//
+// Every wait on an mbarrier is bounded: after SLB_TC_SPIN_LIMIT polls the role
+// records a code in the status word, leaves its loop, and the block frees its TMEM
+// and returns, so a wrong descriptor cannot hang the GPU.
+//
+// Reference analogue: F.linear in the decode step (servelab/parallel/
+// tp_model.py:48-53,67-68,115-119), left to the library there.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int TC_BM = 128;            // rows of W per block (MMA M)
+constexpr int TC_BK = 64;             // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int TC_MAX_TOK = 64;        // MMA N
+constexpr int TC_MAX_STAGES = 12;     // the ring is as deep as shared memory allows
+constexpr int TC_THREADS = 192;       // warp 0 loader, warp 1 MMA + TMEM, warps 2..5 epilogue
+constexpr int TC_TMEM_COLS = 64;
+constexpr uint32_t SLB_TC_SPIN_LIMIT = 1u << 20;
+constexpr int A_STAGE_BYTES = TC_BM * TC_BK * 2;          // 16 KB of W per stage
+constexpr size_t TC_SMEM_BUDGET = 200 * 1024;             // stages + barriers (one block per SM)
+constexpr size_t TC_SMEM_TAIL = 256;                      // barriers and the TMEM address
+
+// x tile of a stage: ntok16 rows of 128 bytes, rounded up so stages stay 1024-aligned
+__host__ __device__ constexpr int b_stage_bytes(int ntok16) { return (ntok16 * TC_BK * 2 + 1023) / 1024 * 1024; }
+__host__ __device__ constexpr int stages_for(int ntok16, int max_stages) {
+    const int s = (int)((TC_SMEM_BUDGET - 1024 - TC_SMEM_TAIL) / (A_STAGE_BYTES + b_stage_bytes(ntok16)));
+    const int cap = (max_stages > 0 && max_stages < TC_MAX_STAGES) ? max_stages : TC_MAX_STAGES;
+    return s > cap ? cap : s;
+}
+
+__device__ int tc_status_word = 0;    // 0 ok; else (role << 8 | what) of the first timeout
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+// Bounded wait for the phase with the given parity; false after the poll limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < SLB_TC_SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+// K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, groups
+// of 8 rows 1024 bytes apart (stride byte offset), version 1 (Blackwell), layout 2.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);            // start address
+    d |= (uint64_t)1 << 16;                                // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset
+    d |= (uint64_t)1 << 46;                                // descriptor version
+    d |= (uint64_t)2 << 61;                                // SWIZZLE_128B
+    return d;
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+}
+
+// grid (row tiles of W, K splits).  ntok16: tokens padded to a multiple of 16.
+// splits == 1: `out` receives the result (+ bias) in its dtype; otherwise `partial`
+// receives float32 [split][M][N].
+template <typename TO>
+__global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
+    const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+    TO* __restrict__ out, int ldo, float* __restrict__ partial, const float* __restrict__ bias,
+    int M, int N, int K, int ntok16, int max_stages, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int B_STAGE_BYTES = b_stage_bytes(ntok16);
+    const int TC_STAGES = stages_for(ntok16, max_stages);
+    unsigned char* a_stage = base;
+    unsigned char* b_stage = base + TC_STAGES * A_STAGE_BYTES;
+    uint64_t* full = reinterpret_cast<uint64_t*>(base + TC_STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+    uint64_t* empty = full + TC_MAX_STAGES;
+    uint64_t* accum = empty + TC_MAX_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * TC_BM;
+    const int splits = gridDim.y, split = blockIdx.y;
+    const int kblocks = (K + TC_BK - 1) / TC_BK;
+    const int per = (kblocks + splits - 1) / splits;
+    const int kb_begin = min(kblocks, split * per);
+    const int kb_end = min(kblocks, kb_begin + per);
+    const int iters = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {                                        // one warp allocates the accumulator
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ loader
+        // W is written by no kernel, x by the preceding one: the W tiles of the first
+        // stages are requested at once, the x tiles after the wait for that kernel.
+        if (lane == 0) {
+            const uint32_t bytes = A_STAGE_BYTES + (uint32_t)ntok16 * TC_BK * 2;
+            const int ahead = min(iters, TC_STAGES);
+            for (int i = 0; i < ahead; ++i) {                 // stages are empty at the start
+                mbar_expect_tx(&full[i], bytes);
+                tma_load_2d(a_stage + i * A_STAGE_BYTES, &map_w, &full[i], (kb_begin + i) * TC_BK, n0);
+            }
+            pdl_wait();
+            for (int i = 0; i < ahead; ++i)
+                tma_load_2d(b_stage + i * B_STAGE_BYTES, &map_x, &full[i], (kb_begin + i) * TC_BK, 0);
+            for (int i = ahead; i < iters; ++i) {
+                const int s = i % TC_STAGES;
+                if (!mbar_wait(&empty[s], ((i / TC_STAGES) & 1) ^ 1)) {
+                    atomicCAS(status, 0, (1 << 8) | 1);
+                    break;
+                }
+                mbar_expect_tx(&full[s], bytes);
+                const int k = (kb_begin + i) * TC_BK;
+                tma_load_2d(a_stage + s * A_STAGE_BYTES, &map_w, &full[s], k, n0);
+                tma_load_2d(b_stage + s * B_STAGE_BYTES, &map_x, &full[s], k, 0);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            // instruction descriptor: D float32, A and B bfloat16, both K-major
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                   ((uint32_t)(ntok16 >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < iters && ok; ++i) {
+                const int s = i % TC_STAGES;
+                if (!mbar_wait(&full[s], (i / TC_STAGES) & 1)) {
+                    atomicCAS(status, 0, (2 << 8) | 1);
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t adesc = umma_desc_sw128(smem_u32(a_stage + s * A_STAGE_BYTES));
+                const uint64_t bdesc = umma_desc_sw128(smem_u32(b_stage + s * B_STAGE_BYTES));
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; ++kk)     // 32 bytes further per K = 16 step
+                    umma_bf16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&empty[s]);                      // stage free once these MMAs have read it
+            }
+            if (ok) umma_commit(accum);                      // accumulator complete
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        pdl_wait();                                          // nothing is written before the
+                                                             // preceding kernel has finished
+        const int quarter = warp & 3;                        // TMEM lanes this warp may read
+        const int row = quarter * 32 + lane;                 // row of the tile = row of W
+        const int n = n0 + row;
+        bool ok = true;
+        if (iters > 0) {
+            ok = mbar_wait(accum, 0);
+            if (!ok) atomicCAS(status, 0, (3 << 8) | 1);
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        pdl_launch_dependents();
+        for (int c0 = 0; c0 < ntok16; c0 += 16) {
+            uint32_t v[16];
+            if (iters > 0 && ok) {
+                tmem_ld16(tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = 0u;
+            }
+            if (n < N && ok) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int tok = c0 + j;
+                    if (tok >= M) break;
+                    const float val = __uint_as_float(v[j]);
+                    if (splits == 1)
+                        out[(size_t)tok * ldo + n] = from_float<TO>(val + (bias ? bias[n] : 0.f));
+                    else
+                        partial[((size_t)split * M + tok) * N + n] = val;
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TC_TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// out[tok, n] = sum over splits (in order) of partial[s][tok][n] (+ bias[n])
+template <typename TO>
+__global__ void gemm_tc_reduce_kernel(const float* __restrict__ partial, TO* __restrict__ out, int ldo,
+                                      const float* __restrict__ bias, int M, int N, int splits) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int n = blockIdx.x * blockDim.x + threadIdx.x;
+    const int tok = blockIdx.y;
+    if (n >= N) return;
+    float sum = 0.f;
+    for (int s = 0; s < splits; ++s) sum += partial[((size_t)s * M + tok) * N + n];
+    if (bias) sum += bias[n];
+    out[(size_t)tok * ldo + n] = from_float<TO>(sum);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// Tensor map of a row-major [rows, K] bfloat16 matrix with leading dimension ld,
+// tiles of box_rows x 64 elements, 128-byte swizzle, zeros outside the matrix.
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr) return SLB_ERR_BAD_ARG;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+                          elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : SLB_ERR_BAD_ARG;
+}
+
+template <typename TO>
+int run(const bf16* x, int ldx, const bf16* W, int ldw, TO* out, int ldo, const float* bias,
+        float* workspace, int M, int N, int K, int splits, int max_stages, cudaStream_t st) {
+    CUtensorMap map_w, map_x;
+    const int ntok16 = (M + 15) / 16 * 16;
+    int rc = make_map(&map_w, W, N, K, ldw, TC_BM);
+    if (rc != 0) return rc;
+    rc = make_map(&map_x, x, M, K, ldx, ntok16);
+    if (rc != 0) return rc;
+    static bool configured[2] = {false, false};
+    constexpr int which = sizeof(TO) == 4 ? 1 : 0;
+    if (!configured[which]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_decode_kernel<TO>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)TC_SMEM_BUDGET);
+        if (e != cudaSuccess) return (int)e;
+        configured[which] = true;
+    }
+    const size_t TC_SMEM = 1024 + (size_t)stages_for(ntok16, max_stages) * (A_STAGE_BYTES + b_stage_bytes(ntok16)) +
+                           TC_SMEM_TAIL;
+    int* status = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&status, tc_status_word);
+    if (e != cudaSuccess) return (int)e;
+    rc = slb_launch(gemm_tc_decode_kernel<TO>, dim3((N + TC_BM - 1) / TC_BM, splits), dim3(TC_THREADS),
+                    TC_SMEM, st, map_w, map_x, out, ldo, workspace, bias, M, N, K, ntok16, max_stages, status);
+    if (rc != 0 || splits == 1) return rc;
+    return slb_launch(gemm_tc_reduce_kernel<TO>, dim3((N + 255) / 256, M), dim3(256), 0, st,
+                      (const float*)workspace, out, ldo, bias, M, N, splits);
+}
+
+}  // namespace
+
+extern "C" {
+
+// workspace: float32 [splits * M * N] when splits > 1 (may be null otherwise).
+// max_stages: cap on the depth of the shared-memory ring (0: as deep as fits).
+int slb_gemm_tc_decode_bf16(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo,
+                            const float* bias, float* workspace, int out_f32, int M, int N, int K,
+                            int splits, int max_stages, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldo < N) return SLB_ERR_BAD_ARG;
+    if (((uintptr_t)x | (uintptr_t)W) % 16) return SLB_ERR_BAD_ARG;
+    if (M > TC_MAX_TOK) return SLB_ERR_TOO_LARGE;
+    const int kblocks = (K + TC_BK - 1) / TC_BK;
+    if (splits < 1 || splits > kblocks || splits > 65535) return SLB_ERR_BAD_ARG;
+    if (splits > 1 && workspace == nullptr) return SLB_ERR_BAD_ARG;
+    if (out_f32)
+        return run<float>(x, ldx, W, ldw, (float*)out, ldo, bias, workspace, M, N, K, splits, max_stages, st);
+    return run<bf16>(x, ldx, W, ldw, (bf16*)out, ldo, bias, workspace, M, N, K, splits, max_stages, st);
+}
+
+// 0 while no wait has timed out; else (role << 8 | code) of the first one.
+// Reading synchronises with the device.
+int slb_gemm_tc_status(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, tc_status_word, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(tc_status_word, &zero, sizeof(int));
+    }
+    return v;
+}
+}

@@ -25,6 +25,7 @@ __global__ void qkv_rope_cache_kernel(
     const float* __restrict__ inv_freq, int rotary_dim,
     T* __restrict__ q_out, int ld_q, T* __restrict__ k_cache, T* __restrict__ v_cache,
     int H, int Hkv, int D, int slots_per_head) {
+    pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const int i = threadIdx.x % slots_per_head;

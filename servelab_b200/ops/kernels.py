@@ -197,3 +197,38 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
         x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
         _p(bias), 1 if out.dtype == _F32 else 0, M, w.shape[0], Kd, rows_per_block_hint,
         _stream()), "gemm_skinny")
+
+
+# ------------------------------------ tcgen05 weight-streaming product (decode)
+TC_MAX_TOKENS = 64
+tc_max_stages = 6          # cap on the kernel's shared-memory ring; shallow rings let the next
+                           # kernel's blocks become resident beside a draining one (measured best)
+
+
+def tc_decode_splits(n_out: int, k: int) -> int:
+    """K splits so that (row tiles x splits) is about one block per SM."""
+    tiles = -(-n_out // 128)
+    kblocks = -(-k // 64)
+    want = max(1, round(_num_sms() / tiles)) if tiles < _num_sms() else 1
+    return max(1, min(want, kblocks // 4 if kblocks >= 8 else 1))
+
+
+def gemm_tc_decode(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+                   bias: Optional[torch.Tensor] = None, splits: int = 0) -> None:
+    """out[M,N] = x[M,K] . w[N,K]^T (+ bias) for up to 64 tokens on tcgen05 tensor
+    cores with TMA-streamed weights; bfloat16 operands, float32 or bfloat16 output."""
+    M, Kd = x.shape
+    N = w.shape[0]
+    splits = splits or tc_decode_splits(N, Kd)
+    ws = torch.empty(splits * M * N, dtype=_F32, device=x.device) if splits > 1 else None
+    L.check(L.core().slb_gemm_tc_decode_bf16(
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+        _p(bias), _p(ws), 1 if out.dtype == _F32 else 0, M, N, Kd, splits, tc_max_stages, _stream()),
+        "gemm_tc_decode")
+    global launch_count
+    launch_count += 1 if splits > 1 else 0
+
+
+def gemm_tc_status(reset: bool = False) -> int:
+    """0 unless a bounded wait inside the tcgen05 kernel ran out (synchronises)."""
+    return L.core().slb_gemm_tc_status(1 if reset else 0)

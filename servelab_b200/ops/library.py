@@ -41,13 +41,15 @@ _CORE_SIGNATURES = {
     "slb_gemm_simt_bf16_f32out": [P, I, P, I, P, I, P, I, I, I, P],
     "slb_sample_rows": [P, I, I, I, P, P, P, P, P, P, P, P],
     "slb_gemm_skinny_bf16": [P, I, P, I, P, I, P, I, I, I, I, I, P],
+    "slb_gemm_tc_decode_bf16": [P, I, P, I, P, I, P, P, I, I, I, I, I, I, P],
+    "slb_gemm_tc_status": [I],
 }
 
 # optional entry points: declared when the library exports them
 _OPTIONAL_SIGNATURES = {}
 
 _libs: Dict[str, ctypes.CDLL] = {}
-_pdl = False
+_pdl = True
 
 
 def set_pdl(on: bool) -> None:

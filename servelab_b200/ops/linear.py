@@ -5,7 +5,9 @@ order per output).  bfloat16: the vendor library's tensor-core GEMM through
 torch (the reference's engine also calls a library for its products,
 servelab/parallel/tp_model.py:48-53), except for shapes whose rows are not
 16-byte aligned, which go to the CUDA-core kernel, and for small token counts
-(decode steps), which go to this package's weight-streaming kernel.
+(decode steps), which go to this package's tcgen05 weight-streaming kernel
+(TMA-fed, accumulating in tensor memory).  An mma.sync weight-streaming kernel
+also exists and is off by default.
 """
 
 from __future__ import annotations
@@ -27,6 +29,15 @@ def _skinny_ok(x, w, M):
             and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
 
 
+tc_max_tokens = 16         # up to this many tokens the tcgen05 weight-streaming kernel runs
+
+
+def _tc_ok(x, w, M):
+    return (0 < M <= min(tc_max_tokens, K.TC_MAX_TOKENS) and w.shape[1] % 8 == 0
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     M, Kd = x.shape
@@ -39,6 +50,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     # bfloat16 activations
     if M == 0:
         return torch.empty((0, N), dtype=out_dtype, device=x.device)
+    if _tc_ok(x, w, M):
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        K.gemm_tc_decode(x, w, out, bias)
+        return out
     if _skinny_ok(x, w, M):
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         K.gemm_skinny(x, w, out, bias)

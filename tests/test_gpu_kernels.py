@@ -445,3 +445,31 @@ def test_gemm_skinny(M, N, Kd):
         other = torch.empty(M, N, device=DEV)
         K().gemm_skinny(x2, w, other, b)
         assert torch.equal(other[1:], o32[1:])
+
+
+# --------------------------------- tcgen05 weight-streaming product (decode)
+@pytest.mark.parametrize("M", [1, 5, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,Kd,splits", [(3584, 3584, 0), (4608, 3584, 4), (37888, 1024, 1),
+                                         (1000, 152, 1), (24, 18944, 0), (300, 4096, 16)])
+def test_gemm_tcgen05_decode(M, N, Kd, splits):
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    w = (torch.randn(N, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    b = torch.randn(N, device=DEV)
+    want = (x.double() @ w.double().t() + b.double()).float()
+    o32 = torch.full((M, N), 9.0, device=DEV)
+    K().gemm_tc_decode(x, w, o32, b, splits)
+    assert K().gemm_tc_status(True) == 0, "a bounded wait in the kernel ran out"
+    assert (o32 - want).abs().max() <= 2e-3
+    ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    K().gemm_tc_decode(x, w, ob, None, splits)
+    assert (ob.float() - (want - b)).abs().max() <= 2e-2
+    again = torch.empty(M, N, device=DEV)
+    K().gemm_tc_decode(x, w, again, b, splits)
+    assert torch.equal(again, o32)                          # deterministic
+    if M >= 2:                                              # a token does not depend on its neighbours
+        x2 = x.clone()
+        x2[0] = 0
+        other = torch.empty(M, N, device=DEV)
+        K().gemm_tc_decode(x2, w, other, b, splits)
+        assert torch.equal(other[1:], o32[1:])
+    assert K().gemm_tc_status(True) == 0
