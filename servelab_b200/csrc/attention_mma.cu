@@ -413,7 +413,11 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
         if (k0 < ctx) {
             float sc[2][4];
             qk_tile<2>(sc, qf, Ks, warp * 16);
-            softmax_tile<2, true>(sc, o, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2);
+            // every key of this warp's 16 is inside the context and the window: no mask
+            if (k0 + 15 < ctx && (window <= 0 || pos - k0 < window))
+                softmax_tile<2, false>(sc, o, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2);
+            else
+                softmax_tile<2, true>(sc, o, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2);
             pv_tile<2>(o, sc, Vs, warp * 16);
         }
         __syncthreads();

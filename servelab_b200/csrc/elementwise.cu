@@ -52,29 +52,59 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
 //   v = resid[src] + delta[src]        (delta may be null)
 //   if no row_map: resid[src] = v      (the stream is updated in place)
 //   out[r] = v * (1/sqrt(mean(v^2) + eps)) * weight
+// The update may instead arrive as `nparts` float32 partial sums (a matrix product
+// split along K): parts[p * part_stride + src * h + i], added in the order of p,
+// plus an optional float32 bias `pbias[i]`.
 // The sum of squares is accumulated per thread over a strided walk and then
 // reduced over the block; both depend only on h and the block size, never on the
 // batch.  VEC: h % 4 == 0 (all rows then start 16-byte aligned).
+template <typename TD>
+__device__ __forceinline__ float4 delta4(const TD* d, const float* parts, int nparts,
+                                         size_t part_stride, const float* pbias, int i) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (d) v = load4(d + i);
+    for (int p = 0; p < nparts; ++p) {
+        const float4 q = load4(parts + p * part_stride + i);
+        v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+    }
+    if (pbias) {
+        const float4 q = load4(pbias + i);
+        v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+    }
+    return v;
+}
+template <typename TD>
+__device__ __forceinline__ float delta1(const TD* d, const float* parts, int nparts,
+                                        size_t part_stride, const float* pbias, int i) {
+    float v = d ? to_float(d[i]) : 0.f;
+    for (int p = 0; p < nparts; ++p) v += parts[p * part_stride + i];
+    if (pbias) v += pbias[i];
+    return v;
+}
+
 template <typename TD, typename TO, bool VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                   const float* __restrict__ parts, int nparts, size_t part_stride,
+                                   const float* __restrict__ pbias,
                                    const float* __restrict__ weight, TO* __restrict__ out,
                                    const int* __restrict__ row_map, int h, float eps) {
     __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
-
     const int r = blockIdx.x;
     const int src = row_map ? row_map[r] : r;
     float* x = resid + (size_t)src * h;
     const TD* d = delta ? delta + (size_t)src * h : nullptr;
-    const bool write_back = (row_map == nullptr) && (d != nullptr);
+    const float* pp = nparts > 0 ? parts + (size_t)src * h : nullptr;
+    const bool has_delta = d != nullptr || nparts > 0;
+    const bool write_back = (row_map == nullptr) && has_delta;
     TO* o = out + (size_t)r * h;
     float ss = 0.f;
     if (VEC) {
         for (int i = threadIdx.x * 4; i < h; i += blockDim.x * 4) {
             float4 v = load4(x + i);
-            if (d) {
-                const float4 dv = load4(d + i);
+            if (has_delta) {
+                const float4 dv = delta4(d, pp, nparts, part_stride, pbias, i);
                 v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
             }
             if (write_back) store4(x + i, v);
@@ -86,7 +116,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
     } else {
         for (int i = threadIdx.x; i < h; i += blockDim.x) {
             float v = x[i];
-            if (d) v += to_float(d[i]);
+            if (has_delta) v += delta1(d, pp, nparts, part_stride, pbias, i);
             if (write_back) x[i] = v;
             ss += v * v;
         }
@@ -96,8 +126,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
     if (VEC) {
         for (int i = threadIdx.x * 4; i < h; i += blockDim.x * 4) {
             float4 v = load4(x + i);
-            if (d && !write_back) {
-                const float4 dv = load4(d + i);
+            if (has_delta && !write_back) {
+                const float4 dv = delta4(d, pp, nparts, part_stride, pbias, i);
                 v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
             }
             const float4 w = load4(weight + i);
@@ -107,7 +137,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
     } else {
         for (int i = threadIdx.x; i < h; i += blockDim.x) {
             float v = x[i];
-            if (d && !write_back) v += to_float(d[i]);
+            if (has_delta && !write_back) v += delta1(d, pp, nparts, part_stride, pbias, i);
             o[i] = from_float<TO>(v * rstd * weight[i]);
         }
     }
@@ -154,15 +184,19 @@ static int launch_embedding(const int* ids, const T* table, float* out, int T_, 
 }
 
 template <typename TD, typename TO>
-static int launch_add_rmsnorm(float* resid, const TD* delta, const float* weight, TO* out,
-                              const int* row_map, int rows, int h, float eps, cudaStream_t st) {
+static int launch_add_rmsnorm(float* resid, const TD* delta, const float* parts, int nparts,
+                              long long part_stride, const float* pbias, const float* weight,
+                              TO* out, const int* row_map, int rows, int h, float eps,
+                              cudaStream_t st) {
     if (rows <= 0) return 0;
-    if (h <= 0) return SLB_ERR_BAD_ARG;
-    if (h % 4 == 0)
+    if (h <= 0 || nparts < 0 || (nparts > 0 && parts == nullptr)) return SLB_ERR_BAD_ARG;
+    if (h % 4 == 0 && part_stride % 4 == 0)
         return slb_launch(add_rmsnorm_kernel<TD, TO, true>, dim3(rows), dim3(norm_threads(h)), 0, st,
-                          resid, delta, weight, out, row_map, h, eps);
+                          resid, delta, parts, nparts, (size_t)part_stride, pbias, weight, out,
+                          row_map, h, eps);
     return slb_launch(add_rmsnorm_kernel<TD, TO, false>, dim3(rows), dim3(norm_threads(h)), 0, st,
-                      resid, delta, weight, out, row_map, h, eps);
+                      resid, delta, parts, nparts, (size_t)part_stride, pbias, weight, out, row_map,
+                      h, eps);
 }
 
 template <typename T>
@@ -192,11 +226,20 @@ int slb_embedding_bf16(const int* ids, const bf16* table, float* out, int T, int
 
 int slb_add_rmsnorm_f32(float* resid, const float* delta, const float* weight, float* out,
                         const int* row_map, int rows, int h, float eps, cudaStream_t st) {
-    return launch_add_rmsnorm<float, float>(resid, delta, weight, out, row_map, rows, h, eps, st);
+    return launch_add_rmsnorm<float, float>(resid, delta, nullptr, 0, 0, nullptr, weight, out,
+                                            row_map, rows, h, eps, st);
 }
 int slb_add_rmsnorm_bf16(float* resid, const bf16* delta, const float* weight, bf16* out,
                          const int* row_map, int rows, int h, float eps, cudaStream_t st) {
-    return launch_add_rmsnorm<bf16, bf16>(resid, delta, weight, out, row_map, rows, h, eps, st);
+    return launch_add_rmsnorm<bf16, bf16>(resid, delta, nullptr, 0, 0, nullptr, weight, out, row_map,
+                                          rows, h, eps, st);
+}
+// the update arrives as `nparts` float32 partial sums [nparts][rows_total][h] (+ bias)
+int slb_add_rmsnorm_parts_bf16(float* resid, const float* parts, int nparts, long long part_stride,
+                               const float* pbias, const float* weight, bf16* out,
+                               const int* row_map, int rows, int h, float eps, cudaStream_t st) {
+    return launch_add_rmsnorm<bf16, bf16>(resid, nullptr, parts, nparts, part_stride, pbias, weight,
+                                          out, row_map, rows, h, eps, st);
 }
 
 int slb_swiglu_f32(const float* gu, float* out, int T, int inter, int ld_gu, int ld_out,

@@ -304,7 +304,8 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box
 
 template <typename TO>
 int run(const bf16* x, int ldx, const bf16* W, int ldw, TO* out, int ldo, const float* bias,
-        float* workspace, int M, int N, int K, int splits, int max_stages, cudaStream_t st) {
+        float* workspace, int M, int N, int K, int splits, int max_stages, int defer_sum,
+        cudaStream_t st) {
     CUtensorMap map_w, map_x;
     const int ntok16 = (M + 15) / 16 * 16;
     int rc = make_map(&map_w, W, N, K, ldw, TC_BM);
@@ -327,7 +328,7 @@ int run(const bf16* x, int ldx, const bf16* W, int ldw, TO* out, int ldo, const 
     if (e != cudaSuccess) return (int)e;
     rc = slb_launch(gemm_tc_decode_kernel<TO>, dim3((N + TC_BM - 1) / TC_BM, splits), dim3(TC_THREADS),
                     TC_SMEM, st, map_w, map_x, out, ldo, workspace, bias, M, N, K, ntok16, max_stages, status);
-    if (rc != 0 || splits == 1) return rc;
+    if (rc != 0 || splits == 1 || defer_sum) return rc;
     return slb_launch(gemm_tc_reduce_kernel<TO>, dim3((N + 255) / 256, M), dim3(256), 0, st,
                       (const float*)workspace, out, ldo, bias, M, N, splits);
 }
@@ -338,9 +339,11 @@ extern "C" {
 
 // workspace: float32 [splits * M * N] when splits > 1 (may be null otherwise).
 // max_stages: cap on the depth of the shared-memory ring (0: as deep as fits).
+// defer_sum: with splits > 1, leave the partial sums [splits][M][N] in the workspace
+// and launch no reduction (the consumer adds them; `out` and `bias` are unused).
 int slb_gemm_tc_decode_bf16(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo,
                             const float* bias, float* workspace, int out_f32, int M, int N, int K,
-                            int splits, int max_stages, cudaStream_t st) {
+                            int splits, int max_stages, int defer_sum, cudaStream_t st) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldo < N) return SLB_ERR_BAD_ARG;
     if (((uintptr_t)x | (uintptr_t)W) % 16) return SLB_ERR_BAD_ARG;
@@ -349,8 +352,22 @@ int slb_gemm_tc_decode_bf16(const bf16* x, int ldx, const bf16* W, int ldw, void
     if (splits < 1 || splits > kblocks || splits > 65535) return SLB_ERR_BAD_ARG;
     if (splits > 1 && workspace == nullptr) return SLB_ERR_BAD_ARG;
     if (out_f32)
-        return run<float>(x, ldx, W, ldw, (float*)out, ldo, bias, workspace, M, N, K, splits, max_stages, st);
-    return run<bf16>(x, ldx, W, ldw, (bf16*)out, ldo, bias, workspace, M, N, K, splits, max_stages, st);
+        return run<float>(x, ldx, W, ldw, (float*)out, ldo, bias, workspace, M, N, K, splits, max_stages,
+                          defer_sum, st);
+    return run<bf16>(x, ldx, W, ldw, (bf16*)out, ldo, bias, workspace, M, N, K, splits, max_stages,
+                     defer_sum, st);
+}
+
+// out[M, N] = sum of float32 partial sums [splits][M][N] (+ bias), in order.
+int slb_split_sum(const float* parts, void* out, int ldo, const float* bias, int out_f32, int M, int N,
+                  int splits, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (splits < 1 || ldo < N || M > 65535) return SLB_ERR_BAD_ARG;
+    if (out_f32)
+        return slb_launch(gemm_tc_reduce_kernel<float>, dim3((N + 255) / 256, M), dim3(256), 0, st, parts,
+                          (float*)out, ldo, bias, M, N, splits);
+    return slb_launch(gemm_tc_reduce_kernel<bf16>, dim3((N + 255) / 256, M), dim3(256), 0, st, parts,
+                      (bf16*)out, ldo, bias, M, N, splits);
 }
 
 // 0 while no wait has timed out; else (role << 8 | code) of the first one.

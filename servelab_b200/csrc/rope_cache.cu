@@ -19,7 +19,8 @@
 // computes sin/cos of its slot once and walks the heads with them.
 template <typename T>
 __global__ void qkv_rope_cache_kernel(
-    const T* __restrict__ qkv, int ld_qkv, const float* __restrict__ bias,
+    const T* __restrict__ qkv, int ld_qkv, const float* __restrict__ parts, int nparts,
+    size_t part_stride, const float* __restrict__ bias,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ block_table, int max_pages, int page_size,
     const float* __restrict__ inv_freq, int rotary_dim,
@@ -49,13 +50,21 @@ __global__ void qkv_rope_cache_kernel(
         have_page = page >= 0;                         // no page: nothing may be written
         kv_base = ((size_t)(have_page ? page : 0) * Hkv * page_size + pos % page_size) * D;
     }
-    const T* x = qkv + (size_t)t * ld_qkv;
+    // the projection arrives either as one tensor or as float32 partial sums
+    // [nparts][T][ld_qkv] of a product split along K (added in order)
+    const T* x = qkv ? qkv + (size_t)t * ld_qkv : nullptr;
+    const float* px = nparts > 0 ? parts + (size_t)t * ld_qkv : nullptr;
     const int heads = write ? H + 2 * Hkv : H;
     for (int j = head_lane; j < heads; j += head_lanes) {
         const bool is_v = j >= H + Hkv;
         const int a = is_v ? c0 : e0, b = is_v ? c1 : e1;
         const size_t off = (size_t)j * D;
-        float va = to_float(x[off + a]), vb = to_float(x[off + b]);
+        float va = 0.f, vb = 0.f;
+        if (x) { va = to_float(x[off + a]); vb = to_float(x[off + b]); }
+        for (int p = 0; p < nparts; ++p) {
+            va += px[p * part_stride + off + a];
+            vb += px[p * part_stride + off + b];
+        }
         if (bias) { va += bias[off + a]; vb += bias[off + b]; }
         if (rot && !is_v) {
             const float ra = va * cs - vb * sn;
@@ -76,7 +85,8 @@ __global__ void qkv_rope_cache_kernel(
 }
 
 template <typename T>
-static int launch_qkv_rope_cache(const T* qkv, int ld_qkv, const float* bias, const int* positions,
+static int launch_qkv_rope_cache(const T* qkv, int ld_qkv, const float* parts, int nparts,
+                                 long long part_stride, const float* bias, const int* positions,
                                  const int* seq_of_token, const int* block_table, int max_pages,
                                  int page_size, const float* inv_freq, int rotary_dim, T* q_out,
                                  int ld_q, T* k_cache, T* v_cache, int T_, int H, int Hkv, int D,
@@ -94,8 +104,9 @@ static int launch_qkv_rope_cache(const T* qkv, int ld_qkv, const float* bias, co
     if (lanes > heads) lanes = heads;
     int threads = slots * lanes;
     threads = (threads + 31) / 32 * 32;
-    return slb_launch(qkv_rope_cache_kernel<T>, dim3(T_), dim3(threads), 0, st, qkv, ld_qkv, bias,
-                      positions, seq_of_token, block_table, max_pages, page_size, inv_freq,
+    if ((qkv == nullptr) == (nparts <= 0)) return SLB_ERR_BAD_ARG;      // exactly one input form
+    return slb_launch(qkv_rope_cache_kernel<T>, dim3(T_), dim3(threads), 0, st, qkv, ld_qkv, parts,
+                      nparts, (size_t)part_stride, bias, positions, seq_of_token, block_table, max_pages, page_size, inv_freq,
                       rotary_dim, q_out, ld_q, k_cache, v_cache, H, Hkv, D, slots);
 }
 
@@ -105,7 +116,7 @@ int slb_qkv_rope_cache_f32(const float* qkv, int ld_qkv, const float* bias, cons
                            int page_size, const float* inv_freq, int rotary_dim, float* q_out,
                            int ld_q, float* k_cache, float* v_cache, int T, int H, int Hkv, int D,
                            cudaStream_t st) {
-    return launch_qkv_rope_cache<float>(qkv, ld_qkv, bias, positions, seq_of_token, block_table,
+    return launch_qkv_rope_cache<float>(qkv, ld_qkv, nullptr, 0, 0, bias, positions, seq_of_token, block_table,
                                         max_pages, page_size, inv_freq, rotary_dim, q_out, ld_q,
                                         k_cache, v_cache, T, H, Hkv, D, st);
 }
@@ -114,8 +125,19 @@ int slb_qkv_rope_cache_bf16(const bf16* qkv, int ld_qkv, const float* bias, cons
                             int page_size, const float* inv_freq, int rotary_dim, bf16* q_out,
                             int ld_q, bf16* k_cache, bf16* v_cache, int T, int H, int Hkv, int D,
                             cudaStream_t st) {
-    return launch_qkv_rope_cache<bf16>(qkv, ld_qkv, bias, positions, seq_of_token, block_table,
+    return launch_qkv_rope_cache<bf16>(qkv, ld_qkv, nullptr, 0, 0, bias, positions, seq_of_token, block_table,
                                        max_pages, page_size, inv_freq, rotary_dim, q_out, ld_q,
                                        k_cache, v_cache, T, H, Hkv, D, st);
+}
+// the fused q|k|v projection arrives as float32 partial sums [nparts][T][ld_qkv]
+int slb_qkv_rope_cache_parts_bf16(const float* parts, int nparts, long long part_stride, int ld_qkv,
+                                  const float* bias, const int* positions, const int* seq_of_token,
+                                  const int* block_table, int max_pages, int page_size,
+                                  const float* inv_freq, int rotary_dim, bf16* q_out, int ld_q,
+                                  bf16* k_cache, bf16* v_cache, int T, int H, int Hkv, int D,
+                                  cudaStream_t st) {
+    return launch_qkv_rope_cache<bf16>(nullptr, ld_qkv, parts, nparts, part_stride, bias, positions,
+                                       seq_of_token, block_table, max_pages, page_size, inv_freq,
+                                       rotary_dim, q_out, ld_q, k_cache, v_cache, T, H, Hkv, D, st);
 }
 }

@@ -96,6 +96,14 @@ class CausalLM:
                 total += t.numel() * t.element_size()
         return total
 
+    @staticmethod
+    def _plain_unless(part, delta):
+        """An update may travel as partial sums of a K-split product (``SplitSum``);
+        parts that do not say they accept one get the plain tensor."""
+        if isinstance(delta, K.SplitSum) and not getattr(part, "accepts_split_sum", False):
+            return delta.materialize()
+        return delta
+
     # ----------------------------------------------------------- forward
     def forward(self, ctx, caches: Dict[int, LayerCache]) -> torch.Tensor:
         """Run the step's tokens; ``caches`` maps a run's index to its cache.
@@ -107,9 +115,11 @@ class CausalLM:
         delta = None
         for i, run in enumerate(self.spec.run_order):
             owner = i if run.cache_of is None else run.cache_of
-            resid, delta = self.blocks[run.layer].forward(ctx, resid, delta, caches[owner],
-                                                          run.cache_of is None)
+            block = self.blocks[run.layer]
+            resid, delta = block.forward(ctx, resid, self._plain_unless(block, delta), caches[owner],
+                                         run.cache_of is None)
         if ctx.num_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.env.device)
-        x = self.final_norm.forward(ctx, resid, delta, out_rows=ctx.logit_rows)
+        x = self.final_norm.forward(ctx, resid, self._plain_unless(self.final_norm, delta),
+                                    out_rows=ctx.logit_rows)
         return linear(x, self.lm_head, out_dtype=torch.float32)

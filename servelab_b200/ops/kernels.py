@@ -19,6 +19,28 @@ _F32, _BF16 = torch.float32, torch.bfloat16
 launch_count = 0       # launches of this package's kernels (library GEMMs not included)
 
 
+class SplitSum:
+    """A [M, N] result that exists as float32 partial sums ``parts`` [splits, M, N]
+    of a matrix product split along K (plus an optional float32 ``bias`` [N] still
+    to be added).  Kernels that consume it add the parts in order, so no separate
+    reduction is launched; ``materialize()`` produces the plain tensor."""
+
+    def __init__(self, parts: torch.Tensor, bias: Optional[torch.Tensor], dtype: torch.dtype):
+        self.parts, self.bias, self.dtype = parts, bias, dtype
+
+    @property
+    def shape(self):
+        return self.parts.shape[1:]
+
+    def materialize(self) -> torch.Tensor:
+        S, M, N = self.parts.shape
+        out = torch.empty((M, N), dtype=self.dtype, device=self.parts.device)
+        L.check(L.core().slb_split_sum(self.parts.data_ptr(), out.data_ptr(), out.stride(0),
+                                       _p(self.bias), 1 if self.dtype == _F32 else 0, M, N, S,
+                                       _stream()), "split_sum")
+        return out
+
+
 def _stream() -> int:
     global launch_count
     launch_count += 1
@@ -57,6 +79,16 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
     """resid += delta (in place, float32; skipped when ``row_map`` selects rows);
     out[r] = rmsnorm(resid[src(r)] (+ delta)) * weight."""
     rows = out.shape[0]
+    if isinstance(delta, SplitSum):
+        if out.dtype != _BF16:
+            delta = delta.materialize()
+        else:
+            S, M, N = delta.parts.shape
+            L.check(L.core().slb_add_rmsnorm_parts_bf16(
+                resid.data_ptr(), delta.parts.data_ptr(), S, M * N, _p(delta.bias),
+                weight.data_ptr(), out.data_ptr(), _p(row_map), rows, out.shape[1], float(eps),
+                _stream()), "add_rmsnorm")
+            return
     fn = getattr(L.core(), "slb_add_rmsnorm_" + _suffix(out.dtype))
     L.check(fn(resid.data_ptr(), _p(delta), weight.data_ptr(), out.data_ptr(), _p(row_map),
                rows, out.shape[1], float(eps), _stream()), "add_rmsnorm")
@@ -75,6 +107,20 @@ def qkv_rope_cache(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: t
                    inv_freq: Optional[torch.Tensor], rotary_dim: int, q_out: torch.Tensor,
                    k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
                    num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+    if isinstance(qkv, SplitSum):
+        if bias is not None and qkv.bias is not None:
+            raise L.KernelError("qkv_rope_cache: two biases")
+        if q_out.dtype != _BF16:
+            qkv = qkv.materialize()
+        else:
+            S, M, N = qkv.parts.shape
+            L.check(L.core().slb_qkv_rope_cache_parts_bf16(
+                qkv.parts.data_ptr(), S, M * N, N, _p(bias if bias is not None else qkv.bias),
+                positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
+                block_table.shape[1], page_size, _p(inv_freq), rotary_dim, q_out.data_ptr(),
+                q_out.stride(0), _p(k_cache), _p(v_cache), M, num_heads, num_kv_heads, head_dim,
+                _stream()), "qkv_rope_cache")
+            return
     fn = getattr(L.core(), "slb_qkv_rope_cache_" + _suffix(qkv.dtype))
     L.check(fn(qkv.data_ptr(), qkv.stride(0), _p(bias), positions.data_ptr(),
                seq_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size,
@@ -213,20 +259,30 @@ def tc_decode_splits(n_out: int, k: int) -> int:
     return max(1, min(want, kblocks // 4 if kblocks >= 8 else 1))
 
 
-def gemm_tc_decode(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
-                   bias: Optional[torch.Tensor] = None, splits: int = 0) -> None:
+def gemm_tc_decode(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor],
+                   bias: Optional[torch.Tensor] = None, splits: int = 0,
+                   defer_sum: bool = False, out_dtype: Optional[torch.dtype] = None):
     """out[M,N] = x[M,K] . w[N,K]^T (+ bias) for up to 64 tokens on tcgen05 tensor
-    cores with TMA-streamed weights; bfloat16 operands, float32 or bfloat16 output."""
+    cores with TMA-streamed weights; bfloat16 operands, float32 or bfloat16 output.
+    With ``defer_sum`` and more than one K split the partial sums are returned as a
+    ``SplitSum`` (no reduction is launched); otherwise ``out`` (allocated if None)."""
+    global launch_count
     M, Kd = x.shape
     N = w.shape[0]
     splits = splits or tc_decode_splits(N, Kd)
-    ws = torch.empty(splits * M * N, dtype=_F32, device=x.device) if splits > 1 else None
+    out_dtype = out.dtype if out is not None else (out_dtype or x.dtype)
+    ws = torch.empty((splits, M, N), dtype=_F32, device=x.device) if splits > 1 else None
+    deferred = defer_sum and splits > 1
+    if out is None and not deferred:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     L.check(L.core().slb_gemm_tc_decode_bf16(
-        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
-        _p(bias), _p(ws), 1 if out.dtype == _F32 else 0, M, N, Kd, splits, tc_max_stages, _stream()),
-        "gemm_tc_decode")
-    global launch_count
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _p(out), out.stride(0) if out is not None else N,
+        _p(bias), _p(ws), 1 if out_dtype == _F32 else 0, M, N, Kd, splits, tc_max_stages,
+        1 if deferred else 0, _stream()), "gemm_tc_decode")
+    if deferred:
+        return SplitSum(ws, bias, out_dtype)
     launch_count += 1 if splits > 1 else 0
+    return out
 
 
 def gemm_tc_status(reset: bool = False) -> int:

@@ -8,7 +8,7 @@ is present, the first use raises ``KernelsUnavailable``.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Dict
 
 from ..csrc import build as _build
@@ -22,7 +22,7 @@ class KernelError(RuntimeError):
     pass
 
 
-P, I, F = c_void_p, c_int, c_float
+P, I, F, LL = c_void_p, c_int, c_float, c_longlong
 
 _CORE_SIGNATURES = {
     "slb_embedding_f32": [P, P, P, I, I, I, P],
@@ -41,7 +41,10 @@ _CORE_SIGNATURES = {
     "slb_gemm_simt_bf16_f32out": [P, I, P, I, P, I, P, I, I, I, P],
     "slb_sample_rows": [P, I, I, I, P, P, P, P, P, P, P, P],
     "slb_gemm_skinny_bf16": [P, I, P, I, P, I, P, I, I, I, I, I, P],
-    "slb_gemm_tc_decode_bf16": [P, I, P, I, P, I, P, P, I, I, I, I, I, I, P],
+    "slb_gemm_tc_decode_bf16": [P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, P],
+    "slb_split_sum": [P, P, I, P, I, I, I, I, P],
+    "slb_add_rmsnorm_parts_bf16": [P, P, I, LL, P, P, P, P, I, I, F, P],
+    "slb_qkv_rope_cache_parts_bf16": [P, I, LL, I, P, P, P, P, I, I, P, I, P, I, P, P, I, I, I, I, P],
     "slb_gemm_tc_status": [I],
 }
 

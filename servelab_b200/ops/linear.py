@@ -30,6 +30,9 @@ def _skinny_ok(x, w, M):
 
 
 tc_max_tokens = 16         # up to this many tokens the tcgen05 weight-streaming kernel runs
+defer_split_sums = False   # hand K-split partial sums to the consuming kernel instead of
+                           # reducing them in a kernel of their own (measured slower: the
+                           # consumers run few blocks and are bound by latency)
 
 
 def _tc_ok(x, w, M):
@@ -39,7 +42,10 @@ def _tc_ok(x, w, M):
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+           out_dtype: Optional[torch.dtype] = None, defer_sum: bool = False):
+    """``defer_sum``: the caller hands the result to a kernel that accepts a
+    ``SplitSum`` (partial sums of a K-split product); it may then get one instead
+    of a tensor."""
     M, Kd = x.shape
     N = w.shape[0]
     out_dtype = out_dtype or x.dtype
@@ -51,9 +57,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     if M == 0:
         return torch.empty((0, N), dtype=out_dtype, device=x.device)
     if _tc_ok(x, w, M):
-        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        K.gemm_tc_decode(x, w, out, bias)
-        return out
+        return K.gemm_tc_decode(x, w, None, bias, defer_sum=defer_sum and defer_split_sums,
+                                out_dtype=out_dtype)
     if _skinny_ok(x, w, M):
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         K.gemm_skinny(x, w, out, bias)

@@ -8,6 +8,7 @@ happens inside the next norm kernel.
 
 from __future__ import annotations
 
+from ..ops.kernels import SplitSum
 from .base import Block
 from .registry import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, build_part, part_class,
                        register_block)
@@ -46,8 +47,18 @@ class PreNormBlock(Block):
         for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward):
             p.load(store)
 
+    accepts_split_sum = True      # the incoming ``delta`` may be a SplitSum
+
+    @staticmethod
+    def _for_norm(norm, delta):
+        """A K-split product may arrive as partial sums; norms that cannot add them
+        themselves get the plain tensor."""
+        if isinstance(delta, SplitSum) and not getattr(norm, "accepts_split_sum", False):
+            return delta.materialize()
+        return delta
+
     def forward(self, ctx, resid, delta, cache, owns_cache):
-        x = self.mixer_norm.forward(ctx, resid, delta)
+        x = self.mixer_norm.forward(ctx, resid, self._for_norm(self.mixer_norm, delta))
         a = self.mixer.forward(ctx, x, cache, owns_cache)
-        x = self.ff_norm.forward(ctx, resid, a)
+        x = self.ff_norm.forward(ctx, resid, self._for_norm(self.ff_norm, a))
         return resid, self.feed_forward.forward(ctx, x)

@@ -18,6 +18,7 @@ from .registry import register_norm
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
     graph_safe = True
+    accepts_split_sum = True      # ``delta`` may be a SplitSum (parts of a K-split product)
 
     @classmethod
     def declare(cls, spec, prefix):
