@@ -77,6 +77,81 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
+// ---- bulk asynchronous copies (one instruction per row) tracked by an mbarrier ----
+constexpr uint32_t ATTN_SPIN_LIMIT = 1u << 22;   // polls before a wait gives up
+__device__ int attn_status_word = 0;             // 0, or a code of the first wait that gave up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+// Bounded wait for the phase of the given parity: false after ATTN_SPIN_LIMIT polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < ATTN_SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gsrc, uint32_t bytes,
+                                              uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// One 64-key tile of K and V by bulk copies: thread t fetches row t % 64 of K (t < 64)
+// or of V (t >= 64) with ONE instruction of D*2 bytes; every thread arrives once on
+// `bar` (initialised with a count of NTHREADS), with the bytes it expects if it
+// copies.  Rows at or beyond kend and rows whose page is absent are filled with
+// zeros by ordinary stores.  Callers make sure all earlier reads of the stage are
+// done (a block-wide barrier) before calling.
+__device__ __forceinline__ void load_kv_tile_bulk(bf16* Ks, bf16* Vs, uint64_t* bar,
+                                                  const bf16* __restrict__ kc,
+                                                  const bf16* __restrict__ vc,
+                                                  const int* __restrict__ table, int k0, int kend,
+                                                  int kvh, int Hkv, int ps) {
+    static_assert(NTHREADS == 2 * BN, "one row of K or V per thread");
+    const int r = threadIdx.x & (BN - 1);
+    const bool is_v = threadIdx.x >= BN;
+    const int kp = k0 + r;
+    bool ok = kp < kend;
+    int page = -1, slot = 0;
+    if (ok) {
+        const bool pow2 = (ps & (ps - 1)) == 0;
+        const int lp = pow2 ? kp >> (__ffs(ps) - 1) : kp / ps;
+        slot = pow2 ? kp & (ps - 1) : kp - lp * ps;
+        page = table[lp];
+        ok = page >= 0;
+    }
+    bf16* dst = (is_v ? Vs : Ks) + r * LDS;
+    if (ok) {
+        const bf16* src = (is_v ? vc : kc) + (((size_t)page * Hkv + kvh) * ps + slot) * D;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive_expect_tx(bar, D * 2);
+        bulk_copy_g2s(dst, src, D * 2, bar);
+    } else {
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0, 0, 0, 0);
+        mbar_arrive(bar);
+    }
+}
+
 // Issue the loads of one 64-key tile of K and V (keys k0 .. k0+63 of the request).
 // Rows at or beyond kend, and rows whose page is absent, are zero-filled.
 __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __restrict__ kc,
@@ -348,6 +423,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
     bf16* stage0 = Qs + 16 * LDS;
     float* red_o = reinterpret_cast<float*>(stage0);       // [4][16][D] after the key loop
     __shared__ float red_m[4][16], red_l[4][16];
+    __shared__ __align__(8) uint64_t full_bar[DSTAGES];    // a stage's K and V rows have landed
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x;
@@ -375,16 +451,23 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
         cp_async16(Qs + r * LDS + c * 8,
                    q + (size_t)s * ldq + (size_t)(kvh * g + h0 + (ok ? r : 0)) * D + c * 8, ok);
     }
-    // groups: {Q, tile 0}, {tile 1}, ... ; DSTAGES - 1 tiles are in flight ahead of the
-    // one being used (empty groups keep the count uniform)
+    cp_async_commit();
+    if (tid == 0) {
+#pragma unroll
+        for (int p = 0; p < DSTAGES; ++p) mbar_init(&full_bar[p], NTHREADS);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    // DSTAGES - 1 tiles are in flight ahead of the one being used
 #pragma unroll
     for (int p = 0; p < DSTAGES - 1; ++p) {
         if (p < ntiles) {
             bf16* Kp = stage0 + p * STAGE_ELEMS;
-            load_kv_tile(Kp, Kp + BN * LDS, kc, vc, table, kstart + p * BN, ctx, kvh, Hkv, ps);
+            load_kv_tile_bulk(Kp, Kp + BN * LDS, &full_bar[p], kc, vc, table, kstart + p * BN, ctx,
+                              kvh, Hkv, ps);
         }
-        cp_async_commit();
     }
+    cp_async_wait<0>();                                     // the Q tile
 
     const int r_lo = lane >> 2, r_hi = r_lo + 8;
     const int pos_lo = r_lo < nrows ? pos : -1;
@@ -397,20 +480,23 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
         for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
+    bool ok = true;
     for (int t = 0; t < ntiles; ++t) {
         bf16* Ks = stage0 + (t % DSTAGES) * STAGE_ELEMS;
         bf16* Vs = Ks + BN * LDS;
         const int tn = t + DSTAGES - 1;                      // its stage was freed by round t - 1
         if (tn < ntiles) {
             bf16* Kn = stage0 + (tn % DSTAGES) * STAGE_ELEMS;
-            load_kv_tile(Kn, Kn + BN * LDS, kc, vc, table, kstart + tn * BN, ctx, kvh, Hkv, ps);
+            load_kv_tile_bulk(Kn, Kn + BN * LDS, &full_bar[tn % DSTAGES], kc, vc, table,
+                              kstart + tn * BN, ctx, kvh, Hkv, ps);
         }
-        cp_async_commit();
-        cp_async_wait<DSTAGES - 1>();
-        __syncthreads();
-        if (t == 0) load_q_frags(qf, Qs);
+        ok = mbar_wait(&full_bar[t % DSTAGES], (t / DSTAGES) & 1);
+        if (t == 0) {
+            __syncthreads();                                 // Q rows of the other threads
+            load_q_frags(qf, Qs);
+        }
         const int k0 = kstart + t * BN + warp * 16;         // this warp's 16 keys of the tile
-        if (k0 < ctx) {
+        if (ok && k0 < ctx) {
             float sc[2][4];
             qk_tile<2>(sc, qf, Ks, warp * 16);
             // every key of this warp's 16 is inside the context and the window: no mask
@@ -420,9 +506,16 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
                 softmax_tile<2, true>(sc, o, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2);
             pv_tile<2>(o, sc, Vs, warp * 16);
         }
-        __syncthreads();
+        // the stage may be refilled next round; if any thread's wait gave up, all stop
+        if (!__syncthreads_and(ok)) {
+            if (tid == 0) atomicCAS(&attn_status_word, 0, 1);
+            // copies already requested must not land in memory of a later block: wait
+            // for them once more (bounded), then leave without writing a result
+            for (int tt = t; tt < min(ntiles, t + DSTAGES); ++tt)
+                mbar_wait(&full_bar[tt % DSTAGES], (tt / DSTAGES) & 1);
+            return;
+        }
     }
-    cp_async_wait<0>();
     __syncthreads();
 
     pdl_launch_dependents();
@@ -507,6 +600,18 @@ SLB_DEFINE_PDL_SWITCH
 extern "C" {
 
 int slb_attention_head_dim() { return D; }
+
+// 0 unless a bounded wait inside an attention kernel gave up (the kernel then wrote
+// nothing for its block).  Reading synchronises with the device.
+int slb_attention_status(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, attn_status_word, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(attn_status_word, &zero, sizeof(int));
+    }
+    return v;
+}
 int slb_prefill_attention_tile_rows() { return BM; }
 int slb_decode_attention_max_splits() { return MAX_SPLITS; }
 

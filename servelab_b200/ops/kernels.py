@@ -186,6 +186,12 @@ def _num_sms() -> int:
     return _sm_count
 
 
+def attention_status(head_dim: int, reset: bool = False) -> int:
+    """0 unless a bounded wait inside the tensor-core attention kernels for this head
+    size gave up (synchronises with the device)."""
+    return L.attention(head_dim).slb_attention_status(1 if reset else 0)
+
+
 def has_fast_attention(head_dim: int) -> bool:
     """The tensor-core kernels exist for head sizes that are multiples of 16 up to
     256; the library for a head size is built when it is first asked for."""

@@ -104,6 +104,7 @@ _ATTN_SIGNATURES = {
     "slb_prefill_attention_tile_rows": [],
     "slb_decode_attention_max_splits": [],
     "slb_attention_head_dim": [],
+    "slb_attention_status": [I],
 }
 
 

@@ -391,3 +391,156 @@ def test_another_position_encoding_defined_in_the_test(dtype, tmp_path):
         for rid, ids in reqs.items():
             for pos in range(len(ids)):
                 assert float(np.abs(got[rid][pos] - ref[rid][pos]).max()) <= TOL[dtype] * 2, (rid, pos)
+
+
+# --------------------------------------------------------------------------- #
+# a feed-forward with routing, defined in this test (top-1 of three experts)
+# --------------------------------------------------------------------------- #
+
+def _register_routed_ff():
+    from servelab_b200.config import (AttentionSpec, BlockSpec, LayerRun, ModelSpec, PartSpec,
+                                      RMSNormSpec, RotarySpec, register_architecture)
+    from servelab_b200.ops.linear import linear
+    from servelab_b200.parts import FEED_FORWARDS, FeedForward, register_feed_forward
+    from servelab_b200.weights import MATRIX, TensorDecl
+
+    if "toy_top1_experts" in FEED_FORWARDS:
+        return
+
+    @dataclass(frozen=True)
+    class RoutedSpec(PartSpec):
+        kind: str = "toy_top1_experts"
+        hidden_size: int = 0
+        intermediate_size: int = 0
+        num_experts: int = 0
+
+    @register_feed_forward("toy_top1_experts")
+    class Top1Experts(FeedForward):
+        """Router logits in float32; each token goes through the one expert with the
+        largest logit (relu MLP), weighted by the softmax probability of that expert."""
+
+        @classmethod
+        def declare(cls, spec, prefix):
+            out = [TensorDecl(prefix + ".router.weight", (spec.num_experts, spec.hidden_size), MATRIX)]
+            for e in range(spec.num_experts):
+                out += [TensorDecl(f"{prefix}.experts.{e}.up.weight",
+                                   (spec.intermediate_size, spec.hidden_size), MATRIX),
+                        TensorDecl(f"{prefix}.experts.{e}.down.weight",
+                                   (spec.hidden_size, spec.intermediate_size), MATRIX)]
+            return out
+
+        def load(self, store):
+            self.router = store.get(self.prefix + ".router.weight").float()
+            self.up = [store.get(f"{self.prefix}.experts.{e}.up.weight") for e in range(self.spec.num_experts)]
+            self.down = [store.get(f"{self.prefix}.experts.{e}.down.weight") for e in range(self.spec.num_experts)]
+
+        def forward(self, ctx, x):
+            probs = torch.softmax(x.float() @ self.router.t(), dim=-1)
+            choice = probs.argmax(dim=-1)
+            out = torch.zeros_like(x)
+            for e in range(self.spec.num_experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                h = torch.relu(linear(x[rows].contiguous(), self.up[e]))
+                y = linear(h, self.down[e]).float() * probs[rows, e][:, None]
+                out[rows] = y.to(x.dtype)
+            return out
+
+    class ToyMoEConfig:
+        architecture = "ToyRoutedForCausalLM"
+
+        def __init__(self, d):
+            self.d = dict(d)
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+        def to_dict(self):
+            return dict(self.d, architectures=[self.architecture])
+
+        def to_model_spec(self):
+            hid = self.d["hidden_size"]
+            norm = RMSNormSpec(dim=hid, eps=1e-6)
+            attn = AttentionSpec(hidden_size=hid, num_heads=2, num_kv_heads=1, head_dim=16,
+                                 qkv_bias=True, position=RotarySpec(head_dim=16, rotary_dim=16, theta=1e4))
+            ff = RoutedSpec(hidden_size=hid, intermediate_size=48, num_experts=3)
+            block = BlockSpec(mixer=attn, feed_forward=ff, mixer_norm=norm, ff_norm=norm)
+            return ModelSpec(architecture=self.architecture, hidden_size=hid,
+                             vocab_size=self.d["vocab_size"], layers=(block, block),
+                             run_order=(LayerRun(0), LayerRun(1)), final_norm=norm,
+                             tie_word_embeddings=True, max_position_embeddings=128)
+
+    register_architecture(ToyMoEConfig.architecture, ToyMoEConfig)
+
+
+def _toy_routed_plain(folder, ids):
+    _, w = P.load_folder(folder)
+    T = len(ids)
+    x = P.embed(torch.tensor(ids), w["model.embed_tokens.weight"])
+    inv, pos = P.rope_inv_freq(16, 1e4), torch.arange(T)
+    for layer in range(2):
+        p = f"model.layers.{layer}."
+        h = P.rms_norm(x, w[p + "input_layernorm.weight"], 1e-6)
+        q = P.rope(P.linear(h, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.q_proj.bias"]).view(T, 2, 16), pos, inv)
+        k = P.rope(P.linear(h, w[p + "self_attn.k_proj.weight"], w[p + "self_attn.k_proj.bias"]).view(T, 1, 16), pos, inv)
+        v = P.linear(h, w[p + "self_attn.v_proj.weight"], w[p + "self_attn.v_proj.bias"]).view(T, 1, 16)
+        x = x + P.linear(P.causal_attention(q, k, v), w[p + "self_attn.o_proj.weight"])
+        h = P.rms_norm(x, w[p + "post_attention_layernorm.weight"], 1e-6)
+        probs = torch.softmax(P.linear(h, w[p + "mlp.router.weight"]), dim=-1)
+        choice = probs.argmax(-1)
+        y = torch.zeros_like(h)
+        for t in range(T):
+            e = int(choice[t])
+            hid = torch.relu(P.linear(h[t:t + 1], w[f"{p}mlp.experts.{e}.up.weight"]))
+            y[t] = P.linear(hid, w[f"{p}mlp.experts.{e}.down.weight"])[0] * probs[t, e]
+        x = x + y
+    return P.linear(P.rms_norm(x, w["model.norm.weight"], 1e-6), w["model.embed_tokens.weight"]).numpy()
+
+
+def test_feed_forward_with_routing_defined_in_the_test(tmp_path):
+    """float32 only: with bfloat16 a near-tie of router logits may pick another expert."""
+    _register_routed_ff()
+    from servelab_b200.config import config_from_dict
+    from servelab_b200.replay import TraceSession
+    from servelab_b200.weights import write_random_model
+    cfg = {"architectures": ["ToyRoutedForCausalLM"], "hidden_size": 32, "vocab_size": 70}
+    folder = write_random_model(str(tmp_path / "moe"), config_from_dict(cfg), seed=3, std=0.2)
+    reqs = {f"m{i}": H.random_ids(n, 70, 40 + i) for i, n in enumerate([33, 41])}
+    ref = {rid: _toy_routed_plain(folder, ids) for rid, ids in reqs.items()}
+    for steps in (H.trace_whole(reqs), H.trace_mixed(reqs, seed=6, max_live=2, tail=10)):
+        sess = TraceSession(folder, "float32", H.peak_tokens(steps), page_size=8, max_live=2)
+        got = H.collect(steps, H.run_session(sess, steps), 70)
+        for rid, ids in reqs.items():
+            for pos in range(len(ids)):
+                assert float(np.abs(got[rid][pos] - ref[rid][pos]).max()) <= 5e-5, (rid, pos)
+
+
+# --------------------------------------------------------------------------- #
+# K-split partial sums handed to the consuming kernels (an optional path)
+# --------------------------------------------------------------------------- #
+
+def test_split_sums_consumed_by_norm_and_rope_kernels(tmp_path):
+    """With ``defer_split_sums`` the tcgen05 product leaves float32 partial sums and the
+    norm / rotary kernels add them; logits must agree with the default path."""
+    from servelab_b200.ops import linear as linear_ops
+    from servelab_b200.replay import TraceSession
+    cfg = dict(H.TINY_B, hidden_size=512, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+               intermediate_size=1024)
+    folder = H.make_model(str(tmp_path / "m"), cfg, 4)
+    reqs = {"a": H.random_ids(40, 512, 1), "b": H.random_ids(37, 512, 2)}
+    steps = H.trace_bulk_tail(reqs, tail=16)
+    outs = {}
+    for flag in (False, True):
+        linear_ops.defer_split_sums = flag
+        try:
+            sess = TraceSession(folder, "bfloat16", H.peak_tokens(steps), page_size=8, max_live=2)
+            outs[flag] = H.collect(steps, H.run_session(sess, steps), 512)
+        finally:
+            linear_ops.defer_split_sums = False
+    ref = {rid: H.plain_logits(folder, ids) for rid, ids in reqs.items()}
+    for rid, ids in reqs.items():
+        for pos in range(len(ids)):
+            assert float(np.abs(outs[True][rid][pos] - ref[rid][pos]).max()) <= 3e-2
+            assert float(np.abs(outs[True][rid][pos] - outs[False][rid][pos]).max()) <= 2e-2
