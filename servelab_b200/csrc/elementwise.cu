@@ -82,7 +82,7 @@ __device__ __forceinline__ float delta1(const TD* d, const float* parts, int npa
     return v;
 }
 
-template <typename TD, typename TO, bool VEC>
+template <typename TD, typename TO, bool VEC, bool PARTS>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const float* __restrict__ parts, int nparts, size_t part_stride,
                                    const float* __restrict__ pbias,
@@ -95,8 +95,9 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
     const int src = row_map ? row_map[r] : r;
     float* x = resid + (size_t)src * h;
     const TD* d = delta ? delta + (size_t)src * h : nullptr;
-    const float* pp = nparts > 0 ? parts + (size_t)src * h : nullptr;
-    const bool has_delta = d != nullptr || nparts > 0;
+    const float* pp = PARTS ? parts + (size_t)src * h : nullptr;
+    if (!PARTS) nparts = 0;
+    const bool has_delta = d != nullptr || PARTS;
     const bool write_back = (row_map == nullptr) && has_delta;
     TO* o = out + (size_t)r * h;
     float ss = 0.f;
@@ -190,13 +191,18 @@ static int launch_add_rmsnorm(float* resid, const TD* delta, const float* parts,
                               cudaStream_t st) {
     if (rows <= 0) return 0;
     if (h <= 0 || nparts < 0 || (nparts > 0 && parts == nullptr)) return SLB_ERR_BAD_ARG;
-    if (h % 4 == 0 && part_stride % 4 == 0)
-        return slb_launch(add_rmsnorm_kernel<TD, TO, true>, dim3(rows), dim3(norm_threads(h)), 0, st,
-                          resid, delta, parts, nparts, (size_t)part_stride, pbias, weight, out,
-                          row_map, h, eps);
-    return slb_launch(add_rmsnorm_kernel<TD, TO, false>, dim3(rows), dim3(norm_threads(h)), 0, st,
-                      resid, delta, parts, nparts, (size_t)part_stride, pbias, weight, out, row_map,
-                      h, eps);
+    const dim3 grid(rows), block(norm_threads(h));
+    const bool vec = h % 4 == 0 && part_stride % 4 == 0;
+#define SLB_NORM_LAUNCH(V, P)                                                                   \
+    return slb_launch(add_rmsnorm_kernel<TD, TO, V, P>, grid, block, 0, st, resid, delta, parts, \
+                      nparts, (size_t)part_stride, pbias, weight, out, row_map, h, eps)
+    if (nparts > 0) {
+        if (vec) SLB_NORM_LAUNCH(true, true);
+        SLB_NORM_LAUNCH(false, true);
+    }
+    if (vec) SLB_NORM_LAUNCH(true, false);
+    SLB_NORM_LAUNCH(false, false);
+#undef SLB_NORM_LAUNCH
 }
 
 template <typename T>

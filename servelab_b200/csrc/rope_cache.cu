@@ -17,7 +17,7 @@
 // rotation pair (i, i + rot/2); the slots after that are pairs of neighbouring
 // elements beyond the rotary part, which pass through.  Thread (i, lane-of-heads)
 // computes sin/cos of its slot once and walks the heads with them.
-template <typename T>
+template <typename T, bool PARTS>
 __global__ void qkv_rope_cache_kernel(
     const T* __restrict__ qkv, int ld_qkv, const float* __restrict__ parts, int nparts,
     size_t part_stride, const float* __restrict__ bias,
@@ -60,10 +60,14 @@ __global__ void qkv_rope_cache_kernel(
         const int a = is_v ? c0 : e0, b = is_v ? c1 : e1;
         const size_t off = (size_t)j * D;
         float va = 0.f, vb = 0.f;
-        if (x) { va = to_float(x[off + a]); vb = to_float(x[off + b]); }
-        for (int p = 0; p < nparts; ++p) {
-            va += px[p * part_stride + off + a];
-            vb += px[p * part_stride + off + b];
+        if (PARTS) {
+            for (int p = 0; p < nparts; ++p) {
+                va += px[p * part_stride + off + a];
+                vb += px[p * part_stride + off + b];
+            }
+        } else {
+            va = to_float(x[off + a]);
+            vb = to_float(x[off + b]);
         }
         if (bias) { va += bias[off + a]; vb += bias[off + b]; }
         if (rot && !is_v) {
@@ -105,7 +109,12 @@ static int launch_qkv_rope_cache(const T* qkv, int ld_qkv, const float* parts, i
     int threads = slots * lanes;
     threads = (threads + 31) / 32 * 32;
     if ((qkv == nullptr) == (nparts <= 0)) return SLB_ERR_BAD_ARG;      // exactly one input form
-    return slb_launch(qkv_rope_cache_kernel<T>, dim3(T_), dim3(threads), 0, st, qkv, ld_qkv, parts,
+    if (nparts > 0)
+        return slb_launch(qkv_rope_cache_kernel<T, true>, dim3(T_), dim3(threads), 0, st, qkv, ld_qkv,
+                          parts, nparts, (size_t)part_stride, bias, positions, seq_of_token,
+                          block_table, max_pages, page_size, inv_freq, rotary_dim, q_out, ld_q,
+                          k_cache, v_cache, H, Hkv, D, slots);
+    return slb_launch(qkv_rope_cache_kernel<T, false>, dim3(T_), dim3(threads), 0, st, qkv, ld_qkv, parts,
                       nparts, (size_t)part_stride, bias, positions, seq_of_token, block_table, max_pages, page_size, inv_freq,
                       rotary_dim, q_out, ld_q, k_cache, v_cache, H, Hkv, D, slots);
 }
