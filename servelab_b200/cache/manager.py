@@ -61,6 +61,8 @@ class PagePool:
         self.free: deque = deque(range(num_pages))
         self.tables: Dict[str, List[int]] = {}
         self._first_live: Dict[str, int] = {}
+        self._serial = 0                       # bumped whenever any table changes
+        self.stamp: Dict[str, int] = {}        # request -> serial of its table's last change
 
     def num_free(self) -> int:
         return len(self.free)
@@ -84,13 +86,20 @@ class PagePool:
             raise CacheError(f"request {req} already has a block table")
         self.tables[req] = []
         self._first_live[req] = 0
+        self._touch(req)
+
+    def _touch(self, req: str) -> None:
+        self._serial += 1
+        self.stamp[req] = self._serial
 
     def grow(self, req: str, num_tokens: int) -> List[int]:
         need = self.new_pages_needed(req, num_tokens)
         if need > len(self.free):
             raise CacheError("grow() without enough free pages")
         new = [self.free.popleft() for _ in range(need)]
-        self.tables[req].extend(new)
+        if new:
+            self.tables[req].extend(new)
+            self._touch(req)
         return new
 
     def trim(self, req: str, next_position: int) -> List[int]:
@@ -108,11 +117,14 @@ class PagePool:
                 table[lp] = -1
         self._first_live[req] = max(self._first_live[req], dead_pages)
         self.free.extend(freed)
+        if freed:
+            self._touch(req)
         return freed
 
     def close(self, req: str) -> List[int]:
         table = self.tables.pop(req, None)
         self._first_live.pop(req, None)
+        self.stamp.pop(req, None)
         if table is None:
             return []
         freed = [p for p in table if p >= 0]
@@ -180,6 +192,11 @@ class CacheManager:
 
     def state_slot(self, req: str) -> int:
         return self.slots.owner[req]
+
+    def table_stamp(self, req: str, group: int) -> int:
+        """A number that changes whenever the request's table in that group changes
+        (unique across requests of the group), so callers can cache copies."""
+        return self.pools[group].stamp[req]
 
     def can_ever_hold(self, total_tokens: int, max_portion: int) -> bool:
         return all(p.peak_pages(total_tokens, max_portion) <= p.num_pages - self.reserve_pages

@@ -86,7 +86,9 @@ class ModelRunner:
         return BatchEntry(tokens=tokens, start=start, want=want,
                           block_tables=[self.cache.block_table(request_id, g)
                                         for g in range(self.num_groups)],
-                          state_slot=self.cache.state_slot(request_id))
+                          state_slot=self.cache.state_slot(request_id),
+                          table_stamps=[self.cache.table_stamp(request_id, g)
+                                        for g in range(self.num_groups)])
 
     def check_tokens(self, tokens: Sequence[int]) -> None:
         v = self.spec.vocab_size
