@@ -1,0 +1,494 @@
+// Paged prefill attention on the 5th-generation tensor cores (tcgen05), bfloat16,
+// head sizes 64 and 128, page sizes that are powers of two from 8.
+//
+// Work unit: 128 query rows x one kv head; the rows of a request are flattened as
+// rho = local_token * g + head_in_group (whole tokens per tile: floor(128 / g) of
+// them), so the g query heads of a group share every key/value tile.  Per 64-key
+// tile, with both accumulators in tensor memory (TMEM):
+//
+//   loader warp     TMA tensor copies (128-byte swizzle) of the tile's pages of K and V
+//                   into a two-stage shared-memory ring          -> kv_full[stage]
+//   MMA warp        S = Q.K^T   (tcgen05.mma M=128 N=64,  K=16 x D/16)  -> s_full
+//                   O += P.V    (tcgen05.mma M=128 N=D,   K=16 x 4)     -> kv_empty, pv_done
+//   softmax warps   thread r owns row r: tcgen05.ld its 64 scores, mask, running max and
+//                   sum in float32 (no shuffles: a row lives in one thread), P as
+//                   bfloat16 into shared memory in the swizzled operand layout -> p_full
+//
+// The running maximum is only raised when the tile's maximum exceeds it by more than
+// 2^8 (scores are in the base-2 domain); otherwise the stale maximum keeps being used
+// (probabilities stay below 256, exact in the float32 sums), so the accumulator in
+// TMEM is rescaled rarely.  Two blocks fit on an SM: one does its softmax while the
+// other's MMAs run.
+//
+// Every mbarrier wait is bounded; a role that gives up records a code in the status
+// word and leaves its loop; the block then frees its TMEM and returns without a result.
+//
+// Reference analogue: the torch loop over sequences (servelab/parallel/
+// tp_model.py:136-157); masking and softmax follow it (r <= a, optional window).
+#include <cuda.h>
+
+#include "common.cuh"
+
+#if (SLB_HEAD_DIM == 64 || SLB_HEAD_DIM == 128)
+
+namespace {
+
+constexpr int D = SLB_HEAD_DIM;
+constexpr int PANELS = D / 64;                 // 64-element (128-byte) column panels
+constexpr int BM = 128, BN = 64;
+constexpr int THREADS = 192;                   // warp 0 loader, warp 1 MMA, warps 2..5 softmax
+constexpr int TMEM_COLS = 256;                 // S at columns 0..63, O at 64..64+D-1
+constexpr int S_COL = 0, O_COL = 64;
+constexpr int Q_BYTES = PANELS * BM * 128;
+constexpr int KV_PANEL_BYTES = BN * 128;
+constexpr int KV_TILE_BYTES = PANELS * KV_PANEL_BYTES;
+constexpr int P_BYTES = BM * 128;
+constexpr int OFF_Q = 0;
+constexpr int OFF_K = OFF_Q + Q_BYTES;
+constexpr int OFF_V = OFF_K + 2 * KV_TILE_BYTES;
+constexpr int OFF_P = OFF_V + 2 * KV_TILE_BYTES;
+constexpr int OFF_BAR = OFF_P + P_BYTES;
+constexpr size_t TC_ATTN_SMEM = OFF_BAR + 128;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr float RESCALE_THRESHOLD = 8.f;       // log2 of the largest probability tolerated
+
+__device__ int tc_attn_status = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0,
+                                            int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+// Shared-memory matrix descriptor, 128-byte swizzle, rows of 128 bytes in groups of 8
+// (1024 bytes).  lbo16: leading byte offset >> 4 (distance of 64-element panels for an
+// operand that is contiguous along M/N; unused for K-major operands).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo16) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)(lbo16 & 0x3FFF) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+__device__ __forceinline__ unsigned pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+__global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
+    const bf16* __restrict__ q, int ldq, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, int ldo,
+    const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_q,
+    const int* __restrict__ ctx_len, const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
+    int H, int Hkv, int ps, int box_rows, float scale_log2, int window, int* __restrict__ status) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);    // [2]
+    uint64_t* kv_empty = kv_full + 2;                                   // [2]
+    uint64_t* s_full = kv_empty + 2;
+    uint64_t* p_full = s_full + 1;
+    uint64_t* pv_done = p_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the last tiles of a prompt see the most keys: start them first
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int kvh = blockIdx.y;
+    const int s = tile_seq[tile];
+    const int row0 = tile_row0[tile];
+    const int g = H / Hkv;
+    const int q0 = cu_q[s];
+    const int qlen = cu_q[s + 1] - q0;
+    const int ctx = ctx_len[s];
+    const int rows_per_tile = (BM / g) * g;
+    const int nrows = min(rows_per_tile, qlen * g - row0);
+    const int tok0 = row0 / g;
+    const int pos_base = ctx - qlen;
+    const int* table = block_table + (size_t)s * max_pages;
+    const bool aligned = (smem_u32(smem) & 1023u) == 0;     // the swizzle needs 1024-byte alignment
+    if (nrows <= 0 || !aligned) {
+        if (!aligned && threadIdx.x == 0) atomicCAS(status, 0, 0x900);
+        return;
+    }
+    const int p_first = pos_base + tok0;
+    const int p_last = pos_base + tok0 + (nrows - 1) / g;
+    int kbeg = 0;
+    if (window > 0) kbeg = max(0, p_first - window + 1) / BN * BN;
+    const int kend = p_last + 1;
+    const int ntiles = (kend - kbeg + BN - 1) / BN;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&kv_full[0], 1); mbar_init(&kv_full[1], 1);
+        mbar_init(&kv_empty[0], 1); mbar_init(&kv_empty[1], 1);
+        mbar_init(s_full, 1);
+        mbar_init(p_full, 128);
+        mbar_init(pv_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // K/V stages start as zeros so that rows no copy fills (absent pages) hold finite values
+    for (int i = threadIdx.x; i < 4 * KV_TILE_BYTES / 16; i += THREADS)
+        reinterpret_cast<uint4*>(smem + OFF_K)[i] = make_uint4(0, 0, 0, 0);
+    // Q tile: the softmax threads copy their rows into the swizzled operand layout
+    if (warp >= 2) {
+        const int r = (warp & 3) * 32 + lane;
+        unsigned char* qs = smem + OFF_Q;
+        if (r < nrows) {
+            const int tl = r / g, hg = r - tl * g;
+            const bf16* src = q + (size_t)(q0 + tok0 + tl) * ldq + (size_t)(kvh * g + hg) * D;
+#pragma unroll
+            for (int c = 0; c < D / 8; ++c) {
+                const uint4 v = *reinterpret_cast<const uint4*>(src + c * 8);
+                *reinterpret_cast<uint4*>(qs + (c >> 3) * (BM * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < D / 8; ++c)
+                *reinterpret_cast<uint4*>(qs + (c >> 3) * (BM * 128) + r * 128 + ((c & 7) << 4)) =
+                    make_uint4(0, 0, 0, 0);
+        }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- loader
+        if (lane == 0) {
+            const int boxes = BN / box_rows;
+            const bool pow2 = true;                       // the launcher only takes such page sizes
+            const int shift = __ffs(ps) - 1;
+            (void)pow2;
+            for (int j = 0; j < ntiles; ++j) {
+                const int st = j & 1;
+                if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1)) { atomicCAS(status, 0, 0x101); break; }
+                const int k0 = kbeg + j * BN;
+                int rows[8];
+                uint32_t bytes = 0;
+                for (int b = 0; b < boxes; ++b) {
+                    const int kp = k0 + b * box_rows;
+                    int page = -1;
+                    if (kp < kend) page = table[kp >> shift];
+                    rows[b] = page >= 0 ? (page * Hkv + kvh) * ps + (kp & (ps - 1)) : -1;
+                    if (page >= 0) bytes += (uint32_t)box_rows * 128u * PANELS * 2u;
+                }
+                if (bytes) mbar_expect_tx(&kv_full[st], bytes); else mbar_arrive(&kv_full[st]);
+                for (int b = 0; b < boxes; ++b) {
+                    if (rows[b] < 0) continue;
+#pragma unroll
+                    for (int p = 0; p < PANELS; ++p) {
+                        tma_load_2d(smem + OFF_K + st * KV_TILE_BYTES + p * KV_PANEL_BYTES + b * box_rows * 128,
+                                    &map_k, &kv_full[st], p * 64, rows[b]);
+                        tma_load_2d(smem + OFF_V + st * KV_TILE_BYTES + p * KV_PANEL_BYTES + b * box_rows * 128,
+                                    &map_v, &kv_full[st], p * 64, rows[b]);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                      ((uint32_t)(BM >> 4) << 24);
+            const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
+                                      ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            const uint32_t q_addr = smem_u32(smem + OFF_Q), p_addr = smem_u32(smem + OFF_P);
+            for (int j = 0; j < ntiles; ++j) {
+                const int st = j & 1;
+                if (!mbar_wait(&kv_full[st], (j >> 1) & 1)) { atomicCAS(status, 0, 0x201); break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t k_addr = smem_u32(smem + OFF_K + st * KV_TILE_BYTES);
+                const uint32_t v_addr = smem_u32(smem + OFF_V + st * KV_TILE_BYTES);
+#pragma unroll
+                for (int p = 0; p < PANELS; ++p)
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)          // 16 elements of D = 32 bytes per step
+                        umma_bf16(tmem + S_COL, umma_desc(q_addr + p * (BM * 128) + kk * 32, 1),
+                                  umma_desc(k_addr + p * KV_PANEL_BYTES + kk * 32, 1), idesc_qk,
+                                  (p > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(s_full);
+                if (!mbar_wait(p_full, j & 1)) { atomicCAS(status, 0, 0x202); break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)              // 16 keys per step: P 32 bytes, V 16 rows
+                    umma_bf16(tmem + O_COL, umma_desc(p_addr + kk * 32, 1),
+                              umma_desc(v_addr + kk * 16 * 128, KV_PANEL_BYTES >> 4), idesc_pv,
+                              (j > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&kv_empty[st]);
+                umma_commit(pv_done);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- softmax + epilogue
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const int pos = r < nrows ? pos_base + tok0 + r / g : -1;
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        unsigned char* prow = smem + OFF_P + r * 128;
+        for (int j = 0; j < ntiles && ok; ++j) {
+            if (!mbar_wait(s_full, j & 1)) { atomicCAS(status, 0, 0x301); ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t raw[2][32];
+            tmem_ld32(tmem + lane_base + S_COL, raw[0]);
+            tmem_ld32(tmem + lane_base + S_COL + 32, raw[1]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            const int k0 = kbeg + j * BN;
+            // visible keys of this row in the tile: [lo, hi)
+            int hi = min(BN, min(kend, pos + 1) - k0);
+            int lo = 0;
+            if (window > 0) lo = max(0, pos - window + 1 - k0);
+            float mt = -INFINITY;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int c = h * 32 + i;
+                    float x = __uint_as_float(raw[h][i]) * scale_log2;
+                    x = (c >= lo && c < hi) ? x : -INFINITY;
+                    raw[h][i] = __float_as_uint(x);
+                    mt = fmaxf(mt, x);
+                }
+            float alpha = 1.f;
+            if (mt > m_ref + RESCALE_THRESHOLD || (m_ref == -INFINITY && mt != -INFINITY)) {
+                alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - mt);
+                m_ref = mt;
+            }
+            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            float sum = 0.f;
+            unsigned packed[32];
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float p0 = exp2f(__uint_as_float(raw[h][i]) - m_use);
+                    const float p1 = exp2f(__uint_as_float(raw[h][i + 1]) - m_use);
+                    sum += p0 + p1;
+                    packed[h * 16 + i / 2] = pack2(p0, p1);
+                }
+            l = l * alpha + sum;
+            if (j > 0) {
+                // P.V of the previous tile must be done: it reads P and writes O
+                if (!mbar_wait(pv_done, (j - 1) & 1)) { atomicCAS(status, 0, 0x302); ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+                    for (int c0 = 0; c0 < D; c0 += 32) {
+                        uint32_t ov[32];
+                        tmem_ld32(tmem + lane_base + O_COL + c0, ov);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+                        tmem_st32(tmem + lane_base + O_COL + c0, ov);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+            }
+            // P row: 64 keys = 8 chunks of 16 bytes, swizzled like a TMA-written operand
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) =
+                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(p_full);
+        }
+        if (ok) {
+            if (!mbar_wait(pv_done, (ntiles - 1) & 1)) { atomicCAS(status, 0, 0x303); ok = false; }
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        pdl_launch_dependents();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const int tl = r / g, hg = r - tl * g;
+        bf16* dst = out + (size_t)(q0 + tok0 + tl) * ldo + (size_t)(kvh * g + hg) * D;
+#pragma unroll
+        for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t ov[32];
+            tmem_ld32(tmem + lane_base + O_COL + c0, ov);            // warp-wide: every lane takes part
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (ok && r < nrows) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    uint4 v;
+                    v.x = pack2(__uint_as_float(ov[i]) * inv, __uint_as_float(ov[i + 1]) * inv);
+                    v.y = pack2(__uint_as_float(ov[i + 2]) * inv, __uint_as_float(ov[i + 3]) * inv);
+                    v.z = pack2(__uint_as_float(ov[i + 4]) * inv, __uint_as_float(ov[i + 5]) * inv);
+                    v.w = pack2(__uint_as_float(ov[i + 6]) * inv, __uint_as_float(ov[i + 7]) * inv);
+                    *reinterpret_cast<uint4*>(dst + c0 + i) = v;
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS)
+                     : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+// the cache of one layer as a matrix [pages * kv heads * page size, D]; boxes of box_rows x 64
+int make_cache_map(CUtensorMap* map, const void* ptr, long long rows, int box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr) return SLB_ERR_BAD_ARG;
+    const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+                          elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : SLB_ERR_BAD_ARG;
+}
+
+}  // namespace
+
+extern "C" {
+
+// 1 if the (head size, page size, group size) is taken by the tcgen05 prefill kernel
+int slb_prefill_attention_tc_supported(int ps, int group) {
+    return ps >= 8 && (ps & (ps - 1)) == 0 && group >= 1 && group <= BM;
+}
+// query rows per tile for a group of g query heads (whole tokens per tile)
+int slb_prefill_attention_tc_tile_rows(int group) { return group >= 1 && group <= BM ? (BM / group) * group : 0; }
+
+// num_pages: pages in k_cache / v_cache ([num_pages][Hkv][ps][D]).
+int slb_prefill_attention_tc_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, bf16* out, int ldo,
+                                  const int* block_table, int max_pages, const int* cu_q,
+                                  const int* ctx_len, const int* tile_seq, const int* tile_row0,
+                                  int num_tiles, int H, int Hkv, int ps, int num_pages, float scale,
+                                  int window, cudaStream_t st) {
+    if (num_tiles <= 0) return 0;
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || max_pages <= 0 || num_pages <= 0 || !(scale > 0.f))
+        return SLB_ERR_BAD_ARG;
+    if (!slb_prefill_attention_tc_supported(ps, H / Hkv)) return SLB_ERR_BAD_ARG;
+    if (ldq % 8 || ldo % 8 || ((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)out) % 16)
+        return SLB_ERR_BAD_ARG;
+    if (Hkv > 65535) return SLB_ERR_TOO_LARGE;
+    const int box_rows = ps < BN ? ps : BN;
+    CUtensorMap map_k, map_v;
+    const long long rows = (long long)num_pages * Hkv * ps;
+    int rc = make_cache_map(&map_k, kc, rows, box_rows);
+    if (rc != 0) return rc;
+    rc = make_cache_map(&map_v, vc, rows, box_rows);
+    if (rc != 0) return rc;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_ATTN_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    int* status = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&status, tc_attn_status);
+    if (e != cudaSuccess) return (int)e;
+    return slb_launch(prefill_attention_tc_kernel, dim3(num_tiles, Hkv), dim3(THREADS), TC_ATTN_SMEM, st, q, ldq,
+                      map_k, map_v, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq, tile_row0, H, Hkv,
+                      ps, box_rows, scale * 1.4426950408889634f, window, status);
+}
+
+int slb_prefill_attention_tc_status(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, tc_attn_status, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(tc_attn_status, &zero, sizeof(int));
+    }
+    return v;
+}
+}
+
+#else   // head sizes the tcgen05 kernel does not take
+
+extern "C" {
+int slb_prefill_attention_tc_supported(int, int) { return 0; }
+int slb_prefill_attention_tc_tile_rows(int) { return 0; }
+int slb_prefill_attention_tc_status(int) { return 0; }
+}
+
+#endif

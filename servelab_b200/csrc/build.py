@@ -136,7 +136,8 @@ def ensure_library(name: str = "slb_core", sources: Optional[List[str]] = None,
 
 def attention_library(head_dim: int) -> str:
     """The tensor-core attention kernels specialised for one head size."""
-    return ensure_library(f"slb_attn_d{head_dim}", ["attention_mma.cu"], {"SLB_HEAD_DIM": head_dim})
+    return ensure_library(f"slb_attn_d{head_dim}", ["attention_mma.cu", "attention_tc.cu"],
+                          {"SLB_HEAD_DIM": head_dim})
 
 
 def build_all(head_dims=(16, 32, 64, 128)) -> List[str]:

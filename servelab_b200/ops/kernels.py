@@ -192,15 +192,34 @@ def attention_status(head_dim: int, reset: bool = False) -> int:
     return L.attention(head_dim).slb_attention_status(1 if reset else 0)
 
 
+def prefill_attention_tc_status(head_dim: int, reset: bool = False) -> int:
+    """0 unless a bounded wait inside the tcgen05 prefill attention gave up."""
+    return L.attention(head_dim).slb_prefill_attention_tc_status(1 if reset else 0)
+
+
 def has_fast_attention(head_dim: int) -> bool:
     """The tensor-core kernels exist for head sizes that are multiples of 16 up to
     256; the library for a head size is built when it is first asked for."""
     return head_dim % 16 == 0 and 16 <= head_dim <= 256
 
 
+use_tc_prefill = True       # tcgen05 prefill attention where it applies (head size 64/128)
+
+
 def prefill_attention(ctx, q, k_cache, v_cache, out, block_table, num_heads, num_kv_heads,
                       head_dim, page_size, scale, window) -> None:
     lib = L.attention(head_dim)
+    group = num_heads // num_kv_heads
+    if (use_tc_prefill and hasattr(lib, "slb_prefill_attention_tc_bf16")
+            and lib.slb_prefill_attention_tc_supported(page_size, group)):
+        tile_seq, tile_row0, n = ctx.attention_tiles(group, lib.slb_prefill_attention_tc_tile_rows(group))
+        L.check(lib.slb_prefill_attention_tc_bf16(
+            q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+            out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.cu_q.data_ptr(),
+            ctx.ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), n, num_heads,
+            num_kv_heads, page_size, k_cache.shape[0], float(scale), int(window), _stream()),
+            "prefill_attention_tc")
+        return
     tile_seq, tile_row0, n = ctx.attention_tiles(num_heads // num_kv_heads,
                                                  lib.slb_prefill_attention_tile_rows())
     L.check(lib.slb_prefill_attention_bf16(

@@ -105,6 +105,9 @@ _ATTN_SIGNATURES = {
     "slb_decode_attention_max_splits": [],
     "slb_attention_head_dim": [],
     "slb_attention_status": [I],
+    "slb_prefill_attention_tc_supported": [I, I],
+    "slb_prefill_attention_tc_tile_rows": [I],
+    "slb_prefill_attention_tc_status": [I],
 }
 
 
@@ -118,6 +121,10 @@ def attention(head_dim: int) -> ctypes.CDLL:
             raise KernelsUnavailable(
                 f"the attention kernels for head size {head_dim} are not available: {e}") from e
         _declare(lib, _ATTN_SIGNATURES, True)
+        if hasattr(lib, "slb_prefill_attention_tc_bf16"):
+            lib.slb_prefill_attention_tc_bf16.argtypes = [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I,
+                                                          F, I, P]
+            lib.slb_prefill_attention_tc_bf16.restype = I
         lib.slb_decode_attention_scratch_bytes.argtypes = [I, I, I]
         lib.slb_decode_attention_scratch_bytes.restype = ctypes.c_longlong
         if lib.slb_attention_head_dim() != head_dim:

@@ -356,7 +356,8 @@ def _ctx_for(case):
 
 
 @pytest.mark.parametrize("H,Hkv,D,ps", [(6, 2, 16, 16), (7, 1, 64, 8), (4, 2, 48, 4),
-                                        (28, 4, 128, 16), (2, 1, 256, 32), (20, 1, 32, 16)])
+                                        (28, 4, 128, 16), (2, 1, 256, 32), (20, 1, 32, 16),
+                                        (3, 3, 64, 64), (10, 2, 128, 128), (8, 1, 128, 32)])
 @pytest.mark.parametrize("window", [0, 40])
 def test_prefill_attention_tensor_cores(H, Hkv, D, ps, window):
     case = PagedCase([37, 150, 1, 263, 34, 300], [37, 19, 1, 1, 2, 300], H, Hkv, D, ps,
@@ -364,11 +365,20 @@ def test_prefill_attention_tensor_cores(H, Hkv, D, ps, window):
     case.scatter()
     ctx, q, table = _ctx_for(case)
     out = torch.empty_like(q)
-    K().prefill_attention(ctx, q, case.kc, case.vc, out, table, H, Hkv, D, ps, 1 / math.sqrt(D), window)
+    from servelab_b200.ops import kernels as kernels_module
     want = case.reference(window=window or None)
-    assert (out.float().cpu() - want).abs().max() <= TOL["bfloat16"]
     plain = run_generic(case, window=window)
-    assert (out.float().cpu() - plain).abs().max() <= TOL["bfloat16"]
+    # the tcgen05 kernel (head sizes 64 and 128) and the mma.sync kernel (every head size)
+    for use_tc in (True, False):
+        kernels_module.use_tc_prefill = use_tc
+        try:
+            out = torch.full_like(q, 3.0)
+            K().prefill_attention(ctx, q, case.kc, case.vc, out, table, H, Hkv, D, ps, 1 / math.sqrt(D), window)
+            assert K().prefill_attention_tc_status(D, reset=True) == 0, "a bounded wait gave up"
+            assert (out.float().cpu() - want).abs().max() <= TOL["bfloat16"], f"tcgen05={use_tc}"
+            assert (out.float().cpu() - plain).abs().max() <= TOL["bfloat16"], f"tcgen05={use_tc}"
+        finally:
+            kernels_module.use_tc_prefill = True
 
 
 @pytest.mark.parametrize("H,Hkv,D,ps", [(6, 2, 16, 16), (7, 1, 64, 8), (4, 2, 48, 4),
