@@ -12,7 +12,10 @@
 //                   O += P.V    (tcgen05.mma M=128 N=D,   K=16 x 4)     -> kv_empty, pv_done
 //   softmax warps   thread r owns row r: tcgen05.ld its 64 scores, mask, running max and
 //                   sum in float32 (no shuffles: a row lives in one thread), P as
-//                   bfloat16 into shared memory in the swizzled operand layout -> p_full
+//                   bfloat16 back into tensor memory (tcgen05.st, over the scores it
+//                   came from), where the second MMA reads its A operand  -> p_full
+// The scores are double buffered: Q.K^T of the next tile runs while this tile's softmax
+// does, and P of a tile never waits for the P.V of the one before.
 //
 // The running maximum is only raised when the tile's maximum exceeds it by more than
 // 2^8 (scores are in the base-2 domain); otherwise the stale maximum keeps being used
@@ -37,17 +40,15 @@ constexpr int D = SLB_HEAD_DIM;
 constexpr int PANELS = D / 64;                 // 64-element (128-byte) column panels
 constexpr int BM = 128, BN = 64;
 constexpr int THREADS = 192;                   // warp 0 loader, warp 1 MMA, warps 2..5 softmax
-constexpr int TMEM_COLS = 256;                 // S at columns 0..63, O at 64..64+D-1
-constexpr int S_COL = 0, O_COL = 64;
+constexpr int TMEM_COLS = 256;                 // two S buffers at columns 0..127, O at 128..128+D-1
+constexpr int S_COL = 0, O_COL = 128;          // S buffer b sits at S_COL + 64 * b
 constexpr int Q_BYTES = PANELS * BM * 128;
 constexpr int KV_PANEL_BYTES = BN * 128;
 constexpr int KV_TILE_BYTES = PANELS * KV_PANEL_BYTES;
-constexpr int P_BYTES = BM * 128;
 constexpr int OFF_Q = 0;
 constexpr int OFF_K = OFF_Q + Q_BYTES;
 constexpr int OFF_V = OFF_K + 2 * KV_TILE_BYTES;
-constexpr int OFF_P = OFF_V + 2 * KV_TILE_BYTES;
-constexpr int OFF_BAR = OFF_P + P_BYTES;
+constexpr int OFF_BAR = OFF_V + 2 * KV_TILE_BYTES;
 constexpr size_t TC_ATTN_SMEM = OFF_BAR + 128;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr float RESCALE_THRESHOLD = 8.f;       // log2 of the largest probability tolerated
@@ -106,6 +107,16 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
         : "memory");
 }
+// same with the A operand in tensor memory (lane = row, 32-bit columns of two bfloat16)
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                  ::"r"(smem_u32(bar)) : "memory");
@@ -146,8 +157,8 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);    // [2]
     uint64_t* kv_empty = kv_full + 2;                                   // [2]
-    uint64_t* s_full = kv_empty + 2;
-    uint64_t* p_full = s_full + 1;
+    uint64_t* s_full = kv_empty + 2;                                    // [2]
+    uint64_t* p_full = s_full + 2;
     uint64_t* pv_done = p_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
 
@@ -182,7 +193,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     if (threadIdx.x == 0) {
         mbar_init(&kv_full[0], 1); mbar_init(&kv_full[1], 1);
         mbar_init(&kv_empty[0], 1); mbar_init(&kv_empty[1], 1);
-        mbar_init(s_full, 1);
+        mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
         mbar_init(p_full, 128);
         mbar_init(pv_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -260,30 +271,41 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
                                       ((uint32_t)(BM >> 4) << 24);
             const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                       ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            const uint32_t q_addr = smem_u32(smem + OFF_Q), p_addr = smem_u32(smem + OFF_P);
-            for (int j = 0; j < ntiles; ++j) {
-                const int st = j & 1;
-                if (!mbar_wait(&kv_full[st], (j >> 1) & 1)) { atomicCAS(status, 0, 0x201); break; }
+            const uint32_t q_addr = smem_u32(smem + OFF_Q);
+            // S = Q.K^T of tile t into score buffer t & 1 (which held the scores and then P of
+            // tile t - 2; its P.V has been issued before)
+            auto issue_qk = [&](int t) -> bool {
+                const int st = t & 1;
+                if (!mbar_wait(&kv_full[st], (t >> 1) & 1)) { atomicCAS(status, 0, 0x201); return false; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t k_addr = smem_u32(smem + OFF_K + st * KV_TILE_BYTES);
-                const uint32_t v_addr = smem_u32(smem + OFF_V + st * KV_TILE_BYTES);
 #pragma unroll
                 for (int p = 0; p < PANELS; ++p)
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)          // 16 elements of D = 32 bytes per step
-                        umma_bf16(tmem + S_COL, umma_desc(q_addr + p * (BM * 128) + kk * 32, 1),
+                        umma_bf16(tmem + S_COL + 64 * st, umma_desc(q_addr + p * (BM * 128) + kk * 32, 1),
                                   umma_desc(k_addr + p * KV_PANEL_BYTES + kk * 32, 1), idesc_qk,
                                   (p > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(s_full);
+                umma_commit(&s_full[st]);
+                return true;
+            };
+            bool ok = issue_qk(0);
+            if (ok && ntiles > 1) ok = issue_qk(1);
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int st = j & 1;
                 if (!mbar_wait(p_full, j & 1)) { atomicCAS(status, 0, 0x202); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t v_addr = smem_u32(smem + OFF_V + st * KV_TILE_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk)              // 16 keys per step: P 32 bytes, V 16 rows
-                    umma_bf16(tmem + O_COL, umma_desc(p_addr + kk * 32, 1),
-                              umma_desc(v_addr + kk * 16 * 128, KV_PANEL_BYTES >> 4), idesc_pv,
-                              (j > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < 4; ++kk)              // 16 keys per step: P 8 columns, V 16 rows
+                    umma_bf16_ts(tmem + O_COL, tmem + S_COL + 64 * st + kk * 8,
+                                 umma_desc(v_addr + kk * 16 * 128, KV_PANEL_BYTES >> 4), idesc_pv,
+                                 (j > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(&kv_empty[st]);
                 umma_commit(pv_done);
+                // the scores of tile j + 2 go where P of tile j was: issued after P.V of tile j
+                // (the tensor core executes in issue order), while the softmax of j + 1 runs
+                if (j + 2 < ntiles) ok = issue_qk(j + 2);
             }
         }
     } else {
@@ -294,71 +316,72 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
         const int pos = r < nrows ? pos_base + tok0 + r / g : -1;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
-        unsigned char* prow = smem + OFF_P + r * 128;
         for (int j = 0; j < ntiles && ok; ++j) {
-            if (!mbar_wait(s_full, j & 1)) { atomicCAS(status, 0, 0x301); ok = false; break; }
+            if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicCAS(status, 0, 0x301); ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t raw[2][32];
-            tmem_ld32(tmem + lane_base + S_COL, raw[0]);
-            tmem_ld32(tmem + lane_base + S_COL + 32, raw[1]);
+            tmem_ld32(tmem + lane_base + S_COL + 64 * (j & 1), raw[0]);
+            tmem_ld32(tmem + lane_base + S_COL + 64 * (j & 1) + 32, raw[1]);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             const int k0 = kbeg + j * BN;
-            // visible keys of this row in the tile: [lo, hi)
-            int hi = min(BN, min(kend, pos + 1) - k0);
-            int lo = 0;
-            if (window > 0) lo = max(0, pos - window + 1 - k0);
-            float mt = -INFINITY;
+            // raw scores stay unscaled; masked ones become -inf.  A tile that every row of
+            // the block sees completely needs no mask (rows of padding compute garbage that
+            // is never stored).
+            const bool open = k0 + BN - 1 <= p_first && (window <= 0 || p_last - k0 < window);
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one
+            if (open) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+                for (int h = 0; h < 2; ++h)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int c = h * 32 + i;
-                    float x = __uint_as_float(raw[h][i]) * scale_log2;
-                    x = (c >= lo && c < hi) ? x : -INFINITY;
-                    raw[h][i] = __float_as_uint(x);
-                    mt = fmaxf(mt, x);
-                }
+                    for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(raw[h][i]));
+            } else {
+                const int hi = min(BN, min(kend, pos + 1) - k0);      // visible keys: [lo, hi)
+                const int lo = window > 0 ? max(0, pos - window + 1 - k0) : 0;
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int c = h * 32 + i;
+                        if (!(c >= lo && c < hi)) raw[h][i] = __float_as_uint(-INFINITY);
+                        mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(raw[h][i]));
+                    }
+            }
+            const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;   // scale > 0
             float alpha = 1.f;
             if (mt > m_ref + RESCALE_THRESHOLD || (m_ref == -INFINITY && mt != -INFINITY)) {
                 alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - mt);
                 m_ref = mt;
             }
             const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-            float sum = 0.f;
-            unsigned packed[32];
+            float sm[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t packed[32];
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float p0 = exp2f(__uint_as_float(raw[h][i]) - m_use);
-                    const float p1 = exp2f(__uint_as_float(raw[h][i + 1]) - m_use);
-                    sum += p0 + p1;
+                    const float p0 = exp2f(fmaf(__uint_as_float(raw[h][i]), scale_log2, -m_use));
+                    const float p1 = exp2f(fmaf(__uint_as_float(raw[h][i + 1]), scale_log2, -m_use));
+                    sm[(i >> 1) & 3] += p0 + p1;
                     packed[h * 16 + i / 2] = pack2(p0, p1);
                 }
-            l = l * alpha + sum;
-            if (j > 0) {
-                // P.V of the previous tile must be done: it reads P and writes O
+            l = l * alpha + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                // the accumulator is rescaled (rarely): P.V of the previous tile must be done
                 if (!mbar_wait(pv_done, (j - 1) & 1)) { atomicCAS(status, 0, 0x302); ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-                    for (int c0 = 0; c0 < D; c0 += 32) {
-                        uint32_t ov[32];
-                        tmem_ld32(tmem + lane_base + O_COL + c0, ov);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t ov[32];
+                    tmem_ld32(tmem + lane_base + O_COL + c0, ov);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-                        tmem_st32(tmem + lane_base + O_COL + c0, ov);
-                    }
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+                    tmem_st32(tmem + lane_base + O_COL + c0, ov);
                 }
             }
-            // P row: 64 keys = 8 chunks of 16 bytes, swizzled like a TMA-written operand
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) =
-                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // P: 64 bfloat16 = 32 columns, written over the first half of this tile's scores
+            tmem_st32(tmem + lane_base + S_COL + 64 * (j & 1), packed);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(p_full);
         }
