@@ -107,6 +107,14 @@ def prefill_flops(cfg, layers, T):
     return lin + attn + 2 * cfg["vocab_size"] * cfg["hidden_size"]
 
 
+_T0 = time.perf_counter()
+
+
+def note(msg: str) -> None:
+    """Progress on stderr (the JSON line on stdout stays alone)."""
+    print(f"[bench +{time.perf_counter() - _T0:6.1f}s] {msg}", file=sys.stderr, flush=True)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -158,6 +166,8 @@ def main(argv=None) -> int:
             K.tc_max_stages = int(value)
         elif name == "decode_ctas_per_sm":
             K.decode_ctas_per_sm = int(value)
+        elif name in ("decode_ws_stages", "decode_ws_force_splits"):
+            setattr(K, name, int(value))
         elif name == "pdl":
             from servelab_b200.ops import library as kernel_library
             kernel_library.set_pdl(bool(int(value)))
@@ -175,6 +185,7 @@ def main(argv=None) -> int:
     max_batch = 64 if not args.skip_points else max(args.batch, 1)
     max_batch = max(max_batch, args.batch)
     pages = max_batch * (CONTEXT // PAGE) + 64
+    note("building the engine (random weights on the device, cache pool)")
     source = RandomSource(declare_tensors(config.to_model_spec()), seed=0, device="cuda:0",
                           dtype=torch.bfloat16)
     engine = LLMEngine(config, CacheConfig(block_size=PAGE, num_blocks=pages),
@@ -182,6 +193,7 @@ def main(argv=None) -> int:
                        dtype="bfloat16", weights=source, cuda_graphs=not args.no_graphs,
                        max_model_len=CONTEXT)
     runner = engine.runner
+    note("engine ready")
     gen = torch.Generator().manual_seed(1)
     V = cfg["vocab_size"]
 
@@ -198,6 +210,7 @@ def main(argv=None) -> int:
         while any(not s.is_decoding() for s in engine.scheduler.running) or engine.scheduler.waiting:
             engine.step()
         assert len(engine.scheduler.running) == batch
+        note(f"batch {batch}: prompts prefilled, timing {steps} decode steps end to end and on the device")
         # (b) end to end: schedule, pack, H2D, graph replay, sample, D2H, bookkeeping
         for _ in range(warmup):
             engine.step()
@@ -273,6 +286,7 @@ def main(argv=None) -> int:
         print(json.dumps({"only": "prefill", "layers": layers, "prefill": run_prefill()}))
         return 0
     clocks = ClockSampler()
+    note(f"decode at batch {args.batch}")
     main_run = run_decode(args.batch, args.steps, args.warmup, clocks)
     wbytes, _ = weight_bytes_per_step(cfg, layers)
     step_bytes = wbytes + main_run["ctx_tokens"] * kv_bytes_per_token(cfg, layers)
@@ -301,6 +315,7 @@ def main(argv=None) -> int:
         "clocks": main_run["clocks"],
     }
     if not args.skip_points:
+        note("prefill of one prompt")
         result["prefill"] = run_prefill()
         points = {}
         for b in (1, 64):
@@ -310,6 +325,7 @@ def main(argv=None) -> int:
             points[f"decode_b{b}_hbm_frac"] = round(sb / (r["dev_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
             points[f"decode_b{b}_e2e"] = round(b / (r["e2e_ms"] * 1e-3), 1)
         result["points"] = points
+    note("done")
     print(json.dumps(result))
     return 0
 

@@ -31,6 +31,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "tma_util.cuh"
 
 #if (SLB_HEAD_DIM == 64 || SLB_HEAD_DIM == 128)
 
@@ -55,6 +56,8 @@ constexpr float RESCALE_THRESHOLD = 8.f;       // log2 of the largest probabilit
 
 __device__ int tc_attn_status = 0;
 
+using slb_tma::tma_load_2d;
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -78,13 +81,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         if (done) return true;
     }
     return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0,
-                                            int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-        : "memory");
 }
 // Shared-memory matrix descriptor, 128-byte swizzle, rows of 128 bytes in groups of 8
 // (1024 bytes).  lbo16: leading byte offset >> 4 (distance of 64-element panels for an
@@ -420,33 +416,9 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
 // the cache of one layer as a matrix [pages * kv heads * page size, D]; boxes of box_rows x 64
 int make_cache_map(CUtensorMap* map, const void* ptr, long long rows, int box_rows) {
-    EncodeTiledFn fn = encode_tiled();
-    if (fn == nullptr) return SLB_ERR_BAD_ARG;
-    const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
-                          elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : SLB_ERR_BAD_ARG;
+    return slb_tma::make_rows_map(map, ptr, D, rows, box_rows);
 }
 
 }  // namespace

@@ -33,7 +33,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--compiler-options", "-fPIC",
 
 CORE_SOURCES = ["elementwise.cu", "rope_cache.cu", "attention_generic.cu", "gemm_simt.cu",
                 "sampling.cu", "gemm_skinny.cu", "gemm_tcgen05.cu"]
-HEADERS = ["common.cuh", "no_alloc.h"]
+HEADERS = ["common.cuh", "no_alloc.h", "mma_util.cuh", "tma_util.cuh"]
 
 _lock = threading.Lock()
 _done: Dict[str, str] = {}
@@ -136,7 +136,7 @@ def ensure_library(name: str = "slb_core", sources: Optional[List[str]] = None,
 
 def attention_library(head_dim: int) -> str:
     """The tensor-core attention kernels specialised for one head size."""
-    return ensure_library(f"slb_attn_d{head_dim}", ["attention_mma.cu", "attention_tc.cu"],
+    return ensure_library(f"slb_attn_d{head_dim}", ["attention_mma.cu", "attention_tc.cu", "attention_decode.cu"],
                           {"SLB_HEAD_DIM": head_dim})
 
 

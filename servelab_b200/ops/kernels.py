@@ -7,7 +7,7 @@ The dtype of the activations selects the float32 or the bfloat16 instance.
 
 from __future__ import annotations
 
-from typing import Optional
+from typing import Dict, Optional
 
 import torch
 
@@ -239,9 +239,11 @@ def decode_splits(num_seqs: int, num_kv_heads: int, group: int, longest_context:
     return max(1, min(want, max_splits, -(-longest_context // 64)))
 
 
-def decode_attention(ctx, q, k_cache, v_cache, out, block_table, num_heads, num_kv_heads,
-                     head_dim, page_size, scale, window) -> None:
-    """Attention for a step of single tokens (every q_len == 1)."""
+def decode_attention_split(ctx, q, k_cache, v_cache, out, block_table, num_heads, num_kv_heads,
+                           head_dim, page_size, scale, window) -> None:
+    """Attention for a step of single tokens, earlier form: four warps share every
+    64-key tile behind a block-wide barrier and a second kernel combines the splits.
+    Kept as the twin of ``decode_attention``."""
     lib = L.attention(head_dim)
     S = ctx.num_seqs
     splits = decode_splits(S, num_kv_heads, num_heads // num_kv_heads, ctx.split_hint_len,
@@ -257,6 +259,89 @@ def decode_attention(ctx, q, k_cache, v_cache, out, block_table, num_heads, num_
         _stream()), "decode_attention")
     global launch_count
     launch_count += 1 if splits > 1 else 0          # the combine kernel
+
+
+decode_ws_stages = 3           # depth of the kernel's shared-memory ring (2..4)
+decode_ws_force_splits = 0     # measurements: this many splits instead of the choice below
+# Cost model behind the choice of splits, in microseconds, fitted to measurements on a
+# B200 at head size 128: a block takes `tile` per 64-key tile; splitting costs
+# `split_fixed` once (partial results, the arrival counter, the last block's combine)
+# plus `split_batch` per eight splits the last block reads.
+decode_ws_cost = {"tile": 0.45, "split_fixed": 3.0, "split_batch": 1.0}
+
+_DECODE_COUNTERS = 1 << 16     # arrival counters held per device (256 KiB)
+_decode_counters: Dict[int, torch.Tensor] = {}
+
+
+def _decode_counter_buffer(device: torch.device) -> torch.Tensor:
+    """Zeroed once; every launch of the decode kernel leaves the counters zero.  One
+    fixed buffer per device, so addresses captured in CUDA graphs stay valid."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _decode_counters.get(index)
+    if buf is None:
+        buf = _decode_counters[index] = torch.zeros(_DECODE_COUNTERS, dtype=torch.int32,
+                                                    device=device)
+    return buf
+
+
+def decode_ws_splits(num_seqs: int, num_kv_heads: int, group: int, longest_context: int,
+                     max_splits: int, tile_keys: int) -> int:
+    """How many ways the keys of each request are split: the count that minimises
+    rounds of blocks x tiles per block x time per tile + the cost of splitting."""
+    head_rows = 8 if group <= 8 else 16
+    pairs = num_seqs * num_kv_heads * (-(-group // head_rows))
+    tiles = max(1, -(-longest_context // tile_keys))
+    slots = 2 * _num_sms()                      # two blocks of three stages fit on an SM
+    cost = decode_ws_cost
+    best, best_time = 1, None
+    for want in range(1, min(max_splits, tiles) + 1):
+        per = -(-tiles // want)
+        splits = -(-tiles // per)               # no split of the longest context is empty
+        if splits != want:
+            continue
+        rounds = -(-pairs * splits // slots)
+        t = rounds * per * cost["tile"]
+        if splits > 1:
+            t += cost["split_fixed"] + cost["split_batch"] * (-(-splits // 8))
+        if best_time is None or t < best_time - 1e-9:
+            best, best_time = splits, t
+    return best
+
+
+def decode_attention(ctx, q, k_cache, v_cache, out, block_table, num_heads, num_kv_heads,
+                     head_dim, page_size, scale, window) -> None:
+    """Attention for a step of single tokens (every q_len == 1): one launch; the
+    splits of a request are combined by the block that finishes last.  Head sizes
+    that are no multiple of 64 and page sizes that are no power of two from 8 go to
+    ``decode_attention_split``."""
+    lib = L.attention(head_dim)
+    if not lib.slb_decode_attention_ws_supported(page_size):
+        decode_attention_split(ctx, q, k_cache, v_cache, out, block_table, num_heads, num_kv_heads,
+                               head_dim, page_size, scale, window)
+        return
+    S = ctx.num_seqs
+    group = num_heads // num_kv_heads
+    splits = decode_ws_force_splits or decode_ws_splits(
+        S, num_kv_heads, group, ctx.split_hint_len, lib.slb_decode_attention_ws_max_splits(),
+        lib.slb_decode_attention_ws_tile_keys())
+    scratch = counters = None
+    if splits > 1:
+        if lib.slb_decode_attention_ws_counters(S, num_heads, num_kv_heads) > _DECODE_COUNTERS:
+            splits = 1
+        else:
+            nbytes = lib.slb_decode_attention_ws_scratch_bytes(S, num_heads, splits)
+            scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=q.device)
+            counters = _decode_counter_buffer(q.device)
+    L.check(lib.slb_decode_attention_ws_bf16(
+        q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+        out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.ctx_len.data_ptr(),
+        _p(scratch), _p(counters), S, num_heads, num_kv_heads, page_size, k_cache.shape[0],
+        float(scale), int(window), splits, int(decode_ws_stages), _stream()), "decode_attention")
+
+
+def decode_attention_status(head_dim: int, reset: bool = False) -> int:
+    """0 unless a bounded wait inside the decode attention kernel gave up."""
+    return L.attention(head_dim).slb_decode_attention_ws_status(1 if reset else 0)
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,

@@ -108,6 +108,11 @@ _ATTN_SIGNATURES = {
     "slb_prefill_attention_tc_supported": [I, I],
     "slb_prefill_attention_tc_tile_rows": [I],
     "slb_prefill_attention_tc_status": [I],
+    "slb_decode_attention_ws_bf16": [P, I, P, P, P, I, P, I, P, P, P, I, I, I, I, I, F, I, I, I, P],
+    "slb_decode_attention_ws_supported": [I],
+    "slb_decode_attention_ws_status": [I],
+    "slb_decode_attention_ws_max_splits": [],
+    "slb_decode_attention_ws_tile_keys": [],
 }
 
 
@@ -127,6 +132,10 @@ def attention(head_dim: int) -> ctypes.CDLL:
             lib.slb_prefill_attention_tc_bf16.restype = I
         lib.slb_decode_attention_scratch_bytes.argtypes = [I, I, I]
         lib.slb_decode_attention_scratch_bytes.restype = ctypes.c_longlong
+        lib.slb_decode_attention_ws_scratch_bytes.argtypes = [I, I, I]
+        lib.slb_decode_attention_ws_scratch_bytes.restype = ctypes.c_longlong
+        lib.slb_decode_attention_ws_counters.argtypes = [I, I, I]
+        lib.slb_decode_attention_ws_counters.restype = ctypes.c_longlong
         if lib.slb_attention_head_dim() != head_dim:
             raise KernelsUnavailable(f"attention library built for head size "
                                      f"{lib.slb_attention_head_dim()}, wanted {head_dim}")

@@ -410,6 +410,53 @@ def test_decode_attention_tensor_cores(H, Hkv, D, ps, window, splits):
     assert (out2.float().cpu() - want).abs().max() <= TOL["bfloat16"]
 
 
+@pytest.mark.parametrize("H,Hkv,D,ps", [(7, 1, 64, 8), (28, 4, 128, 16), (2, 1, 256, 32),
+                                        (20, 1, 64, 16), (16, 1, 192, 64), (9, 1, 128, 128),
+                                        (24, 3, 64, 256), (48, 2, 128, 16),
+                                        (6, 2, 16, 16), (4, 2, 48, 4), (16, 1, 80, 5)])
+@pytest.mark.parametrize("window", [0, 70])
+@pytest.mark.parametrize("splits,stages", [(1, 3), (3, 2), (32, 4), (5, 3)])
+def test_decode_attention_one_launch(H, Hkv, D, ps, window, splits, stages):
+    """The producer/consumer decode kernel whose last block combines the splits:
+    every group size (8 and 16 head rows a block, several head tiles), pages smaller
+    and larger than a key tile, ring depths, more splits than tiles; twice in a row,
+    so the arrival counters came back to 0.  Sizes it refuses reach the earlier
+    kernel through the wrapper."""
+    from servelab_b200.ops import library as L
+    ctxs = [1, 63, 64, 65, 700, 2049, 17]
+    case = PagedCase(ctxs, [1] * len(ctxs), H, Hkv, D, ps, torch.bfloat16, seed=D + splits)
+    case.scatter()
+    ctx, q, table = _ctx_for(case)
+    lib = L.attention(D)
+    if not lib.slb_decode_attention_ws_supported(ps):
+        assert D % 64 or ps < 8 or ps & (ps - 1)
+        out = torch.empty_like(q)
+        K().decode_attention(ctx, q, case.kc, case.vc, out, table, H, Hkv, D, ps, 1 / math.sqrt(D), window)
+        assert (out.float().cpu() - case.reference(window=window or None)).abs().max() <= TOL["bfloat16"]
+        return
+    S = len(ctxs)
+    want = case.reference(window=window or None)
+    counters = torch.zeros(int(lib.slb_decode_attention_ws_counters(S, H, Hkv)), dtype=torch.int32,
+                           device=DEV)
+    for _ in range(2):
+        out = torch.full_like(q, 7.0)
+        scratch = torch.full((max(1, lib.slb_decode_attention_ws_scratch_bytes(S, H, splits) // 4),),
+                             float("nan"), device=DEV)
+        L.check(lib.slb_decode_attention_ws_bf16(
+            q.data_ptr(), q.stride(0), case.kc.data_ptr(), case.vc.data_ptr(), out.data_ptr(),
+            out.stride(0), table.data_ptr(), table.shape[1], ctx.ctx_len.data_ptr(),
+            scratch.data_ptr(), counters.data_ptr(), S, H, Hkv, ps, case.kc.shape[0],
+            1 / math.sqrt(D), window, splits, stages, torch.cuda.current_stream().cuda_stream), "decode")
+        assert K().decode_attention_status(D, reset=True) == 0, "a bounded wait in the kernel gave up"
+        assert (out.float().cpu() - want).abs().max() <= TOL["bfloat16"]
+        assert int(counters.abs().sum()) == 0
+    # the dispatching wrapper (its own choice of splits) and the earlier two-kernel form
+    for fn in (K().decode_attention, K().decode_attention_split):
+        out2 = torch.empty_like(q)
+        fn(ctx, q, case.kc, case.vc, out2, table, H, Hkv, D, ps, 1 / math.sqrt(D), window)
+        assert (out2.float().cpu() - want).abs().max() <= TOL["bfloat16"]
+
+
 @pytest.mark.parametrize("needle", [0, 63, 64, 1023, 1024, 1500])
 def test_fast_attention_finds_one_far_key(needle):
     H, Hkv, D, ps = 14, 2, 128, 16
