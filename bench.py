@@ -168,6 +168,8 @@ def main(argv=None) -> int:
             K.decode_ctas_per_sm = int(value)
         elif name in ("decode_ws_stages", "decode_ws_force_splits"):
             setattr(K, name, int(value))
+        elif name == "use_tc_prefill":
+            K.use_tc_prefill = bool(int(value))
         elif name == "pdl":
             from servelab_b200.ops import library as kernel_library
             kernel_library.set_pdl(bool(int(value)))
@@ -282,8 +284,19 @@ def main(argv=None) -> int:
                 "ms": round(ms, 3),
                 "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
 
+    def kernel_status():
+        """Status words of the kernels with bounded waits (0 = no wait gave up)."""
+        D = cfg["head_dim"]
+        status = {"gemm_tc": K.gemm_tc_status(), "attention": K.attention_status(D),
+                  "prefill_attention_tc": K.prefill_attention_tc_status(D),
+                  "decode_attention": K.decode_attention_status(D)}
+        if status["prefill_attention_tc"]:
+            note(f"tcgen05 prefill attention gave up a wait: {K.prefill_attention_tc_where(D)}")
+        return status
+
     if args.only == "prefill":
-        print(json.dumps({"only": "prefill", "layers": layers, "prefill": run_prefill()}))
+        print(json.dumps({"only": "prefill", "layers": layers, "prefill": run_prefill(),
+                          "kernel_status": kernel_status()}))
         return 0
     clocks = ClockSampler()
     note(f"decode at batch {args.batch}")
@@ -325,6 +338,7 @@ def main(argv=None) -> int:
             points[f"decode_b{b}_hbm_frac"] = round(sb / (r["dev_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
             points[f"decode_b{b}_e2e"] = round(b / (r["e2e_ms"] * 1e-3), 1)
         result["points"] = points
+    result["kernel_status"] = kernel_status()
     note("done")
     print(json.dumps(result))
     return 0

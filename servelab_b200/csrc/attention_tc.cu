@@ -15,7 +15,12 @@
 //                   bfloat16 back into tensor memory (tcgen05.st, over the scores it
 //                   came from), where the second MMA reads its A operand  -> p_full
 // The scores are double buffered: Q.K^T of the next tile runs while this tile's softmax
-// does, and P of a tile never waits for the P.V of the one before.
+// does, and P of a tile never waits for the P.V of the one before.  Every barrier that
+// is waited on by parity is one of a pair indexed by the tile's buffer, so that the
+// side that signals can never be two phases ahead of the side that waits: the softmax
+// warps may finish tile j + 1 before the MMA warp has seen P of tile j (both score
+// buffers are filled ahead), and a single "P is ready" barrier would then have wrapped
+// past the phase the MMA warp still waits for.
 //
 // The running maximum is only raised when the tile's maximum exceeds it by more than
 // 2^8 (scores are in the base-2 domain); otherwise the stale maximum keeps being used
@@ -51,10 +56,21 @@ constexpr int OFF_K = OFF_Q + Q_BYTES;
 constexpr int OFF_V = OFF_K + 2 * KV_TILE_BYTES;
 constexpr int OFF_BAR = OFF_V + 2 * KV_TILE_BYTES;
 constexpr size_t TC_ATTN_SMEM = OFF_BAR + 128;
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr uint32_t SPIN_LIMIT = 1u << 18;     // a poll that suspends takes about 4 us: about a second
 constexpr float RESCALE_THRESHOLD = 8.f;       // log2 of the largest probability tolerated
 
 __device__ int tc_attn_status = 0;
+// Where bounded waits gave up last, four ints per role (loader, MMA issuer, softmax):
+// code, block x | block y << 16, key tile, key tiles of the block.
+__device__ int tc_attn_where[12] = {0};
+
+__device__ __forceinline__ void gave_up(int* status, int code, int role, int tile, int ntiles) {
+    atomicCAS(status, 0, code);
+    tc_attn_where[role * 4 + 0] = code;
+    tc_attn_where[role * 4 + 1] = (int)(blockIdx.x | (blockIdx.y << 16));
+    tc_attn_where[role * 4 + 2] = tile;
+    tc_attn_where[role * 4 + 3] = ntiles;
+}
 
 using slb_tma::tma_load_2d;
 
@@ -154,8 +170,8 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);    // [2]
     uint64_t* kv_empty = kv_full + 2;                                   // [2]
     uint64_t* s_full = kv_empty + 2;                                    // [2]
-    uint64_t* p_full = s_full + 2;
-    uint64_t* pv_done = p_full + 1;
+    uint64_t* p_full = s_full + 2;                                      // [2], one per score buffer
+    uint64_t* pv_done = p_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
 
     pdl_wait();
@@ -190,7 +206,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
         mbar_init(&kv_full[0], 1); mbar_init(&kv_full[1], 1);
         mbar_init(&kv_empty[0], 1); mbar_init(&kv_empty[1], 1);
         mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
-        mbar_init(p_full, 128);
+        mbar_init(&p_full[0], 128); mbar_init(&p_full[1], 128);
         mbar_init(pv_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -236,7 +252,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
             (void)pow2;
             for (int j = 0; j < ntiles; ++j) {
                 const int st = j & 1;
-                if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1)) { atomicCAS(status, 0, 0x101); break; }
+                if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1)) { gave_up(status, 0x101, 0, j, ntiles); break; }
                 const int k0 = kbeg + j * BN;
                 int rows[8];
                 uint32_t bytes = 0;
@@ -272,7 +288,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
             // tile t - 2; its P.V has been issued before)
             auto issue_qk = [&](int t) -> bool {
                 const int st = t & 1;
-                if (!mbar_wait(&kv_full[st], (t >> 1) & 1)) { atomicCAS(status, 0, 0x201); return false; }
+                if (!mbar_wait(&kv_full[st], (t >> 1) & 1)) { gave_up(status, 0x201, 1, t, ntiles); return false; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t k_addr = smem_u32(smem + OFF_K + st * KV_TILE_BYTES);
 #pragma unroll
@@ -289,7 +305,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
             if (ok && ntiles > 1) ok = issue_qk(1);
             for (int j = 0; j < ntiles && ok; ++j) {
                 const int st = j & 1;
-                if (!mbar_wait(p_full, j & 1)) { atomicCAS(status, 0, 0x202); break; }
+                if (!mbar_wait(&p_full[st], (j >> 1) & 1)) { gave_up(status, 0x202, 1, j, ntiles); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t v_addr = smem_u32(smem + OFF_V + st * KV_TILE_BYTES);
 #pragma unroll
@@ -313,7 +329,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < ntiles && ok; ++j) {
-            if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicCAS(status, 0, 0x301); ok = false; break; }
+            if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1)) { if (lane == 0) gave_up(status, 0x301, 2, j, ntiles); ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t raw[2][32];
             tmem_ld32(tmem + lane_base + S_COL + 64 * (j & 1), raw[0]);
@@ -363,7 +379,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
             l = l * alpha + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
                 // the accumulator is rescaled (rarely): P.V of the previous tile must be done
-                if (!mbar_wait(pv_done, (j - 1) & 1)) { atomicCAS(status, 0, 0x302); ok = false; break; }
+                if (!mbar_wait(pv_done, (j - 1) & 1)) { if (lane == 0) gave_up(status, 0x302, 2, j, ntiles); ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int c0 = 0; c0 < D; c0 += 32) {
@@ -379,10 +395,10 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
             tmem_st32(tmem + lane_base + S_COL + 64 * (j & 1), packed);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(p_full);
+            mbar_arrive(&p_full[j & 1]);
         }
         if (ok) {
-            if (!mbar_wait(pv_done, (ntiles - 1) & 1)) { atomicCAS(status, 0, 0x303); ok = false; }
+            if (!mbar_wait(pv_done, (ntiles - 1) & 1)) { if (lane == 0) gave_up(status, 0x303, 2, ntiles, ntiles); ok = false; }
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         pdl_launch_dependents();
@@ -467,6 +483,11 @@ int slb_prefill_attention_tc_bf16(const bf16* q, int ldq, const bf16* kc, const 
                       ps, box_rows, scale * 1.4426950408889634f, window, status);
 }
 
+// copies the twelve ints that say where waits gave up last (see tc_attn_where)
+int slb_prefill_attention_tc_where(int* out12) {
+    return (int)cudaMemcpyFromSymbol(out12, tc_attn_where, 12 * sizeof(int));
+}
+
 int slb_prefill_attention_tc_status(int reset) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, tc_attn_status, sizeof(int)) != cudaSuccess) return -1;
@@ -484,6 +505,10 @@ extern "C" {
 int slb_prefill_attention_tc_supported(int, int) { return 0; }
 int slb_prefill_attention_tc_tile_rows(int) { return 0; }
 int slb_prefill_attention_tc_status(int) { return 0; }
+int slb_prefill_attention_tc_where(int* out12) {
+    for (int i = 0; i < 12; ++i) out12[i] = 0;
+    return 0;
+}
 }
 
 #endif

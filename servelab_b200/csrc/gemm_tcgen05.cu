@@ -34,7 +34,7 @@ constexpr int TC_MAX_TOK = 64;        // MMA N
 constexpr int TC_MAX_STAGES = 12;     // the ring is as deep as shared memory allows
 constexpr int TC_THREADS = 192;       // warp 0 loader, warp 1 MMA + TMEM, warps 2..5 epilogue
 constexpr int TC_TMEM_COLS = 64;
-constexpr uint32_t SLB_TC_SPIN_LIMIT = 1u << 20;
+constexpr uint32_t SLB_TC_SPIN_LIMIT = 1u << 18;
 constexpr int A_STAGE_BYTES = TC_BM * TC_BK * 2;          // 16 KB of W per stage
 constexpr size_t TC_SMEM_BUDGET = 200 * 1024;             // stages + barriers (one block per SM)
 constexpr size_t TC_SMEM_TAIL = 256;                      // barriers and the TMEM address

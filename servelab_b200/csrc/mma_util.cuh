@@ -41,7 +41,8 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 
 // ---- bulk asynchronous copies (one instruction per row) tracked by an mbarrier ----
-constexpr uint32_t ATTN_SPIN_LIMIT = 1u << 22;   // polls before a wait gives up
+constexpr uint32_t ATTN_SPIN_LIMIT = 1u << 18;   // polls before a wait gives up (a poll that
+                                                 // suspends takes about 4 us: about a second)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);

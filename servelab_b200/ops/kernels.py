@@ -197,6 +197,20 @@ def prefill_attention_tc_status(head_dim: int, reset: bool = False) -> int:
     return L.attention(head_dim).slb_prefill_attention_tc_status(1 if reset else 0)
 
 
+def prefill_attention_tc_where(head_dim: int) -> dict:
+    """Where the roles of the tcgen05 prefill attention gave up a bounded wait last:
+    per role (code, block x, block y, key tile, key tiles of the block); zeros if never."""
+    import ctypes
+    buf = (ctypes.c_int * 12)()
+    L.attention(head_dim).slb_prefill_attention_tc_where(ctypes.cast(buf, ctypes.c_void_p))
+    out = {}
+    for i, role in enumerate(("loader", "mma", "softmax")):
+        code, block, tile, ntiles = buf[4 * i:4 * i + 4]
+        out[role] = {"code": hex(code), "block": (block & 0xffff, block >> 16), "tile": tile,
+                     "tiles": ntiles}
+    return out
+
+
 def has_fast_attention(head_dim: int) -> bool:
     """The tensor-core kernels exist for head sizes that are multiples of 16 up to
     256; the library for a head size is built when it is first asked for."""

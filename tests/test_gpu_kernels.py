@@ -381,6 +381,40 @@ def test_prefill_attention_tensor_cores(H, Hkv, D, ps, window):
             kernels_module.use_tc_prefill = True
 
 
+def test_prefill_attention_tcgen05_many_launches_of_a_long_prompt():
+    """A 2,048-token prompt at the 7B head layout, 300 launches back to back with matrix
+    products between them: 137,000 blocks whose roles (loader, MMA issuer, softmax
+    warps) run ahead of one another by different amounts.  No bounded wait may give up
+    (a barrier that wraps past a waiter shows as a status word, and as a test that takes
+    seconds), and every launch gives the result of the mma.sync kernel."""
+    from servelab_b200.ops import kernels as kernels_module
+    H, Hkv, D, ps = 28, 4, 128, 16
+    case = PagedCase([2048], [2048], H, Hkv, D, ps, torch.bfloat16, seed=5)
+    case.scatter()
+    ctx, q, table = _ctx_for(case)
+    kernels_module.use_tc_prefill = False
+    try:
+        want = torch.empty_like(q)
+        K().prefill_attention(ctx, q, case.kc, case.vc, want, table, H, Hkv, D, ps, 1 / math.sqrt(D), 0)
+    finally:
+        kernels_module.use_tc_prefill = True
+    a = torch.randn(2048, 1024, device=DEV).bfloat16()
+    b = torch.randn(1024, 3584, device=DEV).bfloat16()
+    outs = [torch.empty_like(q) for _ in range(4)]
+    worst = 0.0
+    for i in range(300):
+        out = outs[i % 4]
+        if i % 3 == 0:
+            torch.mm(a, b)
+        K().prefill_attention(ctx, q, case.kc, case.vc, out, table, H, Hkv, D, ps, 1 / math.sqrt(D), 0)
+        if i % 50 == 49:
+            assert K().prefill_attention_tc_status(D, reset=True) == 0, \
+                f"a bounded wait gave up: {K().prefill_attention_tc_where(D)}"
+            for o in outs:
+                worst = max(worst, (o.float() - want.float()).abs().max().item())
+    assert worst <= TOL["bfloat16"]
+
+
 @pytest.mark.parametrize("H,Hkv,D,ps", [(6, 2, 16, 16), (7, 1, 64, 8), (4, 2, 48, 4),
                                         (28, 4, 128, 16), (2, 1, 256, 32), (20, 1, 32, 16)])
 @pytest.mark.parametrize("window", [0, 70])
