@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ ctx_len,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int H,
     int Hkv, int ps, int box_rows, float scale_log2, int window, int num_splits, int head_tiles,
-    int stages) {
+    int stages, float split_coef, int unsplit_tiles) {
     constexpr int HR = 8 * NH;                             // query heads per block
     constexpr int QCH = (HR * CHUNKS + 32 * DW - 1) / (32 * DW);   // 16-byte chunks of Q a consumer thread moves
     extern __shared__ unsigned char smem_raw[];
@@ -172,6 +172,33 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     const int h0 = htile * HR;                             // first head of the group in this block
     const int nrows = min(HR, g - h0);
 
+    // context length and block table are written by the host before the step: they may be
+    // read before the preceding kernel has finished
+    const int ctx = ctx_len[s];
+    const int pos = ctx - 1;
+    const int* table = block_table + (size_t)s * max_pages;
+
+    int kbeg = 0;
+    if (window > 0) kbeg = max(0, pos - window + 1) / BN * BN;
+    const int total_tiles = (ctx - kbeg + BN - 1) / BN;
+    // How many of the launch's num_splits this request uses: none beyond one while it has
+    // few tiles; otherwise about split_coef * sqrt(tiles) tiles per split (the cost of a
+    // split grows with the number of splits the last block combines, the cost of a tile
+    // with the tiles per split).  Blocks of unused splits leave at once.
+    int use_splits = 1;
+    if (num_splits > 1 && total_tiles > unsplit_tiles) {
+        const int per = max((int)ceilf(split_coef * sqrtf((float)total_tiles)),
+                            (total_tiles + num_splits - 1) / num_splits);
+        use_splits = (total_tiles + per - 1) / per;
+        if (use_splits > 8 && use_splits <= 12) use_splits = 8;   // the last block reads eight at a time
+    }
+    if (split >= use_splits) return;
+    const int tiles_per_split = (total_tiles + use_splits - 1) / use_splits;
+    const int t_begin = split * tiles_per_split;
+    const int ntiles = max(0, min(total_tiles, t_begin + tiles_per_split) - t_begin);
+    const int kstart = kbeg + t_begin * BN;
+    const int kstop = min(ctx, kstart + ntiles * BN);
+
     if (tid == 0) {
         for (int p = 0; p < stages; ++p) {
             mbar_init(&full_bar[p], 1);
@@ -183,20 +210,6 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    // context length and block table are written by the host before the step: they may be
-    // read before the preceding kernel has finished
-    const int ctx = ctx_len[s];
-    const int pos = ctx - 1;
-    const int* table = block_table + (size_t)s * max_pages;
-
-    int kbeg = 0;
-    if (window > 0) kbeg = max(0, pos - window + 1) / BN * BN;
-    const int total_tiles = (ctx - kbeg + BN - 1) / BN;
-    const int tiles_per_split = (total_tiles + num_splits - 1) / num_splits;
-    const int t_begin = split * tiles_per_split;
-    const int ntiles = max(0, min(total_tiles, t_begin + tiles_per_split) - t_begin);
-    const int kstart = kbeg + t_begin * BN;
-    const int kstop = min(ctx, kstart + ntiles * BN);
 
     const BoxGeometry geo = box_geometry(box_rows);
     const int ps_shift = __ffs(ps) - 1;                    // the launcher takes powers of two only
@@ -463,7 +476,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
                     L[h] += red_l[w][hr] * f[w][h];
                 }
                 const int head = kvh * g + h0 + hr;
-                if (num_splits > 1 && hr < nrows && (warp * RPW) % (MT * 4) == 0 && lane < 4) {
+                if (use_splits > 1 && hr < nrows && (warp * RPW) % (MT * 4) == 0 && lane < 4) {
                     const size_t pi = ((size_t)s * H + head) * num_splits + split;
                     part_ml[pi * 2] = M;
                     part_ml[pi * 2 + 1] = L[h];
@@ -480,7 +493,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
                 const int d = mt * 16 + (lane >> 2) + (e >> 1) * 8;
                 if (hr < nrows) {
                     const int head = kvh * g + h0 + hr;
-                    if (num_splits == 1) {
+                    if (use_splits == 1) {
                         out[(size_t)s * ldo + (size_t)head * D + d] =
                             __float2bfloat16_rn(L[h] > 0.f ? acc / L[h] : 0.f);
                     } else {
@@ -490,7 +503,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
             }
         }
     }
-    if (num_splits == 1) return;
+    if (use_splits == 1) return;
 
     // ---- the block that arrives last combines the splits ----
     // The block barrier orders every thread's partial results before thread 0's release
@@ -501,7 +514,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     if (tid == 0) {
         int before;
         asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(before) : "l"(counter) : "memory");
-        last_block = before == num_splits - 1;
+        last_block = before == use_splits - 1;
         if (last_block) *counter = 0;                      // zero again for the next launch
     }
     __syncthreads();
@@ -513,11 +526,11 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
         // one pass, eight splits' loads in flight together (they come from the L2); the
         // running reference moves as in the online softmax
         float M = -INFINITY, L = 0.f, acc = 0.f;
-        for (int i0 = 0; i0 < num_splits; i0 += 8) {
+        for (int i0 = 0; i0 < use_splits; i0 += 8) {
             float mv[8], lv[8], ov[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const bool in = i0 + j < num_splits;
+                const bool in = i0 + j < use_splits;
                 mv[j] = in ? __ldcg(part_ml + (base + i0 + j) * 2) : -INFINITY;
                 lv[j] = in ? __ldcg(part_ml + (base + i0 + j) * 2 + 1) : 0.f;
                 ov[j] = in ? __ldcg(part_o + (base + i0 + j) * D + d) : 0.f;
@@ -555,7 +568,7 @@ template <int NH>
 int launch_decode(const bf16* q, int ldq, const CUtensorMap& map_k, const CUtensorMap& map_v, bf16* out,
                   int ldo, const int* block_table, int max_pages, const int* ctx_len, float* scratch,
                   int* counters, int S, int H, int Hkv, int ps, int box_rows, float scale, int window,
-                  int num_splits, int stages, cudaStream_t st) {
+                  int num_splits, int stages, float split_coef, int unsplit_tiles, cudaStream_t st) {
     const int g = H / Hkv;
     const int head_tiles = (g + 8 * NH - 1) / (8 * NH);
     if ((long long)Hkv * head_tiles > 65535) return SLB_ERR_TOO_LARGE;
@@ -573,7 +586,8 @@ int launch_decode(const bf16* q, int ldq, const CUtensorMap& map_k, const CUtens
     return slb_launch(decode_attention_ws_kernel<NH>, dim3(num_splits, Hkv * head_tiles, S),
                       dim3(NTHREADS), smem, st, q, ldq, map_k, map_v, out, ldo, block_table, max_pages,
                       ctx_len, part_o, part_ml, counters, H, Hkv, ps, box_rows,
-                      scale * 1.4426950408889634f, window, num_splits, head_tiles, stages);
+                      scale * 1.4426950408889634f, window, num_splits, head_tiles, stages, split_coef,
+                      unsplit_tiles);
 }
 
 }  // namespace
@@ -613,18 +627,21 @@ long long slb_decode_attention_ws_counters(int S, int H, int Hkv) {
 
 // scratch and counters may be null when num_splits == 1.  num_pages: pages in k_cache /
 // v_cache ([num_pages][Hkv][ps][D]).  stages: depth of the shared-memory ring, 2..4.
+// num_splits is the most any request is split; a request of T 64-key tiles uses one split
+// while T <= unsplit_tiles, else ceil(T / max(ceil(split_coef * sqrt(T)), ceil(T /
+// num_splits))) of them (8 instead of 9..12).
 int slb_decode_attention_ws_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, bf16* out,
                                  int ldo, const int* block_table, int max_pages, const int* ctx_len,
                                  float* scratch, int* counters, int S, int H, int Hkv, int ps,
                                  int num_pages, float scale, int window, int num_splits, int stages,
-                                 cudaStream_t st) {
+                                 float split_coef, int unsplit_tiles, cudaStream_t st) {
     if (S <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || max_pages <= 0 || num_pages <= 0 || !(scale > 0.f))
         return SLB_ERR_BAD_ARG;
     if (!slb_decode_attention_ws_supported(ps)) return SLB_ERR_BAD_ARG;
     if (num_splits < 1 || (num_splits > 1 && (scratch == nullptr || counters == nullptr)))
         return SLB_ERR_BAD_ARG;
-    if (stages < 2 || stages > MAX_STAGES) return SLB_ERR_BAD_ARG;
+    if (stages < 2 || stages > MAX_STAGES || !(split_coef >= 0.f) || unsplit_tiles < 0) return SLB_ERR_BAD_ARG;
     if (ldq % 8 || ((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc) % 16) return SLB_ERR_BAD_ARG;
     if (num_splits > MAX_SPLITS || S > 65535) return SLB_ERR_TOO_LARGE;
     const long long rows = (long long)num_pages * Hkv * ps;
@@ -637,9 +654,11 @@ int slb_decode_attention_ws_bf16(const bf16* q, int ldq, const bf16* kc, const b
     if (rc != 0) return rc;
     if (H / Hkv <= 8)
         return launch_decode<1>(q, ldq, map_k, map_v, out, ldo, block_table, max_pages, ctx_len, scratch,
-                                counters, S, H, Hkv, ps, box_rows, scale, window, num_splits, stages, st);
+                                counters, S, H, Hkv, ps, box_rows, scale, window, num_splits, stages, split_coef,
+                                unsplit_tiles, st);
     return launch_decode<2>(q, ldq, map_k, map_v, out, ldo, block_table, max_pages, ctx_len, scratch,
-                            counters, S, H, Hkv, ps, box_rows, scale, window, num_splits, stages, st);
+                            counters, S, H, Hkv, ps, box_rows, scale, window, num_splits, stages, split_coef,
+                                unsplit_tiles, st);
 }
 
 }  // extern "C"
@@ -655,7 +674,7 @@ long long slb_decode_attention_ws_scratch_bytes(int, int, int) { return 0; }
 long long slb_decode_attention_ws_counters(int, int, int) { return 0; }
 int slb_decode_attention_ws_bf16(const bf16*, int, const bf16*, const bf16*, bf16*, int, const int*, int,
                                  const int*, float*, int*, int, int, int, int, int, float, int, int, int,
-                                 cudaStream_t) {
+                                 float, int, cudaStream_t) {
     return SLB_ERR_BAD_ARG;
 }
 }

@@ -7,6 +7,7 @@ The dtype of the activations selects the float32 or the bfloat16 instance.
 
 from __future__ import annotations
 
+import math
 from typing import Dict, Optional
 
 import torch
@@ -276,12 +277,14 @@ def decode_attention_split(ctx, q, k_cache, v_cache, out, block_table, num_heads
 
 
 decode_ws_stages = 3           # depth of the kernel's shared-memory ring (2..4)
-decode_ws_force_splits = 0     # measurements: this many splits instead of the choice below
-# Cost model behind the choice of splits, in microseconds, fitted to measurements on a
-# B200 at head size 128: a block takes `tile` per 64-key tile; splitting costs
-# `split_fixed` once (partial results, the arrival counter, the last block's combine)
-# plus `split_batch` per eight splits the last block reads.
-decode_ws_cost = {"tile": 0.45, "split_fixed": 3.0, "split_batch": 1.0}
+decode_ws_force_splits = 0     # measurements: launch this many splits instead of the choice below
+# The kernel picks each request's number of splits itself, from the request's own length:
+# one while it has at most `decode_ws_unsplit_tiles` 64-key tiles, else about
+# `decode_ws_split_coef` * sqrt(tiles) tiles per split, and never more splits than were
+# launched.  Fitted to measurements on a B200 at head size 128: a tile costs a block about
+# 0.45 us, a split 3 us once plus 1 us per eight splits the last block combines.
+decode_ws_split_coef = 0.8
+decode_ws_unsplit_tiles = 12
 
 _DECODE_COUNTERS = 1 << 16     # arrival counters held per device (256 KiB)
 _decode_counters: Dict[int, torch.Tensor] = {}
@@ -300,26 +303,17 @@ def _decode_counter_buffer(device: torch.device) -> torch.Tensor:
 
 def decode_ws_splits(num_seqs: int, num_kv_heads: int, group: int, longest_context: int,
                      max_splits: int, tile_keys: int) -> int:
-    """How many ways the keys of each request are split: the count that minimises
-    rounds of blocks x tiles per block x time per tile + the cost of splitting."""
+    """The most splits a request may use (the launch's grid): as many as keep all
+    blocks of the step resident at once (two per SM), 1 for short contexts."""
     head_rows = 8 if group <= 8 else 16
     pairs = num_seqs * num_kv_heads * (-(-group // head_rows))
     tiles = max(1, -(-longest_context // tile_keys))
+    if tiles <= decode_ws_unsplit_tiles:
+        return 1
     slots = 2 * _num_sms()                      # two blocks of three stages fit on an SM
-    cost = decode_ws_cost
-    best, best_time = 1, None
-    for want in range(1, min(max_splits, tiles) + 1):
-        per = -(-tiles // want)
-        splits = -(-tiles // per)               # no split of the longest context is empty
-        if splits != want:
-            continue
-        rounds = -(-pairs * splits // slots)
-        t = rounds * per * cost["tile"]
-        if splits > 1:
-            t += cost["split_fixed"] + cost["split_batch"] * (-(-splits // 8))
-        if best_time is None or t < best_time - 1e-9:
-            best, best_time = splits, t
-    return best
+    per = max(1, math.ceil(decode_ws_split_coef * math.sqrt(tiles)))
+    longest_uses = -(-tiles // per)             # the kernel's own rule for the longest context
+    return max(1, min(max_splits, slots // max(pairs, 1), longest_uses))
 
 
 def decode_attention(ctx, q, k_cache, v_cache, out, block_table, num_heads, num_kv_heads,
@@ -350,7 +344,8 @@ def decode_attention(ctx, q, k_cache, v_cache, out, block_table, num_heads, num_
         q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
         out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.ctx_len.data_ptr(),
         _p(scratch), _p(counters), S, num_heads, num_kv_heads, page_size, k_cache.shape[0],
-        float(scale), int(window), splits, int(decode_ws_stages), _stream()), "decode_attention")
+        float(scale), int(window), splits, int(decode_ws_stages), float(decode_ws_split_coef),
+        int(decode_ws_unsplit_tiles), _stream()), "decode_attention")
 
 
 def decode_attention_status(head_dim: int, reset: bool = False) -> int:

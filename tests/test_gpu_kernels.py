@@ -449,12 +449,14 @@ def test_decode_attention_tensor_cores(H, Hkv, D, ps, window, splits):
                                         (24, 3, 64, 256), (48, 2, 128, 16),
                                         (6, 2, 16, 16), (4, 2, 48, 4), (16, 1, 80, 5)])
 @pytest.mark.parametrize("window", [0, 70])
-@pytest.mark.parametrize("splits,stages", [(1, 3), (3, 2), (32, 4), (5, 3)])
-def test_decode_attention_one_launch(H, Hkv, D, ps, window, splits, stages):
+@pytest.mark.parametrize("splits,stages,coef,unsplit", [(1, 3, 0.8, 12), (3, 2, 0.0, 0), (32, 4, 0.0, 0),
+                                                        (5, 3, 0.8, 12), (32, 3, 0.8, 2), (32, 3, 3.0, 0)])
+def test_decode_attention_one_launch(H, Hkv, D, ps, window, splits, stages, coef, unsplit):
     """The producer/consumer decode kernel whose last block combines the splits:
     every group size (8 and 16 head rows a block, several head tiles), pages smaller
-    and larger than a key tile, ring depths, more splits than tiles; twice in a row,
-    so the arrival counters came back to 0.  Sizes it refuses reach the earlier
+    and larger than a key tile, ring depths, more splits than tiles, requests that use
+    fewer splits than were launched (each by its own length); twice in a row, so the
+    arrival counters came back to 0.  Sizes it refuses reach the earlier
     kernel through the wrapper."""
     from servelab_b200.ops import library as L
     ctxs = [1, 63, 64, 65, 700, 2049, 17]
@@ -480,7 +482,8 @@ def test_decode_attention_one_launch(H, Hkv, D, ps, window, splits, stages):
             q.data_ptr(), q.stride(0), case.kc.data_ptr(), case.vc.data_ptr(), out.data_ptr(),
             out.stride(0), table.data_ptr(), table.shape[1], ctx.ctx_len.data_ptr(),
             scratch.data_ptr(), counters.data_ptr(), S, H, Hkv, ps, case.kc.shape[0],
-            1 / math.sqrt(D), window, splits, stages, torch.cuda.current_stream().cuda_stream), "decode")
+            1 / math.sqrt(D), window, splits, stages, coef, unsplit,
+            torch.cuda.current_stream().cuda_stream), "decode")
         assert K().decode_attention_status(D, reset=True) == 0, "a bounded wait in the kernel gave up"
         assert (out.float().cpu() - want).abs().max() <= TOL["bfloat16"]
         assert int(counters.abs().sum()) == 0
