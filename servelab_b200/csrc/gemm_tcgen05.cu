@@ -112,6 +112,20 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "r"(taddr));
 }
 
+// Weights to pull into the L2 cache for the product that follows this one: the first
+// `bytes` of that matrix, requested in pieces of chunk_bytes (a request costs the issuing
+// warp tens of cycles whatever its size, so the pieces are large and few).  The requests
+// are issued when this block's own tiles have all arrived, so they fill the time in which
+// the small kernels between two products leave the memory idle.
+struct Prefetch {
+    const unsigned char* ptr;
+    long long bytes;
+    int chunk_bytes;
+};
+__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 // grid (row tiles of W, K splits).  ntok16: tokens padded to a multiple of 16.
 // splits == 1: `out` receives the result (+ bias) in its dtype; otherwise `partial`
 // receives float32 [split][M][N].
@@ -119,7 +133,7 @@ template <typename TO>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     TO* __restrict__ out, int ldo, float* __restrict__ partial, const float* __restrict__ bias,
-    int M, int N, int K, int ntok16, int max_stages, int* __restrict__ status) {
+    int M, int N, int K, int ntok16, int max_stages, int* __restrict__ status, Prefetch pf) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -223,6 +237,18 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         pdl_launch_dependents();
+        if (pf.ptr != nullptr) {
+            const long long items = (pf.bytes + pf.chunk_bytes - 1) / pf.chunk_bytes;
+            const long long stride = (long long)(gridDim.x * gridDim.y) * (TC_THREADS - 64);
+            // consecutive pieces go to different blocks (one thread of a block at a time)
+            const long long first = (long long)(threadIdx.x - 64) * (gridDim.x * gridDim.y) +
+                                    (blockIdx.y * gridDim.x + blockIdx.x);
+            for (long long it = first; it < items; it += stride) {
+                const long long off = it * pf.chunk_bytes;
+                const long long left = pf.bytes - off;
+                prefetch_l2(pf.ptr + off, (uint32_t)(left < pf.chunk_bytes ? left : pf.chunk_bytes) & ~15u);
+            }
+        }
         for (int c0 = 0; c0 < ntok16; c0 += 16) {
             uint32_t v[16];
             if (iters > 0 && ok) {
@@ -305,7 +331,7 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box
 template <typename TO>
 int run(const bf16* x, int ldx, const bf16* W, int ldw, TO* out, int ldo, const float* bias,
         float* workspace, int M, int N, int K, int splits, int max_stages, int defer_sum,
-        cudaStream_t st) {
+        const Prefetch& pf, cudaStream_t st) {
     CUtensorMap map_w, map_x;
     const int ntok16 = (M + 15) / 16 * 16;
     int rc = make_map(&map_w, W, N, K, ldw, TC_BM);
@@ -327,7 +353,7 @@ int run(const bf16* x, int ldx, const bf16* W, int ldw, TO* out, int ldo, const 
     cudaError_t e = cudaGetSymbolAddress((void**)&status, tc_status_word);
     if (e != cudaSuccess) return (int)e;
     rc = slb_launch(gemm_tc_decode_kernel<TO>, dim3((N + TC_BM - 1) / TC_BM, splits), dim3(TC_THREADS),
-                    TC_SMEM, st, map_w, map_x, out, ldo, workspace, bias, M, N, K, ntok16, max_stages, status);
+                    TC_SMEM, st, map_w, map_x, out, ldo, workspace, bias, M, N, K, ntok16, max_stages, status, pf);
     if (rc != 0 || splits == 1 || defer_sum) return rc;
     return slb_launch(gemm_tc_reduce_kernel<TO>, dim3((N + 255) / 256, M), dim3(256), 0, st,
                       (const float*)workspace, out, ldo, bias, M, N, splits);
@@ -341,9 +367,13 @@ extern "C" {
 // max_stages: cap on the depth of the shared-memory ring (0: as deep as fits).
 // defer_sum: with splits > 1, leave the partial sums [splits][M][N] in the workspace
 // and launch no reduction (the consumer adds them; `out` and `bias` are unused).
+// next_w (may be null): the weights the following product will read; their first
+// next_bytes are requested into the L2 cache in pieces of next_chunk_bytes (both multiples
+// of 16, the address 16-byte aligned).
 int slb_gemm_tc_decode_bf16(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo,
                             const float* bias, float* workspace, int out_f32, int M, int N, int K,
-                            int splits, int max_stages, int defer_sum, cudaStream_t st) {
+                            int splits, int max_stages, int defer_sum, const void* next_w,
+                            long long next_bytes, int next_chunk_bytes, cudaStream_t st) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldo < N) return SLB_ERR_BAD_ARG;
     if (((uintptr_t)x | (uintptr_t)W) % 16) return SLB_ERR_BAD_ARG;
@@ -351,11 +381,17 @@ int slb_gemm_tc_decode_bf16(const bf16* x, int ldx, const bf16* W, int ldw, void
     const int kblocks = (K + TC_BK - 1) / TC_BK;
     if (splits < 1 || splits > kblocks || splits > 65535) return SLB_ERR_BAD_ARG;
     if (splits > 1 && workspace == nullptr) return SLB_ERR_BAD_ARG;
+    Prefetch pf = {nullptr, 0, 0};
+    if (next_w != nullptr && next_bytes >= 16) {
+        if (next_chunk_bytes < 16 || next_chunk_bytes % 16 || next_bytes % 16 || (uintptr_t)next_w % 16)
+            return SLB_ERR_BAD_ARG;
+        pf = {static_cast<const unsigned char*>(next_w), next_bytes, next_chunk_bytes};
+    }
     if (out_f32)
         return run<float>(x, ldx, W, ldw, (float*)out, ldo, bias, workspace, M, N, K, splits, max_stages,
-                          defer_sum, st);
+                          defer_sum, pf, st);
     return run<bf16>(x, ldx, W, ldw, (bf16*)out, ldo, bias, workspace, M, N, K, splits, max_stages,
-                     defer_sum, st);
+                     defer_sum, pf, st);
 }
 
 // out[M, N] = sum of float32 partial sums [splits][M][N] (+ bias), in order.

@@ -19,7 +19,7 @@ import torch
 
 from ..config.specs import ModelSpec
 from ..ops import kernels as K
-from ..ops.linear import linear
+from ..ops.linear import linear, set_weight_order
 from ..parts import BLOCKS, NORMS, POSITIONS, BuildEnv, LayerCache, build_part, part_class
 from ..weights.source import MATRIX, TensorDecl, WeightSource
 from ..weights.store import WeightStore
@@ -75,6 +75,11 @@ class CausalLM:
         self.final_norm.load(store)
         self.lm_head = (self.embed_tokens if self.spec.tie_word_embeddings
                         else store.get(self.spec.lm_head_name))
+        # the order in which a step multiplies by the weights (a cache hint for the products)
+        order = []
+        for run in self.spec.run_order:
+            order += self.blocks[run.layer].matrices()
+        set_weight_order(order + [self.lm_head])
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0

@@ -12,6 +12,7 @@ also exists and is off by default.
 
 from __future__ import annotations
 
+import weakref
 from typing import Optional
 
 import torch
@@ -33,6 +34,28 @@ tc_max_tokens = 16         # up to this many tokens the tcgen05 weight-streaming
 defer_split_sums = False   # hand K-split partial sums to the consuming kernel instead of
                            # reducing them in a kernel of their own (measured slower: the
                            # consumers run few blocks and are bound by latency)
+
+
+# Which weights follow which in a forward pass, by address: a hint with which the tcgen05
+# product warms the L2 cache for its successor.  Set by the model after loading; a
+# matrix used twice keeps its last successor (the hint may be wrong, never harmful).
+# Weak references: the table keeps no model's weights alive.
+_successor = {}
+
+
+def set_weight_order(matrices) -> None:
+    """``matrices``: the weight matrices in the order a forward pass multiplies by them;
+    the last is followed by the first (the next step)."""
+    _successor.clear()
+    ms = [m for m in matrices if m is not None]
+    for a, b in zip(ms, ms[1:] + ms[:1]):
+        if a.data_ptr() != b.data_ptr():
+            _successor[a.data_ptr()] = weakref.ref(b)
+
+
+def _next_weight(w):
+    ref = _successor.get(w.data_ptr())
+    return ref() if ref is not None else None
 
 
 def _tc_ok(x, w, M):
@@ -58,7 +81,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         return torch.empty((0, N), dtype=out_dtype, device=x.device)
     if _tc_ok(x, w, M):
         return K.gemm_tc_decode(x, w, None, bias, defer_sum=defer_sum and defer_split_sums,
-                                out_dtype=out_dtype)
+                                out_dtype=out_dtype, next_weight=_next_weight(w))
     if _skinny_ok(x, w, M):
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         K.gemm_skinny(x, w, out, bias)

@@ -74,6 +74,9 @@ class PagedAttention(Mixer):
         self.w_o = store.get(p + ".o_proj.weight")
         self.b_o = store.get(p + ".o_proj.bias") if self.spec.out_bias else None
 
+    def matrices(self):
+        return [self.w_qkv, self.w_o]
+
     def forward(self, ctx, x, cache, owns_cache):
         s = self.spec
         T = x.shape[0]

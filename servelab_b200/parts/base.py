@@ -76,6 +76,12 @@ class Part:
     def load(self, store: WeightStore) -> None:
         pass
 
+    def matrices(self) -> List[torch.Tensor]:
+        """The weight matrices in the order forward() multiplies by them (after
+        load()).  A hint only: the model uses it to tell each product which weights
+        come next, so that they can be requested into the cache early.  May be empty."""
+        return []
+
 
 class PositionEncoding(Part):
     def rotary_table(self) -> Optional[Tuple[torch.Tensor, int]]:

@@ -47,6 +47,9 @@ class PreNormBlock(Block):
         for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward):
             p.load(store)
 
+    def matrices(self):
+        return self.mixer.matrices() + self.feed_forward.matrices()
+
     accepts_split_sum = True      # the incoming ``delta`` may be a SplitSum
 
     @staticmethod

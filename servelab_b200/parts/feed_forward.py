@@ -37,6 +37,9 @@ class GatedMLP(FeedForward):
                                     self.prefix + ".up_proj.weight"])
         self.w_down = store.get(self.prefix + ".down_proj.weight")
 
+    def matrices(self):
+        return [self.w_gate_up, self.w_down]
+
     def forward(self, ctx, x):
         gu = linear(x, self.w_gate_up)
         act = torch.empty((x.shape[0], self.spec.intermediate_size), dtype=x.dtype, device=x.device)
