@@ -168,7 +168,7 @@ def main(argv=None) -> int:
             K.decode_ctas_per_sm = int(value)
         elif name in ("decode_ws_stages", "decode_ws_force_splits"):
             setattr(K, name, int(value))
-        elif name in ("tc_prefetch_bytes", "tc_prefetch_chunk"):
+        elif name in ("tc_prefetch_bytes", "tc_prefetch_chunk", "tc_blocks_per_sm"):
             setattr(K, name, int(value))
         elif name == "use_tc_prefill":
             K.use_tc_prefill = bool(int(value))

@@ -366,15 +366,23 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
 
 # ------------------------------------ tcgen05 weight-streaming product (decode)
 TC_MAX_TOKENS = 64
-tc_max_stages = 6          # cap on the kernel's shared-memory ring; shallow rings let the next
-                           # kernel's blocks become resident beside a draining one (measured best)
+tc_max_stages = 4          # cap on the kernel's shared-memory ring: with four stages two blocks fit
+                           # on an SM, and the blocks of the next product become resident (and
+                           # request their first weight tiles) beside those of a draining one
+
+
+tc_blocks_per_sm = 2       # blocks of a product the K split aims at per SM.  Measured on the 7B
+                           # shape (ms per decode step at batch 8 / batch 1): 1 block and 6 stages
+                           # 3.48 / 3.31, 2 and 4: 3.39 / 3.20, 2 and 5: 3.66 / 3.45, 3 and 3:
+                           # 3.45 / 3.22, 4 and 2: 3.48 / 3.26
 
 
 def tc_decode_splits(n_out: int, k: int) -> int:
-    """K splits so that (row tiles x splits) is about one block per SM."""
+    """K splits so that (row tiles x splits) is about ``tc_blocks_per_sm`` blocks per SM."""
     tiles = -(-n_out // 128)
     kblocks = -(-k // 64)
-    want = max(1, round(_num_sms() / tiles)) if tiles < _num_sms() else 1
+    slots = tc_blocks_per_sm * _num_sms()
+    want = max(1, round(slots / tiles)) if tiles < slots else 1
     return max(1, min(want, kblocks // 4 if kblocks >= 8 else 1))
 
 
