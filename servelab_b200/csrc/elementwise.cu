@@ -145,8 +145,11 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
 }
 
 // out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(z) = z / (1 + exp(-z)), in float32.
-// VEC: inter, ld_gu and ld_out are multiples of 4.
-template <typename T, bool VEC>
+// V elements per thread and step: 8 (bfloat16 with inter, ld_gu and ld_out multiples of 8:
+// 16-byte accesses), 4 (multiples of 4) or 1.
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
+template <typename T, int V>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
                               int ld_gu, int ld_out) {
     pdl_launch_dependents();
@@ -154,18 +157,28 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     const int t = blockIdx.y;
     const T* row = gu + (size_t)t * ld_gu;
     T* o = out + (size_t)t * ld_out;
-    if (VEC) {
-        const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
-        if (i >= inter) return;
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+    if (i >= inter) return;
+    if constexpr (V == 8) {
+        // two 16-byte loads of 8 bfloat16 each, one 16-byte store
+        const uint4 graw = *reinterpret_cast<const uint4*>(row + i);
+        const uint4 uraw = *reinterpret_cast<const uint4*>(row + inter + i);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+        uint4 res;
+        __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
+            r2[e] = __floats2bfloat162_rn(silu_mul(g.x, u.x), silu_mul(g.y, u.y));
+        }
+        *reinterpret_cast<uint4*>(o + i) = res;
+    } else if constexpr (V == 4) {
         const float4 g = load4(row + i), u = load4(row + inter + i);
-        store4(o + i, make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y,
-                                  g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w));
+        store4(o + i, make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z),
+                                  silu_mul(g.w, u.w)));
     } else {
-        const int i = blockIdx.x * blockDim.x + threadIdx.x;
-        if (i >= inter) return;
-        const float g = to_float(row[i]);
-        const float u = to_float(row[inter + i]);
-        o[i] = from_float<T>(g / (1.0f + expf(-g)) * u);
+        o[i] = from_float<T>(silu_mul(to_float(row[i]), to_float(row[inter + i])));
     }
 }
 
@@ -210,10 +223,16 @@ static int launch_swiglu(const T* gu, T* out, int T_, int inter, int ld_gu, int 
                          cudaStream_t st) {
     if (T_ <= 0) return 0;
     if (inter <= 0 || T_ > 65535) return SLB_ERR_BAD_ARG;
+    if constexpr (sizeof(T) == 2) {
+        if (inter % 8 == 0 && ld_gu % 8 == 0 && ld_out % 8 == 0 &&
+            ((uintptr_t)gu | (uintptr_t)out) % 16 == 0)
+            return slb_launch(swiglu_kernel<T, 8>, dim3((inter / 8 + 255) / 256, T_), dim3(256), 0, st,
+                              gu, out, inter, ld_gu, ld_out);
+    }
     if (inter % 4 == 0 && ld_gu % 4 == 0 && ld_out % 4 == 0)
-        return slb_launch(swiglu_kernel<T, true>, dim3((inter / 4 + 255) / 256, T_), dim3(256), 0, st,
+        return slb_launch(swiglu_kernel<T, 4>, dim3((inter / 4 + 255) / 256, T_), dim3(256), 0, st,
                           gu, out, inter, ld_gu, ld_out);
-    return slb_launch(swiglu_kernel<T, false>, dim3((inter + 255) / 256, T_), dim3(256), 0, st, gu,
+    return slb_launch(swiglu_kernel<T, 1>, dim3((inter + 255) / 256, T_), dim3(256), 0, st, gu,
                       out, inter, ld_gu, ld_out);
 }
 

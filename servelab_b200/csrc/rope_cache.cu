@@ -88,6 +88,101 @@ __global__ void qkv_rope_cache_kernel(
     }
 }
 
+// The same with 16-byte accesses, for layouts whose rotary and pass-through parts are
+// whole vectors (VEC = 16 bytes of T).  One block per token: the first rotary_dim / 2
+// threads compute the token's sines and cosines once into shared memory; then the
+// block walks "units" of 2 * VEC elements: in a rotated head unit u < half / VEC is the
+// VEC rotation pairs (u VEC + e, u VEC + e + half); every other unit is 2 * VEC
+// neighbouring elements that pass through (the tail of a rotated head, a value head).
+template <typename T>
+__global__ void qkv_rope_cache_vec_kernel(
+    const T* __restrict__ qkv, int ld_qkv, const float* __restrict__ bias,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+    const int* __restrict__ block_table, int max_pages, int page_size,
+    const float* __restrict__ inv_freq, int rotary_dim,
+    T* __restrict__ q_out, int ld_q, T* __restrict__ k_cache, T* __restrict__ v_cache,
+    int H, int Hkv, int D) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    extern __shared__ float trig[];                    // cos[half] then sin[half]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int half = (inv_freq != nullptr) ? rotary_dim >> 1 : 0;
+    const bool write = k_cache != nullptr && v_cache != nullptr;
+    const int units_per_head = D / (2 * VEC);
+    const int rot_units = half / VEC;
+    const int heads = write ? H + 2 * Hkv : H;
+    const int units = heads * units_per_head;
+    const T* x = qkv + (size_t)t * ld_qkv;
+
+    // where unit w reads and writes inside its head: a rotation pair, or neighbours
+    auto place = [&](int w, int& j, int& a, int& b, bool& rot, bool& is_v) {
+        j = w / units_per_head;
+        const int u = w - j * units_per_head;
+        is_v = j >= H + Hkv;
+        rot = !is_v && u < rot_units;
+        a = rot ? u * VEC : (is_v ? 2 * VEC * u : 2 * half + 2 * VEC * (u - rot_units));
+        b = rot ? a + half : a + VEC;
+    };
+    const int pos = positions[t];
+    size_t kv_base = 0;
+    bool have_page = false;
+    if (write) {
+        const int page = block_table[(size_t)seq_of_token[t] * max_pages + pos / page_size];
+        have_page = page >= 0;                         // no page: nothing may be written
+        kv_base = ((size_t)(have_page ? page : 0) * Hkv * page_size + pos % page_size) * D;
+    }
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
+        trig[i] = cs;
+        trig[half + i] = sn;
+    }
+    __syncthreads();
+    for (int w = threadIdx.x; w < units; w += blockDim.x) {
+        int j, a, b; bool rot, is_v;
+        place(w, j, a, b, rot, is_v);
+        const size_t off = (size_t)j * D;
+        T va[VEC], vb[VEC];
+        *reinterpret_cast<uint4*>(va) = *reinterpret_cast<const uint4*>(x + off + a);
+        *reinterpret_cast<uint4*>(vb) = *reinterpret_cast<const uint4*>(x + off + b);
+        float fa[VEC], fb[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            fa[e] = to_float(va[e]);
+            fb[e] = to_float(vb[e]);
+            if (bias) {
+                fa[e] += bias[off + a + e];
+                fb[e] += bias[off + b + e];
+            }
+        }
+        if (rot) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                const float cs = trig[a + e], sn = trig[half + a + e];
+                const float ra = fa[e] * cs - fb[e] * sn;
+                fb[e] = fb[e] * cs + fa[e] * sn;
+                fa[e] = ra;
+            }
+        }
+        T* dst;
+        if (j < H) {
+            dst = q_out + (size_t)t * ld_q + off;
+        } else {
+            if (!have_page) continue;
+            const int kvh = is_v ? j - H - Hkv : j - H;
+            dst = (is_v ? v_cache : k_cache) + kv_base + (size_t)kvh * page_size * D;
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            va[e] = from_float<T>(fa[e]);
+            vb[e] = from_float<T>(fb[e]);
+        }
+        *reinterpret_cast<uint4*>(dst + a) = *reinterpret_cast<const uint4*>(va);
+        *reinterpret_cast<uint4*>(dst + b) = *reinterpret_cast<const uint4*>(vb);
+    }
+}
+
 template <typename T>
 static int launch_qkv_rope_cache(const T* qkv, int ld_qkv, const float* parts, int nparts,
                                  long long part_stride, const float* bias, const int* positions,
@@ -109,6 +204,19 @@ static int launch_qkv_rope_cache(const T* qkv, int ld_qkv, const float* parts, i
     int threads = slots * lanes;
     threads = (threads + 31) / 32 * 32;
     if ((qkv == nullptr) == (nparts <= 0)) return SLB_ERR_BAD_ARG;      // exactly one input form
+    constexpr int VEC = 16 / (int)sizeof(T);
+    const int rot = inv_freq != nullptr ? rotary_dim : 0;
+    const bool vec_ok = nparts <= 0 && D % (2 * VEC) == 0 && rot % (2 * VEC) == 0 &&
+                        ld_qkv % VEC == 0 && ld_q % VEC == 0 &&
+                        ((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16 == 0;
+    if (vec_ok) {
+        const int units = heads * (D / (2 * VEC));
+        int vthreads = units < 256 ? (units + 31) / 32 * 32 : 256;
+        if (vthreads < rot / 2) vthreads = ((rot / 2 + 31) / 32 * 32 < 1024) ? (rot / 2 + 31) / 32 * 32 : 1024;
+        return slb_launch(qkv_rope_cache_vec_kernel<T>, dim3(T_), dim3(vthreads), (size_t)rot * sizeof(float), st,
+                          qkv, ld_qkv, bias, positions, seq_of_token, block_table, max_pages, page_size,
+                          inv_freq, rotary_dim, q_out, ld_q, k_cache, v_cache, H, Hkv, D);
+    }
     if (nparts > 0)
         return slb_launch(qkv_rope_cache_kernel<T, true>, dim3(T_), dim3(threads), 0, st, qkv, ld_qkv,
                           parts, nparts, (size_t)part_stride, bias, positions, seq_of_token,

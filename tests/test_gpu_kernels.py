@@ -68,12 +68,13 @@ def test_add_rmsnorm(dtype, h):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_swiglu(dtype):
+@pytest.mark.parametrize("inter", [173, 172, 176, 18944])      # 1, 4 and 8 elements a thread
+def test_swiglu(dtype, inter):
     dt = DT[dtype]
-    gu = (torch.randn(7, 2 * 173, device=DEV) * 3).to(dt)
-    out = torch.empty(7, 173, device=DEV, dtype=dt)
+    gu = (torch.randn(7, 2 * inter, device=DEV) * 3).to(dt)
+    out = torch.empty(7, inter, device=DEV, dtype=dt)
     K().swiglu(gu, out)
-    g, u = gu.float()[:, :173], gu.float()[:, 173:]
+    g, u = gu.float()[:, :inter], gu.float()[:, inter:]
     want = g * torch.sigmoid(g) * u
     # results reach |30|: the bound is relative (one rounding to the output dtype)
     rel = 2.0 ** -8 if dtype == "bfloat16" else 2.0 ** -21
@@ -87,7 +88,8 @@ def _paged(num_pages, Hkv, ps, D, dt):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,Hkv,D,rot", [(6, 2, 48, 48), (5, 5, 16, 8), (3, 1, 80, 0)])
+@pytest.mark.parametrize("H,Hkv,D,rot", [(6, 2, 48, 48), (5, 5, 16, 8), (3, 1, 80, 0),
+                                         (28, 4, 128, 128), (4, 2, 64, 32), (3, 1, 40, 20)])
 def test_qkv_rope_cache(dtype, H, Hkv, D, rot):
     dt = DT[dtype]
     ps, T = 4, 11
