@@ -496,6 +496,48 @@ def test_decode_attention_one_launch(H, Hkv, D, ps, window, splits, stages, coef
         assert (out2.float().cpu() - want).abs().max() <= TOL["bfloat16"]
 
 
+@pytest.mark.parametrize("H,Hkv,D,ps", [(14, 2, 128, 16), (6, 3, 32, 8), (8, 1, 64, 64)])
+@pytest.mark.parametrize("window", [1, 7, 64, 65, 200])
+def test_fast_attention_window_edges(H, Hkv, D, ps, window):
+    """The key just outside the window of the last query would take all the weight if it
+    were visible (the key just inside must be seen): prompt portions through both prefill
+    kernels, single tokens through both decode kernels; windows below, at and above the
+    64-key tile."""
+    from servelab_b200.ops import kernels as kernels_module
+    for q_lens in ([23, 1, 64, 5], [1, 1, 1, 1]):
+        ctxs = [90, 341, 64, 700]
+        case = PagedCase(ctxs, q_lens, H, Hkv, D, ps, torch.bfloat16, seed=window + D)
+        for q, k, c in zip(case.q, case.k, case.ctx_lens):
+            a = c - 1                                        # the last query's position
+            if a - window >= 0:
+                k[a - window] = (q[-1].float().view(Hkv, H // Hkv, D).mean(1) * 50).to(k.dtype)
+        case.scatter()
+        ctx, q, table = _ctx_for(case)
+        want, full = case.reference(window=window), case.reference()
+        assert (want - full).abs().max() > 1e-2              # the window does change the result
+        if all(n == 1 for n in q_lens):
+            runs = [K().decode_attention, K().decode_attention_split]
+        else:
+            def tc(*a):
+                kernels_module.use_tc_prefill = True
+                K().prefill_attention(*a)
+
+            def mma(*a):
+                kernels_module.use_tc_prefill = False
+                try:
+                    K().prefill_attention(*a)
+                finally:
+                    kernels_module.use_tc_prefill = True
+            runs = [tc, mma]
+        for fn in runs:
+            out = torch.full_like(q, 5.0)
+            fn(ctx, q, case.kc, case.vc, out, table, H, Hkv, D, ps, 1 / math.sqrt(D), window)
+            assert (out.float().cpu() - want).abs().max() <= TOL["bfloat16"], (fn, q_lens)
+    assert K().prefill_attention_tc_status(D, reset=True) == 0
+    assert K().decode_attention_status(D, reset=True) == 0
+    assert K().attention_status(D, reset=True) == 0
+
+
 @pytest.mark.parametrize("needle", [0, 63, 64, 1023, 1024, 1500])
 def test_fast_attention_finds_one_far_key(needle):
     H, Hkv, D, ps = 14, 2, 128, 16
