@@ -6,10 +6,11 @@
 // them), so the g query heads of a group share every key/value tile.  Per 64-key
 // tile, with both accumulators in tensor memory (TMEM):
 //
-//   loader warp     TMA tensor copies (128-byte swizzle) of the tile's pages of K and V
-//                   into a two-stage shared-memory ring          -> kv_full[stage]
-//   MMA warp        S = Q.K^T   (tcgen05.mma M=128 N=64,  K=16 x D/16)  -> s_full
-//                   O += P.V    (tcgen05.mma M=128 N=D,   K=16 x 4)     -> kv_empty, pv_done
+//   loader warp     TMA tensor copies (128-byte swizzle) of the tile's pages of K and of V
+//                   into two-stage shared-memory rings, one for keys, one for values
+//                                                          -> k_full[stage], v_full[stage]
+//   MMA warp        S = Q.K^T   (tcgen05.mma M=128 N=64,  K=16 x D/16)  -> s_full, k_empty
+//                   O += P.V    (tcgen05.mma M=128 N=D,   K=16 x 4)     -> v_empty, pv_done
 //   softmax warps   thread r owns row r: tcgen05.ld its 64 scores, mask, running max and
 //                   sum in float32 (no shuffles: a row lives in one thread), P as
 //                   bfloat16 back into tensor memory (tcgen05.st, over the scores it
@@ -98,6 +99,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     }
     return false;
 }
+// The same wait for hand-overs on the critical path of a tile (scores ready, P ready):
+// test_wait does not suspend the thread, so the waiter sees the phase within tens of
+// cycles; bounded by SPIN_LIMIT * 64 polls (a poll that does not suspend is ~60 times
+// shorter).
+__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < SPIN_LIMIT * 64u; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
 // Shared-memory matrix descriptor, 128-byte swizzle, rows of 128 bytes in groups of 8
 // (1024 bytes).  lbo16: leading byte offset >> 4 (distance of 64-element panels for an
 // operand that is contiguous along M/N; unused for K-major operands).
@@ -167,9 +185,11 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     const int* __restrict__ ctx_len, const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
     int H, int Hkv, int ps, int box_rows, float scale_log2, int window, int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);    // [2]
-    uint64_t* kv_empty = kv_full + 2;                                   // [2]
-    uint64_t* s_full = kv_empty + 2;                                    // [2]
+    uint64_t* k_full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);     // [2] per K/V stage
+    uint64_t* k_empty = k_full + 2;                                     // [2]
+    uint64_t* v_full = k_empty + 2;                                     // [2]
+    uint64_t* v_empty = v_full + 2;                                     // [2]
+    uint64_t* s_full = v_empty + 2;                                     // [2] per score buffer
     uint64_t* p_full = s_full + 2;                                      // [2], one per score buffer
     uint64_t* pv_done = p_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
@@ -203,8 +223,10 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     const int ntiles = (kend - kbeg + BN - 1) / BN;
 
     if (threadIdx.x == 0) {
-        mbar_init(&kv_full[0], 1); mbar_init(&kv_full[1], 1);
-        mbar_init(&kv_empty[0], 1); mbar_init(&kv_empty[1], 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+            mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+        }
         mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
         mbar_init(&p_full[0], 128); mbar_init(&p_full[1], 128);
         mbar_init(pv_done, 1);
@@ -245,36 +267,40 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
 
     if (warp == 0) {
         // ---------------------------------------------------------------- loader
-        if (lane == 0) {
-            const int boxes = BN / box_rows;
-            const bool pow2 = true;                       // the launcher only takes such page sizes
-            const int shift = __ffs(ps) - 1;
-            (void)pow2;
-            for (int j = 0; j < ntiles; ++j) {
-                const int st = j & 1;
-                if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1)) { gave_up(status, 0x101, 0, j, ntiles); break; }
-                const int k0 = kbeg + j * BN;
-                int rows[8];
-                uint32_t bytes = 0;
-                for (int b = 0; b < boxes; ++b) {
-                    const int kp = k0 + b * box_rows;
-                    int page = -1;
-                    if (kp < kend) page = table[kp >> shift];
-                    rows[b] = page >= 0 ? (page * Hkv + kvh) * ps + (kp & (ps - 1)) : -1;
-                    if (page >= 0) bytes += (uint32_t)box_rows * 128u * PANELS * 2u;
-                }
-                if (bytes) mbar_expect_tx(&kv_full[st], bytes); else mbar_arrive(&kv_full[st]);
-                for (int b = 0; b < boxes; ++b) {
-                    if (rows[b] < 0) continue;
-#pragma unroll
-                    for (int p = 0; p < PANELS; ++p) {
-                        tma_load_2d(smem + OFF_K + st * KV_TILE_BYTES + p * KV_PANEL_BYTES + b * box_rows * 128,
-                                    &map_k, &kv_full[st], p * 64, rows[b]);
-                        tma_load_2d(smem + OFF_V + st * KV_TILE_BYTES + p * KV_PANEL_BYTES + b * box_rows * 128,
-                                    &map_v, &kv_full[st], p * 64, rows[b]);
-                    }
+        // The keys of a tile are free again when its Q.K^T has run, the values when its P.V
+        // has: K of tile j + 2 is requested two softmax periods before it is needed, V one.
+        // Lane b looks up the page of box b and issues its copies (a copy costs the issuing
+        // warp 60 to 160 cycles, so they are spread over lanes).
+        const int boxes = BN / box_rows;
+        const int shift = __ffs(ps) - 1;                  // the launcher only takes powers of two
+        auto load_tile = [&](const CUtensorMap* map, unsigned char* dst, uint64_t* bar, int j) {
+            int row = -1;
+            if (lane < boxes) {
+                const int kp = kbeg + j * BN + lane * box_rows;
+                if (kp < kend) {
+                    const int page = table[kp >> shift];
+                    if (page >= 0) row = (page * Hkv + kvh) * ps + (kp & (ps - 1));
                 }
             }
+            const unsigned got = __ballot_sync(0xffffffffu, row >= 0);
+            if (lane == 0) {
+                const uint32_t bytes = (uint32_t)__popc(got) * (uint32_t)box_rows * 128u * PANELS;
+                if (bytes) mbar_expect_tx(bar, bytes); else mbar_arrive(bar);
+            }
+            __syncwarp();
+            if (row >= 0) {
+#pragma unroll
+                for (int p = 0; p < PANELS; ++p)
+                    tma_load_2d(dst + p * KV_PANEL_BYTES + lane * box_rows * 128, map, bar, p * 64, row);
+            }
+        };
+        for (int j = 0; j < ntiles; ++j) {
+            const int st = j & 1;
+            const uint32_t parity = ((j >> 1) & 1) ^ 1;
+            if (!mbar_wait(&k_empty[st], parity)) { if (lane == 0) gave_up(status, 0x101, 0, j, ntiles); break; }
+            load_tile(&map_k, smem + OFF_K + st * KV_TILE_BYTES, &k_full[st], j);
+            if (!mbar_wait(&v_empty[st], parity)) { if (lane == 0) gave_up(status, 0x102, 0, j, ntiles); break; }
+            load_tile(&map_v, smem + OFF_V + st * KV_TILE_BYTES, &v_full[st], j);
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
@@ -288,7 +314,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
             // tile t - 2; its P.V has been issued before)
             auto issue_qk = [&](int t) -> bool {
                 const int st = t & 1;
-                if (!mbar_wait(&kv_full[st], (t >> 1) & 1)) { gave_up(status, 0x201, 1, t, ntiles); return false; }
+                if (!mbar_wait(&k_full[st], (t >> 1) & 1)) { gave_up(status, 0x201, 1, t, ntiles); return false; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t k_addr = smem_u32(smem + OFF_K + st * KV_TILE_BYTES);
 #pragma unroll
@@ -299,13 +325,15 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
                                   umma_desc(k_addr + p * KV_PANEL_BYTES + kk * 32, 1), idesc_qk,
                                   (p > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(&s_full[st]);
+                umma_commit(&k_empty[st]);                  // the keys may be replaced
                 return true;
             };
             bool ok = issue_qk(0);
             if (ok && ntiles > 1) ok = issue_qk(1);
             for (int j = 0; j < ntiles && ok; ++j) {
                 const int st = j & 1;
-                if (!mbar_wait(&p_full[st], (j >> 1) & 1)) { gave_up(status, 0x202, 1, j, ntiles); break; }
+                if (!mbar_spin(&p_full[st], (j >> 1) & 1)) { gave_up(status, 0x202, 1, j, ntiles); break; }
+                if (!mbar_wait(&v_full[st], (j >> 1) & 1)) { gave_up(status, 0x203, 1, j, ntiles); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t v_addr = smem_u32(smem + OFF_V + st * KV_TILE_BYTES);
 #pragma unroll
@@ -313,7 +341,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
                     umma_bf16_ts(tmem + O_COL, tmem + S_COL + 64 * st + kk * 8,
                                  umma_desc(v_addr + kk * 16 * 128, KV_PANEL_BYTES >> 4), idesc_pv,
                                  (j > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(&kv_empty[st]);
+                umma_commit(&v_empty[st]);                  // the values may be replaced
                 umma_commit(pv_done);
                 // the scores of tile j + 2 go where P of tile j was: issued after P.V of tile j
                 // (the tensor core executes in issue order), while the softmax of j + 1 runs
@@ -329,7 +357,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < ntiles && ok; ++j) {
-            if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1)) { if (lane == 0) gave_up(status, 0x301, 2, j, ntiles); ok = false; break; }
+            if (!mbar_spin(&s_full[j & 1], (j >> 1) & 1)) { if (lane == 0) gave_up(status, 0x301, 2, j, ntiles); ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t raw[2][32];
             tmem_ld32(tmem + lane_base + S_COL + 64 * (j & 1), raw[0]);
