@@ -6,11 +6,13 @@
 // them), so the g query heads of a group share every key/value tile.  Per 64-key
 // tile, with both accumulators in tensor memory (TMEM):
 //
-//   loader warp     TMA tensor copies (128-byte swizzle) of the tile's pages of K and of V
-//                   into two-stage shared-memory rings, one for keys, one for values
+//   loader warps    TMA tensor copies (128-byte swizzle) of the tile's pages of K (warp 0)
+//                   and of V (warp 6) into two-stage shared-memory rings of their own
 //                                                          -> k_full[stage], v_full[stage]
-//   MMA warp        S = Q.K^T   (tcgen05.mma M=128 N=64,  K=16 x D/16)  -> s_full, k_empty
-//                   O += P.V    (tcgen05.mma M=128 N=D,   K=16 x 4)     -> v_empty, pv_done
+//   MMA warp        S = Q.K^T   (tcgen05.mma M=128 N=64,  K=16 x D/16)  -> s_full (scores ready,
+//                                                                          keys may be replaced)
+//                   O += P.V    (tcgen05.mma M=128 N=D,   K=16 x 4)     -> pv_done (values may
+//                                                                          be replaced, O is final)
 //   softmax warps   thread r owns row r: tcgen05.ld its 64 scores, mask, running max and
 //                   sum in float32 (no shuffles: a row lives in one thread), P as
 //                   bfloat16 back into tensor memory (tcgen05.st, over the scores it
@@ -46,7 +48,8 @@ namespace {
 constexpr int D = SLB_HEAD_DIM;
 constexpr int PANELS = D / 64;                 // 64-element (128-byte) column panels
 constexpr int BM = 128, BN = 64;
-constexpr int THREADS = 192;                   // warp 0 loader, warp 1 MMA, warps 2..5 softmax
+constexpr int THREADS = 224;                   // warp 0 loads keys, 1 issues the MMAs, 2..5 softmax,
+                                               // 6 loads values
 constexpr int TMEM_COLS = 256;                 // two S buffers at columns 0..127, O at 128..128+D-1
 constexpr int S_COL = 0, O_COL = 128;          // S buffer b sits at S_COL + 64 * b
 constexpr int Q_BYTES = PANELS * BM * 128;
@@ -173,6 +176,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32
           "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
         : "memory");
 }
+// 2^x in one MUFU instruction (exp2f adds a range fix-up around it; the probabilities
+// here are rounded to bfloat16 anyway, and -inf gives 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -185,14 +195,15 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     const int* __restrict__ ctx_len, const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
     int H, int Hkv, int ps, int box_rows, float scale_log2, int window, int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    uint64_t* k_full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);     // [2] per K/V stage
-    uint64_t* k_empty = k_full + 2;                                     // [2]
-    uint64_t* v_full = k_empty + 2;                                     // [2]
-    uint64_t* v_empty = v_full + 2;                                     // [2]
-    uint64_t* s_full = v_empty + 2;                                     // [2] per score buffer
+    // All barriers come in pairs indexed by tile parity.  s_full[b]: Q.K^T of a tile is done
+    // (its scores are ready and its keys may be replaced); pv_done[b]: its P.V is done (its
+    // values may be replaced, the accumulator may be rescaled or read).
+    uint64_t* k_full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);     // [2]
+    uint64_t* v_full = k_full + 2;                                      // [2]
+    uint64_t* s_full = v_full + 2;                                      // [2]
     uint64_t* p_full = s_full + 2;                                      // [2], one per score buffer
-    uint64_t* pv_done = p_full + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+    uint64_t* pv_done = p_full + 2;                                     // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
 
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -224,12 +235,12 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
-            mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+            mbar_init(&k_full[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&pv_done[i], 1);
         }
         mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
         mbar_init(&p_full[0], 128); mbar_init(&p_full[1], 128);
-        mbar_init(pv_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -241,7 +252,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     for (int i = threadIdx.x; i < 4 * KV_TILE_BYTES / 16; i += THREADS)
         reinterpret_cast<uint4*>(smem + OFF_K)[i] = make_uint4(0, 0, 0, 0);
     // Q tile: the softmax threads copy their rows into the swizzled operand layout
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 6) {
         const int r = (warp & 3) * 32 + lane;
         unsigned char* qs = smem + OFF_Q;
         if (r < nrows) {
@@ -265,42 +276,52 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 0) {
-        // ---------------------------------------------------------------- loader
-        // The keys of a tile are free again when its Q.K^T has run, the values when its P.V
-        // has: K of tile j + 2 is requested two softmax periods before it is needed, V one.
-        // Lane b looks up the page of box b and issues its copies (a copy costs the issuing
-        // warp 60 to 160 cycles, so they are spread over lanes).
+    if (warp == 0 || warp == 6) {
+        // ---------------------------------------------------------------- loaders
+        // Warp 0 fetches the keys, warp 6 the values, each through its own two-stage ring:
+        // the keys of a tile may be replaced when its Q.K^T has run (two softmax periods
+        // before the new ones are needed), the values when its P.V has.  Lane b looks up the
+        // page of box b, one tile ahead of its use (a dependent global load), and issues the
+        // box's copies (a copy costs the issuing warp 60 to 160 cycles: spread over lanes).
+        const bool keys = warp == 0;
+        const CUtensorMap* map = keys ? &map_k : &map_v;
+        unsigned char* ring = smem + (keys ? OFF_K : OFF_V);
+        uint64_t* full = keys ? k_full : v_full;
+        uint64_t* freed = keys ? s_full : pv_done;
         const int boxes = BN / box_rows;
         const int shift = __ffs(ps) - 1;                  // the launcher only takes powers of two
-        auto load_tile = [&](const CUtensorMap* map, unsigned char* dst, uint64_t* bar, int j) {
+        auto lookup = [&](int j) {                        // first cache row of this lane's box, or -1
             int row = -1;
-            if (lane < boxes) {
+            if (lane < boxes && j < ntiles) {
                 const int kp = kbeg + j * BN + lane * box_rows;
                 if (kp < kend) {
                     const int page = table[kp >> shift];
                     if (page >= 0) row = (page * Hkv + kvh) * ps + (kp & (ps - 1));
                 }
             }
+            return row;
+        };
+        int row = lookup(0);
+        for (int j = 0; j < ntiles; ++j) {
+            const int st = j & 1;
+            const int next_row = lookup(j + 1);
+            if (!mbar_wait(&freed[st], ((j >> 1) & 1) ^ 1)) {
+                if (lane == 0) gave_up(status, keys ? 0x101 : 0x102, 0, j, ntiles);
+                break;
+            }
             const unsigned got = __ballot_sync(0xffffffffu, row >= 0);
             if (lane == 0) {
                 const uint32_t bytes = (uint32_t)__popc(got) * (uint32_t)box_rows * 128u * PANELS;
-                if (bytes) mbar_expect_tx(bar, bytes); else mbar_arrive(bar);
+                if (bytes) mbar_expect_tx(&full[st], bytes); else mbar_arrive(&full[st]);
             }
             __syncwarp();
             if (row >= 0) {
 #pragma unroll
                 for (int p = 0; p < PANELS; ++p)
-                    tma_load_2d(dst + p * KV_PANEL_BYTES + lane * box_rows * 128, map, bar, p * 64, row);
+                    tma_load_2d(ring + st * KV_TILE_BYTES + p * KV_PANEL_BYTES + lane * box_rows * 128, map,
+                                &full[st], p * 64, row);
             }
-        };
-        for (int j = 0; j < ntiles; ++j) {
-            const int st = j & 1;
-            const uint32_t parity = ((j >> 1) & 1) ^ 1;
-            if (!mbar_wait(&k_empty[st], parity)) { if (lane == 0) gave_up(status, 0x101, 0, j, ntiles); break; }
-            load_tile(&map_k, smem + OFF_K + st * KV_TILE_BYTES, &k_full[st], j);
-            if (!mbar_wait(&v_empty[st], parity)) { if (lane == 0) gave_up(status, 0x102, 0, j, ntiles); break; }
-            load_tile(&map_v, smem + OFF_V + st * KV_TILE_BYTES, &v_full[st], j);
+            row = next_row;
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
@@ -309,23 +330,26 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
                                       ((uint32_t)(BM >> 4) << 24);
             const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                       ((uint32_t)(D >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            const uint32_t q_addr = smem_u32(smem + OFF_Q);
+            // operand descriptors are built once; a step along K or to another panel adds its
+            // byte offset / 16 to the address field
+            const uint64_t q_desc = umma_desc(smem_u32(smem + OFF_Q), 1);
+            const uint64_t k_desc0 = umma_desc(smem_u32(smem + OFF_K), 1);
+            const uint64_t v_desc0 = umma_desc(smem_u32(smem + OFF_V), KV_PANEL_BYTES >> 4);
+            constexpr uint64_t STAGE_STEP = KV_TILE_BYTES >> 4;      // to the second stage
             // S = Q.K^T of tile t into score buffer t & 1 (which held the scores and then P of
             // tile t - 2; its P.V has been issued before)
             auto issue_qk = [&](int t) -> bool {
                 const int st = t & 1;
-                if (!mbar_wait(&k_full[st], (t >> 1) & 1)) { gave_up(status, 0x201, 1, t, ntiles); return false; }
+                if (!mbar_spin(&k_full[st], (t >> 1) & 1)) { gave_up(status, 0x201, 1, t, ntiles); return false; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t k_addr = smem_u32(smem + OFF_K + st * KV_TILE_BYTES);
 #pragma unroll
                 for (int p = 0; p < PANELS; ++p)
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)          // 16 elements of D = 32 bytes per step
-                        umma_bf16(tmem + S_COL + 64 * st, umma_desc(q_addr + p * (BM * 128) + kk * 32, 1),
-                                  umma_desc(k_addr + p * KV_PANEL_BYTES + kk * 32, 1), idesc_qk,
+                        umma_bf16(tmem + S_COL + 64 * st, q_desc + ((p * (BM * 128) + kk * 32) >> 4),
+                                  k_desc0 + st * STAGE_STEP + ((p * KV_PANEL_BYTES + kk * 32) >> 4), idesc_qk,
                                   (p > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(&s_full[st]);
-                umma_commit(&k_empty[st]);                  // the keys may be replaced
                 return true;
             };
             bool ok = issue_qk(0);
@@ -333,16 +357,14 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
             for (int j = 0; j < ntiles && ok; ++j) {
                 const int st = j & 1;
                 if (!mbar_spin(&p_full[st], (j >> 1) & 1)) { gave_up(status, 0x202, 1, j, ntiles); break; }
-                if (!mbar_wait(&v_full[st], (j >> 1) & 1)) { gave_up(status, 0x203, 1, j, ntiles); break; }
+                if (!mbar_spin(&v_full[st], (j >> 1) & 1)) { gave_up(status, 0x203, 1, j, ntiles); break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t v_addr = smem_u32(smem + OFF_V + st * KV_TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk)              // 16 keys per step: P 8 columns, V 16 rows
                     umma_bf16_ts(tmem + O_COL, tmem + S_COL + 64 * st + kk * 8,
-                                 umma_desc(v_addr + kk * 16 * 128, KV_PANEL_BYTES >> 4), idesc_pv,
+                                 v_desc0 + st * STAGE_STEP + ((kk * 16 * 128) >> 4), idesc_pv,
                                  (j > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(&v_empty[st]);                  // the values may be replaced
-                umma_commit(pv_done);
+                umma_commit(&pv_done[st]);
                 // the scores of tile j + 2 go where P of tile j was: issued after P.V of tile j
                 // (the tensor core executes in issue order), while the softmax of j + 1 runs
                 if (j + 2 < ntiles) ok = issue_qk(j + 2);
@@ -399,15 +421,15 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
             for (int h = 0; h < 2; ++h)
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float p0 = exp2f(fmaf(__uint_as_float(raw[h][i]), scale_log2, -m_use));
-                    const float p1 = exp2f(fmaf(__uint_as_float(raw[h][i + 1]), scale_log2, -m_use));
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(raw[h][i]), scale_log2, -m_use));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(raw[h][i + 1]), scale_log2, -m_use));
                     sm[(i >> 1) & 3] += p0 + p1;
                     packed[h * 16 + i / 2] = pack2(p0, p1);
                 }
             l = l * alpha + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
                 // the accumulator is rescaled (rarely): P.V of the previous tile must be done
-                if (!mbar_wait(pv_done, (j - 1) & 1)) { if (lane == 0) gave_up(status, 0x302, 2, j, ntiles); ok = false; break; }
+                if (!mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { if (lane == 0) gave_up(status, 0x302, 2, j, ntiles); ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int c0 = 0; c0 < D; c0 += 32) {
@@ -426,7 +448,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
             mbar_arrive(&p_full[j & 1]);
         }
         if (ok) {
-            if (!mbar_wait(pv_done, (ntiles - 1) & 1)) { if (lane == 0) gave_up(status, 0x303, 2, ntiles, ntiles); ok = false; }
+            if (!mbar_wait(&pv_done[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1)) { if (lane == 0) gave_up(status, 0x303, 2, ntiles, ntiles); ok = false; }
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         pdl_launch_dependents();
