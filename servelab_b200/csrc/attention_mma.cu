@@ -231,10 +231,11 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
     bf16* stage0 = Qs + BM * LDS;                          // 2 x (K tile | V tile)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kvh = blockIdx.y;
-    // tiles are listed in position order; the last ones see the most keys, so they
-    // are started first
-    const int tile = gridDim.x - 1 - blockIdx.x;
+    // tiles are listed in position order; the last ones see the most keys, so they are
+    // started first, all kv heads of a tile together (blocks start in the order of their
+    // linear index)
+    const int kvh = blockIdx.x % Hkv;
+    const int tile = (int)(gridDim.x / Hkv) - 1 - (int)(blockIdx.x / Hkv);
     const int s = tile_seq[tile];
     const int row0 = tile_row0[tile];
     const int g = H / Hkv;
@@ -565,7 +566,7 @@ int slb_prefill_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf1
         return SLB_ERR_BAD_ARG;
     if (ldq % 8 || ldo % 8 || ((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)out) % 16)
         return SLB_ERR_BAD_ARG;                            // 16-byte copies
-    if (Hkv > 65535) return SLB_ERR_TOO_LARGE;
+    if ((long long)num_tiles * Hkv > 0x7fffffffll) return SLB_ERR_TOO_LARGE;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel,
@@ -574,7 +575,7 @@ int slb_prefill_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf1
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return slb_launch(prefill_attention_kernel, dim3(num_tiles, Hkv), dim3(NTHREADS), PREFILL_SMEM, st,
+    return slb_launch(prefill_attention_kernel, dim3((unsigned)num_tiles * Hkv), dim3(NTHREADS), PREFILL_SMEM, st,
                       q, ldq, kc, vc, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq,
                       tile_row0, H, Hkv, ps, scale * 1.4426950408889634f, window);
 }

@@ -65,13 +65,13 @@ constexpr float RESCALE_THRESHOLD = 8.f;       // log2 of the largest probabilit
 
 __device__ int tc_attn_status = 0;
 // Where bounded waits gave up last, four ints per role (loader, MMA issuer, softmax):
-// code, block x | block y << 16, key tile, key tiles of the block.
+// code, block, key tile, key tiles of the block.
 __device__ int tc_attn_where[12] = {0};
 
 __device__ __forceinline__ void gave_up(int* status, int code, int role, int tile, int ntiles) {
     atomicCAS(status, 0, code);
     tc_attn_where[role * 4 + 0] = code;
-    tc_attn_where[role * 4 + 1] = (int)(blockIdx.x | (blockIdx.y << 16));
+    tc_attn_where[role * 4 + 1] = (int)blockIdx.x;
     tc_attn_where[role * 4 + 2] = tile;
     tc_attn_where[role * 4 + 3] = ntiles;
 }
@@ -207,9 +207,11 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tc_kernel(
 
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // the last tiles of a prompt see the most keys: start them first
-    const int tile = gridDim.x - 1 - blockIdx.x;
-    const int kvh = blockIdx.y;
+    // Blocks are handed out in the order of their linear index: tile by tile from the last
+    // (most keys) to the first, all kv heads of a tile together, so that no head's long
+    // tiles start late.
+    const int kvh = blockIdx.x % Hkv;
+    const int tile = (int)(gridDim.x / Hkv) - 1 - (int)(blockIdx.x / Hkv);
     const int s = tile_seq[tile];
     const int row0 = tile_row0[tile];
     const int g = H / Hkv;
@@ -510,7 +512,7 @@ int slb_prefill_attention_tc_bf16(const bf16* q, int ldq, const bf16* kc, const 
     if (!slb_prefill_attention_tc_supported(ps, H / Hkv)) return SLB_ERR_BAD_ARG;
     if (ldq % 8 || ldo % 8 || ((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)out) % 16)
         return SLB_ERR_BAD_ARG;
-    if (Hkv > 65535) return SLB_ERR_TOO_LARGE;
+    if ((long long)num_tiles * Hkv > 0x7fffffffll) return SLB_ERR_TOO_LARGE;
     const int box_rows = ps < BN ? ps : BN;
     CUtensorMap map_k, map_v;
     const long long rows = (long long)num_pages * Hkv * ps;
@@ -528,7 +530,7 @@ int slb_prefill_attention_tc_bf16(const bf16* q, int ldq, const bf16* kc, const 
     int* status = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&status, tc_attn_status);
     if (e != cudaSuccess) return (int)e;
-    return slb_launch(prefill_attention_tc_kernel, dim3(num_tiles, Hkv), dim3(THREADS), TC_ATTN_SMEM, st, q, ldq,
+    return slb_launch(prefill_attention_tc_kernel, dim3((unsigned)num_tiles * Hkv), dim3(THREADS), TC_ATTN_SMEM, st, q, ldq,
                       map_k, map_v, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq, tile_row0, H, Hkv,
                       ps, box_rows, scale * 1.4426950408889634f, window, status);
 }

@@ -200,15 +200,14 @@ def prefill_attention_tc_status(head_dim: int, reset: bool = False) -> int:
 
 def prefill_attention_tc_where(head_dim: int) -> dict:
     """Where the roles of the tcgen05 prefill attention gave up a bounded wait last:
-    per role (code, block x, block y, key tile, key tiles of the block); zeros if never."""
+    per role (code, block, key tile, key tiles of the block); zeros if never."""
     import ctypes
     buf = (ctypes.c_int * 12)()
     L.attention(head_dim).slb_prefill_attention_tc_where(ctypes.cast(buf, ctypes.c_void_p))
     out = {}
     for i, role in enumerate(("loader", "mma", "softmax")):
         code, block, tile, ntiles = buf[4 * i:4 * i + 4]
-        out[role] = {"code": hex(code), "block": (block & 0xffff, block >> 16), "tile": tile,
-                     "tiles": ntiles}
+        out[role] = {"code": hex(code), "block": block, "tile": tile, "tiles": ntiles}
     return out
 
 
