@@ -160,8 +160,8 @@ def main(argv=None) -> int:
             linear_ops.skinny_max_tokens = int(value)
         elif name == "tc_max_tokens":
             linear_ops.tc_max_tokens = int(value)
-        elif name == "defer_split_sums":
-            linear_ops.defer_split_sums = bool(int(value))
+        elif name in ("defer_rope", "defer_norm"):
+            linear_ops.defer_split_sums[name[6:]] = bool(int(value))
         elif name == "tc_max_stages":
             K.tc_max_stages = int(value)
         elif name == "decode_ctas_per_sm":

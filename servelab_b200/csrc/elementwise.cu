@@ -144,6 +144,81 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
     }
 }
 
+// ---- the same norm for an update that arrives as K-split partial sums (decode steps) ----
+// A step of few tokens has few rows: a row is shared by a cluster of NORM_CLUSTER blocks
+// (a column range each), so that adding the partial sums is spread over the GPU.  Every
+// block reduces its own sum of squares, publishes it in its shared memory and reads the
+// others' through the cluster's distributed shared memory, in the order of the ranks
+// (the row's result depends on h and the cluster size only, never on the batch).
+constexpr int NORM_CLUSTER = 8;
+
+__device__ __forceinline__ unsigned cluster_ctarank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_arrive() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float load_cluster_shared(const float* mine, unsigned rank) {
+    const uint32_t local = (uint32_t)__cvta_generic_to_shared(mine);
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+// grid (NORM_CLUSTER, rows), cluster (NORM_CLUSTER, 1, 1); chunk: columns per block (a
+// multiple of 4, at most 4 * blockDim.x); h % 4 == 0.
+template <typename TO>
+__global__ void add_rmsnorm_parts_cluster_kernel(float* __restrict__ resid,
+                                                 const float* __restrict__ parts, int nparts,
+                                                 size_t part_stride, const float* __restrict__ pbias,
+                                                 const float* __restrict__ weight, TO* __restrict__ out,
+                                                 const int* __restrict__ row_map, int h, int chunk,
+                                                 float eps) {
+    __shared__ float scratch[33];
+    __shared__ float my_ss;
+    pdl_launch_dependents();
+    pdl_wait();
+    const unsigned rank = cluster_ctarank();
+    const int r = blockIdx.y;
+    const int src = row_map ? row_map[r] : r;
+    const int i = (int)rank * chunk + threadIdx.x * 4;
+    const bool active = (int)threadIdx.x * 4 < chunk && i < h;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (active) {
+        float* x = resid + (size_t)src * h;
+        v = load4(x + i);
+        const float4 dv = delta4<float>(nullptr, parts + (size_t)src * h, nparts, part_stride, pbias, i);
+        v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+        if (row_map == nullptr) store4(x + i, v);          // the stream is updated in place
+    }
+    float ss = v.x * v.x;
+    ss += v.y * v.y;
+    ss += v.z * v.z;
+    ss += v.w * v.w;
+    ss = block_sum(ss, scratch);
+    if (threadIdx.x == 0) my_ss = ss;
+    cluster_arrive();
+    cluster_wait();
+    float total = 0.f;
+#pragma unroll
+    for (unsigned c = 0; c < NORM_CLUSTER; ++c) total += load_cluster_shared(&my_ss, c);
+    cluster_arrive();                                      // this block has read the others' sums
+    const float rstd = 1.0f / sqrtf(total / (float)h + eps);
+    if (active) {
+        const float4 w = load4(weight + i);
+        store4(out + (size_t)r * h + i, make_float4(v.x * rstd * w.x, v.y * rstd * w.y,
+                                                    v.z * rstd * w.z, v.w * rstd * w.w));
+    }
+    cluster_wait();                                        // nobody still reads this block's sum
+}
+
 // out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(z) = z / (1 + exp(-z)), in float32.
 // V elements per thread and step: 8 (bfloat16 with inter, ld_gu and ld_out multiples of 8:
 // 16-byte accesses), 4 (multiples of 4) or 1.
@@ -263,6 +338,27 @@ int slb_add_rmsnorm_bf16(float* resid, const bf16* delta, const float* weight, b
 int slb_add_rmsnorm_parts_bf16(float* resid, const float* parts, int nparts, long long part_stride,
                                const float* pbias, const float* weight, bf16* out,
                                const int* row_map, int rows, int h, float eps, cudaStream_t st) {
+    if (rows <= 0) return 0;
+    const int chunk = ((h / 4 + NORM_CLUSTER - 1) / NORM_CLUSTER) * 4;     // columns per block
+    if (nparts > 0 && parts != nullptr && h > 0 && h % 4 == 0 && part_stride % 4 == 0 &&
+        chunk / 4 <= 1024 && rows <= 65535) {
+        int threads = (chunk / 4 + 31) / 32 * 32;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(NORM_CLUSTER, rows);
+        cfg.blockDim = dim3(threads);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = NORM_CLUSTER;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = slb_pdl_enabled ? 2 : 1;
+        return (int)cudaLaunchKernelEx(&cfg, add_rmsnorm_parts_cluster_kernel<bf16>, resid, parts, nparts,
+                                       (size_t)part_stride, pbias, weight, out, row_map, h, chunk, eps);
+    }
     return launch_add_rmsnorm<bf16, bf16>(resid, nullptr, parts, nparts, part_stride, pbias, weight,
                                           out, row_map, rows, h, eps, st);
 }

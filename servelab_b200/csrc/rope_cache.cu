@@ -17,10 +17,9 @@
 // rotation pair (i, i + rot/2); the slots after that are pairs of neighbouring
 // elements beyond the rotary part, which pass through.  Thread (i, lane-of-heads)
 // computes sin/cos of its slot once and walks the heads with them.
-template <typename T, bool PARTS>
+template <typename T>
 __global__ void qkv_rope_cache_kernel(
-    const T* __restrict__ qkv, int ld_qkv, const float* __restrict__ parts, int nparts,
-    size_t part_stride, const float* __restrict__ bias,
+    const T* __restrict__ qkv, int ld_qkv, const float* __restrict__ bias,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
     const int* __restrict__ block_table, int max_pages, int page_size,
     const float* __restrict__ inv_freq, int rotary_dim,
@@ -50,25 +49,13 @@ __global__ void qkv_rope_cache_kernel(
         have_page = page >= 0;                         // no page: nothing may be written
         kv_base = ((size_t)(have_page ? page : 0) * Hkv * page_size + pos % page_size) * D;
     }
-    // the projection arrives either as one tensor or as float32 partial sums
-    // [nparts][T][ld_qkv] of a product split along K (added in order)
-    const T* x = qkv ? qkv + (size_t)t * ld_qkv : nullptr;
-    const float* px = nparts > 0 ? parts + (size_t)t * ld_qkv : nullptr;
+    const T* x = qkv + (size_t)t * ld_qkv;
     const int heads = write ? H + 2 * Hkv : H;
     for (int j = head_lane; j < heads; j += head_lanes) {
         const bool is_v = j >= H + Hkv;
         const int a = is_v ? c0 : e0, b = is_v ? c1 : e1;
         const size_t off = (size_t)j * D;
-        float va = 0.f, vb = 0.f;
-        if (PARTS) {
-            for (int p = 0; p < nparts; ++p) {
-                va += px[p * part_stride + off + a];
-                vb += px[p * part_stride + off + b];
-            }
-        } else {
-            va = to_float(x[off + a]);
-            vb = to_float(x[off + b]);
-        }
+        float va = to_float(x[off + a]), vb = to_float(x[off + b]);
         if (bias) { va += bias[off + a]; vb += bias[off + b]; }
         if (rot && !is_v) {
             const float ra = va * cs - vb * sn;
@@ -86,6 +73,58 @@ __global__ void qkv_rope_cache_kernel(
         dst[a] = from_float<T>(va);
         dst[b] = from_float<T>(vb);
     }
+}
+
+// The projection as float32 partial sums [nparts][T][ld_qkv] of a product split along K
+// (decode steps): one block per (head, token), so that a step of few tokens still fills
+// the GPU; thread i owns slot i of the head as in the kernel above and adds the parts in
+// their order.
+template <typename T>
+__global__ void qkv_rope_cache_parts_kernel(
+    const float* __restrict__ parts, int nparts, size_t part_stride, int ld_qkv,
+    const float* __restrict__ bias, const int* __restrict__ positions,
+    const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int max_pages,
+    int page_size, const float* __restrict__ inv_freq, int rotary_dim,
+    T* __restrict__ q_out, int ld_q, T* __restrict__ k_cache, T* __restrict__ v_cache,
+    int H, int Hkv, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int j = blockIdx.x, t = blockIdx.y, i = threadIdx.x;
+    if (i >= D / 2) return;
+    const int pos = positions[t];
+    const int half = (inv_freq != nullptr) ? rotary_dim >> 1 : 0;
+    const bool is_v = j >= H + Hkv;
+    const bool rot = i < half && !is_v;
+    // the two elements of this slot: a rotation pair, or neighbours that pass through
+    const int a = rot ? i : (is_v ? 2 * i : (i < half ? i : 2 * half + 2 * (i - half)));
+    const int b = rot ? i + half : (is_v ? 2 * i + 1 : (i < half ? i + half : a + 1));
+    const size_t off = (size_t)j * D;
+    const float* px = parts + (size_t)t * ld_qkv + off;
+    float va = 0.f, vb = 0.f;
+    for (int p = 0; p < nparts; ++p) {
+        va += px[p * part_stride + a];
+        vb += px[p * part_stride + b];
+    }
+    if (bias) { va += bias[off + a]; vb += bias[off + b]; }
+    if (rot) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
+        const float ra = va * cs - vb * sn;
+        vb = vb * cs + va * sn;
+        va = ra;
+    }
+    T* dst;
+    if (j < H) {
+        dst = q_out + (size_t)t * ld_q + off;
+    } else {
+        const int page = block_table[(size_t)seq_of_token[t] * max_pages + pos / page_size];
+        if (page < 0) return;                          // no page: nothing may be written
+        const int kvh = is_v ? j - H - Hkv : j - H;
+        dst = (is_v ? v_cache : k_cache) +
+              (((size_t)page * Hkv + kvh) * page_size + pos % page_size) * D;
+    }
+    dst[a] = from_float<T>(va);
+    dst[b] = from_float<T>(vb);
 }
 
 // The same with 16-byte accesses, for layouts whose rotary and pass-through parts are
@@ -217,14 +256,17 @@ static int launch_qkv_rope_cache(const T* qkv, int ld_qkv, const float* parts, i
                           qkv, ld_qkv, bias, positions, seq_of_token, block_table, max_pages, page_size,
                           inv_freq, rotary_dim, q_out, ld_q, k_cache, v_cache, H, Hkv, D);
     }
-    if (nparts > 0)
-        return slb_launch(qkv_rope_cache_kernel<T, true>, dim3(T_), dim3(threads), 0, st, qkv, ld_qkv,
-                          parts, nparts, (size_t)part_stride, bias, positions, seq_of_token,
-                          block_table, max_pages, page_size, inv_freq, rotary_dim, q_out, ld_q,
-                          k_cache, v_cache, H, Hkv, D, slots);
-    return slb_launch(qkv_rope_cache_kernel<T, false>, dim3(T_), dim3(threads), 0, st, qkv, ld_qkv, parts,
-                      nparts, (size_t)part_stride, bias, positions, seq_of_token, block_table, max_pages, page_size, inv_freq,
-                      rotary_dim, q_out, ld_q, k_cache, v_cache, H, Hkv, D, slots);
+    if (nparts > 0) {
+        if (T_ > 65535) return SLB_ERR_TOO_LARGE;
+        const bool write = k_cache != nullptr && v_cache != nullptr;
+        return slb_launch(qkv_rope_cache_parts_kernel<T>, dim3(write ? heads : H, T_),
+                          dim3((D / 2 + 31) / 32 * 32), 0, st, parts, nparts, (size_t)part_stride,
+                          ld_qkv, bias, positions, seq_of_token, block_table, max_pages, page_size,
+                          inv_freq, rotary_dim, q_out, ld_q, k_cache, v_cache, H, Hkv, D);
+    }
+    return slb_launch(qkv_rope_cache_kernel<T>, dim3(T_), dim3(threads), 0, st, qkv, ld_qkv, bias,
+                      positions, seq_of_token, block_table, max_pages, page_size, inv_freq, rotary_dim,
+                      q_out, ld_q, k_cache, v_cache, H, Hkv, D, slots);
 }
 
 extern "C" {

@@ -31,9 +31,13 @@ def _skinny_ok(x, w, M):
 
 
 tc_max_tokens = 16         # up to this many tokens the tcgen05 weight-streaming kernel runs
-defer_split_sums = False   # hand K-split partial sums to the consuming kernel instead of
-                           # reducing them in a kernel of their own (measured slower: the
-                           # consumers run few blocks and are bound by latency)
+# Hand the K-split partial sums of a decode-step product to the kernel that consumes the
+# result instead of reducing them in a kernel of their own, per kind of consumer.  "rope":
+# the q/k/v kernel takes them with one block per (head, token).  "norm": the norm takes
+# them with a cluster of blocks per row.  Each replaces the reduction kernel and the
+# one-block-per-token form of itself (measured at batch 8 / 1 on the 7B shape: 3.31 / 3.13
+# ms a step without, 3.28 / 3.10 with "rope", 3.22 / 3.04 with both).
+defer_split_sums = {"rope": True, "norm": True}
 
 
 # Which weights follow which in a forward pass, by address: a hint with which the tcgen05
@@ -65,10 +69,10 @@ def _tc_ok(x, w, M):
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           out_dtype: Optional[torch.dtype] = None, defer_sum: bool = False):
-    """``defer_sum``: the caller hands the result to a kernel that accepts a
-    ``SplitSum`` (partial sums of a K-split product); it may then get one instead
-    of a tensor."""
+           out_dtype: Optional[torch.dtype] = None, consumer: Optional[str] = None):
+    """``consumer`` ("rope" or "norm"): the caller hands the result to a kernel of that
+    kind, which accepts a ``SplitSum`` (partial sums of a K-split product); it may then
+    get one instead of a tensor."""
     M, Kd = x.shape
     N = w.shape[0]
     out_dtype = out_dtype or x.dtype
@@ -80,7 +84,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     if M == 0:
         return torch.empty((0, N), dtype=out_dtype, device=x.device)
     if _tc_ok(x, w, M):
-        return K.gemm_tc_decode(x, w, None, bias, defer_sum=defer_sum and defer_split_sums,
+        return K.gemm_tc_decode(x, w, None, bias, defer_sum=defer_split_sums.get(consumer, False),
                                 out_dtype=out_dtype, next_weight=_next_weight(w))
     if _skinny_ok(x, w, M):
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)

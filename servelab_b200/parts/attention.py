@@ -80,7 +80,7 @@ class PagedAttention(Mixer):
     def forward(self, ctx, x, cache, owns_cache):
         s = self.spec
         T = x.shape[0]
-        qkv = linear(x, self.w_qkv, defer_sum=True)       # the next kernel adds K-split parts
+        qkv = linear(x, self.w_qkv, consumer="rope")       # the next kernel may add K-split parts
         q = torch.empty((T, self.q_size), dtype=x.dtype, device=x.device)
         # (a SplitSum has no dtype of its own; q follows the activations)
         table = ctx.block_tables[cache.group]
@@ -92,4 +92,4 @@ class PagedAttention(Mixer):
         out = torch.empty_like(q)
         A.paged_attention(ctx, q, cache.k, cache.v, out, table, s.num_heads, s.num_kv_heads,
                           s.head_dim, cache.page_size, self.scale, s.window or 0)
-        return linear(out, self.w_o, self.b_o, defer_sum=True)   # consumed by a norm kernel
+        return linear(out, self.w_o, self.b_o, consumer="norm")

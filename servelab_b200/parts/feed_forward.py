@@ -44,4 +44,4 @@ class GatedMLP(FeedForward):
         gu = linear(x, self.w_gate_up)
         act = torch.empty((x.shape[0], self.spec.intermediate_size), dtype=x.dtype, device=x.device)
         K.swiglu(gu, act)
-        return linear(act, self.w_down, defer_sum=True)      # consumed by a norm kernel
+        return linear(act, self.w_down, consumer="norm")

@@ -67,6 +67,42 @@ def test_add_rmsnorm(dtype, h):
     assert (sel.float() - want[rows.long()]).abs().max() <= TOL[dtype] * 4
 
 
+@pytest.mark.parametrize("h", [64, 172, 3584, 150, 8200])
+@pytest.mark.parametrize("rows,nparts", [(1, 2), (9, 5), (3, 11)])
+def test_add_rmsnorm_of_split_sums(h, rows, nparts):
+    """The update as float32 partial sums of a K-split product (+ bias): a cluster of
+    blocks per row where the width allows, one block per row otherwise; whole rows and
+    selected rows."""
+    from servelab_b200.ops.kernels import SplitSum
+    resid = torch.randn(rows, h, device=DEV) * 3
+    parts = torch.randn(nparts, rows, h, device=DEV)
+    bias = torch.randn(h, device=DEV)
+    w = 1 + 0.1 * torch.randn(h, device=DEV)
+    want_resid = resid + parts.sum(0) + bias
+    want = P.rms_norm(want_resid, w, 1e-5)
+    out = torch.empty(rows, h, device=DEV, dtype=torch.bfloat16)
+    r = resid.clone()
+    K().add_rmsnorm(r, SplitSum(parts, bias, torch.bfloat16), w, 1e-5, out)
+    assert (r - want_resid).abs().max() <= 1e-5
+    assert (out.float() - want).abs().max() <= TOL["bfloat16"] * 4
+    again = torch.empty_like(out)
+    r2 = resid.clone()
+    K().add_rmsnorm(r2, SplitSum(parts, bias, torch.bfloat16), w, 1e-5, again)
+    assert torch.equal(again, out) and torch.equal(r2, r)    # deterministic
+    # a row does not depend on the rest of the batch (bit-exact)
+    one = torch.empty(1, h, device=DEV, dtype=torch.bfloat16)
+    K().add_rmsnorm(resid[rows - 1:].clone(), SplitSum(parts[:, rows - 1:].contiguous(), bias, torch.bfloat16),
+                    w, 1e-5, one)
+    assert torch.equal(one[0], out[rows - 1])
+    # selected rows: nothing is written back
+    sel_rows = i32([rows - 1, 0])
+    r3 = resid.clone()
+    sel = torch.empty(2, h, device=DEV, dtype=torch.bfloat16)
+    K().add_rmsnorm(r3, SplitSum(parts, bias, torch.bfloat16), w, 1e-5, sel, sel_rows)
+    assert torch.equal(r3, resid)
+    assert torch.equal(sel[0], out[rows - 1]) and torch.equal(sel[1], out[0])
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("inter", [173, 172, 176, 18944])      # 1, 4 and 8 elements a thread
 def test_swiglu(dtype, inter):
@@ -128,6 +164,18 @@ def test_qkv_rope_cache(dtype, H, Hkv, D, rot):
     K().qkv_rope_cache(qkv, bias, i32(positions), i32(seq), table, ps, inv, rot, q_out, None, None,
                        H, Hkv, D)
     assert float(kc2.abs().max()) == 0
+    if dtype == "bfloat16":
+        # the projection as three float32 partial sums of a K-split product (decode steps)
+        from servelab_b200.ops.kernels import SplitSum
+        p1, p2 = torch.randn_like(qkv.float()), torch.randn_like(qkv.float())
+        parts = torch.stack([p1, p2, qkv.float() - p1 - p2]).contiguous()
+        q3 = torch.empty(T, H * D, device=DEV, dtype=dt)
+        kc3, vc3 = _paged(12, Hkv, ps, D, dt)
+        K().qkv_rope_cache(SplitSum(parts, None, dt), bias, i32(positions), i32(seq), table, ps, inv,
+                           rot, q3, kc3, vc3, H, Hkv, D)
+        assert (q3.float() - q_out.float()).abs().max() <= tol
+        assert (kc3.float() - kc.float()).abs().max() <= tol
+        assert (vc3.float() - vc.float()).abs().max() <= tol
 
 
 # ------------------------------------------------------------------ attention

@@ -523,7 +523,7 @@ def test_feed_forward_with_routing_defined_in_the_test(tmp_path):
 
 def test_split_sums_consumed_by_norm_and_rope_kernels(tmp_path):
     """With ``defer_split_sums`` the tcgen05 product leaves float32 partial sums and the
-    norm / rotary kernels add them; logits must agree with the default path."""
+    norm / rotary kernels add them; logits must agree whichever consumers take them."""
     from servelab_b200.ops import linear as linear_ops
     from servelab_b200.replay import TraceSession
     cfg = dict(H.TINY_B, hidden_size=512, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
@@ -532,13 +532,14 @@ def test_split_sums_consumed_by_norm_and_rope_kernels(tmp_path):
     reqs = {"a": H.random_ids(40, 512, 1), "b": H.random_ids(37, 512, 2)}
     steps = H.trace_bulk_tail(reqs, tail=16)
     outs = {}
+    saved = dict(linear_ops.defer_split_sums)
     for flag in (False, True):
-        linear_ops.defer_split_sums = flag
+        linear_ops.defer_split_sums.update(rope=flag, norm=flag)
         try:
             sess = TraceSession(folder, "bfloat16", H.peak_tokens(steps), page_size=8, max_live=2)
             outs[flag] = H.collect(steps, H.run_session(sess, steps), 512)
         finally:
-            linear_ops.defer_split_sums = False
+            linear_ops.defer_split_sums.update(saved)
     ref = {rid: H.plain_logits(folder, ids) for rid, ids in reqs.items()}
     for rid, ids in reqs.items():
         for pos in range(len(ids)):
