@@ -15,12 +15,23 @@ that finished in this step), generate (:249, outputs in input order), stats
 outputs instead of vanishing; ``max_tokens`` counts all generated tokens also
 across a preemption; prompts are checked against the vocabulary and the
 position limit.
+
+Look-ahead: while every running request is decoding and none can end by its length
+in the current step, the engine launches step N+1 before it reads the tokens of
+step N.  Step N+1 takes its input tokens from the sampler's result on the device,
+so the GPU never waits for the host between two decode steps; the host reads the
+tokens of step N while N+1 runs.  A request that turns out to have ended in step N
+(an EOS or stop token) has run one step too many: that result is dropped (the page
+it wrote is already given back; later steps come later on the stream).  ``step()``
+still returns the requests that finished in the step whose tokens it read.
 """
 
 from __future__ import annotations
 
 import time
 from typing import Callable, Dict, List, Optional, Sequence as Seq, Union
+
+import torch
 
 from ..config.engine import CacheConfig, SchedulerConfig
 from ..config.registry import load_config
@@ -29,8 +40,8 @@ from ..sampling.sampler import Sampler
 from ..weights.source import FolderSource, WeightSource
 from .outputs import RequestOutput
 from .runner import ModelRunner
-from .scheduler import Scheduler
-from .sequence import Sequence
+from .scheduler import ScheduledPortion, Scheduler, SchedulerOutput
+from .sequence import Sequence, SequenceStatus
 
 
 class LLMEngine:
@@ -39,7 +50,7 @@ class LLMEngine:
                  dtype: str = "bfloat16", device: str = "cuda:0", tokenizer=None,
                  clock: Optional[Callable[[], float]] = None,
                  weights: Optional[WeightSource] = None, cuda_graphs: bool = True,
-                 max_model_len: Optional[int] = None):
+                 max_model_len: Optional[int] = None, lookahead: bool = True):
         """``model``: a model folder (config.json + safetensors), or a typed
         architecture config together with ``weights``."""
         if isinstance(model, str):
@@ -63,6 +74,9 @@ class LLMEngine:
         self.sampler = Sampler(seed, device)
         self._req_counter = 0
         self.num_steps = 0
+        self.lookahead = lookahead
+        self._ahead = None                 # (requests, their tokens on the way) of a step launched ahead
+        self.num_lookahead_steps = 0
 
     # -------------------------------------------------------------- intake
     def add_request(self, prompt: Optional[str] = None,
@@ -93,25 +107,81 @@ class LLMEngine:
     # ------------------------------------------------------------- stepping
     def step(self) -> List[RequestOutput]:
         """One scheduler step; returns the requests that finished in it."""
-        plan = self.scheduler.schedule()
-        outputs = [RequestOutput.from_sequence(s, self._detokenize) for s in plan.aborted]
-        if plan.is_empty():
-            return outputs
-        entries, logit_seqs = [], []
-        for p in plan.portions:
-            seq = p.seq
-            want = (p.num_tokens - 1,) if p.wants_logits else ()
-            entries.append(self.runner.entry(seq.request_id,
-                                             seq.token_ids[p.start:p.start + p.num_tokens],
-                                             p.start, want))
-            if p.wants_logits:
-                logit_seqs.append(seq)
-        logits = self.runner.step(entries)
-        tokens = self.sampler.sample(logits, logit_seqs)
-        sampled: Dict[str, int] = {s.request_id: t for s, t in zip(logit_seqs, tokens)}
+        outputs: List[RequestOutput] = []
+        adopted = self._adopt_ahead()
+        if adopted is not None:
+            plan, rows, pending = adopted          # launched by the previous call
+            logit_seqs = [p.seq for p in plan.portions]
+        else:
+            plan = self.scheduler.schedule()
+            outputs = [RequestOutput.from_sequence(s, self._detokenize) for s in plan.aborted]
+            if plan.is_empty():
+                return outputs
+            entries, logit_seqs = [], []
+            for p in plan.portions:
+                seq = p.seq
+                want = (p.num_tokens - 1,) if p.wants_logits else ()
+                entries.append(self.runner.entry(seq.request_id,
+                                                 seq.token_ids[p.start:p.start + p.num_tokens],
+                                                 p.start, want))
+                if p.wants_logits:
+                    logit_seqs.append(seq)
+            logits = self.runner.step(entries)
+            pending = self.sampler.sample_async(logits, logit_seqs)
+            rows = list(range(len(logit_seqs)))
+        self._launch_ahead(plan, logit_seqs, rows, pending)
+        tokens = pending.wait()
+        sampled: Dict[str, int] = {s.request_id: tokens[r] for s, r in zip(logit_seqs, rows)}
         finished = self.scheduler.update_after_exec(plan, sampled, now=self.clock())
         self.num_steps += 1
         return outputs + [RequestOutput.from_sequence(s, self._detokenize) for s in finished]
+
+    # ------------------------------------------------------------ look-ahead
+    def _launch_ahead(self, plan: SchedulerOutput, seqs: List[Sequence], rows: List[int],
+                      pending) -> None:
+        """Launch the decode step after ``plan`` now, with the tokens ``pending`` holds on
+        the device, if that step is certain except for stop tokens."""
+        self._ahead = None
+        sch, runner = self.scheduler, self.runner
+        if (not self.lookahead or not seqs or sch.waiting or plan.preempted
+                or len(plan.portions) != len(sch.running) or len(seqs) != len(plan.portions)
+                or not runner.replays_graph(len(seqs))
+                or any(w for w in runner.storage.group_windows)):
+            return
+        for p in plan.portions:
+            seq, sp = p.seq, p.seq.sampling_params
+            if (p.num_tokens != 1 or not p.wants_logits                 # a prompt portion
+                    or seq.num_output_tokens + 1 >= sp.max_tokens        # ends by its length
+                    or seq.get_len() + 1 >= sch.max_model_len):
+                return
+        # every request gets one more token; its position is the current length
+        for seq in seqs:
+            if not runner.cache.ensure(seq.request_id, seq.get_len() + 1):
+                return                              # no page: the scheduler decides next step
+        entries = [runner.entry(seq.request_id, [0], seq.get_len(), (0,)) for seq in seqs]
+        ids = pending.device
+        if rows != list(range(ids.shape[0])):
+            ids = ids[torch.tensor(rows, dtype=torch.long, device=ids.device)]
+        logits = runner.step(entries, token_ids_from=ids)
+        self._ahead = (list(seqs), self.sampler.sample_async(logits, seqs, ahead=1))
+        self.num_lookahead_steps += 1
+
+    def _adopt_ahead(self):
+        """The step launched ahead, as a plan over the requests that are still running
+        (others ended meanwhile; their rows are dropped): (plan, rows, pending) or None."""
+        ahead, self._ahead = self._ahead, None
+        if ahead is None:
+            return None
+        seqs, pending = ahead
+        running = {id(s) for s in self.scheduler.running}
+        plan, rows = SchedulerOutput(), []
+        for r, seq in enumerate(seqs):
+            if id(seq) in running and seq.status == SequenceStatus.RUNNING:
+                plan.portions.append(ScheduledPortion(seq, seq.get_len() - 1, 1))
+                rows.append(r)
+        if not rows:
+            return None
+        return plan, rows, pending
 
     def _detokenize(self, token_ids: List[int]) -> str:
         return "" if self.tokenizer is None else self.tokenizer.decode(token_ids)

@@ -96,19 +96,31 @@ class ModelRunner:
             if not 0 <= t < v:
                 raise ValueError(f"token id {t} outside the vocabulary [0, {v})")
 
+    def replays_graph(self, num_entries: int) -> bool:
+        """Whether a step of ``num_entries`` single tokens, all wanting logits, replays a
+        captured graph."""
+        return self.cuda_graphs and self._graph_safe and 0 < num_entries <= self.max_graph_batch
+
     @torch.no_grad()
-    def step(self, entries: List[BatchEntry]) -> torch.Tensor:
-        """Logits [wanted, vocab] float32 (on the device) of this batch."""
+    def step(self, entries: List[BatchEntry],
+             token_ids_from: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Logits [wanted, vocab] float32 (on the device) of this batch.
+        ``token_ids_from`` (only for steps that replay a graph): int32 token ids on the
+        device, one per entry, that replace the entries' own tokens; they may still be
+        being computed by kernels queued earlier on the stream."""
         self.storage.clear_state_slots(self.cache.slots.drain_to_clear())
-        if (self.cuda_graphs and self._graph_safe and 0 < len(entries) <= self.max_graph_batch
+        if (self.replays_graph(len(entries))
                 and all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries)):
-            return self._step_graph(entries)
+            return self._step_graph(entries, token_ids_from)
+        if token_ids_from is not None:
+            raise ValueError("token ids from the device need a step that replays a graph")
         ctx = StepContext.pack(entries, self.num_groups, self.device)
         if ctx.num_tokens == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         return self.model.forward(ctx, self.storage.layer_caches)
 
-    def _step_graph(self, entries: List[BatchEntry]) -> torch.Tensor:
+    def _step_graph(self, entries: List[BatchEntry],
+                    token_ids_from: Optional[torch.Tensor] = None) -> torch.Tensor:
         """A step of single decoded tokens, all wanting logits: replay the graph
         captured for this batch size.  The returned logits live in the graph's
         memory and are overwritten by the next replay of the same size."""
@@ -130,6 +142,8 @@ class ModelRunner:
             hit = self._graphs[B] = (graph, ctx, logits)
         graph, ctx, logits = hit
         StepContext.pack(entries, self.num_groups, self.device, min_table_width=width, into=ctx)
+        if token_ids_from is not None:
+            ctx.token_ids.copy_(token_ids_from)
         graph.replay()
         self.graph_replays += 1
         return logits

@@ -24,27 +24,64 @@ def _f2i(x: float) -> int:
     return struct.unpack("<i", struct.pack("<f", x))[0]
 
 
+class PendingTokens:
+    """Tokens that have been sampled on the device and are on their way to the host:
+    ``device`` holds them (int32 [R]) for kernels launched after the sampler; ``wait()``
+    blocks until THEIR copy has arrived, not until the stream is idle, so work queued
+    after the sampler keeps running."""
+
+    def __init__(self, device_ids: torch.Tensor, host_ids: torch.Tensor, event):
+        self.device, self._host, self._event = device_ids, host_ids, event
+
+    def wait(self) -> List[int]:
+        if self._event is not None:
+            self._event.synchronize()
+        return self._host.tolist()
+
+
 class Sampler:
     def __init__(self, seed: int = 0, device: str = "cuda:0"):
         self.seed = int(seed) & ((1 << 63) - 1)
         self.device = device
+        self._pinned = {}          # rows -> two pinned host buffers used in turn
+        self._flip = 0
 
     def sample(self, logits: torch.Tensor, seqs: Sequence) -> List[int]:
         """One token per row of ``logits`` [R, V]; ``seqs[r]`` supplies
         ``sampling_params``, ``stream_id`` and ``num_output_tokens``."""
+        return self.sample_async(logits, seqs).wait()
+
+    def _to_host(self, out: torch.Tensor) -> PendingTokens:
+        R = out.shape[0]
+        pair = self._pinned.get(R)
+        if pair is None:
+            pair = self._pinned[R] = [torch.empty(R, dtype=torch.int32, pin_memory=True)
+                                      for _ in range(2)]
+        self._flip ^= 1
+        host = pair[self._flip]
+        host.copy_(out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return PendingTokens(out, host, event)
+
+    def sample_async(self, logits: torch.Tensor, seqs: Sequence, ahead: int = 0) -> PendingTokens:
+        """Launches the sampler and the copy of its result to the host; returns at once.
+        ``ahead``: output tokens each request will have got between now and this draw
+        (a step launched before the previous step's tokens were read back)."""
         R = logits.shape[0]
         if R == 0:
-            return []
+            return PendingTokens(torch.empty(0, dtype=torch.int32, device=self.device),
+                                 torch.empty(0, dtype=torch.int32), None)
         out = torch.empty(R, dtype=torch.int32, device=self.device)
         if all(s.sampling_params.temperature == 0.0 for s in seqs):
             K.sample_rows(logits, out)
-            return out.tolist()
+            return self._to_host(out)
         # [temperature | top_k | top_p | position | seed (2 words) | stream (2 words)]
         words: List[int] = []
         words += [_f2i(float(s.sampling_params.temperature)) for s in seqs]
         words += [int(s.sampling_params.top_k) for s in seqs]
         words += [_f2i(float(s.sampling_params.top_p)) for s in seqs]
-        words += [int(s.num_output_tokens) for s in seqs]
+        words += [int(s.num_output_tokens) + ahead for s in seqs]
         for s in seqs:
             sd = s.sampling_params.seed if s.sampling_params.seed >= 0 else self.seed
             words += [sd & 0xFFFFFFFF, (sd >> 32) & 0xFFFFFFFF]
@@ -61,4 +98,4 @@ class Sampler:
         seed = dev[4 * R:6 * R]
         stream = dev[6 * R:8 * R]
         K.sample_rows(logits, out, temp, top_k, top_p, seed, stream, pos)
-        return out.tolist()
+        return self._to_host(out)

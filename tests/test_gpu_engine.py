@@ -132,6 +132,52 @@ def test_stop_conditions_abort_and_rejections(model):
     assert outs[1].outputs[0].finish_reason == "length"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_lookahead_gives_the_same_tokens_and_frees_every_page(model, dtype):
+    """Steps launched before the previous step's tokens are read: the same tokens as
+    without, with requests that stop at different steps on a stop token (one step too
+    many has then run for them), with random sampling, with an abort and a late arrival
+    between steps; afterwards no page is held."""
+    from servelab_b200.sampling import SamplingParams
+    cfg, w = P.load_folder(model["folder"])
+    prompts = model["prompts"]
+    greedy = [P.generate_greedy(cfg, w, p, 20) for p in prompts]
+    # each request stops at a token it produces at another step (greedy decoding repeats
+    # tokens on these tiny models, so take the first occurrence)
+    stops = [g[min(3 + 4 * i, len(g) - 1)] for i, g in enumerate(greedy)]
+
+    def run(lookahead, sp_list, aborts=False):
+        eng = _engine(model, dtype=dtype, lookahead=lookahead)
+        ids = [eng.add_request(prompt_token_ids=p, sampling_params=sp) for p, sp in zip(prompts, sp_list)]
+        results, steps = {}, 0
+        while eng.has_unfinished():
+            for o in eng.step():
+                results[o.request_id] = (o.outputs[0].token_ids, o.outputs[0].finish_reason)
+            steps += 1
+            if aborts and steps == 4:
+                results["aborted"] = eng.abort_request(ids[0])     # False if it has ended already
+                ids.append(eng.add_request(prompt_token_ids=prompts[0][:3] + [5],
+                                           sampling_params=sp_list[-1]))
+        st = eng.stats()
+        assert st["pages_used"] == [0] * len(st["pages_used"])
+        eng.runner.cache.check_invariants()
+        windowed = any(eng.runner.storage.group_windows)    # no look-ahead with windowed layers
+        return [results.get(i) for i in ids + ["aborted"]], (eng.num_lookahead_steps, windowed)
+
+    stopping = [SamplingParams(temperature=0.0, max_tokens=20, stop_token_ids=(t,)) for t in stops]
+    random_sp = [SamplingParams(temperature=0.8, top_k=20, max_tokens=15, ignore_eos=True)] * len(prompts)
+    for sp_list, aborts in ((stopping, False), (random_sp, False), (stopping, True), (random_sp, True)):
+        with_it, (n_ahead, windowed) = run(True, sp_list, aborts)
+        without, (none_ahead, _) = run(False, sp_list, aborts)
+        assert with_it == without
+        longest = max(len(r[0]) for r in with_it if isinstance(r, tuple))
+        assert none_ahead == 0 and (n_ahead > 0 or longest < 3 or windowed), (n_ahead, longest)
+    if dtype == "float32":
+        got, _ = run(True, stopping)
+        for (toks, reason), g, t in zip(got[:len(prompts)], greedy, stops):
+            assert toks == g[:g.index(t) + 1] and reason == "eos"
+
+
 def test_command_line(model, tmp_path):
     if model["name"] != "A":
         pytest.skip("one configuration is enough for the command line")
