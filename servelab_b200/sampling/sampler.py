@@ -51,6 +51,16 @@ class Sampler:
         ``sampling_params``, ``stream_id`` and ``num_output_tokens``."""
         return self.sample_async(logits, seqs).wait()
 
+    def _pinned_words(self, n: int) -> torch.Tensor:
+        """One of four pinned buffers of ``n`` ints, used in turn (a buffer is written
+        again only after three later steps' parameters have been queued)."""
+        ring = self._pinned.get(("words", n))
+        if ring is None:
+            ring = self._pinned[("words", n)] = [[torch.empty(n, dtype=torch.int32, pin_memory=True)
+                                                  for _ in range(4)], 0]
+        ring[1] = (ring[1] + 1) % 4
+        return ring[0][ring[1]]
+
     def _to_host(self, out: torch.Tensor) -> PendingTokens:
         R = out.shape[0]
         pair = self._pinned.get(R)
@@ -88,9 +98,10 @@ class Sampler:
         for s in seqs:
             st = 0 if s.sampling_params.seed >= 0 else int(s.stream_id)
             words += [st & 0xFFFFFFFF, (st >> 32) & 0xFFFFFFFF]
-        host = torch.tensor([w - (1 << 32) if w >= (1 << 31) else w for w in words],
-                            dtype=torch.int32)
-        dev = host.to(self.device)
+        # pinned and asynchronous: a pageable copy would make the host wait for the stream
+        host = self._pinned_words(len(words))
+        host.numpy()[:] = [w - (1 << 32) if w >= (1 << 31) else w for w in words]
+        dev = host.to(self.device, non_blocking=True)
         temp = dev[0:R].view(torch.float32)
         top_k = dev[R:2 * R]
         top_p = dev[2 * R:3 * R].view(torch.float32)
