@@ -544,6 +544,37 @@ def test_decode_attention_one_launch(H, Hkv, D, ps, window, splits, stages, coef
         assert (out2.float().cpu() - want).abs().max() <= TOL["bfloat16"]
 
 
+def test_decode_attention_many_launches_of_a_mixed_batch():
+    """48 requests of very different lengths at the 7B head layout, 300 launches back to
+    back with matrix products between them (producer and consumers, blocks that leave at
+    once, last blocks that combine: every role runs ahead or behind by different amounts
+    from launch to launch).  No bounded wait may give up, the arrival counters are zero
+    again, and every launch gives bit for bit the result of the first."""
+    from servelab_b200.ops import kernels as kernels_module
+    H, Hkv, D, ps = 28, 4, 128, 16
+    g = torch.Generator().manual_seed(3)
+    ctxs = [int(x) for x in torch.randint(1, 3000, (48,), generator=g)] + [1, 64, 65, 4096]
+    case = PagedCase(ctxs, [1] * len(ctxs), H, Hkv, D, ps, torch.bfloat16, seed=9)
+    case.scatter()
+    ctx, q, table = _ctx_for(case)
+    want = case.reference()
+    a = torch.randn(512, 1024, device=DEV).bfloat16()
+    b = torch.randn(1024, 2048, device=DEV).bfloat16()
+    first = torch.empty_like(q)
+    K().decode_attention(ctx, q, case.kc, case.vc, first, table, H, Hkv, D, ps, 1 / math.sqrt(D), 0)
+    assert (first.float().cpu() - want).abs().max() <= TOL["bfloat16"]
+    outs = [torch.empty_like(q) for _ in range(4)]
+    for i in range(300):
+        if i % 3 == 0:
+            torch.mm(a, b)
+        K().decode_attention(ctx, q, case.kc, case.vc, outs[i % 4], table, H, Hkv, D, ps,
+                             1 / math.sqrt(D), 0)
+        if i % 60 == 59:
+            assert K().decode_attention_status(D, reset=True) == 0, "a bounded wait gave up"
+            assert all(torch.equal(o, first) for o in outs)
+    assert all(int(c.abs().sum()) == 0 for c in kernels_module._decode_counters.values())
+
+
 @pytest.mark.parametrize("H,Hkv,D,ps", [(14, 2, 128, 16), (6, 3, 32, 8), (8, 1, 64, 64)])
 @pytest.mark.parametrize("window", [1, 7, 64, 65, 200])
 def test_fast_attention_window_edges(H, Hkv, D, ps, window):
