@@ -158,8 +158,8 @@ def main(argv=None) -> int:
         name, value = item.split("=")
         if name == "skinny_max_tokens":
             linear_ops.skinny_max_tokens = int(value)
-        elif name == "tc_max_tokens":
-            linear_ops.tc_max_tokens = int(value)
+        elif name in ("tc_max_tokens", "tc_wide_max_tokens"):
+            setattr(linear_ops, name, int(value))
         elif name in ("defer_rope", "defer_norm"):
             linear_ops.defer_split_sums[name[6:]] = bool(int(value))
         elif name == "tc_max_stages":

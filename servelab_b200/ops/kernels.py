@@ -381,7 +381,7 @@ def tc_decode_splits(n_out: int, k: int) -> int:
     tiles = -(-n_out // 128)
     kblocks = -(-k // 64)
     slots = tc_blocks_per_sm * _num_sms()
-    want = max(1, round(slots / tiles)) if tiles < slots else 1
+    want = max(1, slots // tiles) if tiles < slots else 1      # all blocks resident at once
     return max(1, min(want, kblocks // 4 if kblocks >= 8 else 1))
 
 

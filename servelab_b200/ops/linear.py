@@ -31,6 +31,9 @@ def _skinny_ok(x, w, M):
 
 
 tc_max_tokens = 16         # up to this many tokens the tcgen05 weight-streaming kernel runs
+tc_wide_max_tokens = 64    # ... and up to this many for products wide enough to need no K split
+                           # (gate|up: 45.5 us against the library's 47.7 at 64 tokens; the narrow
+                           # products lose to it above 16 tokens: their partial sums grow with M)
 # Hand the K-split partial sums of a decode-step product to the kernel that consumes the
 # result instead of reducing them in a kernel of their own, per kind of consumer.  "rope":
 # the q/k/v kernel takes them with one block per (head, token).  "norm": the norm takes
@@ -63,7 +66,10 @@ def _next_weight(w):
 
 
 def _tc_ok(x, w, M):
-    return (0 < M <= min(tc_max_tokens, K.TC_MAX_TOKENS) and w.shape[1] % 8 == 0
+    limit = tc_max_tokens
+    if M > limit and K.tc_decode_splits(w.shape[0], w.shape[1]) == 1:
+        limit = max(limit, tc_wide_max_tokens)
+    return (0 < M <= min(limit, K.TC_MAX_TOKENS) and w.shape[1] % 8 == 0
             and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
