@@ -190,18 +190,28 @@ __global__ void qkv_rope_cache_vec_kernel(
         for (int e = 0; e < VEC; ++e) {
             fa[e] = to_float(va[e]);
             fb[e] = to_float(vb[e]);
-            if (bias) {
-                fa[e] += bias[off + a + e];
-                fb[e] += bias[off + b + e];
+        }
+        if (bias) {                                    // a and b are multiples of VEC: 16-byte loads
+#pragma unroll
+            for (int e = 0; e < VEC; e += 4) {
+                const float4 ba = *reinterpret_cast<const float4*>(bias + off + a + e);
+                const float4 bb = *reinterpret_cast<const float4*>(bias + off + b + e);
+                fa[e] += ba.x; fa[e + 1] += ba.y; fa[e + 2] += ba.z; fa[e + 3] += ba.w;
+                fb[e] += bb.x; fb[e + 1] += bb.y; fb[e + 2] += bb.z; fb[e + 3] += bb.w;
             }
         }
         if (rot) {
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) {
-                const float cs = trig[a + e], sn = trig[half + a + e];
-                const float ra = fa[e] * cs - fb[e] * sn;
-                fb[e] = fb[e] * cs + fa[e] * sn;
-                fa[e] = ra;
+            for (int e = 0; e < VEC; e += 4) {
+                const float4 c4 = *reinterpret_cast<const float4*>(trig + a + e);
+                const float4 s4 = *reinterpret_cast<const float4*>(trig + half + a + e);
+                const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float ra = fa[e + k] * cs[k] - fb[e + k] * sn[k];
+                    fb[e + k] = fb[e + k] * cs[k] + fa[e + k] * sn[k];
+                    fa[e + k] = ra;
+                }
             }
         }
         T* dst;
