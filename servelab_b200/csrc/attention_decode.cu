@@ -226,13 +226,19 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     int first_pages = -1;
     if (warp < burst) first_pages = lookup((warp * geo.boxes) >> 5);
 
-    pdl_wait();                                            // q and this step's K/V rows
-    if (warp < burst) {
+    // Only the request's newest key and value are written in this step (by the kernel
+    // before this one, into the request's last tile); every earlier tile was written by
+    // earlier steps and is requested at once, while that kernel still runs.
+    const bool last_tile_in_burst = warp < burst && t_begin + warp == total_tiles - 1;
+    auto produce_first = [&]() {
         const int page = __shfl_sync(0xffffffffu, first_pages, (warp * geo.boxes + lane) & 31);
         unsigned char* Kd = stage0 + (size_t)warp * STAGE_BYTES;
         produce_tile(Kd, Kd + TILE_BYTES, &full_bar[warp], &map_k, &map_v, page, kstart + warp * BN, ctx,
                      kvh, Hkv, ps, geo);
-    }
+    };
+    if (warp < burst && !last_tile_in_burst) produce_first();
+    pdl_wait();                                            // q and this step's K/V rows
+    if (last_tile_in_burst) produce_first();
 
     if (warp == DW) {
         // ------------------------------------------------------------ producer
