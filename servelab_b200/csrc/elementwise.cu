@@ -219,14 +219,18 @@ __global__ void add_rmsnorm_parts_cluster_kernel(float* __restrict__ resid,
     cluster_wait();                                        // nobody still reads this block's sum
 }
 
-// out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(z) = z / (1 + exp(-z)), in float32.
-// V elements per thread and step: 8 (bfloat16 with inter, ld_gu and ld_out multiples of 8:
-// 16-byte accesses), 4 (multiples of 4) or 1.
+// out[t, i] = silu(gate_i) * up_i, silu(z) = z / (1 + exp(-z)), in float32.  Layout of a
+// row of gu: block == 0: all gates, then all ups (gate_i at i, up_i at inter + i);
+// block > 0: gates and ups alternate in runs of `block` (gate_i at (i / block) * 2 * block +
+// i % block, up_i `block` further), the order in which a product with row-interleaved
+// weights delivers them.
+// V elements per thread and step: 8 (bfloat16 with inter, block, ld_gu and ld_out multiples
+// of 8: 16-byte accesses), 4 (multiples of 4) or 1.
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
 template <typename T, int V>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
-                              int ld_gu, int ld_out) {
+                              int ld_gu, int ld_out, int block) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.y;
@@ -234,10 +238,12 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     T* o = out + (size_t)t * ld_out;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * V;
     if (i >= inter) return;
+    const int gi = block > 0 ? (i / block) * 2 * block + i % block : i;     // where gate_i sits
+    const int ui = block > 0 ? gi + block : inter + i;                      // where up_i sits
     if constexpr (V == 8) {
         // two 16-byte loads of 8 bfloat16 each, one 16-byte store
-        const uint4 graw = *reinterpret_cast<const uint4*>(row + i);
-        const uint4 uraw = *reinterpret_cast<const uint4*>(row + inter + i);
+        const uint4 graw = *reinterpret_cast<const uint4*>(row + gi);
+        const uint4 uraw = *reinterpret_cast<const uint4*>(row + ui);
         const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
         const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uraw);
         uint4 res;
@@ -249,11 +255,11 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
         }
         *reinterpret_cast<uint4*>(o + i) = res;
     } else if constexpr (V == 4) {
-        const float4 g = load4(row + i), u = load4(row + inter + i);
+        const float4 g = load4(row + gi), u = load4(row + ui);
         store4(o + i, make_float4(silu_mul(g.x, u.x), silu_mul(g.y, u.y), silu_mul(g.z, u.z),
                                   silu_mul(g.w, u.w)));
     } else {
-        o[i] = from_float<T>(silu_mul(to_float(row[i]), to_float(row[inter + i])));
+        o[i] = from_float<T>(silu_mul(to_float(row[gi]), to_float(row[ui])));
     }
 }
 
@@ -294,21 +300,21 @@ static int launch_add_rmsnorm(float* resid, const TD* delta, const float* parts,
 }
 
 template <typename T>
-static int launch_swiglu(const T* gu, T* out, int T_, int inter, int ld_gu, int ld_out,
+static int launch_swiglu(const T* gu, T* out, int T_, int inter, int ld_gu, int ld_out, int block,
                          cudaStream_t st) {
     if (T_ <= 0) return 0;
-    if (inter <= 0 || T_ > 65535) return SLB_ERR_BAD_ARG;
+    if (inter <= 0 || T_ > 65535 || block < 0 || (block > 0 && inter % block)) return SLB_ERR_BAD_ARG;
     if constexpr (sizeof(T) == 2) {
-        if (inter % 8 == 0 && ld_gu % 8 == 0 && ld_out % 8 == 0 &&
+        if (inter % 8 == 0 && block % 8 == 0 && ld_gu % 8 == 0 && ld_out % 8 == 0 &&
             ((uintptr_t)gu | (uintptr_t)out) % 16 == 0)
             return slb_launch(swiglu_kernel<T, 8>, dim3((inter / 8 + 255) / 256, T_), dim3(256), 0, st,
-                              gu, out, inter, ld_gu, ld_out);
+                              gu, out, inter, ld_gu, ld_out, block);
     }
-    if (inter % 4 == 0 && ld_gu % 4 == 0 && ld_out % 4 == 0)
+    if (inter % 4 == 0 && block % 4 == 0 && ld_gu % 4 == 0 && ld_out % 4 == 0)
         return slb_launch(swiglu_kernel<T, 4>, dim3((inter / 4 + 255) / 256, T_), dim3(256), 0, st,
-                          gu, out, inter, ld_gu, ld_out);
+                          gu, out, inter, ld_gu, ld_out, block);
     return slb_launch(swiglu_kernel<T, 1>, dim3((inter + 255) / 256, T_), dim3(256), 0, st, gu,
-                      out, inter, ld_gu, ld_out);
+                      out, inter, ld_gu, ld_out, block);
 }
 
 SLB_DEFINE_PDL_SWITCH
@@ -363,13 +369,14 @@ int slb_add_rmsnorm_parts_bf16(float* resid, const float* parts, int nparts, lon
                                           out, row_map, rows, h, eps, st);
 }
 
-int slb_swiglu_f32(const float* gu, float* out, int T, int inter, int ld_gu, int ld_out,
+// block: 0, or the run length in which gates and ups alternate in a row of gu
+int slb_swiglu_f32(const float* gu, float* out, int T, int inter, int ld_gu, int ld_out, int block,
                    cudaStream_t st) {
-    return launch_swiglu<float>(gu, out, T, inter, ld_gu, ld_out, st);
+    return launch_swiglu<float>(gu, out, T, inter, ld_gu, ld_out, block, st);
 }
-int slb_swiglu_bf16(const bf16* gu, bf16* out, int T, int inter, int ld_gu, int ld_out,
+int slb_swiglu_bf16(const bf16* gu, bf16* out, int T, int inter, int ld_gu, int ld_out, int block,
                     cudaStream_t st) {
-    return launch_swiglu<bf16>(gu, out, T, inter, ld_gu, ld_out, st);
+    return launch_swiglu<bf16>(gu, out, T, inter, ld_gu, ld_out, block, st);
 }
 
 }  // extern "C"

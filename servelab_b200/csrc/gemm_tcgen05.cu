@@ -133,7 +133,7 @@ template <typename TO>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     TO* __restrict__ out, int ldo, float* __restrict__ partial, const float* __restrict__ bias,
-    int M, int N, int K, int ntok16, int max_stages, int* __restrict__ status, Prefetch pf) {
+    int M, int N, int K, int ntok16, int max_stages, int* __restrict__ status, Prefetch pf, int swiglu) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -249,6 +249,42 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
                 prefetch_l2(pf.ptr + off, (uint32_t)(left < pf.chunk_bytes ? left : pf.chunk_bytes) & ~15u);
             }
         }
+        if (swiglu) {
+            // W holds gate and up rows alternating in runs of 64, so this tile's rows are 64
+            // gates and their 64 ups: the upper two warps park the ups in shared memory (the
+            // ring is idle: every tile has arrived and every MMA has run), the lower two
+            // combine: out[tok, tile * 64 + r] = silu(gate_r) * up_r.  One K split only.
+            float* ups = reinterpret_cast<float*>(a_stage);            // [64][ntok16 + 1]
+            const int ld_ups = ntok16 + 1;
+            if (row >= 64) {
+                for (int c0 = 0; c0 < ntok16; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) ups[(row - 64) * ld_ups + c0 + j] = __uint_as_float(v[j]);
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");             // the four epilogue warps
+            if (row < 64) {
+                const int col = (int)blockIdx.x * 64 + row;            // index of the gate
+                for (int c0 = 0; c0 < ntok16; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (col < N / 2 && ok) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int tok = c0 + j;
+                            if (tok >= M) break;
+                            const float gt = __uint_as_float(v[j]);
+                            const float up = ups[row * ld_ups + tok];
+                            out[(size_t)tok * ldo + col] = from_float<TO>(gt / (1.0f + expf(-gt)) * up);
+                        }
+                    }
+                }
+            }
+        } else
         for (int c0 = 0; c0 < ntok16; c0 += 16) {
             uint32_t v[16];
             if (iters > 0 && ok) {
@@ -331,7 +367,7 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box
 template <typename TO>
 int run(const bf16* x, int ldx, const bf16* W, int ldw, TO* out, int ldo, const float* bias,
         float* workspace, int M, int N, int K, int splits, int max_stages, int defer_sum,
-        const Prefetch& pf, cudaStream_t st) {
+        const Prefetch& pf, int swiglu, cudaStream_t st) {
     CUtensorMap map_w, map_x;
     const int ntok16 = (M + 15) / 16 * 16;
     int rc = make_map(&map_w, W, N, K, ldw, TC_BM);
@@ -353,7 +389,8 @@ int run(const bf16* x, int ldx, const bf16* W, int ldw, TO* out, int ldo, const 
     cudaError_t e = cudaGetSymbolAddress((void**)&status, tc_status_word);
     if (e != cudaSuccess) return (int)e;
     rc = slb_launch(gemm_tc_decode_kernel<TO>, dim3((N + TC_BM - 1) / TC_BM, splits), dim3(TC_THREADS),
-                    TC_SMEM, st, map_w, map_x, out, ldo, workspace, bias, M, N, K, ntok16, max_stages, status, pf);
+                    TC_SMEM, st, map_w, map_x, out, ldo, workspace, bias, M, N, K, ntok16, max_stages, status, pf,
+                    swiglu);
     if (rc != 0 || splits == 1 || defer_sum) return rc;
     return slb_launch(gemm_tc_reduce_kernel<TO>, dim3((N + 255) / 256, M), dim3(256), 0, st,
                       (const float*)workspace, out, ldo, bias, M, N, splits);
@@ -373,14 +410,19 @@ extern "C" {
 int slb_gemm_tc_decode_bf16(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo,
                             const float* bias, float* workspace, int out_f32, int M, int N, int K,
                             int splits, int max_stages, int defer_sum, const void* next_w,
-                            long long next_bytes, int next_chunk_bytes, cudaStream_t st) {
+                            long long next_bytes, int next_chunk_bytes, int swiglu, cudaStream_t st) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldo < N) return SLB_ERR_BAD_ARG;
+    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || (!swiglu && ldo < N)) return SLB_ERR_BAD_ARG;
     if (((uintptr_t)x | (uintptr_t)W) % 16) return SLB_ERR_BAD_ARG;
     if (M > TC_MAX_TOK) return SLB_ERR_TOO_LARGE;
     const int kblocks = (K + TC_BK - 1) / TC_BK;
     if (splits < 1 || splits > kblocks || splits > 65535) return SLB_ERR_BAD_ARG;
     if (splits > 1 && workspace == nullptr) return SLB_ERR_BAD_ARG;
+    // swiglu: W's rows are gates and ups alternating in runs of 64; out is [M, N / 2]
+    if (swiglu && (splits != 1 || N % 128 || bias != nullptr || ldo < N / 2)) return SLB_ERR_BAD_ARG;
+    // the ups of a tile wait in the idle ring: [64][tokens + 1] floats
+    if (swiglu && (size_t)stages_for((M + 15) / 16 * 16, max_stages) * A_STAGE_BYTES < (size_t)64 * ((M + 15) / 16 * 16 + 1) * 4)
+        return SLB_ERR_BAD_ARG;
     Prefetch pf = {nullptr, 0, 0};
     if (next_w != nullptr && next_bytes >= 16) {
         if (next_chunk_bytes < 16 || next_chunk_bytes % 16 || next_bytes % 16 || (uintptr_t)next_w % 16)
@@ -389,9 +431,9 @@ int slb_gemm_tc_decode_bf16(const bf16* x, int ldx, const bf16* W, int ldw, void
     }
     if (out_f32)
         return run<float>(x, ldx, W, ldw, (float*)out, ldo, bias, workspace, M, N, K, splits, max_stages,
-                          defer_sum, pf, st);
+                          defer_sum, pf, swiglu, st);
     return run<bf16>(x, ldx, W, ldw, (bf16*)out, ldo, bias, workspace, M, N, K, splits, max_stages,
-                     defer_sum, pf, st);
+                     defer_sum, pf, swiglu, st);
 }
 
 // out[M, N] = sum of float32 partial sums [splits][M][N] (+ bias), in order.

@@ -95,11 +95,13 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
                rows, out.shape[1], float(eps), _stream()), "add_rmsnorm")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i], I = out.shape[1]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
+    """out[t, i] = silu(gate_i) * up_i of row t of ``gate_up`` ([T, 2 I], I = out.shape[1]).
+    ``block`` == 0: a row holds all gates, then all ups; ``block`` > 0: gates and ups
+    alternate in runs of ``block`` elements."""
     fn = getattr(L.core(), "slb_swiglu_" + _suffix(out.dtype))
     L.check(fn(gate_up.data_ptr(), out.data_ptr(), out.shape[0], out.shape[1],
-               gate_up.stride(0), out.stride(0), _stream()), "swiglu")
+               gate_up.stride(0), out.stride(0), int(block), _stream()), "swiglu")
 
 
 # ----------------------------------------------------- rotary + cache write
@@ -406,20 +408,33 @@ def _next_weight_args(next_weight: Optional[torch.Tensor]):
     return next_weight.data_ptr(), nbytes, tc_prefetch_chunk
 
 
+# rows of gates, then as many of ups, and so on: the layout for which the tcgen05 product
+# applies the activation in its epilogue (half of its 128-row tile)
+SWIGLU_BLOCK = 64
+
+
 def gemm_tc_decode(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor],
                    bias: Optional[torch.Tensor] = None, splits: int = 0,
                    defer_sum: bool = False, out_dtype: Optional[torch.dtype] = None,
-                   next_weight: Optional[torch.Tensor] = None):
+                   next_weight: Optional[torch.Tensor] = None, swiglu: bool = False):
     """out[M,N] = x[M,K] . w[N,K]^T (+ bias) for up to 64 tokens on tcgen05 tensor
     cores with TMA-streamed weights; bfloat16 operands, float32 or bfloat16 output.
     With ``defer_sum`` and more than one K split the partial sums are returned as a
     ``SplitSum`` (no reduction is launched); otherwise ``out`` (allocated if None).
     ``next_weight``: the weights of the product that will follow; their leading part is
-    requested into the L2 cache while this kernel drains."""
+    requested into the L2 cache while this kernel drains.
+    ``swiglu``: ``w`` holds gate and up rows alternating in runs of ``SWIGLU_BLOCK``; the
+    result is silu(gate) * up, [M, N / 2] (one K split, no bias)."""
     global launch_count
     M, Kd = x.shape
     N = w.shape[0]
     splits = splits or tc_decode_splits(N, Kd)
+    if swiglu:
+        if splits != 1 or bias is not None or N % (2 * SWIGLU_BLOCK):
+            raise ValueError("gemm_tc_decode: the fused activation needs one K split, no bias and "
+                             f"a multiple of {2 * SWIGLU_BLOCK} rows")
+        if out is None:
+            out = torch.empty((M, N // 2), dtype=out_dtype or x.dtype, device=x.device)
     out_dtype = out.dtype if out is not None else (out_dtype or x.dtype)
     ws = torch.empty((splits, M, N), dtype=_F32, device=x.device) if splits > 1 else None
     deferred = defer_sum and splits > 1
@@ -428,7 +443,8 @@ def gemm_tc_decode(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor]
     L.check(L.core().slb_gemm_tc_decode_bf16(
         x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _p(out), out.stride(0) if out is not None else N,
         _p(bias), _p(ws), 1 if out_dtype == _F32 else 0, M, N, Kd, splits, tc_max_stages,
-        1 if deferred else 0, *_next_weight_args(next_weight), _stream()), "gemm_tc_decode")
+        1 if deferred else 0, *_next_weight_args(next_weight), 1 if swiglu else 0, _stream()),
+        "gemm_tc_decode")
     if deferred:
         return SplitSum(ws, bias, out_dtype)
     launch_count += 1 if splits > 1 else 0

@@ -29,8 +29,8 @@ _CORE_SIGNATURES = {
     "slb_embedding_bf16": [P, P, P, I, I, I, P],
     "slb_add_rmsnorm_f32": [P, P, P, P, P, I, I, F, P],
     "slb_add_rmsnorm_bf16": [P, P, P, P, P, I, I, F, P],
-    "slb_swiglu_f32": [P, P, I, I, I, I, P],
-    "slb_swiglu_bf16": [P, P, I, I, I, I, P],
+    "slb_swiglu_f32": [P, P, I, I, I, I, I, P],
+    "slb_swiglu_bf16": [P, P, I, I, I, I, I, P],
     "slb_qkv_rope_cache_f32": [P, I, P, P, P, P, I, I, P, I, P, I, P, P, I, I, I, I, P],
     "slb_qkv_rope_cache_bf16": [P, I, P, P, P, P, I, I, P, I, P, I, P, P, I, I, I, I, P],
     "slb_paged_attention_generic_f32": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, P],
@@ -41,7 +41,7 @@ _CORE_SIGNATURES = {
     "slb_gemm_simt_bf16_f32out": [P, I, P, I, P, I, P, I, I, I, P],
     "slb_sample_rows": [P, I, I, I, P, P, P, P, P, P, P, P],
     "slb_gemm_skinny_bf16": [P, I, P, I, P, I, P, I, I, I, I, I, P],
-    "slb_gemm_tc_decode_bf16": [P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, P, LL, I, P],
+    "slb_gemm_tc_decode_bf16": [P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, P, LL, I, I, P],
     "slb_split_sum": [P, P, I, P, I, I, I, I, P],
     "slb_add_rmsnorm_parts_bf16": [P, P, I, LL, P, P, P, P, I, I, F, P],
     "slb_qkv_rope_cache_parts_bf16": [P, I, LL, I, P, P, P, P, I, I, P, I, P, I, P, P, I, I, I, I, P],

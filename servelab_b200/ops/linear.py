@@ -41,6 +41,7 @@ tc_wide_max_tokens = 64    # ... and up to this many for products wide enough to
 # one-block-per-token form of itself (measured at batch 8 / 1 on the 7B shape: 3.31 / 3.13
 # ms a step without, 3.28 / 3.10 with "rope", 3.22 / 3.04 with both).
 defer_split_sums = {"rope": True, "norm": True}
+fuse_swiglu = True         # the gate|up product of a decode step applies the activation itself
 
 
 # Which weights follow which in a forward pass, by address: a hint with which the tcgen05
@@ -72,6 +73,22 @@ def _tc_ok(x, w, M):
     return (0 < M <= min(limit, K.TC_MAX_TOKENS) and w.shape[1] % 8 == 0
             and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, block: int) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) for ``w_gate_up`` [2I, h]: gate rows then up rows
+    (``block`` 0), or alternating in runs of ``block`` rows.  Decode steps in bfloat16
+    apply the activation in the product's epilogue; everything else runs the product and
+    then the activation kernel."""
+    M = x.shape[0]
+    inter = w_gate_up.shape[0] // 2
+    if (fuse_swiglu and x.dtype == torch.bfloat16 and block == K.SWIGLU_BLOCK and _tc_ok(x, w_gate_up, M)
+            and K.tc_decode_splits(w_gate_up.shape[0], w_gate_up.shape[1]) == 1):
+        return K.gemm_tc_decode(x, w_gate_up, None, swiglu=True, next_weight=_next_weight(w_gate_up))
+    gu = linear(x, w_gate_up)
+    act = torch.empty((M, inter), dtype=x.dtype, device=x.device)
+    K.swiglu(gu, act, block)
+    return act
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,

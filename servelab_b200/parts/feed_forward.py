@@ -1,6 +1,8 @@
 """Dense gated feed-forward: down(act(gate(x)) * up(x)), no experts, no routing
 (servelab/parallel/tp_model.py:60-68 in the reference).  gate and up are fused
-into one [2I, h] matrix at load so that one product feeds the activation kernel.
+into one [2I, h] matrix at load so that one product feeds the activation kernel;
+when I allows it their rows alternate in runs of 64, so that a 128-row tile of the
+decode-step product holds 64 gates with their ups and applies the activation itself.
 """
 
 from __future__ import annotations
@@ -8,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels as K
-from ..ops.linear import linear
+from ..ops.linear import gated_linear, linear
 from ..weights.source import BIAS, MATRIX, TensorDecl
 from .base import FeedForward
 from .registry import register_feed_forward
@@ -33,15 +35,21 @@ class GatedMLP(FeedForward):
                 TensorDecl(prefix + ".down_proj.weight", (h, i), MATRIX)]
 
     def load(self, store):
-        self.w_gate_up = store.cat([self.prefix + ".gate_proj.weight",
-                                    self.prefix + ".up_proj.weight"])
+        gate = store.get(self.prefix + ".gate_proj.weight")
+        up = store.get(self.prefix + ".up_proj.weight")
+        inter, h = gate.shape
+        self.block = K.SWIGLU_BLOCK if inter % K.SWIGLU_BLOCK == 0 else 0
+        if self.block:
+            b = self.block
+            self.w_gate_up = torch.stack([gate.view(inter // b, b, h), up.view(inter // b, b, h)],
+                                         dim=1).reshape(2 * inter, h).contiguous()
+        else:
+            self.w_gate_up = torch.cat([gate, up], dim=0)
         self.w_down = store.get(self.prefix + ".down_proj.weight")
 
     def matrices(self):
         return [self.w_gate_up, self.w_down]
 
     def forward(self, ctx, x):
-        gu = linear(x, self.w_gate_up)
-        act = torch.empty((x.shape[0], self.spec.intermediate_size), dtype=x.dtype, device=x.device)
-        K.swiglu(gu, act)
+        act = gated_linear(x, self.w_gate_up, self.block)
         return linear(act, self.w_down, consumer="norm")

@@ -117,6 +117,51 @@ def test_swiglu(dtype, inter):
     assert bool(((out.float() - want).abs() <= want.abs() * rel + 1e-6).all())
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("inter,block", [(192, 64), (24, 3), (1280, 64), (160, 16)])
+def test_swiglu_of_alternating_runs(dtype, inter, block):
+    """Gates and ups alternate in runs of ``block`` columns."""
+    dt = DT[dtype]
+    gu = (torch.randn(5, 2 * inter, device=DEV) * 3).to(dt)
+    out = torch.empty(5, inter, device=DEV, dtype=dt)
+    K().swiglu(gu, out, block)
+    runs = gu.float().view(5, inter // block, 2, block)
+    g, u = runs[:, :, 0].reshape(5, inter), runs[:, :, 1].reshape(5, inter)
+    want = g * torch.sigmoid(g) * u
+    rel = 2.0 ** -8 if dtype == "bfloat16" else 2.0 ** -21
+    assert bool(((out.float() - want).abs() <= want.abs() * rel + 1e-6).all())
+
+
+@pytest.mark.parametrize("M,inter,Kd", [(1, 64, 64), (8, 192, 264), (16, 1088, 896), (37, 704, 512),
+                                        (64, 320, 1024)])
+def test_gemm_tcgen05_decode_with_activation(M, inter, Kd):
+    """The product's epilogue applies silu(gate) * up when the weights' rows alternate in
+    runs of 64; compared with the float64 product of the separate matrices."""
+    B = K().SWIGLU_BLOCK
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    gate = (torch.randn(inter, Kd, device=DEV) * 2 / math.sqrt(Kd)).bfloat16()
+    up = (torch.randn(inter, Kd, device=DEV) * 2 / math.sqrt(Kd)).bfloat16()
+    w = torch.stack([gate.view(inter // B, B, Kd), up.view(inter // B, B, Kd)], dim=1).reshape(2 * inter, Kd)
+    g = x.double() @ gate.double().t()
+    want = (g * torch.sigmoid(g) * (x.double() @ up.double().t())).float()
+    out = K().gemm_tc_decode(x, w, None, splits=1, swiglu=True, out_dtype=torch.float32)
+    assert K().gemm_tc_status(True) == 0, "a bounded wait in the kernel ran out"
+    assert out.shape == (M, inter)
+    assert (out - want).abs().max() <= 2e-3
+    ob = K().gemm_tc_decode(x, w, None, splits=1, swiglu=True)
+    assert ob.dtype == torch.bfloat16
+    assert bool(((ob.float() - want).abs() <= want.abs() * 2.0 ** -7 + 2e-3).all())
+    # the same numbers as the product followed by the activation kernel (both round the
+    # float32 sums once)
+    gu = torch.empty(M, 2 * inter, device=DEV)
+    K().gemm_tc_decode(x, w, gu, None, 1)
+    two = torch.empty(M, inter, device=DEV)
+    K().swiglu(gu, two, B)
+    assert (two - out).abs().max() <= 1e-5
+    with pytest.raises(ValueError):
+        K().gemm_tc_decode(x, w, None, splits=2, swiglu=True)
+
+
 # ------------------------------------------------------ rotary + cache write
 def _paged(num_pages, Hkv, ps, D, dt):
     return (torch.zeros(num_pages, Hkv, ps, D, device=DEV, dtype=dt),

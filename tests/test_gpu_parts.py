@@ -60,11 +60,15 @@ def test_norm_part(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_feed_forward_part(dtype):
+@pytest.mark.parametrize("inter,tokens", [(172, 9), (192, 9), (192, 70), (320, 1)])
+def test_feed_forward_part(dtype, inter, tokens):
+    """172: gate rows then up rows.  Multiples of 64: alternating runs, with the activation
+    inside the product for a few tokens in bfloat16 and in its own kernel otherwise."""
     from servelab_b200.config import GatedMLPSpec
     from servelab_b200.parts import FEED_FORWARDS
-    part, w = _build(FEED_FORWARDS, GatedMLPSpec(hidden_size=72, intermediate_size=172), "mlp", dtype)
-    x = torch.randn(9, 72, device=DEV).to(DT[dtype])
+    part, w = _build(FEED_FORWARDS, GatedMLPSpec(hidden_size=72, intermediate_size=inter), "mlp", dtype)
+    assert part.block == (64 if inter % 64 == 0 else 0)
+    x = torch.randn(tokens, 72, device=DEV).to(DT[dtype])
     want = P.swiglu(x.float().cpu(), w["mlp.gate_proj.weight"], w["mlp.up_proj.weight"],
                     w["mlp.down_proj.weight"])
     got = part.forward(None, x)
