@@ -42,9 +42,16 @@ class SplitSum:
         return out
 
 
+# the current stream's handle without building a torch.cuda.Stream object for it (a few
+# microseconds a launch, which a step of a small model notices)
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
     global launch_count
     launch_count += 1
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
