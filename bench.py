@@ -174,6 +174,9 @@ def main(argv=None) -> int:
             linear_ops.fuse_swiglu = bool(int(value))
         elif name == "use_tc_prefill":
             K.use_tc_prefill = bool(int(value))
+        elif name == "fuse_decode_qkv":
+            from servelab_b200.ops import attention as attention_ops
+            attention_ops.fuse_decode_qkv = bool(int(value))
         elif name == "pdl":
             from servelab_b200.ops import library as kernel_library
             kernel_library.set_pdl(bool(int(value)))

@@ -324,6 +324,63 @@ def decode_ws_splits(num_seqs: int, num_kv_heads: int, group: int, longest_conte
     return max(1, min(max_splits, slots // max(pairs, 1), longest_uses))
 
 
+def decode_attention_takes(head_dim: int, page_size: int) -> bool:
+    """Whether the one-launch decode kernel takes this head size and page size."""
+    return has_fast_attention(head_dim) and \
+        bool(L.attention(head_dim).slb_decode_attention_ws_supported(page_size))
+
+
+def _decode_launch_shape(ctx, lib, q_device, num_heads, num_kv_heads):
+    """(splits, scratch, counters) of a launch of the one-launch decode kernel."""
+    S = ctx.num_seqs
+    group = num_heads // num_kv_heads
+    splits = decode_ws_force_splits or decode_ws_splits(
+        S, num_kv_heads, group, ctx.split_hint_len, lib.slb_decode_attention_ws_max_splits(),
+        lib.slb_decode_attention_ws_tile_keys())
+    scratch = counters = None
+    if splits > 1:
+        if lib.slb_decode_attention_ws_counters(S, num_heads, num_kv_heads) > _DECODE_COUNTERS:
+            splits = 1
+        else:
+            nbytes = lib.slb_decode_attention_ws_scratch_bytes(S, num_heads, splits)
+            scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=q_device)
+            counters = _decode_counter_buffer(q_device)
+    return splits, scratch, counters
+
+
+def decode_attention_fused(ctx, qkv, bias, inv_freq, rotary_dim, k_cache, v_cache, write_kv: bool,
+                           out, block_table, num_heads, num_kv_heads, head_dim, page_size, scale,
+                           window) -> None:
+    """A step of single tokens from the q|k|v product itself: ``qkv`` is the
+    product's bfloat16 result [S, (H + 2 Hkv) D] or its K-split partial sums
+    (``SplitSum``).  The attention kernel adds the bias, rotates q and k by the
+    request's position (its context length minus one), writes the new key and value
+    to the cache (``write_kv``) and attends, in one launch; the q/k/v kernel does not
+    run.  Only where ``decode_attention_takes(head_dim, page_size)``."""
+    lib = L.attention(head_dim)
+    parts = dense = None
+    nparts = part_stride = 0
+    if isinstance(qkv, SplitSum):
+        if bias is not None and qkv.bias is not None:
+            raise L.KernelError("decode_attention_fused: two biases")
+        bias = bias if bias is not None else qkv.bias
+        nparts, M, N = qkv.parts.shape
+        parts, part_stride, ld = qkv.parts, M * N, N
+    else:
+        if qkv.dtype != _BF16:
+            raise L.KernelError("decode_attention_fused: bfloat16 only")
+        dense, ld = qkv, qkv.stride(0)
+    splits, scratch, counters = _decode_launch_shape(ctx, lib, out.device, num_heads, num_kv_heads)
+    L.check(lib.slb_decode_attention_ws_fused_bf16(
+        _p(parts), int(nparts), int(part_stride), _p(dense), int(ld), _p(bias), _p(inv_freq),
+        int(rotary_dim), 1 if write_kv else 0, k_cache.data_ptr(), v_cache.data_ptr(),
+        out.data_ptr(), out.stride(0), block_table.data_ptr(), block_table.shape[1],
+        ctx.ctx_len.data_ptr(), _p(scratch), _p(counters), ctx.num_seqs, num_heads, num_kv_heads,
+        page_size, k_cache.shape[0], float(scale), int(window), splits, int(decode_ws_stages),
+        float(decode_ws_split_coef), int(decode_ws_unsplit_tiles), _stream()),
+        "decode_attention_fused")
+
+
 def decode_attention(ctx, q, k_cache, v_cache, out, block_table, num_heads, num_kv_heads,
                      head_dim, page_size, scale, window) -> None:
     """Attention for a step of single tokens (every q_len == 1): one launch; the
@@ -336,18 +393,7 @@ def decode_attention(ctx, q, k_cache, v_cache, out, block_table, num_heads, num_
                                head_dim, page_size, scale, window)
         return
     S = ctx.num_seqs
-    group = num_heads // num_kv_heads
-    splits = decode_ws_force_splits or decode_ws_splits(
-        S, num_kv_heads, group, ctx.split_hint_len, lib.slb_decode_attention_ws_max_splits(),
-        lib.slb_decode_attention_ws_tile_keys())
-    scratch = counters = None
-    if splits > 1:
-        if lib.slb_decode_attention_ws_counters(S, num_heads, num_kv_heads) > _DECODE_COUNTERS:
-            splits = 1
-        else:
-            nbytes = lib.slb_decode_attention_ws_scratch_bytes(S, num_heads, splits)
-            scratch = torch.empty(nbytes // 4, dtype=torch.float32, device=q.device)
-            counters = _decode_counter_buffer(q.device)
+    splits, scratch, counters = _decode_launch_shape(ctx, lib, q.device, num_heads, num_kv_heads)
     L.check(lib.slb_decode_attention_ws_bf16(
         q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
         out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.ctx_len.data_ptr(),

@@ -110,6 +110,8 @@ _ATTN_SIGNATURES = {
     "slb_prefill_attention_tc_status": [I],
     "slb_prefill_attention_tc_where": [P],
     "slb_decode_attention_ws_bf16": [P, I, P, P, P, I, P, I, P, P, P, I, I, I, I, I, F, I, I, I, F, I, P],
+    "slb_decode_attention_ws_fused_bf16": [P, I, LL, P, I, P, P, I, I, P, P, P, I, P, I, P, P, P, I, I,
+                                           I, I, I, F, I, I, I, F, I, P],
     "slb_decode_attention_ws_supported": [I],
     "slb_decode_attention_ws_status": [I],
     "slb_decode_attention_ws_max_splits": [],

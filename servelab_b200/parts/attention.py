@@ -4,8 +4,10 @@ Per step: one fused q|k|v product (weights concatenated at load), then one
 kernel that adds the q/k/v bias, rotates q and k by the token positions and
 writes k (rotated) and v into the request's pages, then attention of every query
 of the step over its request's cached keys (the step's own included), then the
-output projection.  Order and formulas: servelab/parallel/tp_model.py:48-53
-(projections with bias), :128-129 (rotation before the cache write), :136-157
+output projection.  In bfloat16 steps of single tokens the decode kernel can do the
+second and third of these itself, starting from the product (``ops.attention.fuse_decode_qkv``,
+off by default).  Order and formulas:
+servelab/parallel/tp_model.py:48-53 (projections with bias), :128-129 (rotation before the cache write), :136-157
 (scores * D^-1/2, causal mask, float32 softmax, P.V), :131 (bias-free output
 projection).  ``window`` limits the visible keys to the last w positions.
 
@@ -81,11 +83,17 @@ class PagedAttention(Mixer):
         s = self.spec
         T = x.shape[0]
         qkv = linear(x, self.w_qkv, consumer="rope")       # the next kernel may add K-split parts
-        q = torch.empty((T, self.q_size), dtype=x.dtype, device=x.device)
-        # (a SplitSum has no dtype of its own; q follows the activations)
         table = ctx.block_tables[cache.group]
         rot = self.position.rotary_table()
         inv_freq, rotary_dim = rot if rot is not None else (None, 0)
+        if A.fused_decode_applies(ctx, x.dtype, s.head_dim, cache.page_size):
+            out = torch.empty((T, self.q_size), dtype=x.dtype, device=x.device)
+            K.decode_attention_fused(ctx, qkv, self.b_qkv, inv_freq, rotary_dim, cache.k, cache.v,
+                                     owns_cache, out, table, s.num_heads, s.num_kv_heads,
+                                     s.head_dim, cache.page_size, self.scale, s.window or 0)
+            return linear(out, self.w_o, self.b_o, consumer="norm")
+        q = torch.empty((T, self.q_size), dtype=x.dtype, device=x.device)
+        # (a SplitSum has no dtype of its own; q follows the activations)
         K.qkv_rope_cache(qkv, self.b_qkv, ctx.positions, ctx.seq_of_token, table, cache.page_size,
                          inv_freq, rotary_dim, q, cache.k if owns_cache else None,
                          cache.v if owns_cache else None, s.num_heads, s.num_kv_heads, s.head_dim)

@@ -4,6 +4,7 @@ The tiny configurations differ in every size and option: layers, width, head
 counts and groups, head size, intermediate size (172 is no multiple of 8), vocabulary
 (300 is no power of two), rope theta, norm eps, tying, page size, and windowed
 layers (configuration C, whose q width 4*48 also differs from its hidden size).
+Configuration D has head size 64, which the fastest attention kernels take.
 """
 
 from __future__ import annotations
@@ -41,7 +42,18 @@ TINY_C = {
     "max_position_embeddings": 384, "torch_dtype": "float32", "eos_token_id": 299,
     "use_sliding_window": True, "sliding_window": 24, "max_window_layers": 2,
 }
-CONFIGS = {"A": (TINY_A, 0, 16), "B": (TINY_B, 2, 8), "C": (TINY_C, 7, 16)}  # cfg, seed, page
+# head size 64: the tensor-core kernels that the large shapes use (tcgen05 prefill, one-launch
+# decode from the q|k|v product) run inside a tiny model, one layer of it windowed
+TINY_D = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 72, "num_attention_heads": 6,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 200, "vocab_size": 384,
+    "rope_theta": 20000.0, "rms_norm_eps": 2e-6, "tie_word_embeddings": False,
+    "max_position_embeddings": 320, "torch_dtype": "float32", "eos_token_id": 383,
+    "use_sliding_window": True, "sliding_window": 40, "max_window_layers": 1,
+}
+CONFIGS = {"A": (TINY_A, 0, 16), "B": (TINY_B, 2, 8), "C": (TINY_C, 7, 16),
+           "D": (TINY_D, 11, 8)}  # cfg, seed, page
 
 
 def make_model(folder: str, cfg: dict, seed: int) -> str:

@@ -19,12 +19,12 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
 def model(request, tmp_path_factory):
     cfg, seed, page = H.CONFIGS[request.param]
     folder = str(tmp_path_factory.mktemp(f"gen_{request.param}"))
     H.make_model(folder, cfg, seed)
-    lengths = {"A": [5, 17, 33], "B": [1, 9, 40, 70], "C": [3, 26, 48]}[request.param]
+    lengths = {"A": [5, 17, 33], "B": [1, 9, 40, 70], "C": [3, 26, 48], "D": [2, 61, 90]}[request.param]
     prompts = [H.random_ids(n, cfg["vocab_size"] - 2, seed + 1 + i) for i, n in enumerate(lengths)]
     return {"name": request.param, "cfg": cfg, "folder": folder, "page": page, "prompts": prompts}
 

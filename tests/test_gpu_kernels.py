@@ -589,6 +589,96 @@ def test_decode_attention_one_launch(H, Hkv, D, ps, window, splits, stages, coef
         assert (out2.float().cpu() - want).abs().max() <= TOL["bfloat16"]
 
 
+@pytest.mark.parametrize("H,Hkv,D,ps,rot", [(7, 1, 64, 8, 64), (28, 4, 128, 16, 128), (2, 1, 256, 32, 64),
+                                            (20, 1, 64, 16, 0), (24, 3, 64, 256, 32),
+                                            (48, 2, 128, 16, 128)])
+@pytest.mark.parametrize("window", [0, 70])
+@pytest.mark.parametrize("splits,nparts", [(0, 0), (32, 3), (5, 1), (1, 2)])
+def test_decode_attention_from_the_qkv_product(H, Hkv, D, ps, rot, window, splits, nparts):
+    """The decode kernel that starts from the q|k|v product (bias, rotation, cache write
+    inside it) against float32 arithmetic and against the q/k/v kernel followed by the
+    decode kernel: the new key lands on the first row of a tile (context 65, 129), on
+    its last row (64, 128), in a page of its own and in the middle of a long context;
+    full, partial and no rotation; the product as bfloat16 and as K-split partial sums;
+    groups of 8 and 16 head rows and several head tiles a block; and a run that reads a
+    cache another run wrote (nothing may be written)."""
+    from servelab_b200.ops import kernels as kernels_module
+    from servelab_b200.ops.kernels import SplitSum
+    dt = torch.bfloat16
+    ctxs = [1, 63, 64, 65, 700, 2049, 17, 128, 129]
+    S = len(ctxs)
+    case = PagedCase(ctxs, [1] * S, H, Hkv, D, ps, dt, seed=D + splits + nparts)
+    g = torch.Generator().manual_seed(H + rot)
+    width = (H + 2 * Hkv) * D
+    x = torch.randn(S, width, generator=g)
+    bias = torch.randn(width, generator=g)
+    inv = P.rope_inv_freq(rot, 10000.0) if rot else None
+    if nparts:
+        ps_ = [torch.randn(S, width, generator=g) for _ in range(nparts - 1)]
+        parts = torch.stack(ps_ + [x - sum(ps_) if ps_ else x]).contiguous()
+        x = parts.sum(0) if nparts == 1 else x       # what the kernels add up, to rounding
+        src = SplitSum(parts.to(DEV), None, dt)
+    else:
+        x = x.to(dt).float()
+        src = x.to(dt).to(DEV)
+    # float32 arithmetic of the same step; the results go into the case as its q and newest k, v
+    y = x + bias
+    pos = torch.tensor([c - 1 for c in ctxs])
+    qf = y[:, :H * D].view(S, H, D)
+    kf = y[:, H * D:(H + Hkv) * D].view(S, Hkv, D)
+    vf = y[:, (H + Hkv) * D:].view(S, Hkv, D)
+    if rot:
+        qf = torch.cat([P.rope(qf[..., :rot], pos, inv), qf[..., rot:]], -1)
+        kf = torch.cat([P.rope(kf[..., :rot], pos, inv), kf[..., rot:]], -1)
+    for i in range(S):
+        case.q[i] = qf[i:i + 1].to(dt)
+        case.k[i][-1] = kf[i].to(dt)
+        case.v[i][-1] = vf[i].to(dt)
+    want = case.reference(window=window or None)
+    case.scatter()
+    for i, c in enumerate(ctxs):                     # the step's own rows are not in the cache yet
+        page = case.tables[i][(c - 1) // ps]
+        case.kc[page, :, (c - 1) % ps] = 55.0
+        case.vc[page, :, (c - 1) % ps] = -55.0
+    ctx, _, table = _ctx_for(case)
+    bias_d = bias.to(DEV)
+    inv_d = inv.to(DEV) if rot else None
+    scale = 1 / math.sqrt(D)
+    kernels_module.decode_ws_force_splits = splits
+    try:
+        # the q/k/v kernel, then the decode kernel
+        kc1, vc1 = case.kc.clone(), case.vc.clone()
+        q1 = torch.empty(S, H * D, device=DEV, dtype=dt)
+        K().qkv_rope_cache(src, bias_d, i32(pos.tolist()), i32(list(range(S))), table, ps, inv_d, rot, q1,
+                           kc1, vc1, H, Hkv, D)
+        out1 = torch.empty_like(q1)
+        K().decode_attention(ctx, q1, kc1, vc1, out1, table, H, Hkv, D, ps, scale, window)
+        assert (out1.float().cpu() - want).abs().max() <= TOL["bfloat16"]
+        if not K().decode_attention_takes(D, ps):
+            return
+        # one launch from the product
+        for _ in range(2):
+            kc2, vc2 = case.kc.clone(), case.vc.clone()
+            out2 = torch.full_like(q1, 7.0)
+            K().decode_attention_fused(ctx, src, bias_d, inv_d, rot, kc2, vc2, True, out2, table, H, Hkv,
+                                       D, ps, scale, window)
+            assert K().decode_attention_status(D, reset=True) == 0, "a bounded wait in the kernel gave up"
+            assert (out2.float().cpu() - want).abs().max() <= TOL["bfloat16"]
+            for a, b in ((kc2, kc1), (vc2, vc1)):        # at most one bfloat16 step apart, row for row
+                assert ((a.float() - b.float()).abs() <= 2.0 ** -7 * b.float().abs()).all()
+        assert all(int(c.abs().sum()) == 0 for c in kernels_module._decode_counters.values())
+        # a run that reads the cache of another run: the rows are there, nothing is written
+        kc3, vc3 = kc1.clone(), vc1.clone()
+        out3 = torch.full_like(q1, 7.0)
+        K().decode_attention_fused(ctx, src, bias_d, inv_d, rot, kc3, vc3, False, out3, table, H, Hkv, D,
+                                   ps, scale, window)
+        assert K().decode_attention_status(D, reset=True) == 0
+        assert torch.equal(kc3, kc1) and torch.equal(vc3, vc1)
+        assert (out3.float().cpu() - want).abs().max() <= TOL["bfloat16"]
+    finally:
+        kernels_module.decode_ws_force_splits = 0
+
+
 def test_decode_attention_many_launches_of_a_mixed_batch():
     """48 requests of very different lengths at the 7B head layout, 300 launches back to
     back with matrix products between them (producer and consumers, blocks that leave at

@@ -21,7 +21,7 @@ TOL = {"float32": 1e-5, "bfloat16": 2e-2}
 LENGTHS = [70, 45, 97, 33, 58, 81]
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
 def model(request, tmp_path_factory):
     cfg, seed, page = H.CONFIGS[request.param]
     folder = str(tmp_path_factory.mktemp(f"tiny_{request.param}"))
@@ -80,6 +80,20 @@ def test_mixed_with_page_reuse(model, dtype):
     total = sum(-(-len(v) // 64) * 64 for v in model["requests"].values())
     assert need < total, "the pool must be too small to hold all requests at once"
     _check(model, dtype, steps, need)
+
+
+def test_decode_steps_that_start_from_the_qkv_product(model):
+    """The optional form of a decode step in which the attention kernel adds bias, rotates
+    and writes the cache itself (head sizes the one-launch decode kernel takes)."""
+    if model["name"] != "D":
+        pytest.skip("needs a head size that is a multiple of 64")
+    from servelab_b200.ops import attention as A
+    A.fuse_decode_qkv = True
+    try:
+        _check(model, "bfloat16", H.trace_bulk_tail(model["requests"]))
+        _check(model, "bfloat16", H.trace_mixed(model["requests"], seed=11))
+    finally:
+        A.fuse_decode_qkv = False
 
 
 def test_float32_cut_invariance(model):
