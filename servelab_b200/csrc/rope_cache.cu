@@ -260,7 +260,10 @@ static int launch_qkv_rope_cache(const T* qkv, int ld_qkv, const float* parts, i
                         ((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16 == 0;
     if (vec_ok) {
         const int units = heads * (D / (2 * VEC));
-        int vthreads = units < 256 ? (units + 31) / 32 * 32 : 256;
+        // as few equal passes over the units as blocks of up to 512 threads allow (288 units:
+        // one pass of 288 threads, not a full pass of 256 and one that keeps a single warp busy)
+        const int passes = (units + 511) / 512;
+        int vthreads = ((units + passes - 1) / passes + 31) / 32 * 32;
         if (vthreads < rot / 2) vthreads = ((rot / 2 + 31) / 32 * 32 < 1024) ? (rot / 2 + 31) / 32 * 32 : 1024;
         return slb_launch(qkv_rope_cache_vec_kernel<T>, dim3(T_), dim3(vthreads), (size_t)rot * sizeof(float), st,
                           qkv, ld_qkv, bias, positions, seq_of_token, block_table, max_pages, page_size,
