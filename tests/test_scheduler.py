@@ -87,7 +87,8 @@ def test_budget_split_matches_the_reference_walkthrough():
 def test_cross_check_with_the_reference_scheduler():
     """Same arrivals through the reference's own scheduler (if its tree is at hand):
     identical (request, start, n) lists while no preemption happens."""
-    ref_root = os.environ.get("SERVELAB_REFERENCE", "/root/reference")
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref_root = os.environ.get("SERVELAB_REFERENCE", os.path.join(here, "baseline", "_ref"))
     if not os.path.isdir(os.path.join(ref_root, "servelab")):
         pytest.skip("reference tree not available")
     sys.path.insert(0, ref_root)
