@@ -170,8 +170,10 @@ def main(argv=None) -> int:
             setattr(K, name, int(value))
         elif name in ("tc_prefetch_bytes", "tc_prefetch_chunk", "tc_blocks_per_sm"):
             setattr(K, name, int(value))
-        elif name == "fuse_swiglu":
-            linear_ops.fuse_swiglu = bool(int(value))
+        elif name in ("fuse_swiglu", "cluster_sums", "fuse_qkv_rope"):
+            setattr(linear_ops, name, bool(int(value)))
+        elif name == "cluster_max_kblocks":
+            linear_ops.cluster_max_kblocks = int(value)
         elif name == "use_tc_prefill":
             K.use_tc_prefill = bool(int(value))
         elif name == "fuse_decode_qkv":

@@ -332,6 +332,236 @@ __global__ void gemm_tc_reduce_kernel(const float* __restrict__ partial, TO* __r
     out[(size_t)tok * ldo + n] = from_float<TO>(sum);
 }
 
+// ---- the K splits of a row tile as one thread-block cluster ----------------------
+// grid (row tiles of W, K splits), cluster (1, K splits, 1): the blocks that share a row
+// tile run at the same time and can read one another's shared memory.  Each block
+// accumulates its K range in tensor memory as above, parks the result in its own shared
+// memory, and after a cluster barrier block r adds up, in the order of the ranks, the
+// tokens r, r + splits, ... of all blocks and finishes them: no partial sums in global
+// memory, no second kernel, a fixed order of additions.
+//
+// What "finishes" means is the EPI parameter:
+//   EPI_STORE  out[tok, n] = sum + bias[n]
+//   EPI_ROPE   the q|k|v product of an attention layer: bias added, q and k rotated by the
+//              token's position, q written to q_out, k and v into the token's slot of the
+//              paged cache (the arithmetic of the kernel in rope_cache.cu).  A row tile
+//              must hold whole heads: head sizes 16, 32, 64, 128.
+enum { EPI_STORE = 0, EPI_ROPE = 1 };
+
+struct RopeEpilogue {
+    const float* bias;                  // [N] or null
+    const int* positions;               // [M]
+    const int* seq_of_token;            // [M]
+    const int* block_table;             // [requests][max_pages]
+    int max_pages, page_size;
+    const float* inv_freq;              // [rotary_dim / 2] or null
+    int rotary_dim;
+    bf16* q_out;
+    int ld_q;
+    bf16* k_cache;                      // null: nothing is written to the cache
+    bf16* v_cache;
+    int H, Hkv, D;
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+// every thread of every block of the cluster, warps converged
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank) {
+    uint32_t a;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
+    return v;
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
+    const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+    bf16* __restrict__ out, int ldo, const float* __restrict__ bias, int M, int N, int K, int ntok16,
+    int max_stages, int* __restrict__ status, const RopeEpilogue rope) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int B_STAGE_BYTES = b_stage_bytes(ntok16);
+    const int TC_STAGES = stages_for(ntok16, max_stages);
+    unsigned char* a_stage = base;
+    unsigned char* b_stage = base + TC_STAGES * A_STAGE_BYTES;
+    uint64_t* full = reinterpret_cast<uint64_t*>(base + TC_STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+    uint64_t* empty = full + TC_MAX_STAGES;
+    uint64_t* accum = empty + TC_MAX_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+    __shared__ float pair_vals[2][TC_BM];                    // EPI_ROPE: a token's row of the tile
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * TC_BM;
+    const int splits = gridDim.y, split = blockIdx.y;
+    const int kblocks = (K + TC_BK - 1) / TC_BK;
+    const int per = (kblocks + splits - 1) / splits;
+    const int kb_begin = min(kblocks, split * per);
+    const int kb_end = min(kblocks, kb_begin + per);
+    const int iters = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = *tmem_slot;
+    float* acc = reinterpret_cast<float*>(a_stage);          // [ntok16][TC_BM] once the ring is idle
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t bytes = A_STAGE_BYTES + (uint32_t)ntok16 * TC_BK * 2;
+            const int ahead = min(iters, TC_STAGES);
+            for (int i = 0; i < ahead; ++i) {
+                mbar_expect_tx(&full[i], bytes);
+                tma_load_2d(a_stage + i * A_STAGE_BYTES, &map_w, &full[i], (kb_begin + i) * TC_BK, n0);
+            }
+            pdl_wait();
+            for (int i = 0; i < ahead; ++i)
+                tma_load_2d(b_stage + i * B_STAGE_BYTES, &map_x, &full[i], (kb_begin + i) * TC_BK, 0);
+            for (int i = ahead; i < iters; ++i) {
+                const int s = i % TC_STAGES;
+                if (!mbar_wait(&empty[s], ((i / TC_STAGES) & 1) ^ 1)) {
+                    atomicCAS(status, 0, (1 << 8) | 2);
+                    break;
+                }
+                mbar_expect_tx(&full[s], bytes);
+                const int k = (kb_begin + i) * TC_BK;
+                tma_load_2d(a_stage + s * A_STAGE_BYTES, &map_w, &full[s], k, n0);
+                tma_load_2d(b_stage + s * B_STAGE_BYTES, &map_x, &full[s], k, 0);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                   ((uint32_t)(ntok16 >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < iters && ok; ++i) {
+                const int s = i % TC_STAGES;
+                if (!mbar_wait(&full[s], (i / TC_STAGES) & 1)) {
+                    atomicCAS(status, 0, (2 << 8) | 2);
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t adesc = umma_desc_sw128(smem_u32(a_stage + s * A_STAGE_BYTES));
+                const uint64_t bdesc = umma_desc_sw128(smem_u32(b_stage + s * B_STAGE_BYTES));
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; ++kk)
+                    umma_bf16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&empty[s]);
+            }
+            if (ok) umma_commit(accum);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------ epilogue, part 1: accumulator -> acc
+        pdl_wait();
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        bool ok = true;
+        if (iters > 0) {
+            ok = mbar_wait(accum, 0);
+            if (!ok) atomicCAS(status, 0, (3 << 8) | 2);
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        pdl_launch_dependents();
+        for (int c0 = 0; c0 < ntok16; c0 += 16) {
+            uint32_t v[16];
+            if (iters > 0 && ok) {
+                tmem_ld16(tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[(c0 + j) * TC_BM + row] = __uint_as_float(v[j]);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    cluster_sync_all();                                      // every block's acc is complete
+
+    if (warp >= 2) {
+        // ------------------------------- epilogue, part 2: this block's share of the tokens
+        const int row = (warp & 3) * 32 + lane;
+        const int n = n0 + row;
+        const uint32_t rank = cluster_rank(), nranks = cluster_size();
+        int parity = 0;
+        for (int tok = (int)rank; tok < M; tok += (int)nranks) {
+            const uint32_t addr = smem_u32(acc + tok * TC_BM + row);
+            float sum = 0.f;
+            for (uint32_t p = 0; p < nranks; ++p) sum += ld_peer_f32(addr, p);
+            if constexpr (EPI == EPI_STORE) {
+                if (n < N) out[(size_t)tok * ldo + n] = __float2bfloat16_rn(sum + (bias ? bias[n] : 0.f));
+            } else {
+                const int D = rope.D;
+                const int half = rope.inv_freq != nullptr ? rope.rotary_dim >> 1 : 0;
+                float v = (n < N) ? sum + (rope.bias ? rope.bias[n] : 0.f) : 0.f;
+                pair_vals[parity][row] = v;
+                asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps
+                if (n < N) {
+                    const int j = n / D, e = n - j * D;
+                    const bool is_v = j >= rope.H + rope.Hkv;
+                    const int pos = rope.positions[tok];
+                    if (!is_v && e < 2 * half) {
+                        const int i = e < half ? e : e - half;
+                        float sn, cs;
+                        sincosf((float)pos * rope.inv_freq[i], &sn, &cs);
+                        const float other = pair_vals[parity][e < half ? row + half : row - half];
+                        v = e < half ? v * cs - other * sn : v * cs + other * sn;
+                    }
+                    bf16* dst = nullptr;
+                    if (j < rope.H) {
+                        dst = rope.q_out + (size_t)tok * rope.ld_q + (size_t)j * D;
+                    } else if (rope.k_cache != nullptr) {
+                        const int page = rope.block_table[(size_t)rope.seq_of_token[tok] * rope.max_pages +
+                                                          pos / rope.page_size];
+                        if (page >= 0) {
+                            const int kvh = is_v ? j - rope.H - rope.Hkv : j - rope.H;
+                            dst = (is_v ? rope.v_cache : rope.k_cache) +
+                                  (((size_t)page * rope.Hkv + kvh) * rope.page_size + pos % rope.page_size) * D;
+                        }
+                    }
+                    if (dst != nullptr) dst[e] = __float2bfloat16_rn(v);
+                }
+                parity ^= 1;
+            }
+        }
+    }
+    __syncwarp();
+    cluster_sync_all();                                      // no block leaves while its acc is read
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TC_TMEM_COLS)
+                     : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -396,9 +626,108 @@ int run(const bf16* x, int ldx, const bf16* W, int ldw, TO* out, int ldo, const 
                       (const float*)workspace, out, ldo, bias, M, N, splits);
 }
 
+template <typename... KArgs, typename... Args>
+int launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, int cluster_y, size_t smem,
+                   cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = (unsigned)cluster_y;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = slb_pdl_enabled ? 2 : 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+constexpr int TC_MAX_CLUSTER = 8;       // the portable cluster size
+
+template <int EPI>
+int run_cluster(const bf16* x, int ldx, const bf16* W, int ldw, bf16* out, int ldo, const float* bias,
+                int M, int N, int K, int splits, int max_stages, const RopeEpilogue& rope,
+                cudaStream_t st) {
+    CUtensorMap map_w, map_x;
+    const int ntok16 = (M + 15) / 16 * 16;
+    int rc = make_map(&map_w, W, N, K, ldw, TC_BM);
+    if (rc != 0) return rc;
+    rc = make_map(&map_x, x, M, K, ldx, ntok16);
+    if (rc != 0) return rc;
+    static bool configured = false;                         // per instantiation
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_cluster_kernel<EPI>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BUDGET);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int stages = stages_for(ntok16, max_stages);
+    // the parked accumulator [ntok16][128] floats lives in the W stages of the ring
+    if ((size_t)stages * A_STAGE_BYTES < (size_t)ntok16 * TC_BM * 4) return SLB_ERR_BAD_ARG;
+    const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + b_stage_bytes(ntok16)) + TC_SMEM_TAIL;
+    int* status = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&status, tc_status_word);
+    if (e != cudaSuccess) return (int)e;
+    return launch_cluster(gemm_tc_cluster_kernel<EPI>, dim3((N + TC_BM - 1) / TC_BM, splits), dim3(TC_THREADS),
+                          splits, smem, st, map_w, map_x, out, ldo, bias, M, N, K, ntok16, max_stages, status,
+                          rope);
+}
+
+int check_cluster_args(const bf16* x, int ldx, const bf16* W, int ldw, int M, int N, int K, int splits) {
+    if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K) return SLB_ERR_BAD_ARG;
+    if (((uintptr_t)x | (uintptr_t)W) % 16) return SLB_ERR_BAD_ARG;
+    if (M > TC_MAX_TOK) return SLB_ERR_TOO_LARGE;
+    const int kblocks = (K + TC_BK - 1) / TC_BK;
+    if (splits < 1 || splits > kblocks) return SLB_ERR_BAD_ARG;
+    if (splits > TC_MAX_CLUSTER) return SLB_ERR_TOO_LARGE;
+    return 0;
+}
+
 }  // namespace
 
 extern "C" {
+
+// out[M, N] = x . W^T (+ bias), bfloat16, the K splits of a row tile as one cluster (at most 8):
+// no workspace, no second kernel.
+int slb_gemm_tc_cluster_bf16(const bf16* x, int ldx, const bf16* W, int ldw, bf16* out, int ldo,
+                             const float* bias, int M, int N, int K, int splits, int max_stages,
+                             cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (ldo < N || out == nullptr) return SLB_ERR_BAD_ARG;
+    const int rc = check_cluster_args(x, ldx, W, ldw, M, N, K, splits);
+    if (rc != 0) return rc;
+    const RopeEpilogue none = {};
+    return run_cluster<EPI_STORE>(x, ldx, W, ldw, out, ldo, bias, M, N, K, splits, max_stages, none, st);
+}
+
+// The q|k|v product of an attention layer with what follows it: W is [(H + 2 Hkv) D, K]
+// (q heads, k heads, v heads), and the kernel adds the bias, rotates q and k by
+// positions[tok] (angles pos * inv_freq[i], float32), writes q to q_out [M, H D] and k, v to
+// the cache slot of the token (block_table[seq_of_token[tok]][pos / page_size]); k_cache ==
+// null writes no cache.  Head sizes 16, 32, 64, 128.
+int slb_gemm_tc_qkv_rope_bf16(const bf16* x, int ldx, const bf16* W, int ldw, const float* bias,
+                              const int* positions, const int* seq_of_token, const int* block_table,
+                              int max_pages, int page_size, const float* inv_freq, int rotary_dim,
+                              bf16* q_out, int ld_q, bf16* k_cache, bf16* v_cache, int M, int H, int Hkv,
+                              int D, int K, int splits, int max_stages, cudaStream_t st) {
+    if (M <= 0) return 0;
+    if (H <= 0 || Hkv <= 0 || D < 16 || D > TC_BM || TC_BM % D || page_size <= 0 || max_pages <= 0)
+        return SLB_ERR_BAD_ARG;
+    if (rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1) || ld_q < H * D) return SLB_ERR_BAD_ARG;
+    if (positions == nullptr || seq_of_token == nullptr || block_table == nullptr || q_out == nullptr ||
+        (k_cache == nullptr) != (v_cache == nullptr))
+        return SLB_ERR_BAD_ARG;
+    const int N = (H + 2 * Hkv) * D;
+    const int rc = check_cluster_args(x, ldx, W, ldw, M, N, K, splits);
+    if (rc != 0) return rc;
+    RopeEpilogue rope = {bias, positions, seq_of_token, block_table, max_pages, page_size, inv_freq,
+                         inv_freq != nullptr ? rotary_dim : 0, q_out, ld_q, k_cache, v_cache, H, Hkv, D};
+    return run_cluster<EPI_ROPE>(x, ldx, W, ldw, nullptr, 0, nullptr, M, N, K, splits, max_stages, rope, st);
+}
 
 // workspace: float32 [splits * M * N] when splits > 1 (may be null otherwise).
 // max_stages: cap on the depth of the shared-memory ring (0: as deep as fits).

@@ -504,6 +504,49 @@ def gemm_tc_decode(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor]
     return out
 
 
+TC_MAX_CLUSTER = 8             # K splits that can share a row tile as one thread-block cluster
+TC_ROPE_HEAD_DIMS = (16, 32, 64, 128)   # a 128-row tile of the q|k|v product holds whole heads
+
+
+def tc_cluster_splits(n_out: int, k: int) -> int:
+    return min(tc_decode_splits(n_out, k), TC_MAX_CLUSTER)
+
+
+def gemm_tc_cluster(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+                    bias: Optional[torch.Tensor] = None, splits: int = 0) -> torch.Tensor:
+    """out[M,N] = x . w^T (+ bias) in bfloat16 for up to 64 tokens, like
+    ``gemm_tc_decode``, but the K splits of a row tile form a thread-block cluster and
+    add their results up through one another's shared memory: no partial sums in
+    global memory and no reduction kernel; a fixed order of additions."""
+    M, Kd = x.shape
+    N = w.shape[0]
+    splits = splits or tc_cluster_splits(N, Kd)
+    if out is None:
+        out = torch.empty((M, N), dtype=_BF16, device=x.device)
+    L.check(L.core().slb_gemm_tc_cluster_bf16(
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), _p(bias),
+        M, N, Kd, splits, tc_max_stages, _stream()), "gemm_tc_cluster")
+    return out
+
+
+def gemm_tc_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Tensor],
+                     positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                     page_size: int, inv_freq: Optional[torch.Tensor], rotary_dim: int,
+                     q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+                     v_cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int,
+                     head_dim: int, splits: int = 0) -> None:
+    """The q|k|v product of up to 64 tokens together with ``qkv_rope_cache``: the product's
+    epilogue adds the bias, rotates q and k, writes q to ``q_out`` and k, v into the paged
+    cache.  Head sizes in ``TC_ROPE_HEAD_DIMS``."""
+    M, Kd = x.shape
+    splits = splits or tc_cluster_splits(w_qkv.shape[0], Kd)
+    L.check(L.core().slb_gemm_tc_qkv_rope_bf16(
+        x.data_ptr(), x.stride(0), w_qkv.data_ptr(), w_qkv.stride(0), _p(bias), positions.data_ptr(),
+        seq_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size,
+        _p(inv_freq), rotary_dim, q_out.data_ptr(), q_out.stride(0), _p(k_cache), _p(v_cache), M,
+        num_heads, num_kv_heads, head_dim, Kd, splits, tc_max_stages, _stream()), "gemm_tc_qkv_rope")
+
+
 def gemm_tc_status(reset: bool = False) -> int:
     """0 unless a bounded wait inside the tcgen05 kernel ran out (synchronises)."""
     return L.core().slb_gemm_tc_status(1 if reset else 0)

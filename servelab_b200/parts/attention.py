@@ -25,7 +25,7 @@ import torch
 from ..cache.manager import PagedKVRequest
 from ..ops import attention as A
 from ..ops import kernels as K
-from ..ops.linear import linear
+from ..ops.linear import linear, qkv_projection
 from ..weights.source import BIAS, MATRIX, TensorDecl
 from .base import Mixer
 from .registry import POSITIONS, build_part, register_mixer
@@ -82,11 +82,11 @@ class PagedAttention(Mixer):
     def forward(self, ctx, x, cache, owns_cache):
         s = self.spec
         T = x.shape[0]
-        qkv = linear(x, self.w_qkv, consumer="rope")       # the next kernel may add K-split parts
         table = ctx.block_tables[cache.group]
         rot = self.position.rotary_table()
         inv_freq, rotary_dim = rot if rot is not None else (None, 0)
         if A.fused_decode_applies(ctx, x.dtype, s.head_dim, cache.page_size):
+            qkv = linear(x, self.w_qkv, consumer="rope")   # the next kernel may add K-split parts
             out = torch.empty((T, self.q_size), dtype=x.dtype, device=x.device)
             K.decode_attention_fused(ctx, qkv, self.b_qkv, inv_freq, rotary_dim, cache.k, cache.v,
                                      owns_cache, out, table, s.num_heads, s.num_kv_heads,
@@ -94,9 +94,9 @@ class PagedAttention(Mixer):
             return linear(out, self.w_o, self.b_o, consumer="norm")
         q = torch.empty((T, self.q_size), dtype=x.dtype, device=x.device)
         # (a SplitSum has no dtype of its own; q follows the activations)
-        K.qkv_rope_cache(qkv, self.b_qkv, ctx.positions, ctx.seq_of_token, table, cache.page_size,
-                         inv_freq, rotary_dim, q, cache.k if owns_cache else None,
-                         cache.v if owns_cache else None, s.num_heads, s.num_kv_heads, s.head_dim)
+        qkv_projection(x, self.w_qkv, self.b_qkv, ctx.positions, ctx.seq_of_token, table,
+                       cache.page_size, inv_freq, rotary_dim, q, cache.k if owns_cache else None,
+                       cache.v if owns_cache else None, s.num_heads, s.num_kv_heads, s.head_dim)
         out = torch.empty_like(q)
         A.paged_attention(ctx, q, cache.k, cache.v, out, table, s.num_heads, s.num_kv_heads,
                           s.head_dim, cache.page_size, self.scale, s.window or 0)

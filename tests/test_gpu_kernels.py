@@ -826,3 +826,106 @@ def test_gemm_tcgen05_decode(M, N, Kd, splits):
         K().gemm_tc_decode(x2, w, other, b, splits)
         assert torch.equal(other[1:], o32[1:])
     assert K().gemm_tc_status(True) == 0
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 16, 17, 64])
+@pytest.mark.parametrize("N,Kd,splits", [(3584, 3584, 0), (4608, 3584, 8), (3584, 18944, 0), (1000, 152, 1),
+                                         (24, 18944, 7), (300, 4096, 3), (896, 4864, 0)])
+def test_gemm_tcgen05_cluster(M, N, Kd, splits):
+    """The K splits of a row tile as a thread-block cluster that adds its results up
+    through shared memory: against float64, bit for bit the same on a second launch, a
+    token independent of its neighbours, more tokens than ranks and fewer."""
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    w = (torch.randn(N, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    b = torch.randn(N, device=DEV)
+    want = (x.double() @ w.double().t() + b.double()).float()
+    out = torch.full((M, N), 9.0, device=DEV, dtype=torch.bfloat16)
+    K().gemm_tc_cluster(x, w, out, b, splits)
+    assert K().gemm_tc_status(True) == 0, "a bounded wait in the kernel ran out"
+    assert (out.float() - want).abs().max() <= 2e-2
+    again = torch.empty_like(out)
+    K().gemm_tc_cluster(x, w, again, b, splits)
+    assert torch.equal(again, out)
+    nobias = K().gemm_tc_cluster(x, w, None, None, splits)
+    assert (nobias.float() - (want - b)).abs().max() <= 2e-2
+    if M >= 2:
+        x2 = x.clone()
+        x2[0] = 0
+        other = K().gemm_tc_cluster(x2, w, None, b, splits)
+        assert torch.equal(other[1:], out[1:])
+    assert K().gemm_tc_status(True) == 0
+
+
+@pytest.mark.parametrize("H,Hkv,D,rot,hidden", [(28, 4, 128, 128, 3584), (14, 2, 64, 64, 896),
+                                                (6, 2, 64, 32, 72), (5, 1, 32, 32, 160),
+                                                (3, 3, 16, 0, 64), (9, 1, 128, 64, 1024)])
+@pytest.mark.parametrize("M", [1, 8, 13, 64])
+def test_gemm_tcgen05_qkv_with_rotation_and_cache_write(H, Hkv, D, rot, hidden, M):
+    """The q|k|v product whose epilogue adds the bias, rotates and writes the cache, against
+    the library-free path it replaces (product, then the q/k/v kernel) and against float32
+    arithmetic: tokens of two requests at scattered positions, partial and no rotation, a
+    run that writes no cache."""
+    ps = 4
+    g = torch.Generator().manual_seed(M + D)
+    positions = torch.randperm(max(M, 40), generator=g)[:M].tolist()   # distinct: a slot per token
+    seq = [t % 2 for t in range(M)]
+    pages = max(positions) // ps + 1
+    perm = torch.randperm(2 * pages, generator=g).tolist()
+    table = i32([perm[:pages], perm[pages:]])
+    width = (H + 2 * Hkv) * D
+    x = torch.randn(M, hidden, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(width, hidden, generator=g) / math.sqrt(hidden)).bfloat16().to(DEV)
+    bias = torch.randn(width, generator=g).to(DEV)
+    inv = P.rope_inv_freq(rot, 10000.0).to(DEV) if rot else None
+    # float32 arithmetic
+    y = (x.double() @ w.double().t()).float() + bias
+    qf = y[:, :H * D].view(M, H, D).cpu()
+    kf = y[:, H * D:(H + Hkv) * D].view(M, Hkv, D).cpu()
+    vf = y[:, (H + Hkv) * D:].view(M, Hkv, D).cpu()
+    pos_t = torch.tensor(positions)
+    if rot:
+        qf = torch.cat([P.rope(qf[..., :rot], pos_t, inv.cpu()), qf[..., rot:]], -1)
+        kf = torch.cat([P.rope(kf[..., :rot], pos_t, inv.cpu()), kf[..., rot:]], -1)
+    q = torch.full((M, H * D), 7.0, device=DEV, dtype=torch.bfloat16)
+    kc, vc = _paged(2 * pages, Hkv, ps, D, torch.bfloat16)
+    K().gemm_tc_qkv_rope(x, w, bias, i32(positions), i32(seq), table, ps, inv, rot, q, kc, vc, H, Hkv, D)
+    assert K().gemm_tc_status(True) == 0, "a bounded wait in the kernel ran out"
+    tol = 3e-2
+    assert (q.float().cpu().view(M, H, D) - qf).abs().max() <= tol
+    tab = table.cpu()
+    written = set()
+    for t in range(M):
+        page = int(tab[seq[t], positions[t] // ps])
+        written.add((page, positions[t] % ps))
+        assert (kc[page, :, positions[t] % ps].float().cpu() - kf[t]).abs().max() <= tol
+        assert (vc[page, :, positions[t] % ps].float().cpu() - vf[t]).abs().max() <= tol
+    for page in range(2 * pages):                            # no other slot is touched
+        for slot in range(ps):
+            if (page, slot) not in written:
+                assert float(kc[page, :, slot].abs().max()) == 0 and float(vc[page, :, slot].abs().max()) == 0
+    # the two-kernel path gives the same to a bfloat16 step (it rounds the product first)
+    q2 = torch.empty_like(q)
+    kc2, vc2 = _paged(2 * pages, Hkv, ps, D, torch.bfloat16)
+    mid = K().gemm_tc_cluster(x, w, None, None)
+    K().qkv_rope_cache(mid, bias, i32(positions), i32(seq), table, ps, inv, rot, q2, kc2, vc2, H, Hkv, D)
+    assert (q2.float() - q.float()).abs().max() <= 2 * tol
+    assert (kc2.float() - kc.float()).abs().max() <= 2 * tol
+    # a run that reads another run's cache writes none
+    q3 = torch.empty_like(q)
+    kc3, vc3 = _paged(2 * pages, Hkv, ps, D, torch.bfloat16)
+    K().gemm_tc_qkv_rope(x, w, bias, i32(positions), i32(seq), table, ps, inv, rot, q3, None, None, H, Hkv, D)
+    assert torch.equal(q3, q) and float(kc3.abs().max()) == 0
+    assert K().gemm_tc_status(True) == 0
+
+
+def test_kernel_bench_program_runs_on_small_cases(capsys):
+    """The microbenchmark module end to end on its smallest cases: every group, a table
+    with one row per case, status words all zero (exit code 0)."""
+    from servelab_b200.bench import kernel_bench
+    rc = kernel_bench.main(["--shape", "qwen2.5-0.5b", "--batches", "2", "--contexts", "130",
+                            "--prefill-lengths", "70", "--tokens", "3", "--markdown"])
+    out = capsys.readouterr().out
+    assert rc == 0, out
+    for name in ("decode attention (one launch)", "prefill attention (tcgen05)", "q|k|v product",
+                 "LM head", "residual add + RMSNorm", "SwiGLU", "sampler"):
+        assert name in out, name

@@ -526,8 +526,12 @@ def test_feed_forward_with_routing_defined_in_the_test(tmp_path):
 # --------------------------------------------------------------------------- #
 
 def test_split_sums_consumed_by_norm_and_rope_kernels(tmp_path):
-    """With ``defer_split_sums`` the tcgen05 product leaves float32 partial sums and the
-    norm / rotary kernels add them; logits must agree whichever consumers take them."""
+    """The ways a decode step sums the K splits of its narrow products: a reduction kernel,
+    float32 partial sums that the norm / rotary kernels add (``defer_split_sums``), and
+    thread-block clusters that add them through shared memory, with and without the
+    rotation and cache write in the q|k|v product's epilogue.  Logits must agree with the
+    plain implementation and with one another whichever runs."""
+    from servelab_b200.ops import kernels as kernels_module
     from servelab_b200.ops import linear as linear_ops
     from servelab_b200.replay import TraceSession
     cfg = dict(H.TINY_B, hidden_size=512, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
@@ -536,16 +540,27 @@ def test_split_sums_consumed_by_norm_and_rope_kernels(tmp_path):
     reqs = {"a": H.random_ids(40, 512, 1), "b": H.random_ids(37, 512, 2)}
     steps = H.trace_bulk_tail(reqs, tail=16)
     outs = {}
-    saved = dict(linear_ops.defer_split_sums)
-    for flag in (False, True):
-        linear_ops.defer_split_sums.update(rope=flag, norm=flag)
+    saved = (dict(linear_ops.defer_split_sums), linear_ops.cluster_sums, linear_ops.fuse_qkv_rope)
+    modes = {"reduce": (False, False, False), "parts": (True, False, False),
+             "cluster": (True, True, False), "cluster+rope": (True, True, True)}
+    for name, (defer, cluster, rope) in modes.items():
+        linear_ops.defer_split_sums.update(rope=defer, norm=defer)
+        linear_ops.cluster_sums, linear_ops.fuse_qkv_rope = cluster, rope
         try:
+            before = kernels_module.launch_count
             sess = TraceSession(folder, "bfloat16", H.peak_tokens(steps), page_size=8, max_live=2)
-            outs[flag] = H.collect(steps, H.run_session(sess, steps), 512)
+            outs[name] = H.collect(steps, H.run_session(sess, steps), 512)
+            outs[name + " launches"] = kernels_module.launch_count - before
         finally:
-            linear_ops.defer_split_sums.update(saved)
+            linear_ops.defer_split_sums.update(saved[0])
+            linear_ops.cluster_sums, linear_ops.fuse_qkv_rope = saved[1], saved[2]
+    assert kernels_module.gemm_tc_status(True) == 0
+    # fewer kernels run, form by form
+    assert outs["reduce launches"] > outs["parts launches"] >= outs["cluster launches"] \
+        > outs["cluster+rope launches"]
     ref = {rid: H.plain_logits(folder, ids) for rid, ids in reqs.items()}
-    for rid, ids in reqs.items():
-        for pos in range(len(ids)):
-            assert float(np.abs(outs[True][rid][pos] - ref[rid][pos]).max()) <= 3e-2
-            assert float(np.abs(outs[True][rid][pos] - outs[False][rid][pos]).max()) <= 2e-2
+    for name in modes:
+        for rid, ids in reqs.items():
+            for pos in range(len(ids)):
+                assert float(np.abs(outs[name][rid][pos] - ref[rid][pos]).max()) <= 3e-2, name
+                assert float(np.abs(outs[name][rid][pos] - outs["reduce"][rid][pos]).max()) <= 2e-2, name
