@@ -170,7 +170,7 @@ def main(argv=None) -> int:
             setattr(K, name, int(value))
         elif name in ("tc_prefetch_bytes", "tc_prefetch_chunk", "tc_blocks_per_sm"):
             setattr(K, name, int(value))
-        elif name in ("fuse_swiglu", "cluster_sums", "fuse_qkv_rope"):
+        elif name in ("fuse_swiglu", "cluster_sums", "fuse_qkv_rope", "fuse_resid_norm"):
             setattr(linear_ops, name, bool(int(value)))
         elif name == "cluster_max_kblocks":
             linear_ops.cluster_max_kblocks = int(value)

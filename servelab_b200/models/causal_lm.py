@@ -103,11 +103,10 @@ class CausalLM:
 
     @staticmethod
     def _plain_unless(part, delta):
-        """An update may travel as partial sums of a K-split product (``SplitSum``);
-        parts that do not say they accept one get the plain tensor."""
-        if isinstance(delta, K.SplitSum) and not getattr(part, "accepts_split_sum", False):
-            return delta.materialize()
-        return delta
+        """An update may travel unfinished (``SplitSum``: partial sums of a K-split product;
+        ``DeferredLinear``: a product that has not run); parts that do not say they accept
+        the form get the plain tensor."""
+        return K.plain_unless(part, delta)
 
     # ----------------------------------------------------------- forward
     def forward(self, ctx, caches: Dict[int, LayerCache]) -> torch.Tensor:

@@ -42,6 +42,63 @@ class SplitSum:
         return out
 
 
+class DeferredLinear:
+    """A product x . w^T (+ bias) [M, N] that has not run yet and whose result is an update
+    of the float32 residual stream.  The norm that receives it runs it as ONE kernel that
+    adds the result into the stream and leaves the sums of squares the norm needs
+    (``gemm_tc_resid``).  ``materialize()`` runs the plain product."""
+    accept_flag = "accepts_deferred_linear"
+
+    def __init__(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]):
+        self.x, self.w, self.bias, self.dtype = x, w, bias, x.dtype
+
+    @property
+    def shape(self):
+        return (self.x.shape[0], self.w.shape[0])
+
+    def materialize(self) -> torch.Tensor:
+        return gemm_tc_cluster(self.x, self.w, None, self.bias)
+
+
+class LazyNorm:
+    """rmsnorm(resid) * weight [M, h] that has not been computed: ``resid`` (float32, every
+    update added) and ``sumsq`` [tiles, M], the sums of squares of its rows per 128-column
+    tile.  The tcgen05 products build their input from it while they load
+    (``gemm_tc_qkv_rope``, ``gemm_tc_decode``); ``materialize()`` runs the norm kernel."""
+    accept_flag = "accepts_lazy_norm"
+
+    def __init__(self, resid: torch.Tensor, sumsq: torch.Tensor, weight: torch.Tensor, eps: float,
+                 dtype: torch.dtype):
+        self.resid, self.sumsq, self.weight, self.eps, self.dtype = resid, sumsq, weight, eps, dtype
+        self.device = resid.device
+
+    @property
+    def shape(self):
+        return self.resid.shape
+
+    def materialize(self) -> torch.Tensor:
+        out = torch.empty(self.resid.shape, dtype=self.dtype, device=self.resid.device)
+        add_rmsnorm(self.resid, None, self.weight, self.eps, out)
+        return out
+
+    def args(self):
+        return (self.resid.data_ptr(), self.resid.stride(0), self.sumsq.data_ptr(), self.sumsq.shape[0],
+                self.weight.data_ptr(), float(self.eps))
+
+
+_NO_NORM = (None, 0, None, 0, None, 0.0)
+SplitSum.accept_flag = "accepts_split_sum"
+
+
+def plain_unless(part, value):
+    """``value`` as a tensor unless it is one of the unfinished forms above and ``part``
+    says (by the form's flag) that it takes them."""
+    flag = getattr(type(value), "accept_flag", None)
+    if flag is not None and not getattr(part, flag, False):
+        return value.materialize()
+    return value
+
+
 # the current stream's handle without building a torch.cuda.Stream object for it (a few
 # microseconds a launch, which a step of a small model notices)
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
@@ -466,7 +523,7 @@ def _next_weight_args(next_weight: Optional[torch.Tensor]):
 SWIGLU_BLOCK = 64
 
 
-def gemm_tc_decode(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor],
+def gemm_tc_decode(x, w: torch.Tensor, out: Optional[torch.Tensor],
                    bias: Optional[torch.Tensor] = None, splits: int = 0,
                    defer_sum: bool = False, out_dtype: Optional[torch.dtype] = None,
                    next_weight: Optional[torch.Tensor] = None, swiglu: bool = False):
@@ -493,10 +550,13 @@ def gemm_tc_decode(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor]
     deferred = defer_sum and splits > 1
     if out is None and not deferred:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    lazy = isinstance(x, LazyNorm)                          # the loader builds x from the stream
     L.check(L.core().slb_gemm_tc_decode_bf16(
-        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _p(out), out.stride(0) if out is not None else N,
+        None if lazy else x.data_ptr(), 0 if lazy else x.stride(0), w.data_ptr(), w.stride(0), _p(out),
+        out.stride(0) if out is not None else N,
         _p(bias), _p(ws), 1 if out_dtype == _F32 else 0, M, N, Kd, splits, tc_max_stages,
-        1 if deferred else 0, *_next_weight_args(next_weight), 1 if swiglu else 0, _stream()),
+        1 if deferred else 0, *_next_weight_args(next_weight), 1 if swiglu else 0,
+        *(x.args() if lazy else _NO_NORM), _stream()),
         "gemm_tc_decode")
     if deferred:
         return SplitSum(ws, bias, out_dtype)
@@ -529,7 +589,25 @@ def gemm_tc_cluster(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor
     return out
 
 
-def gemm_tc_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Tensor],
+LAZY_NORM_MAX_TOKENS = 16      # tokens up to which a product builds its input from a LazyNorm
+
+
+def gemm_tc_resid(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
+                  resid: torch.Tensor, splits: int = 0) -> torch.Tensor:
+    """resid += x . w^T (+ bias) on the float32 residual stream [M, N], in one kernel (the K
+    splits as a cluster); returns sumsq [ceil(N / 128), M]: the sums of squares of the updated
+    rows per 128-column tile."""
+    M, Kd = x.shape
+    N = w.shape[0]
+    splits = splits or tc_cluster_splits(N, Kd)
+    sumsq = torch.empty((-(-N // 128), M), dtype=_F32, device=x.device)
+    L.check(L.core().slb_gemm_tc_resid_bf16(
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _p(bias), resid.data_ptr(),
+        resid.stride(0), sumsq.data_ptr(), M, N, Kd, splits, tc_max_stages, _stream()), "gemm_tc_resid")
+    return sumsq
+
+
+def gemm_tc_qkv_rope(x, w_qkv: torch.Tensor, bias: Optional[torch.Tensor],
                      positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                      page_size: int, inv_freq: Optional[torch.Tensor], rotary_dim: int,
                      q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
@@ -540,11 +618,13 @@ def gemm_tc_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.
     cache.  Head sizes in ``TC_ROPE_HEAD_DIMS``."""
     M, Kd = x.shape
     splits = splits or tc_cluster_splits(w_qkv.shape[0], Kd)
+    lazy = isinstance(x, LazyNorm)                          # the loader builds x from the stream
     L.check(L.core().slb_gemm_tc_qkv_rope_bf16(
-        x.data_ptr(), x.stride(0), w_qkv.data_ptr(), w_qkv.stride(0), _p(bias), positions.data_ptr(),
-        seq_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size,
-        _p(inv_freq), rotary_dim, q_out.data_ptr(), q_out.stride(0), _p(k_cache), _p(v_cache), M,
-        num_heads, num_kv_heads, head_dim, Kd, splits, tc_max_stages, _stream()), "gemm_tc_qkv_rope")
+        None if lazy else x.data_ptr(), 0 if lazy else x.stride(0), w_qkv.data_ptr(), w_qkv.stride(0),
+        _p(bias), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], page_size, _p(inv_freq), rotary_dim, q_out.data_ptr(), q_out.stride(0),
+        _p(k_cache), _p(v_cache), M, num_heads, num_kv_heads, head_dim, Kd, splits, tc_max_stages,
+        *(x.args() if lazy else _NO_NORM), _stream()), "gemm_tc_qkv_rope")
 
 
 def gemm_tc_status(reset: bool = False) -> int:

@@ -87,6 +87,35 @@ cluster_max_kblocks = 16   # k-blocks (of 64) per block up to which the cluster 
 fuse_qkv_rope = True       # the q|k|v product of a decode step rotates and writes the cache itself
 
 
+# A product whose result updates the residual stream hands itself to the norm that follows
+# (``K.DeferredLinear``): the norm runs it as one kernel that adds into the stream and leaves
+# sums of squares, and returns ``K.LazyNorm``, from which the next product builds its input
+# while it loads.  A decode-step layer is then five kernels (q|k|v, attention, o, gate|up,
+# down) instead of seven.  Off: measured on the 7B shape it is no faster (3.12 against 3.07 ms a
+# step at batch 8, 2.97 against 2.91 at batch 1).  With programmatic dependent launch a norm
+# kernel between two products costs about 1 us, not its 2.2 us alone, because the product after
+# it fetches weights meanwhile; a product that builds its input itself starts its first MMA
+# later (sums of squares, then residual rows, then the conversion: 46.0 against 43.6 us for
+# gate|up, 10.7 against 9.9 for q|k|v), which costs the same again.
+fuse_resid_norm = False
+
+
+def _w_ok(w) -> bool:
+    return w.shape[1] % 8 == 0 and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0
+
+
+def _lazy_ok(x, w) -> bool:
+    """Whether the tcgen05 product of ``x`` (a LazyNorm) by ``w`` can build its input itself."""
+    return (x.dtype == torch.bfloat16 and 0 < x.shape[0] <= K.LAZY_NORM_MAX_TOKENS and _w_ok(w)
+            and x.resid.stride(0) % 4 == 0 and x.resid.data_ptr() % 16 == 0)
+
+
+def _deferred_ok(x, w, M, out_dtype) -> bool:
+    return (fuse_resid_norm and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16
+            and 0 < M <= min(tc_max_tokens, K.LAZY_NORM_MAX_TOKENS) and _tc_ok(x, w, M)
+            and K.tc_decode_splits(w.shape[0], w.shape[1]) > 1)
+
+
 def _cluster_ok(x, w, M) -> bool:
     if not (cluster_sums and x.dtype == torch.bfloat16 and 0 < M <= tc_max_tokens and _tc_ok(x, w, M)):
         return False
@@ -106,13 +135,16 @@ def qkv_projection(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Te
     (``k_cache`` None: no cache write).  One kernel for decode steps in bfloat16 with a head
     size the product's epilogue takes; otherwise the product, then the q/k/v kernel."""
     M = x.shape[0]
-    if (fuse_qkv_rope and x.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16
-            and head_dim in K.TC_ROPE_HEAD_DIMS and 0 < M <= tc_max_tokens and _tc_ok(x, w_qkv, M)
-            and K.tc_decode_splits(w_qkv.shape[0], w_qkv.shape[1]) > 1
-            and q_out.data_ptr() % 2 == 0):
+    lazy = isinstance(x, K.LazyNorm)
+    fusable = (fuse_qkv_rope and x.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16
+               and head_dim in K.TC_ROPE_HEAD_DIMS and 0 < M <= tc_max_tokens
+               and K.tc_decode_splits(w_qkv.shape[0], w_qkv.shape[1]) > 1)
+    if fusable and (_lazy_ok(x, w_qkv) if lazy else _tc_ok(x, w_qkv, M)):
         K.gemm_tc_qkv_rope(x, w_qkv, bias, positions, seq_of_token, block_table, page_size, inv_freq,
                            rotary_dim, q_out, k_cache, v_cache, num_heads, num_kv_heads, head_dim)
         return
+    if lazy:
+        x = x.materialize()
     qkv = linear(x, w_qkv, consumer="rope")                # the next kernel may add K-split parts
     K.qkv_rope_cache(qkv, bias, positions, seq_of_token, block_table, page_size, inv_freq,
                      rotary_dim, q_out, k_cache, v_cache, num_heads, num_kv_heads, head_dim)
@@ -125,9 +157,13 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, block: int) -> torch.
     then the activation kernel."""
     M = x.shape[0]
     inter = w_gate_up.shape[0] // 2
-    if (fuse_swiglu and x.dtype == torch.bfloat16 and block == K.SWIGLU_BLOCK and _tc_ok(x, w_gate_up, M)
-            and K.tc_decode_splits(w_gate_up.shape[0], w_gate_up.shape[1]) == 1):
+    lazy = isinstance(x, K.LazyNorm)
+    if (fuse_swiglu and x.dtype == torch.bfloat16 and block == K.SWIGLU_BLOCK
+            and K.tc_decode_splits(w_gate_up.shape[0], w_gate_up.shape[1]) == 1
+            and (_lazy_ok(x, w_gate_up) if lazy else _tc_ok(x, w_gate_up, M))):
         return K.gemm_tc_decode(x, w_gate_up, None, swiglu=True, next_weight=_next_weight(w_gate_up))
+    if lazy:
+        x = x.materialize()
     gu = linear(x, w_gate_up)
     act = torch.empty((M, inter), dtype=x.dtype, device=x.device)
     K.swiglu(gu, act, block)
@@ -138,10 +174,15 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
            out_dtype: Optional[torch.dtype] = None, consumer: Optional[str] = None):
     """``consumer`` ("rope" or "norm"): the caller hands the result to a kernel of that
     kind, which accepts a ``SplitSum`` (partial sums of a K-split product); it may then
-    get one instead of a tensor."""
+    get one instead of a tensor.  With "norm" the caller returns the result as its update of
+    the residual stream and may get a ``K.DeferredLinear`` (the product has not run)."""
+    if isinstance(x, K.LazyNorm):
+        x = x.materialize()
     M, Kd = x.shape
     N = w.shape[0]
     out_dtype = out_dtype or x.dtype
+    if consumer == "norm" and _deferred_ok(x, w, M, out_dtype):
+        return K.DeferredLinear(x, w, bias)
     if x.dtype == torch.float32:
         out = torch.empty((M, N), dtype=torch.float32, device=x.device)
         K.gemm_simt(x, w, out, bias)

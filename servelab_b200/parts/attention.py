@@ -34,6 +34,7 @@ from .registry import POSITIONS, build_part, register_mixer
 @register_mixer("paged_attention")
 class PagedAttention(Mixer):
     graph_safe = True
+    accepts_lazy_norm = True     # ``x`` may be a K.LazyNorm: the q|k|v product builds its input
 
     def __init__(self, spec, prefix, env):
         super().__init__(spec, prefix, env)
@@ -85,14 +86,15 @@ class PagedAttention(Mixer):
         table = ctx.block_tables[cache.group]
         rot = self.position.rotary_table()
         inv_freq, rotary_dim = rot if rot is not None else (None, 0)
+        device = x.device
         if A.fused_decode_applies(ctx, x.dtype, s.head_dim, cache.page_size):
             qkv = linear(x, self.w_qkv, consumer="rope")   # the next kernel may add K-split parts
-            out = torch.empty((T, self.q_size), dtype=x.dtype, device=x.device)
+            out = torch.empty((T, self.q_size), dtype=x.dtype, device=device)
             K.decode_attention_fused(ctx, qkv, self.b_qkv, inv_freq, rotary_dim, cache.k, cache.v,
                                      owns_cache, out, table, s.num_heads, s.num_kv_heads,
                                      s.head_dim, cache.page_size, self.scale, s.window or 0)
             return linear(out, self.w_o, self.b_o, consumer="norm")
-        q = torch.empty((T, self.q_size), dtype=x.dtype, device=x.device)
+        q = torch.empty((T, self.q_size), dtype=x.dtype, device=device)
         # (a SplitSum has no dtype of its own; q follows the activations)
         qkv_projection(x, self.w_qkv, self.b_qkv, ctx.positions, ctx.seq_of_token, table,
                        cache.page_size, inv_freq, rotary_dim, q, cache.k if owns_cache else None,

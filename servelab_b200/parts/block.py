@@ -8,7 +8,7 @@ happens inside the next norm kernel.
 
 from __future__ import annotations
 
-from ..ops.kernels import SplitSum
+from ..ops.kernels import plain_unless
 from .base import Block
 from .registry import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, build_part, part_class,
                        register_block)
@@ -50,18 +50,22 @@ class PreNormBlock(Block):
     def matrices(self):
         return self.mixer.matrices() + self.feed_forward.matrices()
 
-    accepts_split_sum = True      # the incoming ``delta`` may be a SplitSum
+    accepts_split_sum = True          # the incoming ``delta`` may be a SplitSum
+    accepts_deferred_linear = True    # ... or a product that has not run
 
     @staticmethod
-    def _for_norm(norm, delta):
-        """A K-split product may arrive as partial sums; norms that cannot add them
-        themselves get the plain tensor."""
-        if isinstance(delta, SplitSum) and not getattr(norm, "accepts_split_sum", False):
-            return delta.materialize()
-        return delta
+    def _norm(norm, consumer, ctx, resid, delta):
+        """The norm before ``consumer``.  An update may arrive unfinished (partial sums of
+        a K-split product, a product that has not run); a norm that does not take the
+        form gets the plain tensor.  A norm that can leave its own result unfinished does
+        so if the consumer takes it."""
+        delta = plain_unless(norm, delta)
+        if getattr(norm, "returns_lazy_norm", False) and getattr(consumer, "accepts_lazy_norm", False):
+            return norm.forward(ctx, resid, delta, lazy_ok=True)
+        return norm.forward(ctx, resid, delta)
 
     def forward(self, ctx, resid, delta, cache, owns_cache):
-        x = self.mixer_norm.forward(ctx, resid, self._for_norm(self.mixer_norm, delta))
+        x = self._norm(self.mixer_norm, self.mixer, ctx, resid, delta)
         a = self.mixer.forward(ctx, x, cache, owns_cache)
-        x = self.ff_norm.forward(ctx, resid, self._for_norm(self.ff_norm, a))
+        x = self._norm(self.ff_norm, self.feed_forward, ctx, resid, a)
         return resid, self.feed_forward.forward(ctx, x)

@@ -19,6 +19,7 @@ from .registry import register_feed_forward
 @register_feed_forward("gated_mlp")
 class GatedMLP(FeedForward):
     graph_safe = True
+    accepts_lazy_norm = True     # ``x`` may be a K.LazyNorm: the gate|up product builds its input
 
     def __init__(self, spec, prefix, env):
         super().__init__(spec, prefix, env)

@@ -918,6 +918,81 @@ def test_gemm_tcgen05_qkv_with_rotation_and_cache_write(H, Hkv, D, rot, hidden, 
     assert K().gemm_tc_status(True) == 0
 
 
+@pytest.mark.parametrize("M", [1, 7, 16])
+@pytest.mark.parametrize("N,Kd,splits", [(3584, 3584, 0), (3584, 18944, 0), (896, 4864, 0), (200, 1024, 3),
+                                         (72, 128, 1)])
+def test_gemm_tcgen05_into_the_residual_stream(M, N, Kd, splits):
+    """The product whose epilogue adds into the float32 residual stream and leaves the sums
+    of squares per 128-column tile, and the norm built from them: against float64; the
+    LazyNorm's own ``materialize`` against the norm formula."""
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    w = (torch.randn(N, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    b = torch.randn(N, device=DEV)
+    resid0 = torch.randn(M, N, device=DEV)
+    want = (resid0.double() + x.double() @ w.double().t() + b.double())
+    resid = resid0.clone()
+    sumsq = K().gemm_tc_resid(x, w, b, resid, splits)
+    assert K().gemm_tc_status(True) == 0, "a bounded wait in the kernel ran out"
+    assert (resid.double() - want).abs().max() <= 1e-3
+    tiles = -(-N // 128)
+    assert sumsq.shape == (tiles, M)
+    for t in range(tiles):
+        sq = (want[:, t * 128:(t + 1) * 128] ** 2).sum(1)
+        assert ((sumsq[t].double() - sq).abs() <= 1e-3 * (1 + sq)).all()
+    again = resid0.clone()
+    sumsq2 = K().gemm_tc_resid(x, w, b, again, splits)
+    assert torch.equal(again, resid) and torch.equal(sumsq2, sumsq)
+    weight = torch.randn(N, device=DEV)
+    lazy = K().LazyNorm(resid, sumsq, weight, 1e-5, torch.bfloat16)
+    normed = (want / torch.sqrt((want ** 2).mean(1, keepdim=True) + 1e-5) * weight.double()).float()
+    assert (lazy.materialize().float() - normed).abs().max() <= 2e-2 * max(1.0, float(normed.abs().max()))
+
+
+@pytest.mark.parametrize("M", [1, 8, 13, 16])
+@pytest.mark.parametrize("hidden,inter", [(3584, 1024), (896, 4864), (520, 640), (72, 128)])
+def test_gemm_tcgen05_products_that_build_their_input_from_the_stream(M, hidden, inter):
+    """The q|k|v product and the gate|up product with the RMS norm of the residual stream as
+    their input, built by the loader warp (last k-block partial: 520 = 8 * 64 + 8): against
+    the same products fed with the norm kernel's result, and against float64."""
+    g = torch.Generator().manual_seed(M + hidden)
+    H_, Hkv, D = 4, 2, 64
+    resid = (torch.randn(M, hidden, generator=g) * 2).to(DEV)
+    weight = (1 + 0.1 * torch.randn(hidden, generator=g)).to(DEV)
+    eps = 1e-6
+    tiles = -(-hidden // 128)
+    sumsq = torch.stack([(resid[:, t * 128:(t + 1) * 128] ** 2).sum(1) for t in range(tiles)]).contiguous()
+    lazy = K().LazyNorm(resid, sumsq, weight, eps, torch.bfloat16)
+    x = torch.empty(M, hidden, device=DEV, dtype=torch.bfloat16)
+    K().add_rmsnorm(resid.clone(), None, weight, eps, x)
+    # gate|up with the activation, rows alternating in runs of 64
+    w_gu = (torch.randn(2 * inter, hidden, generator=g) / math.sqrt(hidden)).bfloat16().to(DEV)
+    a = K().gemm_tc_decode(x, w_gu, None, splits=1, swiglu=True)
+    b = K().gemm_tc_decode(lazy, w_gu, None, splits=1, swiglu=True)
+    assert K().gemm_tc_status(True) == 0, "a bounded wait in the kernel ran out"
+    y = (x.double() @ w_gu.double().t()).view(M, inter // 64, 2, 64)
+    want = (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(M, inter).float()
+    assert (a.float() - want).abs().max() <= 2e-2 * max(1.0, float(want.abs().max()))
+    assert (b.float() - a.float()).abs().max() <= 2e-2 * max(1.0, float(want.abs().max()))
+    # q|k|v with rotation and cache write
+    width = (H_ + 2 * Hkv) * D
+    w = (torch.randn(width, hidden, generator=g) / math.sqrt(hidden)).bfloat16().to(DEV)
+    bias = torch.randn(width, generator=g).to(DEV)
+    inv = P.rope_inv_freq(D, 10000.0).to(DEV)
+    ps = 4
+    positions = torch.randperm(40, generator=g)[:M].tolist()
+    table = i32([list(range(10))])
+    seq = [0] * M
+    outs = []
+    for src in (x, lazy):
+        q = torch.full((M, H_ * D), 7.0, device=DEV, dtype=torch.bfloat16)
+        kc, vc = _paged(10, Hkv, ps, D, torch.bfloat16)
+        K().gemm_tc_qkv_rope(src, w, bias, i32(positions), i32(seq), table, ps, inv, D, q, kc, vc, H_, Hkv, D)
+        outs.append((q, kc, vc))
+    assert K().gemm_tc_status(True) == 0
+    for u, v in zip(outs[0], outs[1]):
+        assert (u.float() - v.float()).abs().max() <= 4e-2
+
+
 def test_kernel_bench_program_runs_on_small_cases(capsys):
     """The microbenchmark module end to end on its smallest cases: every group, a table
     with one row per case, status words all zero (exit code 0)."""
