@@ -172,8 +172,8 @@ def main(argv=None) -> int:
             setattr(K, name, int(value))
         elif name in ("fuse_swiglu", "cluster_sums", "fuse_qkv_rope", "fuse_resid_norm"):
             setattr(linear_ops, name, bool(int(value)))
-        elif name == "cluster_max_kblocks":
-            linear_ops.cluster_max_kblocks = int(value)
+        elif name in ("cluster_max_kblocks", "cluster_long_k_max_tokens"):
+            setattr(linear_ops, name, int(value))
         elif name == "use_tc_prefill":
             K.use_tc_prefill = bool(int(value))
         elif name == "fuse_decode_qkv":

@@ -174,7 +174,7 @@ def bench_prefill_attention(shape, peaks, device, lengths, twin: bool) -> List[R
     return rows
 
 
-def bench_products(shape, peaks, device, token_counts) -> List[Row]:
+def bench_products(shape, peaks, device, token_counts, only: Optional[List[str]] = None) -> List[Row]:
     """The matrix products of a layer and the LM head as the engine dispatches them
     (``ops.linear``): this package's tcgen05 kernel for few tokens, the vendor GEMM above."""
     import torch
@@ -185,6 +185,8 @@ def bench_products(shape, peaks, device, token_counts) -> List[Row]:
                 ("gate|up product + SwiGLU", 2 * inter, h, "swiglu"), ("down product", h, inter, "norm"),
                 ("LM head", vocab, h, "f32")]
     rows = []
+    if only:
+        products = [p for p in products if any(o in p[0] for o in only)]
     for name, N, Kd, kind in products:
         for M in token_counts:
             if kind == "f32" and M > 64:
@@ -318,6 +320,8 @@ def main(argv=None) -> int:
     ap.add_argument("--contexts", default="512,2048,8192,32768", help="decode attention: keys a request")
     ap.add_argument("--prefill-lengths", default="512,2048,8192", help="prefill attention: prompt tokens")
     ap.add_argument("--tokens", default="1,8,16,64,2048", help="products and element-wise kernels")
+    ap.add_argument("--products", default="", help="products: only those whose name contains one of "
+                    "these comma-separated pieces (q|k|v, o product, gate|up, down, LM head)")
     ap.add_argument("--no-twins", action="store_true", help="skip the plain twins of the attention kernels")
     ap.add_argument("--peaks", default="", help="JSON file with hbm_gbs and bf16_tflops")
     ap.add_argument("--markdown", action="store_true")
@@ -345,7 +349,8 @@ def main(argv=None) -> int:
             rows += bench_prefill_attention(shape, peaks, device, _ints(args.prefill_lengths),
                                             not args.no_twins)
         elif g == "products":
-            rows += bench_products(shape, peaks, device, _ints(args.tokens))
+            rows += bench_products(shape, peaks, device, _ints(args.tokens),
+                                   [p for p in args.products.split(",") if p])
         else:
             rows += bench_elementwise(shape, peaks, device, _ints(args.tokens))
     print(f"{args.shape}: hidden {shape[0]}, heads {shape[1]}/{shape[2]} x {shape[3]}, intermediate "

@@ -84,6 +84,7 @@ def _tc_ok(x, w, M):
 # stay with the partial sums: 26.7 against 27.3 us.
 cluster_sums = True
 cluster_max_kblocks = 16   # k-blocks (of 64) per block up to which the cluster form is used
+cluster_long_k_max_tokens = 64   # products with longer K ranges use it from 17 tokens up to here
 fuse_qkv_rope = True       # the q|k|v product of a decode step rotates and writes the cache itself
 
 
@@ -117,14 +118,19 @@ def _deferred_ok(x, w, M, out_dtype) -> bool:
 
 
 def _cluster_ok(x, w, M) -> bool:
-    if not (cluster_sums and x.dtype == torch.bfloat16 and 0 < M <= tc_max_tokens and _tc_ok(x, w, M)):
+    if not (cluster_sums and x.dtype == torch.bfloat16 and 0 < M <= K.TC_MAX_TOKENS and _w_ok(w)
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
         return False
     N, Kd = w.shape
     want = K.tc_decode_splits(N, Kd)
     if want <= 1:
         return False
     kblocks = -(-Kd // 64)
-    return -(-kblocks // min(want, K.TC_MAX_CLUSTER)) <= cluster_max_kblocks
+    if -(-kblocks // min(want, K.TC_MAX_CLUSTER)) <= cluster_max_kblocks:
+        return M <= tc_max_tokens
+    # long K ranges (down): streaming the weights is most of the time, and the cluster form
+    # beats the vendor GEMM between 17 and 64 tokens (30.8 against 34.1 us with the norm, 7B shape)
+    return tc_max_tokens < M <= cluster_long_k_max_tokens
 
 
 def qkv_projection(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Tensor], positions,

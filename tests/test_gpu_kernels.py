@@ -373,6 +373,27 @@ def test_bf16_linear_dispatch_shapes():
         assert y32.dtype == torch.float32 and (y32 - want).abs().max() <= 2e-3
 
 
+@pytest.mark.parametrize("N,Kd", [(3584, 3584), (3584, 18944), (4608, 3584), (5120, 13824), (896, 4864)])
+def test_bf16_linear_at_every_token_count_of_a_step(N, Kd):
+    """``linear`` at the layer sizes of the large shapes for 1 to 80 tokens: whichever kernel
+    the dispatch picks (cluster form, partial sums, vendor GEMM), the result agrees with
+    float64, as a tensor and as the update a norm consumes."""
+    from servelab_b200.ops.linear import linear
+    w = (torch.randn(N, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
+    for M in (1, 8, 16, 17, 40, 64, 65, 80):
+        x = torch.randn(M, Kd, device=DEV).bfloat16()
+        want = (x.double() @ w.double().t()).float()
+        y = linear(x, w)
+        assert y.shape == (M, N) and (y.float() - want).abs().max() <= 3e-2, M
+        d = linear(x, w, consumer="norm")
+        resid = torch.zeros(M, N, device=DEV)
+        out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        K().add_rmsnorm(resid, K().plain_unless(None, d) if not isinstance(d, K().SplitSum) else d,
+                        torch.ones(N, device=DEV), 1e-6, out)
+        assert (resid - want).abs().max() <= 3e-2, M
+    assert K().gemm_tc_status(True) == 0
+
+
 # ------------------------------------------------------------------- sampling
 def test_argmax_takes_the_first_of_equal_maxima():
     V = 152064 + 7
