@@ -174,6 +174,8 @@ def main(argv=None) -> int:
             setattr(linear_ops, name, bool(int(value)))
         elif name in ("cluster_max_kblocks", "cluster_long_k_max_tokens"):
             setattr(linear_ops, name, int(value))
+        elif name == "tc_max_cluster":                      # at most 8, the portable cluster size
+            K.TC_MAX_CLUSTER = int(value)
         elif name == "use_tc_prefill":
             K.use_tc_prefill = bool(int(value))
         elif name == "fuse_decode_qkv":
