@@ -16,6 +16,12 @@
 // every SM; with more than one split the blocks write float32 partial sums and a
 // second kernel adds them in a fixed order (deterministic).
 //
+// A second kernel (gemm_tc_cluster_kernel, further down) runs the K splits of a row tile as
+// one thread-block cluster that adds its accumulators up through distributed shared memory,
+// with epilogues that finish the result (store, q|k|v rotation and cache write, add into the
+// residual stream); both kernels can build the x operand from the float32 residual stream
+// (the RMS norm before the product) instead of fetching it.
+//
 // Every wait on an mbarrier is bounded: after SLB_TC_SPIN_LIMIT polls the role
 // records a code in the status word, leaves its loop, and the block frees its TMEM
 // and returns, so a wrong descriptor cannot hang the GPU.
