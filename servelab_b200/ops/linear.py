@@ -176,6 +176,32 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, block: int) -> torch.
     return act
 
 
+def which_kernel(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                 consumer: Optional[str] = None) -> str:
+    """The kernel ``linear`` runs for these operands: "deferred" (none yet: the norm that
+    follows runs the product), "simt" (CUDA cores), "tc_cluster" / "tc" (this package's
+    tcgen05 kernels, K splits as a cluster / as partial sums or unsplit), "skinny"
+    (mma.sync), "vendor" (library GEMM) or "empty"."""
+    M, Kd = x.shape
+    N = w.shape[0]
+    out_dtype = out_dtype or x.dtype
+    if consumer == "norm" and _deferred_ok(x, w, M, out_dtype):
+        return "deferred"
+    if x.dtype == torch.float32:
+        return "simt"
+    if M == 0:
+        return "empty"
+    if out_dtype == torch.bfloat16 and _cluster_ok(x, w, M):
+        return "tc_cluster"
+    if _tc_ok(x, w, M):
+        return "tc"
+    if _skinny_ok(x, w, M):
+        return "skinny"
+    if Kd % 8 or N % 8:
+        return "simt"
+    return "vendor"
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, consumer: Optional[str] = None):
     """``consumer`` ("rope" or "norm"): the caller hands the result to a kernel of that
@@ -184,30 +210,22 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     the residual stream and may get a ``K.DeferredLinear`` (the product has not run)."""
     if isinstance(x, K.LazyNorm):
         x = x.materialize()
-    M, Kd = x.shape
-    N = w.shape[0]
+    M, N = x.shape[0], w.shape[0]
     out_dtype = out_dtype or x.dtype
-    if consumer == "norm" and _deferred_ok(x, w, M, out_dtype):
+    kernel = which_kernel(x, w, out_dtype, consumer)
+    if kernel == "deferred":
         return K.DeferredLinear(x, w, bias)
-    if x.dtype == torch.float32:
-        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
-        K.gemm_simt(x, w, out, bias)
-        return out
-    # bfloat16 activations
-    if M == 0:
+    if kernel == "empty":
         return torch.empty((0, N), dtype=out_dtype, device=x.device)
-    if out_dtype == torch.bfloat16 and _cluster_ok(x, w, M):
+    if kernel == "tc_cluster":
         return K.gemm_tc_cluster(x, w, None, bias)
-    if _tc_ok(x, w, M):
+    if kernel == "tc":
         return K.gemm_tc_decode(x, w, None, bias, defer_sum=defer_split_sums.get(consumer, False),
                                 out_dtype=out_dtype, next_weight=_next_weight(w))
-    if _skinny_ok(x, w, M):
-        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        K.gemm_skinny(x, w, out, bias)
-        return out
-    if Kd % 8 or N % 8:
-        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        K.gemm_simt(x, w, out, bias)
+    if kernel in ("simt", "skinny"):
+        out = torch.empty((M, N), dtype=torch.float32 if x.dtype == torch.float32 else out_dtype,
+                          device=x.device)
+        (K.gemm_simt if kernel == "simt" else K.gemm_skinny)(x, w, out, bias)
         return out
     if out_dtype == torch.float32:
         out = torch.mm(x, w.t(), out_dtype=torch.float32)

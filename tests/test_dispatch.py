@@ -1,0 +1,70 @@
+"""Which kernel a matrix product of a step goes to (``ops.linear.which_kernel``), decided
+on the host from shapes alone: checked here without a GPU for the layer sizes of the three
+large shapes, with the SM count of a B200."""
+
+import pytest
+import torch
+
+from servelab_b200.ops import kernels as K
+from servelab_b200.ops import linear as L
+
+SHAPES = {  # hidden, q width, q|k|v width, intermediate, vocabulary
+    "0.5b": (896, 896, 1152, 4864, 151936),
+    "7b": (3584, 3584, 4608, 18944, 152064),
+    "14b": (5120, 5120, 7168, 13824, 152064),
+}
+
+
+@pytest.fixture(autouse=True)
+def b200(monkeypatch):
+    monkeypatch.setattr(K, "_sm_count", 148)
+
+
+def _ops(m, n, k, dtype=torch.bfloat16):
+    return (torch.empty((m, k), dtype=dtype, device="meta"), torch.empty((n, k), dtype=dtype, device="meta"))
+
+
+@pytest.mark.parametrize("shape", sorted(SHAPES))
+def test_decode_steps_run_this_package_s_tensor_core_kernels(shape):
+    h, q, qkv, inter, vocab = SHAPES[shape]
+    for m in (1, 8, 16):
+        assert L.which_kernel(*_ops(m, qkv, h), consumer="rope") == "tc_cluster"
+        assert L.which_kernel(*_ops(m, h, q), consumer="norm") == "tc_cluster"
+        if shape == "0.5b":      # 76 row tiles: three K splits still fit; the activation is a kernel
+            assert L.which_kernel(*_ops(m, 2 * inter, h)) == "tc_cluster"
+        else:                    # wide: no K split, the activation in the product's epilogue
+            assert L.which_kernel(*_ops(m, 2 * inter, h)) == "tc"
+            assert K.tc_decode_splits(2 * inter, h) == 1
+        assert L.which_kernel(*_ops(m, vocab, h), out_dtype=torch.float32) == "tc"
+    # the down product: long K ranges; partial sums up to 16 tokens unless it is small
+    kinds = {m: L.which_kernel(*_ops(m, h, inter), consumer="norm") for m in (8, 32, 64, 65)}
+    if shape == "0.5b":
+        assert kinds == {8: "tc_cluster", 32: "vendor", 64: "vendor", 65: "vendor"}
+    else:
+        assert kinds == {8: "tc", 32: "tc_cluster", 64: "tc_cluster", 65: "vendor"}
+
+
+def test_many_tokens_go_to_the_vendor_gemm_and_ragged_or_float32_ones_to_cuda_cores():
+    h, q, qkv, inter, vocab = SHAPES["7b"]
+    for m in (65, 512, 2048):
+        for n, k in ((qkv, h), (h, q), (2 * inter, h), (h, inter)):
+            assert L.which_kernel(*_ops(m, n, k)) == "vendor"
+    assert L.which_kernel(*_ops(100, 172, 64)) == "simt"                    # 172 rows: not a multiple of 8
+    assert L.which_kernel(*_ops(40, 172, 64)) == "tc"                       # ... which the tcgen05 kernel takes
+    assert L.which_kernel(*_ops(3, 64, 172)) == "simt"                      # K = 172: rows not 16-byte aligned
+    assert L.which_kernel(*_ops(8, h, q, torch.float32)) == "simt"          # the 32-bit path
+    assert L.which_kernel(*_ops(0, h, q)) == "empty"
+    # gate|up and the LM head stay on the tcgen05 kernel up to 64 tokens, the narrow products do not
+    assert L.which_kernel(*_ops(64, 2 * inter, h)) == "tc"
+    assert L.which_kernel(*_ops(64, qkv, h)) == "vendor"
+
+
+def test_switches_change_the_decision(monkeypatch):
+    h, q, qkv, inter, vocab = SHAPES["7b"]
+    monkeypatch.setattr(L, "cluster_sums", False)
+    assert L.which_kernel(*_ops(8, h, q), consumer="norm") == "tc"
+    assert L.which_kernel(*_ops(32, h, inter), consumer="norm") == "vendor"
+    monkeypatch.setattr(L, "fuse_resid_norm", True)
+    assert L.which_kernel(*_ops(8, h, q), consumer="norm") == "deferred"
+    assert L.which_kernel(*_ops(8, h, q)) == "tc"                            # only an update of the stream
+    assert L.which_kernel(*_ops(17, h, q), consumer="norm") == "vendor"
