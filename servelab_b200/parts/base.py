@@ -25,6 +25,15 @@ Kinds of part and what each must provide (beyond ``declare`` and ``load``):
   Block              ``forward(ctx, resid, delta, cache, owns_cache)`` ->
                      (resid, delta): the float32 stream and a not-yet-added
                      update, so that the add fuses with the next norm.
+
+Optional, for parts that want to take part in kernel fusion across part boundaries: a
+value handed from one part to the next may be unfinished (``ops.kernels.SplitSum``: partial
+sums of a K-split product; ``DeferredLinear``: a product that has not run; ``LazyNorm``: a
+norm that has not run).  A part says which forms it takes with class attributes
+(``accepts_split_sum``, ``accepts_deferred_linear`` for an incoming update,
+``accepts_lazy_norm`` for an incoming ``x``); a norm that can leave its own result
+unfinished sets ``returns_lazy_norm`` and takes ``lazy_ok=True`` in ``forward``.  A part that
+sets none of these always gets and returns plain tensors.
 """
 
 from __future__ import annotations
