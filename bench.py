@@ -166,8 +166,10 @@ def main(argv=None) -> int:
             K.tc_max_stages = int(value)
         elif name == "decode_ctas_per_sm":
             K.decode_ctas_per_sm = int(value)
-        elif name in ("decode_ws_stages", "decode_ws_force_splits"):
+        elif name in ("decode_ws_stages", "decode_ws_force_splits", "decode_ws_unsplit_tiles"):
             setattr(K, name, int(value))
+        elif name == "decode_ws_split_coef":
+            K.decode_ws_split_coef = float(value)
         elif name in ("tc_prefetch_bytes", "tc_prefetch_chunk", "tc_blocks_per_sm"):
             setattr(K, name, int(value))
         elif name in ("fuse_swiglu", "cluster_sums", "fuse_qkv_rope", "fuse_resid_norm"):
