@@ -21,6 +21,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 
@@ -30,7 +31,7 @@ class BatchEntry:
     tokens: Sequence[int]
     start: int                                   # position of tokens[0]
     want: Sequence[int] = ()                     # indices into ``tokens`` whose logits are wanted
-    block_tables: Sequence[Sequence[int]] = ()   # one table per cache group
+    block_tables: Sequence[Sequence[int]] = ()   # one table per cache group (lists or int32 arrays)
     state_slot: int = 0
     table_stamps: Sequence[int] = ()             # per group: changes iff the table changed
                                                  # (empty: unknown, always copy)
@@ -108,16 +109,27 @@ class StepContext:
             hv = host.numpy()
             hv[:] = 0
         o_tok, o_pos, o_seq, o_cu, o_ctx, o_slot, o_rows = offsets[:7]
-        t = 0
-        hv[o_cu] = 0
-        for s, (e, n) in enumerate(zip(entries, q_lens)):
-            hv[o_tok + t:o_tok + t + n] = e.tokens
-            hv[o_pos + t:o_pos + t + n] = range(e.start, e.start + n)
-            hv[o_seq + t:o_seq + t + n] = s
-            t += n
-            hv[o_cu + s + 1] = t
-            hv[o_ctx + s] = e.start + n
-            hv[o_slot + s] = e.state_slot
+        # every array in one assignment (a step of 64 requests would otherwise pay for several
+        # hundred small ones)
+        q = np.asarray(q_lens, dtype=np.int32)
+        starts = np.asarray([e.start for e in entries], dtype=np.int32)
+        cu = np.zeros(S + 1, dtype=np.int32)
+        np.cumsum(q, out=cu[1:])
+        if T == S:
+            hv[o_tok:o_tok + T] = [e.tokens[0] for e in entries]
+            hv[o_pos:o_pos + T] = starts
+            hv[o_seq:o_seq + T] = np.arange(S, dtype=np.int32)
+        else:
+            flat: List[int] = []
+            for e in entries:
+                flat.extend(e.tokens)
+            hv[o_tok:o_tok + T] = flat
+            hv[o_seq:o_seq + T] = np.repeat(np.arange(S, dtype=np.int32), q)
+            # position of token j of request s: start_s + (j - cu_s)
+            hv[o_pos:o_pos + T] = np.arange(T, dtype=np.int32) - np.repeat(cu[:-1] - starts, q)
+        hv[o_cu:o_cu + S + 1] = cu
+        hv[o_ctx:o_ctx + S] = starts + q
+        hv[o_slot:o_slot + S] = [e.state_slot for e in entries]
         hv[o_rows:o_rows + R] = want_rows
         for g, w in enumerate(widths):
             base = offsets[7 + g]
@@ -181,14 +193,13 @@ class StepContext:
         key = (group_size, rows_per_tile)
         hit = self._tiles.get(key)
         if hit is None:
-            seqs, row0s = [], []
-            for s, n in enumerate(self.q_lens):
-                rows = n * group_size
-                for r0 in range(0, rows, rows_per_tile):
-                    seqs.append(s)
-                    row0s.append(r0)
+            rows = np.asarray(self.q_lens, dtype=np.int64) * group_size
+            per_seq = -(-rows // rows_per_tile)                          # tiles of each request
+            first = np.cumsum(per_seq) - per_seq                         # index of its first tile
+            seqs = np.repeat(np.arange(len(self.q_lens)), per_seq)
+            row0s = (np.arange(int(per_seq.sum())) - np.repeat(first, per_seq)) * rows_per_tile
             n_tiles = len(seqs)
-            host = torch.tensor(seqs + row0s, dtype=torch.int32)
+            host = torch.from_numpy(np.concatenate([seqs, row0s]).astype(np.int32))
             if torch.cuda.is_available():
                 host = host.pin_memory()
             dev = host.to(self.device, non_blocking=True)

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 from typing import List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
@@ -73,6 +74,7 @@ class ModelRunner:
             getattr(b, "graph_safe", False)
             for b in list(self.model.blocks) + [self.model.embedding_position])
         self.graph_replays = 0
+        self._table_rows = {}             # (request, group) -> (stamp, block table as int32 array)
         self.graph_kernel_launches = {}   # batch size -> this package's kernels per replay
 
     @classmethod
@@ -83,12 +85,23 @@ class ModelRunner:
     def entry(self, request_id: str, tokens: Sequence[int], start: int,
               want: Sequence[int] = ()) -> BatchEntry:
         """A batch entry with the request's current block tables and state slot."""
+        stamps = [self.cache.table_stamp(request_id, g) for g in range(self.num_groups)]
         return BatchEntry(tokens=tokens, start=start, want=want,
-                          block_tables=[self.cache.block_table(request_id, g)
+                          block_tables=[self._table_row(request_id, g, stamps[g])
                                         for g in range(self.num_groups)],
-                          state_slot=self.cache.state_slot(request_id),
-                          table_stamps=[self.cache.table_stamp(request_id, g)
-                                        for g in range(self.num_groups)])
+                          state_slot=self.cache.state_slot(request_id), table_stamps=stamps)
+
+    def _table_row(self, request_id: str, group: int, stamp: int) -> np.ndarray:
+        """The request's block table as an int32 array, converted anew only when the table
+        has changed (its stamp): packing a step then copies arrays, not Python lists."""
+        key = (request_id, group)
+        hit = self._table_rows.get(key)
+        if hit is None or hit[0] != stamp:
+            if len(self._table_rows) > 8192:               # requests that ended leave their rows
+                self._table_rows.clear()
+            hit = (stamp, np.asarray(self.cache.block_table(request_id, group), dtype=np.int32))
+            self._table_rows[key] = hit
+        return hit[1]
 
     def check_tokens(self, tokens: Sequence[int]) -> None:
         v = self.spec.vocab_size
