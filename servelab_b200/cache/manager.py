@@ -24,7 +24,7 @@ from __future__ import annotations
 
 from collections import deque
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 
 # ------------------------------------------------------------ what mixers ask
@@ -182,6 +182,9 @@ class CacheManager:
         self.slots = StateSlotPool(num_state_slots)
         self.reserve_pages = reserve_pages
         self.alloc_fails = 0
+        # called with the request's id whenever a request gives everything back (it ended,
+        # was aborted or preempted): whoever keeps copies of its tables drops them
+        self.release_listeners: List[Callable[[str], None]] = []
 
     # ------------------------------------------------------------- queries
     def has(self, req: str) -> bool:
@@ -239,6 +242,8 @@ class CacheManager:
         for p in self.pools:
             p.close(req)
         self.slots.give(req)
+        for listener in self.release_listeners:
+            listener(req)
 
     # --------------------------------------------------------------- stats
     def stats(self) -> dict:

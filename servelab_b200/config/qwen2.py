@@ -14,7 +14,12 @@ is kept so that the engine can enforce it; the window keys
 (use_sliding_window / sliding_window / max_window_layers), which the reference
 does not read, select a windowed mixer for the upper layers; model types the
 reference aliases to qwen2 without handling their differences (qwen3) are
-rejected.
+rejected.  The reference drops every key it does not know (config.py:48-72); here a
+key that would change the arithmetic is an error instead of wrong logits:
+``rope_scaling`` other than null (no scaled rotation exists in this engine),
+``attention_bias`` / ``mlp_bias`` / ``partial_rotary_factor`` / ``attn_logit_softcapping``
+and the like with a value other than the architecture's, and any key that is on
+neither the list of keys read nor the list of keys known to be harmless.
 """
 
 from __future__ import annotations
@@ -29,6 +34,29 @@ from .specs import (AttentionSpec, BlockSpec, GatedMLPSpec, LayerRun, ModelSpec,
 
 _REQUIRED = ("hidden_size", "num_hidden_layers", "num_attention_heads",
              "intermediate_size", "vocab_size", "rms_norm_eps")
+
+
+# keys this class reads
+_READ = frozenset(_REQUIRED) | {
+    "num_key_value_heads", "head_dim", "rope_theta", "max_position_embeddings",
+    "tie_word_embeddings", "torch_dtype", "dtype", "eos_token_id", "hidden_act",
+    "use_sliding_window", "sliding_window", "max_window_layers", "layer_types",
+    "architectures", "model_type"}
+# keys that do not change a forward pass of this engine (training, generation defaults,
+# bookkeeping of the library that wrote the file)
+_HARMLESS = frozenset({
+    "attention_dropout", "use_cache", "bos_token_id", "pad_token_id", "initializer_range",
+    "transformers_version", "_name_or_path", "use_mrope", "output_attentions",
+    "output_hidden_states", "return_dict", "is_decoder", "is_encoder_decoder",
+    "tie_encoder_decoder", "add_cross_attention", "chunk_size_feed_forward",
+    "id2label", "label2id", "problem_type", "finetuning_task", "tokenizer_class",
+    "prefix", "sep_token_id", "decoder_start_token_id", "task_specific_params",
+    "torchscript", "pruned_heads"})
+# keys that may only carry the value the architecture has anyway
+_FIXED = {"attention_bias": (None,), "mlp_bias": (False, None), "partial_rotary_factor": (1.0, None),
+          "attn_logit_softcapping": (None,), "final_logit_softcapping": (None,),
+          "rope_scaling": (None,), "rope_parameters": (None,), "qk_norm": (False, None),
+          "quantization_config": (None,)}
 
 
 class ConfigError(ValueError):
@@ -62,6 +90,14 @@ class Qwen2Config:
     @classmethod
     def from_dict(cls, cfg: Dict[str, Any]) -> "Qwen2Config":
         problems = [f"missing key '{k}'" for k in _REQUIRED if k not in cfg]
+        for key, allowed in _FIXED.items():
+            if key in cfg and cfg[key] not in allowed:
+                problems.append(f"'{key}' = {cfg[key]!r} is not supported (it changes the "
+                                f"arithmetic; only {' / '.join(map(repr, allowed))} is taken)")
+        unknown = sorted(k for k in cfg if k not in _READ and k not in _HARMLESS and k not in _FIXED)
+        if unknown:
+            problems.append("unknown key(s) " + ", ".join(repr(k) for k in unknown)
+                            + " (neither read nor known to be harmless)")
         if problems:
             raise ConfigError("invalid Qwen2 config: " + "; ".join(problems))
         heads = int(cfg["num_attention_heads"])
@@ -82,7 +118,7 @@ class Qwen2Config:
             rope_theta=float(cfg.get("rope_theta", 1000000.0)),
             max_position_embeddings=int(cfg.get("max_position_embeddings", 4096)),
             tie_word_embeddings=bool(cfg.get("tie_word_embeddings", False)),
-            torch_dtype=str(cfg.get("torch_dtype", "float16")),
+            torch_dtype=str(cfg.get("torch_dtype", cfg.get("dtype", "float16"))),
             eos_token_ids=eos_ids,
             hidden_act=str(cfg.get("hidden_act", "silu")),
             use_sliding_window=use_win,
@@ -91,6 +127,15 @@ class Qwen2Config:
             max_window_layers=int(cfg.get("max_window_layers", layers)),
         )
         out.validate()
+        kinds = cfg.get("layer_types")
+        if kinds is not None:
+            # a per-layer list of "full_attention" / "sliding_attention": it must say what
+            # the window keys say, or one of the two would be ignored
+            mine = ["sliding_attention" if out.layer_window(i) else "full_attention"
+                    for i in range(layers)]
+            if list(kinds) != mine:
+                raise ConfigError("invalid Qwen2 config: 'layer_types' disagrees with "
+                                  "use_sliding_window / sliding_window / max_window_layers")
         return out
 
     @classmethod

@@ -70,11 +70,15 @@ class ModelRunner:
         self.max_graph_batch = max_num_seqs
         self._graphs = {}
         self._graph_pool = None
-        self._graph_safe = not self.storage.state_layers and all(
+        # every part says itself whether its forward only launches kernels on the step's
+        # device buffers (``graph_safe``); a mixer with state of its own does so too, by
+        # indexing its state with ``ctx.state_slots`` on the device
+        self._graph_safe = all(
             getattr(b, "graph_safe", False)
-            for b in list(self.model.blocks) + [self.model.embedding_position])
+            for b in list(self.model.blocks) + [self.model.embedding_position, self.model.final_norm])
         self.graph_replays = 0
         self._table_rows = {}             # (request, group) -> (stamp, block table as int32 array)
+        self.cache.release_listeners.append(self._forget_table_rows)
         self.graph_kernel_launches = {}   # batch size -> this package's kernels per replay
 
     @classmethod
@@ -97,11 +101,13 @@ class ModelRunner:
         key = (request_id, group)
         hit = self._table_rows.get(key)
         if hit is None or hit[0] != stamp:
-            if len(self._table_rows) > 8192:               # requests that ended leave their rows
-                self._table_rows.clear()
             hit = (stamp, np.asarray(self.cache.block_table(request_id, group), dtype=np.int32))
             self._table_rows[key] = hit
         return hit[1]
+
+    def _forget_table_rows(self, request_id: str) -> None:
+        for g in range(self.num_groups):
+            self._table_rows.pop((request_id, g), None)
 
     def check_tokens(self, tokens: Sequence[int]) -> None:
         v = self.spec.vocab_size

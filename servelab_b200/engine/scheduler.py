@@ -100,6 +100,7 @@ class Scheduler:
                     queue.pop(i)
                     self.cache.release(request_id)
                     s.status = SequenceStatus.FINISHED_ABORTED
+                    s.abort_reason = "aborted by the caller"
                     s.metrics.finished_time = self.clock()
                     return s
         return None
@@ -113,17 +114,10 @@ class Scheduler:
         out = SchedulerOutput()
         budget = self.cfg.max_num_batched_tokens
 
-        # 1) single decoded tokens
-        if self.cfg.chunked_prefill or not self.waiting:
-            num_decodes = 0
-            for seq in list(self.running):
-                if seq not in self.running or not seq.is_decoding():
-                    continue                      # preempted a moment ago / still in prompt
-                if num_decodes >= self.cfg.max_num_seqs or budget < 1:
-                    break
-                if self._reserve(seq, 1, out):
-                    num_decodes += 1
-                    budget -= 1
+        # 1) single decoded tokens (held back in the unchunked mode while anything waits)
+        decodes_held = not self.cfg.chunked_prefill and bool(self.waiting)
+        if not decodes_held:
+            budget = self._schedule_decodes(out, budget)
 
         # 2) prompts in flight
         for seq in _order(self.cfg.policy, [s for s in self.running if not s.is_decoding()]):
@@ -139,10 +133,13 @@ class Scheduler:
         self.waiting = _order(self.cfg.policy, self.waiting)
         while self.waiting and len(self.running) < self.cfg.max_num_seqs and budget > 0:
             seq = self.waiting[0]
-            if (seq.get_len() > self.max_model_len
-                    or not self.cache.can_ever_hold(seq.get_len(), self._max_portion())):
+            too_long = seq.get_len() > self.max_model_len
+            if too_long or not self.cache.can_ever_hold(seq.get_len(), self._max_portion()):
                 self.waiting.pop(0)
                 seq.status = SequenceStatus.FINISHED_ABORTED
+                seq.abort_reason = (f"{seq.get_len()} tokens exceed the position limit "
+                                    f"{self.max_model_len}" if too_long else
+                                    f"{seq.get_len()} tokens can never fit in the cache pool")
                 seq.metrics.finished_time = now
                 out.aborted.append(seq)
                 continue
@@ -158,7 +155,29 @@ class Scheduler:
             self.running.append(seq)
             out.portions.append(ScheduledPortion(seq, 0, n))
             budget -= n
+
+        # The unchunked mode held the decodes back for the waiting requests; if none of
+        # those could be admitted (no pages while the running ones hold them), the step
+        # would be empty for ever: the running requests decode instead, finish and free
+        # their pages.  The reference gets out of the same corner by preempting a running
+        # request when admission fails (scheduler.py:232-237,276-298).
+        if decodes_held and not out.portions and not out.aborted:
+            self._schedule_decodes(out, budget)
         return out
+
+    def _schedule_decodes(self, out: SchedulerOutput, budget: int) -> int:
+        """Phase 1: one token for every running request that is decoding; returns the
+        budget that is left."""
+        num_decodes = 0
+        for seq in list(self.running):
+            if seq not in self.running or not seq.is_decoding():
+                continue                      # preempted a moment ago / still in prompt
+            if num_decodes >= self.cfg.max_num_seqs or budget < 1:
+                break
+            if self._reserve(seq, 1, out):
+                num_decodes += 1
+                budget -= 1
+        return budget
 
     def _max_portion(self) -> int:
         return self.cfg.max_num_batched_tokens if self.cfg.chunked_prefill else 1 << 30
@@ -201,6 +220,7 @@ class Scheduler:
         for p in out.portions:
             seq = p.seq
             seq.num_computed_tokens = p.start + p.num_tokens
+            seq.metrics.num_steps += 1
             self.cache.trim(seq.request_id, seq.num_computed_tokens)
             if seq.request_id not in sampled:
                 continue

@@ -36,6 +36,7 @@ class RequestMetrics:
     first_token_time: float = 0.0
     finished_time: float = 0.0
     num_preemptions: int = 0
+    num_steps: int = 0                    # steps this request took part in
 
     @property
     def ttft(self) -> float:
@@ -47,7 +48,9 @@ class RequestMetrics:
 
     def to_dict(self) -> dict:
         return {"ttft": self.ttft, "latency": self.e2e_latency,
-                "preemptions": self.num_preemptions}
+                "preemptions": self.num_preemptions,
+                "queue_time": max(0.0, self.first_scheduled_time - self.arrival_time),
+                "steps": self.num_steps}
 
 
 class Sequence:
@@ -73,6 +76,7 @@ class Sequence:
         self.arrival_time = arrival_time
         self.stream_id = stream_id            # random stream of this request
         self.status = SequenceStatus.WAITING
+        self.abort_reason: Optional[str] = None     # set with FINISHED_ABORTED
         self.metrics = RequestMetrics(arrival_time=arrival_time)
 
     @property

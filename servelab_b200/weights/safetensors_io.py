@@ -49,8 +49,16 @@ class SafetensorsFile:
             lo, hi = info["data_offsets"]
             if info["dtype"] not in DTYPE_CODES:
                 raise ValueError(f"{path}: tensor {name} has unsupported dtype {info['dtype']}")
-            if lo > hi or self._base + hi > size:
+            if lo < 0 or lo > hi or self._base + hi > size:
                 raise ValueError(f"{path}: tensor {name} points outside the file")
+            count = 1
+            for d in info["shape"]:
+                count *= int(d)
+            itemsize = torch.empty((), dtype=DTYPE_CODES[info["dtype"]]).element_size()
+            if hi - lo != count * itemsize:
+                # a shorter range would make read() return a neighbour's bytes
+                raise ValueError(f"{path}: tensor {name} spans {hi - lo} bytes, its shape "
+                                 f"{list(info['shape'])} and dtype need {count * itemsize}")
         self._map = None
 
     def names(self) -> List[str]:

@@ -142,6 +142,7 @@ def test_entries_follow_the_cache_manager_through_growth_windows_and_reuse_of_id
     runner.cache = CacheManager([None, 12], 64, 4, 8)         # a full group and a windowed one
     runner.num_groups = 2
     runner._table_rows = {}
+    runner.cache.release_listeners.append(runner._forget_table_rows)
     rng = random.Random(5)
     live = {}
 
@@ -170,4 +171,6 @@ def test_entries_follow_the_cache_manager_through_growth_windows_and_reuse_of_id
                 live[rid] = n
                 runner.cache.trim(rid, n)
         check_all()
+        # rows of requests that gave everything back are dropped at once
+        assert {rid for rid, _ in runner._table_rows} <= set(live)
     runner.cache.check_invariants()

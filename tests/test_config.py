@@ -57,6 +57,33 @@ def test_missing_and_invalid_keys_are_all_named():
         config_from_dict(dict(H.TINY_A, use_sliding_window=True))
 
 
+def test_keys_that_change_the_arithmetic_are_refused():
+    """A scaled rotation (legal in Qwen2 checkpoints) or any key this class neither reads nor
+    knows to be harmless is an error, never silently wrong logits."""
+    base = dict(H.TINY_A)
+    with pytest.raises(ConfigError, match="rope_scaling"):
+        Qwen2Config.from_dict({**base, "rope_scaling": {"type": "yarn", "factor": 4.0}})
+    Qwen2Config.from_dict({**base, "rope_scaling": None})
+    with pytest.raises(ConfigError, match="attention_bias"):
+        Qwen2Config.from_dict({**base, "attention_bias": False})
+    with pytest.raises(ConfigError, match="partial_rotary_factor"):
+        Qwen2Config.from_dict({**base, "partial_rotary_factor": 0.5})
+    with pytest.raises(ConfigError) as e:
+        Qwen2Config.from_dict({**base, "num_experts": 8, "logit_scale": 2.0})
+    assert "'logit_scale'" in str(e.value) and "'num_experts'" in str(e.value)
+    # keys that change nothing pass
+    c = Qwen2Config.from_dict({**base, "attention_dropout": 0.0, "use_cache": True,
+                               "bos_token_id": 1, "initializer_range": 0.02,
+                               "transformers_version": "x", "sliding_window": 4096})
+    assert c.sliding_window is None
+    # a per-layer list must agree with the window keys
+    win = dict(H.TINY_C)
+    kinds = ["full_attention"] * 2 + ["sliding_attention"] * 2
+    Qwen2Config.from_dict({**win, "layer_types": kinds})
+    with pytest.raises(ConfigError, match="layer_types"):
+        Qwen2Config.from_dict({**win, "layer_types": ["full_attention"] * 4})
+
+
 def test_registry():
     assert "Qwen2ForCausalLM" in registered_architectures()
     assert resolve_architecture({"model_type": "qwen2"}) == "Qwen2ForCausalLM"

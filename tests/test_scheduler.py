@@ -237,6 +237,32 @@ def test_unchunked_mode_runs_whole_prompts_and_holds_decodes():
     assert [p.seq.request_id for p in plan.portions] == ["b"], "no decode while one waits"
 
 
+def test_unchunked_mode_decodes_when_the_waiting_request_cannot_get_pages():
+    """8 pages of 8: 'a' (40 tokens) holds 5 of them while it decodes, 'b' (40 tokens) waits
+    and cannot be admitted.  Holding the decodes back for 'b' would leave every step empty;
+    'a' has to go on, finish and free its pages."""
+    sched, cache = make(num_pages=8, page=8, budget=16, chunked=False)
+    a = add(sched, "a", 40, max_tokens=6, t=0.0)
+    plan = sched.schedule()
+    sched.update_after_exec(plan, {"a": 7})
+    b = add(sched, "b", 40, max_tokens=6, t=1.0)
+    plan = sched.schedule()
+    assert [(p.seq.request_id, p.num_tokens) for p in plan.portions] == [("a", 1)]
+    sched.update_after_exec(plan, {"a": 7})
+    finished, steps = drive(sched, cache, max_steps=60)
+    assert {s.request_id for s in finished} == {"a", "b"}
+    assert a.num_output_tokens == 6 and b.num_output_tokens == 6
+    assert all(p.num_free() == p.num_pages for p in cache.pools)
+
+
+def test_unchunked_mode_decodes_when_every_sequence_slot_is_taken():
+    sched, cache = make(budget=16, chunked=False, max_seqs=1)
+    add(sched, "a", 10, max_tokens=3, t=0.0)
+    add(sched, "b", 10, max_tokens=3, t=1.0)
+    finished, _ = drive(sched, cache, max_steps=40)
+    assert [s.request_id for s in finished] == ["a", "b"]
+
+
 def test_window_group_frees_pages_during_a_long_request():
     sched, cache = make(num_pages=12, page=4, budget=8, windows=(None, 6), max_seqs=1)
     s = add(sched, "a", 30, max_tokens=10)

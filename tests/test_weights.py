@@ -118,3 +118,27 @@ def test_sharded_folder_and_corrupt_header(tmp_path):
         SafetensorsFile(str(bad))
     with pytest.raises(FileNotFoundError):
         FolderSource(str(tmp_path / "empty"))
+
+
+def _raw_file(path, header: dict, payload: bytes):
+    import struct
+    blob = json.dumps(header).encode()
+    path.write_bytes(struct.pack("<Q", len(blob)) + blob + payload)
+
+
+def test_an_entry_whose_byte_range_does_not_fit_its_shape_is_refused(tmp_path):
+    """Offsets inside the file are not enough: a range shorter than shape x element size
+    would hand out the neighbouring tensor's bytes."""
+    ok = {"a": {"dtype": "F32", "shape": [2, 2], "data_offsets": [0, 16]},
+          "b": {"dtype": "F32", "shape": [4], "data_offsets": [16, 32]}}
+    _raw_file(tmp_path / "ok.safetensors", ok, bytes(32))
+    assert SafetensorsFile(str(tmp_path / "ok.safetensors")).shape("b") == (4,)
+    short = {"a": {"dtype": "F32", "shape": [2, 2], "data_offsets": [0, 8]},
+             "b": {"dtype": "F32", "shape": [4], "data_offsets": [8, 24]}}
+    _raw_file(tmp_path / "short.safetensors", short, bytes(32))
+    with pytest.raises(ValueError, match="tensor a spans 8 bytes"):
+        SafetensorsFile(str(tmp_path / "short.safetensors"))
+    negative = {"a": {"dtype": "F32", "shape": [4], "data_offsets": [-16, 0]}}
+    _raw_file(tmp_path / "neg.safetensors", negative, bytes(32))
+    with pytest.raises(ValueError, match="outside the file"):
+        SafetensorsFile(str(tmp_path / "neg.safetensors"))
