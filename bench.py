@@ -6,11 +6,19 @@
 A "step" is one decode step.  The default run has the layer sizes of the
 Qwen2.5-7B shape with random weights, a batch of 8 requests with 2,048-token
 prompts (context limit 4,096, page size 16).  It prints ONE JSON line:
-decoded tokens per second timed on the device (``value``), the same through the
-Python entry point with host tokens in and out (``e2e``), a 2,048-token prefill
-(``prefill``), the decode step's memory roofline (``roofline``) and decoding at
-batch 1 and 64 (``points``).  Weights (14 GB) are larger than the L2 cache, so
-every timed step reads them from HBM; no extra flush is needed.
+decoded tokens per second timed on the device (``value``: the median of
+``--rounds`` timed regions of ``--steps`` steps each), the same through the Python
+entry point with host tokens in and out (``e2e``), a 2,048-token prefill
+(``prefill``), the decode step's memory roofline (``roofline``), and under
+``points``: decoding at batch 1 and 64, at contexts of 512, 8,192 and 32,768 tokens
+for batch 8, the continuous-batching workloads of the 0.5B and 14B shapes with their
+roofline fractions, and the largest difference between the logits of a graph-replayed
+decode step and the same step run eagerly through the plain twin kernels.  Weights
+(14 GB) are larger than the L2 cache, so every timed step reads them from HBM; no
+extra flush is needed.
+
+``--impl reference``: the reference's engine cannot run (the line says what its import
+raises); its two GPU kernels can, and are timed beside this package's on the same data.
 
 More than one GPU is not supported: one line says so and the exit code is 2.
 """
@@ -28,49 +36,45 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-QWEN25_7B = {
-    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": 28,
-    "hidden_size": 3584, "num_attention_heads": 28, "num_key_value_heads": 4, "head_dim": 128,
-    "intermediate_size": 18944, "vocab_size": 152064, "rope_theta": 1000000.0,
-    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 32768,
-    "use_sliding_window": False, "torch_dtype": "bfloat16", "eos_token_id": 151645,
-}
 PROMPT_LEN, CONTEXT, PAGE = 2048, 4096, 16
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
-
-
-def load_peaks():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    try:
-        with open(path) as f:
-            d = json.load(f)
-        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
-                "source": "measured"}
-    except Exception:
-        return dict(FALLBACK_PEAKS, source="fallback")
+SWEEP_CONTEXTS = (512, 8192, 32768)
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons of the GPU in use with nvidia-smi (a read-only
+    query) while a region runs."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self):
-        self.rows, self.proc = [], None
+    def __init__(self, gpu: str = "0"):
+        """``gpu``: what ``nvidia-smi -i`` takes; the UUID of the CUDA device, because index 0 of
+        nvidia-smi need not be the device this process was given."""
+        self.gpu, self.rows, self.proc = gpu, [], None
+
+    @staticmethod
+    def current_gpu() -> str:
+        try:
+            import torch
+            return "GPU-" + str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
+        except Exception:                                   # noqa: BLE001 (older torch: no uuid)
+            return "0"
 
     def start(self):
+        self.rows = []
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "25"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
+                ["nvidia-smi", "-i", self.gpu, f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "25"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, args=(self.proc, self.rows), daemon=True).start()
         except OSError:
             self.proc = None
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+    @staticmethod
+    def _read(proc, rows):
+        for line in proc.stdout:
+            rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
         if self.proc is not None:
@@ -88,25 +92,6 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
-def weight_bytes_per_step(cfg, layers):
-    h, H, Hkv, D, I, V = (cfg["hidden_size"], cfg["num_attention_heads"],
-                          cfg["num_key_value_heads"], cfg["head_dim"], cfg["intermediate_size"],
-                          cfg["vocab_size"])
-    per_layer = (H + 2 * Hkv) * D * h + H * D * h + 3 * I * h
-    return 2 * (layers * per_layer + V * h), per_layer
-
-
-def kv_bytes_per_token(cfg, layers):
-    return 2 * layers * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
-
-
-def prefill_flops(cfg, layers, T):
-    _, per_layer = weight_bytes_per_step(cfg, layers)
-    lin = 2 * T * layers * per_layer
-    attn = layers * 4 * (T * (T + 1) // 2) * cfg["num_attention_heads"] * cfg["head_dim"]
-    return lin + attn + 2 * cfg["vocab_size"] * cfg["hidden_size"]
-
-
 _T0 = time.perf_counter()
 
 
@@ -115,159 +100,246 @@ def note(msg: str) -> None:
     print(f"[bench +{time.perf_counter() - _T0:6.1f}s] {msg}", file=sys.stderr, flush=True)
 
 
+def reference_arm() -> int:
+    """The reference through its own public API: its engine does not import; its two Triton
+    kernels do and are timed on the reference's own benchmark shapes."""
+    from servelab_b200.bench import reference_kernels as R
+    why = R.reference_engine_error() or "the reference's engine imported, which was not expected"
+    line = {"impl": "reference",
+            "unavailable": "the reference's engine cannot be imported (its tree lacks the model "
+                           "package it imports, excluded by its own .gitignore): " + why}
+    try:
+        import torch
+        if torch.cuda.is_available():
+            line["kernel_level"] = R.compare()
+    except Exception as e:                                  # noqa: BLE001
+        line["kernel_level"] = {"unavailable": f"{type(e).__name__}: {e}"}
+    print(json.dumps(line))
+    return 0
+
+
+TUNABLES = """tc_max_tokens tc_wide_max_tokens cluster_max_kblocks cluster_long_k_max_tokens (ints,
+ops.linear); defer_rope defer_norm fuse_swiglu cluster_sums fuse_qkv_rope (0/1, ops.linear); tc_max_stages
+tc_blocks_per_sm decode_ctas_per_sm decode_ws_stages decode_ws_force_splits decode_ws_unsplit_tiles
+tc_max_cluster (ints, ops.kernels); decode_ws_split_coef (float); use_tc_prefill pdl pdl_early (0/1)"""
+
+
+def apply_tunables(items):
+    from servelab_b200.ops import kernels as K
+    from servelab_b200.ops import library as kernel_library
+    from servelab_b200.ops import linear as linear_ops
+    for item in items:
+        name, value = item.split("=")
+        if name in ("tc_max_tokens", "tc_wide_max_tokens", "cluster_max_kblocks", "cluster_long_k_max_tokens"):
+            setattr(linear_ops, name, int(value))
+        elif name in ("defer_rope", "defer_norm"):
+            linear_ops.defer_split_sums[name[6:]] = bool(int(value))
+        elif name in ("fuse_swiglu", "cluster_sums", "fuse_qkv_rope"):
+            setattr(linear_ops, name, bool(int(value)))
+        elif name in ("tc_max_stages", "tc_blocks_per_sm", "decode_ctas_per_sm", "decode_ws_stages",
+                      "decode_ws_force_splits", "decode_ws_unsplit_tiles"):
+            setattr(K, name, int(value))
+        elif name == "tc_max_cluster":                      # at most 8, the portable cluster size
+            K.TC_MAX_CLUSTER = int(value)
+        elif name == "decode_ws_split_coef":
+            K.decode_ws_split_coef = float(value)
+        elif name == "use_tc_prefill":
+            K.use_tc_prefill = bool(int(value))
+        elif name == "pdl":
+            kernel_library.set_pdl(bool(int(value)))
+        elif name == "pdl_early":
+            kernel_library.set_pdl_early(bool(int(value)))
+        else:
+            raise SystemExit(f"unknown tunable {name}; known: {TUNABLES}")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--rounds", type=int, default=3, help="timed regions of --steps steps; the median is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (0 = all)")
-    ap.add_argument("--skip-points", action="store_true", help="no batch 1/64 and no prefill")
+    ap.add_argument("--skip-points", action="store_true", help="only the headline, its e2e and roofline")
+    ap.add_argument("--skip-workloads", action="store_true", help="no 0.5B / 14B serving workloads")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="profiling aid: run only the decode loop or only the prefill")
     ap.add_argument("--no-graphs", action="store_true", help="profiling aid: launch kernels eagerly")
     ap.add_argument("--tune", action="append", default=[], metavar="NAME=VALUE",
-                    help="measurement aid: set a dispatch tunable (skinny_max_tokens, "
-                         "decode_ctas_per_sm, pdl)")
+                    help="measurement aid: set a dispatch tunable: " + TUNABLES)
     ap.add_argument("--profile-region", action="store_true",
                     help="profiling aid: cudaProfilerStart/Stop around the device-timed region")
+    ap.add_argument("--profile-steps", type=int, default=0, metavar="N",
+                    help="also run N decode steps and one prefill eagerly with a CUDA event after "
+                         "every kernel and print the per-kernel table (stderr; 'step_profile' in the line)")
     args = ap.parse_args(argv)
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference's engine imports servelab.models, a package its tree "
-                          "does not contain (excluded by its own .gitignore), so it cannot run"}))
-        return 0
+        return reference_arm()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
-    if args.warmup < 3:
-        args.warmup = 3
+    args.warmup = max(args.warmup, 3)
+    args.rounds = max(args.rounds, 1)
 
     import torch
-    from servelab_b200.config import CacheConfig, SchedulerConfig, config_from_dict
-    from servelab_b200.engine.llm_engine import LLMEngine
-    from servelab_b200.models import declare_tensors
+    from servelab_b200.bench import workloads as W
+    from servelab_b200.ops import attention as attention_ops
     from servelab_b200.ops import kernels as K
-    from servelab_b200.sampling import SamplingParams
-    from servelab_b200.weights import RandomSource
-
     from servelab_b200.ops import linear as linear_ops
-    for item in args.tune:
-        name, value = item.split("=")
-        if name == "skinny_max_tokens":
-            linear_ops.skinny_max_tokens = int(value)
-        elif name in ("tc_max_tokens", "tc_wide_max_tokens"):
-            setattr(linear_ops, name, int(value))
-        elif name in ("defer_rope", "defer_norm"):
-            linear_ops.defer_split_sums[name[6:]] = bool(int(value))
-        elif name == "tc_max_stages":
-            K.tc_max_stages = int(value)
-        elif name == "decode_ctas_per_sm":
-            K.decode_ctas_per_sm = int(value)
-        elif name in ("decode_ws_stages", "decode_ws_force_splits", "decode_ws_unsplit_tiles"):
-            setattr(K, name, int(value))
-        elif name == "decode_ws_split_coef":
-            K.decode_ws_split_coef = float(value)
-        elif name in ("tc_prefetch_bytes", "tc_prefetch_chunk", "tc_blocks_per_sm"):
-            setattr(K, name, int(value))
-        elif name in ("fuse_swiglu", "cluster_sums", "fuse_qkv_rope", "fuse_resid_norm"):
-            setattr(linear_ops, name, bool(int(value)))
-        elif name in ("cluster_max_kblocks", "cluster_long_k_max_tokens"):
-            setattr(linear_ops, name, int(value))
-        elif name == "tc_max_cluster":                      # at most 8, the portable cluster size
-            K.TC_MAX_CLUSTER = int(value)
-        elif name == "use_tc_prefill":
-            K.use_tc_prefill = bool(int(value))
-        elif name == "fuse_decode_qkv":
-            from servelab_b200.ops import attention as attention_ops
-            attention_ops.fuse_decode_qkv = bool(int(value))
-        elif name == "pdl":
-            from servelab_b200.ops import library as kernel_library
-            kernel_library.set_pdl(bool(int(value)))
-        else:
-            raise SystemExit(f"unknown tunable {name}")
+    from servelab_b200.ops.profile import StepProfile
+    from servelab_b200.sampling import SamplingParams
+    apply_tunables(args.tune)
 
-    cfg = dict(QWEN25_7B)
+    cfg = dict(W.SHAPES["qwen2.5-7b"])
     full_layers = cfg["num_hidden_layers"]
     layers = args.layers or full_layers
     cfg["num_hidden_layers"] = layers
-    config = config_from_dict(cfg)
-    peaks = load_peaks()
+    peaks = W.load_peaks(os.path.join(ROOT, "MEASURED_PEAKS.json"))
     if args.only:
         args.skip_points = True
-    max_batch = 64 if not args.skip_points else max(args.batch, 1)
-    max_batch = max(max_batch, args.batch)
+    max_batch = max(args.batch, 1 if args.skip_points else 64)
     pages = max_batch * (CONTEXT // PAGE) + 64
     note("building the engine (random weights on the device, cache pool)")
-    source = RandomSource(declare_tensors(config.to_model_spec()), seed=0, device="cuda:0",
-                          dtype=torch.bfloat16)
-    engine = LLMEngine(config, CacheConfig(block_size=PAGE, num_blocks=pages),
-                       SchedulerConfig(max_num_seqs=max_batch, max_num_batched_tokens=PROMPT_LEN),
-                       dtype="bfloat16", weights=source, cuda_graphs=not args.no_graphs,
-                       max_model_len=CONTEXT)
+    engine = W.make_engine(cfg, pages, max_batch, PROMPT_LEN, CONTEXT, weights_seed=0, page_size=PAGE,
+                           cuda_graphs=not args.no_graphs)
     runner = engine.runner
     note("engine ready")
     gen = torch.Generator().manual_seed(1)
     V = cfg["vocab_size"]
+    clocks = ClockSampler(ClockSampler.current_gpu())
+    wbytes = W.weight_bytes_per_step(cfg, layers)
+    kvb = W.kv_bytes_per_token(cfg, layers)
 
-    def prompts(n):
-        return [torch.randint(0, V, (PROMPT_LEN,), generator=gen).tolist() for _ in range(n)]
+    def prompts(n, length=PROMPT_LEN):
+        return [torch.randint(0, V, (length,), generator=gen).tolist() for _ in range(n)]
 
-    def run_decode(batch, steps, warmup, clocks=None):
+    def timed_rounds(run_step, steps, rounds, with_clocks):
+        """``rounds`` regions of ``steps`` steps between CUDA events; (ms per step of each, clock
+        record of each)."""
+        times, records = [], []
+        for _ in range(rounds):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            if with_clocks:
+                clocks.start()
+            start.record()
+            for _ in range(steps):
+                run_step()
+            stop.record()
+            torch.cuda.synchronize()
+            if with_clocks:
+                records.append(clocks.stop())
+            times.append(start.elapsed_time(stop) / steps)
+        return times, records
+
+    def decode_entries(seqs):
+        entries = []
+        for s in seqs:
+            runner.cache.ensure(s.request_id, s.get_len())
+            entries.append(runner.entry(s.request_id, [s.token_ids[-1]], s.get_len() - 1, (0,)))
+        return entries
+
+    def logit_check(entries):
+        """The largest difference between the logits of the replayed graph and of the same step
+        run eagerly through the plain twin kernels (CUDA-core attention; K-split sums through
+        global memory instead of clusters)."""
+        fast = runner.step(entries).clone()
+        saved = (runner.cuda_graphs, attention_ops.force_generic, linear_ops.cluster_sums)
+        runner.cuda_graphs, attention_ops.force_generic, linear_ops.cluster_sums = False, True, False
+        try:
+            plain = runner.step(entries)
+        finally:
+            runner.cuda_graphs, attention_ops.force_generic, linear_ops.cluster_sums = saved
+        return {"max_abs_diff": round(float((fast - plain).abs().max()), 5),
+                "largest_logit": round(float(plain.abs().max()), 3),
+                "same_argmax_rows": int((fast.argmax(-1) == plain.argmax(-1)).sum()), "rows": fast.shape[0]}
+
+    def run_decode(batch, steps, warmup, rounds=1, with_clocks=False):
         """Prefill ``batch`` prompts through the engine, then time decode steps
-        (a) on the device through the step function and (b) end to end through
-        engine.step() with host tokens in and out."""
+        (a) end to end through engine.step() with host tokens in and out and (b) on the
+        device through the step function."""
         sp = SamplingParams(temperature=0.0, max_tokens=CONTEXT - PROMPT_LEN - 8, ignore_eos=True)
         for p in prompts(batch):
             engine.add_request(prompt_token_ids=p, sampling_params=sp)
         while any(not s.is_decoding() for s in engine.scheduler.running) or engine.scheduler.waiting:
             engine.step()
         assert len(engine.scheduler.running) == batch
-        note(f"batch {batch}: prompts prefilled, timing {steps} decode steps end to end and on the device")
-        # (b) end to end: schedule, pack, H2D, graph replay, sample, D2H, bookkeeping
+        note(f"batch {batch}: prompts prefilled, timing {rounds} x {steps} decode steps end to end and on the device")
+        # (a) end to end: schedule, pack, H2D, graph replay, sample, D2H, bookkeeping
         for _ in range(warmup):
             engine.step()
-        torch.cuda.synchronize()
-        if clocks:
-            clocks.start()
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            engine.step()
-        torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t0
-        # (a) device time of the same step: replay with CUDA events around it
+        e2e = []
+        for _ in range(rounds):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                engine.step()
+            torch.cuda.synchronize()
+            e2e.append((time.perf_counter() - t0) * 1e3 / steps)
+        # (b) device time of the same step: replay with CUDA events around it
         seqs = list(engine.scheduler.running)
-        entries = []
-        for s in seqs:
-            runner.cache.ensure(s.request_id, s.get_len())
-            entries.append(runner.entry(s.request_id, [s.token_ids[-1]], s.get_len() - 1, (0,)))
+        entries = decode_entries(seqs)
         out_ids = torch.empty(batch, dtype=torch.int32, device="cuda:0")
-        for _ in range(warmup):
+
+        def one_step():
             K.sample_rows(runner.step(entries), out_ids)
-        torch.cuda.synchronize()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(warmup):
+            one_step()
         k0 = K.launch_count
         if args.profile_region:
             torch.cuda.profiler.start()
-        start.record()
-        for _ in range(steps):
-            K.sample_rows(runner.step(entries), out_ids)
-        stop.record()
-        torch.cuda.synchronize()
+        dev, records = timed_rounds(one_step, steps, rounds, with_clocks)
         if args.profile_region:
             torch.cuda.profiler.stop()
-        dev_ms = start.elapsed_time(stop) / steps
-        clk = clocks.stop() if clocks else None
         ctx_tokens = sum(s.get_len() for s in seqs)
-        per_graph = getattr(runner, "graph_kernel_launches", {}).get(batch, 0)
-        launches = (K.launch_count - k0) + per_graph * steps
-        desc_bytes = engine.runner._graphs[batch][1]._dev.numel() * 4 if batch in runner._graphs else 0
+        per_graph = runner.graph_kernel_launches.get(batch, 0)
+        launches = ((K.launch_count - k0) + per_graph * steps * rounds) // rounds
+        desc_bytes = runner._graphs[batch][1]._dev.numel() * 4 if batch in runner._graphs else 0
+        check = logit_check(entries)
+        profile = None
+        if args.profile_steps:
+            saved, runner.cuda_graphs = runner.cuda_graphs, False
+            try:
+                one_step()
+                with StepProfile() as prof:
+                    for _ in range(args.profile_steps):
+                        one_step()
+            finally:
+                runner.cuda_graphs = saved
+            note(f"per-kernel times of an eager decode step at batch {batch}:\n" + prof.render(args.profile_steps))
+            profile = prof.summary(args.profile_steps)
         for s in seqs:
             engine.abort_request(s.request_id)
-        return {"dev_ms": dev_ms, "e2e_ms": e2e_s * 1000 / steps, "ctx_tokens": ctx_tokens,
-                "launches": launches, "h2d": desc_bytes, "d2h": batch * 4, "clocks": clk}
+        med = sorted(dev)[len(dev) // 2]
+        return {"dev_ms": med, "dev_ms_rounds": [round(t, 4) for t in dev],
+                "e2e_ms": sorted(e2e)[len(e2e) // 2], "ctx_tokens": ctx_tokens, "launches": launches,
+                "h2d": desc_bytes, "d2h": batch * 4, "clocks": records, "logit_check": check,
+                "profile": profile}
+
+    def run_context(batch, ctx_len, steps, warmup):
+        """A decode step of ``batch`` requests that each hold ``ctx_len`` tokens.  The pages are
+        taken, not prefilled: the step's time does not depend on the values of the cache."""
+        ids = []
+        for b in range(batch):
+            rid = f"ctx-{ctx_len}-{b}"
+            if not (runner.cache.open(rid) and runner.cache.ensure(rid, ctx_len)):
+                raise RuntimeError(f"no room for {batch} requests of {ctx_len} tokens")
+            ids.append(rid)
+        entries = [runner.entry(rid, [1 + b], ctx_len - 1, (0,)) for b, rid in enumerate(ids)]
+        out_ids = torch.empty(batch, dtype=torch.int32, device="cuda:0")
+
+        def one_step():
+            K.sample_rows(runner.step(entries), out_ids)
+        for _ in range(warmup):
+            one_step()
+        dev, _ = timed_rounds(one_step, steps, 1, False)
+        for rid in ids:
+            runner.cache.release(rid)
+        nbytes = wbytes + batch * ctx_len * kvb
+        return dev[0], nbytes / (dev[0] * 1e-3) / 1e9 / peaks["hbm_gbs"]
 
     def run_prefill():
         """One 2,048-token prompt through the step function, timed on the device
@@ -290,19 +362,24 @@ def main(argv=None) -> int:
             if args.profile_region and i == 4:
                 torch.cuda.profiler.stop()
             times.append(start.elapsed_time(stop))
+            if args.profile_steps and i == 4:
+                with StepProfile() as prof:
+                    runner.step([entry])
+                note("per-kernel times of the 2,048-token prefill:\n" + prof.render())
             runner.cache.release(rid)
         ms = sorted(times[2:])[len(times[2:]) // 2]
-        flops = prefill_flops(cfg, layers, PROMPT_LEN)
+        flops = W.prefill_flops(cfg, layers, PROMPT_LEN)
         return {"value": round(PROMPT_LEN / (ms * 1e-3), 1), "tokens": PROMPT_LEN,
                 "ms": round(ms, 3),
                 "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
 
     def kernel_status():
-        """Status words of the kernels with bounded waits (0 = no wait gave up)."""
+        """Status words of the kernels with bounded waits and page checks (0 = nothing happened)."""
         D = cfg["head_dim"]
         status = {"gemm_tc": K.gemm_tc_status(), "attention": K.attention_status(D),
                   "prefill_attention_tc": K.prefill_attention_tc_status(D),
-                  "decode_attention": K.decode_attention_status(D)}
+                  "decode_attention": K.decode_attention_status(D),
+                  "cache_write": K.cache_write_status()}
         if status["prefill_attention_tc"]:
             note(f"tcgen05 prefill attention gave up a wait: {K.prefill_attention_tc_where(D)}")
         return status
@@ -311,13 +388,18 @@ def main(argv=None) -> int:
         print(json.dumps({"only": "prefill", "layers": layers, "prefill": run_prefill(),
                           "kernel_status": kernel_status()}))
         return 0
-    clocks = ClockSampler()
     note(f"decode at batch {args.batch}")
-    main_run = run_decode(args.batch, args.steps, args.warmup, clocks)
-    wbytes, _ = weight_bytes_per_step(cfg, layers)
-    step_bytes = wbytes + main_run["ctx_tokens"] * kv_bytes_per_token(cfg, layers)
+    main_run = run_decode(args.batch, args.steps, args.warmup, args.rounds, with_clocks=True)
+    step_bytes = wbytes + main_run["ctx_tokens"] * kvb
     achieved = step_bytes / (main_run["dev_ms"] * 1e-3) / 1e9
     value = args.batch / (main_run["dev_ms"] * 1e-3)
+    rec = main_run["clocks"]
+    mhz = sorted(r["sm_mhz"] for r in rec if r["sm_mhz"])
+    clock_line = {"sm_mhz": mhz[len(mhz) // 2] if mhz else None,
+                  "sm_max_mhz": max([r["sm_max_mhz"] or 0 for r in rec] or [0]) or None,
+                  "reasons": sorted({x for r in rec for x in r["reasons"]}),
+                  "samples": sum(r["samples"] for r in rec),
+                  "sm_mhz_rounds": [r["sm_mhz"] for r in rec]}
     result = {
         "metric": "decode tok/s at batch 8, Qwen2.5-7B shape, 2048-token prompts",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
@@ -331,15 +413,20 @@ def main(argv=None) -> int:
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": V, "page_size": PAGE,
                    "parallelism": "single GPU", "cuda_graphs": not args.no_graphs,
-                   "l2": "weights (14 GB) exceed L2; no flush", "peaks": peaks["source"]},
+                   "l2": "weights (14 GB) exceed L2; no flush", "peaks": peaks["source"],
+                   "rounds": args.rounds},
+        "rounds_ms_per_step": main_run["dev_ms_rounds"],
         "e2e": {"value": round(args.batch / (main_run["e2e_ms"] * 1e-3), 1), "unit": "tok/s",
                 "ms_per_step": round(main_run["e2e_ms"], 4),
                 "h2d_bytes_per_step": main_run["h2d"], "d2h_bytes_per_step": main_run["d2h"]},
         "gpu_launches": main_run["launches"],
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4)},
-        "clocks": main_run["clocks"],
+        "clocks": clock_line,
+        "logit_check": {f"decode_b{args.batch}": main_run["logit_check"]},
     }
+    if main_run["profile"]:
+        result["step_profile"] = main_run["profile"]
     if not args.skip_points:
         note("prefill of one prompt")
         result["prefill"] = run_prefill()
@@ -347,11 +434,38 @@ def main(argv=None) -> int:
         for b in (1, 64):
             r = run_decode(b, max(16, args.steps // 2), args.warmup)
             points[f"decode_b{b}"] = round(b / (r["dev_ms"] * 1e-3), 1)
-            sb = wbytes + r["ctx_tokens"] * kv_bytes_per_token(cfg, layers)
+            sb = wbytes + r["ctx_tokens"] * kvb
             points[f"decode_b{b}_hbm_frac"] = round(sb / (r["dev_ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
             points[f"decode_b{b}_e2e"] = round(b / (r["e2e_ms"] * 1e-3), 1)
+            result["logit_check"][f"decode_b{b}"] = r["logit_check"]
         result["points"] = points
     result["kernel_status"] = kernel_status()
+    del runner, engine
+    torch.cuda.empty_cache()
+    if not args.skip_points:
+        # decode at other contexts: an engine whose cache holds 8 requests of 32,768 tokens
+        note("decode at batch 8 over contexts " + ", ".join(str(c) for c in SWEEP_CONTEXTS))
+        long_ctx = max(SWEEP_CONTEXTS) + PAGE
+        engine = W.make_engine(cfg, 8 * (long_ctx // PAGE) + 8, 8, PROMPT_LEN, long_ctx, weights_seed=0,
+                               page_size=PAGE, cuda_graphs=not args.no_graphs)
+        runner = engine.runner
+        for c in SWEEP_CONTEXTS:
+            ms, frac = run_context(8, c, max(16, args.steps // 2), args.warmup)
+            result["points"][f"decode_b8_ctx{c}"] = round(8 / (ms * 1e-3), 1)
+            result["points"][f"decode_b8_ctx{c}_hbm_frac"] = round(frac, 4)
+        st = K.decode_attention_status(cfg["head_dim"])
+        result["kernel_status"]["decode_attention"] = result["kernel_status"]["decode_attention"] or st
+        del runner, engine
+        torch.cuda.empty_cache()
+        if not args.skip_workloads:
+            for shape, key in (("qwen2.5-0.5b", "serve_0.5b"), ("qwen2.5-14b", "serve_14b")):
+                note(f"continuous-batching workload of the {shape} shape")
+                r = W.run_workload(shape, peaks, note=note)
+                result["points"][f"{key}_gen_tok_s"] = r["generated_tokens_per_s"]
+                result["points"][f"{key}_total_tok_s"] = r["total_tokens_per_s"]
+                result["points"][f"{key}_roofline_frac"] = r["roofline_frac"]
+                result["points"][f"{key}_ms_per_step"] = r["ms_per_step"]
+                result["points"][f"{key}_ok"] = bool(r["ok"])
     note("done")
     print(json.dumps(result))
     return 0

@@ -11,8 +11,13 @@ one CUDA graph; the graph is replayed a few times for warm-up and then ``iters``
 between two CUDA events.  Inside a graph the launches follow one another as they do
 in a decode step (programmatic dependent launch on), so the figure is the cost of the
 kernel in a step, not its cold, isolated cost.  Bytes and flops are the algorithmic ones
-(every operand once).  Peaks: a JSON file with ``hbm_gbs`` and ``bf16_tflops`` if given,
-else 6,650 GB/s and 1,590 TFLOP/s.
+(every operand once).  Peaks: the JSON file given with ``--peaks`` (``hbm_gbs``,
+``bf16_tflops``), by default ``MEASURED_PEAKS.json`` beside the package's parent folder when it
+exists, else 6,650 GB/s and 1,590 TFLOP/s; the header line says which were used.
+
+``--only reference_kernels`` times the reference project's own two GPU kernels (Triton; imported
+unmodified from an installed copy of the reference) beside this package's on the same data
+(``bench/reference_kernels.py``).
 
 Reference analogue: servelab/bench/kernel_bench.py:12-23 (CUDA events after warm-up),
 :26-70 (paged decode attention, batch x context).
@@ -26,13 +31,16 @@ import math
 import sys
 from typing import Callable, Dict, List, Optional, Tuple
 
-SHAPES = {  # hidden, heads, kv heads, head size, intermediate, vocabulary
-    "qwen2.5-0.5b": (896, 14, 2, 64, 4864, 151936),
-    "qwen2.5-7b": (3584, 28, 4, 128, 18944, 152064),
-    "qwen2.5-14b": (5120, 40, 8, 128, 13824, 152064),
-}
+import os
+
+from . import workloads as W
+
+# hidden, heads, kv heads, head size, intermediate, vocabulary
+SHAPES = {name: (c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"],
+                 c["intermediate_size"], c["vocab_size"]) for name, c in W.SHAPES.items()}
 PAGE = 16
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+DEFAULT_PEAKS = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                             "MEASURED_PEAKS.json")
 
 
 class Row:
@@ -296,6 +304,7 @@ def bench_elementwise(shape, peaks, device, token_counts) -> List[Row]:
 
 
 GROUPS = ("decode_attention", "prefill_attention", "products", "elementwise")
+EXTRA_GROUPS = ("reference_kernels",)       # only when asked for
 
 
 def render(rows: List[Row], markdown: bool) -> str:
@@ -323,22 +332,19 @@ def main(argv=None) -> int:
     ap.add_argument("--products", default="", help="products: only those whose name contains one of "
                     "these comma-separated pieces (q|k|v, o product, gate|up, down, LM head)")
     ap.add_argument("--no-twins", action="store_true", help="skip the plain twins of the attention kernels")
-    ap.add_argument("--peaks", default="", help="JSON file with hbm_gbs and bf16_tflops")
+    ap.add_argument("--peaks", default=DEFAULT_PEAKS, help="JSON file with hbm_gbs and bf16_tflops")
     ap.add_argument("--markdown", action="store_true")
     args = ap.parse_args(argv)
 
-    peaks = dict(FALLBACK_PEAKS)
-    if args.peaks:
-        with open(args.peaks) as f:
-            peaks.update({k: float(v) for k, v in json.load(f).items() if k in peaks})
+    peaks = W.load_peaks(args.peaks)
     from ..ops import kernels as K
     K.require_cuda()
     device = "cuda:0"
     shape = SHAPES[args.shape]
     groups = [g for g in args.only.split(",") if g] or list(GROUPS)
-    unknown = [g for g in groups if g not in GROUPS]
+    unknown = [g for g in groups if g not in GROUPS + EXTRA_GROUPS]
     if unknown:
-        raise SystemExit(f"unknown group(s) {unknown}; known: {', '.join(GROUPS)}")
+        raise SystemExit(f"unknown group(s) {unknown}; known: {', '.join(GROUPS + EXTRA_GROUPS)}")
     rows: List[Row] = []
     for g in groups:
         print(f"[kernel_bench] {g} ...", file=sys.stderr, flush=True)
@@ -348,14 +354,17 @@ def main(argv=None) -> int:
         elif g == "prefill_attention":
             rows += bench_prefill_attention(shape, peaks, device, _ints(args.prefill_lengths),
                                             not args.no_twins)
+        elif g == "reference_kernels":
+            from .reference_kernels import compare
+            print("reference kernels beside this package's:", json.dumps(compare(device), indent=1))
         elif g == "products":
             rows += bench_products(shape, peaks, device, _ints(args.tokens),
                                    [p for p in args.products.split(",") if p])
         else:
             rows += bench_elementwise(shape, peaks, device, _ints(args.tokens))
     print(f"{args.shape}: hidden {shape[0]}, heads {shape[1]}/{shape[2]} x {shape[3]}, intermediate "
-          f"{shape[4]}, vocabulary {shape[5]}; page {PAGE}; peaks {peaks['hbm_gbs']:.0f} GB/s, "
-          f"{peaks['bf16_tflops']:.0f} TFLOP/s")
+          f"{shape[4]}, vocabulary {shape[5]}; page {PAGE}; peaks ({peaks['source']}) "
+          f"{peaks['hbm_gbs']:.0f} GB/s, {peaks['bf16_tflops']:.0f} TFLOP/s")
     print(render(rows, args.markdown))
     status = {"gemm_tc": K.gemm_tc_status(), "attention": K.attention_status(shape[3]),
               "prefill_attention_tc": K.prefill_attention_tc_status(shape[3]),

@@ -63,6 +63,8 @@ class PagePool:
         self._first_live: Dict[str, int] = {}
         self._serial = 0                       # bumped whenever any table changes
         self.stamp: Dict[str, int] = {}        # request -> serial of its table's last change
+        # called with the pages that return to the free list (a request ended, a window passed them)
+        self.on_free: Optional[Callable[[List[int]], None]] = None
 
     def num_free(self) -> int:
         return len(self.free)
@@ -119,6 +121,8 @@ class PagePool:
         self.free.extend(freed)
         if freed:
             self._touch(req)
+            if self.on_free is not None:
+                self.on_free(freed)
         return freed
 
     def close(self, req: str) -> List[int]:
@@ -129,6 +133,8 @@ class PagePool:
             return []
         freed = [p for p in table if p >= 0]
         self.free.extend(freed)
+        if freed and self.on_free is not None:
+            self.on_free(freed)
         return freed
 
 

@@ -61,18 +61,30 @@ def pages_from_memory(groups, page_size, dtype, free_bytes: int, utilization: fl
     return max(16, int(free_bytes * utilization / per))
 
 
+# What unwritten slots hold in the debugging mode: finite (the fast kernels multiply masked
+# keys' values by a probability of zero, which NaN or infinity would not survive), and so
+# large that a key that is read although it was never written takes the whole softmax and
+# shows in the logits.
+POISON = 1e30
+
+
 class CacheStorage:
     def __init__(self, requests: Sequence[Optional[object]], num_pages: int, page_size: int,
-                 num_state_slots: int, dtype: torch.dtype, device: str):
+                 num_state_slots: int, dtype: torch.dtype, device: str, poison: bool = False):
+        """``poison``: a debugging mode in which every slot that no request has written holds
+        ``POISON`` instead of zeros: fresh pages at the start, and pages again when they are
+        given back (``poison_pages``).  A kernel that reads a slot it should not see (beyond
+        the context, a page of another request's past) then changes the logits visibly."""
         self.groups, self.group_of_layer = plan_groups(requests)
         self.page_size = page_size
         self.num_pages = num_pages
+        self.poison = poison
         self.layer_caches: Dict[int, LayerCache] = {}
         self._buffers = []
         for gi, g in enumerate(self.groups):
             r = g.request
-            buf = torch.zeros((len(g.layers), 2, num_pages, r.num_kv_heads, page_size, r.head_dim),
-                              dtype=dtype, device=device)
+            buf = torch.full((len(g.layers), 2, num_pages, r.num_kv_heads, page_size, r.head_dim),
+                             POISON if poison else 0.0, dtype=dtype, device=device)
             self._buffers.append(buf)
             for li, layer in enumerate(g.layers):
                 self.layer_caches[layer] = LayerCache(group=gi, k=buf[li, 0], v=buf[li, 1],
@@ -98,6 +110,14 @@ class CacheStorage:
         idx = torch.tensor(list(slots), dtype=torch.long, device=self.layer_caches[self.state_layers[0]].state.device)
         for layer in self.state_layers:
             self.layer_caches[layer].state.index_fill_(0, idx, 0.0)
+
+    def poison_pages(self, group: int, pages: Sequence[int]) -> None:
+        """Debugging mode: pages that went back to the free list hold ``POISON`` again."""
+        if not self.poison or not pages:
+            return
+        buf = self._buffers[group]
+        idx = torch.tensor(list(pages), dtype=torch.long, device=buf.device)
+        buf.index_fill_(2, idx, POISON)
 
     def nbytes(self) -> int:
         n = sum(b.numel() * b.element_size() for b in self._buffers)

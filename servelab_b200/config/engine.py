@@ -21,6 +21,8 @@ class CacheConfig:
     num_blocks: Optional[int] = None       # pages per cache group; None => from memory
     gpu_memory_utilization: float = 0.85   # fraction of free device memory for the cache
     reserve_blocks: int = 0                # pages held back from admission only
+    poison_cache: bool = False             # debugging: unwritten slots hold a huge value, so a
+                                           # kernel that reads one changes the logits visibly
 
     def __post_init__(self):
         if self.block_size < 1:

@@ -67,6 +67,13 @@ class AttentionSpec(PartSpec):
     window: Optional[int] = None
     scale: Optional[float] = None          # None => head_dim ** -0.5
     position: PartSpec = field(default_factory=NoPositionSpec)
+    # checkpoint names of the projections under the mixer's prefix (data, like the sizes:
+    # an architecture with the same arithmetic and other names changes these, not the part)
+    q_name: str = "q_proj"
+    k_name: str = "k_proj"
+    v_name: str = "v_proj"
+    o_name: str = "o_proj"
+    position_name: str = "rotary_emb"
 
 
 # -------------------------------------------------------------- feed-forward
@@ -78,6 +85,9 @@ class GatedMLPSpec(PartSpec):
     intermediate_size: int = 0
     activation: str = "silu"
     bias: bool = False
+    gate_name: str = "gate_proj"           # checkpoint names under the feed-forward's prefix
+    up_name: str = "up_proj"
+    down_name: str = "down_proj"
 
 
 # --------------------------------------------------------------------- block
@@ -90,6 +100,11 @@ class BlockSpec(PartSpec):
     feed_forward: PartSpec = None
     mixer_norm: PartSpec = None
     ff_norm: PartSpec = None
+    # checkpoint names of the four parts under the layer's prefix
+    mixer_norm_name: str = "input_layernorm"
+    mixer_name: str = "self_attn"
+    ff_norm_name: str = "post_attention_layernorm"
+    feed_forward_name: str = "mlp"
 
 
 @dataclass(frozen=True)
@@ -130,3 +145,7 @@ class ModelSpec:
     layer_prefix: str = "model.layers.{}"
     # checkpoint tensors that may be present and are ignored
     ignored_suffixes: Tuple[str, ...] = ("rotary_emb.inv_freq",)
+    # arithmetic around the layers that some architectures have; None: not applied
+    embedding_scale: Optional[float] = None      # embedded tokens are multiplied by it
+    logit_scale: Optional[float] = None          # logits are multiplied by it ...
+    logit_softcap: Optional[float] = None        # ... and then become cap * tanh(logits / cap)

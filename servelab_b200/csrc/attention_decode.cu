@@ -26,22 +26,15 @@
 // one request merge in the block that arrives last on a per-(request, head tile)
 // counter in global memory, so a step needs one launch and no second kernel.
 //
-// FUSED form: the kernel before this one is the q|k|v product itself.  Its result (float32
-// partial sums of a K split, or bfloat16) is turned into the block's query rows here: bias
-// added, rotated by the token's position, rounded to bfloat16 into shared memory.  The block
-// that holds the request's last tile does the same for the new key and value, writes them
-// to the cache for later steps and puts them into its copy of the tile (the copy fetched
-// the row as the previous steps left it).  The arithmetic is that of the kernel in
-// rope_cache.cu, which this form makes unnecessary for steps of single tokens.
-//
 // Taken: head sizes that are multiples of 64, page sizes that are powers of two from
 // 8 (what a box copy needs); other sizes use the kernel in attention_mma.cu.
 //
 // Masking: key r is visible to the query at position a = ctx - 1 iff r <= a and,
 // with a window w > 0, a - r < w.  Page layout: [page][kv head][slot][SLB_HEAD_DIM].
 // Pages hold finite values in every slot (the cache starts as zeros), so a masked key
-// may carry any stale row; boxes that are not fetched at all (beyond the context, or
-// a page already given back by a window) are zero-filled in shared memory.
+// may carry any stale row; boxes that are not fetched at all (beyond the context, a
+// page already given back by a window, or a table entry outside the cache, which also
+// sets the status word) are zero-filled in shared memory.
 // Every mbarrier wait is bounded; a wait that gives up sets a status word, the
 // block waits (bounded) for its own copies in flight and writes no result.
 //
@@ -81,7 +74,9 @@ constexpr int MAX_STAGES = 4;
 constexpr int MAX_SPLITS = 32;
 constexpr float LAZY_LOG2 = 8.f;           // the reference moves when exceeded by 2^8
 
-__device__ int dec_status_word = 0;        // 0, or a code of the first wait that gave up
+__device__ int dec_status_word = 0;        // 0, or a code of the first wait that gave up (0x10 producer,
+                                           // 0x20 consumer) or 0x40: a table entry outside the cache
+__device__ int dec_splits_used = 0;        // the most splits any request has used since the last reset
 
 // transpose of an 8x8 matrix of 16-bit elements held one row pair per thread
 __device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
@@ -149,36 +144,18 @@ __device__ __forceinline__ void produce_tile(unsigned char* Kd, unsigned char* V
     }
 }
 
-// Where the FUSED form finds the projection of token s: float32 partial sums
-// parts[p][s][ld] (p < nparts) or, with nparts == 0, bfloat16 qkv[s][ld]; columns are
-// [H heads of q | Hkv of k | Hkv of v] x D.  bias float32 or null; inv_freq
-// [rotary_dim / 2] or null (no rotation).  k_cache / v_cache: where the new key and value
-// are written (null: this layer reads a cache that another layer writes).
-struct QkvSource {
-    const float* parts;
-    const bf16* qkv;
-    int nparts;
-    long long part_stride;
-    int ld;
-    const float* bias;
-    const float* inv_freq;
-    int rotary_dim;
-    bf16* k_cache;
-    bf16* v_cache;
-};
-
 // grid (num_splits, Hkv * head_tiles, S); q_len is 1 for every request.  NH: 8-head
 // tiles per block.  Scratch (only with num_splits > 1): part_o [S][H][num_splits][D]
 // float32 (unnormalised), part_ml [S][H][num_splits][2] (reference max in the base-2
 // domain, sum), counters [S][Hkv * head_tiles] ints that are zero between launches.
-template <int NH, bool FUSED>
+template <int NH>
 __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
-    const bf16* __restrict__ q, int ldq, const QkvSource src, const __grid_constant__ CUtensorMap map_k,
+    const bf16* __restrict__ q, int ldq, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, int ldo,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ ctx_len,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int H,
     int Hkv, int ps, int box_rows, float scale_log2, int window, int num_splits, int head_tiles,
-    int stages, float split_coef, int unsplit_tiles) {
+    int stages, float split_coef, int unsplit_tiles, int num_pages, int pdl_early) {
     constexpr int HR = 8 * NH;                             // query heads per block
     constexpr int QCH = (HR * CHUNKS + 32 * DW - 1) / (32 * DW);   // 16-byte chunks of Q a consumer thread moves
     extern __shared__ unsigned char smem_raw[];
@@ -189,8 +166,6 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     __shared__ float red_m[DW][HR], red_l[DW][HR];
     __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES];
     __shared__ int failed, issued, last_block;
-    __shared__ float trig[FUSED ? D : 1];                  // cos[D / 2] then sin[D / 2] of the position
-    __shared__ __align__(16) bf16 new_kv[FUSED ? 2 * D : 8];   // the step's own key, then its value
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x;
@@ -221,6 +196,9 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
         if (use_splits > 8 && use_splits <= 12) use_splits = 8;   // the last block reads eight at a time
     }
     if (split >= use_splits) return;
+    if (use_splits > 1 && split == 0 && blockIdx.y == 0 && threadIdx.x == 0)
+        atomicMax(&dec_splits_used, use_splits);           // what tests read to see that requests were split
+    if (pdl_early) pdl_launch_dependents();
     const int tiles_per_split = (total_tiles + use_splits - 1) / use_splits;
     const int t_begin = split * tiles_per_split;
     const int ntiles = max(0, min(total_tiles, t_begin + tiles_per_split) - t_begin);
@@ -245,7 +223,12 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     // 32 * group + l of this block's keys.
     auto lookup = [&](int group) {
         const int kp = kstart + (group * 32 + lane) * geo.box_rows;
-        return kp < kstop ? table[kp >> ps_shift] : -1;
+        int page = kp < kstop ? table[kp >> ps_shift] : -1;
+        if (page >= num_pages) {                           // outside the cache: not fetched
+            atomicCAS(&dec_status_word, 0, 0x40);
+            page = -1;
+        }
+        return page;
     };
     // The first `stages` tiles are requested by warps 0 .. stages-1 at once (one warp
     // issues a tile's copies in roughly a microsecond); the producer warp takes over from
@@ -257,11 +240,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     // Only the request's newest key and value are written in this step (by the kernel
     // before this one, into the request's last tile); every earlier tile was written by
     // earlier steps and is requested at once, while that kernel still runs.
-    // (In the FUSED form this kernel writes that row itself, after its copy has landed.)
-    const bool writes_kv = FUSED && src.k_cache != nullptr;
-    // this block holds the request's last tile and supplies the new key and value to it
-    const bool owns_new = writes_kv && ntiles > 0 && kstop == ctx;
-    const bool last_tile_in_burst = !writes_kv && warp < burst && t_begin + warp == total_tiles - 1;
+    const bool last_tile_in_burst = warp < burst && t_begin + warp == total_tiles - 1;
     auto produce_first = [&]() {
         const int page = __shfl_sync(0xffffffffu, first_pages, (warp * geo.boxes + lane) & 31);
         unsigned char* Kd = stage0 + (size_t)warp * STAGE_BYTES;
@@ -314,67 +293,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     if (warp < DW) {
         // ----------------------------------------------------------- consumers
         // the Q rows of the block's heads, zero for heads beyond the group
-        if constexpr (FUSED) {
-            constexpr int HALF = D / 2;
-            const int half = src.inv_freq != nullptr ? src.rotary_dim >> 1 : 0;
-            for (int i = tid; i < half; i += 32 * DW) {
-                float sn, cs;
-                sincosf((float)pos * src.inv_freq[i], &sn, &cs);
-                trig[i] = cs;
-                trig[HALF + i] = sn;
-            }
-            for (int idx = tid; idx < (HR - nrows) * CHUNKS; idx += 32 * DW)
-                *reinterpret_cast<uint4*>(Qs + (nrows + idx / CHUNKS) * LDS + (idx % CHUNKS) * 8) =
-                    make_uint4(0, 0, 0, 0);
-            asm volatile("bar.sync 1, %0;" ::"n"(32 * DW) : "memory");
-            int page = -1;
-            if (owns_new && htile == 0) page = table[pos >> ps_shift];
-            // slot i of a row: a rotation pair (i, i + half), or two neighbours that pass through
-            const int rows = nrows + (owns_new ? 2 : 0);
-            for (int slot = tid; slot < rows * HALF; slot += 32 * DW) {
-                const int r = slot / HALF, i = slot - r * HALF;
-                const bool is_v = r == nrows + 1;
-                const int j = r < nrows ? kvh * g + h0 + r : (is_v ? H + Hkv + kvh : H + kvh);
-                const bool rot = i < half && !is_v;
-                const int a = rot ? i : (is_v ? 2 * i : (i < half ? i : 2 * half + 2 * (i - half)));
-                const int b = rot ? i + half : (is_v ? 2 * i + 1 : (i < half ? i + half : a + 1));
-                const size_t off = (size_t)j * D;
-                float va = 0.f, vb = 0.f;
-                if (src.nparts > 0) {
-                    const float* px = src.parts + (size_t)s * src.ld + off;
-                    for (int p = 0; p < src.nparts; ++p) {
-                        va += __ldcg(px + p * src.part_stride + a);
-                        vb += __ldcg(px + p * src.part_stride + b);
-                    }
-                } else {
-                    const bf16* px = src.qkv + (size_t)s * src.ld + off;
-                    va = __bfloat162float(px[a]);
-                    vb = __bfloat162float(px[b]);
-                }
-                if (src.bias != nullptr) { va += src.bias[off + a]; vb += src.bias[off + b]; }
-                if (rot) {
-                    const float cs = trig[i], sn = trig[HALF + i];
-                    const float ra = va * cs - vb * sn;
-                    vb = vb * cs + va * sn;
-                    va = ra;
-                }
-                const bf16 ha = __float2bfloat16_rn(va), hb = __float2bfloat16_rn(vb);
-                if (r < nrows) {
-                    Qs[r * LDS + a] = ha;
-                    Qs[r * LDS + b] = hb;
-                } else {
-                    new_kv[(is_v ? D : 0) + a] = ha;
-                    new_kv[(is_v ? D : 0) + b] = hb;
-                    if (page >= 0) {                       // one block per kv head writes the cache
-                        bf16* dst = (is_v ? src.v_cache : src.k_cache) +
-                                    (((size_t)page * Hkv + kvh) * ps + (pos & (ps - 1))) * D;
-                        dst[a] = ha;
-                        dst[b] = hb;
-                    }
-                }
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(32 * DW) : "memory");
-        } else {
+        {
             uint4 qv[QCH];
 #pragma unroll
             for (int i = 0; i < QCH; ++i) {
@@ -420,21 +339,6 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
             const unsigned char* Ks = stage0 + (size_t)st * STAGE_BYTES;
             const unsigned char* Vs = Ks + TILE_BYTES;
             const int k0 = kstart + t * BN + warp * 16;    // position of this warp's first key
-            if constexpr (FUSED) {
-                // the step's own key and value replace what the copy fetched for their row;
-                // only the warp whose 16 keys include that row reads it
-                if (owns_new && t == ntiles - 1 && pos >= k0 && pos < k0 + 16) {
-                    const int rr = pos - (kstart + t * BN);
-                    for (int c = lane; c < 2 * CHUNKS; c += 32) {
-                        const int is_v = c >= CHUNKS, cc = c - is_v * CHUNKS;
-                        unsigned char* dst = const_cast<unsigned char*>(is_v ? Vs : Ks) +
-                                             (cc >> 3) * geo.panel_bytes + geo.row_offset(rr) +
-                                             (((cc & 7) ^ (rr & 7)) << 4);
-                        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(new_kv + is_v * D + cc * 8);
-                    }
-                    __syncwarp();
-                }
-            }
             if (k0 < ctx) {
                 // every shared-memory read of the slice is issued before the first MMA needs
                 // its result (the asm statements keep their order)
@@ -677,30 +581,27 @@ static_assert(decode_smem(2, 2) <= MAX_DYNAMIC_SMEM, "two stages must fit for ev
 static_assert((size_t)DW * 2 * (D / 16) * 4 * 32 * sizeof(float) <= 2 * (size_t)STAGE_BYTES,
               "the merge buffer lives in the first two stages");
 
-template <int NH, bool FUSED>
-int launch_decode(const bf16* q, int ldq, const QkvSource& src, const CUtensorMap& map_k, const CUtensorMap& map_v, bf16* out,
+template <int NH>
+int launch_decode(const bf16* q, int ldq, const CUtensorMap& map_k, const CUtensorMap& map_v, bf16* out,
                   int ldo, const int* block_table, int max_pages, const int* ctx_len, float* scratch,
                   int* counters, int S, int H, int Hkv, int ps, int box_rows, float scale, int window,
-                  int num_splits, int stages, float split_coef, int unsplit_tiles, cudaStream_t st) {
+                  int num_splits, int stages, float split_coef, int unsplit_tiles, int num_pages,
+                  cudaStream_t st) {
     const int g = H / Hkv;
     const int head_tiles = (g + 8 * NH - 1) / (8 * NH);
     if ((long long)Hkv * head_tiles > 65535) return SLB_ERR_TOO_LARGE;
     while (stages > 2 && decode_smem(NH, stages) > MAX_DYNAMIC_SMEM) --stages;
     const size_t smem = decode_smem(NH, stages);
-    static size_t configured = 0;                          // per instantiation
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_attention_ws_kernel<NH, FUSED>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = smem;
-    }
+    static unsigned long long configured = 0;              // per instantiation, a bit per device
+    const int rc = slb_configure(&configured, decode_attention_ws_kernel<NH>, MAX_DYNAMIC_SMEM);
+    if (rc != 0) return rc;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)S * H * num_splits * D : nullptr;
-    return slb_launch(decode_attention_ws_kernel<NH, FUSED>, dim3(num_splits, Hkv * head_tiles, S),
-                      dim3(NTHREADS), smem, st, q, ldq, src, map_k, map_v, out, ldo, block_table, max_pages,
+    return slb_launch(decode_attention_ws_kernel<NH>, dim3(num_splits, Hkv * head_tiles, S),
+                      dim3(NTHREADS), smem, st, q, ldq, map_k, map_v, out, ldo, block_table, max_pages,
                       ctx_len, part_o, part_ml, counters, H, Hkv, ps, box_rows,
                       scale * 1.4426950408889634f, window, num_splits, head_tiles, stages, split_coef,
-                      unsplit_tiles);
+                      unsplit_tiles, num_pages, slb_pdl_early);
 }
 
 }  // namespace
@@ -710,7 +611,8 @@ extern "C" {
 // 1 if the kernel takes this page size (the head size is fixed by the library)
 int slb_decode_attention_ws_supported(int ps) { return ps >= 8 && (ps & (ps - 1)) == 0; }
 
-// 0 unless a bounded wait inside the kernel gave up (its block then wrote nothing).
+// 0 unless a bounded wait inside the kernel gave up (its block then wrote nothing) or a
+// block-table entry pointed outside the cache (0x40; that page was read as zeros).
 // Reading synchronises with the device.
 int slb_decode_attention_ws_status(int reset) {
     int v = 0;
@@ -718,6 +620,17 @@ int slb_decode_attention_ws_status(int reset) {
     if (reset && v != 0) {
         const int zero = 0;
         cudaMemcpyToSymbol(dec_status_word, &zero, sizeof(int));
+    }
+    return v;
+}
+// The most splits any request has used in a launch since the last reset (0: every request
+// ran unsplit).  Reading synchronises with the device.
+int slb_decode_attention_ws_splits_used(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, dec_splits_used, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(dec_splits_used, &zero, sizeof(int));
     }
     return v;
 }
@@ -743,11 +656,11 @@ long long slb_decode_attention_ws_counters(int S, int H, int Hkv) {
 // num_splits is the most any request is split; a request of T 64-key tiles uses one split
 // while T <= unsplit_tiles, else ceil(T / max(ceil(split_coef * sqrt(T)), ceil(T /
 // num_splits))) of them (8 instead of 9..12).
-static int run_decode(bool fused, const bf16* q, int ldq, const QkvSource& src, const bf16* kc,
-                      const bf16* vc, bf16* out, int ldo, const int* block_table, int max_pages,
-                      const int* ctx_len, float* scratch, int* counters, int S, int H, int Hkv, int ps,
-                      int num_pages, float scale, int window, int num_splits, int stages,
-                      float split_coef, int unsplit_tiles, cudaStream_t st) {
+int slb_decode_attention_ws_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, bf16* out,
+                                 int ldo, const int* block_table, int max_pages, const int* ctx_len,
+                                 float* scratch, int* counters, int S, int H, int Hkv, int ps,
+                                 int num_pages, float scale, int window, int num_splits, int stages,
+                                 float split_coef, int unsplit_tiles, cudaStream_t st) {
     if (S <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || max_pages <= 0 || num_pages <= 0 || !(scale > 0.f))
         return SLB_ERR_BAD_ARG;
@@ -755,15 +668,7 @@ static int run_decode(bool fused, const bf16* q, int ldq, const QkvSource& src, 
     if (num_splits < 1 || (num_splits > 1 && (scratch == nullptr || counters == nullptr)))
         return SLB_ERR_BAD_ARG;
     if (stages < 2 || stages > MAX_STAGES || !(split_coef >= 0.f) || unsplit_tiles < 0) return SLB_ERR_BAD_ARG;
-    if (((uintptr_t)kc | (uintptr_t)vc) % 16) return SLB_ERR_BAD_ARG;
-    if (fused) {
-        if ((src.nparts > 0 ? (const void*)src.parts : (const void*)src.qkv) == nullptr || src.nparts < 0 ||
-            src.ld < (H + 2 * Hkv) * D || src.rotary_dim < 0 || src.rotary_dim > D || src.rotary_dim % 2 ||
-            (src.k_cache == nullptr) != (src.v_cache == nullptr))
-            return SLB_ERR_BAD_ARG;
-    } else if (ldq % 8 || (uintptr_t)q % 16) {
-        return SLB_ERR_BAD_ARG;
-    }
+    if (((uintptr_t)kc | (uintptr_t)vc) % 16 || ldq % 8 || (uintptr_t)q % 16) return SLB_ERR_BAD_ARG;
     if (num_splits > MAX_SPLITS || S > 65535) return SLB_ERR_TOO_LARGE;
     const long long rows = (long long)num_pages * Hkv * ps;
     if (rows > 0x7fffffffll) return SLB_ERR_TOO_LARGE;     // box coordinates are 32-bit
@@ -773,50 +678,12 @@ static int run_decode(bool fused, const bf16* q, int ldq, const QkvSource& src, 
     if (rc != 0) return rc;
     rc = slb_tma::make_paneled_rows_map(&map_v, vc, D, rows, box_rows);
     if (rc != 0) return rc;
-#define SLB_LAUNCH_DECODE(NH_, FUSED_)                                                                   \
-    launch_decode<NH_, FUSED_>(q, ldq, src, map_k, map_v, out, ldo, block_table, max_pages, ctx_len,     \
-                               scratch, counters, S, H, Hkv, ps, box_rows, scale, window, num_splits,    \
-                               stages, split_coef, unsplit_tiles, st)
-    if (H / Hkv <= 8) return fused ? SLB_LAUNCH_DECODE(1, true) : SLB_LAUNCH_DECODE(1, false);
-    return fused ? SLB_LAUNCH_DECODE(2, true) : SLB_LAUNCH_DECODE(2, false);
+#define SLB_LAUNCH_DECODE(NH_)                                                                           \
+    launch_decode<NH_>(q, ldq, map_k, map_v, out, ldo, block_table, max_pages, ctx_len, scratch,         \
+                       counters, S, H, Hkv, ps, box_rows, scale, window, num_splits, stages, split_coef, \
+                       unsplit_tiles, num_pages, st)
+    return H / Hkv <= 8 ? SLB_LAUNCH_DECODE(1) : SLB_LAUNCH_DECODE(2);
 #undef SLB_LAUNCH_DECODE
-}
-
-int slb_decode_attention_ws_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, bf16* out,
-                                 int ldo, const int* block_table, int max_pages, const int* ctx_len,
-                                 float* scratch, int* counters, int S, int H, int Hkv, int ps,
-                                 int num_pages, float scale, int window, int num_splits, int stages,
-                                 float split_coef, int unsplit_tiles, cudaStream_t st) {
-    const QkvSource none = {};
-    return run_decode(false, q, ldq, none, kc, vc, out, ldo, block_table, max_pages, ctx_len, scratch,
-                      counters, S, H, Hkv, ps, num_pages, scale, window, num_splits, stages, split_coef,
-                      unsplit_tiles, st);
-}
-
-// The same with the q|k|v projection of the step as input (see QkvSource): `parts` with
-// nparts > 0, else `qkv`; write_kv != 0: the new keys and values go into kc / vc.
-int slb_decode_attention_ws_fused_bf16(const float* parts, int nparts, long long part_stride,
-                                       const bf16* qkv, int ld_qkv, const float* bias,
-                                       const float* inv_freq, int rotary_dim, int write_kv, bf16* kc,
-                                       bf16* vc, bf16* out, int ldo, const int* block_table,
-                                       int max_pages, const int* ctx_len, float* scratch, int* counters,
-                                       int S, int H, int Hkv, int ps, int num_pages, float scale,
-                                       int window, int num_splits, int stages, float split_coef,
-                                       int unsplit_tiles, cudaStream_t st) {
-    QkvSource src = {};
-    src.parts = parts;
-    src.qkv = qkv;
-    src.nparts = nparts;
-    src.part_stride = part_stride;
-    src.ld = ld_qkv;
-    src.bias = bias;
-    src.inv_freq = inv_freq;
-    src.rotary_dim = inv_freq != nullptr ? rotary_dim : 0;
-    src.k_cache = write_kv ? kc : nullptr;
-    src.v_cache = write_kv ? vc : nullptr;
-    return run_decode(true, nullptr, 0, src, kc, vc, out, ldo, block_table, max_pages, ctx_len, scratch,
-                      counters, S, H, Hkv, ps, num_pages, scale, window, num_splits, stages, split_coef,
-                      unsplit_tiles, st);
 }
 
 }  // extern "C"
@@ -826,6 +693,7 @@ int slb_decode_attention_ws_fused_bf16(const float* parts, int nparts, long long
 extern "C" {
 int slb_decode_attention_ws_supported(int) { return 0; }
 int slb_decode_attention_ws_status(int) { return 0; }
+int slb_decode_attention_ws_splits_used(int) { return 0; }
 int slb_decode_attention_ws_max_splits() { return 1; }
 int slb_decode_attention_ws_tile_keys() { return 64; }
 long long slb_decode_attention_ws_scratch_bytes(int, int, int) { return 0; }
@@ -833,12 +701,6 @@ long long slb_decode_attention_ws_counters(int, int, int) { return 0; }
 int slb_decode_attention_ws_bf16(const bf16*, int, const bf16*, const bf16*, bf16*, int, const int*, int,
                                  const int*, float*, int*, int, int, int, int, int, float, int, int, int,
                                  float, int, cudaStream_t) {
-    return SLB_ERR_BAD_ARG;
-}
-int slb_decode_attention_ws_fused_bf16(const float*, int, long long, const bf16*, int, const float*,
-                                       const float*, int, int, bf16*, bf16*, bf16*, int, const int*, int,
-                                       const int*, float*, int*, int, int, int, int, int, float, int, int,
-                                       int, float, int, cudaStream_t) {
     return SLB_ERR_BAD_ARG;
 }
 }

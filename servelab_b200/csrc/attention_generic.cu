@@ -28,13 +28,17 @@
 #define AG_THREADS 256
 #define AG_MAX_D 256
 
+// 0, or 1 once a block-table entry pointed outside the cache (page >= num_pages): those keys
+// were read as zeros instead of from outside the pool.
+SLB_DEFINE_STATUS_WORD(generic_attention_status_word, slb_paged_attention_generic_status)
+
 template <typename T>
 __global__ void __launch_bounds__(AG_THREADS) paged_attention_generic_kernel(
     const T* __restrict__ q, int ldq, const T* __restrict__ kc, const T* __restrict__ vc,
     T* __restrict__ out, int ldo, const int* __restrict__ block_table, int max_pages,
     const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
     const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
-    int H, int Hkv, int D, int ps, float scale, int window) {
+    int H, int Hkv, int D, int ps, int num_pages, float scale, int window) {
     extern __shared__ float smem[];
     pdl_wait();
     const int ldd = D + 1;
@@ -90,7 +94,9 @@ __global__ void __launch_bounds__(AG_THREADS) paged_attention_generic_kernel(
             float kv = 0.f, vv = 0.f;
             if (kp < kend) {
                 const int page = table[kp / ps];
-                if (page >= 0) {
+                if (page >= num_pages) {
+                    atomicCAS(&generic_attention_status_word, 0, 1);
+                } else if (page >= 0) {
                     const size_t off = (((size_t)page * Hkv + kvh) * ps + kp % ps) * D + d;
                     kv = to_float(kc[off]);
                     vv = to_float(vc[off]);
@@ -167,23 +173,21 @@ template <typename T>
 static int launch_generic(const T* q, int ldq, const T* kc, const T* vc, T* out, int ldo,
                           const int* block_table, int max_pages, const int* cu_q,
                           const int* ctx_len, const int* tile_seq, const int* tile_row0,
-                          int num_tiles, int H, int Hkv, int D, int ps, float scale, int window,
-                          cudaStream_t st) {
+                          int num_tiles, int H, int Hkv, int D, int ps, int num_pages, float scale,
+                          int window, cudaStream_t st) {
     if (num_tiles <= 0) return 0;
-    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || D <= 0 || ps <= 0 || max_pages <= 0)
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || D <= 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0)
         return SLB_ERR_BAD_ARG;
     if (D > AG_MAX_D || Hkv > 65535) return SLB_ERR_TOO_LARGE;
     const size_t smem = ((size_t)(AG_BM + 2 * AG_BN) * (D + 1) + AG_BM * (AG_BN + 1)) * sizeof(float);
-    static size_t configured = 0;                 // per template instance
-    if (smem > 48 * 1024 && smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(paged_attention_generic_kernel<T>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = smem;
-    }
+    // the largest this kernel can ask for (head size AG_MAX_D), set once per device
+    constexpr size_t SMEM_MAX = ((size_t)(AG_BM + 2 * AG_BN) * (AG_MAX_D + 1) + AG_BM * (AG_BN + 1)) * sizeof(float);
+    static unsigned long long configured = 0;     // per template instance, a bit per device
+    const int rc = slb_configure(&configured, paged_attention_generic_kernel<T>, SMEM_MAX);
+    if (rc != 0) return rc;
     return slb_launch(paged_attention_generic_kernel<T>, dim3(num_tiles, Hkv), dim3(AG_THREADS), smem,
                       st, q, ldq, kc, vc, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq,
-                      tile_row0, H, Hkv, D, ps, scale, window);
+                      tile_row0, H, Hkv, D, ps, num_pages, scale, window);
 }
 
 extern "C" {
@@ -191,17 +195,17 @@ int slb_paged_attention_generic_f32(const float* q, int ldq, const float* kc, co
                                     float* out, int ldo, const int* block_table, int max_pages,
                                     const int* cu_q, const int* ctx_len, const int* tile_seq,
                                     const int* tile_row0, int num_tiles, int H, int Hkv, int D,
-                                    int ps, float scale, int window, cudaStream_t st) {
+                                    int ps, int num_pages, float scale, int window, cudaStream_t st) {
     return launch_generic<float>(q, ldq, kc, vc, out, ldo, block_table, max_pages, cu_q, ctx_len,
-                                 tile_seq, tile_row0, num_tiles, H, Hkv, D, ps, scale, window, st);
+                                 tile_seq, tile_row0, num_tiles, H, Hkv, D, ps, num_pages, scale, window, st);
 }
 int slb_paged_attention_generic_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc,
                                      bf16* out, int ldo, const int* block_table, int max_pages,
                                      const int* cu_q, const int* ctx_len, const int* tile_seq,
                                      const int* tile_row0, int num_tiles, int H, int Hkv, int D,
-                                     int ps, float scale, int window, cudaStream_t st) {
+                                     int ps, int num_pages, float scale, int window, cudaStream_t st) {
     return launch_generic<bf16>(q, ldq, kc, vc, out, ldo, block_table, max_pages, cu_q, ctx_len,
-                                tile_seq, tile_row0, num_tiles, H, Hkv, D, ps, scale, window, st);
+                                tile_seq, tile_row0, num_tiles, H, Hkv, D, ps, num_pages, scale, window, st);
 }
 // rows per tile of the generic kernel (the host builds the tile list with it)
 int slb_paged_attention_generic_tile_rows() { return AG_BM; }

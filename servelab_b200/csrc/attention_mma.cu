@@ -59,7 +59,7 @@ __device__ __forceinline__ void load_kv_tile_bulk(bf16* Ks, bf16* Vs, uint64_t* 
                                                   const bf16* __restrict__ kc,
                                                   const bf16* __restrict__ vc,
                                                   const int* __restrict__ table, int k0, int kend,
-                                                  int kvh, int Hkv, int ps) {
+                                                  int kvh, int Hkv, int ps, int num_pages) {
     static_assert(NTHREADS == 2 * BN, "one row of K or V per thread");
     const int r = threadIdx.x & (BN - 1);
     const bool is_v = threadIdx.x >= BN;
@@ -71,6 +71,10 @@ __device__ __forceinline__ void load_kv_tile_bulk(bf16* Ks, bf16* Vs, uint64_t* 
         const int lp = pow2 ? kp >> (__ffs(ps) - 1) : kp / ps;
         slot = pow2 ? kp & (ps - 1) : kp - lp * ps;
         page = table[lp];
+        if (page >= num_pages) {                            // outside the cache: read as zeros
+            atomicCAS(&attn_status_word, 0, 0x40);
+            page = -1;
+        }
         ok = page >= 0;
     }
     bf16* dst = (is_v ? Vs : Ks) + r * LDS;
@@ -91,7 +95,7 @@ __device__ __forceinline__ void load_kv_tile_bulk(bf16* Ks, bf16* Vs, uint64_t* 
 __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __restrict__ kc,
                                              const bf16* __restrict__ vc,
                                              const int* __restrict__ table, int k0, int kend,
-                                             int kvh, int Hkv, int ps) {
+                                             int kvh, int Hkv, int ps, int num_pages) {
     const bool pow2 = (ps & (ps - 1)) == 0;
     const int shift = __ffs(ps) - 1;
     for (int idx = threadIdx.x; idx < BN * CHUNKS; idx += NTHREADS) {
@@ -102,6 +106,10 @@ __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __r
         const int slot = pow2 ? kp & (ps - 1) : kp - lp * ps;
         int page = -1;
         if (ok) page = table[lp];
+        if (page >= num_pages) {                            // outside the cache: read as zeros
+            atomicCAS(&attn_status_word, 0, 0x40);
+            page = -1;
+        }
         ok = ok && page >= 0;
         const size_t off = ok ? (((size_t)page * Hkv + kvh) * ps + slot) * D + c * 8 : 0;
         cp_async16(Ks + r * LDS + c * 8, kc + off, ok);
@@ -224,7 +232,7 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
     bf16* __restrict__ out, int ldo, const int* __restrict__ block_table, int max_pages,
     const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
     const int* __restrict__ tile_seq, const int* __restrict__ tile_row0, int H, int Hkv, int ps,
-    float scale_log2, int window) {
+    int num_pages, float scale_log2, int window) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_wait();
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [BM][LDS], later the output stage
@@ -264,7 +272,7 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
     const int kend = p_last + 1;
     const int ntiles = (kend - kbeg + BN - 1) / BN;
 
-    load_kv_tile(stage0, stage0 + BN * LDS, kc, vc, table, kbeg, kend, kvh, Hkv, ps);
+    load_kv_tile(stage0, stage0 + BN * LDS, kc, vc, table, kbeg, kend, kvh, Hkv, ps, num_pages);
     cp_async_commit();
 
     // this thread's two rows
@@ -289,7 +297,7 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
         bf16* Vs = Ks + BN * LDS;
         if (t + 1 < ntiles) {
             bf16* Kn = stage0 + ((t + 1) & 1) * STAGE_ELEMS;
-            load_kv_tile(Kn, Kn + BN * LDS, kc, vc, table, kbeg + (t + 1) * BN, kend, kvh, Hkv, ps);
+            load_kv_tile(Kn, Kn + BN * LDS, kc, vc, table, kbeg + (t + 1) * BN, kend, kvh, Hkv, ps, num_pages);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -351,7 +359,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
     const bf16* __restrict__ q, int ldq, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
     bf16* __restrict__ out, int ldo, const int* __restrict__ block_table, int max_pages,
     const int* __restrict__ ctx_len, float* __restrict__ part_o, float* __restrict__ part_ml,
-    int H, int Hkv, int ps, float scale_log2, int window, int num_splits, int head_tiles) {
+    int H, int Hkv, int ps, int num_pages, float scale_log2, int window, int num_splits, int head_tiles) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_wait();
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [16][LDS]
@@ -399,7 +407,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
         if (p < ntiles) {
             bf16* Kp = stage0 + p * STAGE_ELEMS;
             load_kv_tile_bulk(Kp, Kp + BN * LDS, &full_bar[p], kc, vc, table, kstart + p * BN, ctx,
-                              kvh, Hkv, ps);
+                              kvh, Hkv, ps, num_pages);
         }
     }
     cp_async_wait<0>();                                     // the Q tile
@@ -423,7 +431,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
         if (tn < ntiles) {
             bf16* Kn = stage0 + (tn % DSTAGES) * STAGE_ELEMS;
             load_kv_tile_bulk(Kn, Kn + BN * LDS, &full_bar[tn % DSTAGES], kc, vc, table,
-                              kstart + tn * BN, ctx, kvh, Hkv, ps);
+                              kstart + tn * BN, ctx, kvh, Hkv, ps, num_pages);
         }
         ok = mbar_wait(&full_bar[t % DSTAGES], (t / DSTAGES) & 1);
         if (t == 0) {
@@ -448,6 +456,13 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
             // for them once more (bounded), then leave without writing a result
             for (int tt = t; tt < min(ntiles, t + DSTAGES); ++tt)
                 mbar_wait(&full_bar[tt % DSTAGES], (tt / DSTAGES) & 1);
+            // the combine step must not merge what an earlier launch left in these slots:
+            // mark this split of every head as empty (maximum -inf, sum 0)
+            if (num_splits > 1 && tid < nrows) {
+                const size_t pi = ((size_t)s * H + kvh * g + h0 + tid) * num_splits + split;
+                part_ml[pi * 2] = -INFINITY;
+                part_ml[pi * 2 + 1] = 0.f;
+            }
             return;
         }
     }
@@ -559,35 +574,30 @@ long long slb_decode_attention_scratch_bytes(int S, int H, int num_splits) {
 int slb_prefill_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, bf16* out,
                                int ldo, const int* block_table, int max_pages, const int* cu_q,
                                const int* ctx_len, const int* tile_seq, const int* tile_row0,
-                               int num_tiles, int H, int Hkv, int ps, float scale, int window,
-                               cudaStream_t st) {
+                               int num_tiles, int H, int Hkv, int ps, int num_pages, float scale,
+                               int window, cudaStream_t st) {
     if (num_tiles <= 0) return 0;
-    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || !(scale > 0.f))
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0 || !(scale > 0.f))
         return SLB_ERR_BAD_ARG;
     if (ldq % 8 || ldo % 8 || ((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)out) % 16)
         return SLB_ERR_BAD_ARG;                            // 16-byte copies
     if ((long long)num_tiles * Hkv > 0x7fffffffll) return SLB_ERR_TOO_LARGE;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)PREFILL_SMEM);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static unsigned long long configured = 0;              // a bit per device
+    const int crc = slb_configure(&configured, prefill_attention_kernel, PREFILL_SMEM);
+    if (crc != 0) return crc;
     return slb_launch(prefill_attention_kernel, dim3((unsigned)num_tiles * Hkv), dim3(NTHREADS), PREFILL_SMEM, st,
                       q, ldq, kc, vc, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq,
-                      tile_row0, H, Hkv, ps, scale * 1.4426950408889634f, window);
+                      tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window);
 }
 
 // scratch: float32 buffer of at least slb_decode_attention_scratch_bytes(...) bytes
 // (may be null when num_splits == 1).
 int slb_decode_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, bf16* out,
                               int ldo, const int* block_table, int max_pages, const int* ctx_len,
-                              float* scratch, int S, int H, int Hkv, int ps, float scale,
-                              int window, int num_splits, cudaStream_t st) {
+                              float* scratch, int S, int H, int Hkv, int ps, int num_pages,
+                              float scale, int window, int num_splits, cudaStream_t st) {
     if (S <= 0) return 0;
-    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || !(scale > 0.f))
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0 || !(scale > 0.f))
         return SLB_ERR_BAD_ARG;
     if (num_splits < 1 || (num_splits > 1 && scratch == nullptr)) return SLB_ERR_BAD_ARG;
     if (ldq % 8 || ((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc) % 16) return SLB_ERR_BAD_ARG;
@@ -595,19 +605,14 @@ int slb_decode_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf16
     const int g = H / Hkv;
     const int head_tiles = (g + 15) / 16;
     if (Hkv * head_tiles > 65535) return SLB_ERR_TOO_LARGE;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)DECODE_SMEM);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static unsigned long long configured = 0;              // a bit per device
+    const int crc = slb_configure(&configured, decode_attention_kernel, DECODE_SMEM);
+    if (crc != 0) return crc;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)S * H * num_splits * D : nullptr;
     const int rc = slb_launch(decode_attention_kernel, dim3(num_splits, Hkv * head_tiles, S),
                               dim3(NTHREADS), DECODE_SMEM, st, q, ldq, kc, vc, out, ldo, block_table,
-                              max_pages, ctx_len, part_o, part_ml, H, Hkv, ps,
+                              max_pages, ctx_len, part_o, part_ml, H, Hkv, ps, num_pages,
                               scale * 1.4426950408889634f, window, num_splits, head_tiles);
     if (rc != 0 || num_splits == 1) return rc;
     return slb_launch(decode_combine_kernel, dim3(H, S), dim3((D + 31) / 32 * 32), 0, st,
@@ -670,8 +675,8 @@ const char* slb_decode_attention_noalloc_strerror(int code) {
 
 int slb_decode_attention_bf16_noalloc(const bf16* q, int ldq, const bf16* kc, const bf16* vc,
                                       bf16* out, int ldo, const int* block_table, int max_pages,
-                                      const int* ctx_len, int S, int H, int Hkv, int ps, float scale,
-                                      int window, int num_splits, cudaStream_t st) {
+                                      const int* ctx_len, int S, int H, int Hkv, int ps, int num_pages,
+                                      float scale, int window, int num_splits, cudaStream_t st) {
     if (S <= 0) return 0;
     if (H <= 0 || num_splits < 1) return SLB_ERR_BAD_ARG;
     if (slb_decode_attention_scratch_bytes(S, H, num_splits) > NOALLOC_SCRATCH_BYTES)
@@ -680,7 +685,7 @@ int slb_decode_attention_bf16_noalloc(const bf16* q, int ldq, const bf16* kc, co
     const int rc = noalloc_scratch_address(&scratch);
     if (rc != 0) return rc;
     return slb_decode_attention_bf16(q, ldq, kc, vc, out, ldo, block_table, max_pages, ctx_len,
-                                     scratch, S, H, Hkv, ps, scale, window, num_splits, st);
+                                     scratch, S, H, Hkv, ps, num_pages, scale, window, num_splits, st);
 }
 
 }  // extern "C"

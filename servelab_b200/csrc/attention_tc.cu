@@ -516,17 +516,16 @@ int slb_prefill_attention_tc_bf16(const bf16* q, int ldq, const bf16* kc, const 
     const int box_rows = ps < BN ? ps : BN;
     CUtensorMap map_k, map_v;
     const long long rows = (long long)num_pages * Hkv * ps;
+    if (rows > 0x7fffffffll) return SLB_ERR_TOO_LARGE;    // box coordinates are 32-bit
+    // (a block-table entry outside [0, num_pages) names rows outside the tensor map: the copy
+    // reads zeros there, never memory outside the cache)
     int rc = make_cache_map(&map_k, kc, rows, box_rows);
     if (rc != 0) return rc;
     rc = make_cache_map(&map_v, vc, rows, box_rows);
     if (rc != 0) return rc;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_ATTN_SMEM);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static unsigned long long configured = 0;              // a bit per device
+    rc = slb_configure(&configured, prefill_attention_tc_kernel, TC_ATTN_SMEM);
+    if (rc != 0) return rc;
     int* status = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&status, tc_attn_status);
     if (e != cudaSuccess) return (int)e;

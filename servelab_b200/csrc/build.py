@@ -32,7 +32,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--compiler-options", "-fPIC",
               "-Xcudafe", "--diag_suppress=177"]
 
 CORE_SOURCES = ["elementwise.cu", "rope_cache.cu", "attention_generic.cu", "gemm_simt.cu",
-                "sampling.cu", "gemm_skinny.cu", "gemm_tcgen05.cu"]
+                "sampling.cu", "gemm_tcgen05.cu"]
 HEADERS = ["common.cuh", "no_alloc.h", "mma_util.cuh", "tma_util.cuh"]
 
 _lock = threading.Lock()

@@ -91,6 +91,24 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 }
 
 extern int slb_pdl_enabled;          // defined once per shared library (SLB_DEFINE_PDL_SWITCH)
+// Non-zero: the long kernels (matrix products, attention) let their successor be scheduled at
+// their start instead of after their main loop, so that its blocks become resident beside
+// theirs wherever an SM has room and fetch their first weight tiles while these still run.
+extern int slb_pdl_early;
+
+// cudaFuncSetAttribute(max dynamic shared memory) once per device for one kernel: `done` is
+// the caller's static word for that kernel (bit d = done on device d); the attribute belongs
+// to the device that is current, so a process that uses several devices sets it on each.
+template <typename Kernel>
+static inline int slb_configure(unsigned long long* done, Kernel kernel, size_t smem) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return SLB_ERR_BAD_ARG;
+    if (dev >= 0 && dev < 64 && (*done >> dev & 1ull)) return 0;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    if (dev >= 0 && dev < 64) *done |= 1ull << dev;
+    return 0;
+}
 
 template <typename... KArgs, typename... Args>
 static inline int slb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
@@ -108,10 +126,30 @@ static inline int slb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// A status word on the device with its host accessor `fn(reset)`: 0, or the code of the first
+// event recorded since the last reset.  Reading synchronises with the device.
+#define SLB_DEFINE_STATUS_WORD(var, fn)                                               \
+    __device__ int var = 0;                                                           \
+    extern "C" int fn(int reset) {                                                    \
+        int v = 0;                                                                    \
+        if (cudaMemcpyFromSymbol(&v, var, sizeof(int)) != cudaSuccess) return -1;     \
+        if (reset && v != 0) {                                                        \
+            const int zero = 0;                                                       \
+            cudaMemcpyToSymbol(var, &zero, sizeof(int));                              \
+        }                                                                             \
+        return v;                                                                     \
+    }
+
 #define SLB_DEFINE_PDL_SWITCH                                                         \
     int slb_pdl_enabled = 0;                                                          \
+    int slb_pdl_early = 0;                                                            \
     extern "C" int slb_set_pdl(int on) {                                              \
         const int old = slb_pdl_enabled;                                              \
         slb_pdl_enabled = on ? 1 : 0;                                                 \
+        return old;                                                                   \
+    }                                                                                 \
+    extern "C" int slb_set_pdl_early(int on) {                                        \
+        const int old = slb_pdl_early;                                                \
+        slb_pdl_early = on ? 1 : 0;                                                   \
         return old;                                                                   \
     }

@@ -28,11 +28,11 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
     *reinterpret_cast<uint2*>(p) = raw;
 }
 
-// out[t, :] = table[ids[t], :] as float32.  An id outside [0, vocab) yields a
+// out[t, :] = table[ids[t], :] * scale as float32.  An id outside [0, vocab) yields a
 // row of zeros (callers validate ids on the host).  VEC: h % 4 == 0.
 template <typename T, bool VEC>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                 float* __restrict__ out, int h, int vocab) {
+                                 float* __restrict__ out, int h, int vocab, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -41,10 +41,25 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     const T* row = table + (size_t)(ok ? id : 0) * h;
     float* o = out + (size_t)t * h;
     if (VEC) {
-        for (int i = threadIdx.x * 4; i < h; i += blockDim.x * 4)
-            store4(o + i, ok ? load4(row + i) : make_float4(0.f, 0.f, 0.f, 0.f));
+        for (int i = threadIdx.x * 4; i < h; i += blockDim.x * 4) {
+            float4 v = ok ? load4(row + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+            store4(o + i, v);
+        }
     } else {
-        for (int i = threadIdx.x; i < h; i += blockDim.x) o[i] = ok ? to_float(row[i]) : 0.f;
+        for (int i = threadIdx.x; i < h; i += blockDim.x) o[i] = ok ? to_float(row[i]) * scale : 0.f;
+    }
+}
+
+// logits[r, v] = cap * tanh(logits[r, v] * scale / cap) (cap > 0), or logits * scale: what
+// some architectures do to their logits after the LM head.  In place, float32.
+__global__ void logit_transform_kernel(float* __restrict__ logits, int ld, int V, float scale, float cap) {
+    pdl_launch_dependents();
+    pdl_wait();
+    float* row = logits + (size_t)blockIdx.y * ld;
+    for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < V; v += gridDim.x * blockDim.x) {
+        const float x = row[v] * scale;
+        row[v] = cap > 0.f ? cap * tanhf(x / cap) : x;
     }
 }
 
@@ -276,12 +291,12 @@ static int norm_threads(int h) {
 
 template <typename T>
 static int launch_embedding(const int* ids, const T* table, float* out, int T_, int h, int vocab,
-                            cudaStream_t st) {
+                            float scale, cudaStream_t st) {
     if (T_ <= 0) return 0;
     if (h <= 0 || vocab <= 0) return SLB_ERR_BAD_ARG;
     if (h % 4 == 0)
-        return slb_launch(embedding_kernel<T, true>, dim3(T_), dim3(256), 0, st, ids, table, out, h, vocab);
-    return slb_launch(embedding_kernel<T, false>, dim3(T_), dim3(256), 0, st, ids, table, out, h, vocab);
+        return slb_launch(embedding_kernel<T, true>, dim3(T_), dim3(256), 0, st, ids, table, out, h, vocab, scale);
+    return slb_launch(embedding_kernel<T, false>, dim3(T_), dim3(256), 0, st, ids, table, out, h, vocab, scale);
 }
 
 template <typename TD, typename TO>
@@ -327,13 +342,23 @@ SLB_DEFINE_PDL_SWITCH
 
 extern "C" {
 
+// out[t] = table[ids[t]] * scale as float32 (scale 1 for architectures without an embedding scale)
 int slb_embedding_f32(const int* ids, const float* table, float* out, int T, int h, int vocab,
-                      cudaStream_t st) {
-    return launch_embedding<float>(ids, table, out, T, h, vocab, st);
+                      float scale, cudaStream_t st) {
+    return launch_embedding<float>(ids, table, out, T, h, vocab, scale, st);
 }
 int slb_embedding_bf16(const int* ids, const bf16* table, float* out, int T, int h, int vocab,
-                       cudaStream_t st) {
-    return launch_embedding<bf16>(ids, table, out, T, h, vocab, st);
+                       float scale, cudaStream_t st) {
+    return launch_embedding<bf16>(ids, table, out, T, h, vocab, scale, st);
+}
+
+// logits [R, V] float32 (leading dimension ld), in place: multiplied by scale, then with
+// cap > 0 bounded to cap * tanh(x / cap).
+int slb_logit_transform(float* logits, int ld, int R, int V, float scale, float cap, cudaStream_t st) {
+    if (R <= 0 || V <= 0) return 0;
+    if (ld < V || R > 65535 || !(cap >= 0.f)) return SLB_ERR_BAD_ARG;
+    const int blocks = (V + 1023) / 1024 < 64 ? (V + 1023) / 1024 : 64;
+    return slb_launch(logit_transform_kernel, dim3(blocks, R), dim3(256), 0, st, logits, ld, V, scale, cap);
 }
 
 int slb_add_rmsnorm_f32(float* resid, const float* delta, const float* weight, float* out,

@@ -18,9 +18,7 @@
 //
 // A second kernel (gemm_tc_cluster_kernel, further down) runs the K splits of a row tile as
 // one thread-block cluster that adds its accumulators up through distributed shared memory,
-// with epilogues that finish the result (store, q|k|v rotation and cache write, add into the
-// residual stream); both kernels can build the x operand from the float32 residual stream
-// (the RMS norm before the product) instead of fetching it.
+// with epilogues that finish the result (store; q|k|v rotation and cache write).
 //
 // Every wait on an mbarrier is bounded: after SLB_TC_SPIN_LIMIT polls the role
 // records a code in the status word, leaves its loop, and the block frees its TMEM
@@ -118,149 +116,15 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "r"(taddr));
 }
 
-// Weights to pull into the L2 cache for the product that follows this one: the first
-// `bytes` of that matrix, requested in pieces of chunk_bytes (a request costs the issuing
-// warp tens of cycles whatever its size, so the pieces are large and few).  The requests
-// are issued when this block's own tiles have all arrived, so they fill the time in which
-// the small kernels between two products leave the memory idle.
-struct Prefetch {
-    const unsigned char* ptr;
-    long long bytes;
-    int chunk_bytes;
-};
-__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-
-// The x operand as the RMS norm of the float32 residual stream, built by the loader warp
-// instead of fetched by TMA: x[tok][k] = resid[tok][k] * rstd[tok] * weight[k], with
-// rstd[tok] = 1 / sqrt(sum_t sumsq[t][tok] / K + eps) from the partial sums of squares that
-// the product before the norm left per row tile (its EPI_RESID epilogue).  Up to 16 tokens.
-struct NormIn {
-    const float* resid;                 // [M][ld], every update already added; null: x comes by TMA
-    int ld;
-    const float* sumsq;                 // [tiles][M]
-    int tiles;
-    const float* weight;                // [K]
-    float eps;
-};
-constexpr int NORM_IN_MAX_TOK = 16;
-
-__device__ __forceinline__ void mbar_arrive_plain(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-// With NormIn the full barrier of a stage counts two arrivals: the loader thread's, with the
-// bytes of the W tile it requests by TMA, and that of the warp that wrote the stage's x tile.
-__device__ __forceinline__ void load_w_only(const CUtensorMap* map_w, unsigned char* a_stage, int stages,
-                                            uint64_t* full, uint64_t* empty, int kb_begin, int iters,
-                                            int n0, int* status, int code) {
-    const int ahead = min(iters, stages);
-    for (int i = 0; i < ahead; ++i) {                      // W is written by no kernel
-        mbar_expect_tx(&full[i], A_STAGE_BYTES);
-        tma_load_2d(a_stage + i * A_STAGE_BYTES, map_w, &full[i], (kb_begin + i) * TC_BK, n0);
-    }
-    for (int i = ahead; i < iters; ++i) {
-        const int s = i % stages;
-        if (!mbar_wait(&empty[s], ((i / stages) & 1) ^ 1)) {
-            atomicCAS(status, 0, (1 << 8) | code);
-            break;
-        }
-        mbar_expect_tx(&full[s], A_STAGE_BYTES);
-        tma_load_2d(a_stage + s * A_STAGE_BYTES, map_w, &full[s], (kb_begin + i) * TC_BK, n0);
-    }
-}
-
-// The x tiles, written by the four epilogue warps while the main loop runs (they have nothing
-// else to do until the accumulator is complete): warp xw takes the k-blocks i = xw, xw + 4, ...
-// of this block, so each has four k-blocks' time for the loads of one.  The residual rows and
-// norm weights of its next k-block are loaded before the current one is converted.  Called
-// after pdl_wait() by whole warps.
-__device__ __forceinline__ void produce_x_normed(const NormIn& nin, unsigned char* b_stage, int b_stage_bytes_,
-                                                 int stages, uint64_t* full, uint64_t* empty, int kb_begin,
-                                                 int iters, int M, int K, int ntok16, int* status, int xw) {
-    const int lane = threadIdx.x & 31;
-    float rstd = 0.f;
-    if (lane < M) {
-        float ss = 0.f;
-        for (int t = 0; t < nin.tiles; ++t) ss += nin.sumsq[(size_t)t * M + lane];
-        rstd = 1.0f / sqrtf(ss / (float)K + nin.eps);
-    }
-    // A k-block's x tile is M * 8 chunks of 16 bytes; a lane handles chunk `lane` and
-    // `lane + 32` of each half of 64 chunks (8 tokens).  Few registers on purpose: with
-    // fewer than about 100 a thread, a third block fits on an SM beside two of the kernel
-    // before this one and requests its first weight tiles while they finish.
-    const int chunks = M * 8;
-    for (int i = xw; i < iters; i += 4) {
-        const int s = i % stages;
-        const int k0 = (kb_begin + i) * TC_BK;
-        unsigned char* tile = b_stage + s * b_stage_bytes_;
-        bool waited = i < stages;                          // the first use of a stage needs no wait
-        if (waited)
-            for (int off = M * 128 + lane * 16; off < ntok16 * 128; off += 32 * 16)
-                *reinterpret_cast<uint4*>(tile + off) = make_uint4(0, 0, 0, 0);   // rows beyond the tokens
-        bool ok = true;
-        for (int half = 0; half * 64 < chunks && ok; ++half) {
-            float4 v[2][4];                                // residual (2) and weight (2) per chunk
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                const int idx = half * 64 + c * 32 + lane;
-                const int tok = idx >> 3, k = k0 + (idx & 7) * 8;
-                if (idx < chunks && k < K) {               // K is a multiple of 8
-                    const float4* src = reinterpret_cast<const float4*>(nin.resid + (size_t)tok * nin.ld + k);
-                    const float4* wsrc = reinterpret_cast<const float4*>(nin.weight + k);
-                    v[c][0] = __ldcg(src);
-                    v[c][1] = __ldcg(src + 1);
-                    v[c][2] = __ldg(wsrc);
-                    v[c][3] = __ldg(wsrc + 1);
-                } else {
-                    v[c][0] = v[c][1] = v[c][2] = v[c][3] = make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-            }
-            if (!waited) {                                 // the loads are in flight meanwhile
-                if (lane == 0) ok = mbar_wait(&empty[s], ((i / stages) & 1) ^ 1);
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                waited = true;
-                if (!ok) break;
-            }
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                const int idx = half * 64 + c * 32 + lane;
-                const int tok = idx >> 3, j = idx & 7;
-                const float r = __shfl_sync(0xffffffffu, rstd, tok & 31);
-                if (idx < chunks) {
-                    const float4 a = v[c][0], b = v[c][1], w0 = v[c][2], w1 = v[c][3];
-                    __nv_bfloat162 o[4];
-                    o[0] = __floats2bfloat162_rn(a.x * r * w0.x, a.y * r * w0.y);
-                    o[1] = __floats2bfloat162_rn(a.z * r * w0.z, a.w * r * w0.w);
-                    o[2] = __floats2bfloat162_rn(b.x * r * w1.x, b.y * r * w1.y);
-                    o[3] = __floats2bfloat162_rn(b.z * r * w1.z, b.w * r * w1.w);
-                    // 128-byte swizzle of a K-major tile: chunk j of row tok sits at chunk j ^ (tok & 7)
-                    *reinterpret_cast<uint4*>(tile + tok * 128 + ((j ^ (tok & 7)) << 4)) =
-                        *reinterpret_cast<const uint4*>(o);
-                }
-            }
-        }
-        if (!ok) {
-            if (lane == 0) atomicCAS(status, 0, (4 << 8) | 1);
-            break;
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the MMA reads through the async proxy
-        __syncwarp();
-        if (lane == 0) mbar_arrive_plain(&full[s]);
-    }
-    __syncwarp();
-}
-
 // grid (row tiles of W, K splits).  ntok16: tokens padded to a multiple of 16.
 // splits == 1: `out` receives the result (+ bias) in its dtype; otherwise `partial`
 // receives float32 [split][M][N].
-template <typename TO, bool NORM_IN>
+template <typename TO>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     TO* __restrict__ out, int ldo, float* __restrict__ partial, const float* __restrict__ bias,
-    int M, int N, int K, int ntok16, int max_stages, int* __restrict__ status, Prefetch pf, int swiglu,
-    const NormIn nin) {
+    int M, int N, int K, int ntok16, int max_stages, int* __restrict__ status, int swiglu,
+    int pdl_early) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -284,7 +148,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
-            mbar_init(&full[s], NORM_IN ? 2 : 1);
+            mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
         mbar_init(accum, 1);
@@ -299,14 +163,13 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *tmem_slot;
+    if (pdl_early) pdl_launch_dependents();
 
     if (warp == 0) {
         // ------------------------------------------------------------ loader
         // W is written by no kernel, x by the preceding one: the W tiles of the first
         // stages are requested at once, the x tiles after the wait for that kernel.
-        if constexpr (NORM_IN) {
-            if (lane == 0) load_w_only(&map_w, a_stage, TC_STAGES, full, empty, kb_begin, iters, n0, status, 3);
-        } else if (lane == 0) {
+        if (lane == 0) {
             const uint32_t bytes = A_STAGE_BYTES + (uint32_t)ntok16 * TC_BK * 2;
             const int ahead = min(iters, TC_STAGES);
             for (int i = 0; i < ahead; ++i) {                 // stages are empty at the start
@@ -356,9 +219,6 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
         // ------------------------------------------------------------ epilogue
         pdl_wait();                                          // nothing is written before the
                                                              // preceding kernel has finished
-        if constexpr (NORM_IN)
-            produce_x_normed(nin, b_stage, B_STAGE_BYTES, TC_STAGES, full, empty, kb_begin, iters, M, K, ntok16,
-                             status, warp - 2);
         const int quarter = warp & 3;                        // TMEM lanes this warp may read
         const int row = quarter * 32 + lane;                 // row of the tile = row of W
         const int n = n0 + row;
@@ -369,18 +229,6 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         pdl_launch_dependents();
-        if (pf.ptr != nullptr) {
-            const long long items = (pf.bytes + pf.chunk_bytes - 1) / pf.chunk_bytes;
-            const long long stride = (long long)(gridDim.x * gridDim.y) * (TC_THREADS - 64);
-            // consecutive pieces go to different blocks (one thread of a block at a time)
-            const long long first = (long long)(threadIdx.x - 64) * (gridDim.x * gridDim.y) +
-                                    (blockIdx.y * gridDim.x + blockIdx.x);
-            for (long long it = first; it < items; it += stride) {
-                const long long off = it * pf.chunk_bytes;
-                const long long left = pf.bytes - off;
-                prefetch_l2(pf.ptr + off, (uint32_t)(left < pf.chunk_bytes ? left : pf.chunk_bytes) & ~15u);
-            }
-        }
         if (swiglu) {
             // W holds gate and up rows alternating in runs of 64, so this tile's rows are 64
             // gates and their 64 ups: the upper two warps park the ups in shared memory (the
@@ -478,24 +326,14 @@ __global__ void gemm_tc_reduce_kernel(const float* __restrict__ partial, TO* __r
 //              token's position, q written to q_out, k and v into the token's slot of the
 //              paged cache (the arithmetic of the kernel in rope_cache.cu).  A row tile
 //              must hold whole heads: head sizes 16, 32, 64, 128.
-//   EPI_RESID  resid[tok, n] += sum + bias[n] (the float32 residual stream), and the sum of
-//              squares of the tile's 128 updated values of every token to sumsq[tile][tok]:
-//              what the RMS norm that follows needs, so that the product after it can
-//              build its normed input itself (NormIn above).
-enum { EPI_STORE = 0, EPI_ROPE = 1, EPI_RESID = 2 };
-
-struct ResidEpilogue {
-    float* resid;                       // [M][ld]
-    int ld;
-    float* sumsq;                       // [row tiles][M]
-};
+enum { EPI_STORE = 0, EPI_ROPE = 1 };
 
 struct RopeEpilogue {
     const float* bias;                  // [N] or null
     const int* positions;               // [M]
     const int* seq_of_token;            // [M]
     const int* block_table;             // [requests][max_pages]
-    int max_pages, page_size;
+    int max_pages, page_size, num_pages;
     const float* inv_freq;              // [rotary_dim / 2] or null
     int rotary_dim;
     bf16* q_out;
@@ -527,12 +365,11 @@ __device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank)
     return v;
 }
 
-template <int EPI, bool NORM_IN>
+template <int EPI>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     bf16* __restrict__ out, int ldo, const float* __restrict__ bias, int M, int N, int K, int ntok16,
-    int max_stages, int* __restrict__ status, const RopeEpilogue rope, const ResidEpilogue res,
-    const NormIn nin) {
+    int max_stages, int* __restrict__ status, const RopeEpilogue rope, int pdl_early) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -545,7 +382,6 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     uint64_t* accum = empty + TC_MAX_STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
     __shared__ float pair_vals[2][TC_BM];                    // EPI_ROPE: a token's row of the tile
-    __shared__ float warp_sq[2][4];                          // EPI_RESID: sums of squares per warp
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * TC_BM;
@@ -558,7 +394,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
-            mbar_init(&full[s], NORM_IN ? 2 : 1);
+            mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
         mbar_init(accum, 1);
@@ -574,11 +410,10 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *tmem_slot;
     float* acc = reinterpret_cast<float*>(a_stage);          // [ntok16][TC_BM] once the ring is idle
+    if (pdl_early) pdl_launch_dependents();
 
     if (warp == 0) {
-        if constexpr (NORM_IN) {
-            if (lane == 0) load_w_only(&map_w, a_stage, TC_STAGES, full, empty, kb_begin, iters, n0, status, 4);
-        } else if (lane == 0) {
+        if (lane == 0) {
             const uint32_t bytes = A_STAGE_BYTES + (uint32_t)ntok16 * TC_BK * 2;
             const int ahead = min(iters, TC_STAGES);
             for (int i = 0; i < ahead; ++i) {
@@ -627,9 +462,6 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     } else {
         // ------------------------------------------ epilogue, part 1: accumulator -> acc
         pdl_wait();
-        if constexpr (NORM_IN)
-            produce_x_normed(nin, b_stage, B_STAGE_BYTES, TC_STAGES, full, empty, kb_begin, iters, M, K, ntok16,
-                             status, warp - 2);
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         bool ok = true;
@@ -667,20 +499,6 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
             for (uint32_t p = 0; p < nranks; ++p) sum += ld_peer_f32(addr, p);
             if constexpr (EPI == EPI_STORE) {
                 if (n < N) out[(size_t)tok * ldo + n] = __float2bfloat16_rn(sum + (bias ? bias[n] : 0.f));
-            } else if constexpr (EPI == EPI_RESID) {
-                float r = 0.f;
-                if (n < N) {
-                    float* dst = res.resid + (size_t)tok * res.ld + n;
-                    r = *dst + (sum + (bias ? bias[n] : 0.f));
-                    *dst = r;
-                }
-                const float sq = warp_sum(r * r);
-                if (lane == 0) warp_sq[parity][warp & 3] = sq;
-                asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps
-                if (row == 0)
-                    res.sumsq[(size_t)blockIdx.x * M + tok] =
-                        ((warp_sq[parity][0] + warp_sq[parity][1]) + warp_sq[parity][2]) + warp_sq[parity][3];
-                parity ^= 1;
             } else {
                 const int D = rope.D;
                 const int half = rope.inv_freq != nullptr ? rope.rotary_dim >> 1 : 0;
@@ -704,7 +522,9 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
                     } else if (rope.k_cache != nullptr) {
                         const int page = rope.block_table[(size_t)rope.seq_of_token[tok] * rope.max_pages +
                                                           pos / rope.page_size];
-                        if (page >= 0) {
+                        if (page >= rope.num_pages) {            // outside the cache: not written
+                            atomicCAS(status, 0, (5 << 8) | 1);
+                        } else if (page >= 0) {
                             const int kvh = is_v ? j - rope.H - rope.Hkv : j - rope.H;
                             dst = (is_v ? rope.v_cache : rope.k_cache) +
                                   (((size_t)page * rope.Hkv + kvh) * rope.page_size + pos % rope.page_size) * D;
@@ -757,47 +577,30 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box
     return r == CUDA_SUCCESS ? 0 : SLB_ERR_BAD_ARG;
 }
 
-template <typename TO, bool NORM_IN>
+template <typename TO>
 int run(const bf16* x, int ldx, const bf16* W, int ldw, TO* out, int ldo, const float* bias,
-        float* workspace, int M, int N, int K, int splits, int max_stages, int defer_sum,
-        const Prefetch& pf, int swiglu, const NormIn& nin, cudaStream_t st) {
-    CUtensorMap map_w, map_x = {};
+        float* workspace, int M, int N, int K, int splits, int max_stages, int defer_sum, int swiglu,
+        cudaStream_t st) {
+    CUtensorMap map_w, map_x;
     const int ntok16 = (M + 15) / 16 * 16;
     int rc = make_map(&map_w, W, N, K, ldw, TC_BM);
     if (rc != 0) return rc;
-    if (!NORM_IN) {
-        rc = make_map(&map_x, x, M, K, ldx, ntok16);
-        if (rc != 0) return rc;
-    }
-    static bool configured = false;                         // per instantiation
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_decode_kernel<TO, NORM_IN>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)TC_SMEM_BUDGET);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    rc = make_map(&map_x, x, M, K, ldx, ntok16);
+    if (rc != 0) return rc;
+    static unsigned long long configured = 0;               // per instantiation, a bit per device
+    rc = slb_configure(&configured, gemm_tc_decode_kernel<TO>, TC_SMEM_BUDGET);
+    if (rc != 0) return rc;
     const size_t TC_SMEM = 1024 + (size_t)stages_for(ntok16, max_stages) * (A_STAGE_BYTES + b_stage_bytes(ntok16)) +
                            TC_SMEM_TAIL;
     int* status = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&status, tc_status_word);
     if (e != cudaSuccess) return (int)e;
-    rc = slb_launch(gemm_tc_decode_kernel<TO, NORM_IN>, dim3((N + TC_BM - 1) / TC_BM, splits), dim3(TC_THREADS),
-                    TC_SMEM, st, map_w, map_x, out, ldo, workspace, bias, M, N, K, ntok16, max_stages, status, pf,
-                    swiglu, nin);
+    rc = slb_launch(gemm_tc_decode_kernel<TO>, dim3((N + TC_BM - 1) / TC_BM, splits), dim3(TC_THREADS),
+                    TC_SMEM, st, map_w, map_x, out, ldo, workspace, bias, M, N, K, ntok16, max_stages, status,
+                    swiglu, slb_pdl_early);
     if (rc != 0 || splits == 1 || defer_sum) return rc;
     return slb_launch(gemm_tc_reduce_kernel<TO>, dim3((N + 255) / 256, M), dim3(256), 0, st,
                       (const float*)workspace, out, ldo, bias, M, N, splits);
-}
-
-// what a caller may pass as the norm that produces x
-int check_norm_in(const NormIn& nin, int M, int K) {
-    if (nin.resid == nullptr) return 0;
-    if (M > NORM_IN_MAX_TOK) return SLB_ERR_TOO_LARGE;
-    if (nin.sumsq == nullptr || nin.weight == nullptr || nin.tiles < 1 || nin.ld < K || nin.ld % 4 ||
-        !(nin.eps >= 0.f) || ((uintptr_t)nin.resid | (uintptr_t)nin.weight) % 16)
-        return SLB_ERR_BAD_ARG;
-    return 0;
 }
 
 template <typename... KArgs, typename... Args>
@@ -822,25 +625,18 @@ int launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, int cluster_
 
 constexpr int TC_MAX_CLUSTER = 8;       // the portable cluster size
 
-template <int EPI, bool NORM_IN>
+template <int EPI>
 int run_cluster(const bf16* x, int ldx, const bf16* W, int ldw, bf16* out, int ldo, const float* bias,
-                int M, int N, int K, int splits, int max_stages, const RopeEpilogue& rope,
-                const ResidEpilogue& res, const NormIn& nin, cudaStream_t st) {
-    CUtensorMap map_w, map_x = {};
+                int M, int N, int K, int splits, int max_stages, const RopeEpilogue& rope, cudaStream_t st) {
+    CUtensorMap map_w, map_x;
     const int ntok16 = (M + 15) / 16 * 16;
     int rc = make_map(&map_w, W, N, K, ldw, TC_BM);
     if (rc != 0) return rc;
-    if (!NORM_IN) {
-        rc = make_map(&map_x, x, M, K, ldx, ntok16);
-        if (rc != 0) return rc;
-    }
-    static bool configured = false;                         // per instantiation
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_cluster_kernel<EPI, NORM_IN>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BUDGET);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    rc = make_map(&map_x, x, M, K, ldx, ntok16);
+    if (rc != 0) return rc;
+    static unsigned long long configured = 0;               // per instantiation, a bit per device
+    rc = slb_configure(&configured, gemm_tc_cluster_kernel<EPI>, TC_SMEM_BUDGET);
+    if (rc != 0) return rc;
     const int stages = stages_for(ntok16, max_stages);
     // the parked accumulator [ntok16][128] floats lives in the W stages of the ring
     if ((size_t)stages * A_STAGE_BYTES < (size_t)ntok16 * TC_BM * 4) return SLB_ERR_BAD_ARG;
@@ -848,15 +644,14 @@ int run_cluster(const bf16* x, int ldx, const bf16* W, int ldw, bf16* out, int l
     int* status = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&status, tc_status_word);
     if (e != cudaSuccess) return (int)e;
-    return launch_cluster(gemm_tc_cluster_kernel<EPI, NORM_IN>, dim3((N + TC_BM - 1) / TC_BM, splits),
+    return launch_cluster(gemm_tc_cluster_kernel<EPI>, dim3((N + TC_BM - 1) / TC_BM, splits),
                           dim3(TC_THREADS), splits, smem, st, map_w, map_x, out, ldo, bias, M, N, K, ntok16,
-                          max_stages, status, rope, res, nin);
+                          max_stages, status, rope, slb_pdl_early);
 }
 
-// x == nullptr: the x operand is built from the residual stream (NormIn)
 int check_cluster_args(const bf16* x, int ldx, const bf16* W, int ldw, int M, int N, int K, int splits) {
     if (K <= 0 || K % 8 || ldw % 8 || ldw < K || (uintptr_t)W % 16) return SLB_ERR_BAD_ARG;
-    if (x != nullptr && (ldx % 8 || ldx < K || (uintptr_t)x % 16)) return SLB_ERR_BAD_ARG;
+    if (x == nullptr || ldx % 8 || ldx < K || (uintptr_t)x % 16) return SLB_ERR_BAD_ARG;
     if (M > TC_MAX_TOK) return SLB_ERR_TOO_LARGE;
     const int kblocks = (K + TC_BK - 1) / TC_BK;
     if (splits < 1 || splits > kblocks) return SLB_ERR_BAD_ARG;
@@ -877,111 +672,63 @@ int slb_gemm_tc_cluster_bf16(const bf16* x, int ldx, const bf16* W, int ldw, bf1
     if (ldo < N || out == nullptr) return SLB_ERR_BAD_ARG;
     const int rc = check_cluster_args(x, ldx, W, ldw, M, N, K, splits);
     if (rc != 0) return rc;
-    if (x == nullptr) return SLB_ERR_BAD_ARG;
-    return run_cluster<EPI_STORE, false>(x, ldx, W, ldw, out, ldo, bias, M, N, K, splits, max_stages,
-                                         RopeEpilogue{}, ResidEpilogue{}, NormIn{}, st);
-}
-
-// resid[M, N] += x . W^T (+ bias) on the float32 residual stream, and sumsq[tile][tok] = the sum
-// of squares of the updated values of row tile `tile` (ceil(N / 128) tiles) of token tok.
-int slb_gemm_tc_resid_bf16(const bf16* x, int ldx, const bf16* W, int ldw, const float* bias, float* resid,
-                           int ld_resid, float* sumsq, int M, int N, int K, int splits, int max_stages,
-                           cudaStream_t st) {
-    if (M <= 0 || N <= 0) return 0;
-    if (x == nullptr || resid == nullptr || sumsq == nullptr || ld_resid < N) return SLB_ERR_BAD_ARG;
-    const int rc = check_cluster_args(x, ldx, W, ldw, M, N, K, splits);
-    if (rc != 0) return rc;
-    const ResidEpilogue res = {resid, ld_resid, sumsq};
-    return run_cluster<EPI_RESID, false>(x, ldx, W, ldw, nullptr, 0, bias, M, N, K, splits, max_stages,
-                                         RopeEpilogue{}, res, NormIn{}, st);
+    return run_cluster<EPI_STORE>(x, ldx, W, ldw, out, ldo, bias, M, N, K, splits, max_stages, RopeEpilogue{},
+                                  st);
 }
 
 // The q|k|v product of an attention layer with what follows it: W is [(H + 2 Hkv) D, K]
 // (q heads, k heads, v heads), and the kernel adds the bias, rotates q and k by
 // positions[tok] (angles pos * inv_freq[i], float32), writes q to q_out [M, H D] and k, v to
 // the cache slot of the token (block_table[seq_of_token[tok]][pos / page_size]); k_cache ==
-// null writes no cache.  Head sizes 16, 32, 64, 128.
-// With norm_resid != null x is not read: the loader builds it as the RMS norm of the residual
-// stream (NormIn: at most 16 tokens).
+// null writes no cache.  num_pages: pages in the cache (a table entry outside [0, num_pages)
+// is not written and sets the status word).  Head sizes 16, 32, 64, 128.
 int slb_gemm_tc_qkv_rope_bf16(const bf16* x, int ldx, const bf16* W, int ldw, const float* bias,
                               const int* positions, const int* seq_of_token, const int* block_table,
-                              int max_pages, int page_size, const float* inv_freq, int rotary_dim,
-                              bf16* q_out, int ld_q, bf16* k_cache, bf16* v_cache, int M, int H, int Hkv,
-                              int D, int K, int splits, int max_stages, const float* norm_resid,
-                              int norm_ld, const float* norm_sumsq, int norm_tiles, const float* norm_weight,
-                              float norm_eps, cudaStream_t st) {
+                              int max_pages, int page_size, int num_pages, const float* inv_freq,
+                              int rotary_dim, bf16* q_out, int ld_q, bf16* k_cache, bf16* v_cache, int M,
+                              int H, int Hkv, int D, int K, int splits, int max_stages, cudaStream_t st) {
     if (M <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || D < 16 || D > TC_BM || TC_BM % D || page_size <= 0 || max_pages <= 0)
         return SLB_ERR_BAD_ARG;
     if (rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1) || ld_q < H * D) return SLB_ERR_BAD_ARG;
     if (positions == nullptr || seq_of_token == nullptr || block_table == nullptr || q_out == nullptr ||
-        (k_cache == nullptr) != (v_cache == nullptr))
+        (k_cache == nullptr) != (v_cache == nullptr) || (k_cache != nullptr && num_pages <= 0))
         return SLB_ERR_BAD_ARG;
     const int N = (H + 2 * Hkv) * D;
-    const NormIn nin = {norm_resid, norm_ld, norm_sumsq, norm_tiles, norm_weight, norm_eps};
-    const bool normed = norm_resid != nullptr;
-    if (!normed && x == nullptr) return SLB_ERR_BAD_ARG;
-    int rc = check_cluster_args(normed ? nullptr : x, ldx, W, ldw, M, N, K, splits);
+    const int rc = check_cluster_args(x, ldx, W, ldw, M, N, K, splits);
     if (rc != 0) return rc;
-    rc = check_norm_in(nin, M, K);
-    if (rc != 0) return rc;
-    RopeEpilogue rope = {bias, positions, seq_of_token, block_table, max_pages, page_size, inv_freq,
+    int* status = nullptr;
+    if (cudaGetSymbolAddress((void**)&status, tc_status_word) != cudaSuccess) return SLB_ERR_BAD_ARG;
+    RopeEpilogue rope = {bias, positions, seq_of_token, block_table, max_pages, page_size, num_pages, inv_freq,
                          inv_freq != nullptr ? rotary_dim : 0, q_out, ld_q, k_cache, v_cache, H, Hkv, D};
-    if (normed)
-        return run_cluster<EPI_ROPE, true>(x, ldx, W, ldw, nullptr, 0, nullptr, M, N, K, splits, max_stages,
-                                           rope, ResidEpilogue{}, nin, st);
-    return run_cluster<EPI_ROPE, false>(x, ldx, W, ldw, nullptr, 0, nullptr, M, N, K, splits, max_stages, rope,
-                                        ResidEpilogue{}, nin, st);
+    return run_cluster<EPI_ROPE>(x, ldx, W, ldw, nullptr, 0, nullptr, M, N, K, splits, max_stages, rope, st);
 }
 
 // workspace: float32 [splits * M * N] when splits > 1 (may be null otherwise).
 // max_stages: cap on the depth of the shared-memory ring (0: as deep as fits).
 // defer_sum: with splits > 1, leave the partial sums [splits][M][N] in the workspace
 // and launch no reduction (the consumer adds them; `out` and `bias` are unused).
-// next_w (may be null): the weights the following product will read; their first
-// next_bytes are requested into the L2 cache in pieces of next_chunk_bytes (both multiples
-// of 16, the address 16-byte aligned).
+// swiglu: W's rows are gates and ups alternating in runs of 64; out is [M, N / 2] =
+// silu(gate) * up (one K split, no bias).
 int slb_gemm_tc_decode_bf16(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo,
                             const float* bias, float* workspace, int out_f32, int M, int N, int K,
-                            int splits, int max_stages, int defer_sum, const void* next_w,
-                            long long next_bytes, int next_chunk_bytes, int swiglu,
-                            const float* norm_resid, int norm_ld, const float* norm_sumsq, int norm_tiles,
-                            const float* norm_weight, float norm_eps, cudaStream_t st) {
+                            int splits, int max_stages, int defer_sum, int swiglu, cudaStream_t st) {
     if (M <= 0 || N <= 0) return 0;
-    const NormIn nin = {norm_resid, norm_ld, norm_sumsq, norm_tiles, norm_weight, norm_eps};
-    const bool normed = norm_resid != nullptr;               // x is built from the residual stream
     if (K <= 0 || K % 8 || ldw % 8 || ldw < K || (!swiglu && ldo < N)) return SLB_ERR_BAD_ARG;
-    if (!normed && (ldx % 8 || ldx < K || (uintptr_t)x % 16)) return SLB_ERR_BAD_ARG;
-    if ((uintptr_t)W % 16) return SLB_ERR_BAD_ARG;
+    if (x == nullptr || ldx % 8 || ldx < K || (uintptr_t)x % 16 || (uintptr_t)W % 16) return SLB_ERR_BAD_ARG;
     if (M > TC_MAX_TOK) return SLB_ERR_TOO_LARGE;
-    int rc = check_norm_in(nin, M, K);
-    if (rc != 0) return rc;
     const int kblocks = (K + TC_BK - 1) / TC_BK;
     if (splits < 1 || splits > kblocks || splits > 65535) return SLB_ERR_BAD_ARG;
     if (splits > 1 && workspace == nullptr) return SLB_ERR_BAD_ARG;
-    // swiglu: W's rows are gates and ups alternating in runs of 64; out is [M, N / 2]
     if (swiglu && (splits != 1 || N % 128 || bias != nullptr || ldo < N / 2)) return SLB_ERR_BAD_ARG;
     // the ups of a tile wait in the idle ring: [64][tokens + 1] floats
     if (swiglu && (size_t)stages_for((M + 15) / 16 * 16, max_stages) * A_STAGE_BYTES < (size_t)64 * ((M + 15) / 16 * 16 + 1) * 4)
         return SLB_ERR_BAD_ARG;
-    Prefetch pf = {nullptr, 0, 0};
-    if (next_w != nullptr && next_bytes >= 16) {
-        if (next_chunk_bytes < 16 || next_chunk_bytes % 16 || next_bytes % 16 || (uintptr_t)next_w % 16)
-            return SLB_ERR_BAD_ARG;
-        pf = {static_cast<const unsigned char*>(next_w), next_bytes, next_chunk_bytes};
-    }
-    if (normed) {
-        if (out_f32)
-            return run<float, true>(x, ldx, W, ldw, (float*)out, ldo, bias, workspace, M, N, K, splits,
-                                    max_stages, defer_sum, pf, swiglu, nin, st);
-        return run<bf16, true>(x, ldx, W, ldw, (bf16*)out, ldo, bias, workspace, M, N, K, splits, max_stages,
-                               defer_sum, pf, swiglu, nin, st);
-    }
     if (out_f32)
-        return run<float, false>(x, ldx, W, ldw, (float*)out, ldo, bias, workspace, M, N, K, splits,
-                                 max_stages, defer_sum, pf, swiglu, nin, st);
-    return run<bf16, false>(x, ldx, W, ldw, (bf16*)out, ldo, bias, workspace, M, N, K, splits, max_stages,
-                            defer_sum, pf, swiglu, nin, st);
+        return run<float>(x, ldx, W, ldw, (float*)out, ldo, bias, workspace, M, N, K, splits, max_stages,
+                          defer_sum, swiglu, st);
+    return run<bf16>(x, ldx, W, ldw, (bf16*)out, ldo, bias, workspace, M, N, K, splits, max_stages, defer_sum,
+                     swiglu, st);
 }
 
 // out[M, N] = sum of float32 partial sums [splits][M][N] (+ bias), in order.
@@ -996,8 +743,9 @@ int slb_split_sum(const float* parts, void* out, int ldo, const float* bias, int
                       (bf16*)out, ldo, bias, M, N, splits);
 }
 
-// 0 while no wait has timed out; else (role << 8 | code) of the first one.
-// Reading synchronises with the device.
+// 0 while no wait has timed out and no page index was out of range; else (role << 8 | code)
+// of the first event (role 5: a block-table entry outside the cache).  Reading synchronises
+// with the device.
 int slb_gemm_tc_status(int reset) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, tc_status_word, sizeof(int)) != cudaSuccess) return -1;

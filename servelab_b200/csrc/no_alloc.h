@@ -12,7 +12,9 @@
 // variant brings its own: a fixed array that is part of the library image.
 //
 // Contract
-//   * Inputs and outputs are passed exactly as for slb_decode_attention_bf16,
+//   * Inputs and outputs are passed exactly as for slb_decode_attention_bf16
+//     (num_pages is the number of pages in k_cache / v_cache; a block-table entry
+//     outside [0, num_pages) is read as zeros and reported by slb_attention_status),
 //     minus the scratch pointer.  Nothing is allocated or freed: no cudaMalloc,
 //     no cudaFree, no library routine that allocates.
 //   * The scratch is a file-scope device array of
@@ -26,8 +28,12 @@
 //     capture begins.
 //   * All calls share the one array and it keeps what the last call left.  Nothing
 //     in it has to start at zero: every slot the combine step reads is written by
-//     the split kernel of the same call.  Two calls that overlap on the GPU (other
-//     streams, other threads) race on the array; run them one after the other.
+//     the split kernel of the same call.  That also holds for a block that gives up
+//     one of its bounded waits: it marks its slots as empty, so the combine step never
+//     merges an earlier call's leftovers; the result of that head then lacks those
+//     keys, and slb_attention_status() is non-zero -- check it where a wrong result
+//     must not pass silently.  Two calls that overlap on the GPU (other streams, other
+//     threads) race on the array; run them one after the other.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -40,8 +46,8 @@ extern "C" {
 int slb_decode_attention_bf16_noalloc(const __nv_bfloat16* q, int ldq, const __nv_bfloat16* k_cache,
                                       const __nv_bfloat16* v_cache, __nv_bfloat16* out, int ldo,
                                       const int* block_table, int max_pages, const int* ctx_len,
-                                      int S, int H, int Hkv, int page_size, float scale, int window,
-                                      int num_splits, cudaStream_t stream);
+                                      int S, int H, int Hkv, int page_size, int num_pages, float scale,
+                                      int window, int num_splits, cudaStream_t stream);
 
 long long slb_decode_attention_noalloc_capacity_bytes(void);
 

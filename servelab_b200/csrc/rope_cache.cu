@@ -13,6 +13,19 @@
 // manager.py:309-313).  Page layout here: [page][kv head][slot in page][D].
 #include "common.cuh"
 
+// 0, or 1 once a block-table entry pointed outside the cache (page >= num_pages): that key
+// and value were not written.  A table can only be wrong through a fault of the host side;
+// the kernels skip the access and say so instead of writing outside the pool.
+SLB_DEFINE_STATUS_WORD(cache_write_status_word, slb_cache_write_status)
+
+__device__ __forceinline__ bool page_in_cache(int page, int num_pages) {
+    if (page >= num_pages) {
+        atomicCAS(&cache_write_status_word, 0, 1);
+        return false;
+    }
+    return page >= 0;
+}
+
 // One block per token.  A head is D/2 "slots" of two elements: slot i < rot/2 is the
 // rotation pair (i, i + rot/2); the slots after that are pairs of neighbouring
 // elements beyond the rotary part, which pass through.  Thread (i, lane-of-heads)
@@ -21,7 +34,7 @@ template <typename T>
 __global__ void qkv_rope_cache_kernel(
     const T* __restrict__ qkv, int ld_qkv, const float* __restrict__ bias,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-    const int* __restrict__ block_table, int max_pages, int page_size,
+    const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
     const float* __restrict__ inv_freq, int rotary_dim,
     T* __restrict__ q_out, int ld_q, T* __restrict__ k_cache, T* __restrict__ v_cache,
     int H, int Hkv, int D, int slots_per_head) {
@@ -46,7 +59,7 @@ __global__ void qkv_rope_cache_kernel(
     bool have_page = false;
     if (write) {
         const int page = block_table[(size_t)seq_of_token[t] * max_pages + pos / page_size];
-        have_page = page >= 0;                         // no page: nothing may be written
+        have_page = page_in_cache(page, num_pages);    // no page: nothing may be written
         kv_base = ((size_t)(have_page ? page : 0) * Hkv * page_size + pos % page_size) * D;
     }
     const T* x = qkv + (size_t)t * ld_qkv;
@@ -84,7 +97,7 @@ __global__ void qkv_rope_cache_parts_kernel(
     const float* __restrict__ parts, int nparts, size_t part_stride, int ld_qkv,
     const float* __restrict__ bias, const int* __restrict__ positions,
     const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int max_pages,
-    int page_size, const float* __restrict__ inv_freq, int rotary_dim,
+    int page_size, int num_pages, const float* __restrict__ inv_freq, int rotary_dim,
     T* __restrict__ q_out, int ld_q, T* __restrict__ k_cache, T* __restrict__ v_cache,
     int H, int Hkv, int D) {
     pdl_launch_dependents();
@@ -118,7 +131,7 @@ __global__ void qkv_rope_cache_parts_kernel(
         dst = q_out + (size_t)t * ld_q + off;
     } else {
         const int page = block_table[(size_t)seq_of_token[t] * max_pages + pos / page_size];
-        if (page < 0) return;                          // no page: nothing may be written
+        if (!page_in_cache(page, num_pages)) return;   // no page: nothing may be written
         const int kvh = is_v ? j - H - Hkv : j - H;
         dst = (is_v ? v_cache : k_cache) +
               (((size_t)page * Hkv + kvh) * page_size + pos % page_size) * D;
@@ -137,7 +150,7 @@ template <typename T>
 __global__ void qkv_rope_cache_vec_kernel(
     const T* __restrict__ qkv, int ld_qkv, const float* __restrict__ bias,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-    const int* __restrict__ block_table, int max_pages, int page_size,
+    const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
     const float* __restrict__ inv_freq, int rotary_dim,
     T* __restrict__ q_out, int ld_q, T* __restrict__ k_cache, T* __restrict__ v_cache,
     int H, int Hkv, int D) {
@@ -168,7 +181,7 @@ __global__ void qkv_rope_cache_vec_kernel(
     bool have_page = false;
     if (write) {
         const int page = block_table[(size_t)seq_of_token[t] * max_pages + pos / page_size];
-        have_page = page >= 0;                         // no page: nothing may be written
+        have_page = page_in_cache(page, num_pages);    // no page: nothing may be written
         kv_base = ((size_t)(have_page ? page : 0) * Hkv * page_size + pos % page_size) * D;
     }
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -236,12 +249,13 @@ template <typename T>
 static int launch_qkv_rope_cache(const T* qkv, int ld_qkv, const float* parts, int nparts,
                                  long long part_stride, const float* bias, const int* positions,
                                  const int* seq_of_token, const int* block_table, int max_pages,
-                                 int page_size, const float* inv_freq, int rotary_dim, T* q_out,
+                                 int page_size, int num_pages, const float* inv_freq, int rotary_dim, T* q_out,
                                  int ld_q, T* k_cache, T* v_cache, int T_, int H, int Hkv, int D,
                                  cudaStream_t st) {
     if (T_ <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || D <= 0 || (D & 1) || page_size <= 0 || max_pages <= 0)
         return SLB_ERR_BAD_ARG;
+    if (k_cache != nullptr && num_pages <= 0) return SLB_ERR_BAD_ARG;
     if (rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1)) return SLB_ERR_BAD_ARG;
     if (D > 1024) return SLB_ERR_TOO_LARGE;
     int slots = 1;
@@ -266,7 +280,7 @@ static int launch_qkv_rope_cache(const T* qkv, int ld_qkv, const float* parts, i
         int vthreads = ((units + passes - 1) / passes + 31) / 32 * 32;
         if (vthreads < rot / 2) vthreads = ((rot / 2 + 31) / 32 * 32 < 1024) ? (rot / 2 + 31) / 32 * 32 : 1024;
         return slb_launch(qkv_rope_cache_vec_kernel<T>, dim3(T_), dim3(vthreads), (size_t)rot * sizeof(float), st,
-                          qkv, ld_qkv, bias, positions, seq_of_token, block_table, max_pages, page_size,
+                          qkv, ld_qkv, bias, positions, seq_of_token, block_table, max_pages, page_size, num_pages,
                           inv_freq, rotary_dim, q_out, ld_q, k_cache, v_cache, H, Hkv, D);
     }
     if (nparts > 0) {
@@ -274,42 +288,42 @@ static int launch_qkv_rope_cache(const T* qkv, int ld_qkv, const float* parts, i
         const bool write = k_cache != nullptr && v_cache != nullptr;
         return slb_launch(qkv_rope_cache_parts_kernel<T>, dim3(write ? heads : H, T_),
                           dim3((D / 2 + 31) / 32 * 32), 0, st, parts, nparts, (size_t)part_stride,
-                          ld_qkv, bias, positions, seq_of_token, block_table, max_pages, page_size,
+                          ld_qkv, bias, positions, seq_of_token, block_table, max_pages, page_size, num_pages,
                           inv_freq, rotary_dim, q_out, ld_q, k_cache, v_cache, H, Hkv, D);
     }
     return slb_launch(qkv_rope_cache_kernel<T>, dim3(T_), dim3(threads), 0, st, qkv, ld_qkv, bias,
-                      positions, seq_of_token, block_table, max_pages, page_size, inv_freq, rotary_dim,
+                      positions, seq_of_token, block_table, max_pages, page_size, num_pages, inv_freq, rotary_dim,
                       q_out, ld_q, k_cache, v_cache, H, Hkv, D, slots);
 }
 
 extern "C" {
 int slb_qkv_rope_cache_f32(const float* qkv, int ld_qkv, const float* bias, const int* positions,
                            const int* seq_of_token, const int* block_table, int max_pages,
-                           int page_size, const float* inv_freq, int rotary_dim, float* q_out,
+                           int page_size, int num_pages, const float* inv_freq, int rotary_dim, float* q_out,
                            int ld_q, float* k_cache, float* v_cache, int T, int H, int Hkv, int D,
                            cudaStream_t st) {
     return launch_qkv_rope_cache<float>(qkv, ld_qkv, nullptr, 0, 0, bias, positions, seq_of_token, block_table,
-                                        max_pages, page_size, inv_freq, rotary_dim, q_out, ld_q,
+                                        max_pages, page_size, num_pages, inv_freq, rotary_dim, q_out, ld_q,
                                         k_cache, v_cache, T, H, Hkv, D, st);
 }
 int slb_qkv_rope_cache_bf16(const bf16* qkv, int ld_qkv, const float* bias, const int* positions,
                             const int* seq_of_token, const int* block_table, int max_pages,
-                            int page_size, const float* inv_freq, int rotary_dim, bf16* q_out,
+                            int page_size, int num_pages, const float* inv_freq, int rotary_dim, bf16* q_out,
                             int ld_q, bf16* k_cache, bf16* v_cache, int T, int H, int Hkv, int D,
                             cudaStream_t st) {
     return launch_qkv_rope_cache<bf16>(qkv, ld_qkv, nullptr, 0, 0, bias, positions, seq_of_token, block_table,
-                                       max_pages, page_size, inv_freq, rotary_dim, q_out, ld_q,
+                                       max_pages, page_size, num_pages, inv_freq, rotary_dim, q_out, ld_q,
                                        k_cache, v_cache, T, H, Hkv, D, st);
 }
 // the fused q|k|v projection arrives as float32 partial sums [nparts][T][ld_qkv]
 int slb_qkv_rope_cache_parts_bf16(const float* parts, int nparts, long long part_stride, int ld_qkv,
                                   const float* bias, const int* positions, const int* seq_of_token,
-                                  const int* block_table, int max_pages, int page_size,
+                                  const int* block_table, int max_pages, int page_size, int num_pages,
                                   const float* inv_freq, int rotary_dim, bf16* q_out, int ld_q,
                                   bf16* k_cache, bf16* v_cache, int T, int H, int Hkv, int D,
                                   cudaStream_t st) {
     return launch_qkv_rope_cache<bf16>(nullptr, ld_qkv, parts, nparts, part_stride, bias, positions,
-                                       seq_of_token, block_table, max_pages, page_size, inv_freq,
+                                       seq_of_token, block_table, max_pages, page_size, num_pages, inv_freq,
                                        rotary_dim, q_out, ld_q, k_cache, v_cache, T, H, Hkv, D, st);
 }
 }

@@ -77,6 +77,9 @@ class LLMEngine:
         self.lookahead = lookahead
         self._ahead = None                 # (requests, their tokens on the way) of a step launched ahead
         self.num_lookahead_steps = 0
+        # measurements: a list that receives, per step, (tokens run, cached keys read = the sum
+        # of the requests' context lengths, query-key pairs scored, rows of logits)
+        self.step_trace: Optional[list] = None
 
     # -------------------------------------------------------------- intake
     def add_request(self, prompt: Optional[str] = None,
@@ -132,6 +135,12 @@ class LLMEngine:
         self._launch_ahead(plan, logit_seqs, rows, pending)
         tokens = pending.wait()
         sampled: Dict[str, int] = {s.request_id: tokens[r] for s, r in zip(logit_seqs, rows)}
+        if self.step_trace is not None:
+            self.step_trace.append((
+                sum(p.num_tokens for p in plan.portions),
+                sum(p.start + p.num_tokens for p in plan.portions),
+                sum(p.num_tokens * p.start + p.num_tokens * (p.num_tokens + 1) // 2 for p in plan.portions),
+                len(logit_seqs)))
         finished = self.scheduler.update_after_exec(plan, sampled, now=self.clock())
         self.num_steps += 1
         return outputs + [RequestOutput.from_sequence(s, self._detokenize) for s in finished]

@@ -58,9 +58,12 @@ class ModelRunner:
                                           cache_config.gpu_memory_utilization)
         self.num_pages = num_pages
         self.storage = CacheStorage(requests, num_pages, self.page_size, max_num_seqs, self.dtype,
-                                    device)
+                                    device, poison=cache_config.poison_cache)
         self.cache = CacheManager(self.storage.group_windows, num_pages, self.page_size,
                                   max_num_seqs, reserve_pages=cache_config.reserve_blocks)
+        if cache_config.poison_cache:
+            for g, pool in enumerate(self.cache.pools):
+                pool.on_free = (lambda pages, g=g: self.storage.poison_pages(g, pages))
         self.num_groups = len(self.storage.groups)
         self.max_model_len = min(max_model_len or self.spec.max_position_embeddings,
                                  self.spec.max_position_embeddings, num_pages * self.page_size)

@@ -5,7 +5,9 @@ LM head -- built from a ``ModelSpec`` and the part registries.
 building anything), ``CausalLM.load`` fills the parts from a checked source, and
 ``forward`` runs the tokens of one step and returns float32 logits at the wanted
 rows.  Order of operations: servelab/parallel/tp_model.py:121-134 (embed, layers,
-final norm) and :112-119 (LM head; tied weights reuse the embedding table); rows
+final norm) and :112-119 (LM head; tied weights reuse the embedding table); the
+optional embedding scale and logit scale / soft cap of the spec are applied where
+architectures that have them apply them (Qwen2 has none); rows
 are selected before the final norm here, which gives the same result because the
 norm acts per row (the reference norms all rows first, servelab/engine/
 engine.py:217-218).
@@ -19,7 +21,7 @@ import torch
 
 from ..config.specs import ModelSpec
 from ..ops import kernels as K
-from ..ops.linear import linear, set_weight_order
+from ..ops.linear import linear
 from ..parts import BLOCKS, NORMS, POSITIONS, BuildEnv, LayerCache, build_part, part_class
 from ..weights.source import MATRIX, TensorDecl, WeightSource
 from ..weights.store import WeightStore
@@ -75,11 +77,6 @@ class CausalLM:
         self.final_norm.load(store)
         self.lm_head = (self.embed_tokens if self.spec.tie_word_embeddings
                         else store.get(self.spec.lm_head_name))
-        # the order in which a step multiplies by the weights (a cache hint for the products)
-        order = []
-        for run in self.spec.run_order:
-            order += self.blocks[run.layer].matrices()
-        set_weight_order(order + [self.lm_head])
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
@@ -101,29 +98,29 @@ class CausalLM:
                 total += t.numel() * t.element_size()
         return total
 
-    @staticmethod
-    def _plain_unless(part, delta):
-        """An update may travel unfinished (``SplitSum``: partial sums of a K-split product;
-        ``DeferredLinear``: a product that has not run); parts that do not say they accept
-        the form get the plain tensor."""
-        return K.plain_unless(part, delta)
-
     # ----------------------------------------------------------- forward
     def forward(self, ctx, caches: Dict[int, LayerCache]) -> torch.Tensor:
         """Run the step's tokens; ``caches`` maps a run's index to its cache.
         Returns logits [wanted rows, vocab] float32."""
         T = ctx.num_tokens
         resid = torch.empty((T, self.spec.hidden_size), dtype=torch.float32, device=self.env.device)
-        K.embedding(ctx.token_ids, self.embed_tokens, resid)
+        K.embedding(ctx.token_ids, self.embed_tokens, resid,
+                    1.0 if self.spec.embedding_scale is None else self.spec.embedding_scale)
         self.embedding_position.apply_to_embedding(ctx, resid)
         delta = None
         for i, run in enumerate(self.spec.run_order):
             owner = i if run.cache_of is None else run.cache_of
             block = self.blocks[run.layer]
-            resid, delta = block.forward(ctx, resid, self._plain_unless(block, delta), caches[owner],
+            # (an update may travel as the partial sums of a K-split product; a block that
+            # does not say it accepts that form gets the plain tensor)
+            resid, delta = block.forward(ctx, resid, K.plain_unless(block, delta), caches[owner],
                                          run.cache_of is None)
         if ctx.num_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.env.device)
-        x = self.final_norm.forward(ctx, resid, self._plain_unless(self.final_norm, delta),
+        x = self.final_norm.forward(ctx, resid, K.plain_unless(self.final_norm, delta),
                                     out_rows=ctx.logit_rows)
-        return linear(x, self.lm_head, out_dtype=torch.float32)
+        logits = linear(x, self.lm_head, out_dtype=torch.float32)
+        if self.spec.logit_scale is not None or self.spec.logit_softcap is not None:
+            K.logit_transform(logits, 1.0 if self.spec.logit_scale is None else self.spec.logit_scale,
+                              self.spec.logit_softcap or 0.0)
+        return logits

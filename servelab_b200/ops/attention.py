@@ -20,26 +20,12 @@ from . import library as L
 force_generic = False
 use_decode_kernel = True
 use_prefill_kernel = True
-# Steps of single tokens: the decode kernel can take the q|k|v product itself (bias, rotation
-# and the cache write happen inside it), so that the q/k/v kernel does not run.  Off: every
-# block then adds the partial sums of its own query rows behind its wait for the product, a
-# chain of loads that costs more than the kernel it saves, which runs while the attention
-# blocks already fetch their first tiles (7B shape, ms a step with / without at batch 1, 8,
-# 64: 3.07 / 3.01, 3.18 / 3.17, 4.62 / 4.59).
-fuse_decode_qkv = False
-
 MAX_HEAD_DIM = 256
 
 
 def check_supported(head_dim: int, dtype: torch.dtype) -> None:
     if head_dim < 1 or head_dim > MAX_HEAD_DIM:
         raise L.KernelError(f"attention kernels take head sizes 1..{MAX_HEAD_DIM}, got {head_dim}")
-
-
-def fused_decode_applies(ctx, dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
-    """Whether this step's attention can start from the q|k|v product."""
-    return (fuse_decode_qkv and use_decode_kernel and not force_generic and ctx.decode_only
-            and dtype == torch.bfloat16 and K.decode_attention_takes(head_dim, page_size))
 
 
 def _generic(ctx, q, k_cache, v_cache, out, table, H, Hkv, D, page_size, scale, window):

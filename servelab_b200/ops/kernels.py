@@ -26,6 +26,8 @@ class SplitSum:
     to be added).  Kernels that consume it add the parts in order, so no separate
     reduction is launched; ``materialize()`` produces the plain tensor."""
 
+    accept_flag = "accepts_split_sum"
+
     def __init__(self, parts: torch.Tensor, bias: Optional[torch.Tensor], dtype: torch.dtype):
         self.parts, self.bias, self.dtype = parts, bias, dtype
 
@@ -42,57 +44,9 @@ class SplitSum:
         return out
 
 
-class DeferredLinear:
-    """A product x . w^T (+ bias) [M, N] that has not run yet and whose result is an update
-    of the float32 residual stream.  The norm that receives it runs it as ONE kernel that
-    adds the result into the stream and leaves the sums of squares the norm needs
-    (``gemm_tc_resid``).  ``materialize()`` runs the plain product."""
-    accept_flag = "accepts_deferred_linear"
-
-    def __init__(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]):
-        self.x, self.w, self.bias, self.dtype = x, w, bias, x.dtype
-
-    @property
-    def shape(self):
-        return (self.x.shape[0], self.w.shape[0])
-
-    def materialize(self) -> torch.Tensor:
-        return gemm_tc_cluster(self.x, self.w, None, self.bias)
-
-
-class LazyNorm:
-    """rmsnorm(resid) * weight [M, h] that has not been computed: ``resid`` (float32, every
-    update added) and ``sumsq`` [tiles, M], the sums of squares of its rows per 128-column
-    tile.  The tcgen05 products build their input from it while they load
-    (``gemm_tc_qkv_rope``, ``gemm_tc_decode``); ``materialize()`` runs the norm kernel."""
-    accept_flag = "accepts_lazy_norm"
-
-    def __init__(self, resid: torch.Tensor, sumsq: torch.Tensor, weight: torch.Tensor, eps: float,
-                 dtype: torch.dtype):
-        self.resid, self.sumsq, self.weight, self.eps, self.dtype = resid, sumsq, weight, eps, dtype
-        self.device = resid.device
-
-    @property
-    def shape(self):
-        return self.resid.shape
-
-    def materialize(self) -> torch.Tensor:
-        out = torch.empty(self.resid.shape, dtype=self.dtype, device=self.resid.device)
-        add_rmsnorm(self.resid, None, self.weight, self.eps, out)
-        return out
-
-    def args(self):
-        return (self.resid.data_ptr(), self.resid.stride(0), self.sumsq.data_ptr(), self.sumsq.shape[0],
-                self.weight.data_ptr(), float(self.eps))
-
-
-_NO_NORM = (None, 0, None, 0, None, 0.0)
-SplitSum.accept_flag = "accepts_split_sum"
-
-
 def plain_unless(part, value):
-    """``value`` as a tensor unless it is one of the unfinished forms above and ``part``
-    says (by the form's flag) that it takes them."""
+    """``value`` as a tensor unless it is an unfinished form (``SplitSum``) and ``part``
+    says (by the form's flag) that it takes it."""
     flag = getattr(type(value), "accept_flag", None)
     if flag is not None and not getattr(part, flag, False):
         return value.materialize()
@@ -132,11 +86,21 @@ def require_cuda() -> None:
 
 
 # ------------------------------------------------------------- elementwise
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = table[ids[t]] as float32; ids int32 [T], out float32 [T, h]."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] * scale as float32; ids int32 [T], out float32 [T, h]."""
     fn = getattr(L.core(), "slb_embedding_" + _suffix(table.dtype))
     L.check(fn(ids.data_ptr(), table.data_ptr(), out.data_ptr(), ids.numel(), table.shape[1],
-               table.shape[0], _stream()), "embedding")
+               table.shape[0], float(scale), _stream()), "embedding")
+
+
+def logit_transform(logits: torch.Tensor, scale: float = 1.0, softcap: float = 0.0) -> None:
+    """In place on float32 logits [R, V]: times ``scale``, then with ``softcap`` > 0 bounded to
+    softcap * tanh(x / softcap)."""
+    if logits.dtype != _F32:
+        raise L.KernelError("logit_transform: float32 logits only")
+    L.check(L.core().slb_logit_transform(logits.data_ptr(), logits.stride(0), logits.shape[0],
+                                         logits.shape[1], float(scale), float(softcap), _stream()),
+            "logit_transform")
 
 
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
@@ -169,6 +133,22 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
 
 
 # ----------------------------------------------------- rotary + cache write
+def _num_pages(cache: Optional[torch.Tensor]) -> int:
+    """Pages in a layer's cache [pages, kv heads, page size, head size]: the kernels skip a
+    block-table entry beyond it (and set a status word) instead of touching memory outside."""
+    return 0 if cache is None else cache.shape[0]
+
+
+def cache_write_status(reset: bool = False) -> int:
+    """0 unless the q/k/v kernel met a block-table entry outside the cache (synchronises)."""
+    return L.core().slb_cache_write_status(1 if reset else 0)
+
+
+def generic_attention_status(reset: bool = False) -> int:
+    """0 unless the plain attention kernel met a block-table entry outside the cache."""
+    return L.core().slb_paged_attention_generic_status(1 if reset else 0)
+
+
 def qkv_rope_cache(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
                    seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int,
                    inv_freq: Optional[torch.Tensor], rotary_dim: int, q_out: torch.Tensor,
@@ -184,14 +164,14 @@ def qkv_rope_cache(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: t
             L.check(L.core().slb_qkv_rope_cache_parts_bf16(
                 qkv.parts.data_ptr(), S, M * N, N, _p(bias if bias is not None else qkv.bias),
                 positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
-                block_table.shape[1], page_size, _p(inv_freq), rotary_dim, q_out.data_ptr(),
-                q_out.stride(0), _p(k_cache), _p(v_cache), M, num_heads, num_kv_heads, head_dim,
-                _stream()), "qkv_rope_cache")
+                block_table.shape[1], page_size, _num_pages(k_cache), _p(inv_freq), rotary_dim,
+                q_out.data_ptr(), q_out.stride(0), _p(k_cache), _p(v_cache), M, num_heads,
+                num_kv_heads, head_dim, _stream()), "qkv_rope_cache")
             return
     fn = getattr(L.core(), "slb_qkv_rope_cache_" + _suffix(qkv.dtype))
     L.check(fn(qkv.data_ptr(), qkv.stride(0), _p(bias), positions.data_ptr(),
                seq_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size,
-               _p(inv_freq), rotary_dim, q_out.data_ptr(), q_out.stride(0), _p(k_cache),
+               _num_pages(k_cache), _p(inv_freq), rotary_dim, q_out.data_ptr(), q_out.stride(0), _p(k_cache),
                _p(v_cache), qkv.shape[0], num_heads, num_kv_heads, head_dim, _stream()),
             "qkv_rope_cache")
 
@@ -208,8 +188,8 @@ def paged_attention_generic(q, k_cache, v_cache, out, block_table, cu_q, ctx_len
     L.check(fn(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
                out.stride(0), block_table.data_ptr(), block_table.shape[1], cu_q.data_ptr(),
                ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), num_tiles,
-               num_heads, num_kv_heads, head_dim, page_size, float(scale), int(window),
-               _stream()), "paged_attention_generic")
+               num_heads, num_kv_heads, head_dim, page_size, k_cache.shape[0], float(scale),
+               int(window), _stream()), "paged_attention_generic")
 
 
 # ---------------------------------------------------------- matrix products
@@ -306,7 +286,8 @@ def prefill_attention(ctx, q, k_cache, v_cache, out, block_table, num_heads, num
         q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
         out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.cu_q.data_ptr(),
         ctx.ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), n, num_heads,
-        num_kv_heads, page_size, float(scale), int(window), _stream()), "prefill_attention")
+        num_kv_heads, page_size, k_cache.shape[0], float(scale), int(window), _stream()),
+        "prefill_attention")
 
 
 def decode_splits(num_seqs: int, num_kv_heads: int, group: int, longest_context: int,
@@ -335,8 +316,8 @@ def decode_attention_split(ctx, q, k_cache, v_cache, out, block_table, num_heads
     L.check(lib.slb_decode_attention_bf16(
         q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
         out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.ctx_len.data_ptr(),
-        _p(scratch), S, num_heads, num_kv_heads, page_size, float(scale), int(window), splits,
-        _stream()), "decode_attention")
+        _p(scratch), S, num_heads, num_kv_heads, page_size, k_cache.shape[0], float(scale),
+        int(window), splits, _stream()), "decode_attention")
     global launch_count
     launch_count += 1 if splits > 1 else 0          # the combine kernel
 
@@ -405,39 +386,6 @@ def _decode_launch_shape(ctx, lib, q_device, num_heads, num_kv_heads):
     return splits, scratch, counters
 
 
-def decode_attention_fused(ctx, qkv, bias, inv_freq, rotary_dim, k_cache, v_cache, write_kv: bool,
-                           out, block_table, num_heads, num_kv_heads, head_dim, page_size, scale,
-                           window) -> None:
-    """A step of single tokens from the q|k|v product itself: ``qkv`` is the
-    product's bfloat16 result [S, (H + 2 Hkv) D] or its K-split partial sums
-    (``SplitSum``).  The attention kernel adds the bias, rotates q and k by the
-    request's position (its context length minus one), writes the new key and value
-    to the cache (``write_kv``) and attends, in one launch; the q/k/v kernel does not
-    run.  Only where ``decode_attention_takes(head_dim, page_size)``."""
-    lib = L.attention(head_dim)
-    parts = dense = None
-    nparts = part_stride = 0
-    if isinstance(qkv, SplitSum):
-        if bias is not None and qkv.bias is not None:
-            raise L.KernelError("decode_attention_fused: two biases")
-        bias = bias if bias is not None else qkv.bias
-        nparts, M, N = qkv.parts.shape
-        parts, part_stride, ld = qkv.parts, M * N, N
-    else:
-        if qkv.dtype != _BF16:
-            raise L.KernelError("decode_attention_fused: bfloat16 only")
-        dense, ld = qkv, qkv.stride(0)
-    splits, scratch, counters = _decode_launch_shape(ctx, lib, out.device, num_heads, num_kv_heads)
-    L.check(lib.slb_decode_attention_ws_fused_bf16(
-        _p(parts), int(nparts), int(part_stride), _p(dense), int(ld), _p(bias), _p(inv_freq),
-        int(rotary_dim), 1 if write_kv else 0, k_cache.data_ptr(), v_cache.data_ptr(),
-        out.data_ptr(), out.stride(0), block_table.data_ptr(), block_table.shape[1],
-        ctx.ctx_len.data_ptr(), _p(scratch), _p(counters), ctx.num_seqs, num_heads, num_kv_heads,
-        page_size, k_cache.shape[0], float(scale), int(window), splits, int(decode_ws_stages),
-        float(decode_ws_split_coef), int(decode_ws_unsplit_tiles), _stream()),
-        "decode_attention_fused")
-
-
 def decode_attention(ctx, q, k_cache, v_cache, out, block_table, num_heads, num_kv_heads,
                      head_dim, page_size, scale, window) -> None:
     """Attention for a step of single tokens (every q_len == 1): one launch; the
@@ -460,19 +408,15 @@ def decode_attention(ctx, q, k_cache, v_cache, out, block_table, num_heads, num_
 
 
 def decode_attention_status(head_dim: int, reset: bool = False) -> int:
-    """0 unless a bounded wait inside the decode attention kernel gave up."""
+    """0 unless a bounded wait inside the decode attention kernel gave up (or a block-table
+    entry pointed outside the cache: 0x40)."""
     return L.attention(head_dim).slb_decode_attention_ws_status(1 if reset else 0)
 
 
-def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
-                bias: Optional[torch.Tensor] = None, rows_per_block_hint: int = 0) -> None:
-    """out[M,N] = x[M,K] . w[N,K]^T (+ bias) for up to 64 tokens, streaming w once;
-    bfloat16 operands, float32 or bfloat16 output."""
-    M, Kd = x.shape
-    L.check(L.core().slb_gemm_skinny_bf16(
-        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
-        _p(bias), 1 if out.dtype == _F32 else 0, M, w.shape[0], Kd, rows_per_block_hint,
-        _stream()), "gemm_skinny")
+def decode_attention_splits_used(head_dim: int, reset: bool = False) -> int:
+    """The most splits any request has used in a launch of the one-launch decode kernel
+    since the last reset; 0 if every request ran unsplit (synchronises)."""
+    return L.attention(head_dim).slb_decode_attention_ws_splits_used(1 if reset else 0)
 
 
 # ------------------------------------ tcgen05 weight-streaming product (decode)
@@ -497,27 +441,6 @@ def tc_decode_splits(n_out: int, k: int) -> int:
     return max(1, min(want, kblocks // 4 if kblocks >= 8 else 1))
 
 
-tc_prefetch_bytes = 0          # of the weights of the product that follows, this much is
-                               # requested into the L2 cache by each tcgen05 product.  Off:
-                               # measured at batch 8 on the 7B shape, 4 to 32 MB a product made the
-                               # step 0.5 to 3 % slower (3.48 -> 3.50 .. 3.57 ms), whether as one
-                               # piece per row and K split or as leading 32 KB pieces.
-
-
-tc_prefetch_chunk = 32 << 10   # bytes per request
-
-
-def _next_weight_args(next_weight: Optional[torch.Tensor]):
-    """What the tcgen05 product asks for on behalf of its successor: the leading
-    bytes of the successor's weights (contiguous matrices only)."""
-    if next_weight is None or tc_prefetch_bytes <= 0 or not next_weight.is_contiguous():
-        return None, 0, 0
-    nbytes = min(tc_prefetch_bytes, next_weight.numel() * next_weight.element_size()) // 16 * 16
-    if nbytes < 16 or next_weight.data_ptr() % 16:
-        return None, 0, 0
-    return next_weight.data_ptr(), nbytes, tc_prefetch_chunk
-
-
 # rows of gates, then as many of ups, and so on: the layout for which the tcgen05 product
 # applies the activation in its epilogue (half of its 128-row tile)
 SWIGLU_BLOCK = 64
@@ -526,13 +449,11 @@ SWIGLU_BLOCK = 64
 def gemm_tc_decode(x, w: torch.Tensor, out: Optional[torch.Tensor],
                    bias: Optional[torch.Tensor] = None, splits: int = 0,
                    defer_sum: bool = False, out_dtype: Optional[torch.dtype] = None,
-                   next_weight: Optional[torch.Tensor] = None, swiglu: bool = False):
+                   swiglu: bool = False):
     """out[M,N] = x[M,K] . w[N,K]^T (+ bias) for up to 64 tokens on tcgen05 tensor
     cores with TMA-streamed weights; bfloat16 operands, float32 or bfloat16 output.
     With ``defer_sum`` and more than one K split the partial sums are returned as a
     ``SplitSum`` (no reduction is launched); otherwise ``out`` (allocated if None).
-    ``next_weight``: the weights of the product that will follow; their leading part is
-    requested into the L2 cache while this kernel drains.
     ``swiglu``: ``w`` holds gate and up rows alternating in runs of ``SWIGLU_BLOCK``; the
     result is silu(gate) * up, [M, N / 2] (one K split, no bias)."""
     global launch_count
@@ -550,14 +471,11 @@ def gemm_tc_decode(x, w: torch.Tensor, out: Optional[torch.Tensor],
     deferred = defer_sum and splits > 1
     if out is None and not deferred:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    lazy = isinstance(x, LazyNorm)                          # the loader builds x from the stream
     L.check(L.core().slb_gemm_tc_decode_bf16(
-        None if lazy else x.data_ptr(), 0 if lazy else x.stride(0), w.data_ptr(), w.stride(0), _p(out),
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _p(out),
         out.stride(0) if out is not None else N,
         _p(bias), _p(ws), 1 if out_dtype == _F32 else 0, M, N, Kd, splits, tc_max_stages,
-        1 if deferred else 0, *_next_weight_args(next_weight), 1 if swiglu else 0,
-        *(x.args() if lazy else _NO_NORM), _stream()),
-        "gemm_tc_decode")
+        1 if deferred else 0, 1 if swiglu else 0, _stream()), "gemm_tc_decode")
     if deferred:
         return SplitSum(ws, bias, out_dtype)
     launch_count += 1 if splits > 1 else 0
@@ -589,25 +507,7 @@ def gemm_tc_cluster(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor
     return out
 
 
-LAZY_NORM_MAX_TOKENS = 16      # tokens up to which a product builds its input from a LazyNorm
-
-
-def gemm_tc_resid(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
-                  resid: torch.Tensor, splits: int = 0) -> torch.Tensor:
-    """resid += x . w^T (+ bias) on the float32 residual stream [M, N], in one kernel (the K
-    splits as a cluster); returns sumsq [ceil(N / 128), M]: the sums of squares of the updated
-    rows per 128-column tile."""
-    M, Kd = x.shape
-    N = w.shape[0]
-    splits = splits or tc_cluster_splits(N, Kd)
-    sumsq = torch.empty((-(-N // 128), M), dtype=_F32, device=x.device)
-    L.check(L.core().slb_gemm_tc_resid_bf16(
-        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _p(bias), resid.data_ptr(),
-        resid.stride(0), sumsq.data_ptr(), M, N, Kd, splits, tc_max_stages, _stream()), "gemm_tc_resid")
-    return sumsq
-
-
-def gemm_tc_qkv_rope(x, w_qkv: torch.Tensor, bias: Optional[torch.Tensor],
+def gemm_tc_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Tensor],
                      positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                      page_size: int, inv_freq: Optional[torch.Tensor], rotary_dim: int,
                      q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
@@ -618,15 +518,15 @@ def gemm_tc_qkv_rope(x, w_qkv: torch.Tensor, bias: Optional[torch.Tensor],
     cache.  Head sizes in ``TC_ROPE_HEAD_DIMS``."""
     M, Kd = x.shape
     splits = splits or tc_cluster_splits(w_qkv.shape[0], Kd)
-    lazy = isinstance(x, LazyNorm)                          # the loader builds x from the stream
     L.check(L.core().slb_gemm_tc_qkv_rope_bf16(
-        None if lazy else x.data_ptr(), 0 if lazy else x.stride(0), w_qkv.data_ptr(), w_qkv.stride(0),
+        x.data_ptr(), x.stride(0), w_qkv.data_ptr(), w_qkv.stride(0),
         _p(bias), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
-        block_table.shape[1], page_size, _p(inv_freq), rotary_dim, q_out.data_ptr(), q_out.stride(0),
-        _p(k_cache), _p(v_cache), M, num_heads, num_kv_heads, head_dim, Kd, splits, tc_max_stages,
-        *(x.args() if lazy else _NO_NORM), _stream()), "gemm_tc_qkv_rope")
+        block_table.shape[1], page_size, _num_pages(k_cache), _p(inv_freq), rotary_dim,
+        q_out.data_ptr(), q_out.stride(0), _p(k_cache), _p(v_cache), M, num_heads, num_kv_heads,
+        head_dim, Kd, splits, tc_max_stages, _stream()), "gemm_tc_qkv_rope")
 
 
 def gemm_tc_status(reset: bool = False) -> int:
-    """0 unless a bounded wait inside the tcgen05 kernel ran out (synchronises)."""
+    """0 unless a bounded wait inside the tcgen05 kernels ran out, or the q|k|v epilogue met a
+    block-table entry outside the cache (synchronises)."""
     return L.core().slb_gemm_tc_status(1 if reset else 0)

@@ -25,31 +25,31 @@ class KernelError(RuntimeError):
 P, I, F, LL = c_void_p, c_int, c_float, c_longlong
 
 _CORE_SIGNATURES = {
-    "slb_embedding_f32": [P, P, P, I, I, I, P],
-    "slb_embedding_bf16": [P, P, P, I, I, I, P],
+    "slb_embedding_f32": [P, P, P, I, I, I, F, P],
+    "slb_embedding_bf16": [P, P, P, I, I, I, F, P],
+    "slb_logit_transform": [P, I, I, I, F, F, P],
     "slb_add_rmsnorm_f32": [P, P, P, P, P, I, I, F, P],
     "slb_add_rmsnorm_bf16": [P, P, P, P, P, I, I, F, P],
     "slb_swiglu_f32": [P, P, I, I, I, I, I, P],
     "slb_swiglu_bf16": [P, P, I, I, I, I, I, P],
-    "slb_qkv_rope_cache_f32": [P, I, P, P, P, P, I, I, P, I, P, I, P, P, I, I, I, I, P],
-    "slb_qkv_rope_cache_bf16": [P, I, P, P, P, P, I, I, P, I, P, I, P, P, I, I, I, I, P],
-    "slb_paged_attention_generic_f32": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, P],
-    "slb_paged_attention_generic_bf16": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, P],
+    "slb_qkv_rope_cache_f32": [P, I, P, P, P, P, I, I, I, P, I, P, I, P, P, I, I, I, I, P],
+    "slb_qkv_rope_cache_bf16": [P, I, P, P, P, P, I, I, I, P, I, P, I, P, P, I, I, I, I, P],
+    "slb_cache_write_status": [I],
+    "slb_paged_attention_generic_f32": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, F, I, P],
+    "slb_paged_attention_generic_bf16": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, F, I, P],
+    "slb_paged_attention_generic_status": [I],
     "slb_paged_attention_generic_tile_rows": [],
     "slb_gemm_simt_f32": [P, I, P, I, P, I, P, I, I, I, P],
     "slb_gemm_simt_bf16": [P, I, P, I, P, I, P, I, I, I, P],
     "slb_gemm_simt_bf16_f32out": [P, I, P, I, P, I, P, I, I, I, P],
     "slb_sample_rows": [P, I, I, I, P, P, P, P, P, P, P, P],
-    "slb_gemm_skinny_bf16": [P, I, P, I, P, I, P, I, I, I, I, I, P],
-    "slb_gemm_tc_decode_bf16": [P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, P, LL, I, I,
-                                P, I, P, I, P, F, P],
-    "slb_gemm_tc_resid_bf16": [P, I, P, I, P, P, I, P, I, I, I, I, I, P],
+    "slb_gemm_tc_decode_bf16": [P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, I, P],
     "slb_split_sum": [P, P, I, P, I, I, I, I, P],
     "slb_gemm_tc_cluster_bf16": [P, I, P, I, P, I, P, I, I, I, I, I, P],
-    "slb_gemm_tc_qkv_rope_bf16": [P, I, P, I, P, P, P, P, I, I, P, I, P, I, P, P, I, I, I, I, I, I, I,
-                                  P, I, P, I, P, F, P],
+    "slb_gemm_tc_qkv_rope_bf16": [P, I, P, I, P, P, P, P, I, I, I, P, I, P, I, P, P, I, I, I, I, I, I, I,
+                                  P],
     "slb_add_rmsnorm_parts_bf16": [P, P, I, LL, P, P, P, P, I, I, F, P],
-    "slb_qkv_rope_cache_parts_bf16": [P, I, LL, I, P, P, P, P, I, I, P, I, P, I, P, P, I, I, I, I, P],
+    "slb_qkv_rope_cache_parts_bf16": [P, I, LL, I, P, P, P, P, I, I, I, P, I, P, I, P, P, I, I, I, I, P],
     "slb_gemm_tc_status": [I],
 }
 
@@ -58,6 +58,7 @@ _OPTIONAL_SIGNATURES = {}
 
 _libs: Dict[str, ctypes.CDLL] = {}
 _pdl = True
+_pdl_early = False
 
 
 def set_pdl(on: bool) -> None:
@@ -73,6 +74,23 @@ def set_pdl(on: bool) -> None:
 
 def pdl_enabled() -> bool:
     return _pdl
+
+
+def set_pdl_early(on: bool) -> None:
+    """The long kernels (matrix products, decode attention) let their successor be scheduled
+    at their start instead of after their main loop: its blocks become resident beside theirs
+    wherever an SM has room and fetch their first weight tiles meanwhile."""
+    global _pdl_early
+    _pdl_early = bool(on)
+    for lib in _libs.values():
+        lib.slb_set_pdl_early(1 if _pdl_early else 0)
+
+
+def _apply_switches(lib: ctypes.CDLL) -> None:
+    lib.slb_set_pdl.argtypes = [I]
+    lib.slb_set_pdl(1 if _pdl else 0)
+    lib.slb_set_pdl_early.argtypes = [I]
+    lib.slb_set_pdl_early(1 if _pdl_early else 0)
 
 
 def _declare(lib: ctypes.CDLL, sigs: dict, required: bool) -> None:
@@ -97,15 +115,14 @@ def core() -> ctypes.CDLL:
             raise KernelsUnavailable(f"the servelab_b200 CUDA kernels are not available: {e}") from e
         _declare(lib, _CORE_SIGNATURES, True)
         _declare(lib, _OPTIONAL_SIGNATURES, False)
-        lib.slb_set_pdl.argtypes = [I]
-        lib.slb_set_pdl(1 if _pdl else 0)
+        _apply_switches(lib)
         _libs["core"] = lib
     return lib
 
 
 _ATTN_SIGNATURES = {
-    "slb_prefill_attention_bf16": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, F, I, P],
-    "slb_decode_attention_bf16": [P, I, P, P, P, I, P, I, P, P, I, I, I, I, F, I, I, P],
+    "slb_prefill_attention_bf16": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, P],
+    "slb_decode_attention_bf16": [P, I, P, P, P, I, P, I, P, P, I, I, I, I, I, F, I, I, P],
     "slb_prefill_attention_tile_rows": [],
     "slb_decode_attention_max_splits": [],
     "slb_attention_head_dim": [],
@@ -115,10 +132,9 @@ _ATTN_SIGNATURES = {
     "slb_prefill_attention_tc_status": [I],
     "slb_prefill_attention_tc_where": [P],
     "slb_decode_attention_ws_bf16": [P, I, P, P, P, I, P, I, P, P, P, I, I, I, I, I, F, I, I, I, F, I, P],
-    "slb_decode_attention_ws_fused_bf16": [P, I, LL, P, I, P, P, I, I, P, P, P, I, P, I, P, P, P, I, I,
-                                           I, I, I, F, I, I, I, F, I, P],
     "slb_decode_attention_ws_supported": [I],
     "slb_decode_attention_ws_status": [I],
+    "slb_decode_attention_ws_splits_used": [I],
     "slb_decode_attention_ws_max_splits": [],
     "slb_decode_attention_ws_tile_keys": [],
 }
@@ -147,14 +163,20 @@ def attention(head_dim: int) -> ctypes.CDLL:
         if lib.slb_attention_head_dim() != head_dim:
             raise KernelsUnavailable(f"attention library built for head size "
                                      f"{lib.slb_attention_head_dim()}, wanted {head_dim}")
-        lib.slb_set_pdl.argtypes = [I]
-        lib.slb_set_pdl(1 if _pdl else 0)
+        _apply_switches(lib)
         _libs[key] = lib
     return lib
 
 
+# measurements: called with the kernel's name after every launch of this package's kernels
+# (``ops.profile.StepProfile`` records a CUDA event there); None costs one comparison a launch
+after_launch = None
+
+
 def check(code: int, what: str) -> None:
     if code == 0:
+        if after_launch is not None:
+            after_launch(what)
         return
     if code == -1:
         raise KernelError(f"{what}: arguments refused (a size or pointer the kernel does not take)")

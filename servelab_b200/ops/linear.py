@@ -5,30 +5,18 @@ order per output).  bfloat16: the vendor library's tensor-core GEMM through
 torch (the reference's engine also calls a library for its products,
 servelab/parallel/tp_model.py:48-53), except for shapes whose rows are not
 16-byte aligned, which go to the CUDA-core kernel, and for small token counts
-(decode steps), which go to this package's tcgen05 weight-streaming kernel
-(TMA-fed, accumulating in tensor memory).  An mma.sync weight-streaming kernel
-also exists and is off by default.
+(decode steps), which go to this package's tcgen05 weight-streaming kernels
+(TMA-fed, accumulating in tensor memory).
 """
 
 from __future__ import annotations
 
-import weakref
 from typing import Optional
 
 import torch
 
 from . import kernels as K
-from . import library as L
-
-skinny_max_tokens = 0      # up to this many tokens the weight-streaming kernel runs (0: the
-                           # library GEMM measured faster inside a captured step)
-use_skinny = True          # switch for measurements
-
-
-def _skinny_ok(x, w, M):
-    return (use_skinny and M <= skinny_max_tokens and w.shape[1] % 8 == 0
-            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
-
+from .profile import mark as _mark
 
 tc_max_tokens = 16         # up to this many tokens the tcgen05 weight-streaming kernel runs
 tc_wide_max_tokens = 64    # ... and up to this many for products wide enough to need no K split
@@ -44,35 +32,16 @@ defer_split_sums = {"rope": True, "norm": True}
 fuse_swiglu = True         # the gate|up product of a decode step applies the activation itself
 
 
-# Which weights follow which in a forward pass, by address: a hint with which the tcgen05
-# product warms the L2 cache for its successor.  Set by the model after loading; a
-# matrix used twice keeps its last successor (the hint may be wrong, never harmful).
-# Weak references: the table keeps no model's weights alive.
-_successor = {}
-
-
-def set_weight_order(matrices) -> None:
-    """``matrices``: the weight matrices in the order a forward pass multiplies by them;
-    the last is followed by the first (the next step)."""
-    _successor.clear()
-    ms = [m for m in matrices if m is not None]
-    for a, b in zip(ms, ms[1:] + ms[:1]):
-        if a.data_ptr() != b.data_ptr():
-            _successor[a.data_ptr()] = weakref.ref(b)
-
-
-def _next_weight(w):
-    ref = _successor.get(w.data_ptr())
-    return ref() if ref is not None else None
+def _w_ok(w) -> bool:
+    return w.shape[1] % 8 == 0 and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0
 
 
 def _tc_ok(x, w, M):
     limit = tc_max_tokens
     if M > limit and K.tc_decode_splits(w.shape[0], w.shape[1]) == 1:
         limit = max(limit, tc_wide_max_tokens)
-    return (0 < M <= min(limit, K.TC_MAX_TOKENS) and w.shape[1] % 8 == 0
-            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
-            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+    return (0 < M <= min(limit, K.TC_MAX_TOKENS) and _w_ok(w)
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
 
 
 # Narrow products of a decode step (few k-blocks per block): the K splits of a row tile run as
@@ -86,35 +55,6 @@ cluster_sums = True
 cluster_max_kblocks = 16   # k-blocks (of 64) per block up to which the cluster form is used
 cluster_long_k_max_tokens = 64   # products with longer K ranges use it from 17 tokens up to here
 fuse_qkv_rope = True       # the q|k|v product of a decode step rotates and writes the cache itself
-
-
-# A product whose result updates the residual stream hands itself to the norm that follows
-# (``K.DeferredLinear``): the norm runs it as one kernel that adds into the stream and leaves
-# sums of squares, and returns ``K.LazyNorm``, from which the next product builds its input
-# while it loads.  A decode-step layer is then five kernels (q|k|v, attention, o, gate|up,
-# down) instead of seven.  Off: measured on the 7B shape it is no faster (3.12 against 3.07 ms a
-# step at batch 8, 2.97 against 2.91 at batch 1).  With programmatic dependent launch a norm
-# kernel between two products costs about 1 us, not its 2.2 us alone, because the product after
-# it fetches weights meanwhile; a product that builds its input itself starts its first MMA
-# later (sums of squares, then residual rows, then the conversion: 46.0 against 43.6 us for
-# gate|up, 10.7 against 9.9 for q|k|v), which costs the same again.
-fuse_resid_norm = False
-
-
-def _w_ok(w) -> bool:
-    return w.shape[1] % 8 == 0 and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0
-
-
-def _lazy_ok(x, w) -> bool:
-    """Whether the tcgen05 product of ``x`` (a LazyNorm) by ``w`` can build its input itself."""
-    return (x.dtype == torch.bfloat16 and 0 < x.shape[0] <= K.LAZY_NORM_MAX_TOKENS and _w_ok(w)
-            and x.resid.stride(0) % 4 == 0 and x.resid.data_ptr() % 16 == 0)
-
-
-def _deferred_ok(x, w, M, out_dtype) -> bool:
-    return (fuse_resid_norm and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16
-            and 0 < M <= min(tc_max_tokens, K.LAZY_NORM_MAX_TOKENS) and _tc_ok(x, w, M)
-            and K.tc_decode_splits(w.shape[0], w.shape[1]) > 1)
 
 
 def _cluster_ok(x, w, M) -> bool:
@@ -141,16 +81,12 @@ def qkv_projection(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Te
     (``k_cache`` None: no cache write).  One kernel for decode steps in bfloat16 with a head
     size the product's epilogue takes; otherwise the product, then the q/k/v kernel."""
     M = x.shape[0]
-    lazy = isinstance(x, K.LazyNorm)
-    fusable = (fuse_qkv_rope and x.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16
-               and head_dim in K.TC_ROPE_HEAD_DIMS and 0 < M <= tc_max_tokens
-               and K.tc_decode_splits(w_qkv.shape[0], w_qkv.shape[1]) > 1)
-    if fusable and (_lazy_ok(x, w_qkv) if lazy else _tc_ok(x, w_qkv, M)):
+    if (fuse_qkv_rope and x.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16
+            and head_dim in K.TC_ROPE_HEAD_DIMS and 0 < M <= tc_max_tokens
+            and K.tc_decode_splits(w_qkv.shape[0], w_qkv.shape[1]) > 1 and _tc_ok(x, w_qkv, M)):
         K.gemm_tc_qkv_rope(x, w_qkv, bias, positions, seq_of_token, block_table, page_size, inv_freq,
                            rotary_dim, q_out, k_cache, v_cache, num_heads, num_kv_heads, head_dim)
         return
-    if lazy:
-        x = x.materialize()
     qkv = linear(x, w_qkv, consumer="rope")                # the next kernel may add K-split parts
     K.qkv_rope_cache(qkv, bias, positions, seq_of_token, block_table, page_size, inv_freq,
                      rotary_dim, q_out, k_cache, v_cache, num_heads, num_kv_heads, head_dim)
@@ -163,30 +99,23 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, block: int) -> torch.
     then the activation kernel."""
     M = x.shape[0]
     inter = w_gate_up.shape[0] // 2
-    lazy = isinstance(x, K.LazyNorm)
     if (fuse_swiglu and x.dtype == torch.bfloat16 and block == K.SWIGLU_BLOCK
             and K.tc_decode_splits(w_gate_up.shape[0], w_gate_up.shape[1]) == 1
-            and (_lazy_ok(x, w_gate_up) if lazy else _tc_ok(x, w_gate_up, M))):
-        return K.gemm_tc_decode(x, w_gate_up, None, swiglu=True, next_weight=_next_weight(w_gate_up))
-    if lazy:
-        x = x.materialize()
+            and _tc_ok(x, w_gate_up, M)):
+        return K.gemm_tc_decode(x, w_gate_up, None, swiglu=True)
     gu = linear(x, w_gate_up)
     act = torch.empty((M, inter), dtype=x.dtype, device=x.device)
     K.swiglu(gu, act, block)
     return act
 
 
-def which_kernel(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-                 consumer: Optional[str] = None) -> str:
-    """The kernel ``linear`` runs for these operands: "deferred" (none yet: the norm that
-    follows runs the product), "simt" (CUDA cores), "tc_cluster" / "tc" (this package's
-    tcgen05 kernels, K splits as a cluster / as partial sums or unsplit), "skinny"
-    (mma.sync), "vendor" (library GEMM) or "empty"."""
+def which_kernel(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> str:
+    """The kernel ``linear`` runs for these operands: "simt" (CUDA cores), "tc_cluster" /
+    "tc" (this package's tcgen05 kernels, K splits as a cluster / as partial sums or
+    unsplit), "vendor" (library GEMM) or "empty"."""
     M, Kd = x.shape
     N = w.shape[0]
     out_dtype = out_dtype or x.dtype
-    if consumer == "norm" and _deferred_ok(x, w, M, out_dtype):
-        return "deferred"
     if x.dtype == torch.float32:
         return "simt"
     if M == 0:
@@ -195,8 +124,6 @@ def which_kernel(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
         return "tc_cluster"
     if _tc_ok(x, w, M):
         return "tc"
-    if _skinny_ok(x, w, M):
-        return "skinny"
     if Kd % 8 or N % 8:
         return "simt"
     return "vendor"
@@ -206,32 +133,29 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
            out_dtype: Optional[torch.dtype] = None, consumer: Optional[str] = None):
     """``consumer`` ("rope" or "norm"): the caller hands the result to a kernel of that
     kind, which accepts a ``SplitSum`` (partial sums of a K-split product); it may then
-    get one instead of a tensor.  With "norm" the caller returns the result as its update of
-    the residual stream and may get a ``K.DeferredLinear`` (the product has not run)."""
-    if isinstance(x, K.LazyNorm):
-        x = x.materialize()
+    get one instead of a tensor."""
     M, N = x.shape[0], w.shape[0]
     out_dtype = out_dtype or x.dtype
-    kernel = which_kernel(x, w, out_dtype, consumer)
-    if kernel == "deferred":
-        return K.DeferredLinear(x, w, bias)
+    kernel = which_kernel(x, w, out_dtype)
     if kernel == "empty":
         return torch.empty((0, N), dtype=out_dtype, device=x.device)
     if kernel == "tc_cluster":
         return K.gemm_tc_cluster(x, w, None, bias)
     if kernel == "tc":
         return K.gemm_tc_decode(x, w, None, bias, defer_sum=defer_split_sums.get(consumer, False),
-                                out_dtype=out_dtype, next_weight=_next_weight(w))
-    if kernel in ("simt", "skinny"):
+                                out_dtype=out_dtype)
+    if kernel == "simt":
         out = torch.empty((M, N), dtype=torch.float32 if x.dtype == torch.float32 else out_dtype,
                           device=x.device)
-        (K.gemm_simt if kernel == "simt" else K.gemm_skinny)(x, w, out, bias)
+        K.gemm_simt(x, w, out, bias)
         return out
     if out_dtype == torch.float32:
         out = torch.mm(x, w.t(), out_dtype=torch.float32)
         if bias is not None:
             out += bias
-        return out
-    if bias is not None:
-        return torch.addmm(bias.to(x.dtype), x, w.t())
-    return torch.mm(x, w.t())
+    elif bias is not None:
+        out = torch.addmm(bias.to(x.dtype), x, w.t())
+    else:
+        out = torch.mm(x, w.t())
+    _mark("library gemm")
+    return out

@@ -4,9 +4,8 @@ Per step: one fused q|k|v product (weights concatenated at load), then one
 kernel that adds the q/k/v bias, rotates q and k by the token positions and
 writes k (rotated) and v into the request's pages, then attention of every query
 of the step over its request's cached keys (the step's own included), then the
-output projection.  In bfloat16 steps of single tokens the decode kernel can do the
-second and third of these itself, starting from the product (``ops.attention.fuse_decode_qkv``,
-off by default).  Order and formulas:
+output projection.  In bfloat16 decode steps the product's own epilogue does the second of
+these (``ops.linear.qkv_projection``).  Order and formulas:
 servelab/parallel/tp_model.py:48-53 (projections with bias), :128-129 (rotation before the cache write), :136-157
 (scores * D^-1/2, causal mask, float32 softmax, P.V), :131 (bias-free output
 projection).  ``window`` limits the visible keys to the last w positions.
@@ -34,13 +33,12 @@ from .registry import POSITIONS, build_part, register_mixer
 @register_mixer("paged_attention")
 class PagedAttention(Mixer):
     graph_safe = True
-    accepts_lazy_norm = True     # ``x`` may be a K.LazyNorm: the q|k|v product builds its input
 
     def __init__(self, spec, prefix, env):
         super().__init__(spec, prefix, env)
         if spec.num_heads % spec.num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
-        self.position = build_part(POSITIONS, spec.position, prefix + ".rotary_emb", env)
+        self.position = build_part(POSITIONS, spec.position, f"{prefix}.{spec.position_name}", env)
         self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(spec.head_dim)
         self.q_size = spec.num_heads * spec.head_dim
         self.kv_size = spec.num_kv_heads * spec.head_dim
@@ -53,16 +51,14 @@ class PagedAttention(Mixer):
     @classmethod
     def declare(cls, spec, prefix):
         h, q, kv = spec.hidden_size, spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
-        out = [TensorDecl(prefix + ".q_proj.weight", (q, h), MATRIX),
-               TensorDecl(prefix + ".k_proj.weight", (kv, h), MATRIX),
-               TensorDecl(prefix + ".v_proj.weight", (kv, h), MATRIX),
-               TensorDecl(prefix + ".o_proj.weight", (h, q), MATRIX)]
+        qn, kn, vn, on = (f"{prefix}.{n}" for n in (spec.q_name, spec.k_name, spec.v_name, spec.o_name))
+        out = [TensorDecl(qn + ".weight", (q, h), MATRIX), TensorDecl(kn + ".weight", (kv, h), MATRIX),
+               TensorDecl(vn + ".weight", (kv, h), MATRIX), TensorDecl(on + ".weight", (h, q), MATRIX)]
         if spec.qkv_bias:
-            out += [TensorDecl(prefix + ".q_proj.bias", (q,), BIAS),
-                    TensorDecl(prefix + ".k_proj.bias", (kv,), BIAS),
-                    TensorDecl(prefix + ".v_proj.bias", (kv,), BIAS)]
+            out += [TensorDecl(qn + ".bias", (q,), BIAS), TensorDecl(kn + ".bias", (kv,), BIAS),
+                    TensorDecl(vn + ".bias", (kv,), BIAS)]
         if spec.out_bias:
-            out.append(TensorDecl(prefix + ".o_proj.bias", (h,), BIAS))
+            out.append(TensorDecl(on + ".bias", (h,), BIAS))
         return out
 
     @classmethod
@@ -70,15 +66,12 @@ class PagedAttention(Mixer):
         return PagedKVRequest(spec.num_kv_heads, spec.head_dim, spec.window)
 
     def load(self, store):
-        p = self.prefix
-        self.w_qkv = store.cat([p + ".q_proj.weight", p + ".k_proj.weight", p + ".v_proj.weight"])
-        self.b_qkv = (store.cat([p + ".q_proj.bias", p + ".k_proj.bias", p + ".v_proj.bias"])
-                      if self.spec.qkv_bias else None)
-        self.w_o = store.get(p + ".o_proj.weight")
-        self.b_o = store.get(p + ".o_proj.bias") if self.spec.out_bias else None
-
-    def matrices(self):
-        return [self.w_qkv, self.w_o]
+        s = self.spec
+        qn, kn, vn, on = (f"{self.prefix}.{n}" for n in (s.q_name, s.k_name, s.v_name, s.o_name))
+        self.w_qkv = store.cat([qn + ".weight", kn + ".weight", vn + ".weight"])
+        self.b_qkv = store.cat([qn + ".bias", kn + ".bias", vn + ".bias"]) if s.qkv_bias else None
+        self.w_o = store.get(on + ".weight")
+        self.b_o = store.get(on + ".bias") if s.out_bias else None
 
     def forward(self, ctx, x, cache, owns_cache):
         s = self.spec
@@ -87,18 +80,21 @@ class PagedAttention(Mixer):
         rot = self.position.rotary_table()
         inv_freq, rotary_dim = rot if rot is not None else (None, 0)
         device = x.device
-        if A.fused_decode_applies(ctx, x.dtype, s.head_dim, cache.page_size):
-            qkv = linear(x, self.w_qkv, consumer="rope")   # the next kernel may add K-split parts
-            out = torch.empty((T, self.q_size), dtype=x.dtype, device=device)
-            K.decode_attention_fused(ctx, qkv, self.b_qkv, inv_freq, rotary_dim, cache.k, cache.v,
-                                     owns_cache, out, table, s.num_heads, s.num_kv_heads,
-                                     s.head_dim, cache.page_size, self.scale, s.window or 0)
-            return linear(out, self.w_o, self.b_o, consumer="norm")
         q = torch.empty((T, self.q_size), dtype=x.dtype, device=device)
-        # (a SplitSum has no dtype of its own; q follows the activations)
-        qkv_projection(x, self.w_qkv, self.b_qkv, ctx.positions, ctx.seq_of_token, table,
-                       cache.page_size, inv_freq, rotary_dim, q, cache.k if owns_cache else None,
-                       cache.v if owns_cache else None, s.num_heads, s.num_kv_heads, s.head_dim)
+        k_cache, v_cache = (cache.k, cache.v) if owns_cache else (None, None)
+        if self.position.transforms_qk:
+            # an encoding of its own on the projected q and k: product with bias, the
+            # encoding in place, then the q/k/v kernel without rotation (copy + cache write)
+            qkv = linear(x, self.w_qkv, self.b_qkv)
+            self.position.apply_to_qk(
+                ctx, qkv[:, :self.q_size].view(T, s.num_heads, s.head_dim),
+                qkv[:, self.q_size:self.q_size + self.kv_size].view(T, s.num_kv_heads, s.head_dim))
+            K.qkv_rope_cache(qkv, None, ctx.positions, ctx.seq_of_token, table, cache.page_size,
+                             None, 0, q, k_cache, v_cache, s.num_heads, s.num_kv_heads, s.head_dim)
+        else:
+            qkv_projection(x, self.w_qkv, self.b_qkv, ctx.positions, ctx.seq_of_token, table,
+                           cache.page_size, inv_freq, rotary_dim, q, k_cache, v_cache, s.num_heads,
+                           s.num_kv_heads, s.head_dim)
         out = torch.empty_like(q)
         A.paged_attention(ctx, q, cache.k, cache.v, out, table, s.num_heads, s.num_kv_heads,
                           s.head_dim, cache.page_size, self.scale, s.window or 0)

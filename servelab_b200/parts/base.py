@@ -8,9 +8,14 @@ is in: everything it needs arrives through its spec, its prefix, the
 
 Kinds of part and what each must provide (beyond ``declare`` and ``load``):
 
-  PositionEncoding   ``rotary_table()`` -> (inv_freq float32 [rotary_dim/2],
-                     rotary_dim) or None; ``apply_to_embedding(ctx, resid)`` for
-                     encodings added to the embedded tokens (default: nothing).
+  PositionEncoding   one of three seams.  ``rotary_table()`` -> (inv_freq float32
+                     [rotary_dim/2], rotary_dim) or None: rotate-half, fused into the
+                     mixer's q/k kernel.  ``apply_to_qk(ctx, q, k)`` with
+                     ``transforms_qk = True``: any other encoding that acts on the
+                     projected queries [T, H, D] and keys [T, Hkv, D] (bias already
+                     added) in place, before the keys reach the cache.
+                     ``apply_to_embedding(ctx, resid)``: encodings added to the
+                     embedded tokens (default: nothing).
   Norm               ``forward(ctx, resid, delta, out_rows=None)``: adds ``delta``
                      (compute dtype, may be None) into the float32 stream ``resid``
                      in place and returns the normed rows in the compute dtype;
@@ -26,14 +31,11 @@ Kinds of part and what each must provide (beyond ``declare`` and ``load``):
                      (resid, delta): the float32 stream and a not-yet-added
                      update, so that the add fuses with the next norm.
 
-Optional, for parts that want to take part in kernel fusion across part boundaries: a
-value handed from one part to the next may be unfinished (``ops.kernels.SplitSum``: partial
-sums of a K-split product; ``DeferredLinear``: a product that has not run; ``LazyNorm``: a
-norm that has not run).  A part says which forms it takes with class attributes
-(``accepts_split_sum``, ``accepts_deferred_linear`` for an incoming update,
-``accepts_lazy_norm`` for an incoming ``x``); a norm that can leave its own result
-unfinished sets ``returns_lazy_norm`` and takes ``lazy_ok=True`` in ``forward``.  A part that
-sets none of these always gets and returns plain tensors.
+Optional, for parts that want to take part in kernel fusion across part boundaries: an
+update handed from one part to the next may be unfinished (``ops.kernels.SplitSum``: the
+float32 partial sums of a K-split product, which the consuming kernel adds itself).  A part
+says that it takes the form with the class attribute ``accepts_split_sum``; a part that does
+not set it always gets plain tensors.
 """
 
 from __future__ import annotations
@@ -85,16 +87,17 @@ class Part:
     def load(self, store: WeightStore) -> None:
         pass
 
-    def matrices(self) -> List[torch.Tensor]:
-        """The weight matrices in the order forward() multiplies by them (after
-        load()).  A hint only: the model uses it to tell each product which weights
-        come next, so that they can be requested into the cache early.  May be empty."""
-        return []
-
 
 class PositionEncoding(Part):
+    transforms_qk = False         # True: the mixer calls apply_to_qk() instead of rotating
+
     def rotary_table(self) -> Optional[Tuple[torch.Tensor, int]]:
         return None
+
+    def apply_to_qk(self, ctx, q: torch.Tensor, k: torch.Tensor) -> None:
+        """Change q [T, H, D] and k [T, Hkv, D] (views of the step's projection, bias
+        added) in place by the tokens' positions (``ctx.positions``)."""
+        raise NotImplementedError
 
     def apply_to_embedding(self, ctx, resid: torch.Tensor) -> None:
         pass

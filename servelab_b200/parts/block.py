@@ -10,8 +10,7 @@ from __future__ import annotations
 
 from ..ops.kernels import plain_unless
 from .base import Block
-from .registry import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, build_part, part_class,
-                       register_block)
+from .registry import FEED_FORWARDS, MIXERS, NORMS, build_part, part_class, register_block
 
 
 @register_block("pre_norm")
@@ -24,20 +23,25 @@ class PreNormBlock(Block):
         self.graph_safe = all(getattr(p, "graph_safe", False) for p in
                               (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward))
 
+    @staticmethod
+    def _members(spec, prefix):
+        """(registry, spec, prefix) of the four parts; the names under the layer's prefix are
+        the spec's, so the block knows no checkpoint's naming."""
+        return ((NORMS, spec.mixer_norm, f"{prefix}.{spec.mixer_norm_name}"),
+                (MIXERS, spec.mixer, f"{prefix}.{spec.mixer_name}"),
+                (NORMS, spec.ff_norm, f"{prefix}.{spec.ff_norm_name}"),
+                (FEED_FORWARDS, spec.feed_forward, f"{prefix}.{spec.feed_forward_name}"))
+
     def _build(self, spec, prefix, env):
-        self.mixer_norm = build_part(NORMS, spec.mixer_norm, prefix + ".input_layernorm", env)
-        self.mixer = build_part(MIXERS, spec.mixer, prefix + ".self_attn", env)
-        self.ff_norm = build_part(NORMS, spec.ff_norm, prefix + ".post_attention_layernorm", env)
-        self.feed_forward = build_part(FEED_FORWARDS, spec.feed_forward, prefix + ".mlp", env)
+        self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward = (
+            build_part(table, part, name, env) for table, part, name in self._members(spec, prefix))
 
     @classmethod
     def declare(cls, spec, prefix):
-        return (part_class(NORMS, spec.mixer_norm).declare(spec.mixer_norm, prefix + ".input_layernorm")
-                + part_class(MIXERS, spec.mixer).declare(spec.mixer, prefix + ".self_attn")
-                + part_class(NORMS, spec.ff_norm).declare(spec.ff_norm,
-                                                          prefix + ".post_attention_layernorm")
-                + part_class(FEED_FORWARDS, spec.feed_forward).declare(spec.feed_forward,
-                                                                       prefix + ".mlp"))
+        out = []
+        for table, part, name in cls._members(spec, prefix):
+            out += part_class(table, part).declare(part, name)
+        return out
 
     @classmethod
     def cache_request(cls, spec):
@@ -47,25 +51,12 @@ class PreNormBlock(Block):
         for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward):
             p.load(store)
 
-    def matrices(self):
-        return self.mixer.matrices() + self.feed_forward.matrices()
-
     accepts_split_sum = True          # the incoming ``delta`` may be a SplitSum
-    accepts_deferred_linear = True    # ... or a product that has not run
-
-    @staticmethod
-    def _norm(norm, consumer, ctx, resid, delta):
-        """The norm before ``consumer``.  An update may arrive unfinished (partial sums of
-        a K-split product, a product that has not run); a norm that does not take the
-        form gets the plain tensor.  A norm that can leave its own result unfinished does
-        so if the consumer takes it."""
-        delta = plain_unless(norm, delta)
-        if getattr(norm, "returns_lazy_norm", False) and getattr(consumer, "accepts_lazy_norm", False):
-            return norm.forward(ctx, resid, delta, lazy_ok=True)
-        return norm.forward(ctx, resid, delta)
 
     def forward(self, ctx, resid, delta, cache, owns_cache):
-        x = self._norm(self.mixer_norm, self.mixer, ctx, resid, delta)
+        # an update may arrive as the partial sums of a K-split product; a norm that does not
+        # take that form gets the plain tensor
+        x = self.mixer_norm.forward(ctx, resid, plain_unless(self.mixer_norm, delta))
         a = self.mixer.forward(ctx, x, cache, owns_cache)
-        x = self._norm(self.ff_norm, self.feed_forward, ctx, resid, a)
+        x = self.ff_norm.forward(ctx, resid, plain_unless(self.ff_norm, a))
         return resid, self.feed_forward.forward(ctx, x)

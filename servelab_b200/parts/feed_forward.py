@@ -19,7 +19,6 @@ from .registry import register_feed_forward
 @register_feed_forward("gated_mlp")
 class GatedMLP(FeedForward):
     graph_safe = True
-    accepts_lazy_norm = True     # ``x`` may be a K.LazyNorm: the gate|up product builds its input
 
     def __init__(self, spec, prefix, env):
         super().__init__(spec, prefix, env)
@@ -31,13 +30,13 @@ class GatedMLP(FeedForward):
     @classmethod
     def declare(cls, spec, prefix):
         h, i = spec.hidden_size, spec.intermediate_size
-        return [TensorDecl(prefix + ".gate_proj.weight", (i, h), MATRIX),
-                TensorDecl(prefix + ".up_proj.weight", (i, h), MATRIX),
-                TensorDecl(prefix + ".down_proj.weight", (h, i), MATRIX)]
+        return [TensorDecl(f"{prefix}.{spec.gate_name}.weight", (i, h), MATRIX),
+                TensorDecl(f"{prefix}.{spec.up_name}.weight", (i, h), MATRIX),
+                TensorDecl(f"{prefix}.{spec.down_name}.weight", (h, i), MATRIX)]
 
     def load(self, store):
-        gate = store.get(self.prefix + ".gate_proj.weight")
-        up = store.get(self.prefix + ".up_proj.weight")
+        gate = store.get(f"{self.prefix}.{self.spec.gate_name}.weight")
+        up = store.get(f"{self.prefix}.{self.spec.up_name}.weight")
         inter, h = gate.shape
         self.block = K.SWIGLU_BLOCK if inter % K.SWIGLU_BLOCK == 0 else 0
         if self.block:
@@ -46,10 +45,7 @@ class GatedMLP(FeedForward):
                                          dim=1).reshape(2 * inter, h).contiguous()
         else:
             self.w_gate_up = torch.cat([gate, up], dim=0)
-        self.w_down = store.get(self.prefix + ".down_proj.weight")
-
-    def matrices(self):
-        return [self.w_gate_up, self.w_down]
+        self.w_down = store.get(f"{self.prefix}.{self.spec.down_name}.weight")
 
     def forward(self, ctx, x):
         act = gated_linear(x, self.w_gate_up, self.block)

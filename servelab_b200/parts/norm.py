@@ -27,16 +27,7 @@ class RMSNorm(Norm):
     def load(self, store):
         self.weight = store.get(self.prefix + ".weight")
 
-    accepts_deferred_linear = True   # ... or a product that has not run (K.DeferredLinear)
-    returns_lazy_norm = True         # ``forward(..., lazy_ok=True)`` may return a K.LazyNorm
-
-    def forward(self, ctx, resid, delta, out_rows=None, lazy_ok=False):
-        if isinstance(delta, K.DeferredLinear):
-            # one kernel: the product, its add into the stream, sums of squares per tile
-            sumsq = K.gemm_tc_resid(delta.x, delta.w, delta.bias, resid)
-            if lazy_ok and out_rows is None:
-                return K.LazyNorm(resid, sumsq, self.weight, self.spec.eps, self.env.dtype)
-            delta = None
+    def forward(self, ctx, resid, delta, out_rows=None):
         rows = resid.shape[0] if out_rows is None else out_rows.numel()
         out = torch.empty((rows, self.spec.dim), dtype=self.env.dtype, device=resid.device)
         K.add_rmsnorm(resid, delta, self.weight, self.spec.eps, out, out_rows)

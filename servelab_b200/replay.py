@@ -29,15 +29,23 @@ class TraceSession:
     tokens each live request holds.  ``run_step`` executes one trace step."""
 
     def __init__(self, model: str, dtype: str, max_tokens: int, page_size: int = 16,
-                 max_live: int = 8):
+                 max_live: int = 8, poison_cache: bool = False, cuda_graphs: bool = False,
+                 runner=None):
+        """``model``: a model folder; or hand in a ``runner`` built elsewhere (a typed config
+        with weights made on the device).  ``poison_cache`` and ``cuda_graphs`` are what
+        tests switch on: unwritten cache slots hold a huge value; steps of single tokens
+        replay captured graphs, as in generation."""
         from .config.engine import CacheConfig
         from .engine.runner import ModelRunner
 
         self.max_tokens, self.max_live = max_tokens, max_live
-        pages = max(1, -(-max_tokens // page_size))
-        self.runner = ModelRunner.from_folder(
-            model, dtype=dtype, cache_config=CacheConfig(block_size=page_size, num_blocks=pages),
-            max_num_seqs=max_live)
+        if runner is None:
+            pages = max(1, -(-max_tokens // page_size))
+            runner = ModelRunner.from_folder(
+                model, dtype=dtype, max_num_seqs=max_live, cuda_graphs=cuda_graphs,
+                cache_config=CacheConfig(block_size=page_size, num_blocks=pages,
+                                         poison_cache=poison_cache))
+        self.runner = runner
         self.cache = self.runner.cache
         self.held: Dict[str, int] = {}             # request -> tokens in the cache
 

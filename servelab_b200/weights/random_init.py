@@ -21,13 +21,15 @@ from .source import TABLE, RandomSource
 
 
 def write_random_model(folder: str, config, seed: int, dtype: torch.dtype = torch.float32,
-                       std: float = 0.02, norm_std: float = 0.1) -> str:
-    """``config`` is a typed architecture config (``to_dict``/``to_model_spec``)."""
+                       std: float = 0.02, norm_std: float = 0.1, std_of=None) -> str:
+    """``config`` is a typed architecture config (``to_dict``/``to_model_spec``);
+    ``std_of`` maps parts of tensor names to standard deviations of their own
+    (``RandomSource``)."""
     from ..models.causal_lm import declare_tensors  # parts declare their tensors
 
     os.makedirs(folder, exist_ok=True)
     decls = declare_tensors(config.to_model_spec())
-    src = RandomSource(decls, seed, std=std, norm_std=norm_std, dtype=dtype)
+    src = RandomSource(decls, seed, std=std, norm_std=norm_std, dtype=dtype, std_of=std_of)
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(config.to_dict(), f, indent=1)
     write_safetensors(

@@ -19,7 +19,7 @@ import json
 import os
 import zlib
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Sequence, Tuple
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -123,9 +123,13 @@ class RandomSource(WeightSource):
 
     def __init__(self, decls: Iterable[TensorDecl], seed: int, std: float = 0.02,
                  norm_std: float = 0.1, device: str = "cpu",
-                 dtype: torch.dtype = torch.float32):
+                 dtype: torch.dtype = torch.float32, std_of: Optional[Dict[str, float]] = None):
+        """``std_of``: standard deviations for tensors whose name contains a key (the first
+        key that matches), e.g. {"q_proj.weight": 0.25} for queries large enough that the
+        softmax of a tiny model is peaked."""
         self.decls = {d.name: d for d in decls}
         self.seed, self.std, self.norm_std = int(seed), std, norm_std
+        self.std_of = dict(std_of or {})
         self.device, self.dtype = device, dtype
         self.where = f"<random weights, seed {seed}>"
 
@@ -148,7 +152,7 @@ class RandomSource(WeightSource):
         if d.role == NORM:
             t.mul_(self.norm_std).add_(1.0)
         else:
-            t.mul_(self.std)
+            t.mul_(next((v for k, v in self.std_of.items() if k in name), self.std))
         return t.to(self.dtype)
 
 

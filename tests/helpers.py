@@ -4,7 +4,8 @@ The tiny configurations differ in every size and option: layers, width, head
 counts and groups, head size, intermediate size (172 is no multiple of 8), vocabulary
 (300 is no power of two), rope theta, norm eps, tying, page size, and windowed
 layers (configuration C, whose q width 4*48 also differs from its hidden size).
-Configuration D has head size 64, which the fastest attention kernels take.
+Configuration D has head size 64, which the fastest attention kernels take; E has head
+size 128, a long position limit and weights that make the attention peaked.
 """
 
 from __future__ import annotations
@@ -52,14 +53,32 @@ TINY_D = {
     "max_position_embeddings": 320, "torch_dtype": "float32", "eos_token_id": 383,
     "use_sliding_window": True, "sliding_window": 40, "max_window_layers": 1,
 }
+# head size 128 and a position limit beyond 768, so that the kernels of the benchmark's shape
+# run inside a tiny model and a request can be long enough for its decode steps to be split
+# over the keys; its queries and keys are drawn large (``PEAKED``): the scores then have a
+# standard deviation of several units, the softmax is peaked, and a key that is lost, seen
+# twice or rotated by the wrong angle moves the logits far beyond bfloat16 rounding
+TINY_E = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 128, "num_attention_heads": 3,
+    "num_key_value_heads": 1, "head_dim": 128, "intermediate_size": 208, "vocab_size": 320,
+    "rope_theta": 100000.0, "rms_norm_eps": 4e-6, "tie_word_embeddings": True,
+    "max_position_embeddings": 1280, "torch_dtype": "float32", "eos_token_id": 319,
+    "use_sliding_window": False,
+}
+PEAKED = {"q_proj.weight": 0.2, "k_proj.weight": 0.2, "v_proj.weight": 0.1, "lm_head.weight": 0.1,
+          "embed_tokens.weight": 0.1}
 CONFIGS = {"A": (TINY_A, 0, 16), "B": (TINY_B, 2, 8), "C": (TINY_C, 7, 16),
-           "D": (TINY_D, 11, 8)}  # cfg, seed, page
+           "D": (TINY_D, 11, 8), "E": (TINY_E, 13, 16)}  # cfg, seed, page
+STD_OF = {"E": PEAKED}           # per-tensor standard deviations of a configuration's weights
 
 
-def make_model(folder: str, cfg: dict, seed: int) -> str:
+def make_model(folder: str, cfg: dict, seed: int, std_of=None) -> str:
     from servelab_b200.config import config_from_dict
     from servelab_b200.weights import write_random_model
-    return write_random_model(folder, config_from_dict(cfg), seed)
+    if std_of is None:
+        std_of = next((STD_OF[k] for k, v in CONFIGS.items() if v[0] is cfg and k in STD_OF), None)
+    return write_random_model(folder, config_from_dict(cfg), seed, std_of=std_of)
 
 
 def random_ids(n: int, vocab: int, seed: int) -> List[int]:

@@ -28,8 +28,8 @@ def _ops(m, n, k, dtype=torch.bfloat16):
 def test_decode_steps_run_this_package_s_tensor_core_kernels(shape):
     h, q, qkv, inter, vocab = SHAPES[shape]
     for m in (1, 8, 16):
-        assert L.which_kernel(*_ops(m, qkv, h), consumer="rope") == "tc_cluster"
-        assert L.which_kernel(*_ops(m, h, q), consumer="norm") == "tc_cluster"
+        assert L.which_kernel(*_ops(m, qkv, h)) == "tc_cluster"
+        assert L.which_kernel(*_ops(m, h, q)) == "tc_cluster"
         if shape == "0.5b":      # 76 row tiles: three K splits still fit; the activation is a kernel
             assert L.which_kernel(*_ops(m, 2 * inter, h)) == "tc_cluster"
         else:                    # wide: no K split, the activation in the product's epilogue
@@ -37,7 +37,7 @@ def test_decode_steps_run_this_package_s_tensor_core_kernels(shape):
             assert K.tc_decode_splits(2 * inter, h) == 1
         assert L.which_kernel(*_ops(m, vocab, h), out_dtype=torch.float32) == "tc"
     # the down product: long K ranges; partial sums up to 16 tokens unless it is small
-    kinds = {m: L.which_kernel(*_ops(m, h, inter), consumer="norm") for m in (8, 32, 64, 65)}
+    kinds = {m: L.which_kernel(*_ops(m, h, inter)) for m in (8, 32, 64, 65)}
     if shape == "0.5b":
         assert kinds == {8: "tc_cluster", 32: "vendor", 64: "vendor", 65: "vendor"}
     else:
@@ -62,9 +62,8 @@ def test_many_tokens_go_to_the_vendor_gemm_and_ragged_or_float32_ones_to_cuda_co
 def test_switches_change_the_decision(monkeypatch):
     h, q, qkv, inter, vocab = SHAPES["7b"]
     monkeypatch.setattr(L, "cluster_sums", False)
-    assert L.which_kernel(*_ops(8, h, q), consumer="norm") == "tc"
-    assert L.which_kernel(*_ops(32, h, inter), consumer="norm") == "vendor"
-    monkeypatch.setattr(L, "fuse_resid_norm", True)
-    assert L.which_kernel(*_ops(8, h, q), consumer="norm") == "deferred"
-    assert L.which_kernel(*_ops(8, h, q)) == "tc"                            # only an update of the stream
-    assert L.which_kernel(*_ops(17, h, q), consumer="norm") == "vendor"
+    assert L.which_kernel(*_ops(8, h, q)) == "tc"
+    assert L.which_kernel(*_ops(32, h, inter)) == "vendor"
+    assert L.which_kernel(*_ops(17, h, q)) == "vendor"
+    monkeypatch.setattr(L, "tc_max_tokens", 4)
+    assert L.which_kernel(*_ops(8, h, q)) == "vendor"

@@ -549,7 +549,7 @@ def test_decode_attention_tensor_cores(H, Hkv, D, ps, window, splits):
     L.check(lib.slb_decode_attention_bf16(
         q.data_ptr(), q.stride(0), case.kc.data_ptr(), case.vc.data_ptr(), out.data_ptr(),
         out.stride(0), table.data_ptr(), table.shape[1], ctx.ctx_len.data_ptr(),
-        scratch.data_ptr(), S, H, Hkv, ps, 1 / math.sqrt(D), window, splits,
+        scratch.data_ptr(), S, H, Hkv, ps, case.kc.shape[0], 1 / math.sqrt(D), window, splits,
         torch.cuda.current_stream().cuda_stream), "decode")
     want = case.reference(window=window or None)
     assert K().attention_status(D, reset=True) == 0, "a bounded wait in the kernel gave up"
@@ -608,96 +608,6 @@ def test_decode_attention_one_launch(H, Hkv, D, ps, window, splits, stages, coef
         out2 = torch.empty_like(q)
         fn(ctx, q, case.kc, case.vc, out2, table, H, Hkv, D, ps, 1 / math.sqrt(D), window)
         assert (out2.float().cpu() - want).abs().max() <= TOL["bfloat16"]
-
-
-@pytest.mark.parametrize("H,Hkv,D,ps,rot", [(7, 1, 64, 8, 64), (28, 4, 128, 16, 128), (2, 1, 256, 32, 64),
-                                            (20, 1, 64, 16, 0), (24, 3, 64, 256, 32),
-                                            (48, 2, 128, 16, 128)])
-@pytest.mark.parametrize("window", [0, 70])
-@pytest.mark.parametrize("splits,nparts", [(0, 0), (32, 3), (5, 1), (1, 2)])
-def test_decode_attention_from_the_qkv_product(H, Hkv, D, ps, rot, window, splits, nparts):
-    """The decode kernel that starts from the q|k|v product (bias, rotation, cache write
-    inside it) against float32 arithmetic and against the q/k/v kernel followed by the
-    decode kernel: the new key lands on the first row of a tile (context 65, 129), on
-    its last row (64, 128), in a page of its own and in the middle of a long context;
-    full, partial and no rotation; the product as bfloat16 and as K-split partial sums;
-    groups of 8 and 16 head rows and several head tiles a block; and a run that reads a
-    cache another run wrote (nothing may be written)."""
-    from servelab_b200.ops import kernels as kernels_module
-    from servelab_b200.ops.kernels import SplitSum
-    dt = torch.bfloat16
-    ctxs = [1, 63, 64, 65, 700, 2049, 17, 128, 129]
-    S = len(ctxs)
-    case = PagedCase(ctxs, [1] * S, H, Hkv, D, ps, dt, seed=D + splits + nparts)
-    g = torch.Generator().manual_seed(H + rot)
-    width = (H + 2 * Hkv) * D
-    x = torch.randn(S, width, generator=g)
-    bias = torch.randn(width, generator=g)
-    inv = P.rope_inv_freq(rot, 10000.0) if rot else None
-    if nparts:
-        ps_ = [torch.randn(S, width, generator=g) for _ in range(nparts - 1)]
-        parts = torch.stack(ps_ + [x - sum(ps_) if ps_ else x]).contiguous()
-        x = parts.sum(0) if nparts == 1 else x       # what the kernels add up, to rounding
-        src = SplitSum(parts.to(DEV), None, dt)
-    else:
-        x = x.to(dt).float()
-        src = x.to(dt).to(DEV)
-    # float32 arithmetic of the same step; the results go into the case as its q and newest k, v
-    y = x + bias
-    pos = torch.tensor([c - 1 for c in ctxs])
-    qf = y[:, :H * D].view(S, H, D)
-    kf = y[:, H * D:(H + Hkv) * D].view(S, Hkv, D)
-    vf = y[:, (H + Hkv) * D:].view(S, Hkv, D)
-    if rot:
-        qf = torch.cat([P.rope(qf[..., :rot], pos, inv), qf[..., rot:]], -1)
-        kf = torch.cat([P.rope(kf[..., :rot], pos, inv), kf[..., rot:]], -1)
-    for i in range(S):
-        case.q[i] = qf[i:i + 1].to(dt)
-        case.k[i][-1] = kf[i].to(dt)
-        case.v[i][-1] = vf[i].to(dt)
-    want = case.reference(window=window or None)
-    case.scatter()
-    for i, c in enumerate(ctxs):                     # the step's own rows are not in the cache yet
-        page = case.tables[i][(c - 1) // ps]
-        case.kc[page, :, (c - 1) % ps] = 55.0
-        case.vc[page, :, (c - 1) % ps] = -55.0
-    ctx, _, table = _ctx_for(case)
-    bias_d = bias.to(DEV)
-    inv_d = inv.to(DEV) if rot else None
-    scale = 1 / math.sqrt(D)
-    kernels_module.decode_ws_force_splits = splits
-    try:
-        # the q/k/v kernel, then the decode kernel
-        kc1, vc1 = case.kc.clone(), case.vc.clone()
-        q1 = torch.empty(S, H * D, device=DEV, dtype=dt)
-        K().qkv_rope_cache(src, bias_d, i32(pos.tolist()), i32(list(range(S))), table, ps, inv_d, rot, q1,
-                           kc1, vc1, H, Hkv, D)
-        out1 = torch.empty_like(q1)
-        K().decode_attention(ctx, q1, kc1, vc1, out1, table, H, Hkv, D, ps, scale, window)
-        assert (out1.float().cpu() - want).abs().max() <= TOL["bfloat16"]
-        if not K().decode_attention_takes(D, ps):
-            return
-        # one launch from the product
-        for _ in range(2):
-            kc2, vc2 = case.kc.clone(), case.vc.clone()
-            out2 = torch.full_like(q1, 7.0)
-            K().decode_attention_fused(ctx, src, bias_d, inv_d, rot, kc2, vc2, True, out2, table, H, Hkv,
-                                       D, ps, scale, window)
-            assert K().decode_attention_status(D, reset=True) == 0, "a bounded wait in the kernel gave up"
-            assert (out2.float().cpu() - want).abs().max() <= TOL["bfloat16"]
-            for a, b in ((kc2, kc1), (vc2, vc1)):        # at most one bfloat16 step apart, row for row
-                assert ((a.float() - b.float()).abs() <= 2.0 ** -7 * b.float().abs()).all()
-        assert all(int(c.abs().sum()) == 0 for c in kernels_module._decode_counters.values())
-        # a run that reads the cache of another run: the rows are there, nothing is written
-        kc3, vc3 = kc1.clone(), vc1.clone()
-        out3 = torch.full_like(q1, 7.0)
-        K().decode_attention_fused(ctx, src, bias_d, inv_d, rot, kc3, vc3, False, out3, table, H, Hkv, D,
-                                   ps, scale, window)
-        assert K().decode_attention_status(D, reset=True) == 0
-        assert torch.equal(kc3, kc1) and torch.equal(vc3, vc1)
-        assert (out3.float().cpu() - want).abs().max() <= TOL["bfloat16"]
-    finally:
-        kernels_module.decode_ws_force_splits = 0
 
 
 def test_decode_attention_many_launches_of_a_mixed_batch():
@@ -795,33 +705,69 @@ def test_fast_attention_finds_one_far_key(needle):
 
 
 # ------------------------------------------------- weight-streaming product
-@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 32, 40, 64])
-@pytest.mark.parametrize("N,Kd", [(3584, 3584), (4608, 3584), (37888, 1024), (1000, 152), (24, 18944)])
-def test_gemm_skinny(M, N, Kd):
-    x = torch.randn(M, Kd, device=DEV).bfloat16()
-    w = (torch.randn(N, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
-    b = torch.randn(N, device=DEV)
-    want = (x.double() @ w.double().t() + b.double()).float()
-    o32 = torch.full((M, N), 9.0, device=DEV)
-    K().gemm_skinny(x, w, o32, b)
-    assert (o32 - want).abs().max() <= 2e-3
-    ob = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
-    K().gemm_skinny(x, w, ob, None)
-    assert (ob.float() - (want - b)).abs().max() <= 2e-2
-    # deterministic: the same call gives the same bits
-    again = torch.empty(M, N, device=DEV)
-    K().gemm_skinny(x, w, again, b)
-    assert torch.equal(again, o32)
-    # a token's result does not depend on its neighbours in the batch
-    if M >= 2:
-        x2 = x.clone()
-        x2[0] = 0
-        other = torch.empty(M, N, device=DEV)
-        K().gemm_skinny(x2, w, other, b)
-        assert torch.equal(other[1:], o32[1:])
+@pytest.mark.parametrize("D", [48, 64])
+def test_block_table_entries_outside_the_cache_are_skipped_and_reported(D):
+    """A block table can only be wrong through a fault of the host side; the kernels then skip
+    the page (no write, keys read as zeros) and set a status word instead of touching memory
+    outside the pool.  Request 1's second page is given as num_pages + 3; request 0 must come
+    out exactly as without the fault.  Head size 48 takes the mma.sync kernels, 64 the TMA ones."""
+    H, Hkv, ps = 4, 2, 8
+    dt = torch.bfloat16
+    k = K()
+    case = PagedCase([40, 30], [1, 1], H, Hkv, D, ps, dt, seed=D)
+    case.scatter()
+    num_pages = case.kc.shape[0]
+    ctx, q, table = _ctx_for(case)
+    bad = table.clone()
+    bad[1, 1] = num_pages + 3
+    want = case.reference()
+
+    def check(out, what):
+        assert torch.isfinite(out.float()).all(), what
+        assert (out.float().cpu()[0] - want[0]).abs().max() <= TOL["bfloat16"], what
+
+    # plain attention (float32 arithmetic on bfloat16 data)
+    tile_seq, tile_row0, n = ctx.attention_tiles(H // Hkv, k.generic_attention_tile_rows())
+    out = torch.empty_like(q)
+    k.generic_attention_status(reset=True)
+    k.paged_attention_generic(q, case.kc, case.vc, out, bad, ctx.cu_q, ctx.ctx_len, tile_seq, tile_row0,
+                              n, H, Hkv, D, ps, 1 / math.sqrt(D), 0)
+    assert k.generic_attention_status(reset=True) == 1
+    check(out, "generic")
+    # decode kernels: the one-launch kernel where the head size allows it, else the split form
+    for fn, status in ((k.decode_attention, k.decode_attention_status if k.decode_attention_takes(D, ps)
+                        else k.attention_status), (k.decode_attention_split, k.attention_status)):
+        status(D, reset=True)
+        out = torch.empty_like(q)
+        fn(ctx, q, case.kc, case.vc, out, bad, H, Hkv, D, ps, 1 / math.sqrt(D), 0)
+        assert status(D, reset=True) == 0x40, fn.__name__
+        check(out, fn.__name__)
+    # prefill kernels (request 1 as a 2-token portion)
+    pcase = PagedCase([40, 30], [1, 2], H, Hkv, D, ps, dt, seed=D)
+    pcase.scatter()
+    pctx, pq, ptable = _ctx_for(pcase)
+    pbad = ptable.clone()
+    pbad[1, 1] = num_pages + 3
+    out = torch.empty_like(pq)
+    k.prefill_attention(pctx, pq, pcase.kc, pcase.vc, out, pbad, H, Hkv, D, ps, 1 / math.sqrt(D), 0)
+    assert torch.isfinite(out.float()).all()
+    assert (out.float().cpu()[0] - pcase.reference()[0]).abs().max() <= TOL["bfloat16"]
+    if D == 48:
+        assert k.attention_status(D, reset=True) == 0x40
+    # the q/k/v kernel: token 1 (request 1, position 9, second page) is not written
+    kc, vc = _paged(num_pages, Hkv, ps, D, dt)
+    qkv = torch.randn(2, (H + 2 * Hkv) * D, device=DEV).to(dt)
+    q_out = torch.empty(2, H * D, device=DEV, dtype=dt)
+    k.cache_write_status(reset=True)
+    k.qkv_rope_cache(qkv, None, i32([3, 9]), i32([0, 1]), bad, ps, None, 0, q_out, kc, vc, H, Hkv, D)
+    assert k.cache_write_status(reset=True) == 1
+    page0 = int(bad[0, 0])
+    assert float(kc[page0, :, 3].abs().max()) > 0, "the token with a good page is written"
+    kc[page0, :, 3] = 0
+    vc[page0, :, 3] = 0
+    assert float(kc.abs().max()) == 0 and float(vc.abs().max()) == 0, "nothing else is written"
 
 
-# --------------------------------- tcgen05 weight-streaming product (decode)
 @pytest.mark.parametrize("M", [1, 5, 16, 17, 33, 64])
 @pytest.mark.parametrize("N,Kd,splits", [(3584, 3584, 0), (4608, 3584, 4), (37888, 1024, 1),
                                          (1000, 152, 1), (24, 18944, 0), (300, 4096, 16)])
@@ -937,81 +883,6 @@ def test_gemm_tcgen05_qkv_with_rotation_and_cache_write(H, Hkv, D, rot, hidden, 
     K().gemm_tc_qkv_rope(x, w, bias, i32(positions), i32(seq), table, ps, inv, rot, q3, None, None, H, Hkv, D)
     assert torch.equal(q3, q) and float(kc3.abs().max()) == 0
     assert K().gemm_tc_status(True) == 0
-
-
-@pytest.mark.parametrize("M", [1, 7, 16])
-@pytest.mark.parametrize("N,Kd,splits", [(3584, 3584, 0), (3584, 18944, 0), (896, 4864, 0), (200, 1024, 3),
-                                         (72, 128, 1)])
-def test_gemm_tcgen05_into_the_residual_stream(M, N, Kd, splits):
-    """The product whose epilogue adds into the float32 residual stream and leaves the sums
-    of squares per 128-column tile, and the norm built from them: against float64; the
-    LazyNorm's own ``materialize`` against the norm formula."""
-    x = torch.randn(M, Kd, device=DEV).bfloat16()
-    w = (torch.randn(N, Kd, device=DEV) / math.sqrt(Kd)).bfloat16()
-    b = torch.randn(N, device=DEV)
-    resid0 = torch.randn(M, N, device=DEV)
-    want = (resid0.double() + x.double() @ w.double().t() + b.double())
-    resid = resid0.clone()
-    sumsq = K().gemm_tc_resid(x, w, b, resid, splits)
-    assert K().gemm_tc_status(True) == 0, "a bounded wait in the kernel ran out"
-    assert (resid.double() - want).abs().max() <= 1e-3
-    tiles = -(-N // 128)
-    assert sumsq.shape == (tiles, M)
-    for t in range(tiles):
-        sq = (want[:, t * 128:(t + 1) * 128] ** 2).sum(1)
-        assert ((sumsq[t].double() - sq).abs() <= 1e-3 * (1 + sq)).all()
-    again = resid0.clone()
-    sumsq2 = K().gemm_tc_resid(x, w, b, again, splits)
-    assert torch.equal(again, resid) and torch.equal(sumsq2, sumsq)
-    weight = torch.randn(N, device=DEV)
-    lazy = K().LazyNorm(resid, sumsq, weight, 1e-5, torch.bfloat16)
-    normed = (want / torch.sqrt((want ** 2).mean(1, keepdim=True) + 1e-5) * weight.double()).float()
-    assert (lazy.materialize().float() - normed).abs().max() <= 2e-2 * max(1.0, float(normed.abs().max()))
-
-
-@pytest.mark.parametrize("M", [1, 8, 13, 16])
-@pytest.mark.parametrize("hidden,inter", [(3584, 1024), (896, 4864), (520, 640), (72, 128)])
-def test_gemm_tcgen05_products_that_build_their_input_from_the_stream(M, hidden, inter):
-    """The q|k|v product and the gate|up product with the RMS norm of the residual stream as
-    their input, built by the loader warp (last k-block partial: 520 = 8 * 64 + 8): against
-    the same products fed with the norm kernel's result, and against float64."""
-    g = torch.Generator().manual_seed(M + hidden)
-    H_, Hkv, D = 4, 2, 64
-    resid = (torch.randn(M, hidden, generator=g) * 2).to(DEV)
-    weight = (1 + 0.1 * torch.randn(hidden, generator=g)).to(DEV)
-    eps = 1e-6
-    tiles = -(-hidden // 128)
-    sumsq = torch.stack([(resid[:, t * 128:(t + 1) * 128] ** 2).sum(1) for t in range(tiles)]).contiguous()
-    lazy = K().LazyNorm(resid, sumsq, weight, eps, torch.bfloat16)
-    x = torch.empty(M, hidden, device=DEV, dtype=torch.bfloat16)
-    K().add_rmsnorm(resid.clone(), None, weight, eps, x)
-    # gate|up with the activation, rows alternating in runs of 64
-    w_gu = (torch.randn(2 * inter, hidden, generator=g) / math.sqrt(hidden)).bfloat16().to(DEV)
-    a = K().gemm_tc_decode(x, w_gu, None, splits=1, swiglu=True)
-    b = K().gemm_tc_decode(lazy, w_gu, None, splits=1, swiglu=True)
-    assert K().gemm_tc_status(True) == 0, "a bounded wait in the kernel ran out"
-    y = (x.double() @ w_gu.double().t()).view(M, inter // 64, 2, 64)
-    want = (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(M, inter).float()
-    assert (a.float() - want).abs().max() <= 2e-2 * max(1.0, float(want.abs().max()))
-    assert (b.float() - a.float()).abs().max() <= 2e-2 * max(1.0, float(want.abs().max()))
-    # q|k|v with rotation and cache write
-    width = (H_ + 2 * Hkv) * D
-    w = (torch.randn(width, hidden, generator=g) / math.sqrt(hidden)).bfloat16().to(DEV)
-    bias = torch.randn(width, generator=g).to(DEV)
-    inv = P.rope_inv_freq(D, 10000.0).to(DEV)
-    ps = 4
-    positions = torch.randperm(40, generator=g)[:M].tolist()
-    table = i32([list(range(10))])
-    seq = [0] * M
-    outs = []
-    for src in (x, lazy):
-        q = torch.full((M, H_ * D), 7.0, device=DEV, dtype=torch.bfloat16)
-        kc, vc = _paged(10, Hkv, ps, D, torch.bfloat16)
-        K().gemm_tc_qkv_rope(src, w, bias, i32(positions), i32(seq), table, ps, inv, D, q, kc, vc, H_, Hkv, D)
-        outs.append((q, kc, vc))
-    assert K().gemm_tc_status(True) == 0
-    for u, v in zip(outs[0], outs[1]):
-        assert (u.float() - v.float()).abs().max() <= 4e-2
 
 
 def test_kernel_bench_program_runs_on_small_cases(capsys):

@@ -185,19 +185,24 @@ def _register_toy():
         def load(self, store):
             self.gain = store.get(self.prefix + ".gain")
 
+        # forward() launches kernels on the step's device buffers only and reads nothing of
+        # the batch on the host: a decode step with this mixer can be captured in a CUDA graph
+        graph_safe = True
+
         def forward(self, ctx, x, cache, owns_cache):
-            out = torch.empty_like(x)
-            t0 = 0
-            for n, slot in zip(ctx.q_lens, ctx.state_slot_ids):
-                st = cache.state[slot]
-                sums = st[:-1] + torch.cumsum(x[t0:t0 + n].float(), 0)
-                counts = st[-1] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
-                out[t0:t0 + n] = (sums / counts[:, None] * self.gain).to(x.dtype)
-                if owns_cache:
-                    st[:-1] = sums[-1]
-                    st[-1] = counts[-1]
-                t0 += n
-            return out
+            slots, seq = ctx.state_slots.long(), ctx.seq_of_token.long()
+            first = ctx.cu_q[:-1].long()                       # a request's first token of the step
+            last = ctx.cu_q[1:].long() - 1
+            xf = x.float()
+            csum = torch.cumsum(xf, 0)                         # over the packed tokens of all requests
+            before = (csum[first] - xf[first])[seq]            # ... up to the request's own first token
+            state = cache.state[slots]                         # [S, hidden + 1]
+            sums = state[:, :-1][seq] + csum - before
+            index = torch.arange(x.shape[0], device=x.device) - first[seq] + 1
+            counts = state[:, -1][seq] + index.float()
+            if owns_cache:
+                cache.state[slots] = torch.cat([sums[last], counts[last, None]], 1)
+            return (sums / counts[:, None] * self.gain).to(x.dtype)
 
     class ToyConfig:
         architecture = "ToyStateForCausalLM"
@@ -298,6 +303,30 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype, tmp_path):
                 assert err <= TOL[dtype] * 2, (rid, pos, err)
         sess.cache.check_invariants()
         assert sess.cache.slots.num_free() == 2
+
+
+def test_toy_mixer_with_state_decodes_through_replayed_graphs(tmp_path):
+    """The stateful mixer declares itself graph-safe like every other part: steps of single
+    tokens replay a captured graph (the state is indexed by the step's slot ids on the
+    device), and the logits are those of the eager steps.  Two requests, so that the second
+    takes a slot the first has used."""
+    _register_toy()
+    from servelab_b200.config import config_from_dict
+    from servelab_b200.replay import TraceSession
+    from servelab_b200.weights import write_random_model
+    folder = write_random_model(str(tmp_path / "toy"), config_from_dict(TOY), seed=5)
+    reqs = {f"t{i}": H.random_ids(n, 130, 70 + i) for i, n in enumerate([44, 39])}
+    ref = {rid: _toy_plain(folder, ids) for rid, ids in reqs.items()}
+    steps = H.trace_bulk_tail(reqs, tail=20)
+    for dtype in ("float32", "bfloat16"):
+        sess = TraceSession(folder, dtype, H.peak_tokens(steps), page_size=8, max_live=1, cuda_graphs=True)
+        assert sess.runner.storage.state_layers == [1] and sess.runner._graph_safe
+        got = H.collect(steps, H.run_session(sess, steps), 130)
+        assert sess.runner.graph_replays == 40
+        for rid, ids in reqs.items():
+            for pos in range(len(ids)):
+                err = float(np.abs(got[rid][pos] - ref[rid][pos]).max())
+                assert err <= TOL[dtype] * 2, (dtype, rid, pos, err)
 
 
 # --------------------------------------------------------------------------- #
@@ -529,8 +558,7 @@ def test_split_sums_consumed_by_norm_and_rope_kernels(tmp_path):
     """The ways a decode step sums the K splits of its narrow products: a reduction kernel,
     float32 partial sums that the norm / rotary kernels add (``defer_split_sums``), and
     thread-block clusters that add them through shared memory, with and without the
-    rotation and cache write in the q|k|v product's epilogue, and with the residual add in
-    the o and down products and the norms inside the products that follow them.  Logits must agree with the
+    rotation and cache write in the q|k|v product's epilogue.  Logits must agree with the
     plain implementation and with one another whichever runs."""
     from servelab_b200.ops import kernels as kernels_module
     from servelab_b200.ops import linear as linear_ops
@@ -541,15 +569,12 @@ def test_split_sums_consumed_by_norm_and_rope_kernels(tmp_path):
     reqs = {"a": H.random_ids(40, 512, 1), "b": H.random_ids(37, 512, 2)}
     steps = H.trace_bulk_tail(reqs, tail=16)
     outs = {}
-    saved = (dict(linear_ops.defer_split_sums), linear_ops.cluster_sums, linear_ops.fuse_qkv_rope,
-             linear_ops.fuse_resid_norm)
-    modes = {"reduce": (False, False, False, False), "parts": (True, False, False, False),
-             "cluster": (True, True, False, False), "cluster+rope": (True, True, True, False),
-             "five kernels": (True, True, True, True)}
-    for name, (defer, cluster, rope, resid_norm) in modes.items():
+    saved = (dict(linear_ops.defer_split_sums), linear_ops.cluster_sums, linear_ops.fuse_qkv_rope)
+    modes = {"reduce": (False, False, False), "parts": (True, False, False),
+             "cluster": (True, True, False), "cluster+rope": (True, True, True)}
+    for name, (defer, cluster, rope) in modes.items():
         linear_ops.defer_split_sums.update(rope=defer, norm=defer)
         linear_ops.cluster_sums, linear_ops.fuse_qkv_rope = cluster, rope
-        linear_ops.fuse_resid_norm = resid_norm
         try:
             before = kernels_module.launch_count
             sess = TraceSession(folder, "bfloat16", H.peak_tokens(steps), page_size=8, max_live=2)
@@ -558,14 +583,217 @@ def test_split_sums_consumed_by_norm_and_rope_kernels(tmp_path):
         finally:
             linear_ops.defer_split_sums.update(saved[0])
             linear_ops.cluster_sums, linear_ops.fuse_qkv_rope = saved[1], saved[2]
-            linear_ops.fuse_resid_norm = saved[3]
     assert kernels_module.gemm_tc_status(True) == 0
     # fewer kernels run, form by form
     assert outs["reduce launches"] > outs["parts launches"] >= outs["cluster launches"] \
-        > outs["cluster+rope launches"] > outs["five kernels launches"]
+        > outs["cluster+rope launches"]
     ref = {rid: H.plain_logits(folder, ids) for rid, ids in reqs.items()}
     for name in modes:
         for rid, ids in reqs.items():
             for pos in range(len(ids)):
                 assert float(np.abs(outs[name][rid][pos] - ref[rid][pos]).max()) <= 3e-2, name
                 assert float(np.abs(outs[name][rid][pos] - outs["reduce"][rid][pos]).max()) <= 2e-2, name
+
+
+# --------------------------------------------------------------------------- #
+# a position encoding that acts on q and k and is no rotation, defined in this test
+# --------------------------------------------------------------------------- #
+
+def _register_qk_positions():
+    from servelab_b200.config import (AttentionSpec, BlockSpec, GatedMLPSpec, LayerRun, ModelSpec,
+                                      PartSpec, RMSNormSpec, register_architecture)
+    from servelab_b200.parts import POSITIONS, PositionEncoding, register_position
+
+    if "toy_position_gain" in POSITIONS:
+        return
+
+    @dataclass(frozen=True)
+    class GainSpec(PartSpec):
+        kind: str = "toy_position_gain"
+        head_dim: int = 0
+
+    @register_position("toy_position_gain")
+    class PositionGain(PositionEncoding):
+        """q and k are multiplied, element by element, by 1 + 0.5 sin(position * f_d): an
+        encoding inside the scores that is no rotation, so it cannot ride in the mixer's
+        rotary kernel and uses the ``apply_to_qk`` seam instead."""
+        transforms_qk = True
+        graph_safe = True
+
+        def __init__(self, spec, prefix, env):
+            super().__init__(spec, prefix, env)
+            self.freq = (0.3 + 0.05 * torch.arange(spec.head_dim, dtype=torch.float32)).to(env.device)
+
+        def apply_to_qk(self, ctx, q, k):
+            gain = 1.0 + 0.5 * torch.sin(ctx.positions.float()[:, None] * self.freq[None, :])   # [T, D]
+            q.mul_(gain[:, None, :].to(q.dtype))
+            k.mul_(gain[:, None, :].to(k.dtype))
+
+    class ToyGainConfig:
+        architecture = "ToyGainForCausalLM"
+
+        def __init__(self, d):
+            self.d = dict(d)
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+        def to_dict(self):
+            return dict(self.d, architectures=[self.architecture])
+
+        def to_model_spec(self):
+            hid = self.d["hidden_size"]
+            norm = RMSNormSpec(dim=hid, eps=1e-5)
+            attn = AttentionSpec(hidden_size=hid, num_heads=4, num_kv_heads=2, head_dim=hid // 4,
+                                 qkv_bias=True, position=GainSpec(head_dim=hid // 4))
+            block = BlockSpec(mixer=attn, feed_forward=GatedMLPSpec(hidden_size=hid, intermediate_size=80),
+                              mixer_norm=norm, ff_norm=norm)
+            return ModelSpec(architecture=self.architecture, hidden_size=hid, vocab_size=self.d["vocab_size"],
+                             layers=(block, block), run_order=(LayerRun(0), LayerRun(1)), final_norm=norm,
+                             tie_word_embeddings=True, max_position_embeddings=128)
+
+    register_architecture(ToyGainConfig.architecture, ToyGainConfig)
+
+
+def _toy_gain_plain(folder, ids):
+    _, w = P.load_folder(folder)
+    T, hid, Hq, Hkv, D = len(ids), 64, 4, 2, 16
+    gain = 1.0 + 0.5 * torch.sin(torch.arange(T).float()[:, None] * (0.3 + 0.05 * torch.arange(D).float())[None, :])
+    x = P.embed(torch.tensor(ids), w["model.embed_tokens.weight"])
+    for layer in range(2):
+        p = f"model.layers.{layer}."
+        h = P.rms_norm(x, w[p + "input_layernorm.weight"], 1e-5)
+        q = P.linear(h, w[p + "self_attn.q_proj.weight"], w[p + "self_attn.q_proj.bias"]).view(T, Hq, D)
+        k = P.linear(h, w[p + "self_attn.k_proj.weight"], w[p + "self_attn.k_proj.bias"]).view(T, Hkv, D)
+        v = P.linear(h, w[p + "self_attn.v_proj.weight"], w[p + "self_attn.v_proj.bias"]).view(T, Hkv, D)
+        a = P.causal_attention(q * gain[:, None, :], k * gain[:, None, :], v)
+        x = x + P.linear(a, w[p + "self_attn.o_proj.weight"])
+        x = x + P.swiglu(P.rms_norm(x, w[p + "post_attention_layernorm.weight"], 1e-5),
+                         w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                         w[p + "mlp.down_proj.weight"])
+    return P.linear(P.rms_norm(x, w["model.norm.weight"], 1e-5), w["model.embed_tokens.weight"]).numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_position_encoding_inside_the_scores_that_is_no_rotation(dtype, tmp_path):
+    _register_qk_positions()
+    from servelab_b200.config import config_from_dict
+    from servelab_b200.replay import TraceSession
+    from servelab_b200.weights import write_random_model
+    cfg = {"architectures": ["ToyGainForCausalLM"], "hidden_size": 64, "vocab_size": 110}
+    folder = write_random_model(str(tmp_path / "gain"), config_from_dict(cfg), seed=21,
+                                std_of={"q_proj.weight": 0.15, "k_proj.weight": 0.15})
+    reqs = {f"g{i}": H.random_ids(n, 110, 30 + i) for i, n in enumerate([45, 61])}
+    ref = {rid: _toy_gain_plain(folder, ids) for rid, ids in reqs.items()}
+    for steps in (H.trace_whole(reqs), H.trace_mixed(reqs, seed=6, max_live=2, tail=12)):
+        sess = TraceSession(folder, dtype, H.peak_tokens(steps), page_size=8, max_live=2,
+                            cuda_graphs=True)
+        got = H.collect(steps, H.run_session(sess, steps), 110)
+        for rid, ids in reqs.items():
+            for pos in range(len(ids)):
+                err = float(np.abs(got[rid][pos] - ref[rid][pos]).max())
+                assert err <= (1e-4 if dtype == "float32" else 5e-2), (rid, pos, err)
+
+
+# --------------------------------------------------------------------------- #
+# an architecture with the same parts under other tensor names, an embedding scale
+# and transformed logits: a config class alone, nothing else
+# --------------------------------------------------------------------------- #
+
+_RENAMED_LAYER = {"input_layernorm": "ln_1", "self_attn": "attn", "post_attention_layernorm": "ln_2",
+                  "mlp": "ffn", "q_proj": "wq", "k_proj": "wk", "v_proj": "wv", "o_proj": "wo",
+                  "gate_proj": "w1", "up_proj": "w3", "down_proj": "w2"}
+_EMBED_SCALE, _LOGIT_SCALE, _SOFTCAP = 6.0, 0.5, 0.8
+
+
+def _register_renamed():
+    from servelab_b200.config import (AttentionSpec, BlockSpec, GatedMLPSpec, LayerRun, ModelSpec,
+                                      RMSNormSpec, RotarySpec, register_architecture,
+                                      registered_architectures)
+    if "ToyRenamedForCausalLM" in registered_architectures():
+        return
+
+    class ToyRenamedConfig:
+        architecture = "ToyRenamedForCausalLM"
+
+        def __init__(self, d):
+            self.d = dict(d)
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+        def to_dict(self):
+            return dict(self.d, architectures=[self.architecture])
+
+        def to_model_spec(self):
+            d, n = self.d, _RENAMED_LAYER
+            hid, D = d["hidden_size"], d["head_dim"]
+            norm = RMSNormSpec(dim=hid, eps=d["eps"])
+            attn = AttentionSpec(hidden_size=hid, num_heads=d["heads"], num_kv_heads=d["kv_heads"], head_dim=D,
+                                 qkv_bias=True, position=RotarySpec(head_dim=D, rotary_dim=D, theta=d["theta"]),
+                                 q_name=n["q_proj"], k_name=n["k_proj"], v_name=n["v_proj"], o_name=n["o_proj"])
+            ff = GatedMLPSpec(hidden_size=hid, intermediate_size=d["intermediate_size"],
+                              gate_name=n["gate_proj"], up_name=n["up_proj"], down_name=n["down_proj"])
+            block = BlockSpec(mixer=attn, feed_forward=ff, mixer_norm=norm, ff_norm=norm,
+                              mixer_norm_name=n["input_layernorm"], mixer_name=n["self_attn"],
+                              ff_norm_name=n["post_attention_layernorm"], feed_forward_name=n["mlp"])
+            L = d["layers"]
+            return ModelSpec(architecture=self.architecture, hidden_size=hid, vocab_size=d["vocab_size"],
+                             layers=(block,) * L, run_order=tuple(LayerRun(i) for i in range(L)),
+                             final_norm=norm, tie_word_embeddings=False, max_position_embeddings=256,
+                             embed_name="transformer.wte.weight", lm_head_name="output.weight",
+                             final_norm_prefix="transformer.ln_f", layer_prefix="transformer.h.{}",
+                             embedding_scale=_EMBED_SCALE, logit_scale=_LOGIT_SCALE, logit_softcap=_SOFTCAP)
+
+    register_architecture(ToyRenamedConfig.architecture, ToyRenamedConfig)
+
+
+def _renamed_plain(folder, cfg, ids):
+    """The plain Qwen2 implementation on the same tensors under its own names, with the scaled
+    embedding table; then the logit transform."""
+    _, w = P.load_folder(folder)
+    back = {v: k for k, v in _RENAMED_LAYER.items()}
+    renamed = {}
+    for name, t in w.items():
+        parts = name.split(".")
+        if parts[0] == "transformer" and parts[1] == "h":
+            renamed[".".join(["model", "layers", parts[2]] + [back.get(p, p) for p in parts[3:]])] = t
+    renamed["model.embed_tokens.weight"] = w["transformer.wte.weight"] * _EMBED_SCALE
+    renamed["model.norm.weight"] = w["transformer.ln_f.weight"]
+    renamed["lm_head.weight"] = w["output.weight"]
+    qcfg = {"num_hidden_layers": cfg["layers"], "hidden_size": cfg["hidden_size"],
+            "num_attention_heads": cfg["heads"], "num_key_value_heads": cfg["kv_heads"],
+            "head_dim": cfg["head_dim"], "rms_norm_eps": cfg["eps"], "rope_theta": cfg["theta"],
+            "tie_word_embeddings": False}
+    logits = P.forward_logits(qcfg, renamed, ids) * _LOGIT_SCALE
+    return (_SOFTCAP * torch.tanh(logits / _SOFTCAP)).numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_an_architecture_with_other_tensor_names_and_scales_is_a_config_class_alone(dtype, tmp_path):
+    _register_renamed()
+    from servelab_b200.config import config_from_dict
+    from servelab_b200.models import declare_tensors
+    from servelab_b200.replay import TraceSession
+    from servelab_b200.weights import write_random_model
+    cfg = {"architectures": ["ToyRenamedForCausalLM"], "hidden_size": 64, "head_dim": 16, "heads": 4,
+           "kv_heads": 2, "intermediate_size": 128, "vocab_size": 150, "layers": 2, "eps": 1e-5,
+           "theta": 10000.0}
+    config = config_from_dict(cfg)
+    names = {d.name for d in declare_tensors(config.to_model_spec())}
+    assert "transformer.h.1.attn.wk.bias" in names and "transformer.h.0.ffn.w3.weight" in names
+    assert "transformer.wte.weight" in names and "output.weight" in names
+    assert not any("self_attn" in n or "mlp" in n or n.startswith("model.") for n in names)
+    folder = write_random_model(str(tmp_path / "renamed"), config, seed=31, std_of={"output.weight": 0.3})
+    reqs = {f"n{i}": H.random_ids(n, 150, 40 + i) for i, n in enumerate([52, 47])}
+    ref = {rid: _renamed_plain(folder, cfg, ids) for rid, ids in reqs.items()}
+    assert max(float(np.abs(r).max()) for r in ref.values()) > 0.5 * _SOFTCAP, "the cap must bite"
+    for steps in (H.trace_whole(reqs), H.trace_bulk_tail(reqs, tail=12)):
+        sess = TraceSession(folder, dtype, H.peak_tokens(steps), page_size=16, max_live=2, cuda_graphs=True)
+        got = H.collect(steps, H.run_session(sess, steps), 150)
+        for rid, ids in reqs.items():
+            for pos in range(len(ids)):
+                err = float(np.abs(got[rid][pos] - ref[rid][pos]).max())
+                assert err <= (2e-5 if dtype == "float32" else 3e-2), (rid, pos, err)

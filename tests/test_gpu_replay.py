@@ -1,5 +1,7 @@
 """Trace replay against the plain implementation: whole, bulk + tail, portions,
-mixed with page reuse -- in float32 and bfloat16, for three tiny configurations."""
+mixed with page reuse -- in float32 and bfloat16, for five tiny configurations.  Every
+session runs with a poisoned cache: slots that no request has written hold a huge
+value, so a kernel that reads beyond a context or into a page's past shows in the logits."""
 
 import json
 import os
@@ -16,12 +18,22 @@ pytestmark = pytest.mark.gpu
 
 # Largest absolute logit error allowed against the float32 plain implementation.
 # float32: rounding of a handful of float32 reductions.  bfloat16: inputs of
-# every matrix product and the cache are rounded to 8 bits of mantissa.
+# every matrix product and the cache are rounded to 8 bits of mantissa; the bound of
+# a configuration is about twice the worst error its tests print (logits of A-D have a
+# standard deviation near 0.2, those of E, whose attention is peaked, near 1.2).
 TOL = {"float32": 1e-5, "bfloat16": 2e-2}
+TOL_BF16 = {"A": 1.2e-2, "B": 1.2e-2, "C": 1.2e-2, "D": 1.2e-2, "E": 1.5e-1}
+TOL_F32 = {"E": 5e-5}
 LENGTHS = [70, 45, 97, 33, 58, 81]
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
+def tol(model, dtype):
+    if dtype == "bfloat16":
+        return TOL_BF16[model["name"]]
+    return TOL_F32.get(model["name"], TOL["float32"])
+
+
+@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E"])
 def model(request, tmp_path_factory):
     cfg, seed, page = H.CONFIGS[request.param]
     folder = str(tmp_path_factory.mktemp(f"tiny_{request.param}"))
@@ -35,7 +47,8 @@ def model(request, tmp_path_factory):
 
 def _session(model, dtype, max_tokens):
     from servelab_b200.replay import TraceSession
-    return TraceSession(model["folder"], dtype, max_tokens, page_size=model["page"], max_live=4)
+    return TraceSession(model["folder"], dtype, max_tokens, page_size=model["page"], max_live=4,
+                        poison_cache=True)
 
 
 def _check(model, dtype, steps, max_tokens=None):
@@ -51,8 +64,8 @@ def _check(model, dtype, steps, max_tokens=None):
         for pos in range(len(ids)):
             err = float(np.abs(got[rid][pos] - model["ref"][rid][pos]).max())
             assert np.isfinite(err)
-            assert err <= TOL[dtype], (f"config {model['name']} {dtype} request {rid}: first "
-                                       f"wrong position {pos} (err {err:.3e})")
+            assert err <= tol(model, dtype), (f"config {model['name']} {dtype} request {rid}: first "
+                                              f"wrong position {pos} (err {err:.3e})")
             worst = max(worst, err)
     print(f"config {model['name']} {dtype}: worst abs logit error {worst:.3e}")
     return got
@@ -82,20 +95,6 @@ def test_mixed_with_page_reuse(model, dtype):
     _check(model, dtype, steps, need)
 
 
-def test_decode_steps_that_start_from_the_qkv_product(model):
-    """The optional form of a decode step in which the attention kernel adds bias, rotates
-    and writes the cache itself (head sizes the one-launch decode kernel takes)."""
-    if model["name"] != "D":
-        pytest.skip("needs a head size that is a multiple of 64")
-    from servelab_b200.ops import attention as A
-    A.fuse_decode_qkv = True
-    try:
-        _check(model, "bfloat16", H.trace_bulk_tail(model["requests"]))
-        _check(model, "bfloat16", H.trace_mixed(model["requests"], seed=11))
-    finally:
-        A.fuse_decode_qkv = False
-
-
 def test_float32_cut_invariance(model):
     """In float32 the logits of a position are bit-identical however the tokens are cut."""
     a = _check(model, "float32", H.trace_whole(model["requests"]))
@@ -122,7 +121,42 @@ def test_long_decode_and_first_tokens(model, dtype):
     got = H.collect(steps, H.run_session(sess, steps), cfg["vocab_size"])["x"]
     for pos in range(n):
         err = float(np.abs(got[pos] - ref[pos]).max())
-        assert err <= TOL[dtype], f"first wrong position {pos} (err {err:.3e})"
+        assert err <= tol(model, dtype), f"first wrong position {pos} (err {err:.3e})"
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_long_request_whose_decode_steps_split_the_keys(model, graphs):
+    """Configuration E only (head size 128, positions to 1280): a request of 1,150 tokens, most
+    of it in one step, the last 40 one by one -- every decoded token sits beyond 768 keys, where
+    the one-launch decode kernel splits a request over several blocks and the block that
+    arrives last combines them; with ``graphs`` the steps replay a captured graph whose launch
+    is sized for the longest request the engine admits.  The peaked attention of E makes a
+    key that a split loses or counts twice visible in the logits."""
+    if model["name"] != "E":
+        pytest.skip("needs a position limit beyond 768 and a head size the kernel takes")
+    from servelab_b200.ops import kernels as K
+    from servelab_b200.replay import TraceSession
+    cfg = model["cfg"]
+    n = 1150
+    ids = H.random_ids(n, cfg["vocab_size"], 4711)
+    ref = H.plain_logits(model["folder"], ids)
+    steps = H.trace_bulk_tail({"long": ids}, tail=40)
+    steps[0]["entries"][0]["want"] = list(range(n - 40 - 8, n - 40))     # the last rows of the bulk
+    K.decode_attention_splits_used(cfg["head_dim"], reset=True)
+    sess = TraceSession(model["folder"], "bfloat16", H.peak_tokens(steps), page_size=model["page"],
+                        max_live=2, poison_cache=True, cuda_graphs=graphs)
+    got = H.collect(steps, H.run_session(sess, steps), cfg["vocab_size"])["long"]
+    assert K.decode_attention_splits_used(cfg["head_dim"], reset=True) > 1, "no decode step was split"
+    assert K.decode_attention_status(cfg["head_dim"], reset=True) == 0
+    if graphs:
+        assert sess.runner.graph_replays >= 39
+    worst = 0.0
+    for pos in sorted(got):
+        err = float(np.abs(got[pos] - ref[pos]).max())
+        assert err <= tol(model, "bfloat16"), f"first wrong position {pos} (err {err:.3e})"
+        worst = max(worst, err)
+    assert sorted(got) == list(range(n - 48, n))
+    print(f"config E bfloat16 long request (graphs={graphs}): worst abs logit error {worst:.3e}")
 
 
 def test_trace_run_program(model, tmp_path):
@@ -148,4 +182,4 @@ def test_trace_run_program(model, tmp_path):
     got = H.collect(steps, outputs, V)
     for rid, ids in reqs.items():
         for pos in range(len(ids)):
-            assert np.abs(got[rid][pos] - model["ref"][rid][pos]).max() <= TOL["float32"]
+            assert np.abs(got[rid][pos] - model["ref"][rid][pos]).max() <= tol(model, "float32")

@@ -34,6 +34,9 @@ def _definitions():
             if len(named) != len(plist):
                 continue                                    # the stub of a head size that has no kernel
             out.setdefault(m.group(1), plist)
+        # a status word with its accessor `int fn(int reset)`, defined through the macro of common.cuh
+        for m in re.finditer(r"^SLB_DEFINE_STATUS_WORD\(\s*\w+\s*,\s*(slb_\w+)\s*\)", text, re.M):
+            out.setdefault(m.group(1), ["int reset"])
     return out
 
 
