@@ -121,7 +121,8 @@ def reference_arm() -> int:
 TUNABLES = """tc_max_tokens tc_wide_max_tokens cluster_max_kblocks cluster_long_k_max_tokens (ints,
 ops.linear); defer_rope defer_norm fuse_swiglu cluster_sums fuse_qkv_rope (0/1, ops.linear); tc_max_stages
 tc_blocks_per_sm decode_ctas_per_sm decode_ws_stages decode_ws_force_splits decode_ws_unsplit_tiles
-tc_max_cluster (ints, ops.kernels); decode_ws_split_coef (float); use_tc_prefill pdl pdl_early (0/1)"""
+tc_max_cluster (ints, ops.kernels); decode_ws_split_coef (float); use_tc_prefill decode_ws_cluster pdl
+pdl_early (0/1)"""
 
 
 def apply_tunables(items):
@@ -143,8 +144,8 @@ def apply_tunables(items):
             K.TC_MAX_CLUSTER = int(value)
         elif name == "decode_ws_split_coef":
             K.decode_ws_split_coef = float(value)
-        elif name == "use_tc_prefill":
-            K.use_tc_prefill = bool(int(value))
+        elif name in ("use_tc_prefill", "decode_ws_cluster"):
+            setattr(K, name, bool(int(value)))
         elif name == "pdl":
             kernel_library.set_pdl(bool(int(value)))
         elif name == "pdl_early":
@@ -171,6 +172,10 @@ def main(argv=None) -> int:
                     help="measurement aid: set a dispatch tunable: " + TUNABLES)
     ap.add_argument("--profile-region", action="store_true",
                     help="profiling aid: cudaProfilerStart/Stop around the device-timed region")
+    ap.add_argument("--timeline", default="", metavar="FILE",
+                    help="measurement aid: record when every block of the decode kernels started, got "
+                         "past its wait for the preceding kernel and ended (the device's own timer) "
+                         "for one replayed step; rows per launch to FILE (JSON), the first to stderr")
     ap.add_argument("--profile-steps", type=int, default=0, metavar="N",
                     help="also run N decode steps and one prefill eagerly with a CUDA event after "
                          "every kernel and print the per-kernel table (stderr; 'step_profile' in the line)")
@@ -192,6 +197,11 @@ def main(argv=None) -> int:
     from servelab_b200.ops.profile import StepProfile
     from servelab_b200.sampling import SamplingParams
     apply_tunables(args.tune)
+    timeline = None
+    if args.timeline:
+        from servelab_b200.ops.timeline import DeviceTimeline
+        timeline = DeviceTimeline()
+        timeline.__enter__()           # before the graphs are captured: the buffer is a launch argument
 
     cfg = dict(W.SHAPES["qwen2.5-7b"])
     full_layers = cfg["num_hidden_layers"]
@@ -298,6 +308,15 @@ def main(argv=None) -> int:
         per_graph = runner.graph_kernel_launches.get(batch, 0)
         launches = ((K.launch_count - k0) + per_graph * steps * rounds) // rounds
         desc_bytes = runner._graphs[batch][1]._dev.numel() * 4 if batch in runner._graphs else 0
+        if timeline is not None and with_clocks:
+            one_step()
+            timeline.reset()
+            one_step()
+            rows = timeline.launches()
+            with open(args.timeline, "w") as f:
+                json.dump(rows, f)
+            note(f"timeline of one replayed decode step at batch {batch} ({len(rows)} launches; "
+                 f"microseconds):\n" + timeline.render(40))
         check = logit_check(entries)
         profile = None
         if args.profile_steps:

@@ -111,6 +111,20 @@ class CacheStorage:
         for layer in self.state_layers:
             self.layer_caches[layer].state.index_fill_(0, idx, 0.0)
 
+    def snapshot_state(self, slots: Sequence[int]) -> List[torch.Tensor]:
+        """Copies of the state records of ``slots``, one tensor per state layer."""
+        if not self.state_layers or not slots:
+            return []
+        idx = torch.tensor(list(slots), dtype=torch.long, device=self.layer_caches[self.state_layers[0]].state.device)
+        return [self.layer_caches[layer].state.index_select(0, idx) for layer in self.state_layers]
+
+    def restore_state(self, slots: Sequence[int], saved: List[torch.Tensor]) -> None:
+        if not saved:
+            return
+        idx = torch.tensor(list(slots), dtype=torch.long, device=saved[0].device)
+        for layer, copy in zip(self.state_layers, saved):
+            self.layer_caches[layer].state.index_copy_(0, idx, copy)
+
     def poison_pages(self, group: int, pages: Sequence[int]) -> None:
         """Debugging mode: pages that went back to the free list hold ``POISON`` again."""
         if not self.poison or not pages:

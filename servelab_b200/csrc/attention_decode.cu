@@ -22,9 +22,14 @@
 // reference: a head's reference maximum moves only when a score exceeds it by more
 // than 2^8 (checked with one warp vote per slice; no shuffles in the steady state),
 // which changes nothing in exact arithmetic because numerator and denominator use
-// the same reference.  The warps of a block merge through shared memory; splits of
-// one request merge in the block that arrives last on a per-(request, head tile)
-// counter in global memory, so a step needs one launch and no second kernel.
+// the same reference.  The warps of a block merge through shared memory.  The splits of
+// one request merge in one of two ways, both inside the one launch.  With at most eight
+// splits the blocks of a request's (kv head, head tile) are a thread-block cluster: each
+// parks its merged result in its own shared memory and, after a cluster barrier, block r
+// combines a slice of the outputs from all of them through distributed shared memory, in
+// the order of the ranks (no scratch, no counter, no round trip through the L2 cache).
+// With more splits they write partial results to scratch in global memory and the block
+// that arrives last on a per-(request, head tile) counter combines them.
 //
 // Taken: head sizes that are multiples of 64, page sizes that are powers of two from
 // 8 (what a box copy needs); other sizes use the kernel in attention_mma.cu.
@@ -72,6 +77,7 @@ constexpr int TILE_BYTES = PANELS * PANEL_BYTES;           // K or V of one tile
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;                // K tile + V tile
 constexpr int MAX_STAGES = 4;
 constexpr int MAX_SPLITS = 32;
+constexpr int MAX_CLUSTER_SPLITS = 8;      // splits that can form one cluster (the portable size)
 constexpr float LAZY_LOG2 = 8.f;           // the reference moves when exceeded by 2^8
 
 __device__ int dec_status_word = 0;        // 0, or a code of the first wait that gave up (0x10 producer,
@@ -83,6 +89,17 @@ __device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
     unsigned d;
     asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
     return d;
+}
+
+__device__ __forceinline__ void cluster_sync_all_threads() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* mine, uint32_t rank) {
+    uint32_t a;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(mine)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
+    return v;
 }
 
 // Offsets inside a stage.  A page's box lands as [panel][row][64 elements]: key row r
@@ -148,14 +165,15 @@ __device__ __forceinline__ void produce_tile(unsigned char* Kd, unsigned char* V
 // tiles per block.  Scratch (only with num_splits > 1): part_o [S][H][num_splits][D]
 // float32 (unnormalised), part_ml [S][H][num_splits][2] (reference max in the base-2
 // domain, sum), counters [S][Hkv * head_tiles] ints that are zero between launches.
-template <int NH>
+template <int NH, bool CLUSTER>
 __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     const bf16* __restrict__ q, int ldq, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, int ldo,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ ctx_len,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int H,
     int Hkv, int ps, int box_rows, float scale_log2, int window, int num_splits, int head_tiles,
-    int stages, float split_coef, int unsplit_tiles, int num_pages, int pdl_early) {
+    int stages, float split_coef, int unsplit_tiles, int num_pages, int pdl_early,
+    const SlbTraceArg tr) {
     constexpr int HR = 8 * NH;                             // query heads per block
     constexpr int QCH = (HR * CHUNKS + 32 * DW - 1) / (32 * DW);   // 16-byte chunks of Q a consumer thread moves
     extern __shared__ unsigned char smem_raw[];
@@ -163,6 +181,10 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     unsigned char* stage0 = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     bf16* Qs = reinterpret_cast<bf16*>(stage0 + (size_t)stages * STAGE_BYTES);    // [HR][LDS]
     float* red_o = reinterpret_cast<float*>(stage0);       // [DW][registers][32] after the key loop
+    // cluster form: this block's merged result for the other blocks of the cluster to read,
+    // behind red_o: [HR][D] unnormalised sums, then [HR][2] (reference maximum, sum)
+    float* cl_o = red_o + (size_t)DW * (NH * (D / 16) * 4) * 32;
+    float* cl_ml = cl_o + HR * D;
     __shared__ float red_m[DW][HR], red_l[DW][HR];
     __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES];
     __shared__ int failed, issued, last_block;
@@ -195,10 +217,14 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
         use_splits = (total_tiles + per - 1) / per;
         if (use_splits > 8 && use_splits <= 12) use_splits = 8;   // the last block reads eight at a time
     }
-    if (split >= use_splits) return;
+    // (in the cluster form every block stays for the cluster's barriers; one beyond the
+    // request's splits has no tiles)
+    if (!CLUSTER && split >= use_splits) return;
     if (use_splits > 1 && split == 0 && blockIdx.y == 0 && threadIdx.x == 0)
         atomicMax(&dec_splits_used, use_splits);           // what tests read to see that requests were split
+    if (CLUSTER && use_splits == 1 && split > 0) return;   // the whole cluster takes this branch or none
     if (pdl_early) pdl_launch_dependents();
+    if (threadIdx.x == 0) slb_trace_event(tr, 4, SLB_TR_START);
     const int tiles_per_split = (total_tiles + use_splits - 1) / use_splits;
     const int t_begin = split * tiles_per_split;
     const int ntiles = max(0, min(total_tiles, t_begin + tiles_per_split) - t_begin);
@@ -249,6 +275,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     };
     if (warp < burst && !last_tile_in_burst) produce_first();
     pdl_wait();                                            // q and this step's K/V rows
+    if (threadIdx.x == 0) slb_trace_event(tr, 4, SLB_TR_WAITED);
     if (last_tile_in_burst) produce_first();
 
     if (warp == DW) {
@@ -439,6 +466,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     }
     __syncthreads();
     pdl_launch_dependents();
+    if (threadIdx.x == 0) slb_trace_event(tr, 4, SLB_TR_LOOP_DONE);
 
     const bool bad = failed != 0;
     if (bad) {
@@ -447,6 +475,10 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
             for (int tt = max(0, issued - stages); tt < issued; ++tt)
                 mbar_wait(&full_bar[tt % stages], (tt / stages) & 1);
         __syncthreads();
+        if (CLUSTER && tid < HR) {                         // this split counts as empty
+            cl_ml[tid * 2] = -INFINITY;
+            cl_ml[tid * 2 + 1] = 0.f;
+        }
     } else {
         // ---- merge the consumer warps (each saw a quarter of the keys) ----
         // Every warp holds the same fragment of O^T for its own keys: the fragments are
@@ -494,9 +526,14 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
                 }
                 const int head = kvh * g + h0 + hr;
                 if (use_splits > 1 && hr < nrows && (warp * RPW) % (MT * 4) == 0 && lane < 4) {
-                    const size_t pi = ((size_t)s * H + head) * num_splits + split;
-                    part_ml[pi * 2] = M;
-                    part_ml[pi * 2 + 1] = L[h];
+                    if (CLUSTER) {
+                        cl_ml[hr * 2] = M;
+                        cl_ml[hr * 2 + 1] = L[h];
+                    } else {
+                        const size_t pi = ((size_t)s * H + head) * num_splits + split;
+                        part_ml[pi * 2] = M;
+                        part_ml[pi * 2 + 1] = L[h];
+                    }
                 }
             }
 #pragma unroll
@@ -513,6 +550,8 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
                     if (use_splits == 1) {
                         out[(size_t)s * ldo + (size_t)head * D + d] =
                             __float2bfloat16_rn(L[h] > 0.f ? acc / L[h] : 0.f);
+                    } else if (CLUSTER) {
+                        cl_o[hr * D + d] = acc;
                     } else {
                         part_o[(((size_t)s * H + head) * num_splits + split) * D + d] = acc;
                     }
@@ -520,7 +559,50 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
             }
         }
     }
-    if (use_splits == 1) return;
+    if (use_splits == 1) {
+        if (threadIdx.x == 0) slb_trace_event(tr, 4, SLB_TR_END);
+        return;
+    }
+
+    if constexpr (CLUSTER) {
+        // ---- the blocks of the cluster combine a slice of the outputs each ----
+        cluster_sync_all_threads();                        // every block's result is parked
+        const int total = nrows * D;
+        const int chunk = (total + use_splits - 1) / use_splits;
+        const int stop = min(total, (split + 1) * chunk);
+        if (split < use_splits) {
+            for (int idx = split * chunk + tid; idx < stop; idx += NTHREADS) {
+                const int r = idx / D, d = idx - r * D;
+                // all remote loads first, then the merge in the order of the ranks
+                float mv[8], lv[8], ov[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const bool in = j < use_splits;
+                    mv[j] = in ? ld_cluster_f32(cl_ml + r * 2, (uint32_t)j) : -INFINITY;
+                    lv[j] = in ? ld_cluster_f32(cl_ml + r * 2 + 1, (uint32_t)j) : 0.f;
+                    ov[j] = in ? ld_cluster_f32(cl_o + r * D + d, (uint32_t)j) : 0.f;
+                }
+                float M = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) M = fmaxf(M, mv[j]);
+                float L = 0.f, acc = 0.f;
+                if (M != -INFINITY) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (mv[j] == -INFINITY) continue;  // an empty split
+                        const float f = exp2f(mv[j] - M);
+                        L += lv[j] * f;
+                        acc += ov[j] * f;
+                    }
+                }
+                out[(size_t)s * ldo + (size_t)(kvh * g + h0 + r) * D + d] =
+                    __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+            }
+        }
+        cluster_sync_all_threads();                        // nobody leaves while its result is read
+        if (threadIdx.x == 0) slb_trace_event(tr, 4, SLB_TR_END + 1);
+        return;
+    }
 
     // ---- the block that arrives last combines the splits ----
     // The block barrier orders every thread's partial results before thread 0's release
@@ -535,7 +617,10 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
         if (last_block) *counter = 0;                      // zero again for the next launch
     }
     __syncthreads();
-    if (!last_block) return;
+    if (!last_block) {
+        if (threadIdx.x == 0) slb_trace_event(tr, 4, SLB_TR_END);
+        return;
+    }
     for (int idx = tid; idx < nrows * D; idx += NTHREADS) {
         const int r = idx / D, d = idx - r * D;
         const int head = kvh * g + h0 + r;
@@ -570,6 +655,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
         }
         out[(size_t)s * ldo + (size_t)head * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     }
+    if (threadIdx.x == 0) slb_trace_event(tr, 4, SLB_TR_END + 1);     // end of a block that combined
 }
 
 // dynamic shared memory: 1024 bytes of slack for the alignment, the stages, the Q rows
@@ -578,10 +664,10 @@ constexpr size_t decode_smem(int nh, int stages) {
 }
 constexpr size_t MAX_DYNAMIC_SMEM = 220 * 1024;            // of the 227 KB a block may have
 static_assert(decode_smem(2, 2) <= MAX_DYNAMIC_SMEM, "two stages must fit for every head size");
-static_assert((size_t)DW * 2 * (D / 16) * 4 * 32 * sizeof(float) <= 2 * (size_t)STAGE_BYTES,
-              "the merge buffer lives in the first two stages");
+static_assert(((size_t)DW * 2 * (D / 16) * 4 * 32 + 16 * D + 16 * 2) * sizeof(float) <= 2 * (size_t)STAGE_BYTES,
+              "the merge buffer and the parked result live in the first two stages");
 
-template <int NH>
+template <int NH, bool CLUSTER>
 int launch_decode(const bf16* q, int ldq, const CUtensorMap& map_k, const CUtensorMap& map_v, bf16* out,
                   int ldo, const int* block_table, int max_pages, const int* ctx_len, float* scratch,
                   int* counters, int S, int H, int Hkv, int ps, int box_rows, float scale, int window,
@@ -593,15 +679,36 @@ int launch_decode(const bf16* q, int ldq, const CUtensorMap& map_k, const CUtens
     while (stages > 2 && decode_smem(NH, stages) > MAX_DYNAMIC_SMEM) --stages;
     const size_t smem = decode_smem(NH, stages);
     static unsigned long long configured = 0;              // per instantiation, a bit per device
-    const int rc = slb_configure(&configured, decode_attention_ws_kernel<NH>, MAX_DYNAMIC_SMEM);
+    const int rc = slb_configure(&configured, decode_attention_ws_kernel<NH, CLUSTER>, MAX_DYNAMIC_SMEM);
     if (rc != 0) return rc;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)S * H * num_splits * D : nullptr;
-    return slb_launch(decode_attention_ws_kernel<NH>, dim3(num_splits, Hkv * head_tiles, S),
-                      dim3(NTHREADS), smem, st, q, ldq, map_k, map_v, out, ldo, block_table, max_pages,
-                      ctx_len, part_o, part_ml, counters, H, Hkv, ps, box_rows,
-                      scale * 1.4426950408889634f, window, num_splits, head_tiles, stages, split_coef,
-                      unsplit_tiles, num_pages, slb_pdl_early);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(num_splits, Hkv * head_tiles, S);
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    int nattr = 0;
+    if (CLUSTER) {                                         // the splits of a (request, head tile)
+        attr[nattr].id = cudaLaunchAttributeClusterDimension;
+        attr[nattr].val.clusterDim.x = (unsigned)num_splits;
+        attr[nattr].val.clusterDim.y = 1;
+        attr[nattr].val.clusterDim.z = 1;
+        ++nattr;
+    }
+    if (slb_pdl_enabled) {
+        attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+        ++nattr;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = nattr;
+    return (int)cudaLaunchKernelEx(&cfg, decode_attention_ws_kernel<NH, CLUSTER>, q, ldq, map_k, map_v, out,
+                                   ldo, block_table, max_pages, ctx_len, part_o, part_ml, counters, H, Hkv, ps,
+                                   box_rows, scale * 1.4426950408889634f, window, num_splits, head_tiles,
+                                   stages, split_coef, unsplit_tiles, num_pages, slb_pdl_early,
+                                   slb_trace_arg());
 }
 
 }  // namespace
@@ -635,6 +742,7 @@ int slb_decode_attention_ws_splits_used(int reset) {
     return v;
 }
 int slb_decode_attention_ws_max_splits() { return MAX_SPLITS; }
+int slb_decode_attention_ws_max_cluster_splits() { return MAX_CLUSTER_SPLITS; }
 int slb_decode_attention_ws_tile_keys() { return BN; }
 
 // float32 scratch for the partial results of (S requests, H heads, num_splits)
@@ -660,12 +768,16 @@ int slb_decode_attention_ws_bf16(const bf16* q, int ldq, const bf16* kc, const b
                                  int ldo, const int* block_table, int max_pages, const int* ctx_len,
                                  float* scratch, int* counters, int S, int H, int Hkv, int ps,
                                  int num_pages, float scale, int window, int num_splits, int stages,
-                                 float split_coef, int unsplit_tiles, cudaStream_t st) {
+                                 float split_coef, int unsplit_tiles, int cluster, cudaStream_t st) {
     if (S <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || max_pages <= 0 || num_pages <= 0 || !(scale > 0.f))
         return SLB_ERR_BAD_ARG;
     if (!slb_decode_attention_ws_supported(ps)) return SLB_ERR_BAD_ARG;
-    if (num_splits < 1 || (num_splits > 1 && (scratch == nullptr || counters == nullptr)))
+    // cluster != 0: the splits of a request combine through the shared memory of a thread-block
+    // cluster (at most MAX_CLUSTER_SPLITS of them; scratch and counters are not used)
+    const bool clustered = cluster != 0 && num_splits > 1;
+    if (clustered && num_splits > MAX_CLUSTER_SPLITS) return SLB_ERR_TOO_LARGE;
+    if (num_splits < 1 || (num_splits > 1 && !clustered && (scratch == nullptr || counters == nullptr)))
         return SLB_ERR_BAD_ARG;
     if (stages < 2 || stages > MAX_STAGES || !(split_coef >= 0.f) || unsplit_tiles < 0) return SLB_ERR_BAD_ARG;
     if (((uintptr_t)kc | (uintptr_t)vc) % 16 || ldq % 8 || (uintptr_t)q % 16) return SLB_ERR_BAD_ARG;
@@ -678,11 +790,12 @@ int slb_decode_attention_ws_bf16(const bf16* q, int ldq, const bf16* kc, const b
     if (rc != 0) return rc;
     rc = slb_tma::make_paneled_rows_map(&map_v, vc, D, rows, box_rows);
     if (rc != 0) return rc;
-#define SLB_LAUNCH_DECODE(NH_)                                                                           \
-    launch_decode<NH_>(q, ldq, map_k, map_v, out, ldo, block_table, max_pages, ctx_len, scratch,         \
-                       counters, S, H, Hkv, ps, box_rows, scale, window, num_splits, stages, split_coef, \
-                       unsplit_tiles, num_pages, st)
-    return H / Hkv <= 8 ? SLB_LAUNCH_DECODE(1) : SLB_LAUNCH_DECODE(2);
+#define SLB_LAUNCH_DECODE(NH_, CL_)                                                                      \
+    launch_decode<NH_, CL_>(q, ldq, map_k, map_v, out, ldo, block_table, max_pages, ctx_len, scratch,    \
+                            counters, S, H, Hkv, ps, box_rows, scale, window, num_splits, stages,        \
+                            split_coef, unsplit_tiles, num_pages, st)
+    if (clustered) return H / Hkv <= 8 ? SLB_LAUNCH_DECODE(1, true) : SLB_LAUNCH_DECODE(2, true);
+    return H / Hkv <= 8 ? SLB_LAUNCH_DECODE(1, false) : SLB_LAUNCH_DECODE(2, false);
 #undef SLB_LAUNCH_DECODE
 }
 
@@ -695,12 +808,13 @@ int slb_decode_attention_ws_supported(int) { return 0; }
 int slb_decode_attention_ws_status(int) { return 0; }
 int slb_decode_attention_ws_splits_used(int) { return 0; }
 int slb_decode_attention_ws_max_splits() { return 1; }
+int slb_decode_attention_ws_max_cluster_splits() { return 1; }
 int slb_decode_attention_ws_tile_keys() { return 64; }
 long long slb_decode_attention_ws_scratch_bytes(int, int, int) { return 0; }
 long long slb_decode_attention_ws_counters(int, int, int) { return 0; }
 int slb_decode_attention_ws_bf16(const bf16*, int, const bf16*, const bf16*, bf16*, int, const int*, int,
                                  const int*, float*, int*, int, int, int, int, int, float, int, int, int,
-                                 float, int, cudaStream_t) {
+                                 float, int, int, cudaStream_t) {
     return SLB_ERR_BAD_ARG;
 }
 }

@@ -96,6 +96,44 @@ extern int slb_pdl_enabled;          // defined once per shared library (SLB_DEF
 // theirs wherever an SM has room and fetch their first weight tiles while these still run.
 extern int slb_pdl_early;
 
+// ---- device timeline (measurements) -------------------------------------------
+// With a buffer set (slb_set_trace), one thread of every block of the decode-step kernels
+// records when the block started, when its wait for the preceding kernel returned, when its
+// main loop was done and when it ended: the nanosecond timer of the device and the SM's
+// number.  Every (launch, block, event) has a slot of its own, so recording is two plain
+// stores and no atomic operation delays the thread that records:
+//   slot = ((seq % SLB_TR_LAUNCHES) * SLB_TR_BLOCKS + block % SLB_TR_BLOCKS) * SLB_TR_EVENTS + event
+//   buf[2 * slot] = timer, buf[2 * slot + 1] = kernel << 48 | event << 40 | sm << 24 | block
+// (blocks beyond SLB_TR_BLOCKS share slots: of a large grid a sample is kept).  Without a
+// buffer the calls cost a predicated branch.
+constexpr int SLB_TR_LAUNCHES = 2048, SLB_TR_PER_LIBRARY = 512, SLB_TR_BLOCKS = 512, SLB_TR_EVENTS = 5;
+struct SlbTraceArg {
+    unsigned long long* buf;
+    int seq;
+};
+extern unsigned long long* slb_trace_ptr;     // host side, per library; null = off
+extern int slb_trace_seq, slb_trace_base;     // launches counted, first launch slot of this library
+static inline SlbTraceArg slb_trace_arg() {
+    SlbTraceArg a;
+    a.buf = slb_trace_ptr;
+    a.seq = slb_trace_ptr != nullptr ? slb_trace_base + slb_trace_seq++ % SLB_TR_PER_LIBRARY : 0;
+    return a;
+}
+enum { SLB_TR_START = 0, SLB_TR_WAITED = 1, SLB_TR_LOOP_DONE = 2, SLB_TR_END = 3 };
+__device__ __forceinline__ void slb_trace_event(const SlbTraceArg& tr, int kernel_id, int event) {
+    if (tr.buf == nullptr) return;
+    unsigned long long now;
+    unsigned smid;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    const unsigned long long block = blockIdx.x + gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z);
+    const size_t slot = ((size_t)(tr.seq % SLB_TR_LAUNCHES) * SLB_TR_BLOCKS + (size_t)(block % SLB_TR_BLOCKS)) *
+                            SLB_TR_EVENTS + (size_t)event;
+    tr.buf[2 * slot] = now;
+    tr.buf[2 * slot + 1] = ((unsigned long long)kernel_id << 48) | ((unsigned long long)event << 40) |
+                           ((unsigned long long)(smid & 0xffff) << 24) | (block & 0xffffff);
+}
+
 // cudaFuncSetAttribute(max dynamic shared memory) once per device for one kernel: `done` is
 // the caller's static word for that kernel (bit d = done on device d); the attribute belongs
 // to the device that is current, so a process that uses several devices sets it on each.
@@ -152,4 +190,13 @@ static inline int slb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
         const int old = slb_pdl_early;                                                \
         slb_pdl_early = on ? 1 : 0;                                                   \
         return old;                                                                   \
+    }                                                                                 \
+    unsigned long long* slb_trace_ptr = nullptr;                                      \
+    int slb_trace_seq = 0;                                                            \
+    int slb_trace_base = 0;                                                           \
+    extern "C" int slb_set_trace(unsigned long long* buf, int library_index) {        \
+        slb_trace_ptr = buf;                                                          \
+        slb_trace_seq = 0;                                                            \
+        slb_trace_base = (library_index % (SLB_TR_LAUNCHES / SLB_TR_PER_LIBRARY)) * SLB_TR_PER_LIBRARY; \
+        return 0;                                                                     \
     }

@@ -73,19 +73,26 @@ __global__ void logit_transform_kernel(float* __restrict__ logits, int ld, int V
 // The sum of squares is accumulated per thread over a strided walk and then
 // reduced over the block; both depend only on h and the block size, never on the
 // batch.  VEC: h % 4 == 0 (all rows then start 16-byte aligned).
+// The partial sums are fetched eight at a time before any is added (the additions keep the
+// order of p): a loop of load-then-add would wait for every load in turn, ten round trips
+// to the L2 cache for a product split ten ways.
 template <typename TD>
 __device__ __forceinline__ float4 delta4(const TD* d, const float* parts, int nparts,
                                          size_t part_stride, const float* pbias, int i) {
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
     if (d) v = load4(d + i);
-    for (int p = 0; p < nparts; ++p) {
-        const float4 q = load4(parts + p * part_stride + i);
-        v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+    if (pbias) b = load4(pbias + i);
+    for (int p0 = 0; p0 < nparts; p0 += 8) {
+        float4 q[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            q[j] = p0 + j < nparts ? __ldcg(reinterpret_cast<const float4*>(parts + (size_t)(p0 + j) * part_stride + i))
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { v.x += q[j].x; v.y += q[j].y; v.z += q[j].z; v.w += q[j].w; }
     }
-    if (pbias) {
-        const float4 q = load4(pbias + i);
-        v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
-    }
+    v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
     return v;
 }
 template <typename TD>
@@ -97,15 +104,33 @@ __device__ __forceinline__ float delta1(const TD* d, const float* parts, int npa
     return v;
 }
 
+// NV: float4 a thread keeps in registers between the two passes (rows of up to 16 * blockDim
+// elements; longer rows are read again in the second pass).
+constexpr int NORM_NV = 4;
+
 template <typename TD, typename TO, bool VEC, bool PARTS>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const float* __restrict__ parts, int nparts, size_t part_stride,
                                    const float* __restrict__ pbias,
                                    const float* __restrict__ weight, TO* __restrict__ out,
-                                   const int* __restrict__ row_map, int h, float eps) {
+                                   const int* __restrict__ row_map, int h, float eps,
+                                   const SlbTraceArg tr) {
     __shared__ float scratch[33];
     pdl_launch_dependents();
+    if (threadIdx.x == 0) slb_trace_event(tr, 5, SLB_TR_START);
+    // the norm weights are written by no kernel: they are fetched while the kernel before
+    // this one still runs
+    const bool in_regs = VEC && h <= (int)blockDim.x * 4 * NORM_NV;
+    float4 wv[NORM_NV];
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < NORM_NV; ++j) {
+            const int i = (threadIdx.x + j * blockDim.x) * 4;
+            wv[j] = i < h ? load4(weight + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     pdl_wait();
+    if (threadIdx.x == 0) slb_trace_event(tr, 5, SLB_TR_WAITED);
     const int r = blockIdx.x;
     const int src = row_map ? row_map[r] : r;
     float* x = resid + (size_t)src * h;
@@ -116,6 +141,45 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
     const bool write_back = (row_map == nullptr) && has_delta;
     TO* o = out + (size_t)r * h;
     float ss = 0.f;
+    if (in_regs) {
+        // one pass over global memory: the row stays in registers between the sum of squares
+        // and the scaling (same order of additions per thread as the two-pass form)
+        float4 xv[NORM_NV];
+#pragma unroll
+        for (int j = 0; j < NORM_NV; ++j) {
+            const int i = (threadIdx.x + j * blockDim.x) * 4;
+            xv[j] = i < h ? load4(x + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (has_delta) {
+#pragma unroll
+            for (int j = 0; j < NORM_NV; ++j) {
+                const int i = (threadIdx.x + j * blockDim.x) * 4;
+                if (i < h) {
+                    const float4 dv = delta4(d, pp, nparts, part_stride, pbias, i);
+                    xv[j].x += dv.x; xv[j].y += dv.y; xv[j].z += dv.z; xv[j].w += dv.w;
+                    if (write_back) store4(x + i, xv[j]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NORM_NV; ++j) {
+            ss += xv[j].x * xv[j].x;
+            ss += xv[j].y * xv[j].y;
+            ss += xv[j].z * xv[j].z;
+            ss += xv[j].w * xv[j].w;
+        }
+        ss = block_sum(ss, scratch);
+        const float rstd = 1.0f / sqrtf(ss / (float)h + eps);
+#pragma unroll
+        for (int j = 0; j < NORM_NV; ++j) {
+            const int i = (threadIdx.x + j * blockDim.x) * 4;
+            if (i < h)
+                store4(o + i, make_float4(xv[j].x * rstd * wv[j].x, xv[j].y * rstd * wv[j].y,
+                                          xv[j].z * rstd * wv[j].z, xv[j].w * rstd * wv[j].w));
+        }
+        if (threadIdx.x == 0) slb_trace_event(tr, 5, SLB_TR_END);
+        return;
+    }
     if (VEC) {
         for (int i = threadIdx.x * 4; i < h; i += blockDim.x * 4) {
             float4 v = load4(x + i);
@@ -157,6 +221,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
             o[i] = from_float<TO>(v * rstd * weight[i]);
         }
     }
+    if (threadIdx.x == 0) slb_trace_event(tr, 5, SLB_TR_END);
 }
 
 // ---- the same norm for an update that arrives as K-split partial sums (decode steps) ----
@@ -195,16 +260,21 @@ __global__ void add_rmsnorm_parts_cluster_kernel(float* __restrict__ resid,
                                                  size_t part_stride, const float* __restrict__ pbias,
                                                  const float* __restrict__ weight, TO* __restrict__ out,
                                                  const int* __restrict__ row_map, int h, int chunk,
-                                                 float eps) {
+                                                 float eps, const SlbTraceArg tr) {
     __shared__ float scratch[33];
     __shared__ float my_ss;
     pdl_launch_dependents();
-    pdl_wait();
+    if (threadIdx.x == 0) slb_trace_event(tr, 6, SLB_TR_START);
     const unsigned rank = cluster_ctarank();
     const int r = blockIdx.y;
-    const int src = row_map ? row_map[r] : r;
     const int i = (int)rank * chunk + threadIdx.x * 4;
     const bool active = (int)threadIdx.x * 4 < chunk && i < h;
+    // the norm weights are written by no kernel: fetched while the kernel before this one runs
+    float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (active) w = load4(weight + i);
+    pdl_wait();
+    if (threadIdx.x == 0) slb_trace_event(tr, 6, SLB_TR_WAITED);
+    const int src = row_map ? row_map[r] : r;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (active) {
         float* x = resid + (size_t)src * h;
@@ -221,17 +291,20 @@ __global__ void add_rmsnorm_parts_cluster_kernel(float* __restrict__ resid,
     if (threadIdx.x == 0) my_ss = ss;
     cluster_arrive();
     cluster_wait();
+    float part[NORM_CLUSTER];                              // all remote loads first, then the sum
+#pragma unroll
+    for (unsigned c = 0; c < NORM_CLUSTER; ++c) part[c] = load_cluster_shared(&my_ss, c);
     float total = 0.f;
 #pragma unroll
-    for (unsigned c = 0; c < NORM_CLUSTER; ++c) total += load_cluster_shared(&my_ss, c);
+    for (unsigned c = 0; c < NORM_CLUSTER; ++c) total += part[c];
     cluster_arrive();                                      // this block has read the others' sums
     const float rstd = 1.0f / sqrtf(total / (float)h + eps);
     if (active) {
-        const float4 w = load4(weight + i);
         store4(out + (size_t)r * h + i, make_float4(v.x * rstd * w.x, v.y * rstd * w.y,
                                                     v.z * rstd * w.z, v.w * rstd * w.w));
     }
     cluster_wait();                                        // nobody still reads this block's sum
+    if (threadIdx.x == 0) slb_trace_event(tr, 6, SLB_TR_END);
 }
 
 // out[t, i] = silu(gate_i) * up_i, silu(z) = z / (1 + exp(-z)), in float32.  Layout of a
@@ -310,7 +383,7 @@ static int launch_add_rmsnorm(float* resid, const TD* delta, const float* parts,
     const bool vec = h % 4 == 0 && part_stride % 4 == 0;
 #define SLB_NORM_LAUNCH(V, P)                                                                   \
     return slb_launch(add_rmsnorm_kernel<TD, TO, V, P>, grid, block, 0, st, resid, delta, parts, \
-                      nparts, (size_t)part_stride, pbias, weight, out, row_map, h, eps)
+                      nparts, (size_t)part_stride, pbias, weight, out, row_map, h, eps, slb_trace_arg())
     if (nparts > 0) {
         if (vec) SLB_NORM_LAUNCH(true, true);
         SLB_NORM_LAUNCH(false, true);
@@ -394,7 +467,8 @@ int slb_add_rmsnorm_parts_bf16(float* resid, const float* parts, int nparts, lon
         cfg.attrs = attr;
         cfg.numAttrs = slb_pdl_enabled ? 2 : 1;
         return (int)cudaLaunchKernelEx(&cfg, add_rmsnorm_parts_cluster_kernel<bf16>, resid, parts, nparts,
-                                       (size_t)part_stride, pbias, weight, out, row_map, h, chunk, eps);
+                                       (size_t)part_stride, pbias, weight, out, row_map, h, chunk, eps,
+                                       slb_trace_arg());
     }
     return launch_add_rmsnorm<bf16, bf16>(resid, nullptr, parts, nparts, part_stride, pbias, weight,
                                           out, row_map, rows, h, eps, st);

@@ -38,6 +38,7 @@ constexpr int TC_MAX_TOK = 64;        // MMA N
 constexpr int TC_MAX_STAGES = 12;     // the ring is as deep as shared memory allows
 constexpr int TC_THREADS = 192;       // warp 0 loader, warp 1 MMA + TMEM, warps 2..5 epilogue
 constexpr int TC_TMEM_COLS = 64;
+constexpr int TC_MAX_CLUSTER = 8;       // K splits of a row tile that can form one cluster (the portable size)
 constexpr uint32_t SLB_TC_SPIN_LIMIT = 1u << 18;
 constexpr int A_STAGE_BYTES = TC_BM * TC_BK * 2;          // 16 KB of W per stage
 constexpr size_t TC_SMEM_BUDGET = 200 * 1024;             // stages + barriers (one block per SM)
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     TO* __restrict__ out, int ldo, float* __restrict__ partial, const float* __restrict__ bias,
     int M, int N, int K, int ntok16, int max_stages, int* __restrict__ status, int swiglu,
-    int pdl_early) {
+    int pdl_early, const SlbTraceArg tr) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -164,6 +165,8 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *tmem_slot;
     if (pdl_early) pdl_launch_dependents();
+    const bool tracer = threadIdx.x == 64;                  // lane 0 of the first epilogue warp
+    if (tracer) slb_trace_event(tr, 1, SLB_TR_START);
 
     if (warp == 0) {
         // ------------------------------------------------------------ loader
@@ -219,6 +222,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
         // ------------------------------------------------------------ epilogue
         pdl_wait();                                          // nothing is written before the
                                                              // preceding kernel has finished
+        if (tracer) slb_trace_event(tr, 1, SLB_TR_WAITED);
         const int quarter = warp & 3;                        // TMEM lanes this warp may read
         const int row = quarter * 32 + lane;                 // row of the tile = row of W
         const int n = n0 + row;
@@ -229,6 +233,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         pdl_launch_dependents();
+        if (tracer) slb_trace_event(tr, 1, SLB_TR_LOOP_DONE);
         if (swiglu) {
             // W holds gate and up rows alternating in runs of 64, so this tile's rows are 64
             // gates and their 64 ups: the upper two warps park the ups in shared memory (the
@@ -290,6 +295,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (tracer) slb_trace_event(tr, 1, SLB_TR_END);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TC_TMEM_COLS)
@@ -365,11 +371,54 @@ __device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank)
     return v;
 }
 
+// What the q|k|v epilogue needs for element n of token tok besides the sum over the K splits:
+// the bias, sine and cosine of the token's rotation, and where the result goes.  None of it
+// depends on the product, so a block computes it for its first token while its main loop runs.
+struct RopeTarget {
+    float bias, sn, cs;
+    bf16* dst;                          // null: nothing is stored (beyond N, no page, no cache)
+    int other;                          // row of the tile that holds the rotation partner
+    bool rotate, first_half;
+};
+__device__ __forceinline__ RopeTarget rope_target(const RopeEpilogue& rope, int tok, int n, int row, int N,
+                                                  int* status) {
+    RopeTarget t;
+    t.bias = 0.f; t.sn = 0.f; t.cs = 1.f; t.dst = nullptr; t.other = row; t.rotate = false; t.first_half = true;
+    if (n >= N) return t;
+    const int D = rope.D;
+    const int half = rope.inv_freq != nullptr ? rope.rotary_dim >> 1 : 0;
+    const int j = n / D, e = n - j * D;
+    const bool is_v = j >= rope.H + rope.Hkv;
+    if (rope.bias) t.bias = rope.bias[n];
+    const int pos = rope.positions[tok];
+    if (!is_v && e < 2 * half) {
+        const int i = e < half ? e : e - half;
+        sincosf((float)pos * rope.inv_freq[i], &t.sn, &t.cs);
+        t.rotate = true;
+        t.first_half = e < half;
+        t.other = e < half ? row + half : row - half;
+    }
+    if (j < rope.H) {
+        t.dst = rope.q_out + (size_t)tok * rope.ld_q + (size_t)j * D + e;
+    } else if (rope.k_cache != nullptr) {
+        const int page = rope.block_table[(size_t)rope.seq_of_token[tok] * rope.max_pages + pos / rope.page_size];
+        if (page >= rope.num_pages) {                          // outside the cache: not written
+            atomicCAS(status, 0, (5 << 8) | 1);
+        } else if (page >= 0) {
+            const int kvh = is_v ? j - rope.H - rope.Hkv : j - rope.H;
+            t.dst = (is_v ? rope.v_cache : rope.k_cache) +
+                    (((size_t)page * rope.Hkv + kvh) * rope.page_size + pos % rope.page_size) * D + e;
+        }
+    }
+    return t;
+}
+
 template <int EPI>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     bf16* __restrict__ out, int ldo, const float* __restrict__ bias, int M, int N, int K, int ntok16,
-    int max_stages, int* __restrict__ status, const RopeEpilogue rope, int pdl_early) {
+    int max_stages, int* __restrict__ status, const RopeEpilogue rope, int pdl_early,
+    const SlbTraceArg tr) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -410,7 +459,11 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *tmem_slot;
     float* acc = reinterpret_cast<float*>(a_stage);          // [ntok16][TC_BM] once the ring is idle
+    RopeTarget first_target = {};                            // EPI_ROPE: for token `rank` of this block
     if (pdl_early) pdl_launch_dependents();
+    const bool tracer = threadIdx.x == 64;                  // lane 0 of the first epilogue warp
+    constexpr int TRACE_ID = EPI == EPI_ROPE ? 3 : 2;
+    if (tracer) slb_trace_event(tr, TRACE_ID, SLB_TR_START);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -462,8 +515,12 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     } else {
         // ------------------------------------------ epilogue, part 1: accumulator -> acc
         pdl_wait();
+        if (tracer) slb_trace_event(tr, TRACE_ID, SLB_TR_WAITED);
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
+        if constexpr (EPI == EPI_ROPE) {                     // in the shadow of the main loop
+            if ((int)cluster_rank() < M) first_target = rope_target(rope, (int)cluster_rank(), n0 + row, row, N, status);
+        }
         bool ok = true;
         if (iters > 0) {
             ok = mbar_wait(accum, 0);
@@ -471,6 +528,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         pdl_launch_dependents();
+        if (tracer) slb_trace_event(tr, TRACE_ID, SLB_TR_LOOP_DONE);
         for (int c0 = 0; c0 < ntok16; c0 += 16) {
             uint32_t v[16];
             if (iters > 0 && ok) {
@@ -494,50 +552,34 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
         const uint32_t rank = cluster_rank(), nranks = cluster_size();
         int parity = 0;
         for (int tok = (int)rank; tok < M; tok += (int)nranks) {
+            // the blocks' values are fetched together and then added in rank order: a loop of
+            // load-then-add would wait for every remote load in turn
             const uint32_t addr = smem_u32(acc + tok * TC_BM + row);
+            float part[TC_MAX_CLUSTER];
+#pragma unroll
+            for (uint32_t p = 0; p < (uint32_t)TC_MAX_CLUSTER; ++p) part[p] = p < nranks ? ld_peer_f32(addr, p) : 0.f;
             float sum = 0.f;
-            for (uint32_t p = 0; p < nranks; ++p) sum += ld_peer_f32(addr, p);
+#pragma unroll
+            for (uint32_t p = 0; p < (uint32_t)TC_MAX_CLUSTER; ++p) sum += part[p];
             if constexpr (EPI == EPI_STORE) {
                 if (n < N) out[(size_t)tok * ldo + n] = __float2bfloat16_rn(sum + (bias ? bias[n] : 0.f));
             } else {
-                const int D = rope.D;
-                const int half = rope.inv_freq != nullptr ? rope.rotary_dim >> 1 : 0;
-                float v = (n < N) ? sum + (rope.bias ? rope.bias[n] : 0.f) : 0.f;
+                const RopeTarget t = tok == (int)rank ? first_target : rope_target(rope, tok, n, row, N, status);
+                float v = sum + t.bias;
                 pair_vals[parity][row] = v;
                 asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps
-                if (n < N) {
-                    const int j = n / D, e = n - j * D;
-                    const bool is_v = j >= rope.H + rope.Hkv;
-                    const int pos = rope.positions[tok];
-                    if (!is_v && e < 2 * half) {
-                        const int i = e < half ? e : e - half;
-                        float sn, cs;
-                        sincosf((float)pos * rope.inv_freq[i], &sn, &cs);
-                        const float other = pair_vals[parity][e < half ? row + half : row - half];
-                        v = e < half ? v * cs - other * sn : v * cs + other * sn;
-                    }
-                    bf16* dst = nullptr;
-                    if (j < rope.H) {
-                        dst = rope.q_out + (size_t)tok * rope.ld_q + (size_t)j * D;
-                    } else if (rope.k_cache != nullptr) {
-                        const int page = rope.block_table[(size_t)rope.seq_of_token[tok] * rope.max_pages +
-                                                          pos / rope.page_size];
-                        if (page >= rope.num_pages) {            // outside the cache: not written
-                            atomicCAS(status, 0, (5 << 8) | 1);
-                        } else if (page >= 0) {
-                            const int kvh = is_v ? j - rope.H - rope.Hkv : j - rope.H;
-                            dst = (is_v ? rope.v_cache : rope.k_cache) +
-                                  (((size_t)page * rope.Hkv + kvh) * rope.page_size + pos % rope.page_size) * D;
-                        }
-                    }
-                    if (dst != nullptr) dst[e] = __float2bfloat16_rn(v);
+                if (t.rotate) {
+                    const float other = pair_vals[parity][t.other];
+                    v = t.first_half ? v * t.cs - other * t.sn : v * t.cs + other * t.sn;
                 }
+                if (t.dst != nullptr) *t.dst = __float2bfloat16_rn(v);
                 parity ^= 1;
             }
         }
     }
     __syncwarp();
     cluster_sync_all();                                      // no block leaves while its acc is read
+    if (tracer) slb_trace_event(tr, TRACE_ID, SLB_TR_END);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TC_TMEM_COLS)
@@ -597,7 +639,7 @@ int run(const bf16* x, int ldx, const bf16* W, int ldw, TO* out, int ldo, const 
     if (e != cudaSuccess) return (int)e;
     rc = slb_launch(gemm_tc_decode_kernel<TO>, dim3((N + TC_BM - 1) / TC_BM, splits), dim3(TC_THREADS),
                     TC_SMEM, st, map_w, map_x, out, ldo, workspace, bias, M, N, K, ntok16, max_stages, status,
-                    swiglu, slb_pdl_early);
+                    swiglu, slb_pdl_early, slb_trace_arg());
     if (rc != 0 || splits == 1 || defer_sum) return rc;
     return slb_launch(gemm_tc_reduce_kernel<TO>, dim3((N + 255) / 256, M), dim3(256), 0, st,
                       (const float*)workspace, out, ldo, bias, M, N, splits);
@@ -623,7 +665,6 @@ int launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, int cluster_
     return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
-constexpr int TC_MAX_CLUSTER = 8;       // the portable cluster size
 
 template <int EPI>
 int run_cluster(const bf16* x, int ldx, const bf16* W, int ldw, bf16* out, int ldo, const float* bias,
@@ -646,7 +687,7 @@ int run_cluster(const bf16* x, int ldx, const bf16* W, int ldw, bf16* out, int l
     if (e != cudaSuccess) return (int)e;
     return launch_cluster(gemm_tc_cluster_kernel<EPI>, dim3((N + TC_BM - 1) / TC_BM, splits),
                           dim3(TC_THREADS), splits, smem, st, map_w, map_x, out, ldo, bias, M, N, K, ntok16,
-                          max_stages, status, rope, slb_pdl_early);
+                          max_stages, status, rope, slb_pdl_early, slb_trace_arg());
 }
 
 int check_cluster_args(const bf16* x, int ldx, const bf16* W, int ldw, int M, int N, int K, int splits) {

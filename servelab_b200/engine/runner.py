@@ -11,6 +11,8 @@ one function.  Reference analogue: the packing and forward part of
 
 from __future__ import annotations
 
+import gc
+import weakref
 from typing import List, Optional, Sequence
 
 import numpy as np
@@ -62,8 +64,9 @@ class ModelRunner:
         self.cache = CacheManager(self.storage.group_windows, num_pages, self.page_size,
                                   max_num_seqs, reserve_pages=cache_config.reserve_blocks)
         if cache_config.poison_cache:
+            storage = self.storage             # (the pools must not keep the runner alive)
             for g, pool in enumerate(self.cache.pools):
-                pool.on_free = (lambda pages, g=g: self.storage.poison_pages(g, pages))
+                pool.on_free = (lambda pages, g=g, storage=storage: storage.poison_pages(g, pages))
         self.num_groups = len(self.storage.groups)
         self.max_model_len = min(max_model_len or self.spec.max_position_embeddings,
                                  self.spec.max_position_embeddings, num_pages * self.page_size)
@@ -81,7 +84,11 @@ class ModelRunner:
             for b in list(self.model.blocks) + [self.model.embedding_position, self.model.final_norm])
         self.graph_replays = 0
         self._table_rows = {}             # (request, group) -> (stamp, block table as int32 array)
-        self.cache.release_listeners.append(self._forget_table_rows)
+        # through a weak reference: the cache manager must not keep the runner alive in a
+        # cycle, or a dropped engine (its graphs, its memory pool) would be destroyed only when
+        # the garbage collector runs, which may be in the middle of another engine's capture
+        me = weakref.ref(self)
+        self.cache.release_listeners.append(lambda rid: me() is not None and me()._forget_table_rows(rid))
         self.graph_kernel_launches = {}   # batch size -> this package's kernels per replay
 
     @classmethod
@@ -152,14 +159,29 @@ class ModelRunner:
         if hit is None:
             ctx = StepContext.pack(entries, self.num_groups, self.device, min_table_width=width)
             ctx.split_hint_len = self.max_model_len     # launch shapes must not depend on the step
-            self.model.forward(ctx, self.storage.layer_caches)      # warm-up outside capture
+            # the warm-up outside capture runs the step once and the first replay runs it again:
+            # keys and values land in the same slots both times, but a mixer's own state would
+            # advance twice, so the state of the step's slots is put back after the warm-up
+            saved = self.storage.snapshot_state(ctx.state_slot_ids)
+            self.model.forward(ctx, self.storage.layer_caches)
+            self.storage.restore_state(ctx.state_slot_ids, saved)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             before = K.launch_count
-            with torch.cuda.graph(graph, pool=self._graph_pool):
-                logits = self.model.forward(ctx, self.storage.layer_caches)
+            # objects that own device memory or graphs must not be destroyed while the stream is
+            # capturing (their CUDA calls would invalidate the capture): collect what is garbage
+            # now, and keep the collector off until the capture has ended
+            gc.collect()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    logits = self.model.forward(ctx, self.storage.layer_caches)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             self.graph_kernel_launches[B] = K.launch_count - before
             hit = self._graphs[B] = (graph, ctx, logits)
         graph, ctx, logits = hit

@@ -59,6 +59,11 @@ _OPTIONAL_SIGNATURES = {}
 _libs: Dict[str, ctypes.CDLL] = {}
 _pdl = True
 _pdl_early = False
+trace_buffer = None        # device address of a timeline buffer (``ops.timeline``) or None
+
+
+def loaded_libraries():
+    return list(_libs.values())
 
 
 def set_pdl(on: bool) -> None:
@@ -91,6 +96,8 @@ def _apply_switches(lib: ctypes.CDLL) -> None:
     lib.slb_set_pdl(1 if _pdl else 0)
     lib.slb_set_pdl_early.argtypes = [I]
     lib.slb_set_pdl_early(1 if _pdl_early else 0)
+    lib.slb_set_trace.argtypes = [P, I]
+    lib.slb_set_trace(trace_buffer, len(_libs))
 
 
 def _declare(lib: ctypes.CDLL, sigs: dict, required: bool) -> None:
@@ -131,7 +138,8 @@ _ATTN_SIGNATURES = {
     "slb_prefill_attention_tc_tile_rows": [I],
     "slb_prefill_attention_tc_status": [I],
     "slb_prefill_attention_tc_where": [P],
-    "slb_decode_attention_ws_bf16": [P, I, P, P, P, I, P, I, P, P, P, I, I, I, I, I, F, I, I, I, F, I, P],
+    "slb_decode_attention_ws_bf16": [P, I, P, P, P, I, P, I, P, P, P, I, I, I, I, I, F, I, I, I, F, I, I, P],
+    "slb_decode_attention_ws_max_cluster_splits": [],
     "slb_decode_attention_ws_supported": [I],
     "slb_decode_attention_ws_status": [I],
     "slb_decode_attention_ws_splits_used": [I],

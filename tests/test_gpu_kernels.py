@@ -590,18 +590,22 @@ def test_decode_attention_one_launch(H, Hkv, D, ps, window, splits, stages, coef
     want = case.reference(window=window or None)
     counters = torch.zeros(int(lib.slb_decode_attention_ws_counters(S, H, Hkv)), dtype=torch.int32,
                            device=DEV)
-    for _ in range(2):
+    # twice through global scratch and the arrival counters, then (up to eight splits) with the
+    # splits of a request as a thread-block cluster, which needs neither
+    for cluster in (0, 0, 1):
+        if cluster and splits > lib.slb_decode_attention_ws_max_cluster_splits():
+            continue
         out = torch.full_like(q, 7.0)
         scratch = torch.full((max(1, lib.slb_decode_attention_ws_scratch_bytes(S, H, splits) // 4),),
                              float("nan"), device=DEV)
         L.check(lib.slb_decode_attention_ws_bf16(
             q.data_ptr(), q.stride(0), case.kc.data_ptr(), case.vc.data_ptr(), out.data_ptr(),
             out.stride(0), table.data_ptr(), table.shape[1], ctx.ctx_len.data_ptr(),
-            scratch.data_ptr(), counters.data_ptr(), S, H, Hkv, ps, case.kc.shape[0],
-            1 / math.sqrt(D), window, splits, stages, coef, unsplit,
+            None if cluster else scratch.data_ptr(), None if cluster else counters.data_ptr(), S, H, Hkv, ps,
+            case.kc.shape[0], 1 / math.sqrt(D), window, splits, stages, coef, unsplit, cluster,
             torch.cuda.current_stream().cuda_stream), "decode")
         assert K().decode_attention_status(D, reset=True) == 0, "a bounded wait in the kernel gave up"
-        assert (out.float().cpu() - want).abs().max() <= TOL["bfloat16"]
+        assert (out.float().cpu() - want).abs().max() <= TOL["bfloat16"], f"cluster={cluster}"
         assert int(counters.abs().sum()) == 0
     # the dispatching wrapper (its own choice of splits) and the earlier two-kernel form
     for fn in (K().decode_attention, K().decode_attention_split):

@@ -22,7 +22,7 @@ pytestmark = pytest.mark.gpu
 # a configuration is about twice the worst error its tests print (logits of A-D have a
 # standard deviation near 0.2, those of E, whose attention is peaked, near 1.2).
 TOL = {"float32": 1e-5, "bfloat16": 2e-2}
-TOL_BF16 = {"A": 1.2e-2, "B": 1.2e-2, "C": 1.2e-2, "D": 1.2e-2, "E": 1.5e-1}
+TOL_BF16 = {"A": 1.2e-2, "B": 1.2e-2, "C": 1.2e-2, "D": 1.2e-2, "E": 4e-1}
 TOL_F32 = {"E": 5e-5}
 LENGTHS = [70, 45, 97, 33, 58, 81]
 
