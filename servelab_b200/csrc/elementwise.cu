@@ -151,16 +151,22 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
             xv[j] = i < h ? load4(x + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
         if (has_delta) {
+            // every load of the update before the first store of the stream (a store between
+            // two loads would make the second wait for the first)
+            float4 dv[NORM_NV];
 #pragma unroll
             for (int j = 0; j < NORM_NV; ++j) {
                 const int i = (threadIdx.x + j * blockDim.x) * 4;
-                if (i < h) {
-                    const float4 dv = delta4(d, pp, nparts, part_stride, pbias, i);
-                    xv[j].x += dv.x; xv[j].y += dv.y; xv[j].z += dv.z; xv[j].w += dv.w;
-                    if (write_back) store4(x + i, xv[j]);
-                }
+                dv[j] = i < h ? delta4(d, pp, nparts, part_stride, pbias, i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < NORM_NV; ++j) {
+                const int i = (threadIdx.x + j * blockDim.x) * 4;
+                xv[j].x += dv[j].x; xv[j].y += dv[j].y; xv[j].z += dv[j].z; xv[j].w += dv[j].w;
+                if (write_back && i < h) store4(x + i, xv[j]);
             }
         }
+        if (threadIdx.x == 0) slb_trace_event(tr, 5, SLB_TR_LOOP_DONE);
 #pragma unroll
         for (int j = 0; j < NORM_NV; ++j) {
             ss += xv[j].x * xv[j].x;
@@ -287,10 +293,12 @@ __global__ void add_rmsnorm_parts_cluster_kernel(float* __restrict__ resid,
     ss += v.y * v.y;
     ss += v.z * v.z;
     ss += v.w * v.w;
+    if (threadIdx.x == 0) slb_trace_event(tr, 6, SLB_TR_LOOP_DONE);
     ss = block_sum(ss, scratch);
     if (threadIdx.x == 0) my_ss = ss;
     cluster_arrive();
     cluster_wait();
+    if (threadIdx.x == 0) slb_trace_event(tr, 6, 4);
     float part[NORM_CLUSTER];                              // all remote loads first, then the sum
 #pragma unroll
     for (unsigned c = 0; c < NORM_CLUSTER; ++c) part[c] = load_cluster_shared(&my_ss, c);
@@ -358,7 +366,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 }
 
 static int norm_threads(int h) {
-    int t = ((h + 7) / 8 + 31) / 32 * 32;          // about two vectors of 4 per thread
+    int t = ((h + 15) / 16 + 31) / 32 * 32;        // about four vectors of 4 per thread, all in flight
     return t < 32 ? 32 : (t > 1024 ? 1024 : t);
 }
 

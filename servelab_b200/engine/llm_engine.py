@@ -154,8 +154,7 @@ class LLMEngine:
         sch, runner = self.scheduler, self.runner
         if (not self.lookahead or not seqs or sch.waiting or plan.preempted
                 or len(plan.portions) != len(sch.running) or len(seqs) != len(plan.portions)
-                or not runner.replays_graph(len(seqs))
-                or any(w for w in runner.storage.group_windows)):
+                or not runner.replays_graph(len(seqs))):
             return
         for p in plan.portions:
             seq, sp = p.seq, p.seq.sampling_params
@@ -163,7 +162,10 @@ class LLMEngine:
                     or seq.num_output_tokens + 1 >= sp.max_tokens        # ends by its length
                     or seq.get_len() + 1 >= sch.max_model_len):
                 return
-        # every request gets one more token; its position is the current length
+        # every request gets one more token; its position is the current length.  (Windowed
+        # groups: the pages that step N's bookkeeping gives back afterwards are still read by
+        # the step launched here; whoever gets them next writes them in a later step, which
+        # the stream runs after this one.)
         for seq in seqs:
             if not runner.cache.ensure(seq.request_id, seq.get_len() + 1):
                 return                              # no page: the scheduler decides next step

@@ -36,24 +36,42 @@ def _w_ok(w) -> bool:
     return w.shape[1] % 8 == 0 and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0
 
 
+# Matrices up to this many bytes keep their products on this package's kernels up to 64 tokens
+# instead of 16.  Meant for shapes whose steps are launch-bound (the 0.5B shape: 2 to 9 MB a
+# product), because this package's kernels chain through programmatic dependent launch inside a
+# captured step and the library's GEMMs do not.  Off: measured on the 0.5B shape at 64 requests
+# the step took 1.70 ms against 1.25 ms with the library's GEMMs -- with few row tiles a block
+# of the cluster form finishes 8 to 22 tokens one after the other in its epilogue.
+tc_small_weight_bytes = 0        # off: see the note above
+
+
+def _token_limit(w) -> int:
+    if w.numel() * w.element_size() <= tc_small_weight_bytes:
+        return K.TC_MAX_TOKENS
+    return tc_max_tokens
+
+
 def _tc_ok(x, w, M):
-    limit = tc_max_tokens
+    limit = _token_limit(w)
     if M > limit and K.tc_decode_splits(w.shape[0], w.shape[1]) == 1:
         limit = max(limit, tc_wide_max_tokens)
     return (0 < M <= min(limit, K.TC_MAX_TOKENS) and _w_ok(w)
             and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
 
 
-# Narrow products of a decode step (few k-blocks per block): the K splits of a row tile run as
-# one thread-block cluster and add their results through shared memory, so the product needs
-# neither partial sums in global memory nor a kernel that adds them.  Measured on the 7B shape
-# at 8 tokens, product and the kernel after it, in a graph: o 10.4 -> 9.6 us; the q|k|v product
-# with bias, rotation and cache write in its epilogue 11.7 -> 9.7 us.  Products with long K
-# ranges (down: 37 k-blocks a block with the 8 splits a cluster allows, against 27 with 11)
-# stay with the partial sums: 26.7 against 27.3 us.
+# The K splits of a decode-step product's row tile run as one thread-block cluster and add
+# their results through shared memory, so the product needs neither partial sums in global
+# memory nor a kernel that adds them.  Measured on the 7B shape at 8 tokens, product and the
+# kernel after it, in a graph: o 10.4 -> 9.6 us; the q|k|v product with bias, rotation and
+# cache write in its epilogue 11.7 -> 9.7 us.  Products with long K ranges (down: 37 k-blocks a
+# block with the 8 splits a cluster allows, against 30 with 10) gained from it once the blocks
+# fetched one another's sums together instead of one after the other: the batch-8 step went
+# from 2.97 to 2.91 ms with down in the cluster form and a plain norm after it, instead of
+# float32 partial sums that a cluster of norm blocks adds.
 cluster_sums = True
-cluster_max_kblocks = 16   # k-blocks (of 64) per block up to which the cluster form is used
-cluster_long_k_max_tokens = 64   # products with longer K ranges use it from 17 tokens up to here
+cluster_max_kblocks = 64   # k-blocks (of 64) per block up to which the cluster form is used
+cluster_long_k_kblocks = 16      # products whose blocks stream more k-blocks than this ("long K") ...
+cluster_long_k_max_tokens = 64   # ... use the cluster form also from 17 tokens up to here
 fuse_qkv_rope = True       # the q|k|v product of a decode step rotates and writes the cache itself
 
 
@@ -65,12 +83,14 @@ def _cluster_ok(x, w, M) -> bool:
     want = K.tc_decode_splits(N, Kd)
     if want <= 1:
         return False
-    kblocks = -(-Kd // 64)
-    if -(-kblocks // min(want, K.TC_MAX_CLUSTER)) <= cluster_max_kblocks:
-        return M <= tc_max_tokens
+    per_block = -(-(-(-Kd // 64)) // min(want, K.TC_MAX_CLUSTER))      # k-blocks of 64 a block streams
+    if per_block > cluster_max_kblocks:
+        return False
+    if M <= _token_limit(w):
+        return True
     # long K ranges (down): streaming the weights is most of the time, and the cluster form
     # beats the vendor GEMM between 17 and 64 tokens (30.8 against 34.1 us with the norm, 7B shape)
-    return tc_max_tokens < M <= cluster_long_k_max_tokens
+    return per_block > cluster_long_k_kblocks and M <= cluster_long_k_max_tokens
 
 
 def qkv_projection(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Tensor], positions,
@@ -82,7 +102,7 @@ def qkv_projection(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Te
     size the product's epilogue takes; otherwise the product, then the q/k/v kernel."""
     M = x.shape[0]
     if (fuse_qkv_rope and x.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16
-            and head_dim in K.TC_ROPE_HEAD_DIMS and 0 < M <= tc_max_tokens
+            and head_dim in K.TC_ROPE_HEAD_DIMS and 0 < M <= _token_limit(w_qkv)
             and K.tc_decode_splits(w_qkv.shape[0], w_qkv.shape[1]) > 1 and _tc_ok(x, w_qkv, M)):
         K.gemm_tc_qkv_rope(x, w_qkv, bias, positions, seq_of_token, block_table, page_size, inv_freq,
                            rotary_dim, q_out, k_cache, v_cache, num_heads, num_kv_heads, head_dim)

@@ -11,7 +11,8 @@ One thread of every block of the decode-step kernels (the tcgen05 products, the 
 attention, the norms) records the device's nanosecond timer when the block starts, when its
 wait for the preceding kernel returns, when its main loop is done and when it ends
 (``csrc/common.cuh``).  ``launches()`` condenses that to one row per launch: first start,
-first and last return of the wait, last main loop done, last end, relative to the first event;
+first and last return of the wait, last main loop done (the norms: inputs loaded), an extra
+mark (the cluster norm: sums of squares exchanged), last end, relative to the first event;
 ``render()`` prints them with the gaps between consecutive launches, which is what the time of
 a decode step beyond its memory traffic consists of.  The reference has no counterpart (its
 docs name profiler command lines, docs/benchmark_guide.md:29-49).
@@ -89,14 +90,15 @@ class DeviceTimeline:
                         "first_start": min(t.get(0, [0.0])), "last_start": max(t.get(0, [0.0])),
                         "first_waited": min(t.get(1, [float("nan")])), "last_waited": max(t.get(1, [float("nan")])),
                         "last_loop_done": max(t.get(2, [float("nan")])),
-                        "last_end": max(t.get(3, [0.0]) + t.get(4, [0.0]))})
+                        "last_extra": max(t.get(4, [float("nan")])),
+                        "last_end": max(t.get(3, [0.0]) + (t.get(4, [0.0]) if row["kernel"] == KERNELS[4] else [0.0]))})
         out.sort(key=lambda r: r["first_waited"] if r["first_waited"] == r["first_waited"] else r["first_start"])
         return out
 
     def render(self, limit: int = 80) -> str:
         rows = self.launches()[:limit]
         head = ("kernel", "blocks", "SMs", "first start", "last start", "waited (first..last)",
-                "loop done", "end", "ran", "after prev end")
+                "loop done", "extra", "end", "ran", "after prev end")
         table = [head]
         prev_end = None
         for r in rows:
@@ -104,7 +106,8 @@ class DeviceTimeline:
             gap = "" if prev_end is None else f"{r['first_waited'] - prev_end:+.2f}"
             table.append((r["kernel"], str(r["blocks"]), str(r["sms"]), f"{r['first_start']:.2f}",
                           f"{r['last_start']:.2f}", f"{r['first_waited']:.2f}..{r['last_waited']:.2f}",
-                          f"{r['last_loop_done']:.2f}", f"{r['last_end']:.2f}", f"{ran:.2f}", gap))
+                          f"{r['last_loop_done']:.2f}", f"{r['last_extra']:.2f}", f"{r['last_end']:.2f}",
+                          f"{ran:.2f}", gap))
             prev_end = r["last_end"]
         widths = [max(len(row[i]) for row in table) for i in range(len(head))]
         return "\n".join("  ".join(c.ljust(w) for c, w in zip(row, widths)) for row in table)

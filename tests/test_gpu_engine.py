@@ -161,17 +161,27 @@ def test_lookahead_gives_the_same_tokens_and_frees_every_page(model, dtype):
         st = eng.stats()
         assert st["pages_used"] == [0] * len(st["pages_used"])
         eng.runner.cache.check_invariants()
-        windowed = any(eng.runner.storage.group_windows)    # no look-ahead with windowed layers
-        return [results.get(i) for i in ids + ["aborted"]], (eng.num_lookahead_steps, windowed)
+        return [results.get(i) for i in ids + ["aborted"]], eng.num_lookahead_steps
 
     stopping = [SamplingParams(temperature=0.0, max_tokens=20, stop_token_ids=(t,)) for t in stops]
     random_sp = [SamplingParams(temperature=0.8, top_k=20, max_tokens=15, ignore_eos=True)] * len(prompts)
     for sp_list, aborts in ((stopping, False), (random_sp, False), (stopping, True), (random_sp, True)):
-        with_it, (n_ahead, windowed) = run(True, sp_list, aborts)
-        without, (none_ahead, _) = run(False, sp_list, aborts)
-        assert with_it == without
+        with_it, n_ahead = run(True, sp_list, aborts)
+        without, none_ahead = run(False, sp_list, aborts)
+        if dtype == "float32" or not (aborts and sp_list is random_sp):
+            assert with_it == without
+        else:
+            # After the abort a step launched ahead is adopted first, so the late arrival is
+            # admitted one step later than without look-ahead and two decode rows go through
+            # the graph instead of through a step with a prompt portion: other kernels, other
+            # bfloat16 rounding, and a random draw near a boundary of the distribution may
+            # fall the other way (float32 is bit-identical on every path and is compared
+            # above).  What must still agree: how much every request generated and why it ended.
+            shape = lambda rs: [(len(r[0]), r[1]) if isinstance(r, tuple) else r for r in rs]
+            assert shape(with_it) == shape(without)
         longest = max(len(r[0]) for r in with_it if isinstance(r, tuple))
-        assert none_ahead == 0 and (n_ahead > 0 or longest < 3 or windowed), (n_ahead, longest)
+        # (configurations C and D have windowed layers: steps are launched ahead there too)
+        assert none_ahead == 0 and (n_ahead > 0 or longest < 3), (n_ahead, longest)
     if dtype == "float32":
         got, _ = run(True, stopping)
         for (toks, reason), g, t in zip(got[:len(prompts)], greedy, stops):
