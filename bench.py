@@ -118,11 +118,11 @@ def reference_arm() -> int:
     return 0
 
 
-TUNABLES = """tc_max_tokens tc_wide_max_tokens cluster_max_kblocks cluster_long_k_max_tokens (ints,
-ops.linear); defer_rope defer_norm fuse_swiglu cluster_sums fuse_qkv_rope (0/1, ops.linear); tc_max_stages
+TUNABLES = """tc_max_tokens tc_wide_max_tokens cluster_max_kblocks cluster_long_k_max_tokens
+cluster_max_tokens_per_block tc_small_weight_bytes (ints, ops.linear); defer_rope defer_norm fuse_swiglu cluster_sums fuse_qkv_rope (0/1, ops.linear); tc_max_stages
 tc_blocks_per_sm decode_ctas_per_sm decode_ws_stages decode_ws_force_splits decode_ws_unsplit_tiles
 tc_max_cluster (ints, ops.kernels); decode_ws_split_coef (float); use_tc_prefill decode_ws_cluster pdl
-pdl_early (0/1)"""
+pdl_early evict_first (0/1)"""
 
 
 def apply_tunables(items):
@@ -131,7 +131,8 @@ def apply_tunables(items):
     from servelab_b200.ops import linear as linear_ops
     for item in items:
         name, value = item.split("=")
-        if name in ("tc_max_tokens", "tc_wide_max_tokens", "cluster_max_kblocks", "cluster_long_k_max_tokens"):
+        if name in ("tc_max_tokens", "tc_wide_max_tokens", "cluster_max_kblocks", "cluster_long_k_max_tokens",
+                    "cluster_max_tokens_per_block", "tc_small_weight_bytes"):
             setattr(linear_ops, name, int(value))
         elif name in ("defer_rope", "defer_norm"):
             linear_ops.defer_split_sums[name[6:]] = bool(int(value))
@@ -150,6 +151,8 @@ def apply_tunables(items):
             kernel_library.set_pdl(bool(int(value)))
         elif name == "pdl_early":
             kernel_library.set_pdl_early(bool(int(value)))
+        elif name == "evict_first":
+            kernel_library.set_evict_first(bool(int(value)))
         else:
             raise SystemExit(f"unknown tunable {name}; known: {TUNABLES}")
 

@@ -130,7 +130,7 @@ __device__ __forceinline__ BoxGeometry box_geometry(int rows) {
 __device__ __forceinline__ void produce_tile(unsigned char* Kd, unsigned char* Vd, uint64_t* bar,
                                              const CUtensorMap* map_k, const CUtensorMap* map_v,
                                              int page, int k0, int ctx, int kvh, int Hkv, int ps,
-                                             const BoxGeometry& geo) {
+                                             const BoxGeometry& geo, bool evict_first) {
     const int lane = threadIdx.x & 31;
     int row0 = -1;                                         // first cache row of this lane's box
     if (lane < geo.boxes) {
@@ -156,8 +156,14 @@ __device__ __forceinline__ void produce_tile(unsigned char* Kd, unsigned char* V
     }
     __syncwarp();
     if (row0 >= 0) {
-        tma_load_3d(Kd + lane * geo.box_bytes, map_k, bar, 0, row0, 0);
-        tma_load_3d(Vd + lane * geo.box_bytes, map_v, bar, 0, row0, 0);
+        if (evict_first) {                                 // the cache is streamed once a step
+            const uint64_t policy = l2_evict_first_policy();
+            slb_tma::tma_load_3d_hint(Kd + lane * geo.box_bytes, map_k, bar, 0, row0, 0, policy);
+            slb_tma::tma_load_3d_hint(Vd + lane * geo.box_bytes, map_v, bar, 0, row0, 0, policy);
+        } else {
+            tma_load_3d(Kd + lane * geo.box_bytes, map_k, bar, 0, row0, 0);
+            tma_load_3d(Vd + lane * geo.box_bytes, map_v, bar, 0, row0, 0);
+        }
     }
 }
 
@@ -172,7 +178,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ ctx_len,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int H,
     int Hkv, int ps, int box_rows, float scale_log2, int window, int num_splits, int head_tiles,
-    int stages, float split_coef, int unsplit_tiles, int num_pages, int pdl_early,
+    int stages, float split_coef, int unsplit_tiles, int num_pages, int flags,
     const SlbTraceArg tr) {
     constexpr int HR = 8 * NH;                             // query heads per block
     constexpr int QCH = (HR * CHUNKS + 32 * DW - 1) / (32 * DW);   // 16-byte chunks of Q a consumer thread moves
@@ -223,7 +229,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     if (use_splits > 1 && split == 0 && blockIdx.y == 0 && threadIdx.x == 0)
         atomicMax(&dec_splits_used, use_splits);           // what tests read to see that requests were split
     if (CLUSTER && use_splits == 1 && split > 0) return;   // the whole cluster takes this branch or none
-    if (pdl_early) pdl_launch_dependents();
+    if (flags & SLB_FLAG_PDL_EARLY) pdl_launch_dependents();
     if (threadIdx.x == 0) slb_trace_event(tr, 4, SLB_TR_START);
     const int tiles_per_split = (total_tiles + use_splits - 1) / use_splits;
     const int t_begin = split * tiles_per_split;
@@ -271,7 +277,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
         const int page = __shfl_sync(0xffffffffu, first_pages, (warp * geo.boxes + lane) & 31);
         unsigned char* Kd = stage0 + (size_t)warp * STAGE_BYTES;
         produce_tile(Kd, Kd + TILE_BYTES, &full_bar[warp], &map_k, &map_v, page, kstart + warp * BN, ctx,
-                     kvh, Hkv, ps, geo);
+                     kvh, Hkv, ps, geo, (flags & SLB_FLAG_EVICT_FIRST) != 0);
     };
     if (warp < burst && !last_tile_in_burst) produce_first();
     pdl_wait();                                            // q and this step's K/V rows
@@ -299,7 +305,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
             }
             unsigned char* Kd = stage0 + (size_t)st * STAGE_BYTES;
             produce_tile(Kd, Kd + TILE_BYTES, &full_bar[st], &map_k, &map_v, page, kstart + t * BN, ctx,
-                         kvh, Hkv, ps, geo);
+                         kvh, Hkv, ps, geo, (flags & SLB_FLAG_EVICT_FIRST) != 0);
             if (lane == 0) issued = t + 1;
         }
     }
@@ -707,7 +713,7 @@ int launch_decode(const bf16* q, int ldq, const CUtensorMap& map_k, const CUtens
     return (int)cudaLaunchKernelEx(&cfg, decode_attention_ws_kernel<NH, CLUSTER>, q, ldq, map_k, map_v, out,
                                    ldo, block_table, max_pages, ctx_len, part_o, part_ml, counters, H, Hkv, ps,
                                    box_rows, scale * 1.4426950408889634f, window, num_splits, head_tiles,
-                                   stages, split_coef, unsplit_tiles, num_pages, slb_pdl_early,
+                                   stages, split_coef, unsplit_tiles, num_pages, slb_kernel_flags,
                                    slb_trace_arg());
 }
 

@@ -91,10 +91,22 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 }
 
 extern int slb_pdl_enabled;          // defined once per shared library (SLB_DEFINE_PDL_SWITCH)
-// Non-zero: the long kernels (matrix products, attention) let their successor be scheduled at
-// their start instead of after their main loop, so that its blocks become resident beside
-// theirs wherever an SM has room and fetch their first weight tiles while these still run.
-extern int slb_pdl_early;
+// Switches of the long kernels (matrix products, decode attention), handed to them as one word:
+//   SLB_FLAG_PDL_EARLY    they let their successor be scheduled at their start instead of after
+//                         their main loop, so that its blocks become resident beside theirs
+//                         wherever an SM has room and fetch their first weight tiles meanwhile;
+//   SLB_FLAG_EVICT_FIRST  what they stream once a step (weights, cached keys and values) is
+//                         fetched with the L2 policy "evict first", so that the few hundred KB of
+//                         activations between the kernels (the float32 residual stream above
+//                         all) stay in the L2 cache instead of being pushed out by 400 MB of
+//                         weights a layer and fetched from HBM again by the next norm.
+enum { SLB_FLAG_PDL_EARLY = 1, SLB_FLAG_EVICT_FIRST = 2 };
+extern int slb_kernel_flags;
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
 
 // ---- device timeline (measurements) -------------------------------------------
 // With a buffer set (slb_set_trace), one thread of every block of the decode-step kernels
@@ -180,15 +192,15 @@ static inline int slb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 
 #define SLB_DEFINE_PDL_SWITCH                                                         \
     int slb_pdl_enabled = 0;                                                          \
-    int slb_pdl_early = 0;                                                            \
+    int slb_kernel_flags = SLB_FLAG_EVICT_FIRST;                                      \
     extern "C" int slb_set_pdl(int on) {                                              \
         const int old = slb_pdl_enabled;                                              \
         slb_pdl_enabled = on ? 1 : 0;                                                 \
         return old;                                                                   \
     }                                                                                 \
-    extern "C" int slb_set_pdl_early(int on) {                                        \
-        const int old = slb_pdl_early;                                                \
-        slb_pdl_early = on ? 1 : 0;                                                   \
+    extern "C" int slb_set_kernel_flags(int flags) {                                  \
+        const int old = slb_kernel_flags;                                             \
+        slb_kernel_flags = flags;                                                     \
         return old;                                                                   \
     }                                                                                 \
     unsigned long long* slb_trace_ptr = nullptr;                                      \

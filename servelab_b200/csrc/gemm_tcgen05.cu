@@ -85,6 +85,22 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
         : "memory");
 }
+// the same copy with an L2 eviction policy for the lines it brings (createpolicy)
+__device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                                 int c0, int c1, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
+          "l"(policy)
+        : "memory");
+}
+// a W tile: streamed once a step
+__device__ __forceinline__ void load_w_tile(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0,
+                                            int c1, bool evict_first, uint64_t policy) {
+    if (evict_first) tma_load_2d_hint(smem_dst, map, bar, c0, c1, policy);
+    else tma_load_2d(smem_dst, map, bar, c0, c1);
+}
 // K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, groups
 // of 8 rows 1024 bytes apart (stride byte offset), version 1 (Blackwell), layout 2.
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
@@ -125,7 +141,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     TO* __restrict__ out, int ldo, float* __restrict__ partial, const float* __restrict__ bias,
     int M, int N, int K, int ntok16, int max_stages, int* __restrict__ status, int swiglu,
-    int pdl_early, const SlbTraceArg tr) {
+    int flags, const SlbTraceArg tr) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -164,7 +180,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *tmem_slot;
-    if (pdl_early) pdl_launch_dependents();
+    if (flags & SLB_FLAG_PDL_EARLY) pdl_launch_dependents();
     const bool tracer = threadIdx.x == 64;                  // lane 0 of the first epilogue warp
     if (tracer) slb_trace_event(tr, 1, SLB_TR_START);
 
@@ -174,10 +190,12 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
         // stages are requested at once, the x tiles after the wait for that kernel.
         if (lane == 0) {
             const uint32_t bytes = A_STAGE_BYTES + (uint32_t)ntok16 * TC_BK * 2;
+            const bool w_first = (flags & SLB_FLAG_EVICT_FIRST) != 0;
+            const uint64_t w_policy = w_first ? l2_evict_first_policy() : 0;
             const int ahead = min(iters, TC_STAGES);
             for (int i = 0; i < ahead; ++i) {                 // stages are empty at the start
                 mbar_expect_tx(&full[i], bytes);
-                tma_load_2d(a_stage + i * A_STAGE_BYTES, &map_w, &full[i], (kb_begin + i) * TC_BK, n0);
+                load_w_tile(a_stage + i * A_STAGE_BYTES, &map_w, &full[i], (kb_begin + i) * TC_BK, n0, w_first, w_policy);
             }
             pdl_wait();
             for (int i = 0; i < ahead; ++i)
@@ -190,7 +208,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
                 }
                 mbar_expect_tx(&full[s], bytes);
                 const int k = (kb_begin + i) * TC_BK;
-                tma_load_2d(a_stage + s * A_STAGE_BYTES, &map_w, &full[s], k, n0);
+                load_w_tile(a_stage + s * A_STAGE_BYTES, &map_w, &full[s], k, n0, w_first, w_policy);
                 tma_load_2d(b_stage + s * B_STAGE_BYTES, &map_x, &full[s], k, 0);
             }
         }
@@ -380,8 +398,9 @@ struct RopeTarget {
     int other;                          // row of the tile that holds the rotation partner
     bool rotate, first_half;
 };
-__device__ __forceinline__ RopeTarget rope_target(const RopeEpilogue& rope, int tok, int n, int row, int N,
-                                                  int* status) {
+// pos: the token's position; page: its entry of the block table (negative: nothing to write)
+__device__ __forceinline__ RopeTarget rope_target(const RopeEpilogue& rope, int tok, int pos, int page, int n,
+                                                  int row, int N) {
     RopeTarget t;
     t.bias = 0.f; t.sn = 0.f; t.cs = 1.f; t.dst = nullptr; t.other = row; t.rotate = false; t.first_half = true;
     if (n >= N) return t;
@@ -390,7 +409,6 @@ __device__ __forceinline__ RopeTarget rope_target(const RopeEpilogue& rope, int 
     const int j = n / D, e = n - j * D;
     const bool is_v = j >= rope.H + rope.Hkv;
     if (rope.bias) t.bias = rope.bias[n];
-    const int pos = rope.positions[tok];
     if (!is_v && e < 2 * half) {
         const int i = e < half ? e : e - half;
         sincosf((float)pos * rope.inv_freq[i], &t.sn, &t.cs);
@@ -400,15 +418,10 @@ __device__ __forceinline__ RopeTarget rope_target(const RopeEpilogue& rope, int 
     }
     if (j < rope.H) {
         t.dst = rope.q_out + (size_t)tok * rope.ld_q + (size_t)j * D + e;
-    } else if (rope.k_cache != nullptr) {
-        const int page = rope.block_table[(size_t)rope.seq_of_token[tok] * rope.max_pages + pos / rope.page_size];
-        if (page >= rope.num_pages) {                          // outside the cache: not written
-            atomicCAS(status, 0, (5 << 8) | 1);
-        } else if (page >= 0) {
-            const int kvh = is_v ? j - rope.H - rope.Hkv : j - rope.H;
-            t.dst = (is_v ? rope.v_cache : rope.k_cache) +
-                    (((size_t)page * rope.Hkv + kvh) * rope.page_size + pos % rope.page_size) * D + e;
-        }
+    } else if (rope.k_cache != nullptr && page >= 0) {
+        const int kvh = is_v ? j - rope.H - rope.Hkv : j - rope.H;
+        t.dst = (is_v ? rope.v_cache : rope.k_cache) +
+                (((size_t)page * rope.Hkv + kvh) * rope.page_size + pos % rope.page_size) * D + e;
     }
     return t;
 }
@@ -417,7 +430,7 @@ template <int EPI>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     bf16* __restrict__ out, int ldo, const float* __restrict__ bias, int M, int N, int K, int ntok16,
-    int max_stages, int* __restrict__ status, const RopeEpilogue rope, int pdl_early,
+    int max_stages, int* __restrict__ status, const RopeEpilogue rope, int flags,
     const SlbTraceArg tr) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
@@ -430,7 +443,13 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     uint64_t* empty = full + TC_MAX_STAGES;
     uint64_t* accum = empty + TC_MAX_STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
-    __shared__ float pair_vals[2][TC_BM];                    // EPI_ROPE: a token's row of the tile
+    // Static shared memory is kept to a few hundred bytes on purpose: with the ring's 75 KB a
+    // third block (of the kernel after this one) fits on an SM beside two of this kernel only
+    // while a block needs less than about 76.5 KB in all, and that third block is what fetches
+    // the next product's first weight tiles while this one finishes (a block 3 KB larger cost
+    // 9 us a layer).  The rows that the rotation exchanges live in the idle x stages of the ring.
+    __shared__ int tok_pos[TC_MAX_TOK], tok_page[TC_MAX_TOK]; // EPI_ROPE: position and cache page of every token
+    float (*pair_vals)[TC_BM] = reinterpret_cast<float (*)[TC_BM]>(b_stage);         // [2][128]: 1 KB
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * TC_BM;
@@ -460,7 +479,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     const uint32_t tmem_d = *tmem_slot;
     float* acc = reinterpret_cast<float*>(a_stage);          // [ntok16][TC_BM] once the ring is idle
     RopeTarget first_target = {};                            // EPI_ROPE: for token `rank` of this block
-    if (pdl_early) pdl_launch_dependents();
+    if (flags & SLB_FLAG_PDL_EARLY) pdl_launch_dependents();
     const bool tracer = threadIdx.x == 64;                  // lane 0 of the first epilogue warp
     constexpr int TRACE_ID = EPI == EPI_ROPE ? 3 : 2;
     if (tracer) slb_trace_event(tr, TRACE_ID, SLB_TR_START);
@@ -468,10 +487,12 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     if (warp == 0) {
         if (lane == 0) {
             const uint32_t bytes = A_STAGE_BYTES + (uint32_t)ntok16 * TC_BK * 2;
+            const bool w_first = (flags & SLB_FLAG_EVICT_FIRST) != 0;
+            const uint64_t w_policy = w_first ? l2_evict_first_policy() : 0;
             const int ahead = min(iters, TC_STAGES);
             for (int i = 0; i < ahead; ++i) {
                 mbar_expect_tx(&full[i], bytes);
-                tma_load_2d(a_stage + i * A_STAGE_BYTES, &map_w, &full[i], (kb_begin + i) * TC_BK, n0);
+                load_w_tile(a_stage + i * A_STAGE_BYTES, &map_w, &full[i], (kb_begin + i) * TC_BK, n0, w_first, w_policy);
             }
             pdl_wait();
             for (int i = 0; i < ahead; ++i)
@@ -484,7 +505,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
                 }
                 mbar_expect_tx(&full[s], bytes);
                 const int k = (kb_begin + i) * TC_BK;
-                tma_load_2d(a_stage + s * A_STAGE_BYTES, &map_w, &full[s], k, n0);
+                load_w_tile(a_stage + s * A_STAGE_BYTES, &map_w, &full[s], k, n0, w_first, w_policy);
                 tma_load_2d(b_stage + s * B_STAGE_BYTES, &map_x, &full[s], k, 0);
             }
         }
@@ -518,8 +539,27 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
         if (tracer) slb_trace_event(tr, TRACE_ID, SLB_TR_WAITED);
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
-        if constexpr (EPI == EPI_ROPE) {                     // in the shadow of the main loop
-            if ((int)cluster_rank() < M) first_target = rope_target(rope, (int)cluster_rank(), n0 + row, row, N, status);
+        if constexpr (EPI == EPI_ROPE) {
+            // In the shadow of the main loop: the positions and cache pages of the step's tokens
+            // (one token a thread: dependent loads from global memory, which would otherwise be
+            // waited for token by token), then what this block's first token needs.
+            const int t = (int)threadIdx.x - 64;
+            if (t < M) {
+                const int pos = rope.positions[t];
+                int page = -1;
+                if (rope.k_cache != nullptr) {
+                    page = rope.block_table[(size_t)rope.seq_of_token[t] * rope.max_pages + pos / rope.page_size];
+                    if (page >= rope.num_pages) {            // outside the cache: not written
+                        atomicCAS(status, 0, (5 << 8) | 1);
+                        page = -1;
+                    }
+                }
+                tok_pos[t] = pos;
+                tok_page[t] = page;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");               // the four epilogue warps
+            const int tok0 = (int)cluster_rank();
+            if (tok0 < M) first_target = rope_target(rope, tok0, tok_pos[tok0], tok_page[tok0], n0 + row, row, N);
         }
         bool ok = true;
         if (iters > 0) {
@@ -553,7 +593,9 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
         int parity = 0;
         for (int tok = (int)rank; tok < M; tok += (int)nranks) {
             // the blocks' values are fetched together and then added in rank order: a loop of
-            // load-then-add would wait for every remote load in turn
+            // load-then-add would wait for every remote load in turn.  (Fetching those of four
+            // tokens together was tried for steps of up to 64 tokens: the registers it takes cost
+            // the 8-token step 0.13 ms, and at 64 tokens the library's GEMM stayed faster.)
             const uint32_t addr = smem_u32(acc + tok * TC_BM + row);
             float part[TC_MAX_CLUSTER];
 #pragma unroll
@@ -564,7 +606,8 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
             if constexpr (EPI == EPI_STORE) {
                 if (n < N) out[(size_t)tok * ldo + n] = __float2bfloat16_rn(sum + (bias ? bias[n] : 0.f));
             } else {
-                const RopeTarget t = tok == (int)rank ? first_target : rope_target(rope, tok, n, row, N, status);
+                const RopeTarget t = tok == (int)rank ? first_target
+                                                      : rope_target(rope, tok, tok_pos[tok], tok_page[tok], n, row, N);
                 float v = sum + t.bias;
                 pair_vals[parity][row] = v;
                 asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps
@@ -639,7 +682,7 @@ int run(const bf16* x, int ldx, const bf16* W, int ldw, TO* out, int ldo, const 
     if (e != cudaSuccess) return (int)e;
     rc = slb_launch(gemm_tc_decode_kernel<TO>, dim3((N + TC_BM - 1) / TC_BM, splits), dim3(TC_THREADS),
                     TC_SMEM, st, map_w, map_x, out, ldo, workspace, bias, M, N, K, ntok16, max_stages, status,
-                    swiglu, slb_pdl_early, slb_trace_arg());
+                    swiglu, slb_kernel_flags, slb_trace_arg());
     if (rc != 0 || splits == 1 || defer_sum) return rc;
     return slb_launch(gemm_tc_reduce_kernel<TO>, dim3((N + 255) / 256, M), dim3(256), 0, st,
                       (const float*)workspace, out, ldo, bias, M, N, splits);
@@ -681,13 +724,15 @@ int run_cluster(const bf16* x, int ldx, const bf16* W, int ldw, bf16* out, int l
     const int stages = stages_for(ntok16, max_stages);
     // the parked accumulator [ntok16][128] floats lives in the W stages of the ring
     if ((size_t)stages * A_STAGE_BYTES < (size_t)ntok16 * TC_BM * 4) return SLB_ERR_BAD_ARG;
+    // ... and the rows that the rotation exchanges (2 x 128 floats) in its x stages
+    if (EPI == EPI_ROPE && (size_t)stages * b_stage_bytes(ntok16) < 2 * TC_BM * sizeof(float)) return SLB_ERR_BAD_ARG;
     const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + b_stage_bytes(ntok16)) + TC_SMEM_TAIL;
     int* status = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&status, tc_status_word);
     if (e != cudaSuccess) return (int)e;
     return launch_cluster(gemm_tc_cluster_kernel<EPI>, dim3((N + TC_BM - 1) / TC_BM, splits),
                           dim3(TC_THREADS), splits, smem, st, map_w, map_x, out, ldo, bias, M, N, K, ntok16,
-                          max_stages, status, rope, slb_pdl_early, slb_trace_arg());
+                          max_stages, status, rope, slb_kernel_flags, slb_trace_arg());
 }
 
 int check_cluster_args(const bf16* x, int ldx, const bf16* W, int ldw, int M, int N, int K, int splits) {

@@ -81,6 +81,14 @@ def pdl_enabled() -> bool:
     return _pdl
 
 
+_FLAG_PDL_EARLY, _FLAG_EVICT_FIRST = 1, 2
+_evict_first = True
+
+
+def _kernel_flags() -> int:
+    return (_FLAG_PDL_EARLY if _pdl_early else 0) | (_FLAG_EVICT_FIRST if _evict_first else 0)
+
+
 def set_pdl_early(on: bool) -> None:
     """The long kernels (matrix products, decode attention) let their successor be scheduled
     at their start instead of after their main loop: its blocks become resident beside theirs
@@ -88,14 +96,23 @@ def set_pdl_early(on: bool) -> None:
     global _pdl_early
     _pdl_early = bool(on)
     for lib in _libs.values():
-        lib.slb_set_pdl_early(1 if _pdl_early else 0)
+        lib.slb_set_kernel_flags(_kernel_flags())
+
+
+def set_evict_first(on: bool) -> None:
+    """What a step streams once (weights, the cache) is fetched with the L2 policy "evict first",
+    so that the activations between the kernels stay in the L2 cache (on by default)."""
+    global _evict_first
+    _evict_first = bool(on)
+    for lib in _libs.values():
+        lib.slb_set_kernel_flags(_kernel_flags())
 
 
 def _apply_switches(lib: ctypes.CDLL) -> None:
     lib.slb_set_pdl.argtypes = [I]
     lib.slb_set_pdl(1 if _pdl else 0)
-    lib.slb_set_pdl_early.argtypes = [I]
-    lib.slb_set_pdl_early(1 if _pdl_early else 0)
+    lib.slb_set_kernel_flags.argtypes = [I]
+    lib.slb_set_kernel_flags(_kernel_flags())
     lib.slb_set_trace.argtypes = [P, I]
     lib.slb_set_trace(trace_buffer, len(_libs))
 

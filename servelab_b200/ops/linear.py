@@ -70,6 +70,11 @@ def _tc_ok(x, w, M):
 # float32 partial sums that a cluster of norm blocks adds.
 cluster_sums = True
 cluster_max_kblocks = 64   # k-blocks (of 64) per block up to which the cluster form is used
+cluster_max_tokens_per_block = 2  # tokens a block of the cluster may finish in its epilogue for a
+                                  # narrow product of more than 16 tokens.  With 8 (the cluster
+                                  # form up to 64 tokens at 8 splits) a step of 64 requests on the
+                                  # 7B shape took 4.57 ms against 4.33 ms with the library's GEMM
+                                  # and the q/k/v kernel, so the narrow products leave at 17.
 cluster_long_k_kblocks = 16      # products whose blocks stream more k-blocks than this ("long K") ...
 cluster_long_k_max_tokens = 64   # ... use the cluster form also from 17 tokens up to here
 fuse_qkv_rope = True       # the q|k|v product of a decode step rotates and writes the cache itself
@@ -88,8 +93,13 @@ def _cluster_ok(x, w, M) -> bool:
         return False
     if M <= _token_limit(w):
         return True
-    # long K ranges (down): streaming the weights is most of the time, and the cluster form
-    # beats the vendor GEMM between 17 and 64 tokens (30.8 against 34.1 us with the norm, 7B shape)
+    # Above that a block of the cluster finishes its share of the tokens one after the other in
+    # its epilogue (tokens rank, rank + splits, ...): the cluster form is taken while that
+    # share stays small, or for long K ranges (down), where streaming the weights is most of
+    # the time either way (30.8 against 34.1 us with the norm at 64 tokens, 7B shape).
+    splits = min(want, K.TC_MAX_CLUSTER)
+    if -(-M // splits) <= cluster_max_tokens_per_block:
+        return True
     return per_block > cluster_long_k_kblocks and M <= cluster_long_k_max_tokens
 
 
@@ -102,8 +112,7 @@ def qkv_projection(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Te
     size the product's epilogue takes; otherwise the product, then the q/k/v kernel."""
     M = x.shape[0]
     if (fuse_qkv_rope and x.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16
-            and head_dim in K.TC_ROPE_HEAD_DIMS and 0 < M <= _token_limit(w_qkv)
-            and K.tc_decode_splits(w_qkv.shape[0], w_qkv.shape[1]) > 1 and _tc_ok(x, w_qkv, M)):
+            and head_dim in K.TC_ROPE_HEAD_DIMS and _cluster_ok(x, w_qkv, M)):
         K.gemm_tc_qkv_rope(x, w_qkv, bias, positions, seq_of_token, block_table, page_size, inv_freq,
                            rotary_dim, q_out, k_cache, v_cache, num_heads, num_kv_heads, head_dim)
         return

@@ -36,12 +36,15 @@ def test_decode_steps_run_this_package_s_tensor_core_kernels(shape):
             assert L.which_kernel(*_ops(m, 2 * inter, h)) == "tc"
             assert K.tc_decode_splits(2 * inter, h) == 1
         assert L.which_kernel(*_ops(m, vocab, h), out_dtype=torch.float32) == "tc"
-    # the down product: long K ranges; partial sums up to 16 tokens unless it is small
+    # the down product: the cluster form up to 64 tokens (8 K splits: a block finishes 8 tokens)
     kinds = {m: L.which_kernel(*_ops(m, h, inter)) for m in (8, 32, 64, 65)}
-    if shape == "0.5b":       # short K ranges: the library above 16 tokens
+    if shape == "0.5b":       # few k-blocks a block: like the narrow products, the library above 16 tokens
         assert kinds == {8: "tc_cluster", 32: "vendor", 64: "vendor", 65: "vendor"}
     else:
         assert kinds == {8: "tc_cluster", 32: "tc_cluster", 64: "tc_cluster", 65: "vendor"}
+    # the narrow products above 16 tokens go to the library's GEMM
+    for n, k in ((qkv, h), (h, q)):
+        assert L.which_kernel(*_ops(16, n, k)) == "tc_cluster" and L.which_kernel(*_ops(17, n, k)) == "vendor"
 
 
 def test_many_tokens_go_to_the_vendor_gemm_and_ragged_or_float32_ones_to_cuda_cores():
