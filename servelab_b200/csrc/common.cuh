@@ -94,7 +94,13 @@ extern int slb_pdl_enabled;          // defined once per shared library (SLB_DEF
 // Switches of the long kernels (matrix products, decode attention), handed to them as one word:
 //   SLB_FLAG_PDL_EARLY    they let their successor be scheduled at their start instead of after
 //                         their main loop, so that its blocks become resident beside theirs
-//                         wherever an SM has room and fetch their first weight tiles meanwhile;
+//                         wherever an SM has room and fetch their first weight tiles meanwhile
+//                         (off: measured slower, 2.89 against 2.85 ms a batch-8 step of the 7B
+//                         shape -- the early fetches compete with the running product for the
+//                         memory, while fetches during its epilogue use time in which the
+//                         memory is idle; early starts of only the attention, only the o and
+//                         down products, or norms that release their successor late: 2.85,
+//                         2.95, 2.88 ms);
 //   SLB_FLAG_EVICT_FIRST  what they stream once a step (weights, cached keys and values) is
 //                         fetched with the L2 policy "evict first", so that the few hundred KB of
 //                         activations between the kernels (the float32 residual stream above
