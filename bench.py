@@ -229,7 +229,7 @@ def main(argv=None) -> int:
     def prompts(n, length=PROMPT_LEN):
         return [torch.randint(0, V, (length,), generator=gen).tolist() for _ in range(n)]
 
-    def timed_rounds(run_step, steps, rounds, with_clocks, warmup=0):
+    def timed_rounds(run_step, steps, rounds, with_clocks, warmup=0, profile=False):
         """``warmup`` untimed steps, then ``rounds`` regions of ``steps`` steps between CUDA events;
         (ms per step of each region, one clock record over warm-up and regions: the sampler's
         own start takes longer than a short region)."""
@@ -237,6 +237,8 @@ def main(argv=None) -> int:
             clocks.start()
         for _ in range(warmup):
             run_step()
+        if profile:
+            torch.cuda.profiler.start()
         times = []
         for _ in range(rounds):
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -247,6 +249,8 @@ def main(argv=None) -> int:
             stop.record()
             torch.cuda.synchronize()
             times.append(start.elapsed_time(stop) / steps)
+        if profile:
+            torch.cuda.profiler.stop()
         return times, (clocks.stop() if with_clocks else None)
 
     def decode_entries(seqs):
@@ -308,14 +312,11 @@ def main(argv=None) -> int:
         for _ in range(3):
             one_step()
         k0 = K.launch_count
-        if args.profile_region:
-            torch.cuda.profiler.start()
-        dev, record = timed_rounds(one_step, steps, rounds, with_clocks, warmup=max(0, warmup - 3) + (200 if with_clocks else 0))
-        if args.profile_region:
-            torch.cuda.profiler.stop()
+        dev, record = timed_rounds(one_step, steps, rounds, with_clocks, profile=args.profile_region,
+                                   warmup=max(0, warmup - 3) + (200 if with_clocks and not args.profile_region else 0))
         ctx_tokens = sum(s.get_len() for s in seqs)
         per_graph = runner.graph_kernel_launches.get(batch, 0)
-        ran = steps * rounds + max(0, warmup - 3) + (200 if with_clocks else 0)     # steps since k0
+        ran = steps * rounds + max(0, warmup - 3) + (200 if with_clocks and not args.profile_region else 0)
         launches = round(((K.launch_count - k0) + per_graph * ran) / ran * steps)   # of one timed region
         desc_bytes = runner._graphs[batch][1]._dev.numel() * 4 if batch in runner._graphs else 0
         if timeline is not None and with_clocks:
