@@ -1,5 +1,5 @@
 """Writes tests/golden/plain_tiny.npz: logits of the plain implementation
-(tests/plain_model.py) on the three tiny random models, so that a change in the
+(tests/plain_model.py) on the tiny random models of tests/helpers.py, so that a change in the
 plain implementation itself shows up.
 
 The reference's own model code (servelab/models/decoder.py) is absent from its

@@ -19,10 +19,14 @@ pytestmark = pytest.mark.gpu
 # Largest absolute logit error allowed against the float32 plain implementation.
 # float32: rounding of a handful of float32 reductions.  bfloat16: inputs of
 # every matrix product and the cache are rounded to 8 bits of mantissa; the bound of
-# a configuration is about twice the worst error its tests print (logits of A-D have a
-# standard deviation near 0.2, those of E, whose attention is peaked, near 1.2).
+# a configuration is about twice the worst error its tests print (observed: A 3.4e-3, B 6.2e-3,
+# C 5.8e-3, D 5.6e-3 on logits with a standard deviation near 0.2; E, whose attention is peaked,
+# 2.6e-1 and 3.3e-1 for its long request on logits with a standard deviation near 1.2 that
+# reach 6.6 -- a key lost or seen too early there moves them by more than that: with the
+# newest key hidden from the decode kernel, or one future key visible to the prefill kernel,
+# the tests of D and E fail).
 TOL = {"float32": 1e-5, "bfloat16": 2e-2}
-TOL_BF16 = {"A": 1.2e-2, "B": 1.2e-2, "C": 1.2e-2, "D": 1.2e-2, "E": 4e-1}
+TOL_BF16 = {"A": 8e-3, "B": 1.2e-2, "C": 1.2e-2, "D": 1.2e-2, "E": 6e-1}
 TOL_F32 = {"E": 5e-5}
 LENGTHS = [70, 45, 97, 33, 58, 81]
 

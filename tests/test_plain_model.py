@@ -20,8 +20,13 @@ def test_golden_file_still_matches():
     spec.loader.exec_module(mod)
     now = mod.compute()
     gold = np.load(os.path.join(HERE, "golden", "plain_tiny.npz"))
-    for k in gold.files:
-        np.testing.assert_allclose(now[k], gold[k], rtol=0, atol=2e-6, err_msg=k)
+    # every configuration of the tests, not whatever the file happens to hold
+    assert sorted(gold.files) == sorted(f"{name}_{what}" for name in H.CONFIGS for what in ("ids", "logits_rows"))
+    for name, (cfg, _, _) in H.CONFIGS.items():
+        scale = float(np.abs(gold[f"{name}_logits_rows"]).max())
+        assert np.array_equal(now[f"{name}_ids"], gold[f"{name}_ids"]), name
+        np.testing.assert_allclose(now[f"{name}_logits_rows"], gold[f"{name}_logits_rows"], rtol=0,
+                                   atol=2e-6 * max(1.0, scale), err_msg=name)
 
 
 def test_rms_norm_and_swiglu_formulas():
