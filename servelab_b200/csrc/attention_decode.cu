@@ -588,9 +588,12 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
                     lv[j] = in ? ld_cluster_f32(cl_ml + r * 2 + 1, (uint32_t)j) : 0.f;
                     ov[j] = in ? ld_cluster_f32(cl_o + r * D + d, (uint32_t)j) : 0.f;
                 }
-                float M = -INFINITY;
+                float M = -INFINITY, touched = 0.f;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) M = fmaxf(M, mv[j]);
+                for (int j = 0; j < 8; ++j) {
+                    M = fmaxf(M, mv[j]);
+                    touched += lv[j] + ov[j];              // (every loaded value, also of empty splits)
+                }
                 float L = 0.f, acc = 0.f;
                 if (M != -INFINITY) {
 #pragma unroll
@@ -603,9 +606,17 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
                 }
                 out[(size_t)s * ldo + (size_t)(kvh * g + h0 + r) * D + d] =
                     __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+                // what was read has arrived once this store has its operand (see below)
+                asm volatile("st.volatile.shared.f32 [%0], %1;" ::"r"(smem_u32(red_o + tid)), "f"(touched + M) : "memory");
             }
         }
-        cluster_sync_all_threads();                        // nobody leaves while its result is read
+        // A relaxed arrival: it orders nothing, so the stores to `out` are not waited for (with a
+        // releasing one a block spent microseconds here while the next product's weight fetches kept
+        // the memory busy).  What was read from the other blocks has arrived: every loaded value went
+        // into a volatile store to this block's own idle shared memory (red_o), which needs it in a
+        // register, and the arrival follows those stores.
+        asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
+                                                           // nobody leaves while its result is read
         if (threadIdx.x == 0) slb_trace_event(tr, 4, SLB_TR_END + 1);
         return;
     }

@@ -35,6 +35,7 @@ namespace {
 constexpr int TC_BM = 128;            // rows of W per block (MMA M)
 constexpr int TC_BK = 64;             // k per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int TC_MAX_TOK = 64;        // MMA N
+constexpr int tc_cluster_single_max_tokens = 16;   // up to here the cluster form finishes one token at a time
 constexpr int TC_MAX_STAGES = 12;     // the ring is as deep as shared memory allows
 constexpr int TC_THREADS = 192;       // warp 0 loader, warp 1 MMA + TMEM, warps 2..5 epilogue
 constexpr int TC_TMEM_COLS = 64;
@@ -136,12 +137,44 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 // grid (row tiles of W, K splits).  ntok16: tokens padded to a multiple of 16.
 // splits == 1: `out` receives the result (+ bias) in its dtype; otherwise `partial`
 // receives float32 [split][M][N].
+// The x operand is the z of a product with the residual-and-norm epilogue (EPI_RESID below): every token's result is to be multiplied by
+// rstd[tok], from the sums of squares that product left per row tile.  sumsq == null: no scale.
+struct RowScale {
+    const float* sumsq;                 // [tiles][M]
+    int tiles;
+    float width;                        // elements of a normed row
+    float eps;
+};
+// rstd[t] = 1 / rms of token t's input row for all M tokens, by four warps (`warp4` 0..3) that a
+// named barrier joins afterwards: a warp takes tokens warp4, warp4 + 4, ..., its lanes the tiles,
+// and the loads of four tokens are in flight together (one trip to the L2 for a decode step of up
+// to 16 requests).  The order of additions is fixed.
+__device__ __forceinline__ void rows_rstd(const RowScale& rs, int M, int warp4, int lane, float* rstd) {
+    for (int t0 = warp4; t0 < M; t0 += 16) {
+        float part[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int t = t0 + 4 * j;
+            part[j] = 0.f;
+            if (t < M)
+                for (int tile = lane; tile < rs.tiles; tile += 32) part[j] += __ldcg(rs.sumsq + (size_t)tile * M + t);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int t = t0 + 4 * j;
+            const float ss = warp_sum(part[j]);
+            if (t < M && lane == 0) rstd[t] = 1.0f / sqrtf(ss / rs.width + rs.eps);
+        }
+    }
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     TO* __restrict__ out, int ldo, float* __restrict__ partial, const float* __restrict__ bias,
     int M, int N, int K, int ntok16, int max_stages, int* __restrict__ status, int swiglu,
-    int flags, const SlbTraceArg tr) {
+    int flags, const RowScale rs, const SlbTraceArg tr) {
+    __shared__ float rstd_s[TC_MAX_TOK];                    // RowScale: 1 / rms of every token's input row
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -242,6 +275,11 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
                                                              // preceding kernel has finished
         if (tracer) slb_trace_event(tr, 1, SLB_TR_WAITED);
         const int quarter = warp & 3;                        // TMEM lanes this warp may read
+        const bool scaled = rs.sumsq != nullptr;
+        if (scaled) {                                        // in the shadow of the main loop
+            rows_rstd(rs, M, quarter, lane, rstd_s);
+            asm volatile("bar.sync 1, 128;" ::: "memory");               // the four epilogue warps
+        }
         const int row = quarter * 32 + lane;                 // row of the tile = row of W
         const int n = n0 + row;
         bool ok = true;
@@ -280,8 +318,9 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
                         for (int j = 0; j < 16; ++j) {
                             const int tok = c0 + j;
                             if (tok >= M) break;
-                            const float gt = __uint_as_float(v[j]);
-                            const float up = ups[row * ld_ups + tok];
+                            const float rstd = scaled ? rstd_s[tok] : 1.f;
+                            const float gt = __uint_as_float(v[j]) * rstd;
+                            const float up = ups[row * ld_ups + tok] * rstd;
                             out[(size_t)tok * ldo + col] = from_float<TO>(gt / (1.0f + expf(-gt)) * up);
                         }
                     }
@@ -302,7 +341,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
                 for (int j = 0; j < 16; ++j) {
                     const int tok = c0 + j;
                     if (tok >= M) break;
-                    const float val = __uint_as_float(v[j]);
+                    const float val = __uint_as_float(v[j]) * (scaled ? rstd_s[tok] : 1.f);   // (partial sums too)
                     if (splits == 1)
                         out[(size_t)tok * ldo + n] = from_float<TO>(val + (bias ? bias[n] : 0.f));
                     else
@@ -350,7 +389,24 @@ __global__ void gemm_tc_reduce_kernel(const float* __restrict__ partial, TO* __r
 //              token's position, q written to q_out, k and v into the token's slot of the
 //              paged cache (the arithmetic of the kernel in rope_cache.cu).  A row tile
 //              must hold whole heads: head sizes 16, 32, 64, 128.
-enum { EPI_STORE = 0, EPI_ROPE = 1 };
+//   EPI_RESID  the product updates the float32 residual stream and prepares the RMS norm that
+//              follows, so that no norm kernel runs: resid[tok, n] += sum + bias[n];
+//              z[tok, n] = bfloat16(resid[tok, n] * norm_weight[n]) -- the normed row without its
+//              factor 1 / rms, which is one number a token; sumsq[tile][tok] = the sum of squares of
+//              the tile's 128 updated values.  The product that consumes z multiplies its result
+//              by rstd[tok] = 1 / sqrt(sum over tiles of sumsq / N + eps) in its epilogue
+//              (RowScale), because W (z rstd) = rstd (W z).
+enum { EPI_STORE = 0, EPI_ROPE = 1, EPI_RESID = 2 };
+
+struct ResidEpilogue {
+    float* resid;                       // [M][ld] float32, updated in place
+    int ld;
+    const float* norm_weight;           // [N]
+    bf16* z;                            // [M][ldz]
+    int ldz;
+    float* sumsq;                       // [row tiles][M]
+};
+
 
 struct RopeEpilogue {
     const float* bias;                  // [N] or null
@@ -381,11 +437,40 @@ __device__ __forceinline__ uint32_t cluster_size() {
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The two halves of a cluster barrier that only says "I have read what I needed of your shared
+// memory": arriving orders nothing (the values read have been used in arithmetic by then), so the
+// block's stores to global memory after it are not waited for -- with a releasing arrival after
+// them a block spent up to 4 us at the barrier while the next product's weight fetches kept the
+// memory busy.
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+// ... once `value` exists, i.e. once the remote loads it was computed from have returned: the
+// value is first stored (volatile, to a word of this block's own shared memory that nothing
+// reads), which needs it in a register, and the arrival follows the store.  Without that the
+// compiler may place the arrival before the additions, and a block of the cluster could leave,
+// and its shared memory be refilled by the next kernel, under a load in flight.
+__device__ __forceinline__ void cluster_arrive_relaxed_after(float value, float* sink) {
+    asm volatile("st.volatile.shared.f32 [%0], %1;\n\tbarrier.cluster.arrive.relaxed.aligned;"
+                 ::"r"(smem_u32(sink)), "f"(value) : "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+}
 __device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank) {
     uint32_t a;
     float v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(rank));
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ float4 ld_peer_f32x4(uint32_t local_addr, uint32_t rank) {     // 16-byte aligned
+    uint32_t a;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a) : "memory");
     return v;
 }
 
@@ -426,12 +511,12 @@ __device__ __forceinline__ RopeTarget rope_target(const RopeEpilogue& rope, int 
     return t;
 }
 
-template <int EPI>
+template <int EPI, bool WIDE>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     bf16* __restrict__ out, int ldo, const float* __restrict__ bias, int M, int N, int K, int ntok16,
-    int max_stages, int* __restrict__ status, const RopeEpilogue rope, int flags,
-    const SlbTraceArg tr) {
+    int max_stages, int* __restrict__ status, const RopeEpilogue rope, const ResidEpilogue res,
+    const RowScale rs, int flags, const SlbTraceArg tr) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -449,7 +534,10 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     // the next product's first weight tiles while this one finishes (a block 3 KB larger cost
     // 9 us a layer).  The rows that the rotation exchanges live in the idle x stages of the ring.
     __shared__ int tok_pos[TC_MAX_TOK], tok_page[TC_MAX_TOK]; // EPI_ROPE: position and cache page of every token
+    __shared__ float rstd_s[TC_MAX_TOK];                      // RowScale: 1 / rms of every token's input row
+    __shared__ float warp_sq[2][4];                           // EPI_RESID: sums of squares per epilogue warp
     float (*pair_vals)[TC_BM] = reinterpret_cast<float (*)[TC_BM]>(b_stage);         // [2][128]: 1 KB
+    float* sink = reinterpret_cast<float*>(b_stage) + 2 * TC_BM;                     // [192] behind them
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * TC_BM;
@@ -479,9 +567,10 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     const uint32_t tmem_d = *tmem_slot;
     float* acc = reinterpret_cast<float*>(a_stage);          // [ntok16][TC_BM] once the ring is idle
     RopeTarget first_target = {};                            // EPI_ROPE: for token `rank` of this block
+    float resid_ahead0 = 0.f, resid_ahead1 = 0.f, norm_w = 0.f, bias_n = 0.f;   // EPI_RESID: fetched while the main loop runs
     if (flags & SLB_FLAG_PDL_EARLY) pdl_launch_dependents();
     const bool tracer = threadIdx.x == 64;                  // lane 0 of the first epilogue warp
-    constexpr int TRACE_ID = EPI == EPI_ROPE ? 3 : 2;
+    constexpr int TRACE_ID = EPI == EPI_ROPE ? 3 : (EPI == EPI_RESID ? 7 : 2);
     if (tracer) slb_trace_event(tr, TRACE_ID, SLB_TR_START);
 
     if (warp == 0) {
@@ -539,6 +628,17 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
         if (tracer) slb_trace_event(tr, TRACE_ID, SLB_TR_WAITED);
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
+        if (rs.sumsq != nullptr) rows_rstd(rs, M, quarter, lane, rstd_s);   // in the shadow of the main loop
+        if constexpr (EPI == EPI_RESID && !WIDE) {
+            // what this thread's column needs of the first two tokens of this block's share
+            const int tok0 = (int)cluster_rank(), tok1 = tok0 + (int)cluster_size();
+            if (n0 + row < N) {
+                norm_w = res.norm_weight[n0 + row];
+                if (bias) bias_n = bias[n0 + row];
+                if (tok0 < M) resid_ahead0 = __ldcg(res.resid + (size_t)tok0 * res.ld + n0 + row);
+                if (tok1 < M) resid_ahead1 = __ldcg(res.resid + (size_t)tok1 * res.ld + n0 + row);
+            }
+        }
         if constexpr (EPI == EPI_ROPE) {
             // In the shadow of the main loop: the positions and cache pages of the step's tokens
             // (one token a thread: dependent loads from global memory, which would otherwise be
@@ -559,7 +659,8 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");               // the four epilogue warps
             const int tok0 = (int)cluster_rank();
-            if (tok0 < M) first_target = rope_target(rope, tok0, tok_pos[tok0], tok_page[tok0], n0 + row, row, N);
+            if (!WIDE && tok0 < M)
+                first_target = rope_target(rope, tok0, tok_pos[tok0], tok_page[tok0], n0 + row, row, N);
         }
         bool ok = true;
         if (iters > 0) {
@@ -584,18 +685,111 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     cluster_sync_all();                                      // every block's acc is complete
+    if (tracer) slb_trace_event(tr, TRACE_ID, SLB_TR_END + 1);
 
     if (warp >= 2) {
         // ------------------------------- epilogue, part 2: this block's share of the tokens
         const int row = (warp & 3) * 32 + lane;
         const int n = n0 + row;
         const uint32_t rank = cluster_rank(), nranks = cluster_size();
-        int parity = 0;
+        bool arrived = false;
+        if constexpr (WIDE) {
+            // Steps of more than 16 tokens, where a block finishes up to eight tokens: a warp takes a
+            // whole token (a lane four consecutive rows of the tile, fetched from every block with
+            // one 16-byte load), the four warps the block's tokens in turn.  The rotation partner
+            // and the sum of squares of a token then lie within one warp: shuffles, no barrier.
+            const int w4 = warp & 3, r4 = 4 * lane, n4 = n0 + r4;
+            float4 nw = make_float4(0.f, 0.f, 0.f, 0.f), bs = nw;
+            if (EPI != EPI_ROPE)
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    if (n4 + c < N) {
+                        if (EPI == EPI_RESID) (&nw.x)[c] = res.norm_weight[n4 + c];
+                        if (bias) (&bs.x)[c] = bias[n4 + c];
+                    }
+            for (int tok = (int)rank + w4 * (int)nranks; tok < M; tok += 4 * (int)nranks) {
+                const uint32_t addr = smem_u32(acc + tok * TC_BM + r4);
+                float4 part[TC_MAX_CLUSTER];
+#pragma unroll
+                for (uint32_t p = 0; p < (uint32_t)TC_MAX_CLUSTER; ++p)
+                    part[p] = p < nranks ? ld_peer_f32x4(addr, p) : make_float4(0.f, 0.f, 0.f, 0.f);
+                float before[4] = {0.f, 0.f, 0.f, 0.f};
+                if constexpr (EPI == EPI_RESID)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        if (n4 + c < N) before[c] = __ldcg(res.resid + (size_t)tok * res.ld + n4 + c);
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (uint32_t p = 0; p < (uint32_t)TC_MAX_CLUSTER; ++p) {
+                    v[0] += part[p].x; v[1] += part[p].y; v[2] += part[p].z; v[3] += part[p].w;
+                }
+                if (tok + 4 * (int)nranks >= M) {            // this warp's last values of other blocks are here
+                    cluster_arrive_relaxed_after((v[0] + v[1]) + (v[2] + v[3]), sink + threadIdx.x);
+                    arrived = true;
+                }
+                if (rs.sumsq != nullptr) {
+                    const float rstd = rstd_s[tok];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) v[c] *= rstd;
+                }
+                if constexpr (EPI == EPI_STORE) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        if (n4 + c < N) out[(size_t)tok * ldo + n4 + c] = __float2bfloat16_rn(v[c] + (&bs.x)[c]);
+                } else if constexpr (EPI == EPI_RESID) {
+                    float sq = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        if (n4 + c < N) {
+                            const float r = before[c] + (v[c] + (&bs.x)[c]);
+                            res.resid[(size_t)tok * res.ld + n4 + c] = r;
+                            res.z[(size_t)tok * res.ldz + n4 + c] = __float2bfloat16_rn(r * (&nw.x)[c]);
+                            sq += r * r;
+                        }
+                    sq = warp_sum(sq);
+                    if (lane == 0) res.sumsq[(size_t)blockIdx.x * M + tok] = sq;
+                } else {
+                    // (host: the width is a multiple of 16, half the rotary size a multiple of 4, so a
+                    // lane's four rows lie in one head, on one side of the rotation, or beyond N)
+                    const int D = rope.D, half = rope.inv_freq != nullptr ? rope.rotary_dim >> 1 : 0;
+                    const int j = n4 / D, e0 = n4 - j * D;
+                    const bool in = n4 < N, is_v = j >= rope.H + rope.Hkv;
+                    const bool rotate = in && !is_v && e0 < 2 * half, first_half = e0 < half;
+                    if (in && rope.bias)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) v[c] += rope.bias[n4 + c];
+                    const int partner = rotate ? (first_half ? lane + (half >> 2) : lane - (half >> 2)) : lane;
+                    float other[4];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) other[c] = __shfl_sync(0xffffffffu, v[c], partner);
+                    const int pos = tok_pos[tok], page = tok_page[tok];
+                    if (rotate) {
+                        const int i0 = first_half ? e0 : e0 - half;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            float sn, cs;
+                            sincosf((float)pos * rope.inv_freq[i0 + c], &sn, &cs);
+                            v[c] = first_half ? v[c] * cs - other[c] * sn : v[c] * cs + other[c] * sn;
+                        }
+                    }
+                    bf16* dst = nullptr;
+                    if (in && j < rope.H) {
+                        dst = rope.q_out + (size_t)tok * rope.ld_q + (size_t)j * D + e0;
+                    } else if (in && rope.k_cache != nullptr && page >= 0) {
+                        const int kvh = is_v ? j - rope.H - rope.Hkv : j - rope.H;
+                        dst = (is_v ? rope.v_cache : rope.k_cache) +
+                              (((size_t)page * rope.Hkv + kvh) * rope.page_size + pos % rope.page_size) * D + e0;
+                    }
+                    if (dst != nullptr)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) dst[c] = __float2bfloat16_rn(v[c]);
+                }
+            }
+        } else {
+        int parity = 0, turn = 0;
         for (int tok = (int)rank; tok < M; tok += (int)nranks) {
             // the blocks' values are fetched together and then added in rank order: a loop of
-            // load-then-add would wait for every remote load in turn.  (Fetching those of four
-            // tokens together was tried for steps of up to 64 tokens: the registers it takes cost
-            // the 8-token step 0.13 ms, and at 64 tokens the library's GEMM stayed faster.)
+            // load-then-add would wait for every remote load in turn
             const uint32_t addr = smem_u32(acc + tok * TC_BM + row);
             float part[TC_MAX_CLUSTER];
 #pragma unroll
@@ -603,8 +797,30 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
             float sum = 0.f;
 #pragma unroll
             for (uint32_t p = 0; p < (uint32_t)TC_MAX_CLUSTER; ++p) sum += part[p];
+            if (tok + (int)nranks >= M) {                    // the last values of other blocks are here
+                cluster_arrive_relaxed_after(sum, sink + threadIdx.x);
+                arrived = true;
+            }
+            if (rs.sumsq != nullptr) sum *= rstd_s[tok];
             if constexpr (EPI == EPI_STORE) {
                 if (n < N) out[(size_t)tok * ldo + n] = __float2bfloat16_rn(sum + (bias ? bias[n] : 0.f));
+            } else if constexpr (EPI == EPI_RESID) {
+                float r = 0.f;
+                if (n < N) {
+                    float* dst = res.resid + (size_t)tok * res.ld + n;
+                    const float before = turn == 0 ? resid_ahead0 : (turn == 1 ? resid_ahead1 : __ldcg(dst));
+                    r = before + (sum + bias_n);
+                    *dst = r;
+                    res.z[(size_t)tok * res.ldz + n] = __float2bfloat16_rn(r * norm_w);
+                }
+                ++turn;
+                const float sq = warp_sum(r * r);
+                if (lane == 0) warp_sq[parity][warp & 3] = sq;
+                asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps
+                if (row == 0)
+                    res.sumsq[(size_t)blockIdx.x * M + tok] =
+                        ((warp_sq[parity][0] + warp_sq[parity][1]) + warp_sq[parity][2]) + warp_sq[parity][3];
+                parity ^= 1;
             } else {
                 const RopeTarget t = tok == (int)rank ? first_target
                                                       : rope_target(rope, tok, tok_pos[tok], tok_page[tok], n, row, N);
@@ -619,9 +835,13 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
                 parity ^= 1;
             }
         }
+        }
+        if (!arrived) cluster_arrive_relaxed();              // (a block without a token of its own)
+    } else {
+        cluster_arrive_relaxed();
     }
     __syncwarp();
-    cluster_sync_all();                                      // no block leaves while its acc is read
+    cluster_wait();                                          // no block leaves while its acc is read
     if (tracer) slb_trace_event(tr, TRACE_ID, SLB_TR_END);
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -665,7 +885,7 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box
 template <typename TO>
 int run(const bf16* x, int ldx, const bf16* W, int ldw, TO* out, int ldo, const float* bias,
         float* workspace, int M, int N, int K, int splits, int max_stages, int defer_sum, int swiglu,
-        cudaStream_t st) {
+        const RowScale& rs, cudaStream_t st) {
     CUtensorMap map_w, map_x;
     const int ntok16 = (M + 15) / 16 * 16;
     int rc = make_map(&map_w, W, N, K, ldw, TC_BM);
@@ -682,7 +902,7 @@ int run(const bf16* x, int ldx, const bf16* W, int ldw, TO* out, int ldo, const 
     if (e != cudaSuccess) return (int)e;
     rc = slb_launch(gemm_tc_decode_kernel<TO>, dim3((N + TC_BM - 1) / TC_BM, splits), dim3(TC_THREADS),
                     TC_SMEM, st, map_w, map_x, out, ldo, workspace, bias, M, N, K, ntok16, max_stages, status,
-                    swiglu, slb_kernel_flags, slb_trace_arg());
+                    swiglu, slb_kernel_flags, rs, slb_trace_arg());
     if (rc != 0 || splits == 1 || defer_sum) return rc;
     return slb_launch(gemm_tc_reduce_kernel<TO>, dim3((N + 255) / 256, M), dim3(256), 0, st,
                       (const float*)workspace, out, ldo, bias, M, N, splits);
@@ -711,28 +931,38 @@ int launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, int cluster_
 
 template <int EPI>
 int run_cluster(const bf16* x, int ldx, const bf16* W, int ldw, bf16* out, int ldo, const float* bias,
-                int M, int N, int K, int splits, int max_stages, const RopeEpilogue& rope, cudaStream_t st) {
+                int M, int N, int K, int splits, int max_stages, const RopeEpilogue& rope,
+                const ResidEpilogue& res, const RowScale& rs, cudaStream_t st) {
     CUtensorMap map_w, map_x;
     const int ntok16 = (M + 15) / 16 * 16;
     int rc = make_map(&map_w, W, N, K, ldw, TC_BM);
     if (rc != 0) return rc;
     rc = make_map(&map_x, x, M, K, ldx, ntok16);
     if (rc != 0) return rc;
-    static unsigned long long configured = 0;               // per instantiation, a bit per device
-    rc = slb_configure(&configured, gemm_tc_cluster_kernel<EPI>, TC_SMEM_BUDGET);
+    static unsigned long long configured = 0, configured_wide = 0;   // per instantiation, a bit per device
+    // the warp-per-token epilogue: above 16 tokens, where its shapes allow it (see the kernel)
+    const bool few = M <= tc_cluster_single_max_tokens ||
+                     (EPI == EPI_ROPE && (N % 16 != 0 || (rope.inv_freq != nullptr && rope.rotary_dim % 8 != 0)));
+    rc = few ? slb_configure(&configured, gemm_tc_cluster_kernel<EPI, false>, TC_SMEM_BUDGET)
+             : slb_configure(&configured_wide, gemm_tc_cluster_kernel<EPI, true>, TC_SMEM_BUDGET);
     if (rc != 0) return rc;
     const int stages = stages_for(ntok16, max_stages);
     // the parked accumulator [ntok16][128] floats lives in the W stages of the ring
     if ((size_t)stages * A_STAGE_BYTES < (size_t)ntok16 * TC_BM * 4) return SLB_ERR_BAD_ARG;
     // ... and the rows that the rotation exchanges (2 x 128 floats) in its x stages
-    if (EPI == EPI_ROPE && (size_t)stages * b_stage_bytes(ntok16) < 2 * TC_BM * sizeof(float)) return SLB_ERR_BAD_ARG;
+    // and a word a thread (see cluster_arrive_relaxed_after)
+    if ((size_t)stages * b_stage_bytes(ntok16) < (2 * TC_BM + TC_THREADS) * sizeof(float)) return SLB_ERR_BAD_ARG;
     const size_t smem = 1024 + (size_t)stages * (A_STAGE_BYTES + b_stage_bytes(ntok16)) + TC_SMEM_TAIL;
     int* status = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&status, tc_status_word);
     if (e != cudaSuccess) return (int)e;
-    return launch_cluster(gemm_tc_cluster_kernel<EPI>, dim3((N + TC_BM - 1) / TC_BM, splits),
+    if (few)
+        return launch_cluster(gemm_tc_cluster_kernel<EPI, false>, dim3((N + TC_BM - 1) / TC_BM, splits),
+                              dim3(TC_THREADS), splits, smem, st, map_w, map_x, out, ldo, bias, M, N, K, ntok16,
+                              max_stages, status, rope, res, rs, slb_kernel_flags, slb_trace_arg());
+    return launch_cluster(gemm_tc_cluster_kernel<EPI, true>, dim3((N + TC_BM - 1) / TC_BM, splits),
                           dim3(TC_THREADS), splits, smem, st, map_w, map_x, out, ldo, bias, M, N, K, ntok16,
-                          max_stages, status, rope, slb_kernel_flags, slb_trace_arg());
+                          max_stages, status, rope, res, rs, slb_kernel_flags, slb_trace_arg());
 }
 
 int check_cluster_args(const bf16* x, int ldx, const bf16* W, int ldw, int M, int N, int K, int splits) {
@@ -750,16 +980,38 @@ int check_cluster_args(const bf16* x, int ldx, const bf16* W, int ldw, int M, in
 extern "C" {
 
 // out[M, N] = x . W^T (+ bias), bfloat16, the K splits of a row tile as one cluster (at most 8):
-// no workspace, no second kernel.
+// no workspace, no second kernel.  scale_sumsq: as for slb_gemm_tc_decode_bf16.
 int slb_gemm_tc_cluster_bf16(const bf16* x, int ldx, const bf16* W, int ldw, bf16* out, int ldo,
                              const float* bias, int M, int N, int K, int splits, int max_stages,
-                             cudaStream_t st) {
+                             const float* scale_sumsq, int scale_tiles, float scale_eps, cudaStream_t st) {
     if (M <= 0 || N <= 0) return 0;
     if (ldo < N || out == nullptr) return SLB_ERR_BAD_ARG;
     const int rc = check_cluster_args(x, ldx, W, ldw, M, N, K, splits);
     if (rc != 0) return rc;
+    if (scale_sumsq != nullptr && scale_tiles <= 0) return SLB_ERR_BAD_ARG;
+    const RowScale rs = {scale_sumsq, scale_tiles, (float)K, scale_eps};
     return run_cluster<EPI_STORE>(x, ldx, W, ldw, out, ldo, bias, M, N, K, splits, max_stages, RopeEpilogue{},
-                                  st);
+                                  ResidEpilogue{}, rs, st);
+}
+
+// The product that closes a residual branch together with the RMS norm that follows it:
+// resid[M, N] (float32) += x . W^T (+ bias); z[M, N] = bfloat16(resid * norm_weight), the normed
+// rows without their factor 1 / rms; sumsq[row tiles][M] = per 128-column tile, the sum of squares
+// of the updated resid.  The product that reads z passes sumsq on (scale_sumsq below) and multiplies
+// its result by 1 / sqrt(sum(sumsq) / N + eps) per token.  sumsq needs (N + 127) / 128 * M floats.
+int slb_gemm_tc_resid_norm_bf16(const bf16* x, int ldx, const bf16* W, int ldw, const float* bias,
+                                float* resid, int ld_resid, const float* norm_weight, bf16* z, int ldz,
+                                float* sumsq, int M, int N, int K, int splits, int max_stages,
+                                cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (resid == nullptr || norm_weight == nullptr || z == nullptr || sumsq == nullptr || ld_resid < N ||
+        ldz < N)
+        return SLB_ERR_BAD_ARG;
+    const int rc = check_cluster_args(x, ldx, W, ldw, M, N, K, splits);
+    if (rc != 0) return rc;
+    const ResidEpilogue res = {resid, ld_resid, norm_weight, z, ldz, sumsq};
+    return run_cluster<EPI_RESID>(x, ldx, W, ldw, nullptr, 0, bias, M, N, K, splits, max_stages, RopeEpilogue{},
+                                  res, RowScale{}, st);
 }
 
 // The q|k|v product of an attention layer with what follows it: W is [(H + 2 Hkv) D, K]
@@ -772,7 +1024,8 @@ int slb_gemm_tc_qkv_rope_bf16(const bf16* x, int ldx, const bf16* W, int ldw, co
                               const int* positions, const int* seq_of_token, const int* block_table,
                               int max_pages, int page_size, int num_pages, const float* inv_freq,
                               int rotary_dim, bf16* q_out, int ld_q, bf16* k_cache, bf16* v_cache, int M,
-                              int H, int Hkv, int D, int K, int splits, int max_stages, cudaStream_t st) {
+                              int H, int Hkv, int D, int K, int splits, int max_stages,
+                              const float* scale_sumsq, int scale_tiles, float scale_eps, cudaStream_t st) {
     if (M <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || D < 16 || D > TC_BM || TC_BM % D || page_size <= 0 || max_pages <= 0)
         return SLB_ERR_BAD_ARG;
@@ -787,18 +1040,25 @@ int slb_gemm_tc_qkv_rope_bf16(const bf16* x, int ldx, const bf16* W, int ldw, co
     if (cudaGetSymbolAddress((void**)&status, tc_status_word) != cudaSuccess) return SLB_ERR_BAD_ARG;
     RopeEpilogue rope = {bias, positions, seq_of_token, block_table, max_pages, page_size, num_pages, inv_freq,
                          inv_freq != nullptr ? rotary_dim : 0, q_out, ld_q, k_cache, v_cache, H, Hkv, D};
-    return run_cluster<EPI_ROPE>(x, ldx, W, ldw, nullptr, 0, nullptr, M, N, K, splits, max_stages, rope, st);
+    if (scale_sumsq != nullptr && scale_tiles <= 0) return SLB_ERR_BAD_ARG;
+    const RowScale rs = {scale_sumsq, scale_tiles, (float)K, scale_eps};
+    return run_cluster<EPI_ROPE>(x, ldx, W, ldw, nullptr, 0, nullptr, M, N, K, splits, max_stages, rope,
+                                 ResidEpilogue{}, rs, st);
 }
 
 // workspace: float32 [splits * M * N] when splits > 1 (may be null otherwise).
 // max_stages: cap on the depth of the shared-memory ring (0: as deep as fits).
+// scale_sumsq [scale_tiles][M] (or null): x is the z of slb_gemm_tc_resid_norm_bf16, whose rows still
+// lack their factor 1 / rms; the result of token t is multiplied by
+// 1 / sqrt(sum over tiles of scale_sumsq[.][t] / K + scale_eps) before the bias and the activation.
 // defer_sum: with splits > 1, leave the partial sums [splits][M][N] in the workspace
 // and launch no reduction (the consumer adds them; `out` and `bias` are unused).
 // swiglu: W's rows are gates and ups alternating in runs of 64; out is [M, N / 2] =
 // silu(gate) * up (one K split, no bias).
 int slb_gemm_tc_decode_bf16(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo,
                             const float* bias, float* workspace, int out_f32, int M, int N, int K,
-                            int splits, int max_stages, int defer_sum, int swiglu, cudaStream_t st) {
+                            int splits, int max_stages, int defer_sum, int swiglu,
+                            const float* scale_sumsq, int scale_tiles, float scale_eps, cudaStream_t st) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ldw % 8 || ldw < K || (!swiglu && ldo < N)) return SLB_ERR_BAD_ARG;
     if (x == nullptr || ldx % 8 || ldx < K || (uintptr_t)x % 16 || (uintptr_t)W % 16) return SLB_ERR_BAD_ARG;
@@ -810,11 +1070,13 @@ int slb_gemm_tc_decode_bf16(const bf16* x, int ldx, const bf16* W, int ldw, void
     // the ups of a tile wait in the idle ring: [64][tokens + 1] floats
     if (swiglu && (size_t)stages_for((M + 15) / 16 * 16, max_stages) * A_STAGE_BYTES < (size_t)64 * ((M + 15) / 16 * 16 + 1) * 4)
         return SLB_ERR_BAD_ARG;
+    if (scale_sumsq != nullptr && scale_tiles <= 0) return SLB_ERR_BAD_ARG;
+    const RowScale rs = {scale_sumsq, scale_tiles, (float)K, scale_eps};
     if (out_f32)
         return run<float>(x, ldx, W, ldw, (float*)out, ldo, bias, workspace, M, N, K, splits, max_stages,
-                          defer_sum, swiglu, st);
+                          defer_sum, swiglu, rs, st);
     return run<bf16>(x, ldx, W, ldw, (bf16*)out, ldo, bias, workspace, M, N, K, splits, max_stages, defer_sum,
-                     swiglu, st);
+                     swiglu, rs, st);
 }
 
 // out[M, N] = sum of float32 partial sums [splits][M][N] (+ bias), in order.

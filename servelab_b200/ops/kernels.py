@@ -44,9 +44,58 @@ class SplitSum:
         return out
 
 
+class DeferredLinear:
+    """A [M, N] result x . w^T (+ bias) whose product has not been launched: the consumer
+    (a norm that takes it) launches the product with its own work in the product's epilogue
+    (``gemm_tc_resid_norm``).  ``materialize()`` runs the plain product."""
+
+    accept_flag = "accepts_deferred_linear"
+
+    def __init__(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]):
+        self.x, self.w, self.bias = x, w, bias
+
+    @property
+    def shape(self):
+        return (self.x.shape[0], self.w.shape[0])
+
+    def materialize(self) -> torch.Tensor:
+        return gemm_tc_cluster(self.x, self.w, None, self.bias)
+
+
+class ScaledRows:
+    """Normed rows [M, h] without their factor 1 / rms: ``z`` = bfloat16(resid * weight) and
+    ``sumsq`` [tiles, M], the sums of squares of resid per 128-column tile, as
+    ``gemm_tc_resid_norm`` leaves them.  A matrix product that takes this form multiplies
+    its result by 1 / sqrt(sum(sumsq) / h + eps) per token in its epilogue, which equals the
+    product of the normed rows because the factor is one number a row.  ``materialize()``
+    runs the norm kernel on the (already updated) residual stream."""
+
+    accept_flag = "accepts_scaled_rows"
+
+    def __init__(self, z, sumsq, eps: float, resid, weight):
+        self.z, self.sumsq, self.eps, self.resid, self.weight = z, sumsq, eps, resid, weight
+
+    @property
+    def shape(self):
+        return self.z.shape
+
+    @property
+    def dtype(self):
+        return self.z.dtype
+
+    @property
+    def device(self):
+        return self.z.device
+
+    def materialize(self) -> torch.Tensor:
+        out = torch.empty_like(self.z)
+        add_rmsnorm(self.resid, None, self.weight, self.eps, out)
+        return out
+
+
 def plain_unless(part, value):
-    """``value`` as a tensor unless it is an unfinished form (``SplitSum``) and ``part``
-    says (by the form's flag) that it takes it."""
+    """``value`` as a tensor unless it is an unfinished form (``SplitSum``, ``DeferredLinear``,
+    ``ScaledRows``) and ``part`` says (by the form's flag) that it takes it."""
     flag = getattr(type(value), "accept_flag", None)
     if flag is not None and not getattr(part, flag, False):
         return value.materialize()
@@ -460,6 +509,13 @@ def tc_decode_splits(n_out: int, k: int) -> int:
 SWIGLU_BLOCK = 64
 
 
+def _row_scale(x):
+    """(x as the tensor a product reads, sumsq pointer, tiles, eps)"""
+    if isinstance(x, ScaledRows):
+        return x.z, x.sumsq.data_ptr(), x.sumsq.shape[0], float(x.eps)
+    return x, None, 0, 0.0
+
+
 def gemm_tc_decode(x, w: torch.Tensor, out: Optional[torch.Tensor],
                    bias: Optional[torch.Tensor] = None, splits: int = 0,
                    defer_sum: bool = False, out_dtype: Optional[torch.dtype] = None,
@@ -469,8 +525,9 @@ def gemm_tc_decode(x, w: torch.Tensor, out: Optional[torch.Tensor],
     With ``defer_sum`` and more than one K split the partial sums are returned as a
     ``SplitSum`` (no reduction is launched); otherwise ``out`` (allocated if None).
     ``swiglu``: ``w`` holds gate and up rows alternating in runs of ``SWIGLU_BLOCK``; the
-    result is silu(gate) * up, [M, N / 2] (one K split, no bias)."""
+    result is silu(gate) * up, [M, N / 2] (one K split, no bias).  ``x`` may be ``ScaledRows``."""
     global launch_count
+    x, sumsq, tiles, eps = _row_scale(x)
     M, Kd = x.shape
     N = w.shape[0]
     splits = splits or tc_decode_splits(N, Kd)
@@ -489,7 +546,7 @@ def gemm_tc_decode(x, w: torch.Tensor, out: Optional[torch.Tensor],
         x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _p(out),
         out.stride(0) if out is not None else N,
         _p(bias), _p(ws), 1 if out_dtype == _F32 else 0, M, N, Kd, splits, tc_max_stages,
-        1 if deferred else 0, 1 if swiglu else 0, _stream()), "gemm_tc_decode")
+        1 if deferred else 0, 1 if swiglu else 0, sumsq, tiles, eps, _stream()), "gemm_tc_decode")
     if deferred:
         return SplitSum(ws, bias, out_dtype)
     launch_count += 1 if splits > 1 else 0
@@ -509,7 +566,9 @@ def gemm_tc_cluster(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor
     """out[M,N] = x . w^T (+ bias) in bfloat16 for up to 64 tokens, like
     ``gemm_tc_decode``, but the K splits of a row tile form a thread-block cluster and
     add their results up through one another's shared memory: no partial sums in
-    global memory and no reduction kernel; a fixed order of additions."""
+    global memory and no reduction kernel; a fixed order of additions.  ``x`` may be
+    ``ScaledRows``."""
+    x, sumsq, tiles, eps = _row_scale(x)
     M, Kd = x.shape
     N = w.shape[0]
     splits = splits or tc_cluster_splits(N, Kd)
@@ -517,7 +576,7 @@ def gemm_tc_cluster(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor
         out = torch.empty((M, N), dtype=_BF16, device=x.device)
     L.check(L.core().slb_gemm_tc_cluster_bf16(
         x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), _p(bias),
-        M, N, Kd, splits, tc_max_stages, _stream()), "gemm_tc_cluster")
+        M, N, Kd, splits, tc_max_stages, sumsq, tiles, eps, _stream()), "gemm_tc_cluster")
     return out
 
 
@@ -529,7 +588,8 @@ def gemm_tc_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.
                      head_dim: int, splits: int = 0) -> None:
     """The q|k|v product of up to 64 tokens together with ``qkv_rope_cache``: the product's
     epilogue adds the bias, rotates q and k, writes q to ``q_out`` and k, v into the paged
-    cache.  Head sizes in ``TC_ROPE_HEAD_DIMS``."""
+    cache.  Head sizes in ``TC_ROPE_HEAD_DIMS``.  ``x`` may be ``ScaledRows``."""
+    x, sumsq, tiles, eps = _row_scale(x)
     M, Kd = x.shape
     splits = splits or tc_cluster_splits(w_qkv.shape[0], Kd)
     L.check(L.core().slb_gemm_tc_qkv_rope_bf16(
@@ -537,7 +597,26 @@ def gemm_tc_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.
         _p(bias), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], page_size, _num_pages(k_cache), _p(inv_freq), rotary_dim,
         q_out.data_ptr(), q_out.stride(0), _p(k_cache), _p(v_cache), M, num_heads, num_kv_heads,
-        head_dim, Kd, splits, tc_max_stages, _stream()), "gemm_tc_qkv_rope")
+        head_dim, Kd, splits, tc_max_stages, sumsq, tiles, eps, _stream()), "gemm_tc_qkv_rope")
+
+
+def gemm_tc_resid_norm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
+                       resid: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+                       splits: int = 0) -> ScaledRows:
+    """The product that closes a residual branch with the add and the RMS norm that follow
+    it, in one kernel: resid (float32, in place) += x . w^T (+ bias); the result is the normed
+    rows in the form ``ScaledRows`` (bfloat16(resid * norm_weight) and per-tile sums of
+    squares), whose factor 1 / rms the next product applies.  Up to 64 tokens."""
+    M, Kd = x.shape
+    N = w.shape[0]
+    splits = splits or tc_cluster_splits(N, Kd)
+    z = torch.empty((M, N), dtype=_BF16, device=x.device)
+    sumsq = torch.empty((-(-N // 128), M), dtype=_F32, device=x.device)
+    L.check(L.core().slb_gemm_tc_resid_norm_bf16(
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _p(bias), resid.data_ptr(),
+        resid.stride(0), norm_weight.data_ptr(), z.data_ptr(), z.stride(0), sumsq.data_ptr(),
+        M, N, Kd, splits, tc_max_stages, _stream()), "gemm_tc_resid_norm")
+    return ScaledRows(z, sumsq, eps, resid, norm_weight)
 
 
 def gemm_tc_status(reset: bool = False) -> int:

@@ -30,6 +30,11 @@ tc_wide_max_tokens = 64    # ... and up to this many for products wide enough to
 # ms a step without, 3.28 / 3.10 with "rope", 3.22 / 3.04 with both).
 defer_split_sums = {"rope": True, "norm": True}
 fuse_swiglu = True         # the gate|up product of a decode step applies the activation itself
+# The product that closes a residual branch (o, down) of a decode step also does the add and
+# the RMS norm that follow it: its epilogue updates the float32 stream and writes the normed
+# rows without their factor 1 / rms, which the next product (q|k|v, gate|up) applies in its own
+# epilogue.  The two norm kernels of a layer are not launched.
+fuse_resid_norm = True
 
 
 def _w_ok(w) -> bool:
@@ -111,8 +116,9 @@ def qkv_projection(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.Te
     (``k_cache`` None: no cache write).  One kernel for decode steps in bfloat16 with a head
     size the product's epilogue takes; otherwise the product, then the q/k/v kernel."""
     M = x.shape[0]
-    if (fuse_qkv_rope and x.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16
-            and head_dim in K.TC_ROPE_HEAD_DIMS and _cluster_ok(x, w_qkv, M)):
+    xt = x.z if isinstance(x, K.ScaledRows) else x
+    if (fuse_qkv_rope and xt.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16
+            and head_dim in K.TC_ROPE_HEAD_DIMS and _cluster_ok(xt, w_qkv, M)):
         K.gemm_tc_qkv_rope(x, w_qkv, bias, positions, seq_of_token, block_table, page_size, inv_freq,
                            rotary_dim, q_out, k_cache, v_cache, num_heads, num_kv_heads, head_dim)
         return
@@ -128,9 +134,10 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, block: int) -> torch.
     then the activation kernel."""
     M = x.shape[0]
     inter = w_gate_up.shape[0] // 2
-    if (fuse_swiglu and x.dtype == torch.bfloat16 and block == K.SWIGLU_BLOCK
+    xt = x.z if isinstance(x, K.ScaledRows) else x
+    if (fuse_swiglu and xt.dtype == torch.bfloat16 and block == K.SWIGLU_BLOCK
             and K.tc_decode_splits(w_gate_up.shape[0], w_gate_up.shape[1]) == 1
-            and _tc_ok(x, w_gate_up, M)):
+            and _tc_ok(xt, w_gate_up, M)):
         return K.gemm_tc_decode(x, w_gate_up, None, swiglu=True)
     gu = linear(x, w_gate_up)
     act = torch.empty((M, inter), dtype=x.dtype, device=x.device)
@@ -161,14 +168,20 @@ def which_kernel(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) ->
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, consumer: Optional[str] = None):
     """``consumer`` ("rope" or "norm"): the caller hands the result to a kernel of that
-    kind, which accepts a ``SplitSum`` (partial sums of a K-split product); it may then
-    get one instead of a tensor."""
+    kind, which accepts an unfinished form: a ``SplitSum`` (partial sums of a K-split
+    product) or, for "norm", a ``DeferredLinear`` (the product not launched yet: the norm
+    launches it with itself in the epilogue).  The caller may then get one instead of a
+    tensor and passes it on through ``plain_unless``."""
     M, N = x.shape[0], w.shape[0]
     out_dtype = out_dtype or x.dtype
-    kernel = which_kernel(x, w, out_dtype)
+    kernel = which_kernel(x.z if isinstance(x, K.ScaledRows) else x, w, out_dtype)
+    if kernel not in ("tc_cluster", "tc"):
+        x = K.plain_unless(None, x)            # (only this package's tcgen05 kernels take ScaledRows)
     if kernel == "empty":
         return torch.empty((0, N), dtype=out_dtype, device=x.device)
     if kernel == "tc_cluster":
+        if consumer == "norm" and fuse_resid_norm:
+            return K.DeferredLinear(x, w, bias)
         return K.gemm_tc_cluster(x, w, None, bias)
     if kernel == "tc":
         return K.gemm_tc_decode(x, w, None, bias, defer_sum=defer_split_sums.get(consumer, False),

@@ -12,7 +12,8 @@ attention, the norms) records the device's nanosecond timer when the block start
 wait for the preceding kernel returns, when its main loop is done and when it ends
 (``csrc/common.cuh``).  ``launches()`` condenses that to one row per launch: first start,
 first and last return of the wait, last main loop done (the norms: inputs loaded), an extra
-mark (the cluster norm: sums of squares exchanged), last end, relative to the first event;
+mark (the cluster norm: sums of squares exchanged; the cluster products: the blocks' results
+parked, from where a block sums its share of the tokens), last end, relative to the first event;
 ``render()`` prints them with the gaps between consecutive launches, which is what the time of
 a decode step beyond its memory traffic consists of.  The reference has no counterpart (its
 docs name profiler command lines, docs/benchmark_guide.md:29-49).
@@ -27,7 +28,8 @@ import torch
 from . import library as L
 
 KERNELS = {1: "gemm_tc_decode", 2: "gemm_tc_cluster (store)", 3: "gemm_tc_cluster (q|k|v + rope)",
-           4: "decode_attention_ws", 5: "add_rmsnorm", 6: "add_rmsnorm_parts_cluster"}
+           4: "decode_attention_ws", 5: "add_rmsnorm", 6: "add_rmsnorm_parts_cluster",
+           7: "gemm_tc_cluster (+ resid, norm)"}
 
 
 LAUNCHES, BLOCKS, EVENTS = 2048, 512, 5     # the slot layout of csrc/common.cuh (512 launches a library)

@@ -33,6 +33,7 @@ from .registry import POSITIONS, build_part, register_mixer
 @register_mixer("paged_attention")
 class PagedAttention(Mixer):
     graph_safe = True
+    accepts_scaled_rows = True        # ``x`` may be ScaledRows: the q|k|v product applies 1 / rms
 
     def __init__(self, spec, prefix, env):
         super().__init__(spec, prefix, env)
@@ -75,7 +76,7 @@ class PagedAttention(Mixer):
 
     def forward(self, ctx, x, cache, owns_cache):
         s = self.spec
-        T = x.shape[0]
+        T = x.shape[0]                        # (x may be ScaledRows: the q|k|v product applies 1 / rms)
         table = ctx.block_tables[cache.group]
         rot = self.position.rotary_table()
         inv_freq, rotary_dim = rot if rot is not None else (None, 0)
@@ -83,6 +84,7 @@ class PagedAttention(Mixer):
         q = torch.empty((T, self.q_size), dtype=x.dtype, device=device)
         k_cache, v_cache = (cache.k, cache.v) if owns_cache else (None, None)
         if self.position.transforms_qk:
+            x = K.plain_unless(None, x)
             # an encoding of its own on the projected q and k: product with bias, the
             # encoding in place, then the q/k/v kernel without rotation (copy + cache write)
             qkv = linear(x, self.w_qkv, self.b_qkv)

@@ -52,11 +52,13 @@ class PreNormBlock(Block):
             p.load(store)
 
     accepts_split_sum = True          # the incoming ``delta`` may be a SplitSum
+    accepts_deferred_linear = True    # ... or a DeferredLinear
 
     def forward(self, ctx, resid, delta, cache, owns_cache):
-        # an update may arrive as the partial sums of a K-split product; a norm that does not
-        # take that form gets the plain tensor
+        # An update may arrive in an unfinished form (the partial sums of a K-split product, a
+        # product not launched yet), and a norm may return its rows in one (ScaledRows): a part
+        # that does not say that it takes the form gets the plain tensor.
         x = self.mixer_norm.forward(ctx, resid, plain_unless(self.mixer_norm, delta))
-        a = self.mixer.forward(ctx, x, cache, owns_cache)
+        a = self.mixer.forward(ctx, plain_unless(self.mixer, x), cache, owns_cache)
         x = self.ff_norm.forward(ctx, resid, plain_unless(self.ff_norm, a))
-        return resid, self.feed_forward.forward(ctx, x)
+        return resid, self.feed_forward.forward(ctx, plain_unless(self.feed_forward, x))

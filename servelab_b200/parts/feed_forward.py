@@ -19,6 +19,7 @@ from .registry import register_feed_forward
 @register_feed_forward("gated_mlp")
 class GatedMLP(FeedForward):
     graph_safe = True
+    accepts_scaled_rows = True        # ``x`` may be ScaledRows: the gate|up product applies 1 / rms
 
     def __init__(self, spec, prefix, env):
         super().__init__(spec, prefix, env)

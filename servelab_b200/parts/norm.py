@@ -19,6 +19,8 @@ from .registry import register_norm
 class RMSNorm(Norm):
     graph_safe = True
     accepts_split_sum = True      # ``delta`` may be a SplitSum (parts of a K-split product)
+    accepts_deferred_linear = True    # ... or a product not launched yet, which then runs with the
+                                      # add and this norm in its epilogue; the result is ScaledRows
 
     @classmethod
     def declare(cls, spec, prefix):
@@ -28,6 +30,11 @@ class RMSNorm(Norm):
         self.weight = store.get(self.prefix + ".weight")
 
     def forward(self, ctx, resid, delta, out_rows=None):
+        if isinstance(delta, K.DeferredLinear):
+            if out_rows is None and self.env.dtype == torch.bfloat16:
+                return K.gemm_tc_resid_norm(delta.x, delta.w, delta.bias, resid, self.weight,
+                                            self.spec.eps)
+            delta = delta.materialize()
         rows = resid.shape[0] if out_rows is None else out_rows.numel()
         out = torch.empty((rows, self.spec.dim), dtype=self.env.dtype, device=resid.device)
         K.add_rmsnorm(resid, delta, self.weight, self.spec.eps, out, out_rows)

@@ -827,6 +827,81 @@ def test_gemm_tcgen05_cluster(M, N, Kd, splits):
     assert K().gemm_tc_status(True) == 0
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 16, 23, 64])
+@pytest.mark.parametrize("N,Kd,splits", [(3584, 3584, 0), (3584, 18944, 0), (896, 4864, 0), (1000, 152, 2),
+                                         (24, 1024, 7), (300, 4096, 3)])
+def test_gemm_tcgen05_product_with_residual_add_and_norm(M, N, Kd, splits):
+    """The product that closes a residual branch, with the add and the RMS norm in its epilogue
+    (the rows are left without 1 / rms), and the products that apply that factor afterwards:
+    the stream, the normed rows and the three kinds of consumer against float64; one row of the
+    stream is made a thousand times larger than the others, so a factor taken from a
+    neighbour's row would show."""
+    g = torch.Generator().manual_seed(M * 7 + N)
+    x = torch.randn(M, Kd, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, Kd, generator=g) / math.sqrt(Kd)).bfloat16().to(DEV)
+    b = torch.randn(N, generator=g).to(DEV)
+    resid0 = torch.randn(M, N, generator=g).to(DEV)
+    resid0[M // 2] *= 1000.0
+    nw = (1.0 + 0.3 * torch.randn(N, generator=g)).to(DEV)
+    eps = 1e-5
+    want_resid = resid0.double() + x.double() @ w.double().t() + b.double()
+    rstd = torch.rsqrt((want_resid * want_resid).mean(-1, keepdim=True) + eps)
+    want_normed = want_resid * rstd * nw.double()
+    resid = resid0.clone()
+    rows = K().gemm_tc_resid_norm(x, w, b, resid, nw, eps, splits)
+    assert K().gemm_tc_status(True) == 0, "a bounded wait in the kernel ran out"
+    scale = want_resid.abs().amax(-1, keepdim=True).float()
+    assert ((resid - want_resid.float()).abs() / scale).max() <= 1e-5
+    assert torch.equal(rows.resid, resid) and rows.sumsq.shape == ((N + 127) // 128, M)
+    ss = rows.sumsq.double().sum(0)
+    assert ((ss - (want_resid * want_resid).sum(-1)).abs() / ss).max() <= 1e-5
+    # the plain form: the norm kernel on the updated stream
+    plain = rows.materialize()
+    assert (plain.float() - want_normed.float()).abs().max() <= 4e-2
+    # z is resid * weight in bfloat16
+    assert ((rows.z.float() - (want_resid * nw.double()).float()).abs() / scale).max() <= 8e-3
+    again = resid0.clone()
+    rows2 = K().gemm_tc_resid_norm(x, w, b, again, nw, eps, splits)
+    assert torch.equal(again, resid) and torch.equal(rows2.z, rows.z) and torch.equal(rows2.sumsq, rows.sumsq)
+    # consumers: they must give what the product of the normed rows gives
+    N2 = 256
+    w2 = (torch.randn(N2, N, generator=g) / math.sqrt(N)).bfloat16().to(DEV)
+    b2 = torch.randn(N2, generator=g).to(DEV)
+    zn = rows.z.double() * rstd                             # what the consumer multiplies, exactly
+    want2 = (zn @ w2.double().t() + b2.double()).float()
+    if N % 8 == 0:
+        two = 2 if N > 64 else 1                            # K splits cannot outnumber the k-blocks
+        got = K().gemm_tc_cluster(rows, w2, None, b2, two)
+        assert (got.float() - want2).abs().max() <= 3e-2
+        got = torch.empty(M, N2, device=DEV)
+        K().gemm_tc_decode(rows, w2, got, b2, 1)
+        assert (got - want2).abs().max() <= 2e-3
+        got = torch.empty(M, N2, device=DEV)
+        K().gemm_tc_decode(rows, w2, got, b2, two)
+        assert (got - want2).abs().max() <= 2e-3
+        act = K().gemm_tc_decode(rows, w2, None, splits=1, swiglu=True)
+        y = (zn @ w2.double().t()).float().view(M, N2 // 128, 2, 64)
+        want_act = (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(M, N2 // 2)
+        assert (act.float() - want_act).abs().max() <= 3e-2
+        # q|k|v with rotation: one head of 128 and two of keys / values ... against the plain rows
+        H, Hkv, D, ps = 1, 1, 64, 4
+        w3 = (torch.randn((H + 2 * Hkv) * D, N, generator=g) / math.sqrt(N)).bfloat16().to(DEV)
+        positions = i32(list(range(M)))
+        seq = i32([0] * M)
+        table = i32([list(range((M + ps - 1) // ps))])
+        inv = P.rope_inv_freq(D, 10000.0).to(DEV)
+        q = torch.empty(M, H * D, device=DEV, dtype=torch.bfloat16)
+        kc, vc = _paged((M + ps - 1) // ps, Hkv, ps, D, torch.bfloat16)
+        K().gemm_tc_qkv_rope(rows, w3, None, positions, seq, table, ps, inv, D, q, kc, vc, H, Hkv, D, two)
+        y3 = (zn @ w3.double().t()).float().cpu()
+        qf = P.rope(y3[:, :D].view(M, 1, D), torch.arange(M), inv.cpu())
+        assert (q.float().cpu().view(M, 1, D) - qf).abs().max() <= 3e-2
+        vf = y3[:, 2 * D:]
+        for t in range(M):
+            assert (vc[t // ps, 0, t % ps].float().cpu() - vf[t]).abs().max() <= 3e-2
+    assert K().gemm_tc_status(True) == 0
+
+
 @pytest.mark.parametrize("H,Hkv,D,rot,hidden", [(28, 4, 128, 128, 3584), (14, 2, 64, 64, 896),
                                                 (6, 2, 64, 32, 72), (5, 1, 32, 32, 160),
                                                 (3, 3, 16, 0, 64), (9, 1, 128, 64, 1024)])

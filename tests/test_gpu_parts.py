@@ -558,7 +558,8 @@ def test_split_sums_consumed_by_norm_and_rope_kernels(tmp_path):
     """The ways a decode step sums the K splits of its narrow products: a reduction kernel,
     float32 partial sums that the norm / rotary kernels add (``defer_split_sums``), and
     thread-block clusters that add them through shared memory, with and without the
-    rotation and cache write in the q|k|v product's epilogue.  Logits must agree with the
+    rotation and cache write in the q|k|v product's epilogue, and with and without the
+    residual add and the norm in the epilogue of the o and down products.  Logits must agree with the
     plain implementation and with one another whichever runs."""
     from servelab_b200.ops import kernels as kernels_module
     from servelab_b200.ops import linear as linear_ops
@@ -569,12 +570,14 @@ def test_split_sums_consumed_by_norm_and_rope_kernels(tmp_path):
     reqs = {"a": H.random_ids(40, 512, 1), "b": H.random_ids(37, 512, 2)}
     steps = H.trace_bulk_tail(reqs, tail=16)
     outs = {}
-    saved = (dict(linear_ops.defer_split_sums), linear_ops.cluster_sums, linear_ops.fuse_qkv_rope)
-    modes = {"reduce": (False, False, False), "parts": (True, False, False),
-             "cluster": (True, True, False), "cluster+rope": (True, True, True)}
-    for name, (defer, cluster, rope) in modes.items():
+    saved = (dict(linear_ops.defer_split_sums), linear_ops.cluster_sums, linear_ops.fuse_qkv_rope,
+             linear_ops.fuse_resid_norm)
+    modes = {"reduce": (False, False, False, False), "parts": (True, False, False, False),
+             "cluster": (True, True, False, False), "cluster+rope": (True, True, True, False),
+             "cluster+norm": (True, True, False, True), "cluster+rope+norm": (True, True, True, True)}
+    for name, (defer, cluster, rope, norm) in modes.items():
         linear_ops.defer_split_sums.update(rope=defer, norm=defer)
-        linear_ops.cluster_sums, linear_ops.fuse_qkv_rope = cluster, rope
+        linear_ops.cluster_sums, linear_ops.fuse_qkv_rope, linear_ops.fuse_resid_norm = cluster, rope, norm
         try:
             before = kernels_module.launch_count
             sess = TraceSession(folder, "bfloat16", H.peak_tokens(steps), page_size=8, max_live=2)
@@ -582,11 +585,12 @@ def test_split_sums_consumed_by_norm_and_rope_kernels(tmp_path):
             outs[name + " launches"] = kernels_module.launch_count - before
         finally:
             linear_ops.defer_split_sums.update(saved[0])
-            linear_ops.cluster_sums, linear_ops.fuse_qkv_rope = saved[1], saved[2]
+            linear_ops.cluster_sums, linear_ops.fuse_qkv_rope, linear_ops.fuse_resid_norm = saved[1:]
     assert kernels_module.gemm_tc_status(True) == 0
     # fewer kernels run, form by form
     assert outs["reduce launches"] > outs["parts launches"] >= outs["cluster launches"] \
-        > outs["cluster+rope launches"]
+        > outs["cluster+rope launches"] > outs["cluster+rope+norm launches"]
+    assert outs["cluster launches"] > outs["cluster+norm launches"]
     ref = {rid: H.plain_logits(folder, ids) for rid, ids in reqs.items()}
     for name in modes:
         for rid, ids in reqs.items():
