@@ -105,10 +105,14 @@ def make_engine(cfg: dict, pages: int, max_num_seqs: int, chunk: int, max_model_
 def run_workload(shape: str, peaks: Dict[str, float], layers: int = 0, requests: int = 0,
                  prompt_len: Optional[Tuple[int, int]] = None, max_tokens: int = 0,
                  temperature: float = -1.0, chunk: int = 0, max_num_seqs: int = 0, page_size: int = 16,
-                 num_blocks: int = 0, dtype: str = "bfloat16", warmup: int = 1, note=None) -> dict:
+                 num_blocks: int = 0, dtype: str = "bfloat16", warmup: int = 1, note=None,
+                 repeats: int = 3) -> dict:
     """The continuous-batching workload of a shape through ``LLMEngine.generate`` (host token
     ids in, host token ids out), timed by the wall clock around it after ``warmup`` untimed
-    passes (graphs of the decode batch sizes are captured at their first use)."""
+    passes (graphs of the decode batch sizes are captured at their first use).  The pass is
+    timed ``repeats`` times and the median reported with all times beside it: the steps of a
+    small model are bound by the host, whose speed varied by half between runs on shared
+    machines."""
     import torch
     from ..sampling import SamplingParams
     n, (lo, hi), new, temp, wchunk, wseed, sseed = WORKLOADS[shape]
@@ -137,18 +141,24 @@ def run_workload(shape: str, peaks: Dict[str, float], layers: int = 0, requests:
     for _ in range(warmup):
         engine.generate(prompts, sp)
     steps0, ahead0, preempt0 = engine.num_steps, engine.num_lookahead_steps, engine.scheduler.num_preemptions
-    engine.step_trace = []
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    outs = engine.generate(prompts, sp)
-    torch.cuda.synchronize()
-    seconds = time.perf_counter() - t0
-    trace, engine.step_trace = engine.step_trace, None
+    times = []
+    for _ in range(max(1, repeats)):
+        steps0, ahead0, preempt0 = (engine.num_steps, engine.num_lookahead_steps,
+                                    engine.scheduler.num_preemptions)
+        engine.step_trace = []
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        outs = engine.generate(prompts, sp)
+        torch.cuda.synchronize()
+        times.append(time.perf_counter() - t0)
+        trace, engine.step_trace = engine.step_trace, None
+    seconds = sorted(times)[len(times) // 2]
     floor = sum(step_floor_seconds(cfg, layers, t, kv, pairs, rows, peaks) for t, kv, pairs, rows in trace)
     generated = sum(len(o.outputs[0].token_ids) for o in outs)
     result = {
         "shape": shape, "layers": layers, "layers_of_shape": full_layers, "dtype": dtype, "requests": n,
         "prompt_tokens": sum(lengths), "generated_tokens": generated, "seconds": round(seconds, 4),
+        "seconds_of_each_pass": [round(t, 4) for t in times],
         "generated_tokens_per_s": round(generated / seconds, 1),
         "total_tokens_per_s": round((generated + sum(lengths)) / seconds, 1),
         "steps": engine.num_steps - steps0, "lookahead_steps": engine.num_lookahead_steps - ahead0,

@@ -140,30 +140,40 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 // The x operand is the z of a product with the residual-and-norm epilogue (EPI_RESID below): every token's result is to be multiplied by
 // rstd[tok], from the sums of squares that product left per row tile.  sumsq == null: no scale.
 struct RowScale {
-    const float* sumsq;                 // [tiles][M]
+    const float* sumsq;                 // [M][tiles]
     int tiles;
     float width;                        // elements of a normed row
     float eps;
 };
 // rstd[t] = 1 / rms of token t's input row for all M tokens, by four warps (`warp4` 0..3) that a
-// named barrier joins afterwards: a warp takes tokens warp4, warp4 + 4, ..., its lanes the tiles,
-// and the loads of four tokens are in flight together (one trip to the L2 for a decode step of up
-// to 16 requests).  The order of additions is fixed.
+// named barrier joins afterwards: a warp takes tokens warp4, warp4 + 4, ... (at most 16), its lanes
+// the tiles (consecutive in memory), and the loads of eight tokens are issued before the first is
+// used: they travel while the product's weight tiles keep the memory busy.  The order of additions
+// is fixed.
 __device__ __forceinline__ void rows_rstd(const RowScale& rs, int M, int warp4, int lane, float* rstd) {
-    for (int t0 = warp4; t0 < M; t0 += 16) {
-        float part[4];
+    // Eight of a warp's tokens at a time (all of a step of up to 32 tokens), and no loop around the
+    // loads of a token: loads inside a loop of unknown length are not moved ahead of the previous
+    // token's additions, and 16 tokens then took 16 round trips (22 us).
+    constexpr int GROUP = 8;
+#pragma unroll 1
+    for (int j0 = 0; warp4 + 4 * j0 < M; j0 += GROUP) {
+        float lo[GROUP], hi[GROUP];                          // tiles lane and lane + 32 of each token
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int t = t0 + 4 * j;
-            part[j] = 0.f;
-            if (t < M)
-                for (int tile = lane; tile < rs.tiles; tile += 32) part[j] += __ldcg(rs.sumsq + (size_t)tile * M + t);
+        for (int j = 0; j < GROUP; ++j) {
+            const int t = warp4 + 4 * (j0 + j);
+            const int at = t * rs.tiles + lane;
+            lo[j] = (t < M && lane < rs.tiles) ? __ldcg(rs.sumsq + at) : 0.f;
+            hi[j] = (t < M && lane + 32 < rs.tiles) ? __ldcg(rs.sumsq + at + 32) : 0.f;
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int t = t0 + 4 * j;
-            const float ss = warp_sum(part[j]);
-            if (t < M && lane == 0) rstd[t] = 1.0f / sqrtf(ss / rs.width + rs.eps);
+        for (int j = 0; j < GROUP; ++j) {
+            const int t = warp4 + 4 * (j0 + j);
+            if (t >= M) break;                               // (the same for every lane)
+            float part = lo[j] + hi[j];
+            for (int tile = lane + 64; tile < rs.tiles; tile += 32)    // rows wider than 8,192
+                part += __ldcg(rs.sumsq + (size_t)t * rs.tiles + tile);
+            const float ss = warp_sum(part);
+            if (lane == 0) rstd[t] = 1.0f / sqrtf(ss / rs.width + rs.eps);
         }
     }
 }
@@ -392,7 +402,7 @@ __global__ void gemm_tc_reduce_kernel(const float* __restrict__ partial, TO* __r
 //   EPI_RESID  the product updates the float32 residual stream and prepares the RMS norm that
 //              follows, so that no norm kernel runs: resid[tok, n] += sum + bias[n];
 //              z[tok, n] = bfloat16(resid[tok, n] * norm_weight[n]) -- the normed row without its
-//              factor 1 / rms, which is one number a token; sumsq[tile][tok] = the sum of squares of
+//              factor 1 / rms, which is one number a token; sumsq[tok][tile] = the sum of squares of
 //              the tile's 128 updated values.  The product that consumes z multiplies its result
 //              by rstd[tok] = 1 / sqrt(sum over tiles of sumsq / N + eps) in its epilogue
 //              (RowScale), because W (z rstd) = rstd (W z).
@@ -404,7 +414,7 @@ struct ResidEpilogue {
     const float* norm_weight;           // [N]
     bf16* z;                            // [M][ldz]
     int ldz;
-    float* sumsq;                       // [row tiles][M]
+    float* sumsq;                       // [M][row tiles]
 };
 
 
@@ -707,26 +717,8 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
                         if (EPI == EPI_RESID) (&nw.x)[c] = res.norm_weight[n4 + c];
                         if (bias) (&bs.x)[c] = bias[n4 + c];
                     }
-            for (int tok = (int)rank + w4 * (int)nranks; tok < M; tok += 4 * (int)nranks) {
-                const uint32_t addr = smem_u32(acc + tok * TC_BM + r4);
-                float4 part[TC_MAX_CLUSTER];
-#pragma unroll
-                for (uint32_t p = 0; p < (uint32_t)TC_MAX_CLUSTER; ++p)
-                    part[p] = p < nranks ? ld_peer_f32x4(addr, p) : make_float4(0.f, 0.f, 0.f, 0.f);
-                float before[4] = {0.f, 0.f, 0.f, 0.f};
-                if constexpr (EPI == EPI_RESID)
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        if (n4 + c < N) before[c] = __ldcg(res.resid + (size_t)tok * res.ld + n4 + c);
-                float v[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (uint32_t p = 0; p < (uint32_t)TC_MAX_CLUSTER; ++p) {
-                    v[0] += part[p].x; v[1] += part[p].y; v[2] += part[p].z; v[3] += part[p].w;
-                }
-                if (tok + 4 * (int)nranks >= M) {            // this warp's last values of other blocks are here
-                    cluster_arrive_relaxed_after((v[0] + v[1]) + (v[2] + v[3]), sink + threadIdx.x);
-                    arrived = true;
-                }
+            // what is left to do for a token once its sums v[0..3] (rows r4 .. r4 + 3) exist
+            auto finish = [&](int tok, float (&v)[4], const float (&before)[4]) {
                 if (rs.sumsq != nullptr) {
                     const float rstd = rstd_s[tok];
 #pragma unroll
@@ -747,7 +739,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
                             sq += r * r;
                         }
                     sq = warp_sum(sq);
-                    if (lane == 0) res.sumsq[(size_t)blockIdx.x * M + tok] = sq;
+                    if (lane == 0) res.sumsq[(size_t)tok * gridDim.x + blockIdx.x] = sq;
                 } else {
                     // (host: the width is a multiple of 16, half the rotary size a multiple of 4, so a
                     // lane's four rows lie in one head, on one side of the rotation, or beyond N)
@@ -784,6 +776,42 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
 #pragma unroll
                         for (int c = 0; c < 4; ++c) dst[c] = __float2bfloat16_rn(v[c]);
                 }
+            };
+            // two tokens a turn, the remote values (and residual rows) of both requested before
+            // either is used: a warp's tokens would otherwise cost a round trip each
+            for (int tok = (int)rank + w4 * (int)nranks; tok < M; tok += 8 * (int)nranks) {
+                const int tok2 = tok + 4 * (int)nranks;
+                float4 part[2][TC_MAX_CLUSTER];
+                float before[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int t = u == 0 ? tok : tok2;
+                    const bool live = t < M;
+                    const uint32_t addr = smem_u32(acc + (live ? t : 0) * TC_BM + r4);
+#pragma unroll
+                    for (uint32_t p = 0; p < (uint32_t)TC_MAX_CLUSTER; ++p)
+                        part[u][p] = (live && p < nranks) ? ld_peer_f32x4(addr, p) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    if constexpr (EPI == EPI_RESID)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+                            if (live && n4 + c < N) before[u][c] = __ldcg(res.resid + (size_t)t * res.ld + n4 + c);
+                }
+                float v[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+#pragma unroll
+                    for (uint32_t p = 0; p < (uint32_t)TC_MAX_CLUSTER; ++p) {
+                        v[u][0] += part[u][p].x; v[u][1] += part[u][p].y;
+                        v[u][2] += part[u][p].z; v[u][3] += part[u][p].w;
+                    }
+                if (tok + 8 * (int)nranks >= M) {            // this warp's last values of other blocks are here
+                    cluster_arrive_relaxed_after(((v[0][0] + v[0][1]) + (v[0][2] + v[0][3])) +
+                                                     ((v[1][0] + v[1][1]) + (v[1][2] + v[1][3])),
+                                                 sink + threadIdx.x);
+                    arrived = true;
+                }
+                finish(tok, v[0], before[0]);
+                if (tok2 < M) finish(tok2, v[1], before[1]);
             }
         } else {
         int parity = 0, turn = 0;
@@ -818,7 +846,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
                 if (lane == 0) warp_sq[parity][warp & 3] = sq;
                 asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps
                 if (row == 0)
-                    res.sumsq[(size_t)blockIdx.x * M + tok] =
+                    res.sumsq[(size_t)tok * gridDim.x + blockIdx.x] =
                         ((warp_sq[parity][0] + warp_sq[parity][1]) + warp_sq[parity][2]) + warp_sq[parity][3];
                 parity ^= 1;
             } else {
@@ -996,7 +1024,7 @@ int slb_gemm_tc_cluster_bf16(const bf16* x, int ldx, const bf16* W, int ldw, bf1
 
 // The product that closes a residual branch together with the RMS norm that follows it:
 // resid[M, N] (float32) += x . W^T (+ bias); z[M, N] = bfloat16(resid * norm_weight), the normed
-// rows without their factor 1 / rms; sumsq[row tiles][M] = per 128-column tile, the sum of squares
+// rows without their factor 1 / rms; sumsq[M][row tiles] = per 128-column tile, the sum of squares
 // of the updated resid.  The product that reads z passes sumsq on (scale_sumsq below) and multiplies
 // its result by 1 / sqrt(sum(sumsq) / N + eps) per token.  sumsq needs (N + 127) / 128 * M floats.
 int slb_gemm_tc_resid_norm_bf16(const bf16* x, int ldx, const bf16* W, int ldw, const float* bias,
@@ -1048,9 +1076,9 @@ int slb_gemm_tc_qkv_rope_bf16(const bf16* x, int ldx, const bf16* W, int ldw, co
 
 // workspace: float32 [splits * M * N] when splits > 1 (may be null otherwise).
 // max_stages: cap on the depth of the shared-memory ring (0: as deep as fits).
-// scale_sumsq [scale_tiles][M] (or null): x is the z of slb_gemm_tc_resid_norm_bf16, whose rows still
+// scale_sumsq [M][scale_tiles] (or null): x is the z of slb_gemm_tc_resid_norm_bf16, whose rows still
 // lack their factor 1 / rms; the result of token t is multiplied by
-// 1 / sqrt(sum over tiles of scale_sumsq[.][t] / K + scale_eps) before the bias and the activation.
+// 1 / sqrt(sum over tiles of scale_sumsq[t][.] / K + scale_eps) before the bias and the activation.
 // defer_sum: with splits > 1, leave the partial sums [splits][M][N] in the workspace
 // and launch no reduction (the consumer adds them; `out` and `bias` are unused).
 // swiglu: W's rows are gates and ups alternating in runs of 64; out is [M, N / 2] =

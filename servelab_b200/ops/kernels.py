@@ -64,7 +64,7 @@ class DeferredLinear:
 
 class ScaledRows:
     """Normed rows [M, h] without their factor 1 / rms: ``z`` = bfloat16(resid * weight) and
-    ``sumsq`` [tiles, M], the sums of squares of resid per 128-column tile, as
+    ``sumsq`` [M, tiles], the sums of squares of resid per 128-column tile, as
     ``gemm_tc_resid_norm`` leaves them.  A matrix product that takes this form multiplies
     its result by 1 / sqrt(sum(sumsq) / h + eps) per token in its epilogue, which equals the
     product of the normed rows because the factor is one number a row.  ``materialize()``
@@ -512,7 +512,7 @@ SWIGLU_BLOCK = 64
 def _row_scale(x):
     """(x as the tensor a product reads, sumsq pointer, tiles, eps)"""
     if isinstance(x, ScaledRows):
-        return x.z, x.sumsq.data_ptr(), x.sumsq.shape[0], float(x.eps)
+        return x.z, x.sumsq.data_ptr(), x.sumsq.shape[1], float(x.eps)
     return x, None, 0, 0.0
 
 
@@ -576,7 +576,7 @@ def gemm_tc_cluster(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor
         out = torch.empty((M, N), dtype=_BF16, device=x.device)
     L.check(L.core().slb_gemm_tc_cluster_bf16(
         x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), _p(bias),
-        M, N, Kd, splits, tc_max_stages, sumsq, tiles, eps, _stream()), "gemm_tc_cluster")
+        M, N, Kd, splits, _cluster_stages(M), sumsq, tiles, eps, _stream()), "gemm_tc_cluster")
     return out
 
 
@@ -597,7 +597,18 @@ def gemm_tc_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.
         _p(bias), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], page_size, _num_pages(k_cache), _p(inv_freq), rotary_dim,
         q_out.data_ptr(), q_out.stride(0), _p(k_cache), _p(v_cache), M, num_heads, num_kv_heads,
-        head_dim, Kd, splits, tc_max_stages, sumsq, tiles, eps, _stream()), "gemm_tc_qkv_rope")
+        head_dim, Kd, splits, _cluster_stages(M), sumsq, tiles, eps, _stream()), "gemm_tc_qkv_rope")
+
+
+tc_cluster_many_token_stages = 3   # ring depth of the cluster products above 16 tokens: their x tiles grow
+                                   # with the tokens, and with four stages only two blocks fit on an SM,
+                                   # which is fewer clusters of eight than a 36-tile product has at once
+                                   # (the rest started when the first had finished: 38 against 25 us for
+                                   # q|k|v at 64 tokens)
+
+
+def _cluster_stages(M: int) -> int:
+    return tc_max_stages if M <= 16 else min(tc_max_stages, tc_cluster_many_token_stages)
 
 
 def gemm_tc_resid_norm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
@@ -611,11 +622,11 @@ def gemm_tc_resid_norm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Te
     N = w.shape[0]
     splits = splits or tc_cluster_splits(N, Kd)
     z = torch.empty((M, N), dtype=_BF16, device=x.device)
-    sumsq = torch.empty((-(-N // 128), M), dtype=_F32, device=x.device)
+    sumsq = torch.empty((M, -(-N // 128)), dtype=_F32, device=x.device)
     L.check(L.core().slb_gemm_tc_resid_norm_bf16(
         x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _p(bias), resid.data_ptr(),
         resid.stride(0), norm_weight.data_ptr(), z.data_ptr(), z.stride(0), sumsq.data_ptr(),
-        M, N, Kd, splits, tc_max_stages, _stream()), "gemm_tc_resid_norm")
+        M, N, Kd, splits, _cluster_stages(M), _stream()), "gemm_tc_resid_norm")
     return ScaledRows(z, sumsq, eps, resid, norm_weight)
 
 

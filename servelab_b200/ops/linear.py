@@ -18,10 +18,10 @@ import torch
 from . import kernels as K
 from .profile import mark as _mark
 
-tc_max_tokens = 16         # up to this many tokens the tcgen05 weight-streaming kernel runs
+tc_max_tokens = 16         # up to this many tokens the tcgen05 weight-streaming kernels run whatever the
+                           # product's shape (above: see ``cluster_max_tokens_per_block``)
 tc_wide_max_tokens = 64    # ... and up to this many for products wide enough to need no K split
-                           # (gate|up: 45.5 us against the library's 47.7 at 64 tokens; the narrow
-                           # products lose to it above 16 tokens: their partial sums grow with M)
+                           # (gate|up: 45.5 us against the library's 47.7 at 64 tokens)
 # Hand the K-split partial sums of a decode-step product to the kernel that consumes the
 # result instead of reducing them in a kernel of their own, per kind of consumer.  "rope":
 # the q/k/v kernel takes them with one block per (head, token).  "norm": the norm takes
@@ -75,11 +75,16 @@ def _tc_ok(x, w, M):
 # float32 partial sums that a cluster of norm blocks adds.
 cluster_sums = True
 cluster_max_kblocks = 64   # k-blocks (of 64) per block up to which the cluster form is used
-cluster_max_tokens_per_block = 2  # tokens a block of the cluster may finish in its epilogue for a
-                                  # narrow product of more than 16 tokens.  With 8 (the cluster
-                                  # form up to 64 tokens at 8 splits) a step of 64 requests on the
-                                  # 7B shape took 4.57 ms against 4.33 ms with the library's GEMM
-                                  # and the q/k/v kernel, so the narrow products leave at 17.
+cluster_max_tokens_per_block = 8  # tokens a block of the cluster may finish in its epilogue for a
+                                  # product of more than 16 tokens (a warp a token, two tokens in
+                                  # flight per warp).  Measured against the library's GEMMs for the
+                                  # narrow products, ms a decode step on the 7B shape (8 K splits) at
+                                  # 17 / 24 / 32 / 48 / 64 requests: 3.04 / 3.47 / 3.43 / 3.95 / 4.43
+                                  # against 3.51 / 3.70 / 3.61 / 4.00 / 4.42 -- this package's kernels
+                                  # chain through programmatic dependent launch and carry rotation,
+                                  # cache write, residual add and norm in their epilogues.  With few
+                                  # row tiles (the 0.5B shape: 3 K splits, 22 tokens a block at 64
+                                  # requests) the library stays faster: 1.39 against 1.67 ms a step.
 cluster_long_k_kblocks = 16      # products whose blocks stream more k-blocks than this ("long K") ...
 cluster_long_k_max_tokens = 64   # ... use the cluster form also from 17 tokens up to here
 fuse_qkv_rope = True       # the q|k|v product of a decode step rotates and writes the cache itself

@@ -36,15 +36,19 @@ def test_decode_steps_run_this_package_s_tensor_core_kernels(shape):
             assert L.which_kernel(*_ops(m, 2 * inter, h)) == "tc"
             assert K.tc_decode_splits(2 * inter, h) == 1
         assert L.which_kernel(*_ops(m, vocab, h), out_dtype=torch.float32) == "tc"
-    # the down product: the cluster form up to 64 tokens (8 K splits: a block finishes 8 tokens)
+    # Above 16 tokens the cluster form stays while a block finishes at most 8 tokens in its
+    # epilogue: 8 K splits (7B: every narrow product) reach 64 tokens, 3 splits (0.5B) reach 24.
     kinds = {m: L.which_kernel(*_ops(m, h, inter)) for m in (8, 32, 64, 65)}
-    if shape == "0.5b":       # few k-blocks a block: like the narrow products, the library above 16 tokens
-        assert kinds == {8: "tc_cluster", 32: "vendor", 64: "vendor", 65: "vendor"}
-    else:
-        assert kinds == {8: "tc_cluster", 32: "tc_cluster", 64: "tc_cluster", 65: "vendor"}
-    # the narrow products above 16 tokens go to the library's GEMM
+    assert kinds == {8: "tc_cluster", 32: "tc_cluster", 64: "tc_cluster", 65: "vendor"}   # down: 7 to 8 splits
     for n, k in ((qkv, h), (h, q)):
-        assert L.which_kernel(*_ops(16, n, k)) == "tc_cluster" and L.which_kernel(*_ops(17, n, k)) == "vendor"
+        splits = min(K.tc_decode_splits(n, k), K.TC_MAX_CLUSTER)
+        reach = min(64, 8 * splits)
+        assert L.which_kernel(*_ops(max(16, reach), n, k)) == "tc_cluster"
+        assert L.which_kernel(*_ops(max(16, reach) + 1, n, k)) == "vendor"
+    if shape == "0.5b":
+        assert L.which_kernel(*_ops(24, qkv, h)) == "tc_cluster" and L.which_kernel(*_ops(25, qkv, h)) == "vendor"
+    if shape == "7b":
+        assert L.which_kernel(*_ops(64, qkv, h)) == "tc_cluster" and L.which_kernel(*_ops(64, h, q)) == "tc_cluster"
 
 
 def test_many_tokens_go_to_the_vendor_gemm_and_ragged_or_float32_ones_to_cuda_cores():
@@ -57,13 +61,15 @@ def test_many_tokens_go_to_the_vendor_gemm_and_ragged_or_float32_ones_to_cuda_co
     assert L.which_kernel(*_ops(3, 64, 172)) == "simt"                      # K = 172: rows not 16-byte aligned
     assert L.which_kernel(*_ops(8, h, q, torch.float32)) == "simt"          # the 32-bit path
     assert L.which_kernel(*_ops(0, h, q)) == "empty"
-    # gate|up and the LM head stay on the tcgen05 kernel up to 64 tokens, the narrow products do not
+    # gate|up and the LM head stay on the tcgen05 kernel up to 64 tokens
     assert L.which_kernel(*_ops(64, 2 * inter, h)) == "tc"
-    assert L.which_kernel(*_ops(64, qkv, h)) == "vendor"
 
 
 def test_switches_change_the_decision(monkeypatch):
     h, q, qkv, inter, vocab = SHAPES["7b"]
+    monkeypatch.setattr(L, "cluster_max_tokens_per_block", 2)
+    assert L.which_kernel(*_ops(16, h, q)) == "tc_cluster" and L.which_kernel(*_ops(17, h, q)) == "vendor"
+    assert L.which_kernel(*_ops(64, h, inter)) == "tc_cluster"          # long K ranges keep it
     monkeypatch.setattr(L, "cluster_sums", False)
     assert L.which_kernel(*_ops(8, h, q)) == "tc"
     assert L.which_kernel(*_ops(32, h, inter)) == "vendor"

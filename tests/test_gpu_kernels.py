@@ -852,8 +852,8 @@ def test_gemm_tcgen05_product_with_residual_add_and_norm(M, N, Kd, splits):
     assert K().gemm_tc_status(True) == 0, "a bounded wait in the kernel ran out"
     scale = want_resid.abs().amax(-1, keepdim=True).float()
     assert ((resid - want_resid.float()).abs() / scale).max() <= 1e-5
-    assert torch.equal(rows.resid, resid) and rows.sumsq.shape == ((N + 127) // 128, M)
-    ss = rows.sumsq.double().sum(0)
+    assert torch.equal(rows.resid, resid) and rows.sumsq.shape == (M, (N + 127) // 128)
+    ss = rows.sumsq.double().sum(1)
     assert ((ss - (want_resid * want_resid).sum(-1)).abs() / ss).max() <= 1e-5
     # the plain form: the norm kernel on the updated stream
     plain = rows.materialize()
