@@ -178,6 +178,29 @@ __device__ __forceinline__ void rows_rstd(const RowScale& rs, int M, int warp4, 
     }
 }
 
+// four consecutive outputs; dst is 8-byte aligned
+__device__ __forceinline__ void store4_bf16(bf16* dst, const float (&o)[4]) {
+    uint2 packed;
+    __nv_bfloat162 h;
+    h = __floats2bfloat162_rn(o[0], o[1]); packed.x = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2bfloat162_rn(o[2], o[3]); packed.y = *reinterpret_cast<uint32_t*>(&h);
+    *reinterpret_cast<uint2*>(dst) = packed;
+}
+// eight consecutive outputs; dst is 16-byte aligned for bfloat16 (32-byte for float)
+__device__ __forceinline__ void store8(bf16* dst, const float (&o)[8]) {
+    uint4 packed;
+    __nv_bfloat162 h;
+    h = __floats2bfloat162_rn(o[0], o[1]); packed.x = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2bfloat162_rn(o[2], o[3]); packed.y = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2bfloat162_rn(o[4], o[5]); packed.z = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2bfloat162_rn(o[6], o[7]); packed.w = *reinterpret_cast<uint32_t*>(&h);
+    *reinterpret_cast<uint4*>(dst) = packed;
+}
+__device__ __forceinline__ void store8(float* dst, const float (&o)[8]) {
+    *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(o[4], o[5], o[6], o[7]);
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -302,38 +325,35 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
         if (tracer) slb_trace_event(tr, 1, SLB_TR_LOOP_DONE);
         if (swiglu) {
             // W holds gate and up rows alternating in runs of 64, so this tile's rows are 64
-            // gates and their 64 ups: the upper two warps park the ups in shared memory (the
-            // ring is idle: every tile has arrived and every MMA has run), the lower two
-            // combine: out[tok, tile * 64 + r] = silu(gate_r) * up_r.  One K split only.
-            float* ups = reinterpret_cast<float*>(a_stage);            // [64][ntok16 + 1]
-            const int ld_ups = ntok16 + 1;
-            if (row >= 64) {
-                for (int c0 = 0; c0 < ntok16; c0 += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            // gates and their 64 ups.  Every warp parks its 32 rows in shared memory (the ring is
+            // idle: every tile has arrived and every MMA has run); then a thread takes eight
+            // neighbouring outputs of a token, out[tok, tile * 64 + c] = silu(gate_c) * up_c, and
+            // stores them with one 16-byte access.  (Before, the two warps that hold the gates wrote
+            // every token's value with a 2-byte store of its own: 7.5 us at 64 tokens.)  One K split.
+            float* vals = reinterpret_cast<float*>(a_stage);           // [128][ntok16 + 1]
+            const int ld = ntok16 + 1;
+            for (int c0 = 0; c0 < ntok16; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) ups[(row - 64) * ld_ups + c0 + j] = __uint_as_float(v[j]);
-                }
+                for (int j = 0; j < 16; ++j) vals[row * ld + c0 + j] = __uint_as_float(v[j]);
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");             // the four epilogue warps
-            if (row < 64) {
-                const int col = (int)blockIdx.x * 64 + row;            // index of the gate
-                for (int c0 = 0; c0 < ntok16; c0 += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (col < N / 2 && ok) {
+            const int t = (int)threadIdx.x - 64;
+            const int c8 = (t & 7) * 8;                                // first of this thread's eight columns
+            if (ok) {
+                for (int tok = t >> 3; tok < M; tok += 16) {
+                    const float rstd = scaled ? rstd_s[tok] : 1.f;
+                    float o[8];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int tok = c0 + j;
-                            if (tok >= M) break;
-                            const float rstd = scaled ? rstd_s[tok] : 1.f;
-                            const float gt = __uint_as_float(v[j]) * rstd;
-                            const float up = ups[row * ld_ups + tok] * rstd;
-                            out[(size_t)tok * ldo + col] = from_float<TO>(gt / (1.0f + expf(-gt)) * up);
-                        }
+                    for (int e = 0; e < 8; ++e) {
+                        const float gt = vals[(c8 + e) * ld + tok] * rstd;
+                        const float up = vals[(64 + c8 + e) * ld + tok] * rstd;
+                        o[e] = gt / (1.0f + expf(-gt)) * up;
                     }
+                    TO* dst = out + (size_t)tok * ldo + (size_t)blockIdx.x * 64 + c8;
+                    store8(dst, o);
                 }
             }
         } else
@@ -577,6 +597,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     const uint32_t tmem_d = *tmem_slot;
     float* acc = reinterpret_cast<float*>(a_stage);          // [ntok16][TC_BM] once the ring is idle
     RopeTarget first_target = {};                            // EPI_ROPE: for token `rank` of this block
+    float first_sn[2][4] = {}, first_cs[2][4] = {};          // EPI_ROPE, WIDE: of this warp's first two tokens
     float resid_ahead0 = 0.f, resid_ahead1 = 0.f, norm_w = 0.f, bias_n = 0.f;   // EPI_RESID: fetched while the main loop runs
     if (flags & SLB_FLAG_PDL_EARLY) pdl_launch_dependents();
     const bool tracer = threadIdx.x == 64;                  // lane 0 of the first epilogue warp
@@ -634,25 +655,14 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
         __syncwarp();
     } else {
         // ------------------------------------------ epilogue, part 1: accumulator -> acc
-        pdl_wait();
-        if (tracer) slb_trace_event(tr, TRACE_ID, SLB_TR_WAITED);
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
-        if (rs.sumsq != nullptr) rows_rstd(rs, M, quarter, lane, rstd_s);   // in the shadow of the main loop
-        if constexpr (EPI == EPI_RESID && !WIDE) {
-            // what this thread's column needs of the first two tokens of this block's share
-            const int tok0 = (int)cluster_rank(), tok1 = tok0 + (int)cluster_size();
-            if (n0 + row < N) {
-                norm_w = res.norm_weight[n0 + row];
-                if (bias) bias_n = bias[n0 + row];
-                if (tok0 < M) resid_ahead0 = __ldcg(res.resid + (size_t)tok0 * res.ld + n0 + row);
-                if (tok1 < M) resid_ahead1 = __ldcg(res.resid + (size_t)tok1 * res.ld + n0 + row);
-            }
-        }
         if constexpr (EPI == EPI_ROPE) {
-            // In the shadow of the main loop: the positions and cache pages of the step's tokens
-            // (one token a thread: dependent loads from global memory, which would otherwise be
-            // waited for token by token), then what this block's first token needs.
+            // Before the wait for the preceding kernel, which writes none of this (the step's
+            // positions and block tables are in place before its first kernel starts): the
+            // positions and cache pages of the step's tokens (one token a thread: dependent loads
+            // from global memory, which would otherwise be waited for token by token), then what
+            // this block's first token needs.
             const int t = (int)threadIdx.x - 64;
             if (t < M) {
                 const int pos = rope.positions[t];
@@ -671,6 +681,35 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
             const int tok0 = (int)cluster_rank();
             if (!WIDE && tok0 < M)
                 first_target = rope_target(rope, tok0, tok_pos[tok0], tok_page[tok0], n0 + row, row, N);
+            if constexpr (WIDE) {
+                // sine and cosine of this warp's first two tokens, for this lane's four rows
+                const int half = rope.inv_freq != nullptr ? rope.rotary_dim >> 1 : 0;
+                const int n4 = n0 + 4 * lane, e0 = n4 % rope.D;
+                if (n4 < N && n4 / rope.D < rope.H + rope.Hkv && e0 < 2 * half) {
+                    const float4 fr = *reinterpret_cast<const float4*>(rope.inv_freq + (e0 < half ? e0 : e0 - half));
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int tok = (int)cluster_rank() + (quarter + 4 * u) * (int)cluster_size();
+                        if (tok < M)
+#pragma unroll
+                            for (int c = 0; c < 4; ++c)
+                                sincosf((float)tok_pos[tok] * (&fr.x)[c], &first_sn[u][c], &first_cs[u][c]);
+                    }
+                }
+            }
+        }
+        pdl_wait();
+        if (tracer) slb_trace_event(tr, TRACE_ID, SLB_TR_WAITED);
+        if (rs.sumsq != nullptr) rows_rstd(rs, M, quarter, lane, rstd_s);   // in the shadow of the main loop
+        if constexpr (EPI == EPI_RESID && !WIDE) {
+            // what this thread's column needs of the first two tokens of this block's share
+            const int tok0 = (int)cluster_rank(), tok1 = tok0 + (int)cluster_size();
+            if (n0 + row < N) {
+                norm_w = res.norm_weight[n0 + row];
+                if (bias) bias_n = bias[n0 + row];
+                if (tok0 < M) resid_ahead0 = __ldcg(res.resid + (size_t)tok0 * res.ld + n0 + row);
+                if (tok1 < M) resid_ahead1 = __ldcg(res.resid + (size_t)tok1 * res.ld + n0 + row);
+            }
         }
         bool ok = true;
         if (iters > 0) {
@@ -708,73 +747,87 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
             // whole token (a lane four consecutive rows of the tile, fetched from every block with
             // one 16-byte load), the four warps the block's tokens in turn.  The rotation partner
             // and the sum of squares of a token then lie within one warp: shuffles, no barrier.
+            // (host: N is a multiple of 4, so a lane's four rows are all inside or all beyond N, and
+            // what a lane reads and writes of a row is 8- or 16-byte aligned)
             const int w4 = warp & 3, r4 = 4 * lane, n4 = n0 + r4;
-            float4 nw = make_float4(0.f, 0.f, 0.f, 0.f), bs = nw;
-            if (EPI != EPI_ROPE)
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    if (n4 + c < N) {
-                        if (EPI == EPI_RESID) (&nw.x)[c] = res.norm_weight[n4 + c];
-                        if (bias) (&bs.x)[c] = bias[n4 + c];
-                    }
+            const bool in = n4 < N;
+            float4 nw = make_float4(0.f, 0.f, 0.f, 0.f), bs = nw, fr = nw;
+            // the q|k|v form: where this lane's rows lie (the same for every token)
+            int rope_j = 0, rope_e0 = 0, partner = lane;
+            bool rotate = false, first_half = true, is_v = false;
+            if constexpr (EPI == EPI_ROPE) {
+                // (host: the width is a multiple of 16 and half the rotary size a multiple of 4, so the
+                // four rows lie in one head and on one side of the rotation)
+                const int half = rope.inv_freq != nullptr ? rope.rotary_dim >> 1 : 0;
+                rope_j = n4 / rope.D;
+                rope_e0 = n4 - rope_j * rope.D;
+                is_v = rope_j >= rope.H + rope.Hkv;
+                rotate = in && !is_v && rope_e0 < 2 * half;
+                first_half = rope_e0 < half;
+                if (rotate) {
+                    partner = first_half ? lane + (half >> 2) : lane - (half >> 2);
+                    fr = *reinterpret_cast<const float4*>(rope.inv_freq + (first_half ? rope_e0 : rope_e0 - half));
+                }
+                if (in && rope.bias) bs = *reinterpret_cast<const float4*>(rope.bias + n4);
+            } else if (in) {
+                if (EPI == EPI_RESID) nw = *reinterpret_cast<const float4*>(res.norm_weight + n4);
+                if (bias) bs = *reinterpret_cast<const float4*>(bias + n4);
+            }
             // what is left to do for a token once its sums v[0..3] (rows r4 .. r4 + 3) exist
-            auto finish = [&](int tok, float (&v)[4], const float (&before)[4]) {
+            auto finish = [&](int tok, float (&v)[4], const float (&before)[4], bool first_turn, int u) {
                 if (rs.sumsq != nullptr) {
                     const float rstd = rstd_s[tok];
 #pragma unroll
                     for (int c = 0; c < 4; ++c) v[c] *= rstd;
                 }
-                if constexpr (EPI == EPI_STORE) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        if (n4 + c < N) out[(size_t)tok * ldo + n4 + c] = __float2bfloat16_rn(v[c] + (&bs.x)[c]);
+                for (int c = 0; c < 4; ++c) v[c] += (&bs.x)[c];
+                if constexpr (EPI == EPI_STORE) {
+                    if (in) store4_bf16(out + (size_t)tok * ldo + n4, v);
                 } else if constexpr (EPI == EPI_RESID) {
                     float sq = 0.f;
+                    if (in) {
+                        float r[4], zv[4];
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        if (n4 + c < N) {
-                            const float r = before[c] + (v[c] + (&bs.x)[c]);
-                            res.resid[(size_t)tok * res.ld + n4 + c] = r;
-                            res.z[(size_t)tok * res.ldz + n4 + c] = __float2bfloat16_rn(r * (&nw.x)[c]);
-                            sq += r * r;
+                        for (int c = 0; c < 4; ++c) {
+                            r[c] = before[c] + v[c];
+                            zv[c] = r[c] * (&nw.x)[c];
+                            sq += r[c] * r[c];
                         }
+                        *reinterpret_cast<float4*>(res.resid + (size_t)tok * res.ld + n4) =
+                            make_float4(r[0], r[1], r[2], r[3]);
+                        store4_bf16(res.z + (size_t)tok * res.ldz + n4, zv);
+                    }
                     sq = warp_sum(sq);
                     if (lane == 0) res.sumsq[(size_t)tok * gridDim.x + blockIdx.x] = sq;
                 } else {
-                    // (host: the width is a multiple of 16, half the rotary size a multiple of 4, so a
-                    // lane's four rows lie in one head, on one side of the rotation, or beyond N)
-                    const int D = rope.D, half = rope.inv_freq != nullptr ? rope.rotary_dim >> 1 : 0;
-                    const int j = n4 / D, e0 = n4 - j * D;
-                    const bool in = n4 < N, is_v = j >= rope.H + rope.Hkv;
-                    const bool rotate = in && !is_v && e0 < 2 * half, first_half = e0 < half;
-                    if (in && rope.bias)
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) v[c] += rope.bias[n4 + c];
-                    const int partner = rotate ? (first_half ? lane + (half >> 2) : lane - (half >> 2)) : lane;
                     float other[4];
 #pragma unroll
                     for (int c = 0; c < 4; ++c) other[c] = __shfl_sync(0xffffffffu, v[c], partner);
                     const int pos = tok_pos[tok], page = tok_page[tok];
                     if (rotate) {
-                        const int i0 = first_half ? e0 : e0 - half;
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
                             float sn, cs;
-                            sincosf((float)pos * rope.inv_freq[i0 + c], &sn, &cs);
+                            if (first_turn) {                          // computed before the main loop ended
+                                sn = first_sn[u][c];
+                                cs = first_cs[u][c];
+                            } else {
+                                sincosf((float)pos * (&fr.x)[c], &sn, &cs);
+                            }
                             v[c] = first_half ? v[c] * cs - other[c] * sn : v[c] * cs + other[c] * sn;
                         }
                     }
                     bf16* dst = nullptr;
-                    if (in && j < rope.H) {
-                        dst = rope.q_out + (size_t)tok * rope.ld_q + (size_t)j * D + e0;
+                    if (in && rope_j < rope.H) {
+                        dst = rope.q_out + (size_t)tok * rope.ld_q + (size_t)rope_j * rope.D + rope_e0;
                     } else if (in && rope.k_cache != nullptr && page >= 0) {
-                        const int kvh = is_v ? j - rope.H - rope.Hkv : j - rope.H;
+                        const int kvh = is_v ? rope_j - rope.H - rope.Hkv : rope_j - rope.H;
                         dst = (is_v ? rope.v_cache : rope.k_cache) +
-                              (((size_t)page * rope.Hkv + kvh) * rope.page_size + pos % rope.page_size) * D + e0;
+                              (((size_t)page * rope.Hkv + kvh) * rope.page_size + pos % rope.page_size) * rope.D +
+                              rope_e0;
                     }
-                    if (dst != nullptr)
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) dst[c] = __float2bfloat16_rn(v[c]);
+                    if (dst != nullptr) store4_bf16(dst, v);
                 }
             };
             // two tokens a turn, the remote values (and residual rows) of both requested before
@@ -792,9 +845,10 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
                     for (uint32_t p = 0; p < (uint32_t)TC_MAX_CLUSTER; ++p)
                         part[u][p] = (live && p < nranks) ? ld_peer_f32x4(addr, p) : make_float4(0.f, 0.f, 0.f, 0.f);
                     if constexpr (EPI == EPI_RESID)
-#pragma unroll
-                        for (int c = 0; c < 4; ++c)
-                            if (live && n4 + c < N) before[u][c] = __ldcg(res.resid + (size_t)t * res.ld + n4 + c);
+                        if (live && in) {
+                            const float4 b4 = __ldcg(reinterpret_cast<const float4*>(res.resid + (size_t)t * res.ld + n4));
+                            before[u][0] = b4.x; before[u][1] = b4.y; before[u][2] = b4.z; before[u][3] = b4.w;
+                        }
                 }
                 float v[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -810,8 +864,9 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
                                                  sink + threadIdx.x);
                     arrived = true;
                 }
-                finish(tok, v[0], before[0]);
-                if (tok2 < M) finish(tok2, v[1], before[1]);
+                const bool first_turn = tok == (int)rank + w4 * (int)nranks;
+                finish(tok, v[0], before[0], first_turn, 0);
+                if (tok2 < M) finish(tok2, v[1], before[1], first_turn, 1);
             }
         } else {
         int parity = 0, turn = 0;
@@ -969,8 +1024,20 @@ int run_cluster(const bf16* x, int ldx, const bf16* W, int ldw, bf16* out, int l
     if (rc != 0) return rc;
     static unsigned long long configured = 0, configured_wide = 0;   // per instantiation, a bit per device
     // the warp-per-token epilogue: above 16 tokens, where its shapes allow it (see the kernel)
-    const bool few = M <= tc_cluster_single_max_tokens ||
-                     (EPI == EPI_ROPE && (N % 16 != 0 || (rope.inv_freq != nullptr && rope.rotary_dim % 8 != 0)));
+    auto aligned = [](const void* p, int ld, int elem_bytes, int bytes) {
+        return p == nullptr || ((uintptr_t)p % bytes == 0 && ((size_t)ld * elem_bytes) % bytes == 0);
+    };
+    bool wide_ok = N % 4 == 0 && aligned(bias, 0, 4, 16);
+    if (EPI == EPI_STORE) wide_ok = wide_ok && aligned(out, ldo, 2, 8);
+    if (EPI == EPI_RESID)
+        wide_ok = wide_ok && aligned(res.resid, res.ld, 4, 16) && aligned(res.z, res.ldz, 2, 8) &&
+                  aligned(res.norm_weight, 0, 4, 16);
+    if (EPI == EPI_ROPE)
+        wide_ok = wide_ok && N % 16 == 0 && (rope.inv_freq == nullptr || rope.rotary_dim % 8 == 0) &&
+                  aligned(rope.bias, 0, 4, 16) && aligned(rope.inv_freq, 0, 4, 16) &&
+                  aligned(rope.q_out, rope.ld_q, 2, 8) && aligned(rope.k_cache, 0, 2, 8) &&
+                  aligned(rope.v_cache, 0, 2, 8);
+    const bool few = M <= tc_cluster_single_max_tokens || !wide_ok;
     rc = few ? slb_configure(&configured, gemm_tc_cluster_kernel<EPI, false>, TC_SMEM_BUDGET)
              : slb_configure(&configured_wide, gemm_tc_cluster_kernel<EPI, true>, TC_SMEM_BUDGET);
     if (rc != 0) return rc;
@@ -1095,8 +1162,10 @@ int slb_gemm_tc_decode_bf16(const bf16* x, int ldx, const bf16* W, int ldw, void
     if (splits < 1 || splits > kblocks || splits > 65535) return SLB_ERR_BAD_ARG;
     if (splits > 1 && workspace == nullptr) return SLB_ERR_BAD_ARG;
     if (swiglu && (splits != 1 || N % 128 || bias != nullptr || ldo < N / 2)) return SLB_ERR_BAD_ARG;
-    // the ups of a tile wait in the idle ring: [64][tokens + 1] floats
-    if (swiglu && (size_t)stages_for((M + 15) / 16 * 16, max_stages) * A_STAGE_BYTES < (size_t)64 * ((M + 15) / 16 * 16 + 1) * 4)
+    // (its outputs are stored eight at a time)
+    if (swiglu && (ldo % 8 || (uintptr_t)out % (out_f32 ? 32 : 16))) return SLB_ERR_BAD_ARG;
+    // the tile waits in the idle ring: [128][tokens + 1] floats
+    if (swiglu && (size_t)stages_for((M + 15) / 16 * 16, max_stages) * A_STAGE_BYTES < (size_t)128 * ((M + 15) / 16 * 16 + 1) * 4)
         return SLB_ERR_BAD_ARG;
     if (scale_sumsq != nullptr && scale_tiles <= 0) return SLB_ERR_BAD_ARG;
     const RowScale rs = {scale_sumsq, scale_tiles, (float)K, scale_eps};
