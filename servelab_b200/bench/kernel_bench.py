@@ -182,7 +182,8 @@ def bench_prefill_attention(shape, peaks, device, lengths, twin: bool) -> List[R
     return rows
 
 
-def bench_products(shape, peaks, device, token_counts, only: Optional[List[str]] = None) -> List[Row]:
+def bench_products(shape, peaks, device, token_counts, only: Optional[List[str]] = None,
+                   fused_only: bool = False) -> List[Row]:
     """The matrix products of a layer and the LM head as the engine dispatches them
     (``ops.linear``): this package's tcgen05 kernel for few tokens, the vendor GEMM above."""
     import torch
@@ -220,8 +221,33 @@ def bench_products(shape, peaks, device, token_counts, only: Optional[List[str]]
                             if isinstance(y, K.DeferredLinear):      # timed as the plain product
                                 y.materialize()
                 return run
-            us = time_in_graph(build) * 1e3 / copies
-            rows.append(Row(name, f"{M} tokens [{N} x {Kd}]", us, nbytes, flops, peaks))
+            if not fused_only:
+                us = time_in_graph(build) * 1e3 / copies
+                rows.append(Row(name, f"{M} tokens [{N} x {Kd}]", us, nbytes, flops, peaks))
+            if kind != "norm" or M > K.TC_MAX_TOKENS:
+                continue
+            # the product with the residual add and the RMS norm that follow it: as two kernels
+            # (product, then add + norm) and as the one kernel that carries both in its epilogue
+            # (float32 stream read and written, normed rows out: 10 more bytes an element)
+
+            def build_pair(fused):
+                ws = [(torch.randn(N, Kd, device=device) * 0.02).bfloat16() for _ in range(copies)]
+                x = torch.randn(M, Kd, device=device).bfloat16()
+                resid = torch.randn(M, N, device=device)
+                weight = torch.ones(N, device=device)
+                out = torch.empty(M, N, device=device, dtype=torch.bfloat16)
+
+                def run():
+                    for w in ws:
+                        if fused:
+                            K.gemm_tc_resid_norm(x, w, None, resid, weight, 1e-6)
+                        else:
+                            K.add_rmsnorm(resid, K.gemm_tc_cluster(x, w), weight, 1e-6, out)
+                return run
+            for fused in ((True,) if fused_only else (False, True)):
+                us = time_in_graph(lambda: build_pair(fused)) * 1e3 / copies
+                label = name + (" + add + norm (one kernel)" if fused else " + add + norm (two kernels)")
+                rows.append(Row(label, f"{M} tokens [{N} x {Kd}]", us, nbytes + M * N * 10, flops, peaks))
     return rows
 
 
@@ -333,6 +359,8 @@ def main(argv=None) -> int:
     ap.add_argument("--tokens", default="1,8,16,64,2048", help="products and element-wise kernels")
     ap.add_argument("--products", default="", help="products: only those whose name contains one of "
                     "these comma-separated pieces (q|k|v, o product, gate|up, down, LM head)")
+    ap.add_argument("--fused-only", action="store_true",
+                    help="products: only the o and down products with add and norm in their epilogue")
     ap.add_argument("--no-twins", action="store_true", help="skip the plain twins of the attention kernels")
     ap.add_argument("--peaks", default=DEFAULT_PEAKS, help="JSON file with hbm_gbs and bf16_tflops")
     ap.add_argument("--markdown", action="store_true")
@@ -361,7 +389,7 @@ def main(argv=None) -> int:
             print("reference kernels beside this package's:", json.dumps(compare(device), indent=1))
         elif g == "products":
             rows += bench_products(shape, peaks, device, _ints(args.tokens),
-                                   [p for p in args.products.split(",") if p])
+                                   [p for p in args.products.split(",") if p], args.fused_only)
         else:
             rows += bench_elementwise(shape, peaks, device, _ints(args.tokens))
     print(f"{args.shape}: hidden {shape[0]}, heads {shape[1]}/{shape[2]} x {shape[3]}, intermediate "

@@ -76,7 +76,7 @@ constexpr int PANEL_BYTES = BN * 128;
 constexpr int TILE_BYTES = PANELS * PANEL_BYTES;           // K or V of one tile, swizzled
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;                // K tile + V tile
 constexpr int MAX_STAGES = 4;
-constexpr int MAX_SPLITS = 32;
+constexpr int MAX_SPLITS = 64;
 constexpr int MAX_CLUSTER_SPLITS = 8;      // splits that can form one cluster (the portable size)
 constexpr float LAZY_LOG2 = 8.f;           // the reference moves when exceeded by 2^8
 
@@ -218,11 +218,28 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     // with the tiles per split).  Blocks of unused splits leave at once.
     int use_splits = 1;
     if (num_splits > 1 && total_tiles > unsplit_tiles) {
-        const int per = max((int)ceilf(split_coef * sqrtf((float)total_tiles)),
-                            (total_tiles + num_splits - 1) / num_splits);
+        // (cluster form: combining costs about the same whatever the number of splits, so a request
+        // takes as many as the launch has, down to two tiles a split)
+        const int least = CLUSTER ? 2 : (int)ceilf(split_coef * sqrtf((float)total_tiles));
+        const int per = max(least, (total_tiles + num_splits - 1) / num_splits);
         use_splits = (total_tiles + per - 1) / per;
-        if (use_splits > 8 && use_splits <= 12) use_splits = 8;   // the last block reads eight at a time
+        if (!CLUSTER && use_splits > 8 && use_splits <= 12) use_splits = 8;   // the last block reads eight at a time
     }
+    // Cluster form: the launch's splits come as clusters of `csize` blocks; a request that uses more
+    // splits than a cluster has uses several clusters ("groups"), each of which combines its own
+    // splits through shared memory and leaves one partial result in global memory; the groups'
+    // results are combined slice by slice by whichever block finishes a slice last.
+    const int csize = CLUSTER ? min(num_splits, MAX_CLUSTER_SPLITS) : 1;
+    if (CLUSTER && use_splits > csize) {
+        // several clusters cost about 3 us more than one (partial results through global memory): worth
+        // it when a block then has at least four tiles (of about 0.8 us) fewer
+        const int per_one = (total_tiles + csize - 1) / csize;
+        const int per_many = (total_tiles + use_splits - 1) / use_splits;
+        if (per_one - per_many < 4) use_splits = (total_tiles + per_one - 1) / per_one;
+    }
+    const int group = CLUSTER ? split / csize : 0, crank = CLUSTER ? split - group * csize : 0;
+    const int groups_used = CLUSTER ? (use_splits + csize - 1) / csize : 1;
+    if (CLUSTER && group >= groups_used) return;           // a whole cluster
     // (in the cluster form every block stays for the cluster's barriers; one beyond the
     // request's splits has no tiles)
     if (!CLUSTER && split >= use_splits) return;
@@ -573,17 +590,20 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
     if constexpr (CLUSTER) {
         // ---- the blocks of the cluster combine a slice of the outputs each ----
         cluster_sync_all_threads();                        // every block's result is parked
+        // (every block of the cluster takes a slice, also one beyond the request's splits, which has
+        // parked an empty result: the slices are then the same in every group)
         const int total = nrows * D;
-        const int chunk = (total + use_splits - 1) / use_splits;
-        const int stop = min(total, (split + 1) * chunk);
-        if (split < use_splits) {
-            for (int idx = split * chunk + tid; idx < stop; idx += NTHREADS) {
+        const int chunk = (total + csize - 1) / csize;
+        const int begin = crank * chunk, stop = min(total, (crank + 1) * chunk);
+        const bool several = groups_used > 1;
+        {
+            for (int idx = begin + tid; idx < stop; idx += NTHREADS) {
                 const int r = idx / D, d = idx - r * D;
                 // all remote loads first, then the merge in the order of the ranks
                 float mv[8], lv[8], ov[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const bool in = j < use_splits;
+                    const bool in = j < csize;
                     mv[j] = in ? ld_cluster_f32(cl_ml + r * 2, (uint32_t)j) : -INFINITY;
                     lv[j] = in ? ld_cluster_f32(cl_ml + r * 2 + 1, (uint32_t)j) : 0.f;
                     ov[j] = in ? ld_cluster_f32(cl_o + r * D + d, (uint32_t)j) : 0.f;
@@ -604,19 +624,78 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_ws_kernel(
                         acc += ov[j] * f;
                     }
                 }
-                out[(size_t)s * ldo + (size_t)(kvh * g + h0 + r) * D + d] =
-                    __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+                const int head = kvh * g + h0 + r;
+                if (!several) {
+                    out[(size_t)s * ldo + (size_t)head * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+                } else {
+                    // this group's partial result; its (maximum, sum) once per row and slice
+                    part_o[(((size_t)s * H + head) * num_splits + group) * D + d] = acc;
+                    if (d == 0 || idx == begin) {
+                        const size_t pi = ((size_t)s * H + head) * num_splits + group * csize + crank;
+                        part_ml[pi * 2] = M;
+                        part_ml[pi * 2 + 1] = L;
+                    }
+                }
                 // what was read has arrived once this store has its operand (see below)
                 asm volatile("st.volatile.shared.f32 [%0], %1;" ::"r"(smem_u32(red_o + tid)), "f"(touched + M) : "memory");
             }
         }
-        // A relaxed arrival: it orders nothing, so the stores to `out` are not waited for (with a
+        // A relaxed arrival: it orders nothing, so the stores above are not waited for (with a
         // releasing one a block spent microseconds here while the next product's weight fetches kept
         // the memory busy).  What was read from the other blocks has arrived: every loaded value went
         // into a volatile store to this block's own idle shared memory (red_o), which needs it in a
         // register, and the arrival follows those stores.
         asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
                                                            // nobody leaves while its result is read
+        if (!several) {
+            if (threadIdx.x == 0) slb_trace_event(tr, 4, SLB_TR_END + 1);
+            return;
+        }
+        // ---- several groups: the block that finishes slice `crank` last combines it ----
+        __threadfence();
+        __syncthreads();
+        int* counter = counters + ((size_t)s * gridDim.y + blockIdx.y) * MAX_CLUSTER_SPLITS + crank;
+        if (tid == 0) {
+            int before;
+            asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(before) : "l"(counter) : "memory");
+            last_block = before == groups_used - 1;
+            if (last_block) *counter = 0;                  // zero again for the next launch
+        }
+        __syncthreads();
+        if (!last_block) {
+            if (threadIdx.x == 0) slb_trace_event(tr, 4, SLB_TR_END);
+            return;
+        }
+        for (int idx = begin + tid; idx < stop; idx += NTHREADS) {
+            const int r = idx / D, d = idx - r * D;
+            const int head = kvh * g + h0 + r;
+            const size_t base = ((size_t)s * H + head) * num_splits;
+            float mv[MAX_SPLITS / MAX_CLUSTER_SPLITS], lv[MAX_SPLITS / MAX_CLUSTER_SPLITS],
+                ov[MAX_SPLITS / MAX_CLUSTER_SPLITS];
+#pragma unroll
+            for (int j = 0; j < MAX_SPLITS / MAX_CLUSTER_SPLITS; ++j) {
+                const bool in = j < groups_used;
+                // the slice of group j that holds (r, d) wrote this row's maximum and sum
+                const size_t pi = base + j * csize + crank;
+                mv[j] = in ? __ldcg(part_ml + pi * 2) : -INFINITY;
+                lv[j] = in ? __ldcg(part_ml + pi * 2 + 1) : 0.f;
+                ov[j] = in ? __ldcg(part_o + (base + j) * D + d) : 0.f;
+            }
+            float M = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < MAX_SPLITS / MAX_CLUSTER_SPLITS; ++j) M = fmaxf(M, mv[j]);
+            float L = 0.f, acc = 0.f;
+            if (M != -INFINITY) {
+#pragma unroll
+                for (int j = 0; j < MAX_SPLITS / MAX_CLUSTER_SPLITS; ++j) {
+                    if (mv[j] == -INFINITY) continue;
+                    const float f = exp2f(mv[j] - M);
+                    L += lv[j] * f;
+                    acc += ov[j] * f;
+                }
+            }
+            out[(size_t)s * ldo + (size_t)head * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        }
         if (threadIdx.x == 0) slb_trace_event(tr, 4, SLB_TR_END + 1);
         return;
     }
@@ -707,9 +786,9 @@ int launch_decode(const bf16* q, int ldq, const CUtensorMap& map_k, const CUtens
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
     int nattr = 0;
-    if (CLUSTER) {                                         // the splits of a (request, head tile)
+    if (CLUSTER) {                                         // (up to eight of) the splits of a (request, head tile)
         attr[nattr].id = cudaLaunchAttributeClusterDimension;
-        attr[nattr].val.clusterDim.x = (unsigned)num_splits;
+        attr[nattr].val.clusterDim.x = (unsigned)(num_splits < MAX_CLUSTER_SPLITS ? num_splits : MAX_CLUSTER_SPLITS);
         attr[nattr].val.clusterDim.y = 1;
         attr[nattr].val.clusterDim.z = 1;
         ++nattr;
@@ -773,14 +852,15 @@ long long slb_decode_attention_ws_counters(int S, int H, int Hkv) {
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0) return 0;
     const int g = H / Hkv;
     const int hr = g <= 8 ? 8 : 16;
-    return (long long)S * Hkv * ((g + hr - 1) / hr);
+    return (long long)S * Hkv * ((g + hr - 1) / hr) * MAX_CLUSTER_SPLITS;      // (one per slice in the cluster form)
 }
 
 // scratch and counters may be null when num_splits == 1.  num_pages: pages in k_cache /
 // v_cache ([num_pages][Hkv][ps][D]).  stages: depth of the shared-memory ring, 2..4.
 // num_splits is the most any request is split; a request of T 64-key tiles uses one split
 // while T <= unsplit_tiles, else ceil(T / max(ceil(split_coef * sqrt(T)), ceil(T /
-// num_splits))) of them (8 instead of 9..12).
+// num_splits))) of them (8 instead of 9..12); in the cluster form ceil(T / max(2, ceil(T /
+// num_splits))).
 int slb_decode_attention_ws_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, bf16* out,
                                  int ldo, const int* block_table, int max_pages, const int* ctx_len,
                                  float* scratch, int* counters, int S, int H, int Hkv, int ps,
@@ -790,11 +870,14 @@ int slb_decode_attention_ws_bf16(const bf16* q, int ldq, const bf16* kc, const b
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || max_pages <= 0 || num_pages <= 0 || !(scale > 0.f))
         return SLB_ERR_BAD_ARG;
     if (!slb_decode_attention_ws_supported(ps)) return SLB_ERR_BAD_ARG;
-    // cluster != 0: the splits of a request combine through the shared memory of a thread-block
-    // cluster (at most MAX_CLUSTER_SPLITS of them; scratch and counters are not used)
+    // cluster != 0: the splits of a request combine through the shared memory of thread-block
+    // clusters of up to MAX_CLUSTER_SPLITS blocks; with more splits than that (a multiple of it) every
+    // cluster leaves a partial result in the scratch, and the results are combined slice by slice
+    // through the counters.  Up to MAX_CLUSTER_SPLITS splits scratch and counters are not used.
     const bool clustered = cluster != 0 && num_splits > 1;
-    if (clustered && num_splits > MAX_CLUSTER_SPLITS) return SLB_ERR_TOO_LARGE;
-    if (num_splits < 1 || (num_splits > 1 && !clustered && (scratch == nullptr || counters == nullptr)))
+    if (clustered && num_splits > MAX_CLUSTER_SPLITS && num_splits % MAX_CLUSTER_SPLITS) return SLB_ERR_BAD_ARG;
+    const bool needs_scratch = num_splits > 1 && (!clustered || num_splits > MAX_CLUSTER_SPLITS);
+    if (num_splits < 1 || (needs_scratch && (scratch == nullptr || counters == nullptr)))
         return SLB_ERR_BAD_ARG;
     if (stages < 2 || stages > MAX_STAGES || !(split_coef >= 0.f) || unsplit_tiles < 0) return SLB_ERR_BAD_ARG;
     if (((uintptr_t)kc | (uintptr_t)vc) % 16 || ldq % 8 || (uintptr_t)q % 16) return SLB_ERR_BAD_ARG;

@@ -379,7 +379,7 @@ decode_ws_force_splits = 0     # measurements: launch this many splits instead o
 # launched.  Fitted to measurements on a B200 at head size 128: a tile costs a block about
 # 0.45 us, a split 3 us once plus 1 us per eight splits the last block combines.
 decode_ws_split_coef = 0.8
-decode_ws_unsplit_tiles = 12
+decode_ws_unsplit_tiles = 6    # (us at 256 / 512 keys, batch 8: 5.4 / 8.4 with 12, 5.4 / 6.0 with 6, 5.9 / 6.0 with 3)
 
 _DECODE_COUNTERS = 1 << 16     # arrival counters held per device (256 KiB)
 _decode_counters: Dict[int, torch.Tensor] = {}
@@ -397,16 +397,18 @@ def _decode_counter_buffer(device: torch.device) -> torch.Tensor:
 
 
 def decode_ws_splits(num_seqs: int, num_kv_heads: int, group: int, longest_context: int,
-                     max_splits: int, tile_keys: int) -> int:
+                     max_splits: int, tile_keys: int, cluster: bool = False) -> int:
     """The most splits a request may use (the launch's grid): as many as keep all
-    blocks of the step resident at once (two per SM), 1 for short contexts."""
+    blocks of the step resident at once (two per SM), 1 for short contexts.  ``cluster``:
+    the kernel's rule for the cluster form (two tiles a split at least) instead of the one
+    for the arrival counter (about ``decode_ws_split_coef`` * sqrt(tiles) tiles a split)."""
     head_rows = 8 if group <= 8 else 16
     pairs = num_seqs * num_kv_heads * (-(-group // head_rows))
     tiles = max(1, -(-longest_context // tile_keys))
     if tiles <= decode_ws_unsplit_tiles:
         return 1
     slots = 2 * _num_sms()                      # two blocks of three stages fit on an SM
-    per = max(1, math.ceil(decode_ws_split_coef * math.sqrt(tiles)))
+    per = 2 if cluster else max(1, math.ceil(decode_ws_split_coef * math.sqrt(tiles)))
     longest_uses = -(-tiles // per)             # the kernel's own rule for the longest context
     return max(1, min(max_splits, slots // max(pairs, 1), longest_uses))
 
@@ -420,7 +422,11 @@ def decode_attention_takes(head_dim: int, page_size: int) -> bool:
 # The splits of a request combine through the shared memory of a thread-block cluster when
 # there are at most eight of them (no scratch, no arrival counter, no round trip through the
 # L2 cache: 7 us -> 2 us after the last key at batch 8 on the 7B shape).  A step that would
-# like more splits but already has enough blocks to fill the GPU with eight takes eight.
+# like more splits but already has enough blocks to fill the GPU with eight takes eight; one
+# with few requests and long contexts takes several clusters a request (up to 64 splits), whose
+# partial results meet in global memory: every block of the cluster that finishes a slice of
+# the outputs last combines that slice (at batch 1 the arrival-counter form, where one block
+# combined everything, spent 16 us there whatever the number of splits).
 decode_ws_cluster = True
 
 
@@ -430,16 +436,18 @@ def _decode_launch_shape(ctx, lib, q_device, num_heads, num_kv_heads):
     group = num_heads // num_kv_heads
     splits = decode_ws_force_splits or decode_ws_splits(
         S, num_kv_heads, group, ctx.split_hint_len, lib.slb_decode_attention_ws_max_splits(),
-        lib.slb_decode_attention_ws_tile_keys())
+        lib.slb_decode_attention_ws_tile_keys(), decode_ws_cluster)
     scratch = counters = None
     cluster = False
+    most = lib.slb_decode_attention_ws_max_cluster_splits()
     if splits > 1 and decode_ws_cluster:
-        most = lib.slb_decode_attention_ws_max_cluster_splits()
         pairs = S * num_kv_heads * (-(-group // (8 if group <= 8 else 16)))
         if splits > most and pairs * most >= _num_sms():
             splits = most
-        cluster = splits <= most
-    if splits > 1 and not cluster:
+        if splits > most:
+            splits = splits // most * most          # whole clusters: their results meet in global memory
+        cluster = True
+    if splits > 1 and (not cluster or splits > most):
         if lib.slb_decode_attention_ws_counters(S, num_heads, num_kv_heads) > _DECODE_COUNTERS:
             splits = 1
         else:

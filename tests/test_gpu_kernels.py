@@ -590,18 +590,21 @@ def test_decode_attention_one_launch(H, Hkv, D, ps, window, splits, stages, coef
     want = case.reference(window=window or None)
     counters = torch.zeros(int(lib.slb_decode_attention_ws_counters(S, H, Hkv)), dtype=torch.int32,
                            device=DEV)
-    # twice through global scratch and the arrival counters, then (up to eight splits) with the
-    # splits of a request as a thread-block cluster, which needs neither
-    for cluster in (0, 0, 1):
-        if cluster and splits > lib.slb_decode_attention_ws_max_cluster_splits():
+    # twice through global scratch and the arrival counters, then twice with the splits of a
+    # request as thread-block clusters: up to eight splits one cluster, which needs neither;
+    # beyond, several clusters a request, whose results meet in the scratch slice by slice
+    most = lib.slb_decode_attention_ws_max_cluster_splits()
+    for cluster in (0, 0, 1, 1):
+        if cluster and splits > most and splits % most:
             continue
+        bare = cluster and splits <= most
         out = torch.full_like(q, 7.0)
         scratch = torch.full((max(1, lib.slb_decode_attention_ws_scratch_bytes(S, H, splits) // 4),),
                              float("nan"), device=DEV)
         L.check(lib.slb_decode_attention_ws_bf16(
             q.data_ptr(), q.stride(0), case.kc.data_ptr(), case.vc.data_ptr(), out.data_ptr(),
             out.stride(0), table.data_ptr(), table.shape[1], ctx.ctx_len.data_ptr(),
-            None if cluster else scratch.data_ptr(), None if cluster else counters.data_ptr(), S, H, Hkv, ps,
+            None if bare else scratch.data_ptr(), None if bare else counters.data_ptr(), S, H, Hkv, ps,
             case.kc.shape[0], 1 / math.sqrt(D), window, splits, stages, coef, unsplit, cluster,
             torch.cuda.current_stream().cuda_stream), "decode")
         assert K().decode_attention_status(D, reset=True) == 0, "a bounded wait in the kernel gave up"
@@ -612,6 +615,41 @@ def test_decode_attention_one_launch(H, Hkv, D, ps, window, splits, stages, coef
         out2 = torch.empty_like(q)
         fn(ctx, q, case.kc, case.vc, out2, table, H, Hkv, D, ps, 1 / math.sqrt(D), window)
         assert (out2.float().cpu() - want).abs().max() <= TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("ctxs", [[9000], [9000, 3000, 130], [20000, 70], [1500, 1400, 1300, 1200, 1100]])
+@pytest.mark.parametrize("H,Hkv,D", [(28, 4, 128), (8, 1, 64)])
+def test_decode_attention_of_few_long_requests_uses_several_clusters(ctxs, H, Hkv, D):
+    """Few requests with long contexts: the wrapper launches more splits than a cluster holds,
+    every cluster leaves a partial result and the last block of each slice combines them; one
+    far key is made to dominate a head, so a group whose result were dropped would show.  Twice,
+    bit for bit the same (the counters came back to zero)."""
+    from servelab_b200.ops import kernels as kernels_module
+    ps = 16
+    case = PagedCase(ctxs, [1] * len(ctxs), H, Hkv, D, ps, torch.bfloat16, seed=len(ctxs) + D)
+    g = H // Hkv
+    for i, c in enumerate(ctxs):                            # a key that the first head of each group
+        for kvh in range(Hkv):                              # attends to alone, at a different depth each
+            far = (kvh + 1) * c // (Hkv + 2)
+            case.k[i][far, kvh] = (4.0 * case.q[i][0, kvh * g].float()).to(torch.bfloat16)
+            case.v[i][far, kvh] = 5.0
+    case.scatter()
+    ctx, q, table = _ctx_for(case)
+    want = case.reference()
+    assert float(want.view(len(ctxs), H, D)[:, ::g].min()) > 4.0       # those heads see that key only
+    K().decode_attention_splits_used(D, reset=True)
+    out = torch.full_like(q, 7.0)
+    K().decode_attention(ctx, q, case.kc, case.vc, out, table, H, Hkv, D, ps, 1 / math.sqrt(D), 0)
+    assert K().decode_attention_status(D, reset=True) == 0
+    used = K().decode_attention_splits_used(D, reset=True)
+    if max(ctxs) >= 9000:
+        assert used > 8, used                               # more than one cluster for the long request
+    assert (out.float().cpu() - want).abs().max() <= TOL["bfloat16"]
+    again = torch.full_like(q, 3.0)
+    K().decode_attention(ctx, q, case.kc, case.vc, again, table, H, Hkv, D, ps, 1 / math.sqrt(D), 0)
+    assert torch.equal(again, out)
+    buf = kernels_module._decode_counters.get(torch.cuda.current_device())
+    assert buf is None or int(buf.abs().sum()) == 0
 
 
 def test_decode_attention_many_launches_of_a_mixed_batch():
