@@ -119,7 +119,7 @@ def reference_arm() -> int:
 
 
 TUNABLES = """tc_max_tokens tc_wide_max_tokens cluster_max_kblocks cluster_long_k_max_tokens
-cluster_max_tokens_per_block tc_small_weight_bytes (ints, ops.linear); defer_rope defer_norm fuse_swiglu cluster_sums fuse_qkv_rope fuse_resid_norm (0/1, ops.linear); tc_max_stages
+cluster_max_tokens_per_block (ints, ops.linear); defer_rope defer_norm fuse_swiglu cluster_sums fuse_qkv_rope fuse_resid_norm (0/1, ops.linear); tc_max_stages
 tc_blocks_per_sm decode_ctas_per_sm decode_ws_stages decode_ws_force_splits decode_ws_unsplit_tiles
 tc_max_cluster (ints, ops.kernels); decode_ws_split_coef (float); use_tc_prefill decode_ws_cluster pdl
 pdl_early evict_first (0/1)"""
@@ -132,7 +132,7 @@ def apply_tunables(items):
     for item in items:
         name, value = item.split("=")
         if name in ("tc_max_tokens", "tc_wide_max_tokens", "cluster_max_kblocks", "cluster_long_k_max_tokens",
-                    "cluster_max_tokens_per_block", "tc_small_weight_bytes"):
+                    "cluster_max_tokens_per_block"):
             setattr(linear_ops, name, int(value))
         elif name in ("defer_rope", "defer_norm"):
             linear_ops.defer_split_sums[name[6:]] = bool(int(value))

@@ -41,23 +41,8 @@ def _w_ok(w) -> bool:
     return w.shape[1] % 8 == 0 and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0
 
 
-# Matrices up to this many bytes keep their products on this package's kernels up to 64 tokens
-# instead of 16.  Meant for shapes whose steps are launch-bound (the 0.5B shape: 2 to 9 MB a
-# product), because this package's kernels chain through programmatic dependent launch inside a
-# captured step and the library's GEMMs do not.  Off: measured on the 0.5B shape at 64 requests
-# the step took 1.70 ms against 1.25 ms with the library's GEMMs -- with few row tiles a block
-# of the cluster form finishes 8 to 22 tokens one after the other in its epilogue.
-tc_small_weight_bytes = 0        # off: see the note above
-
-
-def _token_limit(w) -> int:
-    if w.numel() * w.element_size() <= tc_small_weight_bytes:
-        return K.TC_MAX_TOKENS
-    return tc_max_tokens
-
-
 def _tc_ok(x, w, M):
-    limit = _token_limit(w)
+    limit = tc_max_tokens
     if M > limit and K.tc_decode_splits(w.shape[0], w.shape[1]) == 1:
         limit = max(limit, tc_wide_max_tokens)
     return (0 < M <= min(limit, K.TC_MAX_TOKENS) and _w_ok(w)
@@ -101,7 +86,7 @@ def _cluster_ok(x, w, M) -> bool:
     per_block = -(-(-(-Kd // 64)) // min(want, K.TC_MAX_CLUSTER))      # k-blocks of 64 a block streams
     if per_block > cluster_max_kblocks:
         return False
-    if M <= _token_limit(w):
+    if M <= tc_max_tokens:
         return True
     # Above that a block of the cluster finishes its share of the tokens one after the other in
     # its epilogue (tokens rank, rank + splits, ...): the cluster form is taken while that
