@@ -109,7 +109,7 @@ def run_workload(shape: str, peaks: Dict[str, float], layers: int = 0, requests:
                  prompt_len: Optional[Tuple[int, int]] = None, max_tokens: int = 0,
                  temperature: float = -1.0, chunk: int = 0, max_num_seqs: int = 0, page_size: int = 16,
                  num_blocks: int = 0, dtype: str = "bfloat16", warmup: int = 1, note=None,
-                 repeats: int = 3) -> dict:
+                 repeats: int = 3, portion_graphs: bool = True) -> dict:
     """The continuous-batching workload of a shape through ``LLMEngine.generate`` (host token
     ids in, host token ids out), timed by the wall clock around it after ``warmup`` untimed
     passes (graphs of the decode batch sizes are captured at their first use).  The pass is
@@ -139,6 +139,7 @@ def run_workload(shape: str, peaks: Dict[str, float], layers: int = 0, requests:
              f"each, chunk {chunk}, {pages} pages of {page_size}")
     engine = make_engine(cfg, pages, max_num_seqs or n, chunk, hi + new + page_size, wseed, sseed,
                          page_size, dtype)
+    engine.runner.portion_graphs = engine.runner.portion_graphs and portion_graphs
     sp = SamplingParams(temperature=temp, max_tokens=new, ignore_eos=True)
     free_before = engine.runner.cache.stats()["pages_free"]
     for _ in range(warmup):
@@ -170,6 +171,8 @@ def run_workload(shape: str, peaks: Dict[str, float], layers: int = 0, requests:
         "all_pages_returned": engine.runner.cache.stats()["pages_free"] == free_before,
         "floor_seconds": round(floor, 4), "roofline_frac": round(floor / seconds, 4),
         "peaks": peaks.get("source", "given"),
+        "portion_graph_replays": engine.runner.portion_graph_replays,
+        "portion_graphs_held": len(engine.runner._portion_graphs),
     }
     result["ok"] = generated == n * new and result["all_pages_returned"]
     del engine

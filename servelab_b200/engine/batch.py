@@ -67,10 +67,17 @@ class StepContext:
     # ------------------------------------------------------------ packing
     @classmethod
     def pack(cls, entries: Sequence[BatchEntry], num_groups: int, device: str,
-             min_table_width: int = 1, into: Optional["StepContext"] = None) -> "StepContext":
+             min_table_width: int = 1, into: Optional["StepContext"] = None,
+             pad: Optional[Tuple[int, int, int]] = None, _host_only: bool = False) -> "StepContext":
         """``into``: a context packed earlier for the same number of requests,
         tokens, wanted rows and table widths; its device buffer is overwritten in
-        place (a captured CUDA graph keeps reading the same addresses)."""
+        place (a captured CUDA graph keeps reading the same addresses).
+        ``pad`` = (tokens, requests, wanted rows): the step is laid out for these sizes,
+        which must exceed what the entries hold in requests and not fall short in the
+        others.  Padding tokens belong to the last, empty request (no pages: nothing is
+        written to the cache, no attention tile covers them); padding rows repeat row 0."""
+        if pad is not None:
+            return cls._pack_padded(entries, num_groups, device, min_table_width, into, pad)
         ctx = cls(device)
         S = len(entries)
         q_lens = [len(e.tokens) for e in entries]
@@ -104,7 +111,8 @@ class StepContext:
             stamps = into._stamps[into._flip]
             hv = host.numpy()
         else:
-            host = torch.empty(total, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+            host = torch.empty(total, dtype=torch.int32,
+                               pin_memory=torch.cuda.is_available() and not _host_only)
             stamps = None
             hv = host.numpy()
             hv[:] = 0
@@ -115,7 +123,7 @@ class StepContext:
         starts = np.asarray([e.start for e in entries], dtype=np.int32)
         cu = np.zeros(S + 1, dtype=np.int32)
         np.cumsum(q, out=cu[1:])
-        if T == S:
+        if T == S and all(n == 1 for n in q_lens):
             hv[o_tok:o_tok + T] = [e.tokens[0] for e in entries]
             hv[o_pos:o_pos + T] = starts
             hv[o_seq:o_seq + T] = np.arange(S, dtype=np.int32)
@@ -165,6 +173,14 @@ class StepContext:
             into.ctx_lens = [e.start + n for e, n in zip(entries, q_lens)]
             into.max_ctx_len = max(into.ctx_lens) if into.ctx_lens else 0
             return into
+        if _host_only:                                # (the padded form lays the arrays out anew)
+            ctx._host = host
+            ctx._widths = widths
+            ctx.q_lens = q_lens
+            ctx.state_slot_ids = [e.state_slot for e in entries]
+            ctx.ctx_lens = [e.start + n for e, n in zip(entries, q_lens)]
+            ctx.max_ctx_len = max(ctx.ctx_lens) if ctx.ctx_lens else 0
+            return ctx
         dev = host.to(device, non_blocking=True)
         ctx._host = host                              # keep the pinned buffer alive
         ctx._dev = dev
@@ -186,11 +202,114 @@ class StepContext:
         ctx.decode_only = S > 0 and all(n == 1 for n in q_lens)
         return ctx
 
+    @classmethod
+    def _pack_padded(cls, entries, num_groups, device, min_table_width, into, pad):
+        """The padded form of ``pack``: empty entries fill the requests, the last of them
+        takes the padding tokens in the flat arrays only (its q_len stays 0, so no kernel
+        that walks requests or tiles sees them)."""
+        Tp, Sp, Rp = pad
+        S = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        R = sum(len(e.want) for e in entries)
+        if Sp <= S or Tp < T or Rp < R:
+            raise ValueError("padding sizes must exceed the requests and hold the tokens and rows")
+        empty_tables = [np.empty(0, dtype=np.int32)] * num_groups
+        filler = [BatchEntry(tokens=(), start=0, want=(), block_tables=empty_tables, state_slot=0,
+                             table_stamps=[-1] * num_groups) for _ in range(Sp - S)]
+        inner = cls.pack(list(entries) + filler, num_groups, device, min_table_width, _host_only=True)
+        # the inner layout has T tokens and R rows; rebuild it with the padded sizes
+        widths = inner._widths
+        sizes = [Tp, Tp, Tp, Sp + 1, Sp, Sp, Rp] + [Sp * w for w in widths]
+        offsets, total = [], 0
+        for n in sizes:
+            offsets.append(total)
+            total += _align4(max(n, 1))
+        src = inner._host.numpy()
+        in_sizes = [T, T, T, Sp + 1, Sp, Sp, R] + [Sp * w for w in widths]
+        in_off, acc = [], 0
+        for n in in_sizes:
+            in_off.append(acc)
+            acc += _align4(max(n, 1))
+        reuse = into is not None
+        if reuse:
+            if into._layout != ("padded", Tp, Sp, Rp, tuple(widths)):
+                raise ValueError("batch does not have the shape of the context to overwrite")
+            into._flip ^= 1
+            host = into._host2[into._flip]
+        else:
+            host = torch.empty(total, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        hv = host.numpy()
+        hv[:] = 0
+        for i, (o, n) in enumerate(zip(in_off, in_sizes)):
+            hv[offsets[i]:offsets[i] + n] = src[o:o + n]
+        hv[offsets[2] + T:offsets[2] + Tp] = Sp - 1           # padding tokens: the last, empty request
+        ctx = into if reuse else cls(device)
+        if reuse:
+            ctx._dev.copy_(host, non_blocking=True)
+        else:
+            other = torch.empty(total, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+            ctx._host2, ctx._flip = [host, other], 0
+            ctx._dev = host.to(device, non_blocking=True)
+            ctx._layout = ("padded", Tp, Sp, Rp, tuple(widths))
+            dev = ctx._dev
+
+            def view(k, n):
+                return dev[offsets[k]:offsets[k] + n]
+            ctx.token_ids, ctx.positions, ctx.seq_of_token = view(0, Tp), view(1, Tp), view(2, Tp)
+            ctx.cu_q, ctx.ctx_len = view(3, Sp + 1), view(4, Sp)
+            ctx.state_slots, ctx.logit_rows = view(5, Sp), view(6, Rp)
+            ctx.block_tables = [view(7 + g, Sp * w).view(Sp, w) for g, w in enumerate(widths)]
+            ctx.num_tokens, ctx.num_seqs, ctx.num_logit_rows = Tp, Sp, Rp
+            ctx._padded_tiles = {}
+        ctx._host = host
+        ctx.q_lens, ctx.state_slot_ids = inner.q_lens, inner.state_slot_ids
+        ctx.ctx_lens, ctx.max_ctx_len = inner.ctx_lens, inner.max_ctx_len
+        ctx.split_hint_len = inner.max_ctx_len
+        ctx.decode_only = False
+        ctx.real_sizes = (T, S, R)
+        for key in ctx._padded_tiles:                       # the work lists of the kernels that asked
+            ctx._refresh_tiles(key)
+        return ctx
+
+    def _tile_bound(self, group_size: int, rows_per_tile: int) -> int:
+        return -(-self.num_tokens * group_size // rows_per_tile) + self.num_seqs
+
+    def _refresh_tiles(self, key):
+        group_size, rows_per_tile = key
+        dev, hosts, flip = self._padded_tiles[key]
+        bound = dev.numel() // 2
+        rows = np.asarray(self.q_lens, dtype=np.int64) * group_size
+        per_seq = -(-rows // rows_per_tile)
+        first = np.cumsum(per_seq) - per_seq
+        seqs = np.repeat(np.arange(len(self.q_lens)), per_seq)
+        n = len(seqs)
+        host = hosts[flip]
+        hv = host.numpy()
+        hv[:bound] = self.num_seqs - 1                      # tiles beyond the step's: the empty request
+        hv[bound:] = 0
+        hv[:n] = seqs
+        hv[bound:bound + n] = (np.arange(n) - np.repeat(first, per_seq)) * rows_per_tile
+        dev.copy_(host, non_blocking=True)
+        self._padded_tiles[key] = (dev, hosts, flip ^ 1)
+
     # ------------------------------------------------- attention work list
     def attention_tiles(self, group_size: int, rows_per_tile: int):
         """Tiles of ``rows_per_tile`` query rows over each request's q_len *
         group_size flattened rows: (tile_seq, tile_row0, count) on the device."""
         key = (group_size, rows_per_tile)
+        padded = getattr(self, "_padded_tiles", None)
+        if padded is not None:
+            # a padded context (it may be replayed in a graph): lists of a fixed length at fixed
+            # addresses, rewritten whenever the context is packed anew
+            if key not in padded:
+                bound = self._tile_bound(group_size, rows_per_tile)
+                pin = torch.cuda.is_available()
+                hosts = [torch.empty(2 * bound, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+                padded[key] = (torch.empty(2 * bound, dtype=torch.int32, device=self.device), hosts, 0)
+                self._refresh_tiles(key)
+            dev = padded[key][0]
+            bound = dev.numel() // 2
+            return dev[:bound], dev[bound:], bound
         hit = self._tiles.get(key)
         if hit is None:
             rows = np.asarray(self.q_lens, dtype=np.int64) * group_size

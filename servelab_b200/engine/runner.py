@@ -83,6 +83,18 @@ class ModelRunner:
             getattr(b, "graph_safe", False)
             for b in list(self.model.blocks) + [self.model.embedding_position, self.model.final_norm])
         self.graph_replays = 0
+        # Steps with prompt portions replay graphs too, captured for padded sizes (tokens,
+        # requests, wanted rows rounded up; ``StepContext.pack(pad=...)``): a layer costs the
+        # host 0.2 ms of launches when run eagerly, which binds the steps of a small model.
+        # A shape is captured when it comes up the second time; at most
+        # ``max_portion_graphs`` are kept (least recently used first out).
+        self.portion_graphs = cuda_graphs
+        self.max_portion_graph_tokens = 2048
+        self.max_portion_graphs = 24
+        self.portion_graph_after = 2      # times a shape is asked for before it is captured
+        self._portion_graphs = {}         # padded sizes -> (graph, context, logits)
+        self._portion_seen = {}           # padded sizes -> times asked for
+        self.portion_graph_replays = 0
         self._table_rows = {}             # (request, group) -> (stamp, block table as int32 array)
         # through a weak reference: the cache manager must not keep the runner alive in a
         # cycle, or a dropped engine (its graphs, its memory pool) would be destroyed only when
@@ -143,10 +155,67 @@ class ModelRunner:
             return self._step_graph(entries, token_ids_from)
         if token_ids_from is not None:
             raise ValueError("token ids from the device need a step that replays a graph")
+        if self.portion_graphs and self._graph_safe and not self.storage.state_layers:
+            pad = self._portion_pad(entries)
+            if pad is not None:
+                hit = self._portion_graphs.get(pad)
+                seen = self._portion_seen[pad] = self._portion_seen.get(pad, 0) + 1
+                if hit is not None or seen >= self.portion_graph_after:
+                    return self._step_portion_graph(entries, pad)
         ctx = StepContext.pack(entries, self.num_groups, self.device)
         if ctx.num_tokens == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         return self.model.forward(ctx, self.storage.layer_caches)
+
+    @staticmethod
+    def _round_up(n: int, steps) -> int:
+        for limit, unit in steps:
+            if n <= limit:
+                return -(-n // unit) * unit
+        return n
+
+    def _portion_pad(self, entries: List[BatchEntry]):
+        """(tokens, requests, wanted rows) a step is padded to, or None if it runs eagerly."""
+        T = sum(len(e.tokens) for e in entries)
+        R = sum(len(e.want) for e in entries)
+        if T == 0 or T > self.max_portion_graph_tokens:
+            return None
+        Tp = self._round_up(T, ((64, 16), (512, 64), (self.max_portion_graph_tokens, 256)))
+        Sp = 1 << len(entries).bit_length()                 # a power of two above the requests
+        Rp = 1 << (R - 1).bit_length() if R else 0
+        return Tp, Sp, Rp
+
+    def _step_portion_graph(self, entries: List[BatchEntry], pad) -> torch.Tensor:
+        """A step of any composition through the graph captured for its padded sizes.  The
+        returned logits live in the graph's memory until its next replay."""
+        width = -(-self.max_model_len // self.page_size)
+        R = sum(len(e.want) for e in entries)
+        hit = self._portion_graphs.pop(pad, None)
+        if hit is None:
+            ctx = StepContext.pack(entries, self.num_groups, self.device, min_table_width=width, pad=pad)
+            self.model.forward(ctx, self.storage.layer_caches)        # builds libraries, warms caches
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            gc.collect()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    logits = self.model.forward(ctx, self.storage.layer_caches)
+            finally:
+                if gc_was_on:
+                    gc.enable()
+            hit = (graph, ctx, logits)
+            while len(self._portion_graphs) >= self.max_portion_graphs:
+                self._portion_graphs.pop(next(iter(self._portion_graphs)))
+        graph, ctx, logits = hit
+        self._portion_graphs[pad] = hit                     # (most recently used last)
+        StepContext.pack(entries, self.num_groups, self.device, min_table_width=width, into=ctx, pad=pad)
+        graph.replay()
+        self.portion_graph_replays += 1
+        return logits[:R]
 
     def _step_graph(self, entries: List[BatchEntry],
                     token_ids_from: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -99,6 +99,30 @@ def test_mixed_with_page_reuse(model, dtype):
     _check(model, dtype, steps, need)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_with_portions_replayed_as_padded_graphs(model, dtype):
+    """Steps of any composition replay graphs captured for padded sizes (tokens, requests and
+    wanted rows rounded up; the padding tokens write no cache and belong to no attention tile):
+    the mixed trace with page reuse, every shape captured at its first use.  Logits within the
+    bound of the plain implementation; in float32 bit for bit those of the eager steps."""
+    from servelab_b200.replay import TraceSession
+    steps = H.trace_mixed(model["requests"], seed=11)
+    need = H.peak_tokens(steps)
+    sess = TraceSession(model["folder"], dtype, need, page_size=model["page"], max_live=4,
+                        poison_cache=True, cuda_graphs=True)
+    sess.runner.portion_graph_after = 1
+    got = H.collect(steps, H.run_session(sess, steps), model["cfg"]["vocab_size"])
+    assert sess.runner.portion_graph_replays > 0
+    sess.cache.check_invariants()
+    eager = _check(model, dtype, steps, need)
+    for rid, ids in model["requests"].items():
+        for pos in range(len(ids)):
+            err = float(np.abs(got[rid][pos] - model["ref"][rid][pos]).max())
+            assert err <= tol(model, dtype), (rid, pos, err)
+            if dtype == "float32":
+                assert np.array_equal(got[rid][pos], eager[rid][pos]), (rid, pos)
+
+
 def test_float32_cut_invariance(model):
     """In float32 the logits of a position are bit-identical however the tokens are cut."""
     a = _check(model, "float32", H.trace_whole(model["requests"]))
