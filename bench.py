@@ -138,7 +138,7 @@ def apply_tunables(items):
             linear_ops.defer_split_sums[name[6:]] = bool(int(value))
         elif name in ("fuse_swiglu", "cluster_sums", "fuse_qkv_rope", "fuse_resid_norm"):
             setattr(linear_ops, name, bool(int(value)))
-        elif name in ("tc_max_stages", "tc_blocks_per_sm", "decode_ctas_per_sm", "decode_ws_stages",
+        elif name in ("tc_max_stages", "tc_token_group", "tc_token_group_bytes", "tc_blocks_per_sm", "decode_ctas_per_sm", "decode_ws_stages",
                       "decode_ws_force_splits", "decode_ws_unsplit_tiles"):
             setattr(K, name, int(value))
         elif name == "tc_max_cluster":                      # at most 8, the portable cluster size

@@ -204,10 +204,18 @@ __device__ __forceinline__ void store8(float* dst, const float (&o)[8]) {
 template <typename TO>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-    TO* __restrict__ out, int ldo, float* __restrict__ partial, const float* __restrict__ bias,
-    int M, int N, int K, int ntok16, int max_stages, int* __restrict__ status, int swiglu,
-    int flags, const RowScale rs, const SlbTraceArg tr) {
+    TO* __restrict__ out_all, int ldo, float* __restrict__ partial, const float* __restrict__ bias,
+    int M_all, int N, int K, int ntok16, int max_stages, int* __restrict__ status, int swiglu,
+    int flags, const RowScale rs_all, int tok_group, const SlbTraceArg tr) {
     __shared__ float rstd_s[TC_MAX_TOK];                    // RowScale: 1 / rms of every token's input row
+    // tok_group > 0: the step's tokens in groups of that many (grid z), each block one group --
+    // for matrices small enough to be read once per group from the L2 cache, so that a block
+    // finishes few tokens however many the step has
+    const int tok_base = tok_group > 0 ? (int)blockIdx.z * tok_group : 0;
+    const int M = tok_group > 0 ? min(tok_group, M_all - tok_base) : M_all;
+    TO* out = out_all != nullptr ? out_all + (size_t)tok_base * ldo : nullptr;
+    RowScale rs = rs_all;
+    if (rs.sumsq != nullptr) rs.sumsq += (size_t)tok_base * rs.tiles;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -265,7 +273,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
             }
             pdl_wait();
             for (int i = 0; i < ahead; ++i)
-                tma_load_2d(b_stage + i * B_STAGE_BYTES, &map_x, &full[i], (kb_begin + i) * TC_BK, 0);
+                tma_load_2d(b_stage + i * B_STAGE_BYTES, &map_x, &full[i], (kb_begin + i) * TC_BK, tok_base);
             for (int i = ahead; i < iters; ++i) {
                 const int s = i % TC_STAGES;
                 if (!mbar_wait(&empty[s], ((i / TC_STAGES) & 1) ^ 1)) {
@@ -275,7 +283,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
                 mbar_expect_tx(&full[s], bytes);
                 const int k = (kb_begin + i) * TC_BK;
                 load_w_tile(a_stage + s * A_STAGE_BYTES, &map_w, &full[s], k, n0, w_first, w_policy);
-                tma_load_2d(b_stage + s * B_STAGE_BYTES, &map_x, &full[s], k, 0);
+                tma_load_2d(b_stage + s * B_STAGE_BYTES, &map_x, &full[s], k, tok_base);
             }
         }
     } else if (warp == 1) {
@@ -375,7 +383,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_decode_kernel(
                     if (splits == 1)
                         out[(size_t)tok * ldo + n] = from_float<TO>(val + (bias ? bias[n] : 0.f));
                     else
-                        partial[((size_t)split * M + tok) * N + n] = val;
+                        partial[((size_t)split * M_all + tok_base + tok) * N + n] = val;
                 }
             }
         }
@@ -544,9 +552,29 @@ __device__ __forceinline__ RopeTarget rope_target(const RopeEpilogue& rope, int 
 template <int EPI, bool WIDE>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-    bf16* __restrict__ out, int ldo, const float* __restrict__ bias, int M, int N, int K, int ntok16,
-    int max_stages, int* __restrict__ status, const RopeEpilogue rope, const ResidEpilogue res,
-    const RowScale rs, int flags, const SlbTraceArg tr) {
+    bf16* __restrict__ out_all, int ldo, const float* __restrict__ bias, int M_all, int N, int K, int ntok16,
+    int max_stages, int* __restrict__ status, const RopeEpilogue rope_all, const ResidEpilogue res_all,
+    const RowScale rs_all, int flags, int tok_group, const SlbTraceArg tr) {
+    // tok_group > 0: the step's tokens in groups (grid z), as in gemm_tc_decode_kernel
+    const int tok_base = tok_group > 0 ? (int)blockIdx.z * tok_group : 0;
+    const int M = tok_group > 0 ? min(tok_group, M_all - tok_base) : M_all;
+    bf16* out = out_all != nullptr ? out_all + (size_t)tok_base * ldo : nullptr;
+    RopeEpilogue rope = rope_all;
+    ResidEpilogue res = res_all;
+    RowScale rs = rs_all;
+    if (tok_base > 0) {
+        if (EPI == EPI_ROPE) {
+            rope.positions += tok_base;
+            rope.seq_of_token += tok_base;
+            rope.q_out += (size_t)tok_base * rope.ld_q;
+        }
+        if (EPI == EPI_RESID) {
+            res.resid += (size_t)tok_base * res.ld;
+            res.z += (size_t)tok_base * res.ldz;
+            res.sumsq += (size_t)tok_base * gridDim.x;
+        }
+        if (rs.sumsq != nullptr) rs.sumsq += (size_t)tok_base * rs.tiles;
+    }
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -616,7 +644,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
             }
             pdl_wait();
             for (int i = 0; i < ahead; ++i)
-                tma_load_2d(b_stage + i * B_STAGE_BYTES, &map_x, &full[i], (kb_begin + i) * TC_BK, 0);
+                tma_load_2d(b_stage + i * B_STAGE_BYTES, &map_x, &full[i], (kb_begin + i) * TC_BK, tok_base);
             for (int i = ahead; i < iters; ++i) {
                 const int s = i % TC_STAGES;
                 if (!mbar_wait(&empty[s], ((i / TC_STAGES) & 1) ^ 1)) {
@@ -626,7 +654,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
                 mbar_expect_tx(&full[s], bytes);
                 const int k = (kb_begin + i) * TC_BK;
                 load_w_tile(a_stage + s * A_STAGE_BYTES, &map_w, &full[s], k, n0, w_first, w_policy);
-                tma_load_2d(b_stage + s * B_STAGE_BYTES, &map_x, &full[s], k, 0);
+                tma_load_2d(b_stage + s * B_STAGE_BYTES, &map_x, &full[s], k, tok_base);
             }
         }
         __syncwarp();
@@ -968,9 +996,11 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box
 template <typename TO>
 int run(const bf16* x, int ldx, const bf16* W, int ldw, TO* out, int ldo, const float* bias,
         float* workspace, int M, int N, int K, int splits, int max_stages, int defer_sum, int swiglu,
-        const RowScale& rs, cudaStream_t st) {
+        const RowScale& rs, int tok_group, cudaStream_t st) {
     CUtensorMap map_w, map_x;
-    const int ntok16 = (M + 15) / 16 * 16;
+    const int Mb = tok_group > 0 ? (M < tok_group ? M : tok_group) : M;      // tokens a block sees
+    const int groups = tok_group > 0 ? (M + tok_group - 1) / tok_group : 1;
+    const int ntok16 = (Mb + 15) / 16 * 16;
     int rc = make_map(&map_w, W, N, K, ldw, TC_BM);
     if (rc != 0) return rc;
     rc = make_map(&map_x, x, M, K, ldx, ntok16);
@@ -983,9 +1013,9 @@ int run(const bf16* x, int ldx, const bf16* W, int ldw, TO* out, int ldo, const 
     int* status = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&status, tc_status_word);
     if (e != cudaSuccess) return (int)e;
-    rc = slb_launch(gemm_tc_decode_kernel<TO>, dim3((N + TC_BM - 1) / TC_BM, splits), dim3(TC_THREADS),
+    rc = slb_launch(gemm_tc_decode_kernel<TO>, dim3((N + TC_BM - 1) / TC_BM, splits, groups), dim3(TC_THREADS),
                     TC_SMEM, st, map_w, map_x, out, ldo, workspace, bias, M, N, K, ntok16, max_stages, status,
-                    swiglu, slb_kernel_flags, rs, slb_trace_arg());
+                    swiglu, slb_kernel_flags, rs, tok_group, slb_trace_arg());
     if (rc != 0 || splits == 1 || defer_sum) return rc;
     return slb_launch(gemm_tc_reduce_kernel<TO>, dim3((N + 255) / 256, M), dim3(256), 0, st,
                       (const float*)workspace, out, ldo, bias, M, N, splits);
@@ -1015,9 +1045,11 @@ int launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, int cluster_
 template <int EPI>
 int run_cluster(const bf16* x, int ldx, const bf16* W, int ldw, bf16* out, int ldo, const float* bias,
                 int M, int N, int K, int splits, int max_stages, const RopeEpilogue& rope,
-                const ResidEpilogue& res, const RowScale& rs, cudaStream_t st) {
+                const ResidEpilogue& res, const RowScale& rs, int tok_group, cudaStream_t st) {
     CUtensorMap map_w, map_x;
-    const int ntok16 = (M + 15) / 16 * 16;
+    const int Mb = tok_group > 0 ? (M < tok_group ? M : tok_group) : M;      // tokens a block sees
+    const int groups = tok_group > 0 ? (M + tok_group - 1) / tok_group : 1;
+    const int ntok16 = (Mb + 15) / 16 * 16;
     int rc = make_map(&map_w, W, N, K, ldw, TC_BM);
     if (rc != 0) return rc;
     rc = make_map(&map_x, x, M, K, ldx, ntok16);
@@ -1037,7 +1069,8 @@ int run_cluster(const bf16* x, int ldx, const bf16* W, int ldw, bf16* out, int l
                   aligned(rope.bias, 0, 4, 16) && aligned(rope.inv_freq, 0, 4, 16) &&
                   aligned(rope.q_out, rope.ld_q, 2, 8) && aligned(rope.k_cache, 0, 2, 8) &&
                   aligned(rope.v_cache, 0, 2, 8);
-    const bool few = M <= tc_cluster_single_max_tokens || !wide_ok;
+    // a thread a row while a block finishes at most two tokens, else a warp a token
+    const bool few = (Mb <= tc_cluster_single_max_tokens && (Mb + splits - 1) / splits <= 2) || !wide_ok;
     rc = few ? slb_configure(&configured, gemm_tc_cluster_kernel<EPI, false>, TC_SMEM_BUDGET)
              : slb_configure(&configured_wide, gemm_tc_cluster_kernel<EPI, true>, TC_SMEM_BUDGET);
     if (rc != 0) return rc;
@@ -1052,17 +1085,25 @@ int run_cluster(const bf16* x, int ldx, const bf16* W, int ldw, bf16* out, int l
     cudaError_t e = cudaGetSymbolAddress((void**)&status, tc_status_word);
     if (e != cudaSuccess) return (int)e;
     if (few)
-        return launch_cluster(gemm_tc_cluster_kernel<EPI, false>, dim3((N + TC_BM - 1) / TC_BM, splits),
+        return launch_cluster(gemm_tc_cluster_kernel<EPI, false>, dim3((N + TC_BM - 1) / TC_BM, splits, groups),
                               dim3(TC_THREADS), splits, smem, st, map_w, map_x, out, ldo, bias, M, N, K, ntok16,
-                              max_stages, status, rope, res, rs, slb_kernel_flags, slb_trace_arg());
-    return launch_cluster(gemm_tc_cluster_kernel<EPI, true>, dim3((N + TC_BM - 1) / TC_BM, splits),
+                              max_stages, status, rope, res, rs, slb_kernel_flags, tok_group, slb_trace_arg());
+    return launch_cluster(gemm_tc_cluster_kernel<EPI, true>, dim3((N + TC_BM - 1) / TC_BM, splits, groups),
                           dim3(TC_THREADS), splits, smem, st, map_w, map_x, out, ldo, bias, M, N, K, ntok16,
-                          max_stages, status, rope, res, rs, slb_kernel_flags, slb_trace_arg());
+                          max_stages, status, rope, res, rs, slb_kernel_flags, tok_group, slb_trace_arg());
 }
 
-int check_cluster_args(const bf16* x, int ldx, const bf16* W, int ldw, int M, int N, int K, int splits) {
+// tok_group: 0, or the tokens a block takes (a multiple of 16 up to 64); the step's tokens are
+// then cut into groups of that many
+int check_tok_group(int tok_group) {
+    return (tok_group < 0 || tok_group % 16 || tok_group > TC_MAX_TOK) ? SLB_ERR_BAD_ARG : 0;
+}
+
+int check_cluster_args(const bf16* x, int ldx, const bf16* W, int ldw, int M, int N, int K, int splits,
+                       int tok_group) {
     if (K <= 0 || K % 8 || ldw % 8 || ldw < K || (uintptr_t)W % 16) return SLB_ERR_BAD_ARG;
     if (x == nullptr || ldx % 8 || ldx < K || (uintptr_t)x % 16) return SLB_ERR_BAD_ARG;
+    if (check_tok_group(tok_group) != 0) return SLB_ERR_BAD_ARG;
     if (M > TC_MAX_TOK) return SLB_ERR_TOO_LARGE;
     const int kblocks = (K + TC_BK - 1) / TC_BK;
     if (splits < 1 || splits > kblocks) return SLB_ERR_BAD_ARG;
@@ -1078,15 +1119,16 @@ extern "C" {
 // no workspace, no second kernel.  scale_sumsq: as for slb_gemm_tc_decode_bf16.
 int slb_gemm_tc_cluster_bf16(const bf16* x, int ldx, const bf16* W, int ldw, bf16* out, int ldo,
                              const float* bias, int M, int N, int K, int splits, int max_stages,
-                             const float* scale_sumsq, int scale_tiles, float scale_eps, cudaStream_t st) {
+                             const float* scale_sumsq, int scale_tiles, float scale_eps, int tok_group,
+                             cudaStream_t st) {
     if (M <= 0 || N <= 0) return 0;
     if (ldo < N || out == nullptr) return SLB_ERR_BAD_ARG;
-    const int rc = check_cluster_args(x, ldx, W, ldw, M, N, K, splits);
+    const int rc = check_cluster_args(x, ldx, W, ldw, M, N, K, splits, tok_group);
     if (rc != 0) return rc;
     if (scale_sumsq != nullptr && scale_tiles <= 0) return SLB_ERR_BAD_ARG;
     const RowScale rs = {scale_sumsq, scale_tiles, (float)K, scale_eps};
     return run_cluster<EPI_STORE>(x, ldx, W, ldw, out, ldo, bias, M, N, K, splits, max_stages, RopeEpilogue{},
-                                  ResidEpilogue{}, rs, st);
+                                  ResidEpilogue{}, rs, tok_group, st);
 }
 
 // The product that closes a residual branch together with the RMS norm that follows it:
@@ -1097,16 +1139,16 @@ int slb_gemm_tc_cluster_bf16(const bf16* x, int ldx, const bf16* W, int ldw, bf1
 int slb_gemm_tc_resid_norm_bf16(const bf16* x, int ldx, const bf16* W, int ldw, const float* bias,
                                 float* resid, int ld_resid, const float* norm_weight, bf16* z, int ldz,
                                 float* sumsq, int M, int N, int K, int splits, int max_stages,
-                                cudaStream_t st) {
+                                int tok_group, cudaStream_t st) {
     if (M <= 0 || N <= 0) return 0;
     if (resid == nullptr || norm_weight == nullptr || z == nullptr || sumsq == nullptr || ld_resid < N ||
         ldz < N)
         return SLB_ERR_BAD_ARG;
-    const int rc = check_cluster_args(x, ldx, W, ldw, M, N, K, splits);
+    const int rc = check_cluster_args(x, ldx, W, ldw, M, N, K, splits, tok_group);
     if (rc != 0) return rc;
     const ResidEpilogue res = {resid, ld_resid, norm_weight, z, ldz, sumsq};
     return run_cluster<EPI_RESID>(x, ldx, W, ldw, nullptr, 0, bias, M, N, K, splits, max_stages, RopeEpilogue{},
-                                  res, RowScale{}, st);
+                                  res, RowScale{}, tok_group, st);
 }
 
 // The q|k|v product of an attention layer with what follows it: W is [(H + 2 Hkv) D, K]
@@ -1120,7 +1162,8 @@ int slb_gemm_tc_qkv_rope_bf16(const bf16* x, int ldx, const bf16* W, int ldw, co
                               int max_pages, int page_size, int num_pages, const float* inv_freq,
                               int rotary_dim, bf16* q_out, int ld_q, bf16* k_cache, bf16* v_cache, int M,
                               int H, int Hkv, int D, int K, int splits, int max_stages,
-                              const float* scale_sumsq, int scale_tiles, float scale_eps, cudaStream_t st) {
+                              const float* scale_sumsq, int scale_tiles, float scale_eps, int tok_group,
+                              cudaStream_t st) {
     if (M <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || D < 16 || D > TC_BM || TC_BM % D || page_size <= 0 || max_pages <= 0)
         return SLB_ERR_BAD_ARG;
@@ -1129,7 +1172,7 @@ int slb_gemm_tc_qkv_rope_bf16(const bf16* x, int ldx, const bf16* W, int ldw, co
         (k_cache == nullptr) != (v_cache == nullptr) || (k_cache != nullptr && num_pages <= 0))
         return SLB_ERR_BAD_ARG;
     const int N = (H + 2 * Hkv) * D;
-    const int rc = check_cluster_args(x, ldx, W, ldw, M, N, K, splits);
+    const int rc = check_cluster_args(x, ldx, W, ldw, M, N, K, splits, tok_group);
     if (rc != 0) return rc;
     int* status = nullptr;
     if (cudaGetSymbolAddress((void**)&status, tc_status_word) != cudaSuccess) return SLB_ERR_BAD_ARG;
@@ -1138,7 +1181,7 @@ int slb_gemm_tc_qkv_rope_bf16(const bf16* x, int ldx, const bf16* W, int ldw, co
     if (scale_sumsq != nullptr && scale_tiles <= 0) return SLB_ERR_BAD_ARG;
     const RowScale rs = {scale_sumsq, scale_tiles, (float)K, scale_eps};
     return run_cluster<EPI_ROPE>(x, ldx, W, ldw, nullptr, 0, nullptr, M, N, K, splits, max_stages, rope,
-                                 ResidEpilogue{}, rs, st);
+                                 ResidEpilogue{}, rs, tok_group, st);
 }
 
 // workspace: float32 [splits * M * N] when splits > 1 (may be null otherwise).
@@ -1153,8 +1196,10 @@ int slb_gemm_tc_qkv_rope_bf16(const bf16* x, int ldx, const bf16* W, int ldw, co
 int slb_gemm_tc_decode_bf16(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo,
                             const float* bias, float* workspace, int out_f32, int M, int N, int K,
                             int splits, int max_stages, int defer_sum, int swiglu,
-                            const float* scale_sumsq, int scale_tiles, float scale_eps, cudaStream_t st) {
+                            const float* scale_sumsq, int scale_tiles, float scale_eps, int tok_group,
+                            cudaStream_t st) {
     if (M <= 0 || N <= 0) return 0;
+    if (check_tok_group(tok_group) != 0) return SLB_ERR_BAD_ARG;
     if (K <= 0 || K % 8 || ldw % 8 || ldw < K || (!swiglu && ldo < N)) return SLB_ERR_BAD_ARG;
     if (x == nullptr || ldx % 8 || ldx < K || (uintptr_t)x % 16 || (uintptr_t)W % 16) return SLB_ERR_BAD_ARG;
     if (M > TC_MAX_TOK) return SLB_ERR_TOO_LARGE;
@@ -1171,9 +1216,9 @@ int slb_gemm_tc_decode_bf16(const bf16* x, int ldx, const bf16* W, int ldw, void
     const RowScale rs = {scale_sumsq, scale_tiles, (float)K, scale_eps};
     if (out_f32)
         return run<float>(x, ldx, W, ldw, (float*)out, ldo, bias, workspace, M, N, K, splits, max_stages,
-                          defer_sum, swiglu, rs, st);
+                          defer_sum, swiglu, rs, tok_group, st);
     return run<bf16>(x, ldx, W, ldw, (bf16*)out, ldo, bias, workspace, M, N, K, splits, max_stages, defer_sum,
-                     swiglu, rs, st);
+                     swiglu, rs, tok_group, st);
 }
 
 // out[M, N] = sum of float32 partial sums [splits][M][N] (+ bias), in order.

@@ -503,9 +503,26 @@ tc_blocks_per_sm = 2       # blocks of a product the K split aims at per SM.  Me
                            # 3.45 / 3.22, 4 and 2: 3.48 / 3.26
 
 
-def tc_decode_splits(n_out: int, k: int) -> int:
-    """K splits so that (row tiles x splits) is about ``tc_blocks_per_sm`` blocks per SM."""
-    tiles = -(-n_out // 128)
+tc_token_group = 16            # tokens a block takes when a step's tokens are cut into groups
+tc_token_group_bytes = 20 << 20    # ... which happens for matrices up to this size from 17 tokens on: every
+                                   # group reads the matrix again, from the L2 cache
+
+
+def tc_token_groups(m: int, w) -> int:
+    """Into how many groups of ``tc_token_group`` tokens the tcgen05 products cut a step of
+    ``m`` tokens for the matrix ``w`` (1: not at all).  Small matrices only: with few row
+    tiles a product has few blocks, and each would finish many tokens one after the other;
+    cut into groups it has as many blocks again per group, at the price of reading the
+    matrix once per group."""
+    if m <= tc_token_group or w.numel() * w.element_size() > tc_token_group_bytes:
+        return 1
+    return -(-m // tc_token_group)
+
+
+def tc_decode_splits(n_out: int, k: int, groups: int = 1) -> int:
+    """K splits so that (row tiles x token groups x splits) is about ``tc_blocks_per_sm``
+    blocks per SM."""
+    tiles = -(-n_out // 128) * groups
     kblocks = -(-k // 64)
     slots = tc_blocks_per_sm * _num_sms()
     want = max(1, slots // tiles) if tiles < slots else 1      # all blocks resident at once
@@ -538,7 +555,8 @@ def gemm_tc_decode(x, w: torch.Tensor, out: Optional[torch.Tensor],
     x, sumsq, tiles, eps = _row_scale(x)
     M, Kd = x.shape
     N = w.shape[0]
-    splits = splits or tc_decode_splits(N, Kd)
+    groups = tc_token_groups(M, w)
+    splits = splits or tc_decode_splits(N, Kd, groups)
     if swiglu:
         if splits != 1 or bias is not None or N % (2 * SWIGLU_BLOCK):
             raise ValueError("gemm_tc_decode: the fused activation needs one K split, no bias and "
@@ -554,7 +572,8 @@ def gemm_tc_decode(x, w: torch.Tensor, out: Optional[torch.Tensor],
         x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _p(out),
         out.stride(0) if out is not None else N,
         _p(bias), _p(ws), 1 if out_dtype == _F32 else 0, M, N, Kd, splits, tc_max_stages,
-        1 if deferred else 0, 1 if swiglu else 0, sumsq, tiles, eps, _stream()), "gemm_tc_decode")
+        1 if deferred else 0, 1 if swiglu else 0, sumsq, tiles, eps,
+        tc_token_group if groups > 1 else 0, _stream()), "gemm_tc_decode")
     if deferred:
         return SplitSum(ws, bias, out_dtype)
     launch_count += 1 if splits > 1 else 0
@@ -565,8 +584,8 @@ TC_MAX_CLUSTER = 8             # K splits that can share a row tile as one threa
 TC_ROPE_HEAD_DIMS = (16, 32, 64, 128)   # a 128-row tile of the q|k|v product holds whole heads
 
 
-def tc_cluster_splits(n_out: int, k: int) -> int:
-    return min(tc_decode_splits(n_out, k), TC_MAX_CLUSTER)
+def tc_cluster_splits(n_out: int, k: int, groups: int = 1) -> int:
+    return min(tc_decode_splits(n_out, k, groups), TC_MAX_CLUSTER)
 
 
 def gemm_tc_cluster(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -579,12 +598,14 @@ def gemm_tc_cluster(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor
     x, sumsq, tiles, eps = _row_scale(x)
     M, Kd = x.shape
     N = w.shape[0]
-    splits = splits or tc_cluster_splits(N, Kd)
+    groups = tc_token_groups(M, w)
+    splits = splits or tc_cluster_splits(N, Kd, groups)
     if out is None:
         out = torch.empty((M, N), dtype=_BF16, device=x.device)
     L.check(L.core().slb_gemm_tc_cluster_bf16(
         x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), _p(bias),
-        M, N, Kd, splits, _cluster_stages(M), sumsq, tiles, eps, _stream()), "gemm_tc_cluster")
+        M, N, Kd, splits, _cluster_stages(M, groups), sumsq, tiles, eps,
+        tc_token_group if groups > 1 else 0, _stream()), "gemm_tc_cluster")
     return out
 
 
@@ -599,13 +620,15 @@ def gemm_tc_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, bias: Optional[torch.
     cache.  Head sizes in ``TC_ROPE_HEAD_DIMS``.  ``x`` may be ``ScaledRows``."""
     x, sumsq, tiles, eps = _row_scale(x)
     M, Kd = x.shape
-    splits = splits or tc_cluster_splits(w_qkv.shape[0], Kd)
+    groups = tc_token_groups(M, w_qkv)
+    splits = splits or tc_cluster_splits(w_qkv.shape[0], Kd, groups)
     L.check(L.core().slb_gemm_tc_qkv_rope_bf16(
         x.data_ptr(), x.stride(0), w_qkv.data_ptr(), w_qkv.stride(0),
         _p(bias), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], page_size, _num_pages(k_cache), _p(inv_freq), rotary_dim,
         q_out.data_ptr(), q_out.stride(0), _p(k_cache), _p(v_cache), M, num_heads, num_kv_heads,
-        head_dim, Kd, splits, _cluster_stages(M), sumsq, tiles, eps, _stream()), "gemm_tc_qkv_rope")
+        head_dim, Kd, splits, _cluster_stages(M, groups), sumsq, tiles, eps,
+        tc_token_group if groups > 1 else 0, _stream()), "gemm_tc_qkv_rope")
 
 
 tc_cluster_many_token_stages = 3   # ring depth of the cluster products above 16 tokens: their x tiles grow
@@ -615,8 +638,10 @@ tc_cluster_many_token_stages = 3   # ring depth of the cluster products above 16
                                    # q|k|v at 64 tokens)
 
 
-def _cluster_stages(M: int) -> int:
-    return tc_max_stages if M <= 16 else min(tc_max_stages, tc_cluster_many_token_stages)
+def _cluster_stages(M: int, groups: int = 1) -> int:
+    if M <= 16 or (groups > 1 and tc_token_group <= 16):    # (what a block sees)
+        return tc_max_stages
+    return min(tc_max_stages, tc_cluster_many_token_stages)
 
 
 def gemm_tc_resid_norm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
@@ -628,13 +653,15 @@ def gemm_tc_resid_norm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Te
     squares), whose factor 1 / rms the next product applies.  Up to 64 tokens."""
     M, Kd = x.shape
     N = w.shape[0]
-    splits = splits or tc_cluster_splits(N, Kd)
+    groups = tc_token_groups(M, w)
+    splits = splits or tc_cluster_splits(N, Kd, groups)
     z = torch.empty((M, N), dtype=_BF16, device=x.device)
     sumsq = torch.empty((M, -(-N // 128)), dtype=_F32, device=x.device)
     L.check(L.core().slb_gemm_tc_resid_norm_bf16(
         x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _p(bias), resid.data_ptr(),
         resid.stride(0), norm_weight.data_ptr(), z.data_ptr(), z.stride(0), sumsq.data_ptr(),
-        M, N, Kd, splits, _cluster_stages(M), _stream()), "gemm_tc_resid_norm")
+        M, N, Kd, splits, _cluster_stages(M, groups), tc_token_group if groups > 1 else 0,
+        _stream()), "gemm_tc_resid_norm")
     return ScaledRows(z, sumsq, eps, resid, norm_weight)
 
 

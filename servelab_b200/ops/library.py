@@ -43,12 +43,12 @@ _CORE_SIGNATURES = {
     "slb_gemm_simt_bf16": [P, I, P, I, P, I, P, I, I, I, P],
     "slb_gemm_simt_bf16_f32out": [P, I, P, I, P, I, P, I, I, I, P],
     "slb_sample_rows": [P, I, I, I, P, P, P, P, P, P, P, P],
-    "slb_gemm_tc_decode_bf16": [P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, I, P, I, F, P],
+    "slb_gemm_tc_decode_bf16": [P, I, P, I, P, I, P, P, I, I, I, I, I, I, I, I, P, I, F, I, P],
     "slb_split_sum": [P, P, I, P, I, I, I, I, P],
-    "slb_gemm_tc_cluster_bf16": [P, I, P, I, P, I, P, I, I, I, I, I, P, I, F, P],
+    "slb_gemm_tc_cluster_bf16": [P, I, P, I, P, I, P, I, I, I, I, I, P, I, F, I, P],
     "slb_gemm_tc_qkv_rope_bf16": [P, I, P, I, P, P, P, P, I, I, I, P, I, P, I, P, P, I, I, I, I, I, I, I,
-                                  P, I, F, P],
-    "slb_gemm_tc_resid_norm_bf16": [P, I, P, I, P, P, I, P, P, I, P, I, I, I, I, I, P],
+                                  P, I, F, I, P],
+    "slb_gemm_tc_resid_norm_bf16": [P, I, P, I, P, P, I, P, P, I, P, I, I, I, I, I, I, P],
     "slb_add_rmsnorm_parts_bf16": [P, P, I, LL, P, P, P, P, I, I, F, P],
     "slb_qkv_rope_cache_parts_bf16": [P, I, LL, I, P, P, P, P, I, I, I, P, I, P, I, P, P, I, I, I, I, P],
     "slb_gemm_tc_status": [I],

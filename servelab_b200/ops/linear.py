@@ -43,7 +43,7 @@ def _w_ok(w) -> bool:
 
 def _tc_ok(x, w, M):
     limit = tc_max_tokens
-    if M > limit and K.tc_decode_splits(w.shape[0], w.shape[1]) == 1:
+    if M > limit and K.tc_decode_splits(w.shape[0], w.shape[1], K.tc_token_groups(M, w)) == 1:
         limit = max(limit, tc_wide_max_tokens)
     return (0 < M <= min(limit, K.TC_MAX_TOKENS) and _w_ok(w)
             and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
@@ -80,9 +80,12 @@ def _cluster_ok(x, w, M) -> bool:
             and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
         return False
     N, Kd = w.shape
-    want = K.tc_decode_splits(N, Kd)
+    groups = K.tc_token_groups(M, w)
+    want = K.tc_decode_splits(N, Kd, groups)
     if want <= 1:
         return False
+    if groups > 1:
+        M = K.tc_token_group                   # (what a block sees)
     per_block = -(-(-(-Kd // 64)) // min(want, K.TC_MAX_CLUSTER))      # k-blocks of 64 a block streams
     if per_block > cluster_max_kblocks:
         return False
@@ -126,7 +129,8 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, block: int) -> torch.
     inter = w_gate_up.shape[0] // 2
     xt = x.z if isinstance(x, K.ScaledRows) else x
     if (fuse_swiglu and xt.dtype == torch.bfloat16 and block == K.SWIGLU_BLOCK
-            and K.tc_decode_splits(w_gate_up.shape[0], w_gate_up.shape[1]) == 1
+            and K.tc_decode_splits(w_gate_up.shape[0], w_gate_up.shape[1],
+                                   K.tc_token_groups(M, w_gate_up)) == 1
             and _tc_ok(xt, w_gate_up, M)):
         return K.gemm_tc_decode(x, w_gate_up, None, swiglu=True)
     gu = linear(x, w_gate_up)

@@ -37,16 +37,26 @@ def test_decode_steps_run_this_package_s_tensor_core_kernels(shape):
             assert K.tc_decode_splits(2 * inter, h) == 1
         assert L.which_kernel(*_ops(m, vocab, h), out_dtype=torch.float32) == "tc"
     # Above 16 tokens the cluster form stays while a block finishes at most 8 tokens in its
-    # epilogue: 8 K splits (7B: every narrow product) reach 64 tokens, 3 splits (0.5B) reach 24.
+    # epilogue: 8 K splits (7B: every narrow product) reach 64 tokens.  Matrices of at most 20 MB
+    # (every one of the 0.5B shape) are instead read once per group of 16 tokens, so a block
+    # never sees more than 16: they stay on this package's kernels up to 64 tokens too.
     kinds = {m: L.which_kernel(*_ops(m, h, inter)) for m in (8, 32, 64, 65)}
     assert kinds == {8: "tc_cluster", 32: "tc_cluster", 64: "tc_cluster", 65: "vendor"}   # down: 7 to 8 splits
-    for n, k in ((qkv, h), (h, q)):
-        splits = min(K.tc_decode_splits(n, k), K.TC_MAX_CLUSTER)
-        reach = min(64, 8 * splits)
-        assert L.which_kernel(*_ops(max(16, reach), n, k)) == "tc_cluster"
-        assert L.which_kernel(*_ops(max(16, reach) + 1, n, k)) == "vendor"
     if shape == "0.5b":
-        assert L.which_kernel(*_ops(24, qkv, h)) == "tc_cluster" and L.which_kernel(*_ops(25, qkv, h)) == "vendor"
+        for n, k in ((qkv, h), (h, q), (h, inter)):
+            w = _ops(64, n, k)[1]
+            assert K.tc_token_groups(64, w) == 4 and K.tc_token_groups(16, w) == 1
+            assert L.which_kernel(*_ops(64, n, k)) == "tc_cluster" and L.which_kernel(*_ops(65, n, k)) == "vendor"
+        # gate|up: 76 row tiles x 4 groups fill the GPU without a K split: the activation is fused
+        assert L.which_kernel(*_ops(64, 2 * inter, h)) == "tc"
+        assert K.tc_decode_splits(2 * inter, h, 4) == 1
+    else:
+        for n, k in ((qkv, h), (h, q)):
+            assert K.tc_token_groups(64, _ops(64, n, k)[1]) == 1
+            splits = min(K.tc_decode_splits(n, k), K.TC_MAX_CLUSTER)
+            reach = min(64, 8 * splits)
+            assert L.which_kernel(*_ops(max(16, reach), n, k)) == "tc_cluster"
+            assert L.which_kernel(*_ops(max(16, reach) + 1, n, k)) == "vendor"
     if shape == "7b":
         assert L.which_kernel(*_ops(64, qkv, h)) == "tc_cluster" and L.which_kernel(*_ops(64, h, q)) == "tc_cluster"
 
