@@ -100,7 +100,9 @@ extern int slb_pdl_enabled;          // defined once per shared library (SLB_DEF
 //                         memory, while fetches during its epilogue use time in which the
 //                         memory is idle; early starts of only the attention, only the o and
 //                         down products, or norms that release their successor late: 2.85,
-//                         2.95, 2.88 ms);
+//                         2.95, 2.88 ms.  The one exception that pays is in the kernel itself:
+//                         the q|k|v product of a step of few tokens, whose successor -- the
+//                         attention -- has look-ups and old keys to fetch meanwhile);
 //   SLB_FLAG_EVICT_FIRST  what they stream once a step (weights, cached keys and values) is
 //                         fetched with the L2 policy "evict first", so that the few hundred KB of
 //                         activations between the kernels (the float32 residual stream above
