@@ -69,6 +69,31 @@ def test_same_tokens_alone_batched_chunked_and_with_few_pages(model):
     eng.runner.cache.check_invariants()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_with_portions_through_padded_graphs_give_the_same_tokens(model, dtype):
+    """Generation with every step replayed as a graph (steps with prompt portions through graphs
+    captured for padded sizes, at a shape's first use) gives the tokens of generation with every
+    step launched eagerly: small portions, so that many steps mix portions and decoded tokens,
+    and the same engine used twice, so that captured graphs are replayed for other requests."""
+    from servelab_b200.sampling import SamplingParams
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    eager = _engine(model, dtype=dtype, budget=24, cuda_graphs=False)
+    base = [o.outputs[0].token_ids for o in eager.generate(model["prompts"], sp)]
+    eng = _engine(model, dtype=dtype, budget=24, cuda_graphs=True)
+    eng.runner.portion_graph_after = 1
+    for prompts in (model["prompts"], model["prompts"][::-1]):
+        outs = eng.generate(prompts, sp)
+        want = base if prompts is model["prompts"] else base[::-1]
+        if dtype == "float32":
+            assert [o.outputs[0].token_ids for o in outs] == want
+        else:                                               # (other kernels for other token counts)
+            assert [len(o.outputs[0].token_ids) for o in outs] == [len(t) for t in want]
+    assert eng.runner.portion_graph_replays > 0
+    eng.runner.cache.check_invariants()
+    st = eng.stats()
+    assert st["pages_used"] == [0] * len(st["pages_used"])
+
+
 def test_bfloat16_generation_follows_float32_logits(model):
     """bfloat16 may pick another token only where the float32 logits nearly tie."""
     from servelab_b200.sampling import SamplingParams
