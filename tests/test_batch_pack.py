@@ -75,6 +75,46 @@ def test_fresh_contexts(seed):
     check(StepContext.pack(entries, groups, "cpu", min_table_width=width), entries, groups, width)
 
 
+@pytest.mark.parametrize("seed", range(6))
+def test_padded_contexts_fresh_and_overwritten(seed):
+    """The padded form that graphs of steps with prompt portions replay: the step's own arrays first,
+    then padding tokens that belong to the last, empty request (no page in its table, q_len 0),
+    empty requests, rows that repeat row 0; work lists of attention tiles of a fixed length whose
+    surplus entries name the empty request.  Overwritten in place three times with other steps."""
+    rng = random.Random(100 + seed)
+    groups = 1 + seed % 2
+    width = 64
+    ctx = None
+    for _ in range(4):
+        entries = random_entries(rng, groups, page=8, count=rng.randint(1, 6))
+        T = sum(len(e.tokens) for e in entries)
+        R = sum(len(e.want) for e in entries)
+        pad = (512, 8, 32)
+        ctx = StepContext.pack(entries, groups, "cpu", min_table_width=width, pad=pad, into=ctx)
+        tok, pos, seq, cu, ctx_len, slots, rows, tables = expected(entries, groups, width)
+        S = len(entries)
+        assert (ctx.num_tokens, ctx.num_seqs, ctx.num_logit_rows) == pad and ctx.real_sizes == (T, S, R)
+        assert ctx.token_ids.tolist() == tok + [0] * (512 - T)
+        assert ctx.positions.tolist() == pos + [0] * (512 - T)
+        assert ctx.seq_of_token.tolist() == seq + [7] * (512 - T)
+        assert ctx.cu_q.tolist() == cu + [T] * (8 - S)
+        assert ctx.ctx_len.tolist() == ctx_len + [0] * (8 - S)
+        assert ctx.logit_rows.tolist() == rows + [0] * (32 - R)
+        for g in range(groups):
+            got = ctx.block_tables[g].tolist()
+            assert got[:S] == tables[g] and all(v == -1 for row in got[S:] for v in row)
+        assert not ctx.decode_only and ctx.q_lens == [len(e.tokens) for e in entries] + [0] * (8 - S)
+        for group_size, rows_per_tile in ((2, 16), (7, 128)):
+            tile_seq, tile_row0, n = ctx.attention_tiles(group_size, rows_per_tile)
+            assert n == -(-512 * group_size // rows_per_tile) + 8 and len(tile_seq) == n
+            want = [(s, r0) for s, e in enumerate(entries)
+                    for r0 in range(0, len(e.tokens) * group_size, rows_per_tile)]
+            got = list(zip(tile_seq.tolist(), tile_row0.tolist()))
+            assert got[:len(want)] == want and all(t == (7, 0) for t in got[len(want):])
+    with pytest.raises(ValueError):
+        StepContext.pack(entries, groups, "cpu", min_table_width=width, pad=(512, len(entries), 32))
+
+
 def test_entries_without_stamps_and_empty_want():
     e = [BatchEntry(tokens=[4, 5, 6], start=2, want=(), block_tables=[[7]], state_slot=3),
          BatchEntry(tokens=[9], start=40, want=(0,), block_tables=[[1, 2, 3, 4, 5, 6]], state_slot=0)]
