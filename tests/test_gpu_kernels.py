@@ -940,6 +940,47 @@ def test_gemm_tcgen05_product_with_residual_add_and_norm(M, N, Kd, splits):
     assert K().gemm_tc_status(True) == 0
 
 
+@pytest.mark.parametrize("M", [8, 16, 40])
+def test_cluster_products_of_a_layer_launched_back_to_back_many_times(M):
+    """The products of a decode layer one after the other, 150 times, with programmatic dependent
+    launch: blocks of the next product become resident and fill their shared memory while the
+    blocks of a cluster still read one another's (the closing barrier of a cluster arrives
+    relaxed, after the remote values have been used).  Every round must give bit for bit the
+    result of the first; no bounded wait may give up."""
+    h, Hq, Hkv, D, inter, ps = 1024, 8, 2, 128, 2816, 16
+    g = torch.Generator().manual_seed(M)
+    def w(n, k):
+        return (torch.randn(n, k, generator=g) / math.sqrt(k)).bfloat16().to(DEV)
+    w_qkv, w_o, w_gu, w_down = w((Hq + 2 * Hkv) * D, h), w(h, Hq * D), w(2 * inter, h), w(h, inter)
+    bias = torch.randn((Hq + 2 * Hkv) * D, generator=g).to(DEV)
+    nw = (1.0 + 0.1 * torch.randn(h, generator=g)).to(DEV)
+    inv = P.rope_inv_freq(D, 10000.0).to(DEV)
+    x0 = torch.randn(M, h, generator=g).bfloat16().to(DEV)
+    attn = torch.randn(M, Hq * D, generator=g).bfloat16().to(DEV)
+    resid0 = torch.randn(M, h, generator=g).to(DEV)
+    positions, seq = i32(list(range(100, 100 + M))), i32([0] * M)
+    pages = (100 + M) // ps + 1
+    table = i32([list(range(pages))])
+    first = None
+    for it in range(150):
+        resid = resid0.clone()
+        q = torch.empty(M, Hq * D, device=DEV, dtype=torch.bfloat16)
+        kc, vc = _paged(pages, Hkv, ps, D, torch.bfloat16)
+        K().gemm_tc_qkv_rope(x0, w_qkv, bias, positions, seq, table, ps, inv, D, q, kc, vc, Hq, Hkv, D)
+        rows = K().gemm_tc_resid_norm(attn, w_o, None, resid, nw, 1e-6)
+        act = K().gemm_tc_decode(rows, w_gu, None, splits=1, swiglu=True)
+        rows2 = K().gemm_tc_resid_norm(act, w_down, None, resid, nw, 1e-6)
+        out = K().gemm_tc_cluster(rows2, w_qkv, None, bias)
+        got = (q, kc, rows.z, rows.sumsq, act, rows2.z, rows2.sumsq, resid, out)
+        if first is None:
+            first = [t.clone() for t in got]
+            assert all(bool(torch.isfinite(t.float()).all()) for t in first)
+        elif it % 10 == 9 or it < 5:
+            for a, b in zip(got, first):
+                assert torch.equal(a, b), f"round {it}"
+    assert K().gemm_tc_status(True) == 0
+
+
 @pytest.mark.parametrize("H,Hkv,D,rot,hidden", [(28, 4, 128, 128, 3584), (14, 2, 64, 64, 896),
                                                 (6, 2, 64, 32, 72), (5, 1, 32, 32, 160),
                                                 (3, 3, 16, 0, 64), (9, 1, 128, 64, 1024)])
