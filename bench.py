@@ -391,8 +391,12 @@ def main(argv=None) -> int:
                 torch.cuda.profiler.stop()
             times.append(start.elapsed_time(stop))
             if args.profile_steps and i == 4:
-                with StepProfile() as prof:
-                    runner.step([entry])
+                saved, runner.cuda_graphs = runner.cuda_graphs, False    # (launched one by one)
+                try:
+                    with StepProfile() as prof:
+                        runner.step([entry])
+                finally:
+                    runner.cuda_graphs = saved
                 note("per-kernel times of the 2,048-token prefill:\n" + prof.render())
             runner.cache.release(rid)
         ms = sorted(times[2:])[len(times[2:]) // 2]

@@ -88,7 +88,7 @@ class ModelRunner:
         # host 0.2 ms of launches when run eagerly, which binds the steps of a small model.
         # A shape is captured when it comes up the second time; at most
         # ``max_portion_graphs`` are kept (least recently used first out).
-        self.portion_graphs = cuda_graphs
+        self.portion_graphs = True        # (only with ``cuda_graphs``)
         self.max_portion_graph_tokens = 2048
         self.max_portion_graphs = 24
         self.portion_graph_after = 2      # times a shape is asked for before it is captured
@@ -155,7 +155,7 @@ class ModelRunner:
             return self._step_graph(entries, token_ids_from)
         if token_ids_from is not None:
             raise ValueError("token ids from the device need a step that replays a graph")
-        if self.portion_graphs and self._graph_safe and not self.storage.state_layers:
+        if self.cuda_graphs and self.portion_graphs and self._graph_safe and not self.storage.state_layers:
             pad = self._portion_pad(entries)
             if pad is not None:
                 hit = self._portion_graphs.get(pad)
