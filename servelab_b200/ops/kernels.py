@@ -373,11 +373,13 @@ def decode_attention_split(ctx, q, k_cache, v_cache, out, block_table, num_heads
 
 decode_ws_stages = 3           # depth of the kernel's shared-memory ring (2..4)
 decode_ws_force_splits = 0     # measurements: launch this many splits instead of the choice below
-# The kernel picks each request's number of splits itself, from the request's own length:
-# one while it has at most `decode_ws_unsplit_tiles` 64-key tiles, else about
-# `decode_ws_split_coef` * sqrt(tiles) tiles per split, and never more splits than were
-# launched.  Fitted to measurements on a B200 at head size 128: a tile costs a block about
-# 0.45 us, a split 3 us once plus 1 us per eight splits the last block combines.
+# The kernel picks each request's number of splits itself, from the request's own length: one
+# while it has at most `decode_ws_unsplit_tiles` 64-key tiles, and never more splits than were
+# launched.  In the cluster form (the default) a split has two tiles at least, and a request
+# takes more splits than one cluster holds only when that saves a block four tiles or more
+# (a tile costs a block about 0.8 us while the GPU is not full, a second level of combining
+# about 3 us).  In the arrival-counter form (the twin) a split has about
+# `decode_ws_split_coef` * sqrt(tiles) tiles: there one block combines every split.
 decode_ws_split_coef = 0.8
 decode_ws_unsplit_tiles = 6    # (us at 256 / 512 keys, batch 8: 5.4 / 8.4 with 12, 5.4 / 6.0 with 6, 5.9 / 6.0 with 3)
 

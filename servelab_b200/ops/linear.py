@@ -22,7 +22,8 @@ tc_max_tokens = 16         # up to this many tokens the tcgen05 weight-streaming
                            # product's shape (above: see ``cluster_max_tokens_per_block``)
 tc_wide_max_tokens = 64    # ... and up to this many for products wide enough to need no K split
                            # (gate|up: 45.5 us against the library's 47.7 at 64 tokens)
-# Hand the K-split partial sums of a decode-step product to the kernel that consumes the
+# (The plain twin of the cluster products, taken when ``cluster_sums`` is off.)  Hand the
+# K-split partial sums of a decode-step product to the kernel that consumes the
 # result instead of reducing them in a kernel of their own, per kind of consumer.  "rope":
 # the q/k/v kernel takes them with one block per (head, token).  "norm": the norm takes
 # them with a cluster of blocks per row.  Each replaces the reduction kernel and the
