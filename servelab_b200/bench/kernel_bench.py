@@ -362,6 +362,10 @@ def main(argv=None) -> int:
     ap.add_argument("--fused-only", action="store_true",
                     help="products: only the o and down products with add and norm in their epilogue")
     ap.add_argument("--no-twins", action="store_true", help="skip the plain twins of the attention kernels")
+    ap.add_argument("--force-splits", type=int, default=0,
+                    help="decode attention: launch this many key splits instead of the launcher's choice")
+    ap.add_argument("--no-cluster", action="store_true",
+                    help="decode attention: combine the splits through the arrival counter, not clusters")
     ap.add_argument("--peaks", default=DEFAULT_PEAKS, help="JSON file with hbm_gbs and bf16_tflops")
     ap.add_argument("--markdown", action="store_true")
     args = ap.parse_args(argv)
@@ -369,6 +373,8 @@ def main(argv=None) -> int:
     peaks = W.load_peaks(args.peaks)
     from ..ops import kernels as K
     K.require_cuda()
+    K.decode_ws_force_splits = args.force_splits
+    K.decode_ws_cluster = not args.no_cluster
     device = "cuda:0"
     shape = SHAPES[args.shape]
     groups = [g for g in args.only.split(",") if g] or list(GROUPS)
