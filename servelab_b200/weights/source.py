@@ -76,24 +76,54 @@ class WeightSource:
         raise NotImplementedError
 
 
+class _StateDictFile:
+    """A ``pytorch_model.bin``: a state dict written by ``torch.save`` (the reference's tests
+    write their tiny checkpoints so, tests/helpers_tiny_model.py:55).  Read with
+    ``weights_only=True`` (tensors only, nothing is unpickled into code) and memory-mapped."""
+
+    def __init__(self, path: str):
+        try:
+            self._tensors = torch.load(path, map_location="cpu", weights_only=True, mmap=True)
+        except (RuntimeError, ValueError):                 # (an archive written without mmap support)
+            self._tensors = torch.load(path, map_location="cpu", weights_only=True)
+        if not isinstance(self._tensors, dict) or not all(
+                isinstance(v, torch.Tensor) for v in self._tensors.values()):
+            raise ValueError(f"{path}: not a state dict of tensors")
+
+    def names(self):
+        return list(self._tensors)
+
+    def shape(self, name):
+        return tuple(self._tensors[name].shape)
+
+    def dtype(self, name):
+        return self._tensors[name].dtype
+
+    def read(self, name):
+        return self._tensors[name]
+
+
 class FolderSource(WeightSource):
-    """``model.safetensors`` or the shards named by ``model.safetensors.index.json``."""
+    """``model.safetensors``, the shards named by ``model.safetensors.index.json``, or a
+    ``pytorch_model.bin`` state dict (in that order)."""
 
     def __init__(self, folder: str):
         self.where = folder
         index = os.path.join(folder, "model.safetensors.index.json")
         single = os.path.join(folder, "model.safetensors")
-        self._file_of: Dict[str, SafetensorsFile] = {}
+        self._file_of: Dict[str, object] = {}
         if os.path.isfile(single):
             files = [SafetensorsFile(single)]
         elif os.path.isfile(index):
             with open(index) as f:
                 shard_names = sorted(set(json.load(f)["weight_map"].values()))
             files = [SafetensorsFile(os.path.join(folder, s)) for s in shard_names]
+        elif os.path.isfile(os.path.join(folder, "pytorch_model.bin")):
+            files = [_StateDictFile(os.path.join(folder, "pytorch_model.bin"))]
         else:
             raise FileNotFoundError(
-                f"model folder {folder!r} has neither model.safetensors nor "
-                f"model.safetensors.index.json")
+                f"model folder {folder!r} has neither model.safetensors, "
+                f"model.safetensors.index.json nor pytorch_model.bin")
         for sf in files:
             for n in sf.names():
                 self._file_of[n] = sf

@@ -120,6 +120,30 @@ def test_sharded_folder_and_corrupt_header(tmp_path):
         FolderSource(str(tmp_path / "empty"))
 
 
+def test_a_state_dict_checkpoint_is_read_by_name_like_a_safetensors_one(tmp_path):
+    """``pytorch_model.bin`` (a state dict from ``torch.save``, the form the reference's tests
+    write): the same tensors by the same names, checked and loaded like a safetensors folder;
+    a file that is no dict of tensors is refused."""
+    folder = H.make_model(str(tmp_path / "st"), H.TINY_A, 3)
+    tensors = plain_model.read_safetensors(os.path.join(folder, "model.safetensors"))
+    other = tmp_path / "bin"
+    other.mkdir()
+    torch.save(dict(tensors), str(other / "pytorch_model.bin"))
+    (other / "config.json").write_text(open(os.path.join(folder, "config.json")).read())
+    spec, decls = _decls(H.TINY_A)
+    src = FolderSource(str(other))
+    check_source(src, decls, spec.ignored_suffixes)
+    assert sorted(src.names()) == sorted(tensors)
+    for name, t in tensors.items():
+        assert src.shape(name) == tuple(t.shape) and src.stored_dtype(name) == t.dtype
+        assert torch.equal(src.read(name), t)
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    torch.save([1, 2, 3], str(bad / "pytorch_model.bin"))
+    with pytest.raises(ValueError, match="state dict"):
+        FolderSource(str(bad))
+
+
 def _raw_file(path, header: dict, payload: bytes):
     import struct
     blob = json.dumps(header).encode()
